@@ -1,0 +1,133 @@
+"""The five benchmark models as layer lists, and their seeded synthetic inputs.
+
+Weights are Glorot-uniform from a seed and uploaded through the flat parameter buffer on
+both sides of every comparison: the reference's own constructors leave the parameters of
+MultiHeadAttention / TransformerBlock at zero (their Build re-binds sub-layers to fresh
+buffers, internal/layer/transformer.go:367-379, :1035-1056), so initial weights are always
+supplied by the caller.  Flat layout = Network.initBuffers (internal/net/net.go:91-127)."""
+import math
+
+import numpy as np
+
+from . import descriptors as D
+
+
+def mlp(in_size=784, hidden=128, classes=10):
+    return [D.Dense(in_size, hidden, D.RELU), D.Dense(hidden, classes, D.SOFTMAX)], D.CROSS_ENTROPY
+
+
+def cnn(hw=32, c0=3, c1=16, c2=32, classes=10):
+    h2, h4 = hw // 2, hw // 4
+    return [D.Conv2D(c0, c1, 3, 1, 1, D.RELU, hw, hw), D.MaxPool2D(c1, 2, 2, 0, hw, hw),
+            D.Conv2D(c1, c2, 3, 1, 1, D.RELU, h2, h2), D.MaxPool2D(c2, 2, 2, 0, h2, h2),
+            D.Flatten(), D.Dense(c2 * h4 * h4, classes, D.SOFTMAX)], D.CROSS_ENTROPY
+
+
+def recurrent(in_size=16, hidden=128, seq_len=64):
+    return [D.SequenceUnrollerLSTM(in_size, hidden, seq_len, False), D.Dense(hidden, 1, D.LINEAR)], D.MSE
+
+
+def transformer(vocab, dim, seq_len, heads, ff_dim, n_blocks):
+    layers = [D.Embedding(vocab, dim, seq_len), D.PositionalEncoding(seq_len, dim)]
+    layers += [D.TransformerBlock(dim, heads, seq_len, ff_dim, True) for _ in range(n_blocks)]
+    layers += [D.CLSPooling(seq_len, dim), D.Dense(dim, vocab, D.LOGSOFTMAX)]
+    return layers, D.CROSS_ENTROPY
+
+
+CONFIGS = {
+    # name: (builder, kwargs, batch, lr)
+    "mlp": (mlp, {}, 64, 1e-3),
+    "cnn": (cnn, {}, 128, 1e-3),
+    "lstm": (recurrent, {}, 256, 1e-3),
+    "transformer_small": (transformer, dict(vocab=8192, dim=256, seq_len=128, heads=8, ff_dim=1024, n_blocks=4), 64, 3e-4),
+    "transformer_large": (transformer, dict(vocab=32000, dim=1024, seq_len=512, heads=16, ff_dim=4096, n_blocks=8), 256, 1e-4),
+}
+SEEDS = {"mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
+
+
+def build(name, **override):
+    fn, kw, batch, lr = CONFIGS[name]
+    kw = dict(kw)
+    kw.update(override)
+    layers, loss = fn(**kw)
+    return layers, loss, batch, lr
+
+
+def _glorot(rng, shape, fan_in, fan_out):
+    a = math.sqrt(6.0 / (fan_in + fan_out))
+    return rng.uniform(-a, a, size=shape).astype(np.float32)
+
+
+def _dense_params(rng, i, o):
+    return [_glorot(rng, (o, i), i, o).ravel(), np.zeros(o, np.float32)]
+
+
+def init_params(layers, rng):
+    """Flat parameter vector in the reference's layout, Glorot-uniform weights, zero biases,
+    LSTM forget-gate bias 1 (lstm.go:191-193), LayerNorm gamma 1 / beta 0, Embedding
+    U(+-sqrt(3/d)) (embedding.go:50), positional table U(+-sqrt(1/d)) (transformer.go:60)."""
+    parts = []
+    for l in layers:
+        k = l.kind
+        if k == D.DENSE:
+            parts += _dense_params(rng, l.in_size, l.out_size)
+        elif k == D.CONV2D:
+            kk = l.kernel * l.kernel
+            parts += [_glorot(rng, (l.out_size, l.in_size, l.kernel, l.kernel), l.in_size * kk, l.out_size * kk).ravel(),
+                      np.zeros(l.out_size, np.float32)]
+        elif k == D.LSTM_UNROLLED:
+            H, i = l.out_size, l.in_size
+            b = np.zeros(4 * H, np.float32)
+            b[H:2 * H] = 1.0
+            parts += [_glorot(rng, (4 * H, i), i, H).ravel(), _glorot(rng, (4 * H, H), H, H).ravel(), b]
+        elif k == D.EMBEDDING:
+            a = math.sqrt(3.0 / l.out_size)
+            parts.append(rng.uniform(-a, a, size=l.in_size * l.out_size).astype(np.float32))
+        elif k == D.POSENC:
+            a = math.sqrt(1.0 / l.dim)
+            parts.append(rng.uniform(-a, a, size=l.seq_len * l.dim).astype(np.float32))
+        elif k == D.TRANSFORMER_BLOCK:
+            d, f = l.dim, l.ff_dim
+            for _ in range(4):
+                parts += _dense_params(rng, d, d)
+            parts += [np.ones(d, np.float32), np.zeros(d, np.float32)] * 2
+            parts += _dense_params(rng, d, f)
+            parts += _dense_params(rng, f, d)
+        elif k == D.LAYERNORM:
+            parts += [np.ones(l.dim, np.float32), np.zeros(l.dim, np.float32)]
+    return np.concatenate(parts) if parts else np.zeros(0, np.float32)
+
+
+def make_inputs(name, layers, batch, rng):
+    """Seeded synthetic batch with the shapes and value distributions the benchmark names."""
+    first, last = layers[0], layers[-1]
+    if first.kind == D.EMBEDDING:
+        T = first.seq_len
+        x = rng.integers(0, first.in_size, size=(batch, T)).astype(np.float32)
+        tgt = rng.integers(0, last.out_size, size=batch)
+        y = np.zeros((batch, last.out_size), np.float32)
+        y[np.arange(batch), tgt] = 1.0
+    elif first.kind == D.LSTM_UNROLLED:
+        x = rng.standard_normal((batch, first.seq_len * first.in_size)).astype(np.float32)
+        y = rng.standard_normal((batch, last.out_size)).astype(np.float32)
+    elif first.kind == D.CONV2D:
+        x = rng.standard_normal((batch, first.in_size * first.in_h * first.in_w)).astype(np.float32)
+        tgt = rng.integers(0, last.out_size, size=batch)
+        y = np.zeros((batch, last.out_size), np.float32)
+        y[np.arange(batch), tgt] = 1.0
+    else:
+        x = rng.random((batch, first.in_size), dtype=np.float32)
+        tgt = rng.integers(0, last.out_size, size=batch)
+        y = np.zeros((batch, last.out_size), np.float32)
+        y[np.arange(batch), tgt] = 1.0
+    return x, y
+
+
+def make_case(name, batch=None, seed=None, **override):
+    """(layers, loss, params, x, y, lr) for a named config; draw order weights -> inputs -> labels."""
+    layers, loss, b, lr = build(name, **override)
+    batch = batch or b
+    rng = np.random.Generator(np.random.PCG64(seed if seed is not None else SEEDS[name]))
+    params = init_params(layers, rng)
+    x, y = make_inputs(name, layers, batch, rng)
+    return layers, loss, params, x, y, lr

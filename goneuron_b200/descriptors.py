@@ -1,0 +1,77 @@
+"""Layer descriptors: the Python mirror of `gn_layer_desc` (include/goneuron_cuda.h) and
+constructors named after the reference's (goneuron/goneuron.go:59-340, internal/layer)."""
+import ctypes as C
+
+# gn_layer_kind
+DENSE, CONV2D, MAXPOOL2D, FLATTEN, LSTM_UNROLLED, EMBEDDING, POSENC, TRANSFORMER_BLOCK, CLS_POOLING, LAYERNORM = range(1, 11)
+# gn_activation
+LINEAR, RELU, SIGMOID, TANH, SOFTMAX, LOGSOFTMAX = range(6)
+# gn_loss_kind
+MSE, CROSS_ENTROPY = 0, 1
+
+
+class LayerDesc(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "kind", "activation", "in_size", "out_size", "kernel", "stride", "padding", "in_h", "in_w",
+        "seq_len", "dim", "heads", "ff_dim", "causal", "return_seq", "reserved")]
+
+    def __repr__(self):
+        return "LayerDesc(" + ", ".join(f"{n}={getattr(self, n)}" for n, _ in self._fields_ if getattr(self, n)) + ")"
+
+
+def layers_to_array(layers):
+    arr = (LayerDesc * len(layers))()
+    for i, l in enumerate(layers):
+        arr[i] = l
+    return arr
+
+
+def Dense(in_size, out_size, activation=LINEAR):
+    """layer.NewDense(in, out, act) -- internal/layer/layer.go:224-340."""
+    return LayerDesc(kind=DENSE, in_size=in_size, out_size=out_size, activation=activation)
+
+
+def Conv2D(in_channels, out_channels, kernel, stride, padding, activation, in_h, in_w):
+    """layer.NewConv2D(inC, outC, k, stride, pad, act) + SetInputDimensions(h, w) -- conv2d.go:60-140, :686-691."""
+    return LayerDesc(kind=CONV2D, in_size=in_channels, out_size=out_channels, kernel=kernel, stride=stride,
+                     padding=padding, activation=activation, in_h=in_h, in_w=in_w)
+
+
+def MaxPool2D(in_channels, kernel, stride, padding, in_h, in_w):
+    """layer.NewMaxPool2D(inC, k, stride, pad) -- maxpool2d.go:46."""
+    return LayerDesc(kind=MAXPOOL2D, in_size=in_channels, kernel=kernel, stride=stride, padding=padding, in_h=in_h, in_w=in_w)
+
+
+def Flatten():
+    """layer.NewFlatten() -- reshape.go:64-96."""
+    return LayerDesc(kind=FLATTEN)
+
+
+def SequenceUnrollerLSTM(in_size, hidden, seq_len, return_seq=False):
+    """layer.NewSequenceUnroller(layer.NewLSTM(in, hidden), T, returnSeq) -- unroller.go:57, lstm.go:276."""
+    return LayerDesc(kind=LSTM_UNROLLED, in_size=in_size, out_size=hidden, seq_len=seq_len, return_seq=int(return_seq))
+
+
+def Embedding(vocab, dim, seq_len=0):
+    """layer.NewEmbedding(vocab, dim) -- embedding.go:30-60."""
+    return LayerDesc(kind=EMBEDDING, in_size=vocab, out_size=dim, seq_len=seq_len)
+
+
+def PositionalEncoding(seq_len, dim):
+    """layer.NewPositionalEncoding(T, dim) -- transformer.go:12-84."""
+    return LayerDesc(kind=POSENC, seq_len=seq_len, dim=dim)
+
+
+def TransformerBlock(dim, heads, seq_len, ff_dim, causal=True):
+    """layer.NewTransformerBlock(dim, heads, T, ffDim, causal) -- transformer.go:859-1279."""
+    return LayerDesc(kind=TRANSFORMER_BLOCK, dim=dim, heads=heads, seq_len=seq_len, ff_dim=ff_dim, causal=int(causal))
+
+
+def CLSPooling(seq_len, dim):
+    """layer.NewCLSPooling(T, dim) -- transformer.go:1647-1777."""
+    return LayerDesc(kind=CLS_POOLING, seq_len=seq_len, dim=dim)
+
+
+def LayerNorm(dim):
+    """layer.NewLayerNorm(dim, 1e-5, true) applied to consecutive rows of `dim` -- layernorm.go:193-441."""
+    return LayerDesc(kind=LAYERNORM, dim=dim)

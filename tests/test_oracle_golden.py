@@ -1,0 +1,111 @@
+"""Pins the CPU checker (float instantiation) to the reference's own golden vectors and
+known-answer tables (tests/golden/reference_fixtures.json, made by make_reference_fixtures.py).
+Tolerances are the reference's: internal/validation/pytorch_validation_test.go:164-344."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from goneuron_b200 import descriptors as D
+
+FX = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_fixtures.json")))
+
+
+@pytest.mark.parametrize("case", ["dense_simple", "dense_batch"])
+def test_dense_forward(oracle, case):
+    f = FX[case]
+    out = oracle.gemm_nt(np.array(f["input"]), np.array(f["weights"]), np.array(f["biases"]))
+    np.testing.assert_allclose(out, np.array(f["output"], np.float32), atol=1e-4, rtol=0)
+    # the same numbers through a one-layer Network forward
+    layers = [D.Dense(4, 3, D.LINEAR)]
+    st = oracle.OracleState(layers, D.MSE, np.concatenate([np.array(f["weights"], np.float32).ravel(), np.array(f["biases"], np.float32)]))
+    np.testing.assert_allclose(st.forward_batch(np.array(f["input"]), precision=32), np.array(f["output"], np.float32), atol=1e-4, rtol=0)
+
+
+def test_dense_simple_literal():
+    # the value the reference documents for dense_simple
+    np.testing.assert_allclose(np.array(FX["dense_simple"]["output"]).ravel(), [3.0674953, 0.60423696, 1.6263502], rtol=1e-6)
+
+
+@pytest.mark.parametrize("name,act,tol", [("relu", D.RELU, 1e-5), ("sigmoid", D.SIGMOID, 1e-5), ("tanh", D.TANH, 1e-5)])
+def test_scalar_activations(oracle, name, act, tol):
+    f = FX["activation_" + name]
+    np.testing.assert_allclose(oracle.activation(act, np.array(f["input"]).ravel()), np.array(f["output"], np.float32).ravel(), atol=tol, rtol=0)
+
+
+@pytest.mark.parametrize("name,act", [("softmax", D.SOFTMAX), ("log_softmax", D.LOGSOFTMAX)])
+def test_row_activations_fixture(oracle, name, act):
+    f = FX["activation_" + name]
+    for row, exp in zip(f["input"], f["output"]):
+        np.testing.assert_allclose(oracle.activation(act, np.array(row)), np.array(exp, np.float32), atol=1e-4, rtol=0)
+
+
+@pytest.mark.parametrize("table,act", [("softmax_table", D.SOFTMAX), ("log_softmax_table", D.LOGSOFTMAX)])
+def test_row_activations_tables(oracle, table, act):
+    for x, exp in FX[table]:
+        np.testing.assert_allclose(oracle.activation(act, np.array(x, np.float32)), np.array(exp, np.float32), atol=1e-6, rtol=0)
+
+
+def test_mse(oracle):
+    f = FX["loss_mse"]
+    assert abs(oracle.loss(D.MSE, f["y_pred"], f["y_true"]) - f["loss"][0]) < 1e-5
+    for p, y, exp in FX["mse_table"]:
+        assert abs(oracle.loss(D.MSE, p, y) - exp) < 1e-6
+    for p, y, exp in FX["mse_grad_table"]:
+        np.testing.assert_allclose(oracle.loss_grad(D.MSE, p, y), np.array(exp, np.float32), atol=1e-6, rtol=0)
+
+
+def test_cross_entropy_tables(oracle):
+    for p, y, lo, hi in FX["ce_range_table"]:
+        v = oracle.loss(D.CROSS_ENTROPY, p, y)
+        assert lo <= v <= hi
+    for p, y, exp in FX["ce_grad_table"]:
+        np.testing.assert_allclose(oracle.loss_grad(D.CROSS_ENTROPY, p, y), np.array(exp, np.float32), atol=1e-6, rtol=0)
+
+
+def test_logsoftmax_against_torch_logits_ce(oracle):
+    # torch.nn.CrossEntropyLoss over logits = mean of -log_softmax(logits)[target]
+    f = FX["loss_cross_entropy_logits"]
+    vals = [-oracle.activation(D.LOGSOFTMAX, np.array(row))[int(t)] for row, t in zip(f["logits"], f["targets"])]
+    assert abs(np.mean(vals) - f["loss"][0]) < 1e-5
+
+
+def test_cross_entropy_of_logsoftmax_is_constant(oracle):
+    # every log-probability is <= 0 < 1e-10, so the clipped loss is -log(1e-10) per one-hot sample
+    lp = oracle.activation(D.LOGSOFTMAX, np.array([0.3, -1.0, 2.0], np.float32))
+    assert abs(oracle.loss(D.CROSS_ENTROPY, lp, [0, 1, 0]) - 23.02585) < 1e-4
+
+
+def test_adam_single_step(oracle):
+    f = FX["optimizer_adam_step"]
+    z = np.zeros(3, np.float32)
+    # a fresh optimiser called directly (no NewStep) uses exponent t = 1: opt.go:237
+    p, m, v = oracle.adam(f["param"], f["grad"], z, z, f["lr"][0], f["beta1"][0], f["beta2"][0], f["eps"][0], 1)
+    np.testing.assert_allclose(p, np.array(f["param_updated"], np.float32), atol=1e-3, rtol=0)   # reference tolerance
+    np.testing.assert_allclose(p, np.array(f["param_updated"], np.float32), atol=2e-6, rtol=0)   # and much tighter
+    np.testing.assert_allclose(m, 0.1 * np.array(f["grad"], np.float32), rtol=1e-6)
+
+
+def test_adam_first_network_step_uses_t2(oracle):
+    # Network.Step calls NewStep() (counter -> 1) and StepInPlace uses counter + 1
+    layers = [D.Dense(2, 1, D.LINEAR)]
+    w = np.array([0.5, -0.25, 0.1], np.float32)
+    st = oracle.OracleState(layers, D.MSE, w, lr=1e-2)
+    x, y = np.array([[1.0, 2.0]], np.float32), np.array([[0.7]], np.float32)
+    st.train_batch(x, y, precision=32)
+    g = st.grads.copy()
+    p2, _, _ = oracle.adam(w, g, np.zeros(3), np.zeros(3), 1e-2, 0.9, 0.999, 1e-8, 2)
+    np.testing.assert_array_equal(st.params, p2)
+    assert st.timestep == 1
+    pred = w[0] * 1 + w[1] * 2 + w[2]
+    np.testing.assert_allclose(g, 2 * (pred - 0.7) * np.array([1, 2, 1]), rtol=1e-6)
+
+
+def test_conv2d_simple(oracle):
+    f = FX["conv2d_simple"]
+    layers = [D.Conv2D(1, 1, f["kernel"], f["stride"], f["padding"], D.LINEAR, 3, 3)]
+    params = np.array([f["weight_fill"]] * 4 + [f["bias_fill"]], np.float32)
+    st = oracle.OracleState(layers, D.MSE, params)
+    out = st.forward_batch(np.array(f["input"], np.float32).reshape(1, 9), precision=32)
+    np.testing.assert_allclose(out.ravel(), np.array(f["output"], np.float32).ravel(), atol=1e-4, rtol=0)
