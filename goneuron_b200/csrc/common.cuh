@@ -1,0 +1,107 @@
+// common.cuh -- context, error handling and launch bookkeeping shared by all kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "../../include/goneuron_cuda.h"
+
+namespace gn {
+
+// Per-thread message of the most recent failure (gn_last_error()).
+inline std::string& last_error() { thread_local std::string e; return e; }
+inline int fail(int code, const char* fmt, ...) {
+  char buf[1024]; va_list ap; va_start(ap, fmt); vsnprintf(buf, sizeof buf, fmt, ap); va_end(ap);
+  last_error() = buf; return code;
+}
+
+#define GN_CUDA(call)                                                                        \
+  do { cudaError_t e_ = (call); if (e_ != cudaSuccess)                                       \
+      return gn::fail(e_ == cudaErrorMemoryAllocation ? GN_ERR_OOM : GN_ERR_CUDA, "%s failed at %s:%d: %s", #call, __FILE__, __LINE__, cudaGetErrorString(e_)); } while (0)
+#define GN_TRY(call) do { int rc_ = (call); if (rc_ != GN_OK) return rc_; } while (0)
+
+struct NcclApi;   // resolved at run time from libnccl.so.2 (nccl_dl.cuh)
+
+struct Ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  int rank = 0, world = 1;
+  void* comm = nullptr;            // ncclComm_t
+  NcclApi* nccl = nullptr;
+  int sm_count = 148;
+  int64_t launches = 0;            // kernels launched by this library on this context
+  // contraction profiling (gn_model_set_profiling)
+  int profile = 0;
+  double gemm_flops = 0; float gemm_ms = 0; int64_t gemm_launches = 0;
+  std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev_pool; size_t ev_used = 0;
+  int* d_status = nullptr;         // device word set by kernels whose bounded waits gave up
+  bool tc_ok = false;              // tcgen05 engine usable (driver entry point for tensor maps found)
+  void* encode_tiled = nullptr;    // cuTensorMapEncodeTiled
+};
+
+inline unsigned cdiv(long a, long b) { return (unsigned)((a + b - 1) / b); }
+
+// Every kernel launch of the library goes through this macro so that the launch count is exact.
+#define GN_LAUNCH(ctx, kernel, grid, block, smem, ...)                         \
+  do { kernel<<<(grid), (block), (smem), (ctx)->stream>>>(__VA_ARGS__); (ctx)->launches++; } while (0)
+
+inline int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(GN_ERR_CUDA, "kernel launch failed (%s): %s", what, cudaGetErrorString(e));
+  return GN_OK;
+}
+
+// Owning device buffer.
+struct DevBuf {
+  float* p = nullptr; size_t n = 0;
+  DevBuf() {}
+  DevBuf(const DevBuf&) = delete; DevBuf& operator=(const DevBuf&) = delete;
+  DevBuf(DevBuf&& o) noexcept : p(o.p), n(o.n) { o.p = nullptr; o.n = 0; }
+  DevBuf& operator=(DevBuf&& o) noexcept { release(); p = o.p; n = o.n; o.p = nullptr; o.n = 0; return *this; }
+  ~DevBuf() { release(); }
+  void release() { if (p) cudaFree(p); p = nullptr; n = 0; }
+  int alloc(size_t count) {
+    release(); if (count == 0) return GN_OK;
+    cudaError_t e = cudaMalloc(&p, count * sizeof(float));
+    if (e != cudaSuccess) { p = nullptr; return fail(GN_ERR_OOM, "cudaMalloc of %zu bytes failed: %s", count * sizeof(float), cudaGetErrorString(e)); }
+    n = count; return GN_OK;
+  }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// Block-wide sum / max; every thread receives the result.  `red` holds >= 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) { float t = lane < nw ? red[lane] : 0.f; t = warp_sum(t); if (lane == 0) red[32] = t; }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  int lane = threadIdx.x & 31, w = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[w] = v;
+  __syncthreads();
+  if (w == 0) { float t = lane < nw ? red[lane] : -INFINITY; t = warp_max(t); if (lane == 0) red[32] = t; }
+  __syncthreads();
+  return red[32];
+}
+
+}  // namespace gn

@@ -1,0 +1,253 @@
+// conv_lstm.cuh -- Conv2D / MaxPool2D kernels (NCHW) and the LSTM recurrence kernels.
+#pragma once
+#include <cooperative_groups.h>
+#include "common.cuh"
+#include "rowops.cuh"
+
+namespace gn {
+namespace cg = cooperative_groups;
+
+struct ConvShape { int B, inC, outC, k, s, p, H, W, oH, oW; };
+
+// z[b,oc,oh,ow] = bias[oc] + sum_{ic,kh,kw} W[oc,ic,kh,kw] x[b,ic,oh*s+kh-p,ow*s+kw-p]; a = act(z)
+// reference: conv2d.go:716-959 (zero padding = out-of-range taps skipped; bias added last)
+__global__ void conv2d_fwd_kernel(const float* __restrict__ x, const float* __restrict__ Wt, const float* __restrict__ bias,
+                                  float* __restrict__ z, float* __restrict__ a, ConvShape c, int act) {
+  long total = (long)c.B * c.outC * c.oH * c.oW;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int ow = (int)(i % c.oW); long r = i / c.oW; int oh = (int)(r % c.oH); r /= c.oH; int oc = (int)(r % c.outC); int b = (int)(r / c.outC);
+    const float* xb = x + (long)b * c.inC * c.H * c.W;
+    const float* w = Wt + (long)oc * c.inC * c.k * c.k;
+    float acc = 0.f;
+    for (int ic = 0; ic < c.inC; ic++)
+      for (int kh = 0; kh < c.k; kh++) {
+        int ih = oh * c.s + kh - c.p; if (ih < 0 || ih >= c.H) continue;
+        for (int kw = 0; kw < c.k; kw++) {
+          int iw = ow * c.s + kw - c.p; if (iw < 0 || iw >= c.W) continue;
+          acc = fmaf(__ldg(w + (ic * c.k + kh) * c.k + kw), xb[((long)ic * c.H + ih) * c.W + iw], acc);
+        }
+      }
+    acc += bias[oc];
+    z[i] = acc; a[i] = act_fwd(act, acc);
+  }
+}
+// dx[b,ic,ih,iw] = sum_{oc,kh,kw} g[b,oc,oh,ow] W[oc,ic,kh,kw] with oh*s+kh-p = ih   (conv2d.go:1151-1162)
+__global__ void conv2d_dgrad_kernel(const float* __restrict__ g, const float* __restrict__ Wt, float* __restrict__ dx, ConvShape c) {
+  long total = (long)c.B * c.inC * c.H * c.W;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int iw = (int)(i % c.W); long r = i / c.W; int ih = (int)(r % c.H); r /= c.H; int ic = (int)(r % c.inC); int b = (int)(r / c.inC);
+    const float* gb = g + (long)b * c.outC * c.oH * c.oW;
+    float acc = 0.f;
+    for (int oc = 0; oc < c.outC; oc++)
+      for (int kh = 0; kh < c.k; kh++) {
+        int th = ih + c.p - kh; if (th < 0 || th % c.s) continue; int oh = th / c.s; if (oh >= c.oH) continue;
+        for (int kw = 0; kw < c.k; kw++) {
+          int tw = iw + c.p - kw; if (tw < 0 || tw % c.s) continue; int ow = tw / c.s; if (ow >= c.oW) continue;
+          acc = fmaf(gb[((long)oc * c.oH + oh) * c.oW + ow], __ldg(Wt + (((long)oc * c.inC + ic) * c.k + kh) * c.k + kw), acc);
+        }
+      }
+    dx[i] = acc;
+  }
+}
+// One block per weight: dW[oc,ic,kh,kw] += sum_{b,oh,ow} g * x ; blocks >= nW reduce one bias each.
+__global__ void conv2d_wgrad_kernel(const float* __restrict__ g, const float* __restrict__ x, float* __restrict__ dW, float* __restrict__ db, ConvShape c) {
+  __shared__ float red[33];
+  int nW = c.outC * c.inC * c.k * c.k;
+  int wi = blockIdx.x;
+  long span = (long)c.B * c.oH * c.oW;
+  float s = 0.f;
+  if (wi < nW) {
+    int kw = wi % c.k; int r = wi / c.k; int kh = r % c.k; r /= c.k; int ic = r % c.inC; int oc = r / c.inC;
+    for (long i = threadIdx.x; i < span; i += blockDim.x) {
+      int ow = (int)(i % c.oW); long q = i / c.oW; int oh = (int)(q % c.oH); int b = (int)(q / c.oH);
+      int ih = oh * c.s + kh - c.p, iw = ow * c.s + kw - c.p;
+      if (ih < 0 || ih >= c.H || iw < 0 || iw >= c.W) continue;
+      s = fmaf(g[(((long)b * c.outC + oc) * c.oH + oh) * c.oW + ow], x[(((long)b * c.inC + ic) * c.H + ih) * c.W + iw], s);
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) dW[wi] += s;
+  } else {
+    int oc = wi - nW;
+    for (long i = threadIdx.x; i < span; i += blockDim.x) {
+      long q = i / ((long)c.oH * c.oW); long rem = i % ((long)c.oH * c.oW);
+      s += g[((long)q * c.outC + oc) * c.oH * c.oW + rem];
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) db[oc] += s;
+  }
+}
+
+struct PoolShape { int B, C, k, s, p, H, W, oH, oW; };
+// reference: maxpool2d.go:192-221 (init -inf, strict '>', first maximum wins, argmax = flat CHW index)
+__global__ void maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int* __restrict__ arg, PoolShape c) {
+  long total = (long)c.B * c.C * c.oH * c.oW;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int ow = (int)(i % c.oW); long r = i / c.oW; int oh = (int)(r % c.oH); r /= c.oH; int ch = (int)(r % c.C); int b = (int)(r / c.C);
+    const float* xb = x + (long)b * c.C * c.H * c.W;
+    float mv = -INFINITY; int mi = -1;
+    for (int kh = 0; kh < c.k; kh++) for (int kw = 0; kw < c.k; kw++) {
+      int ih = oh * c.s + kh - c.p, iw = ow * c.s + kw - c.p;
+      if (ih >= 0 && ih < c.H && iw >= 0 && iw < c.W) { int idx = (ch * c.H + ih) * c.W + iw; float v = xb[idx]; if (v > mv) { mv = v; mi = idx; } }
+    }
+    y[i] = mv; arg[i] = mi;
+  }
+}
+// dx zero-filled beforehand; windows may overlap when stride < kernel, hence the atomic add (maxpool2d.go:395-406)
+__global__ void maxpool_bwd_kernel(const float* __restrict__ g, const int* __restrict__ arg, float* __restrict__ dx, PoolShape c) {
+  long total = (long)c.B * c.C * c.oH * c.oW; long per_out = (long)c.C * c.oH * c.oW, per_in = (long)c.C * c.H * c.W;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int a = arg[i]; if (a >= 0) atomicAdd(dx + (i / per_out) * per_in + a, g[i]);
+  }
+}
+
+// ---------------------------------------------------------------- LSTM
+// Forward recurrence of one sample per block, thread i = hidden unit i.
+// reference: lstm.go:276-407.  The reference's gate helpers (lstm.go:1065-1101) run over the first H of the
+// 4H pre-activation rows, so only the input gate receives Wx*x + Wh*h; forget, cell and output gates see
+// their biases alone and are constant over time.
+// Saves per (sample, t): input-gate pre-activation, cell state, hidden state.
+__global__ void lstm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ Wx, const float* __restrict__ Wh, const float* __restrict__ bias,
+                                float* __restrict__ pre_i, float* __restrict__ c_all, float* __restrict__ h_all, float* __restrict__ out,
+                                int T, int in, int H, int return_seq) {
+  extern __shared__ float sm[];
+  float* WhT = sm;                 // [H][H]  WhT[j*H+i] = Wh[i,j], rows 0..H-1 of the 4H
+  float* WxT = WhT + (long)H * H;  // [in][H]
+  float* hbuf = WxT + (long)in * H;  // [2][H]
+  float* xbuf = hbuf + 2 * H;        // [in]
+  const int s = blockIdx.x, i = threadIdx.x;
+  for (int e = threadIdx.x; e < H * H; e += blockDim.x) { int r = e / H, j = e % H; WhT[j * H + r] = Wh[e]; }
+  for (int e = threadIdx.x; e < H * in; e += blockDim.x) { int r = e / in, j = e % in; WxT[j * H + r] = Wx[e]; }
+  if (i < H) { hbuf[i] = 0.f; hbuf[H + i] = 0.f; }
+  float bi = 0.f, fg = 0.f, cg = 0.f, og = 0.f, c = 0.f;
+  if (i < H) { bi = bias[i]; fg = act_fwd(GN_ACT_SIGMOID, bias[H + i]); cg = act_fwd(GN_ACT_TANH, bias[2 * H + i]); og = act_fwd(GN_ACT_SIGMOID, bias[3 * H + i]); }
+  __syncthreads();
+  const float* xs = x + (long)s * T * in;
+  for (int t = 0; t < T; t++) {
+    for (int e = threadIdx.x; e < in; e += blockDim.x) xbuf[e] = xs[(long)t * in + e];
+    __syncthreads();
+    const float* hp = hbuf + (t & 1) * H; float* hn = hbuf + ((t + 1) & 1) * H;
+    if (i < H) {
+      float sx = 0.f;
+      for (int j = 0; j < in; j++) sx = fmaf(WxT[j * H + i], xbuf[j], sx);
+      float pre = bi + sx;
+      for (int j = 0; j < H; j++) pre = fmaf(WhT[j * H + i], hp[j], pre);
+      float ig = act_fwd(GN_ACT_SIGMOID, pre);
+      c = fg * c + ig * cg;
+      float h = og * act_fwd(GN_ACT_TANH, c);
+      long o = ((long)s * T + t) * H + i;
+      pre_i[o] = pre; c_all[o] = c; h_all[o] = h; hn[i] = h;
+      if (return_seq) out[o] = h; else if (t == T - 1) out[(long)s * H + i] = h;
+    }
+    __syncthreads();
+  }
+}
+// Back-propagation through time of one sample per block; writes the gate deltas D[s,t,4H].
+// reference: lstm.go:476-698 + unroller.go:190-209: the hidden-state gradient handed to step t-1 is the
+// gradient of step t PLUS Wh^T d (a running sum), because LSTM.Backward adds dhPrev into its argument.
+__global__ void lstm_bwd_kernel(const float* __restrict__ gout, const float* __restrict__ Wh, const float* __restrict__ bias,
+                                const float* __restrict__ pre_i, const float* __restrict__ c_all, float* __restrict__ D,
+                                int T, int H, int return_seq) {
+  extern __shared__ float sm[];
+  float* d = sm;   // [4H]
+  const int s = blockIdx.x, i = threadIdx.x;
+  float cur = 0.f, dcNext = 0.f, bf = 0.f, bg = 0.f, bo = 0.f;
+  if (i < H) { bf = bias[H + i]; bg = bias[2 * H + i]; bo = bias[3 * H + i]; }
+  for (int t = T - 1; t >= 0; t--) {
+    if (i < H) {
+      if (return_seq) cur += gout[((long)s * T + t) * H + i]; else if (t == T - 1) cur += gout[(long)s * H + i];
+      long o = ((long)s * T + t) * H + i;
+      float pre = pre_i[o], c = c_all[o], cprev = t > 0 ? c_all[o - H] : 0.f;
+      float ig = act_fwd(GN_ACT_SIGMOID, pre), fg = act_fwd(GN_ACT_SIGMOID, bf), cgt = act_fwd(GN_ACT_TANH, bg), og = act_fwd(GN_ACT_SIGMOID, bo);
+      float tanhC = act_fwd(GN_ACT_TANH, c);
+      float dc = cur * og * (1.f - tanhC * tanhC) + dcNext;
+      float di = dc * cgt * act_der(GN_ACT_SIGMOID, pre);
+      float df = dc * cprev * act_der(GN_ACT_SIGMOID, bf);
+      float dg = dc * ig * act_der(GN_ACT_TANH, bg);
+      float dout = cur * tanhC * act_der(GN_ACT_SIGMOID, bo);
+      dcNext = dc * fg;
+      d[i] = di; d[H + i] = df; d[2 * H + i] = dg; d[3 * H + i] = dout;
+      float* Dr = D + ((long)s * T + t) * 4 * H;
+      Dr[i] = di; Dr[H + i] = df; Dr[2 * H + i] = dg; Dr[3 * H + i] = dout;
+    }
+    __syncthreads();
+    if (i < H) {
+      float sum = 0.f;
+      for (int r = 0; r < 4 * H; r++) sum = fmaf(Wh[(long)r * H + i], d[r], sum);
+      cur += sum;
+    }
+    __syncthreads();
+  }
+}
+
+// The reference clips the WHOLE accumulated LSTM gradient to L2 norm <= 1 after every time-step of every
+// sample (lstm.go:694, :725-751), so the gradient of a worker chunk is a sequential recurrence over its
+// (sample, t) updates  g <- clip(g + d_k (x) [x_last ; h_{t-1} ; 1]).  One thread-block cluster runs one
+// chunk: the 4H gradient rows are split over the cluster's CTAs, each keeps its rows in shared memory,
+// and the squared norm is exchanged through distributed shared memory once per update.
+// Row r of the running gradient is [gWx[r,:] | gWh[r,:] | gb[r]].
+constexpr int SCAN_CLUSTER = 8, SCAN_THREADS = 256;
+__global__ void __launch_bounds__(SCAN_THREADS) lstm_grad_scan_kernel(
+    const float* __restrict__ D, const float* __restrict__ x, const float* __restrict__ h_all, float* __restrict__ out,
+    int T, int in, int H, int n_samples_total, int chunk, int first_sample_offset) {
+  cg::cluster_group cluster = cg::this_cluster();
+  const int rank = cluster.block_rank();
+  const int cl = blockIdx.x / SCAN_CLUSTER;                    // which worker chunk
+  const int R4 = 4 * H, ZW = in + H + 1;
+  const int rpc = (R4 + SCAN_CLUSTER - 1) / SCAN_CLUSTER, row0 = rank * rpc, nrows = max(0, min(rpc, R4 - row0));
+  extern __shared__ float sm[];
+  float* acc = sm;                         // [rpc][ZW]
+  float* dsh = acc + (long)rpc * ZW;       // [rpc]
+  float* zsh = dsh + rpc;                  // [ZW]
+  float* red = zsh + ZW;                   // [33]
+  __shared__ float part[2][SCAN_CLUSTER];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = SCAN_THREADS >> 5;
+  for (int e = tid; e < rpc * ZW; e += SCAN_THREADS) acc[e] = 0.f;
+  cluster.sync();
+  // samples of this chunk, relative to the tensors passed in
+  int s_begin = cl * chunk - first_sample_offset, s_end = min(n_samples_total, s_begin + chunk);
+  s_begin = max(s_begin, 0);
+  long step = 0;
+  for (int s = s_begin; s < s_end; s++) {
+    for (int t = T - 1; t >= 0; t--, step++) {
+      const int buf = (int)(step & 1);
+      const float* Dr = D + ((long)s * T + t) * R4 + row0;
+      for (int e = tid; e < nrows; e += SCAN_THREADS) dsh[e] = Dr[e];
+      for (int e = tid; e < ZW; e += SCAN_THREADS) {
+        float v;
+        if (e < in) v = x[(long)s * T * in + (long)(T - 1) * in + e];           // lstm.go:592-621: input of the LAST forward call
+        else if (e < in + H) v = t > 0 ? h_all[((long)s * T + (t - 1)) * H + (e - in)] : 0.f;
+        else v = 1.f;
+        zsh[e] = v;
+      }
+      __syncthreads();
+      float sq = 0.f;
+      for (int r = warp; r < nrows; r += nwarps) {
+        float dr = dsh[r]; float* a = acc + (long)r * ZW;
+        for (int c = lane; c < ZW; c += 32) { float v = fmaf(dr, zsh[c], a[c]); a[c] = v; sq = fmaf(v, v, sq); }
+      }
+      sq = block_sum(sq, red);
+      if (tid < SCAN_CLUSTER) { float* remote = cluster.map_shared_rank(&part[buf][rank], tid); *remote = sq; }
+      cluster.sync();
+      float total = 0.f;
+#pragma unroll
+      for (int q = 0; q < SCAN_CLUSTER; q++) total += part[buf][q];
+      float norm = sqrtf(total);
+      if (norm > 1.f) {
+        float sc = 1.f / norm;
+        for (int r = warp; r < nrows; r += nwarps) { float* a = acc + (long)r * ZW; for (int c = lane; c < ZW; c += 32) a[c] *= sc; }
+      }
+    }
+  }
+  __syncthreads();
+  // write out in the flat layout: gWx[4H,in] | gWh[4H,H] | gb[4H]
+  float* o = out + (long)cl * ((long)R4 * ZW);
+  for (int e = tid; e < nrows * ZW; e += SCAN_THREADS) {
+    int r = e / ZW, c = e % ZW, gr = row0 + r; float v = acc[(long)r * ZW + c];
+    if (c < in) o[(long)gr * in + c] = v;
+    else if (c < in + H) o[(long)R4 * in + (long)gr * H + (c - in)] = v;
+    else o[(long)R4 * in + (long)R4 * H + gr] = v;
+  }
+  cluster.sync();
+}
+
+}  // namespace gn

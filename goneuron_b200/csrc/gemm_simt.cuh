@@ -1,0 +1,118 @@
+// gemm_simt.cuh -- strided, batched fp32 contraction on the CUDA cores.
+//
+// C[b](m,n) = act( alpha * sum_k A[b](m,k) * B[b](k,n) + bias[n] + R[b](m,n) )
+// with arbitrary element strides for A and B, so every transpose variant of the
+// training step (X*W^T, dZ*W, dZ^T*X, Q*K^T, P*V, dS^T*Q ...) and every sub-view
+// (one head of a [tokens, d] tensor, the last token of every sequence) is the same
+// kernel.  It is the exact-fp32 engine: small and oddly shaped contractions use it,
+// and the tensor-core engine is checked against it.
+#pragma once
+#include "common.cuh"
+
+namespace gn {
+
+enum { GEMM_KBEG_AT_M0 = 1, GEMM_KEND_AT_M0 = 2, GEMM_SKIP_UPPER = 4 };
+
+struct GemmDesc {
+  int M = 0, N = 0, K = 0;
+  const float* A = nullptr; long sa_m = 0, sa_k = 0;
+  const float* B = nullptr; long sb_k = 0, sb_n = 0;   // B(k,n)
+  float* C = nullptr; long ldc = 0;
+  const float* bias = nullptr;                          // [N]
+  const float* R = nullptr; long ldr = 0;               // residual added to the result (may alias C)
+  int act = GN_ACT_LINEAR;                              // LINEAR or RELU
+  float alpha = 1.f;
+  int batch1 = 1, batch2 = 1;                           // batch index b -> (b / batch2, b % batch2)
+  long a_b1 = 0, a_b2 = 0, b_b1 = 0, b_b2 = 0, c_b1 = 0, c_b2 = 0, r_b1 = 0, r_b2 = 0;
+  // Causal structure of attention: tiles that are entirely masked are never touched.
+  //   GEMM_SKIP_UPPER : do not compute output tiles with n0 > m0 + BM - 1 (S = Q K^T)
+  //   GEMM_KEND_AT_M0 : contraction index stops at m0 + BM            (P V, dS K)
+  //   GEMM_KBEG_AT_M0 : contraction index starts at m0                (dS^T Q, P^T dA)
+  int flags = 0;
+};
+
+constexpr int SG_BM = 128, SG_BN = 128, SG_BK = 16, SG_PAD = 4, SG_THREADS = 256;
+
+template <bool A_KFAST, bool B_NFAST>
+__global__ void __launch_bounds__(SG_THREADS) gemm_simt_kernel(GemmDesc g) {
+  __shared__ __align__(16) float As[SG_BK][SG_BM + SG_PAD];
+  __shared__ __align__(16) float Bs[SG_BK][SG_BN + SG_PAD];
+  const int b = blockIdx.z, b1 = b / g.batch2, b2 = b % g.batch2;
+  const float* A = g.A + b1 * g.a_b1 + b2 * g.a_b2;
+  const float* B = g.B + b1 * g.b_b1 + b2 * g.b_b2;
+  float* C = g.C + b1 * g.c_b1 + b2 * g.c_b2;
+  const int m0 = blockIdx.y * SG_BM, n0 = blockIdx.x * SG_BN;
+  if ((g.flags & GEMM_SKIP_UPPER) && n0 > m0 + SG_BM - 1) return;
+  int kbeg = 0, kend = g.K;
+  if (g.flags & GEMM_KBEG_AT_M0) kbeg = (m0 / SG_BK) * SG_BK;
+  if (g.flags & GEMM_KEND_AT_M0) kend = min(g.K, m0 + SG_BM);
+  const int t = threadIdx.x, ty = t / 16, tx = t % 16;
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; i++)
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+
+  for (int k0 = kbeg; k0 < kend; k0 += SG_BK) {
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      int idx = t + SG_THREADS * e;
+      int m, k;
+      if (A_KFAST) { k = idx % SG_BK; m = idx / SG_BK; } else { m = idx % SG_BM; k = idx / SG_BM; }
+      int gm = m0 + m, gk = k0 + k;
+      As[k][m] = (gm < g.M && gk < kend) ? A[gm * g.sa_m + gk * g.sa_k] : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+      int idx = t + SG_THREADS * e;
+      int n, k;
+      if (B_NFAST) { n = idx % SG_BN; k = idx / SG_BN; } else { k = idx % SG_BK; n = idx / SG_BK; }
+      int gn_ = n0 + n, gk = k0 + k;
+      Bs[k][n] = (gn_ < g.N && gk < kend) ? B[gk * g.sb_k + gn_ * g.sb_n] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < SG_BK; k++) {
+      float4 a0 = *reinterpret_cast<const float4*>(&As[k][ty * 4]);
+      float4 a1 = *reinterpret_cast<const float4*>(&As[k][64 + ty * 4]);
+      float4 c0 = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+      float4 c1 = *reinterpret_cast<const float4*>(&Bs[k][64 + tx * 4]);
+      float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      float bv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  const float* R = g.R ? g.R + b1 * g.r_b1 + b2 * g.r_b2 : nullptr;
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+    if (m >= g.M) continue;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+      int n = n0 + (j < 4 ? tx * 4 + j : 64 + tx * 4 + (j - 4));
+      if (n >= g.N) continue;
+      float v = g.alpha * acc[i][j];
+      if (g.bias) v += g.bias[n];
+      if (R) v += R[m * g.ldr + n];
+      if (g.act == GN_ACT_RELU) v = v > 0.f ? v : 0.f;
+      C[m * g.ldc + n] = v;
+    }
+  }
+}
+
+inline int gemm_simt(Ctx* ctx, const GemmDesc& g) {
+  if (g.M <= 0 || g.N <= 0) return GN_OK;
+  dim3 grid(cdiv(g.N, SG_BN), cdiv(g.M, SG_BM), g.batch1 * g.batch2);
+  bool ak = (g.sa_k == 1), bn = (g.sb_n == 1);
+  if (ak && bn) GN_LAUNCH(ctx, (gemm_simt_kernel<true, true>), grid, SG_THREADS, 0, g);
+  else if (ak && !bn) GN_LAUNCH(ctx, (gemm_simt_kernel<true, false>), grid, SG_THREADS, 0, g);
+  else if (!ak && bn) GN_LAUNCH(ctx, (gemm_simt_kernel<false, true>), grid, SG_THREADS, 0, g);
+  else GN_LAUNCH(ctx, (gemm_simt_kernel<false, false>), grid, SG_THREADS, 0, g);
+  return check_launch("gemm_simt");
+}
+
+}  // namespace gn

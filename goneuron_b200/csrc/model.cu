@@ -1,0 +1,741 @@
+// model.cu -- the compiled model (execution plan over device-resident tensors) and the C ABI.
+//
+// One gn_model owns: the flat parameter buffer, the flat gradient buffer and the Adam moments, all in the
+// reference's flat layout (Network.initBuffers, internal/net/net.go:91-127); per-layer activation buffers
+// sized for the largest batch seen; and shared scratch.  One gn_train_batch call runs the whole
+// Network.TrainBatch (net.go:412-436, :721-784) for a batch on the device.
+//
+// Batch-level restatement of the per-sample reference semantics:
+//  * top-level Dense / Conv2D use each sample's own input and pre-activation (layer.go:488-667);
+//  * Dense layers inside MultiHeadAttention / TransformerBlock are called once per token and keep only their
+//    LAST call's input and pre-activation (layer.go:352, :496-497, :563-567), so per sample
+//        gW = (sum_t dz_t) (x) x_{T-1},   FFN ReLU mask of every token = mask of token T-1
+//    which at batch level is  gW = Delta^T * X_last  (a contraction over the batch) with Delta[s] = sum_t dz[s,t];
+//  * Embedding gradient: only the last sample of each worker chunk (embedding.go:151-154);
+//  * LSTM: see conv_lstm.cuh.
+#include <cmath>
+#include <cstring>
+#include <memory>
+
+#include "common.cuh"
+#include "gemm_simt.cuh"
+#include "gemm_tc.cuh"
+#include "rowops.cuh"
+#include "conv_lstm.cuh"
+#include "nccl_dl.cuh"
+
+namespace gn {
+
+// ------------------------------------------------------------------ contraction dispatch
+// Chooses the tensor-core engine for large K-major x K-major products and the SIMT engine for the rest.
+static int gemm(Ctx* ctx, const GemmDesc& g) {
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  if (ctx->profile) {
+    if (ctx->ev_used == ctx->ev_pool.size()) {
+      cudaEvent_t a, b; GN_CUDA(cudaEventCreate(&a)); GN_CUDA(cudaEventCreate(&b)); ctx->ev_pool.push_back({a, b});
+    }
+    e0 = ctx->ev_pool[ctx->ev_used].first; e1 = ctx->ev_pool[ctx->ev_used].second; ctx->ev_used++;
+    GN_CUDA(cudaEventRecord(e0, ctx->stream));
+  }
+  int rc;
+  if (gemm_tc_eligible(ctx, g)) rc = gemm_tc(ctx, g);
+  else rc = gemm_simt(ctx, g);
+  if (ctx->profile) { GN_CUDA(cudaEventRecord(e1, ctx->stream)); }
+  double nb = (double)g.batch1 * g.batch2;
+  double flops = 2.0 * g.M * (double)g.N * g.K * nb;
+  if (g.flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0)) flops *= 0.5;   // causal: about half the tiles exist
+  ctx->gemm_flops += flops; ctx->gemm_launches++;
+  return rc;
+}
+// Y[M,N] = X[M,K] * W[N,K]^T + bias (+R) (act)           -- Dense forward at batch level
+static int gemm_nt(Ctx* ctx, int M, int N, int K, const float* X, long ldx, const float* W, const float* bias, float* Y, long ldy,
+                   int act = GN_ACT_LINEAR, const float* R = nullptr, long ldr = 0) {
+  GemmDesc g; g.M = M; g.N = N; g.K = K; g.A = X; g.sa_m = ldx; g.sa_k = 1; g.B = W; g.sb_k = 1; g.sb_n = K;
+  g.C = Y; g.ldc = ldy; g.bias = bias; g.act = act; g.R = R; g.ldr = ldr; return gemm(ctx, g);
+}
+// dX[M,K] = dZ[M,N] * W[N,K] (+R)                          -- gradIn = W^T dz   (layer.go:631-663)
+static int gemm_nn(Ctx* ctx, int M, int N, int K, const float* dZ, long ldz, const float* W, float* dX, long ldx, const float* R = nullptr, long ldr = 0) {
+  GemmDesc g; g.M = M; g.N = K; g.K = N; g.A = dZ; g.sa_m = ldz; g.sa_k = 1; g.B = W; g.sb_k = K; g.sb_n = 1;
+  g.C = dX; g.ldc = ldx; g.R = R; g.ldr = ldr; return gemm(ctx, g);
+}
+// gW[N,K] = dZ[R,N]^T * X[R,K]                              -- gradW += dz (x) x   (layer.go:591-625)
+static int gemm_tn(Ctx* ctx, int R, int N, int K, const float* dZ, long ldz, const float* X, long ldx, float* gW) {
+  GemmDesc g; g.M = N; g.N = K; g.K = R; g.A = dZ; g.sa_m = 1; g.sa_k = ldz; g.B = X; g.sb_k = ldx; g.sb_n = 1;
+  g.C = gW; g.ldc = K; return gemm(ctx, g);
+}
+
+// ------------------------------------------------------------------ model
+struct LayerRT {
+  gn_layer_desc d{};
+  int in_size = 0, out_size = 0;
+  int64_t p_off = 0, p_cnt = 0;
+  // forward state kept for backward
+  DevBuf out, z;                       // activation / pre-activation  [cap, out_size]
+  DevBuf q, k, v, att, r1, n1, mid, r2, stat;   // TransformerBlock
+  DevBuf pre_i, c_all, h_all, dgate;   // LSTM
+  DevBuf idx;                          // int32 payload: MaxPool argmax / embedding token ids
+  const float* fin = nullptr;          // input of the last forward call (device pointer, not owned)
+};
+
+}  // namespace gn
+
+struct gn_ctx { gn::Ctx c; bool alive = true; };
+
+struct gn_model {
+  gn_ctx* ctx = nullptr;
+  std::mutex mu;
+  std::vector<gn::LayerRT> L;
+  int loss_kind = 0, W = 1;
+  int64_t P = 0; int in_size = 0, out_size = 0;
+  gn::DevBuf params, grads, m1, v2;
+  float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f; int timestep = 0;
+  int cap = 0;                          // batch capacity of the activation buffers
+  gn::DevBuf xin, yin, lossg, loss_s, loss_sum;
+  std::vector<gn::DevBuf> scratch;      // growable shared scratch, by slot
+  float last_inv_batch = 1.f;
+  gn_step_stats stats{};
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr, ar0 = nullptr, ar1 = nullptr;
+  bool alive = true;
+  bool has_lstm = false;
+};
+
+namespace gn {
+
+enum Slot { S_G0 = 0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+
+static int ensure(gn_model* m, int slot, size_t n, float** out) {
+  if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
+  DevBuf& b = m->scratch[slot];
+  if (b.n < n) { GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); GN_TRY(b.alloc(n)); }
+  *out = b.p; return GN_OK;
+}
+
+static int plan_layers(gn_model* m, const gn_layer_desc* layers, int n) {
+  int cur = -1; int64_t off = 0;
+  for (int i = 0; i < n; i++) {
+    LayerRT l; l.d = layers[i]; const gn_layer_desc& d = l.d;
+    switch (d.kind) {
+      case GN_LAYER_DENSE:
+        if (d.in_size <= 0 || d.out_size <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: Dense sizes must be positive", i);
+        l.in_size = d.in_size; l.out_size = d.out_size; l.p_cnt = (int64_t)d.in_size * d.out_size + d.out_size; break;
+      case GN_LAYER_CONV2D: {
+        if (d.in_size <= 0 || d.out_size <= 0 || d.kernel <= 0 || d.stride <= 0 || d.in_h <= 0 || d.in_w <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad Conv2D descriptor", i);
+        if (d.activation == GN_ACT_SOFTMAX || d.activation == GN_ACT_LOGSOFTMAX) return fail(GN_ERR_UNSUPPORTED, "layer %d: Conv2D with a softmax activation", i);
+        int oh = (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, ow = (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1;
+        l.in_size = d.in_size * d.in_h * d.in_w; l.out_size = d.out_size * oh * ow;
+        l.p_cnt = (int64_t)d.out_size * d.in_size * d.kernel * d.kernel + d.out_size; break; }
+      case GN_LAYER_MAXPOOL2D: {
+        if (d.in_size <= 0 || d.kernel <= 0 || d.stride <= 0 || d.in_h <= 0 || d.in_w <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad MaxPool2D descriptor", i);
+        int oh = (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, ow = (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1;
+        l.in_size = d.in_size * d.in_h * d.in_w; l.out_size = d.in_size * oh * ow; break; }
+      case GN_LAYER_FLATTEN:
+        if (cur < 0) return fail(GN_ERR_INVALID_ARG, "Flatten cannot be the first layer");
+        l.in_size = l.out_size = cur; break;
+      case GN_LAYER_LSTM_UNROLLED:
+        if (d.in_size <= 0 || d.out_size <= 0 || d.seq_len <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad LSTM descriptor", i);
+        if (d.out_size > 1024) return fail(GN_ERR_UNSUPPORTED, "layer %d: LSTM hidden size > 1024", i);
+        l.in_size = d.seq_len * d.in_size; l.out_size = d.return_seq ? d.seq_len * d.out_size : d.out_size;
+        l.p_cnt = (int64_t)4 * d.out_size * d.in_size + (int64_t)4 * d.out_size * d.out_size + 4 * d.out_size; m->has_lstm = true; break;
+      case GN_LAYER_EMBEDDING: {
+        int T = d.seq_len; for (int j = i + 1; j < n && T <= 0; j++) T = layers[j].seq_len;
+        if (T <= 0 || d.in_size <= 0 || d.out_size <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: Embedding needs vocab, dim and a sequence length", i);
+        l.d.seq_len = T; l.in_size = T; l.out_size = T * d.out_size; l.p_cnt = (int64_t)d.in_size * d.out_size; break; }
+      case GN_LAYER_POSENC:
+        if (d.seq_len <= 0 || d.dim <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad PositionalEncoding descriptor", i);
+        l.in_size = l.out_size = d.seq_len * d.dim; l.p_cnt = (int64_t)d.seq_len * d.dim; break;
+      case GN_LAYER_TRANSFORMER_BLOCK:
+        if (d.seq_len <= 0 || d.dim <= 0 || d.heads <= 0 || d.ff_dim <= 0 || d.dim % d.heads) return fail(GN_ERR_INVALID_ARG, "layer %d: bad TransformerBlock descriptor (dim must be divisible by heads)", i);
+        l.in_size = l.out_size = d.seq_len * d.dim;
+        l.p_cnt = 4 * ((int64_t)d.dim * d.dim + d.dim) + 4 * (int64_t)d.dim + ((int64_t)d.dim * d.ff_dim + d.ff_dim) + ((int64_t)d.ff_dim * d.dim + d.dim); break;
+      case GN_LAYER_CLS_POOLING:
+        if (d.seq_len <= 0 || d.dim <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad CLSPooling descriptor", i);
+        l.in_size = d.seq_len * d.dim; l.out_size = d.dim; break;
+      case GN_LAYER_LAYERNORM:
+        if (cur < 0 || d.dim <= 0 || cur % d.dim) return fail(GN_ERR_INVALID_ARG, "layer %d: LayerNorm width must divide the input size", i);
+        l.in_size = l.out_size = cur; l.p_cnt = 2 * (int64_t)d.dim; break;
+      default: return fail(GN_ERR_UNSUPPORTED, "layer %d: unknown layer kind %d", i, d.kind);
+    }
+    if (cur >= 0 && l.in_size != cur) return fail(GN_ERR_INVALID_ARG, "layer %d: input size mismatch: expected %d, got %d", i, l.in_size, cur);
+    if (i == 0) m->in_size = l.in_size;
+    cur = l.out_size; l.p_off = off; off += l.p_cnt;
+    m->L.push_back(std::move(l));
+  }
+  m->out_size = cur; m->P = off; return GN_OK;
+}
+
+// (Re)allocates every per-layer activation buffer for `cap` samples.
+static int alloc_activations(gn_model* m, int cap) {
+  GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream));
+  size_t c = (size_t)cap;
+  GN_TRY(m->xin.alloc(c * m->in_size)); GN_TRY(m->yin.alloc(c * m->out_size));
+  GN_TRY(m->lossg.alloc(c * m->out_size)); GN_TRY(m->loss_s.alloc(c)); GN_TRY(m->loss_sum.alloc(4));
+  for (auto& l : m->L) {
+    const gn_layer_desc& d = l.d;
+    switch (d.kind) {
+      case GN_LAYER_DENSE:
+        GN_TRY(l.out.alloc(c * l.out_size));
+        if (d.activation != GN_ACT_LINEAR && d.activation != GN_ACT_RELU) GN_TRY(l.z.alloc(c * l.out_size));
+        break;
+      case GN_LAYER_CONV2D: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.z.alloc(c * l.out_size)); break;
+      case GN_LAYER_MAXPOOL2D: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.idx.alloc(c * l.out_size)); break;
+      case GN_LAYER_FLATTEN: break;
+      case GN_LAYER_LSTM_UNROLLED: {
+        size_t th = c * d.seq_len * d.out_size;
+        GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.pre_i.alloc(th)); GN_TRY(l.c_all.alloc(th)); GN_TRY(l.h_all.alloc(th)); GN_TRY(l.dgate.alloc(4 * th)); break; }
+      case GN_LAYER_EMBEDDING: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.idx.alloc(c * d.seq_len)); break;
+      case GN_LAYER_POSENC: GN_TRY(l.out.alloc(c * l.out_size)); break;
+      case GN_LAYER_TRANSFORMER_BLOCK: {
+        size_t nd = c * d.seq_len * d.dim, nf = c * d.seq_len * d.ff_dim, nt = c * d.seq_len;
+        GN_TRY(l.q.alloc(nd)); GN_TRY(l.k.alloc(nd)); GN_TRY(l.v.alloc(nd)); GN_TRY(l.att.alloc(nd)); GN_TRY(l.r1.alloc(nd)); GN_TRY(l.n1.alloc(nd));
+        GN_TRY(l.mid.alloc(nf)); GN_TRY(l.r2.alloc(nd)); GN_TRY(l.out.alloc(nd)); GN_TRY(l.stat.alloc(4 * nt)); break; }
+      case GN_LAYER_CLS_POOLING: GN_TRY(l.out.alloc(c * l.out_size)); break;
+      case GN_LAYER_LAYERNORM: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.stat.alloc(2 * c * (l.in_size / d.dim))); break;
+    }
+  }
+  m->cap = cap; return GN_OK;
+}
+
+static inline unsigned ew_grid(Ctx* ctx, long n, int block = 256) { long g = (n + block - 1) / block; long mx = (long)ctx->sm_count * 16; return (unsigned)std::max<long>(1, std::min(g, mx)); }
+
+// out[c] (=|+=) sum over R rows of in[r*ld + c]
+static int colsum(gn_model* m, const float* in, long ld, int R, int C, float* out, bool accumulate) {
+  Ctx* ctx = &m->ctx->c;
+  int chunks = std::max(1, std::min(R / 64, 128));
+  float* part; GN_TRY(ensure(m, S_PART, (size_t)chunks * C * 2, &part));
+  GN_LAUNCH(ctx, colsum_partial_kernel, dim3(cdiv(C, 128), chunks), 128, 0, in, ld, R, C, part);
+  GN_LAUNCH(ctx, colsum_final_kernel, cdiv(C, 128), 128, 0, part, chunks, C, out, accumulate ? 1 : 0);
+  return check_launch("colsum");
+}
+
+// ---------------------------------------------------------------- forward
+static int attention_forward(gn_model* m, LayerRT& l, int B, float* P) {
+  Ctx* ctx = &m->ctx->c; const gn_layer_desc& d = l.d;
+  const int T = d.seq_len, D = d.dim, Hh = d.heads, hd = D / Hh; const long TD = (long)T * D, TT = (long)T * T;
+  GemmDesc g; g.M = T; g.N = T; g.K = hd; g.A = l.q.p; g.sa_m = D; g.sa_k = 1; g.B = l.k.p; g.sb_k = 1; g.sb_n = D;
+  g.C = P; g.ldc = T; g.batch1 = B; g.batch2 = Hh; g.a_b1 = TD; g.a_b2 = hd; g.b_b1 = TD; g.b_b2 = hd; g.c_b1 = Hh * TT; g.c_b2 = TT;
+  g.flags = d.causal ? GEMM_SKIP_UPPER : 0;
+  GN_TRY(gemm(ctx, g));
+  long rows = (long)B * Hh * T;
+  float inv_scale = 1.f / sqrtf((float)hd);
+  GN_LAUNCH(ctx, attn_softmax_kernel, cdiv(rows, 8), 256, 0, P, T, inv_scale, d.causal, rows);
+  GemmDesc o; o.M = T; o.N = hd; o.K = T; o.A = P; o.sa_m = T; o.sa_k = 1; o.B = l.v.p; o.sb_k = D; o.sb_n = 1;
+  o.C = l.att.p; o.ldc = D; o.batch1 = B; o.batch2 = Hh; o.a_b1 = Hh * TT; o.a_b2 = TT; o.b_b1 = TD; o.b_b2 = hd; o.c_b1 = TD; o.c_b2 = hd;
+  o.flags = d.causal ? GEMM_KEND_AT_M0 : 0;
+  return gemm(ctx, o);
+}
+
+struct BlockParams { const float *wq, *bq, *wk, *bk, *wv, *bv, *wo, *bo, *g1, *be1, *g2, *be2, *w1, *b1, *w2, *b2; };
+static BlockParams block_params(const float* p, int D, int F) {
+  BlockParams b; long dd = (long)D * D;
+  b.wq = p; b.bq = p + dd; p += dd + D; b.wk = p; b.bk = p + dd; p += dd + D; b.wv = p; b.bv = p + dd; p += dd + D; b.wo = p; b.bo = p + dd; p += dd + D;
+  b.g1 = p; b.be1 = p + D; p += 2 * D; b.g2 = p; b.be2 = p + D; p += 2 * D;
+  b.w1 = p; b.b1 = p + (long)D * F; p += (long)D * F + F; b.w2 = p; b.b2 = p + (long)F * D; return b;
+}
+
+static int forward(gn_model* m, const float* x, int B, const float** y_out) {
+  Ctx* ctx = &m->ctx->c;
+  const float* cur = x;
+  for (size_t li = 0; li < m->L.size(); li++) {
+    LayerRT& l = m->L[li]; const gn_layer_desc& d = l.d; const float* p = m->params.p + l.p_off;
+    l.fin = cur;
+    switch (d.kind) {
+      case GN_LAYER_DENSE: {
+        const float* W = p; const float* bias = p + (long)d.in_size * d.out_size;
+        if (d.activation == GN_ACT_LINEAR || d.activation == GN_ACT_RELU) {
+          GN_TRY(gemm_nt(ctx, B, d.out_size, d.in_size, cur, d.in_size, W, bias, l.out.p, d.out_size, d.activation));
+        } else {
+          GN_TRY(gemm_nt(ctx, B, d.out_size, d.in_size, cur, d.in_size, W, bias, l.z.p, d.out_size));
+          if (d.activation == GN_ACT_SOFTMAX || d.activation == GN_ACT_LOGSOFTMAX)
+            GN_LAUNCH(ctx, softmax_rows_kernel, B, 256, 0, l.z.p, l.out.p, d.out_size, d.activation == GN_ACT_LOGSOFTMAX ? 1 : 0);
+          else { long n = (long)B * d.out_size; GN_LAUNCH(ctx, act_forward_kernel, ew_grid(ctx, n), 256, 0, l.z.p, l.out.p, n, d.activation); }
+        }
+        cur = l.out.p; break; }
+      case GN_LAYER_CONV2D: {
+        ConvShape c{B, d.in_size, d.out_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
+                    (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
+        long n = (long)B * l.out_size;
+        GN_LAUNCH(ctx, conv2d_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, p, p + (long)d.out_size * d.in_size * d.kernel * d.kernel, l.z.p, l.out.p, c, d.activation);
+        cur = l.out.p; break; }
+      case GN_LAYER_MAXPOOL2D: {
+        PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
+                    (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
+        long n = (long)B * l.out_size;
+        GN_LAUNCH(ctx, maxpool_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, l.out.p, (int*)l.idx.p, c);
+        cur = l.out.p; break; }
+      case GN_LAYER_FLATTEN: break;
+      case GN_LAYER_LSTM_UNROLLED: {
+        int H = d.out_size, in = d.in_size; int threads = ((H + 31) / 32) * 32;
+        size_t smem = ((size_t)H * H + (size_t)in * H + 2 * H + in) * sizeof(float);
+        if (smem > 200 * 1024) return fail(GN_ERR_UNSUPPORTED, "LSTM of hidden size %d needs %zu bytes of shared memory", H, smem);
+        GN_CUDA(cudaFuncSetAttribute(lstm_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        GN_LAUNCH(ctx, lstm_fwd_kernel, B, threads, smem, cur, p, p + (long)4 * H * in, p + (long)4 * H * in + (long)4 * H * H,
+                  l.pre_i.p, l.c_all.p, l.h_all.p, l.out.p, d.seq_len, in, H, d.return_seq);
+        cur = l.out.p; break; }
+      case GN_LAYER_EMBEDDING: {
+        // fused with a directly following PositionalEncoding
+        long tokens = (long)B * d.seq_len; const float* P = nullptr;
+        bool fuse = li + 1 < m->L.size() && m->L[li + 1].d.kind == GN_LAYER_POSENC && m->L[li + 1].d.dim == d.out_size;
+        if (fuse) P = m->params.p + m->L[li + 1].p_off;
+        float* dst = fuse ? m->L[li + 1].out.p : l.out.p;
+        GN_LAUNCH(ctx, embedding_fwd_kernel, (unsigned)tokens, 128, 0, cur, p, P, dst, tokens, d.seq_len, d.out_size, d.in_size, (int*)l.idx.p);
+        cur = dst; if (fuse) li++; break; }
+      case GN_LAYER_POSENC: {
+        long n = (long)B * l.out_size;
+        GN_LAUNCH(ctx, posenc_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, p, l.out.p, n, (long)l.out_size);
+        cur = l.out.p; break; }
+      case GN_LAYER_TRANSFORMER_BLOCK: {
+        const int T = d.seq_len, D = d.dim, F = d.ff_dim; const int N = B * T; BlockParams bp = block_params(p, D, F);
+        GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wq, bp.bq, l.q.p, D));
+        GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wk, bp.bk, l.k.p, D));
+        GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wv, bp.bv, l.v.p, D));
+        float* P; GN_TRY(ensure(m, S_ATT0, (size_t)B * d.heads * T * T, &P));
+        GN_TRY(attention_forward(m, l, B, P));
+        GN_TRY(gemm_nt(ctx, N, D, D, l.att.p, D, bp.wo, bp.bo, l.r1.p, D, GN_ACT_LINEAR, cur, D));          // res1 = x + att
+        float* st = l.stat.p;
+        GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(N, 8), 256, 0, l.r1.p, bp.g1, bp.be1, l.n1.p, st, st + N, (long)N, D, 1e-5f);
+        GN_TRY(gemm_nt(ctx, N, F, D, l.n1.p, D, bp.w1, bp.b1, l.mid.p, F, GN_ACT_RELU));
+        GN_TRY(gemm_nt(ctx, N, D, F, l.mid.p, F, bp.w2, bp.b2, l.r2.p, D, GN_ACT_LINEAR, l.n1.p, D));        // res2 = norm1 + ff
+        GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(N, 8), 256, 0, l.r2.p, bp.g2, bp.be2, l.out.p, st + 2 * N, st + 3 * N, (long)N, D, 1e-5f);
+        cur = l.out.p; break; }
+      case GN_LAYER_CLS_POOLING:
+        GN_LAUNCH(ctx, cls_fwd_kernel, B, 128, 0, cur, l.out.p, d.seq_len, d.dim); cur = l.out.p; break;
+      case GN_LAYER_LAYERNORM: {
+        long rows = (long)B * (l.in_size / d.dim);
+        GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(rows, 8), 256, 0, cur, p, p + d.dim, l.out.p, l.stat.p, l.stat.p + rows, rows, d.dim, 1e-5f);
+        cur = l.out.p; break; }
+    }
+    GN_TRY(check_launch("forward"));
+  }
+  *y_out = cur; return GN_OK;
+}
+
+// ---------------------------------------------------------------- backward
+// Gradient of one inner Dense of a TransformerBlock at batch level:
+//   gb = sum over all tokens of dz ; gW = Delta^T * X_last with Delta[s] = sum_t dz[s,t], X_last[s] = x[s,T-1]
+static int inner_dense_param_grads(gn_model* m, const float* dz, int B, int T, int out, const float* x, int in, float* gW, float* gb) {
+  Ctx* ctx = &m->ctx->c; float* delta; GN_TRY(ensure(m, S_DELTA, (size_t)B * out, &delta));
+  GN_LAUNCH(ctx, token_sum_kernel, dim3(cdiv(out, 128), B), 128, 0, dz, T, out, delta);
+  GN_TRY(colsum(m, delta, out, B, out, gb, false));
+  return gemm_tn(ctx, B, out, in, delta, out, x + (long)(T - 1) * in, (long)T * in, gW);
+}
+
+static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, const float* gout, float* dx) {
+  Ctx* ctx = &m->ctx->c; const gn_layer_desc& d = l.d;
+  const int T = d.seq_len, D = d.dim, F = d.ff_dim, Hh = d.heads, hd = D / Hh; const int N = B * T; const long ND = (long)N * D;
+  BlockParams bp = block_params(m->params.p + l.p_off, D, F); BlockParams gp = block_params(m->grads.p + l.p_off, D, F);
+  float *dR2, *dM, *comb, *dR1, *dA, *P, *dP; float* st = l.stat.p;
+  GN_TRY(ensure(m, S_ND0, ND, &dR2)); GN_TRY(ensure(m, S_NFF, (size_t)N * F, &dM)); GN_TRY(ensure(m, S_ND1, ND, &comb));
+  GN_TRY(ensure(m, S_ND2, ND, &dR1)); GN_TRY(ensure(m, S_ND3, ND, &dA));
+  GN_TRY(ensure(m, S_ATT0, (size_t)B * Hh * T * T, &P)); GN_TRY(ensure(m, S_ATT1, (size_t)B * Hh * T * T, &dP));
+  float* part; int chunks = std::max(1, std::min(N / 64, 128)); GN_TRY(ensure(m, S_PART2, (size_t)chunks * 2 * std::max(D, F), &part));
+  // LayerNorm 2
+  GN_LAUNCH(ctx, layernorm_pgrad_partial_kernel, dim3(cdiv(D, 128), chunks), 128, 0, gout, l.r2.p, st + 2 * N, st + 3 * N, (long)N, D, part);
+  GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(D, 128), 128, 0, part, chunks, D, (float*)gp.g2, (float*)gp.be2);
+  GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(N, 8), 256, 0, gout, l.r2.p, bp.g2, st + 2 * N, st + 3 * N, dR2, (long)N, D);
+  // ff2 then ff1, token by token in the reference (transformer.go:1238-1250)
+  GN_TRY(inner_dense_param_grads(m, dR2, B, T, D, l.mid.p, F, (float*)gp.w2, (float*)gp.b2));
+  GN_TRY(gemm_nn(ctx, N, D, F, dR2, D, bp.w2, dM, F));
+  { long n = (long)N * F; GN_LAUNCH(ctx, relu_mask_last_token_kernel, ew_grid(ctx, n), 256, 0, dM, l.mid.p, T, F, n); }
+  GN_TRY(inner_dense_param_grads(m, dM, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1));
+  GN_TRY(gemm_nn(ctx, N, F, D, dM, F, bp.w1, comb, D, dR2, D));                          // combined = gradRes2 + W1^T dz1
+  // LayerNorm 1
+  GN_LAUNCH(ctx, layernorm_pgrad_partial_kernel, dim3(cdiv(D, 128), chunks), 128, 0, comb, l.r1.p, st, st + N, (long)N, D, part);
+  GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(D, 128), 128, 0, part, chunks, D, (float*)gp.g1, (float*)gp.be1);
+  GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(N, 8), 256, 0, comb, l.r1.p, bp.g1, st, st + N, dR1, (long)N, D);
+  // output projection
+  GN_TRY(inner_dense_param_grads(m, dR1, B, T, D, l.att.p, D, (float*)gp.wo, (float*)gp.bo));
+  GN_TRY(gemm_nn(ctx, N, D, D, dR1, D, bp.wo, dA, D));
+  // attention: recompute P (transformer.go:610-622), then dP, dS, dQ, dK, dV
+  const long TD = (long)T * D, TT = (long)T * T; const float inv_scale = 1.f / sqrtf((float)hd); const long rows = (long)B * Hh * T;
+  {
+    GemmDesc g; g.M = T; g.N = T; g.K = hd; g.A = l.q.p; g.sa_m = D; g.sa_k = 1; g.B = l.k.p; g.sb_k = 1; g.sb_n = D;
+    g.C = P; g.ldc = T; g.batch1 = B; g.batch2 = Hh; g.a_b1 = TD; g.a_b2 = hd; g.b_b1 = TD; g.b_b2 = hd; g.c_b1 = Hh * TT; g.c_b2 = TT;
+    g.flags = d.causal ? GEMM_SKIP_UPPER : 0; GN_TRY(gemm(ctx, g));
+    GN_LAUNCH(ctx, attn_softmax_kernel, cdiv(rows, 8), 256, 0, P, T, inv_scale, d.causal, rows);
+    g.A = dA; g.B = l.v.p; g.C = dP; GN_TRY(gemm(ctx, g));                               // dP = dA V^T
+    GN_LAUNCH(ctx, attn_ds_kernel, cdiv(rows, 8), 256, 0, P, dP, T, inv_scale, d.causal, rows);   // dP <- dS (scaled)
+  }
+  float *dQ, *dK, *dV;
+  GN_TRY(ensure(m, S_ND0, ND, &dQ)); GN_TRY(ensure(m, S_ND1, ND, &dK)); GN_TRY(ensure(m, S_ND4, ND, &dV));   // dR2 / comb are dead by now
+  {
+    GemmDesc g; g.M = T; g.N = hd; g.K = T; g.batch1 = B; g.batch2 = Hh; g.a_b1 = Hh * TT; g.a_b2 = TT; g.b_b1 = TD; g.b_b2 = hd; g.c_b1 = TD; g.c_b2 = hd; g.ldc = D;
+    g.sb_k = D; g.sb_n = 1;
+    g.A = dP; g.sa_m = T; g.sa_k = 1; g.B = l.k.p; g.C = dQ; g.flags = d.causal ? GEMM_KEND_AT_M0 : 0; GN_TRY(gemm(ctx, g));     // dQ = dS K
+    g.A = dP; g.sa_m = 1; g.sa_k = T; g.B = l.q.p; g.C = dK; g.flags = d.causal ? GEMM_KBEG_AT_M0 : 0; GN_TRY(gemm(ctx, g));     // dK = dS^T Q
+    g.A = P; g.B = dA; g.C = dV; GN_TRY(gemm(ctx, g));                                                                          // dV = P^T dA
+  }
+  // q, k, v projections; gradIn = dq + dk + dv, block input gradient = gradRes1 + gradIn
+  GN_TRY(inner_dense_param_grads(m, dQ, B, T, D, xin, D, (float*)gp.wq, (float*)gp.bq));
+  GN_TRY(inner_dense_param_grads(m, dK, B, T, D, xin, D, (float*)gp.wk, (float*)gp.bk));
+  GN_TRY(inner_dense_param_grads(m, dV, B, T, D, xin, D, (float*)gp.wv, (float*)gp.bv));
+  GN_TRY(gemm_nn(ctx, N, D, D, dQ, D, bp.wq, dx, D, dR1, D));
+  GN_TRY(gemm_nn(ctx, N, D, D, dK, D, bp.wk, dx, D, dx, D));
+  GN_TRY(gemm_nn(ctx, N, D, D, dV, D, bp.wv, dx, D, dx, D));
+  return check_launch("block_backward");
+}
+
+static int lstm_backward(gn_model* m, LayerRT& l, size_t li, int B, const float* xin, const float* gout, int global_batch, int first_sample, float* dx) {
+  Ctx* ctx = &m->ctx->c; const gn_layer_desc& d = l.d; const int H = d.out_size, in = d.in_size, T = d.seq_len;
+  const float* p = m->params.p + l.p_off; const float* Wx = p; const float* Wh = p + (long)4 * H * in; const float* bias = Wh + (long)4 * H * H;
+  int threads = ((H + 31) / 32) * 32;
+  GN_LAUNCH(ctx, lstm_bwd_kernel, B, threads, (size_t)4 * H * sizeof(float), gout, Wh, bias, l.pre_i.p, l.c_all.p, l.dgate.p, T, H, d.return_seq);
+  if (li > 0) GN_TRY(gemm_nn(ctx, B * T, 4 * H, in, l.dgate.p, 4 * H, Wx, dx, in));   // dx_t = Wx^T d_t
+  if (m->ctx->c.world > 1) return fail(GN_ERR_UNSUPPORTED, "LSTM gradient scan is single-GPU in this build");
+  (void)first_sample;
+  int chunk = (global_batch + m->W - 1) / m->W, nchunks = (B + chunk - 1) / chunk;
+  const int R4 = 4 * H, ZW = in + H + 1, rpc = (R4 + SCAN_CLUSTER - 1) / SCAN_CLUSTER;
+  size_t smem = ((size_t)rpc * ZW + rpc + ZW + 33) * sizeof(float);
+  if (smem > 220 * 1024) return fail(GN_ERR_UNSUPPORTED, "LSTM gradient of %d x %d per cluster CTA exceeds shared memory", rpc, ZW);
+  float* scan; GN_TRY(ensure(m, S_SCAN, (size_t)nchunks * R4 * ZW, &scan));
+  GN_CUDA(cudaFuncSetAttribute(lstm_grad_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  cudaLaunchConfig_t cfg{}; cfg.gridDim = dim3(nchunks * SCAN_CLUSTER); cfg.blockDim = dim3(SCAN_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
+  cudaLaunchAttribute at[1]; at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = SCAN_CLUSTER; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  GN_CUDA(cudaLaunchKernelEx(&cfg, lstm_grad_scan_kernel, (const float*)l.dgate.p, xin, (const float*)l.h_all.p, scan, T, in, H, B, chunk, 0));
+  ctx->launches++;
+  // worker gradients are summed in worker order (net.go:694-700)
+  GN_LAUNCH(ctx, colsum_final_kernel, cdiv((long)R4 * ZW, 128), 128, 0, scan, nchunks, R4 * ZW, m->grads.p + l.p_off, 0);
+  return check_launch("lstm_backward");
+}
+
+static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, int global_batch, int first_sample) {
+  Ctx* ctx = &m->ctx->c;
+  const float* g = gloss;
+  float* pp[2] = {nullptr, nullptr}; int flip = 0;
+  size_t maxio = 0; for (auto& l : m->L) maxio = std::max<size_t>(maxio, std::max(l.in_size, l.out_size));
+  GN_TRY(ensure(m, S_G0, (size_t)B * maxio, &pp[0])); GN_TRY(ensure(m, S_G1, (size_t)B * maxio, &pp[1]));
+  for (int li = (int)m->L.size() - 1; li >= 0; li--) {
+    LayerRT& l = m->L[li]; const gn_layer_desc& d = l.d;
+    const float* xin = l.fin;
+    const float* p = m->params.p + l.p_off; float* gr = m->grads.p + l.p_off;
+    float* dx = pp[flip]; bool need_dx = li > 0;
+    switch (d.kind) {
+      case GN_LAYER_DENSE: {
+        const float* W = p; long wn = (long)d.in_size * d.out_size; const float* dz = g;
+        if (d.activation != GN_ACT_LINEAR) {
+          float* dzb; GN_TRY(ensure(m, S_DZ, (size_t)B * d.out_size, &dzb)); long n = (long)B * d.out_size;
+          if (d.activation == GN_ACT_SOFTMAX || d.activation == GN_ACT_LOGSOFTMAX)
+            GN_LAUNCH(ctx, head_jacobian_kernel, B, 256, 0, g, l.out.p, dzb, d.out_size, d.activation == GN_ACT_LOGSOFTMAX ? 1 : 0);
+          else GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, d.activation == GN_ACT_RELU ? l.out.p : l.z.p, dzb, n, d.activation);
+          dz = dzb;
+        }
+        GN_TRY(colsum(m, dz, d.out_size, B, d.out_size, gr + wn, false));
+        GN_TRY(gemm_tn(ctx, B, d.out_size, d.in_size, dz, d.out_size, xin, d.in_size, gr));
+        if (need_dx) { GN_TRY(gemm_nn(ctx, B, d.out_size, d.in_size, dz, d.out_size, W, dx, d.in_size)); g = dx; flip ^= 1; }
+        break; }
+      case GN_LAYER_CONV2D: {
+        ConvShape c{B, d.in_size, d.out_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
+                    (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
+        long n = (long)B * l.out_size; float* dzb; GN_TRY(ensure(m, S_DZ, (size_t)n, &dzb));
+        GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, l.z.p, dzb, n, d.activation);
+        int nW = d.out_size * d.in_size * d.kernel * d.kernel;
+        GN_LAUNCH(ctx, conv2d_wgrad_kernel, nW + d.out_size, 256, 0, dzb, xin, gr, gr + nW, c);
+        if (need_dx) { long ni = (long)B * l.in_size; GN_LAUNCH(ctx, conv2d_dgrad_kernel, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c); g = dx; flip ^= 1; }
+        break; }
+      case GN_LAYER_MAXPOOL2D: {
+        PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
+                    (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
+        GN_CUDA(cudaMemsetAsync(dx, 0, (size_t)B * l.in_size * sizeof(float), ctx->stream));
+        long n = (long)B * l.out_size;
+        GN_LAUNCH(ctx, maxpool_bwd_kernel, ew_grid(ctx, n), 256, 0, g, (const int*)l.idx.p, dx, c);
+        g = dx; flip ^= 1; break; }
+      case GN_LAYER_FLATTEN: break;
+      case GN_LAYER_LSTM_UNROLLED:
+        GN_TRY(lstm_backward(m, l, li, B, xin, g, global_batch, first_sample, dx)); if (need_dx) { g = dx; flip ^= 1; } break;
+      case GN_LAYER_EMBEDDING: {
+        int chunk = (global_batch + m->W - 1) / m->W;
+        GN_LAUNCH(ctx, embedding_bwd_kernel, dim3(d.seq_len, B), 128, 0, g, (const int*)l.idx.p, gr, d.seq_len, d.out_size, first_sample, global_batch, chunk);
+        break; }
+      case GN_LAYER_POSENC:
+        GN_TRY(colsum(m, g, l.out_size, B, l.out_size, gr, false)); break;     // gP = sum over samples; dx = g
+      case GN_LAYER_TRANSFORMER_BLOCK:
+        GN_TRY(block_backward(m, l, B, xin, g, dx)); g = dx; flip ^= 1; break;
+      case GN_LAYER_CLS_POOLING: {
+        long n = (long)B * l.in_size;
+        GN_LAUNCH(ctx, cls_bwd_kernel, ew_grid(ctx, n), 256, 0, g, dx, d.seq_len, d.dim, n); g = dx; flip ^= 1; break; }
+      case GN_LAYER_LAYERNORM: {
+        long rows = (long)B * (l.in_size / d.dim); int chunks = (int)std::max<long>(1, std::min<long>(rows / 64, 128));
+        float* part; GN_TRY(ensure(m, S_PART2, (size_t)chunks * 2 * d.dim, &part));
+        GN_LAUNCH(ctx, layernorm_pgrad_partial_kernel, dim3(cdiv(d.dim, 128), chunks), 128, 0, g, xin, l.stat.p, l.stat.p + rows, rows, d.dim, part);
+        GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(d.dim, 128), 128, 0, part, chunks, d.dim, gr, gr + d.dim);
+        GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(rows, 8), 256, 0, g, xin, p, l.stat.p, l.stat.p + rows, dx, rows, d.dim);
+        g = dx; flip ^= 1; break; }
+    }
+    GN_TRY(check_launch("backward"));
+  }
+  return GN_OK;
+}
+
+// ---------------------------------------------------------------- Adam
+static void adam_coeffs(float lr, float b1, float b2, int t, float* effLR) {
+  // opt.go:237-242: bias terms through float64 pow, rounded to float32; sqrt through float64
+  float bias1 = (float)(1.0 - std::pow((double)b1, (double)t));
+  float bias2 = (float)(1.0 - std::pow((double)b2, (double)t));
+  *effLR = lr * (float)std::sqrt((double)bias2) / bias1;
+}
+static int adam_launch(Ctx* ctx, float* p, const float* g, float* m1, float* v, int64_t n, float lr, float b1, float b2, float eps, int t, float grad_scale) {
+  float effLR; adam_coeffs(lr, b1, b2, t, &effLR);
+  GN_LAUNCH(ctx, adam_kernel, ew_grid(ctx, (n + 3) / 4), 256, 0, p, g, m1, v, (long)n, effLR, b1, b2, 1.f - b1, 1.f - b2, eps, grad_scale);
+  return check_launch("adam");
+}
+
+static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B, int global_batch, int first_sample, float* mean_loss) {
+  Ctx* ctx = &m->ctx->c;
+  if (global_batch <= 0) { global_batch = B; first_sample = 0; }
+  if (B > m->cap) GN_TRY(alloc_activations(m, B));
+  int64_t launches0 = ctx->launches; ctx->gemm_flops = 0; ctx->gemm_launches = 0; ctx->gemm_ms = 0; ctx->ev_used = 0;
+  GN_CUDA(cudaEventRecord(m->ev0, ctx->stream));
+  GN_CUDA(cudaMemsetAsync(m->grads.p, 0, (size_t)m->P * sizeof(float), ctx->stream));     // Network.ClearGradients, net.go:813-823
+  const float* yp;
+  GN_TRY(forward(m, x_dev, B, &yp));
+  GN_LAUNCH(ctx, loss_rows_kernel, B, 256, 0, yp, y_dev, m->lossg.p, m->loss_s.p, m->out_size, m->loss_kind);
+  GN_LAUNCH(ctx, loss_total_kernel, 1, 32, 0, m->loss_s.p, B, m->loss_sum.p);
+  GN_TRY(backward(m, x_dev, B, m->lossg.p, global_batch, first_sample));
+  if (ctx->world > 1) {
+    GN_CUDA(cudaEventRecord(m->ar0, ctx->stream));
+    int rc = ctx->nccl->AllReduce(m->grads.p, m->grads.p, (size_t)m->P, NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->stream);
+    if (rc) return fail(GN_ERR_NCCL, "ncclAllReduce(grads): %s", ctx->nccl->GetErrorString(rc));
+    rc = ctx->nccl->AllReduce(m->loss_sum.p, m->loss_sum.p, 1, NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->stream);
+    if (rc) return fail(GN_ERR_NCCL, "ncclAllReduce(loss): %s", ctx->nccl->GetErrorString(rc));
+    GN_CUDA(cudaEventRecord(m->ar1, ctx->stream));
+  }
+  // Network.Step (net.go:260-284): NewStep() then StepInPlace with t = timestep + 1
+  m->timestep += 1;
+  float inv = (float)(1.0 / (double)global_batch);                                        // net.go:703
+  m->last_inv_batch = inv;
+  GN_TRY(adam_launch(ctx, m->params.p, m->grads.p, m->m1.p, m->v2.p, m->P, m->lr, m->b1, m->b2, m->eps, m->timestep + 1, inv));
+  GN_CUDA(cudaEventRecord(m->ev1, ctx->stream));
+  float hsum = 0.f;
+  GN_CUDA(cudaMemcpyAsync(&hsum, m->loss_sum.p, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  GN_CUDA(cudaStreamSynchronize(ctx->stream));
+  if (mean_loss) *mean_loss = hsum / (float)global_batch;
+  m->stats.kernel_launches = ctx->launches - launches0;
+  cudaEventElapsedTime(&m->stats.step_ms, m->ev0, m->ev1);
+  m->stats.allreduce_ms = 0.f; if (ctx->world > 1) cudaEventElapsedTime(&m->stats.allreduce_ms, m->ar0, m->ar1);
+  m->stats.gemm_flops = ctx->gemm_flops; m->stats.gemm_launches = ctx->gemm_launches; m->stats.gemm_ms = 0.f;
+  if (ctx->profile) { float tot = 0.f; for (size_t i = 0; i < ctx->ev_used; i++) { float ms = 0.f; cudaEventElapsedTime(&ms, ctx->ev_pool[i].first, ctx->ev_pool[i].second); tot += ms; } m->stats.gemm_ms = tot; }
+  int st = 0; GN_CUDA(cudaMemcpy(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (st != 0) { cudaMemset(ctx->d_status, 0, sizeof(int)); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
+  return GN_OK;
+}
+
+static int make_ctx(int device, int rank, int world, const unsigned char* id, gn_ctx** out) {
+  if (!out) return fail(GN_ERR_INVALID_ARG, "out is null");
+  int n = 0; cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0) return fail(GN_ERR_NO_DEVICE, "no CUDA device: %s", cudaGetErrorString(e));
+  if (device < 0 || device >= n) return fail(GN_ERR_INVALID_ARG, "device %d out of range [0,%d)", device, n);
+  GN_CUDA(cudaSetDevice(device));
+  cudaDeviceProp prop; GN_CUDA(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) return fail(GN_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
+  std::unique_ptr<gn_ctx> c(new gn_ctx());
+  c->c.device = device; c->c.rank = rank; c->c.world = world; c->c.sm_count = prop.multiProcessorCount;
+  GN_CUDA(cudaStreamCreateWithFlags(&c->c.stream, cudaStreamNonBlocking));
+  GN_CUDA(cudaMalloc(&c->c.d_status, sizeof(int))); GN_CUDA(cudaMemset(c->c.d_status, 0, sizeof(int)));
+  tc_init(&c->c);
+  if (world > 1) {
+    NcclApi* api = nccl_api(); if (!api) return fail(GN_ERR_NCCL, "libnccl.so.2 could not be loaded");
+    NcclUniqueId uid; memcpy(uid.internal, id, GN_UNIQUE_ID_BYTES);
+    int rc = api->CommInitRank(&c->c.comm, world, uid, rank);
+    if (rc) return fail(GN_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString(rc));
+    c->c.nccl = api;
+  }
+  *out = c.release(); return GN_OK;
+}
+
+}  // namespace gn
+
+using namespace gn;
+
+#define CHECK_MODEL(m) do { if (!(m) || !(m)->alive) return fail(GN_ERR_INVALID_ARG, "model handle is null or destroyed"); } while (0)
+#define USE_DEVICE(m) GN_CUDA(cudaSetDevice((m)->ctx->c.device))
+
+extern "C" {
+
+const char* gn_last_error(void) { return last_error().c_str(); }
+
+int gn_init(int device, gn_ctx** out) { return make_ctx(device, 0, 1, nullptr, out); }
+
+int gn_get_unique_id(unsigned char id[GN_UNIQUE_ID_BYTES]) {
+  if (!id) return fail(GN_ERR_INVALID_ARG, "id is null");
+  NcclApi* api = nccl_api(); if (!api) return fail(GN_ERR_NCCL, "libnccl.so.2 could not be loaded");
+  NcclUniqueId uid; int rc = api->GetUniqueId(&uid); if (rc) return fail(GN_ERR_NCCL, "ncclGetUniqueId: %s", api->GetErrorString(rc));
+  memcpy(id, uid.internal, GN_UNIQUE_ID_BYTES); return GN_OK;
+}
+
+int gn_init_rank(int device, int rank, int world_size, const unsigned char id[GN_UNIQUE_ID_BYTES], gn_ctx** out) {
+  if (world_size < 1 || rank < 0 || rank >= world_size) return fail(GN_ERR_INVALID_ARG, "rank %d / world %d invalid", rank, world_size);
+  if (world_size > 1 && !id) return fail(GN_ERR_INVALID_ARG, "id is null");
+  return make_ctx(device, rank, world_size, id, out);
+}
+
+int gn_shutdown(gn_ctx* ctx) {
+  if (!ctx || !ctx->alive) return GN_OK;
+  cudaSetDevice(ctx->c.device);
+  if (ctx->c.stream) cudaStreamSynchronize(ctx->c.stream);
+  if (ctx->c.comm && ctx->c.nccl) ctx->c.nccl->CommDestroy(ctx->c.comm);
+  for (auto& e : ctx->c.ev_pool) { cudaEventDestroy(e.first); cudaEventDestroy(e.second); }
+  ctx->c.ev_pool.clear();
+  if (ctx->c.d_status) cudaFree(ctx->c.d_status);
+  if (ctx->c.stream) cudaStreamDestroy(ctx->c.stream);
+  ctx->c.comm = nullptr; ctx->c.d_status = nullptr; ctx->c.stream = nullptr; ctx->alive = false;
+  return GN_OK;   // the handle itself stays allocated so that a second call is harmless
+}
+
+int gn_ctx_world_size(gn_ctx* ctx, int* world_size, int* rank) {
+  if (!ctx || !ctx->alive) return fail(GN_ERR_INVALID_ARG, "context is null or shut down");
+  if (world_size) *world_size = ctx->c.world; if (rank) *rank = ctx->c.rank; return GN_OK;
+}
+
+int gn_synchronize(gn_ctx* ctx) {
+  if (!ctx || !ctx->alive) return fail(GN_ERR_INVALID_ARG, "context is null or shut down");
+  GN_CUDA(cudaSetDevice(ctx->c.device)); GN_CUDA(cudaStreamSynchronize(ctx->c.stream)); return GN_OK;
+}
+
+int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int loss_kind, int virtual_workers, gn_model** out) {
+  if (!ctx || !ctx->alive) return fail(GN_ERR_INVALID_ARG, "context is null or shut down");
+  if (!layers || n_layers <= 0 || !out) return fail(GN_ERR_INVALID_ARG, "layers/out is null or n_layers <= 0");
+  if (loss_kind != GN_LOSS_MSE && loss_kind != GN_LOSS_CROSS_ENTROPY) return fail(GN_ERR_UNSUPPORTED, "loss kind %d", loss_kind);
+  GN_CUDA(cudaSetDevice(ctx->c.device));
+  std::unique_ptr<gn_model> m(new gn_model());
+  m->ctx = ctx; m->loss_kind = loss_kind; m->W = virtual_workers < 1 ? 1 : virtual_workers;
+  GN_TRY(plan_layers(m.get(), layers, n_layers));
+  size_t P = (size_t)std::max<int64_t>(m->P, 4);
+  GN_TRY(m->params.alloc(P)); GN_TRY(m->grads.alloc(P)); GN_TRY(m->m1.alloc(P)); GN_TRY(m->v2.alloc(P));
+  GN_CUDA(cudaMemset(m->params.p, 0, P * 4)); GN_CUDA(cudaMemset(m->grads.p, 0, P * 4)); GN_CUDA(cudaMemset(m->m1.p, 0, P * 4)); GN_CUDA(cudaMemset(m->v2.p, 0, P * 4));
+  GN_CUDA(cudaEventCreate(&m->ev0)); GN_CUDA(cudaEventCreate(&m->ev1)); GN_CUDA(cudaEventCreate(&m->ar0)); GN_CUDA(cudaEventCreate(&m->ar1));
+  m->scratch.resize(S_COUNT);
+  *out = m.release(); return GN_OK;
+}
+
+int gn_model_destroy(gn_model* m) {
+  if (!m || !m->alive) return GN_OK;
+  std::lock_guard<std::mutex> lk(m->mu);
+  cudaSetDevice(m->ctx->c.device);
+  if (m->ctx->alive && m->ctx->c.stream) cudaStreamSynchronize(m->ctx->c.stream);
+  m->L.clear(); m->scratch.clear(); m->params.release(); m->grads.release(); m->m1.release(); m->v2.release();
+  m->xin.release(); m->yin.release(); m->lossg.release(); m->loss_s.release(); m->loss_sum.release();
+  if (m->ev0) cudaEventDestroy(m->ev0); if (m->ev1) cudaEventDestroy(m->ev1); if (m->ar0) cudaEventDestroy(m->ar0); if (m->ar1) cudaEventDestroy(m->ar1);
+  m->ev0 = m->ev1 = m->ar0 = m->ar1 = nullptr; m->alive = false; return GN_OK;
+}
+
+int gn_model_param_count(gn_model* m, int64_t* n) { CHECK_MODEL(m); if (!n) return fail(GN_ERR_INVALID_ARG, "n is null"); *n = m->P; return GN_OK; }
+int gn_model_in_size(gn_model* m, int64_t* n) { CHECK_MODEL(m); if (!n) return fail(GN_ERR_INVALID_ARG, "n is null"); *n = m->in_size; return GN_OK; }
+int gn_model_out_size(gn_model* m, int64_t* n) { CHECK_MODEL(m); if (!n) return fail(GN_ERR_INVALID_ARG, "n is null"); *n = m->out_size; return GN_OK; }
+
+int gn_model_set_params(gn_model* m, const float* host, int64_t n) {
+  CHECK_MODEL(m); if (!host || n != m->P) return fail(GN_ERR_INVALID_ARG, "set_params: expected %lld floats, got %lld", (long long)m->P, (long long)n);
+  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  GN_CUDA(cudaMemcpyAsync(m->params.p, host, (size_t)n * 4, cudaMemcpyHostToDevice, m->ctx->c.stream));
+  GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); return GN_OK;
+}
+int gn_model_get_params(gn_model* m, float* host, int64_t n) {
+  CHECK_MODEL(m); if (!host || n != m->P) return fail(GN_ERR_INVALID_ARG, "get_params: expected %lld floats, got %lld", (long long)m->P, (long long)n);
+  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  GN_CUDA(cudaMemcpyAsync(host, m->params.p, (size_t)n * 4, cudaMemcpyDeviceToHost, m->ctx->c.stream));
+  GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); return GN_OK;
+}
+int gn_model_get_grads(gn_model* m, float* host, int64_t n) {
+  CHECK_MODEL(m); if (!host || n != m->P) return fail(GN_ERR_INVALID_ARG, "get_grads: expected %lld floats, got %lld", (long long)m->P, (long long)n);
+  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  GN_CUDA(cudaMemcpyAsync(host, m->grads.p, (size_t)n * 4, cudaMemcpyDeviceToHost, m->ctx->c.stream));
+  GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream));
+  // the device keeps the batch-summed gradient; the 1/batch factor of net.go:702-706 is applied inside the Adam
+  // pass and here, with the same float32 multiplication
+  const float inv = m->last_inv_batch;
+  for (int64_t i = 0; i < n; i++) host[i] *= inv;
+  return GN_OK;
+}
+
+int gn_adam_set(gn_model* m, float lr, float beta1, float beta2, float eps, int timestep) {
+  CHECK_MODEL(m); std::lock_guard<std::mutex> lk(m->mu);
+  // zero betas / eps select the defaults, as Adam.StepInPlace does (opt.go:211-223)
+  m->lr = lr; m->b1 = beta1 == 0.f ? 0.9f : beta1; m->b2 = beta2 == 0.f ? 0.999f : beta2; m->eps = eps == 0.f ? 1e-8f : eps;
+  if (timestep >= 0) m->timestep = timestep; return GN_OK;
+}
+int gn_adam_get_state(gn_model* m, float* m1, float* v, int64_t n, int* timestep) {
+  CHECK_MODEL(m); if (n != m->P) return fail(GN_ERR_INVALID_ARG, "adam state: expected %lld floats", (long long)m->P);
+  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  if (m1) GN_CUDA(cudaMemcpy(m1, m->m1.p, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  if (v) GN_CUDA(cudaMemcpy(v, m->v2.p, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  if (timestep) *timestep = m->timestep; return GN_OK;
+}
+int gn_adam_set_state(gn_model* m, const float* m1, const float* v, int64_t n, int timestep) {
+  CHECK_MODEL(m); if (n != m->P || !m1 || !v) return fail(GN_ERR_INVALID_ARG, "adam state: expected %lld floats", (long long)m->P);
+  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  GN_CUDA(cudaMemcpy(m->m1.p, m1, (size_t)n * 4, cudaMemcpyHostToDevice)); GN_CUDA(cudaMemcpy(m->v2.p, v, (size_t)n * 4, cudaMemcpyHostToDevice));
+  if (timestep >= 0) m->timestep = timestep; return GN_OK;
+}
+
+int gn_train_batch_device(gn_model* m, const float* x_dev, const float* y_dev, int batch, int global_batch, int first_sample, float* mean_loss) {
+  CHECK_MODEL(m); if (!x_dev || !y_dev || batch <= 0) return fail(GN_ERR_INVALID_ARG, "train_batch: null input or batch <= 0");
+  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  return train_step(m, x_dev, y_dev, batch, global_batch, first_sample, mean_loss);
+}
+
+int gn_train_batch(gn_model* m, const float* x, const float* y, int batch, int global_batch, int first_sample, float* mean_loss) {
+  CHECK_MODEL(m); if (!x || !y || batch <= 0) return fail(GN_ERR_INVALID_ARG, "train_batch: null input or batch <= 0");
+  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  if (batch > m->cap) GN_TRY(alloc_activations(m, batch));
+  cudaStream_t s = m->ctx->c.stream;
+  GN_CUDA(cudaMemcpyAsync(m->xin.p, x, (size_t)batch * m->in_size * 4, cudaMemcpyHostToDevice, s));
+  GN_CUDA(cudaMemcpyAsync(m->yin.p, y, (size_t)batch * m->out_size * 4, cudaMemcpyHostToDevice, s));
+  return train_step(m, m->xin.p, m->yin.p, batch, global_batch, first_sample, mean_loss);
+}
+
+int gn_forward_batch(gn_model* m, const float* x, int batch, float* out) {
+  CHECK_MODEL(m); if (!x || !out || batch <= 0) return fail(GN_ERR_INVALID_ARG, "forward_batch: null pointer or batch <= 0");
+  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  if (batch > m->cap) GN_TRY(alloc_activations(m, batch));
+  cudaStream_t s = m->ctx->c.stream;
+  GN_CUDA(cudaMemcpyAsync(m->xin.p, x, (size_t)batch * m->in_size * 4, cudaMemcpyHostToDevice, s));
+  const float* yp; GN_TRY(forward(m, m->xin.p, batch, &yp));
+  GN_CUDA(cudaMemcpyAsync(out, yp, (size_t)batch * m->out_size * 4, cudaMemcpyDeviceToHost, s));
+  GN_CUDA(cudaStreamSynchronize(s)); return GN_OK;
+}
+
+int gn_device_alloc(gn_ctx* ctx, int64_t n, float** dev) {
+  if (!ctx || !ctx->alive || !dev || n <= 0) return fail(GN_ERR_INVALID_ARG, "device_alloc: bad argument");
+  GN_CUDA(cudaSetDevice(ctx->c.device)); cudaError_t e = cudaMalloc(dev, (size_t)n * 4);
+  if (e != cudaSuccess) return fail(GN_ERR_OOM, "cudaMalloc(%lld floats): %s", (long long)n, cudaGetErrorString(e)); return GN_OK;
+}
+int gn_device_free(gn_ctx* ctx, float* dev) { if (!ctx || !ctx->alive) return GN_OK; cudaSetDevice(ctx->c.device); if (dev) cudaFree(dev); return GN_OK; }
+int gn_device_upload(gn_ctx* ctx, float* dev, const float* host, int64_t n) {
+  if (!ctx || !ctx->alive || !dev || !host) return fail(GN_ERR_INVALID_ARG, "device_upload: bad argument");
+  GN_CUDA(cudaSetDevice(ctx->c.device)); GN_CUDA(cudaMemcpyAsync(dev, host, (size_t)n * 4, cudaMemcpyHostToDevice, ctx->c.stream)); GN_CUDA(cudaStreamSynchronize(ctx->c.stream)); return GN_OK;
+}
+int gn_device_download(gn_ctx* ctx, float* host, const float* dev, int64_t n) {
+  if (!ctx || !ctx->alive || !dev || !host) return fail(GN_ERR_INVALID_ARG, "device_download: bad argument");
+  GN_CUDA(cudaSetDevice(ctx->c.device)); GN_CUDA(cudaMemcpyAsync(host, dev, (size_t)n * 4, cudaMemcpyDeviceToHost, ctx->c.stream)); GN_CUDA(cudaStreamSynchronize(ctx->c.stream)); return GN_OK;
+}
+
+int gn_model_last_stats(gn_model* m, gn_step_stats* out) { CHECK_MODEL(m); if (!out) return fail(GN_ERR_INVALID_ARG, "out is null"); *out = m->stats; return GN_OK; }
+int gn_model_set_profiling(gn_model* m, int level) { CHECK_MODEL(m); m->ctx->c.profile = level; return GN_OK; }
+
+int gn_op_gemm_nt(gn_ctx* ctx, int engine, int M, int N, int K, const float* A, const float* B, const float* bias, float* C) {
+  if (!ctx || !ctx->alive || !A || !B || !C || M <= 0 || N <= 0 || K <= 0) return fail(GN_ERR_INVALID_ARG, "op_gemm_nt: bad argument");
+  Ctx* c = &ctx->c; GN_CUDA(cudaSetDevice(c->device));
+  DevBuf dA, dB, dC, db; GN_TRY(dA.alloc((size_t)M * K)); GN_TRY(dB.alloc((size_t)N * K)); GN_TRY(dC.alloc((size_t)M * N)); if (bias) GN_TRY(db.alloc(N));
+  GN_CUDA(cudaMemcpyAsync(dA.p, A, (size_t)M * K * 4, cudaMemcpyHostToDevice, c->stream)); GN_CUDA(cudaMemcpyAsync(dB.p, B, (size_t)N * K * 4, cudaMemcpyHostToDevice, c->stream));
+  if (bias) GN_CUDA(cudaMemcpyAsync(db.p, bias, (size_t)N * 4, cudaMemcpyHostToDevice, c->stream));
+  GemmDesc g; g.M = M; g.N = N; g.K = K; g.A = dA.p; g.sa_m = K; g.sa_k = 1; g.B = dB.p; g.sb_k = 1; g.sb_n = K; g.C = dC.p; g.ldc = N; g.bias = bias ? db.p : nullptr;
+  if (engine == 1) { if (!gemm_tc_supported(c, g)) return fail(GN_ERR_UNSUPPORTED, "tcgen05 engine cannot run this shape (M=%d N=%d K=%d)", M, N, K); GN_TRY(gemm_tc(c, g)); }
+  else GN_TRY(gemm_simt(c, g));
+  GN_CUDA(cudaMemcpyAsync(C, dC.p, (size_t)M * N * 4, cudaMemcpyDeviceToHost, c->stream)); GN_CUDA(cudaStreamSynchronize(c->stream));
+  int st = 0; GN_CUDA(cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (st != 0) { cudaMemset(c->d_status, 0, sizeof(int)); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
+  return GN_OK;
+}
+
+int gn_op_adam(gn_ctx* ctx, float* params, const float* grads, float* m1, float* v, int64_t n, float lr, float beta1, float beta2, float eps, int t, float grad_scale) {
+  if (!ctx || !ctx->alive || !params || !grads || !m1 || !v || n <= 0) return fail(GN_ERR_INVALID_ARG, "op_adam: bad argument");
+  Ctx* c = &ctx->c; GN_CUDA(cudaSetDevice(c->device));
+  DevBuf dp, dg, dm, dv; size_t nn = (size_t)n; GN_TRY(dp.alloc(nn + 4)); GN_TRY(dg.alloc(nn + 4)); GN_TRY(dm.alloc(nn + 4)); GN_TRY(dv.alloc(nn + 4));
+  GN_CUDA(cudaMemcpy(dp.p, params, nn * 4, cudaMemcpyHostToDevice)); GN_CUDA(cudaMemcpy(dg.p, grads, nn * 4, cudaMemcpyHostToDevice));
+  GN_CUDA(cudaMemcpy(dm.p, m1, nn * 4, cudaMemcpyHostToDevice)); GN_CUDA(cudaMemcpy(dv.p, v, nn * 4, cudaMemcpyHostToDevice));
+  GN_TRY(adam_launch(c, dp.p, dg.p, dm.p, dv.p, n, lr, beta1, beta2, eps, t, grad_scale));
+  GN_CUDA(cudaStreamSynchronize(c->stream));
+  GN_CUDA(cudaMemcpy(params, dp.p, nn * 4, cudaMemcpyDeviceToHost)); GN_CUDA(cudaMemcpy(m1, dm.p, nn * 4, cudaMemcpyDeviceToHost)); GN_CUDA(cudaMemcpy(v, dv.p, nn * 4, cudaMemcpyDeviceToHost));
+  return GN_OK;
+}
+
+}  // extern "C"

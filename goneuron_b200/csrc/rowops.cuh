@@ -1,0 +1,275 @@
+// rowops.cuh -- the memory-bound kernels of the training step: activations and their
+// derivatives, (log-)softmax heads with the reference's loss gradients, LayerNorm,
+// embedding / positional table / CLS pooling, the attention row kernels, reductions over
+// samples and tokens, and the fused Adam update.  All are coalesced, 128-bit where the
+// shape allows, and reduce with warp shuffles.
+#pragma once
+#include "common.cuh"
+
+namespace gn {
+
+// ---------------------------------------------------------------- activations
+// reference: internal/activations/activations.go:25-58, :135-143 (float64 libm then rounded)
+__device__ __forceinline__ float act_fwd(int act, float x) {
+  switch (act) {
+    case GN_ACT_RELU: return x > 0.f ? x : 0.f;
+    case GN_ACT_SIGMOID: return 1.f / (1.f + (float)exp((double)-x));
+    case GN_ACT_TANH: return (float)tanh((double)x);
+    default: return x;
+  }
+}
+__device__ __forceinline__ float act_der(int act, float x) {
+  switch (act) {
+    case GN_ACT_RELU: return x > 0.f ? 1.f : 0.f;
+    case GN_ACT_SIGMOID: { float s = 1.f / (1.f + (float)exp((double)-x)); return s * (1.f - s); }
+    case GN_ACT_TANH: { float t = (float)tanh((double)x); return 1.f - t * t; }
+    default: return 1.f;
+  }
+}
+__global__ void act_forward_kernel(const float* __restrict__ z, float* __restrict__ a, long n, int act) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) a[i] = act_fwd(act, z[i]);
+}
+// dz = dA * act'(z)   (Dense.Backward default branch, layer.go:563-567; Conv2D.Backward conv2d.go:1133)
+__global__ void act_backward_kernel(const float* __restrict__ dA, const float* __restrict__ z, float* __restrict__ dz, long n, int act) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) dz[i] = dA[i] * act_der(act, z[i]);
+}
+
+// ---------------------------------------------------------------- softmax heads
+// One block per row.  reference: activations.go:160-183 / :204-236
+__global__ void softmax_rows_kernel(const float* __restrict__ z, float* __restrict__ out, int n, int log_mode) {
+  __shared__ float red[33];
+  const float* zr = z + (long)blockIdx.x * n; float* o = out + (long)blockIdx.x * n;
+  float mx = -INFINITY;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) mx = fmaxf(mx, zr[i]);
+  mx = block_max(mx, red);
+  float s = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) s += expf(zr[i] - mx);
+  s = block_sum(s, red);
+  if (log_mode) { float ls = logf(s); for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = zr[i] - mx - ls; }
+  else for (int i = threadIdx.x; i < n; i += blockDim.x) o[i] = expf(zr[i] - mx) / s;
+}
+
+// Per-sample loss value and dL/dy.  reference: loss.go:53-68,91-105 (MSE), :120-140,165-178 (CrossEntropy:
+// value = -sum y*log(max(p,1e-10)); gradient returned as p - y).
+__global__ void loss_rows_kernel(const float* __restrict__ p, const float* __restrict__ y, float* __restrict__ grad,
+                                 float* __restrict__ loss, int n, int kind) {
+  __shared__ float red[33];
+  const long off = (long)blockIdx.x * n;
+  float s = 0.f;
+  if (kind == GN_LOSS_MSE) {
+    float f = 2.f / (float)n;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) { float d = p[off + i] - y[off + i]; s += d * d; grad[off + i] = f * d; }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) loss[blockIdx.x] = s / (float)n;
+  } else {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+      float pr = p[off + i], yy = y[off + i];
+      grad[off + i] = pr - yy;
+      if (yy != 0.f) s -= yy * logf(fmaxf(pr, 1e-10f));
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) loss[blockIdx.x] = s;
+  }
+}
+
+// Dense.Backward for a Softmax head (layer.go:516-528):  dz_k = sum_i g_i p_i (delta_ik - p_k) = p_k (g_k - sum_i g_i p_i)
+// and for a LogSoftmax head (layer.go:547-559):          dz_k = sum_i g_i (delta_ik - e^{l_k})  = g_k - e^{l_k} sum_i g_i
+__global__ void head_jacobian_kernel(const float* __restrict__ g, const float* __restrict__ out, float* __restrict__ dz, int n, int log_mode) {
+  __shared__ float red[33];
+  const long off = (long)blockIdx.x * n;
+  float s = 0.f;
+  if (log_mode) for (int i = threadIdx.x; i < n; i += blockDim.x) s += g[off + i];
+  else for (int i = threadIdx.x; i < n; i += blockDim.x) s += g[off + i] * out[off + i];
+  s = block_sum(s, red);
+  if (log_mode) for (int i = threadIdx.x; i < n; i += blockDim.x) dz[off + i] = g[off + i] - expf(out[off + i]) * s;
+  else for (int i = threadIdx.x; i < n; i += blockDim.x) dz[off + i] = out[off + i] * (g[off + i] - s);
+}
+
+// mean loss = sum_s loss_s / global_batch; sequential like net.go:711-716 (one thread: B is small)
+__global__ void loss_total_kernel(const float* __restrict__ loss, int n, float* __restrict__ out_sum) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) { float s = 0.f; for (int i = 0; i < n; i++) s += loss[i]; out_sum[0] = s; }
+}
+
+// ---------------------------------------------------------------- reductions
+// out[c] (=|+=) sum_r in[r*ld + c], rows in `chunks` slabs, partials reduced in slab order.
+__global__ void colsum_partial_kernel(const float* __restrict__ in, long ld, int R, int C, float* __restrict__ part) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= C) return;
+  int chunks = gridDim.y, per = (R + chunks - 1) / chunks, r0 = blockIdx.y * per, r1 = min(R, r0 + per);
+  float s = 0.f;
+  for (int r = r0; r < r1; r++) s += in[(long)r * ld + c];
+  part[(long)blockIdx.y * C + c] = s;
+}
+__global__ void colsum_final_kernel(const float* __restrict__ part, int chunks, int C, float* __restrict__ out, int accumulate) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= C) return;
+  float s = 0.f;
+  for (int k = 0; k < chunks; k++) s += part[(long)k * C + c];
+  out[c] = accumulate ? out[c] + s : s;
+}
+// delta[s, c] = sum_t in[s, t, c]   ([B,T,C] -> [B,C]); the reference adds per-token terms one token after another.
+__global__ void token_sum_kernel(const float* __restrict__ in, int T, int C, float* __restrict__ out) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= C) return;
+  const float* p = in + (long)blockIdx.y * T * C + c;
+  float s = 0.f;
+  for (int t = 0; t < T; t++) s += p[(long)t * C];
+  out[(long)blockIdx.y * C + c] = s;
+}
+
+// ---------------------------------------------------------------- LayerNorm
+// One warp per row.  reference: layernorm.go:268-301
+__global__ void layernorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                     float* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ std_out, long rows, int n, float eps) {
+  long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if (row >= rows) return;
+  int lane = threadIdx.x & 31;
+  const float* xr = x + row * n; float* yr = y + row * n;
+  float s = 0.f;
+  for (int i = lane; i < n; i += 32) s += xr[i];
+  float mean = warp_sum(s) / (float)n;
+  float ss = 0.f;
+  for (int i = lane; i < n; i += 32) { float d = xr[i] - mean; ss += d * d; }
+  float var = warp_sum(ss) / (float)n;
+  float sd = sqrtf(var + eps);
+  for (int i = lane; i < n; i += 32) yr[i] = gamma[i] * ((xr[i] - mean) / sd) + beta[i];
+  if (lane == 0) { mean_out[row] = mean; std_out[row] = sd; }
+}
+// reference: layernorm.go:389-417 -- the second term is divided by N*std*std (not std^3).
+// dx may alias g.
+__global__ void layernorm_bwd_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
+                                     const float* __restrict__ mean_in, const float* __restrict__ std_in, float* dx, long rows, int n) {
+  long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if (row >= rows) return;
+  int lane = threadIdx.x & 31;
+  const float* xr = x + row * n; const float* gr = g + row * n; float* dr = dx + row * n;
+  float mean = mean_in[row], sd = std_in[row];
+  float sg = 0.f, sgx = 0.f;
+  for (int i = lane; i < n; i += 32) { float q = gr[i] * gamma[i]; sg += q; sgx += q * (xr[i] - mean); }
+  sg = warp_sum(sg); sgx = warp_sum(sgx);
+  float fn = (float)n;
+  for (int i = lane; i < n; i += 32) {
+    float q = gr[i] * gamma[i], d = xr[i] - mean;
+    float v = (q - sg / fn) / sd;
+    v -= (d * sgx) / (fn * sd * sd);
+    dr[i] = v;
+  }
+}
+// gGamma[c] += sum_r g*(x-mean)/std ; gBeta[c] += sum_r g     (layernorm.go:421-433)
+__global__ void layernorm_pgrad_partial_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ mean_in,
+                                               const float* __restrict__ std_in, long rows, int n, float* __restrict__ part) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= n) return;
+  long chunks = gridDim.y, per = (rows + chunks - 1) / chunks, r0 = blockIdx.y * per, r1 = min(rows, r0 + per);
+  float sgam = 0.f, sbet = 0.f;
+  for (long r = r0; r < r1; r++) { float gg = g[r * n + c]; sgam += gg * ((x[r * n + c] - mean_in[r]) / std_in[r]); sbet += gg; }
+  part[((long)blockIdx.y * 2) * n + c] = sgam; part[((long)blockIdx.y * 2 + 1) * n + c] = sbet;
+}
+__global__ void layernorm_pgrad_final_kernel(const float* __restrict__ part, int chunks, int n, float* __restrict__ gGamma, float* __restrict__ gBeta) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= n) return;
+  float a = 0.f, b = 0.f;
+  for (int k = 0; k < chunks; k++) { a += part[((long)k * 2) * n + c]; b += part[((long)k * 2 + 1) * n + c]; }
+  gGamma[c] += a; gBeta[c] += b;
+}
+
+// ---------------------------------------------------------------- embedding / positional / CLS
+// out[s,t,:] = E[floor(id)] (+ P[t,:])   reference: embedding.go:120-136, transformer.go:80-82
+__global__ void embedding_fwd_kernel(const float* __restrict__ ids, const float* __restrict__ E, const float* __restrict__ P,
+                                     float* __restrict__ out, long tokens, int T, int d, int V, int* __restrict__ idx_out) {
+  long tok = blockIdx.x; if (tok >= tokens) return;
+  int id = (int)floorf(ids[tok]); id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  if (threadIdx.x == 0 && idx_out) idx_out[tok] = id;
+  const float* e = E + (long)id * d; float* o = out + tok * d;
+  if (P) { const float* p = P + (long)(tok % T) * d; for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = e[i] + p[i]; }
+  else for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = e[i];
+}
+__global__ void posenc_fwd_kernel(const float* __restrict__ x, const float* __restrict__ P, float* __restrict__ out, long total, long per_sample) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) out[i] = x[i] + P[i % per_sample];
+}
+// Embedding.Backward zeroes its whole gradient at every call (embedding.go:151-154), so only the last
+// sample of each worker chunk reaches the table: scatter-add the rows of exactly those samples.
+__global__ void embedding_bwd_kernel(const float* __restrict__ g, const int* __restrict__ idx, float* __restrict__ gE, int T, int d,
+                                     int first_sample, int global_batch, int chunk) {
+  int s = blockIdx.y, gidx = first_sample + s;
+  bool last = ((gidx + 1) % chunk == 0) || (gidx == global_batch - 1);
+  if (!last) return;
+  int t = blockIdx.x; long tok = (long)s * T + t;
+  float* dst = gE + (long)idx[tok] * d; const float* src = g + tok * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(dst + i, src[i]);
+}
+// CLSPooling: y[s,:] = x[s,0,:]; backward: zeros except token 0   transformer.go:1684, :1715-1724
+__global__ void cls_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int T, int d) {
+  const float* src = x + (long)blockIdx.x * T * d; float* dst = y + (long)blockIdx.x * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = src[i];
+}
+__global__ void cls_bwd_kernel(const float* __restrict__ g, float* __restrict__ dx, int T, int d, long total) {
+  long per = (long)T * d;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    long s = i / per, r = i % per;
+    dx[i] = r < d ? g[s * d + r] : 0.f;
+  }
+}
+
+// ---------------------------------------------------------------- attention row kernels
+// P[i, :] = softmax over j <= i of S[i,j] * inv_scale, zeros for j > i.  reference: transformer.go:470-491
+// (masked scores are -1e9 before the softmax, whose exponentials are exactly 0 in fp32).
+// One warp per row; rows are [batch*heads*T].
+__global__ void attn_softmax_kernel(float* __restrict__ S, int T, float inv_scale, int causal, long rows) {
+  long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if (row >= rows) return;
+  int lane = threadIdx.x & 31; int i = (int)(row % T); int lim = causal ? i + 1 : T;
+  float* r = S + row * T;
+  float mx = -INFINITY;
+  for (int j = lane; j < lim; j += 32) mx = fmaxf(mx, r[j] * inv_scale);
+  mx = warp_max(mx);
+  float s = 0.f;
+  for (int j = lane; j < lim; j += 32) s += expf(r[j] * inv_scale - mx);
+  s = warp_sum(s);
+  for (int j = lane; j < T; j += 32) r[j] = j < lim ? expf(r[j] * inv_scale - mx) / s : 0.f;
+}
+// dS[i,j] = P[i,j] * (dP[i,j] - sum_k dP[i,k] P[i,k]) * inv_scale for j <= i, else 0.  transformer.go:625-648
+__global__ void attn_ds_kernel(const float* __restrict__ P, float* __restrict__ dP, int T, float inv_scale, int causal, long rows) {
+  long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if (row >= rows) return;
+  int lane = threadIdx.x & 31; int i = (int)(row % T); int lim = causal ? i + 1 : T;
+  const float* p = P + row * T; float* d = dP + row * T;
+  float s = 0.f;
+  for (int j = lane; j < lim; j += 32) s += d[j] * p[j];
+  s = warp_sum(s);
+  for (int j = lane; j < T; j += 32) d[j] = j < lim ? p[j] * (d[j] - s) * inv_scale : 0.f;
+}
+// dZ1[s,t,c] = dM[s,t,c] * 1[M[s,T-1,c] > 0]: inside a TransformerBlock every token's ff1.Backward uses
+// the pre-activation of the LAST token (layer.go:563-567 via transformer.go:1238-1250).
+__global__ void relu_mask_last_token_kernel(float* __restrict__ dM, const float* __restrict__ M, int T, int C, long total) {
+  long per = (long)T * C;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    long s = i / per; int c = (int)(i % C);
+    if (!(M[s * per + (long)(T - 1) * C + c] > 0.f)) dM[i] = 0.f;
+  }
+}
+
+// ---------------------------------------------------------------- misc elementwise
+__global__ void add3_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ c, float* __restrict__ out, long n) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = a[i] + b[i] + (c ? c[i] : 0.f);
+}
+__global__ void scale_kernel(float* __restrict__ x, long n, float s) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) x[i] *= s;
+}
+
+// ---------------------------------------------------------------- Adam
+// reference: opt.go:237-251.  Every operation is rounded separately (no fused multiply-add), as the Go
+// code does, so that the update is bit-identical to the CPU path for identical gradients.
+//   g' = g * grad_scale (the 1/batch averaging of net.go:702-706, folded into this pass)
+//   m = b1*m + (1-b1)*g' ; v = b2*v + (1-b2)*g'*g' ; p -= effLR * m / (sqrt(v) + eps)
+__global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v, long n,
+                            float effLR, float b1, float b2, float omb1, float omb2, float eps, float grad_scale) {
+  long n4 = n >> 2;
+  float4* p4 = reinterpret_cast<float4*>(p); const float4* g4 = reinterpret_cast<const float4*>(g);
+  float4* m4 = reinterpret_cast<float4*>(m); float4* v4 = reinterpret_cast<float4*>(v);
+  auto upd = [&](float& pp, float gg, float& mm, float& vv) {
+    float gs = __fmul_rn(gg, grad_scale);
+    mm = __fadd_rn(__fmul_rn(b1, mm), __fmul_rn(omb1, gs));
+    vv = __fadd_rn(__fmul_rn(b2, vv), __fmul_rn(__fmul_rn(omb2, gs), gs));
+    pp = __fsub_rn(pp, __fdiv_rn(__fmul_rn(effLR, mm), __fadd_rn(__fsqrt_rn(vv), eps)));
+  };
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+    float4 P = p4[i], G = g4[i], M = m4[i], V = v4[i];
+    upd(P.x, G.x, M.x, V.x); upd(P.y, G.y, M.y, V.y); upd(P.z, G.z, M.z, V.z); upd(P.w, G.w, M.w, V.w);
+    p4[i] = P; m4[i] = M; v4[i] = V;
+  }
+  for (long i = (n4 << 2) + blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) upd(p[i], g[i], m[i], v[i]);
+}
+
+}  // namespace gn

