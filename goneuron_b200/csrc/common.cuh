@@ -41,6 +41,7 @@ struct Ctx {
   int* d_status = nullptr;         // device word set by kernels whose bounded waits gave up
   bool tc_ok = false;              // tcgen05 engine usable (driver entry point for tensor maps found)
   void* encode_tiled = nullptr;    // cuTensorMapEncodeTiled
+  cudaEvent_t t0 = nullptr, t1 = nullptr;   // gn_timer_start / gn_timer_stop
 };
 
 inline unsigned cdiv(long a, long b) { return (unsigned)((a + b - 1) / b); }

@@ -14,6 +14,7 @@
 //  * Embedding gradient: only the last sample of each worker chunk (embedding.go:151-154);
 //  * LSTM: see conv_lstm.cuh.
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 
@@ -38,7 +39,8 @@ static int gemm(Ctx* ctx, const GemmDesc& g) {
     GN_CUDA(cudaEventRecord(e0, ctx->stream));
   }
   int rc;
-  if (gemm_tc_eligible(ctx, g)) rc = gemm_tc(ctx, g);
+  static const bool force_simt = [] { const char* e = getenv("GONEURON_CUDA_ENGINE"); return e && strcmp(e, "simt") == 0; }();
+  if (!force_simt && gemm_tc_eligible(ctx, g)) rc = gemm_tc(ctx, g);
   else rc = gemm_simt(ctx, g);
   if (ctx->profile) { GN_CUDA(cudaEventRecord(e1, ctx->stream)); }
   double nb = (double)g.batch1 * g.batch2;
@@ -576,6 +578,7 @@ int gn_shutdown(gn_ctx* ctx) {
   for (auto& e : ctx->c.ev_pool) { cudaEventDestroy(e.first); cudaEventDestroy(e.second); }
   ctx->c.ev_pool.clear();
   if (ctx->c.d_status) cudaFree(ctx->c.d_status);
+  if (ctx->c.t0) { cudaEventDestroy(ctx->c.t0); cudaEventDestroy(ctx->c.t1); ctx->c.t0 = ctx->c.t1 = nullptr; }
   if (ctx->c.stream) cudaStreamDestroy(ctx->c.stream);
   ctx->c.comm = nullptr; ctx->c.d_status = nullptr; ctx->c.stream = nullptr; ctx->alive = false;
   return GN_OK;   // the handle itself stays allocated so that a second call is harmless
@@ -589,6 +592,19 @@ int gn_ctx_world_size(gn_ctx* ctx, int* world_size, int* rank) {
 int gn_synchronize(gn_ctx* ctx) {
   if (!ctx || !ctx->alive) return fail(GN_ERR_INVALID_ARG, "context is null or shut down");
   GN_CUDA(cudaSetDevice(ctx->c.device)); GN_CUDA(cudaStreamSynchronize(ctx->c.stream)); return GN_OK;
+}
+
+int gn_timer_start(gn_ctx* ctx) {
+  if (!ctx || !ctx->alive) return fail(GN_ERR_INVALID_ARG, "context is null or shut down");
+  GN_CUDA(cudaSetDevice(ctx->c.device));
+  if (!ctx->c.t0) { GN_CUDA(cudaEventCreate(&ctx->c.t0)); GN_CUDA(cudaEventCreate(&ctx->c.t1)); }
+  GN_CUDA(cudaEventRecord(ctx->c.t0, ctx->c.stream)); return GN_OK;
+}
+int gn_timer_stop(gn_ctx* ctx, float* ms) {
+  if (!ctx || !ctx->alive || !ms || !ctx->c.t0) return fail(GN_ERR_INVALID_ARG, "timer not started");
+  GN_CUDA(cudaSetDevice(ctx->c.device));
+  GN_CUDA(cudaEventRecord(ctx->c.t1, ctx->c.stream)); GN_CUDA(cudaEventSynchronize(ctx->c.t1));
+  GN_CUDA(cudaEventElapsedTime(ms, ctx->c.t0, ctx->c.t1)); return GN_OK;
 }
 
 int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int loss_kind, int virtual_workers, gn_model** out) {

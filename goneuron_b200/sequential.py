@@ -41,6 +41,14 @@ class Device:
     def synchronize(self):
         _lib.check(_lib.load().gn_synchronize(self.handle))
 
+    def timer_start(self):
+        _lib.check(_lib.load().gn_timer_start(self.handle))
+
+    def timer_stop(self):
+        ms = C.c_float()
+        _lib.check(_lib.load().gn_timer_stop(self.handle, C.byref(ms)))
+        return ms.value
+
     def alloc(self, host_array):
         """Copies a host array into device memory; returns an opaque device pointer (freed by free())."""
         a = _f32(host_array)

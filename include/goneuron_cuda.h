@@ -111,6 +111,10 @@ int gn_init_rank(int device, int rank, int world_size,
 int gn_shutdown(gn_ctx* ctx);                 /* idempotent; mirrors MetalDevice.Close */
 int gn_ctx_world_size(gn_ctx* ctx, int* world_size, int* rank);
 int gn_synchronize(gn_ctx* ctx);              /* drains the context's stream (metal.go:199 waitForMetal) */
+/* CUDA-event stopwatch on the stream every kernel of this context is launched on: start records an
+ * event, stop records a second one, waits for it and returns the device time between the two. */
+int gn_timer_start(gn_ctx* ctx);
+int gn_timer_stop(gn_ctx* ctx, float* ms);
 const char* gn_last_error(void);
 
 /* ---- model ------------------------------------------------------------- */
