@@ -13,7 +13,11 @@
 //   warps 2-5  epilogue: tcgen05.ld of the accumulator, bias / residual / ReLU, transposed through
 //              shared memory so that global stores are 128-byte coalesced
 //
-// Tile 128 x 256 x 32, 2 stages of 96 KB; accumulator 128 lanes x 256 columns of TMEM.
+// Tile 128 x 256 x 32, 2 stages of 96 KB.  Two accumulators of 128 lanes x 256 columns fill the 512 TMEM
+// columns: the hi*hi products go to one, the small cross terms (hi*lo, lo*hi) to the other, and the epilogue
+// adds them.  The tensor core truncates when it aligns a product sum to the running accumulator, an error
+// proportional to the accumulator's magnitude per MMA; keeping the cross terms out of the large accumulator
+// cuts the number of such truncations on it by three.
 // Every mbarrier wait is bounded; a wait that gives up sets the context's status word and the kernel
 // still runs to its end (TMEM is always released).
 #pragma once
@@ -68,6 +72,15 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
+        "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
+        "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+
 struct TcEpilogue {
   float* C; long ldc; const float* bias; const float* R; long ldr; int act; int M, N, K; int* status;
 };
@@ -90,7 +103,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)TC_BN) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * TC_BN)) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -127,9 +140,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
 #pragma unroll
         for (int k = 0; k < TC_BK / 8; k++) {
           const uint64_t adv = (uint64_t)((k * 8 * 4) >> 4);          // 8 tf32 = 32 bytes along K inside the swizzle atom
-          tc_mma_tf32(tmem_base, alo + adv, bhi + adv, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          tc_mma_tf32(tmem_base, ahi + adv, blo + adv, idesc, 1u);
-          tc_mma_tf32(tmem_base, ahi + adv, bhi + adv, idesc, 1u);
+          const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
+          tc_mma_tf32(tmem_base + TC_BN, alo + adv, bhi + adv, idesc, acc);     // cross terms -> second accumulator
+          tc_mma_tf32(tmem_base + TC_BN, ahi + adv, blo + adv, idesc, 1u);
+          tc_mma_tf32(tmem_base, ahi + adv, bhi + adv, idesc, acc);             // main term
         }
         tc_commit(empty0 + 8 * s);           // frees this stage once the MMAs above have read it
       }
@@ -151,15 +165,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
     for (int c = 0; c < TC_BN / 32; c++) {
       const int col0 = n0 + c * 32;
       if (col0 >= ep.N) break;
-      uint32_t r[32];
+      uint32_t r[32], q[32];
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
-      asm volatile(
-          "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]),
-            "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]),
-            "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-          : "r"(taddr) : "memory");
+      tmem_ld32(taddr, r);
+      tmem_ld32(taddr + TC_BN, q);
       asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+      for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
 #pragma unroll
       for (int j = 0; j < 32; j++) tile[lane * 33 + j] = __uint_as_float(r[j]);     // thread = row, conflict-free (stride 33)
       __syncwarp();
@@ -181,7 +193,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)TC_BN) : "memory");
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * TC_BN)) : "memory");
 }
 
 // ------------------------------------------------------------------ operand split (memory-bound)
