@@ -160,10 +160,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="transformer_large", choices=sorted(WORKLOADS))
+    ap.add_argument("--global-batch", type=int, default=0, help="override the global batch (profiling a smaller case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
-    workload = WORKLOADS[args.workload]
+    workload = dict(WORKLOADS[args.workload])
+    if args.global_batch > 0:
+        workload["global_batch"] = args.global_batch
     if args.impl == "reference":
         return run_reference(args, workload)
 
