@@ -755,3 +755,5 @@ int gn_op_adam(gn_ctx* ctx, float* params, const float* grads, float* m1, float*
 }
 
 }  // extern "C"
+
+#include "gemm_static.cuh"

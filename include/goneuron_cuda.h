@@ -198,6 +198,19 @@ int gn_op_gemm_nt(gn_ctx* ctx, int engine, int M, int N, int K,
 int gn_op_adam(gn_ctx* ctx, float* params, const float* grads, float* m1, float* v,
                int64_t n, float lr, float beta1, float beta2, float eps, int t, float grad_scale);
 
+/* The same product as gn_op_gemm_nt with engine 1 (C = A B^T + bias on the tensor cores), for callers that
+ * must not allocate device memory: hosts whose own pool already owns all of HBM, and hosts with a per-step
+ * latency budget (cudaMalloc / cudaFree lock the allocator, cudaFree waits for the device).  It has no
+ * counterpart in the reference.  A, B, bias (may be NULL) and C are DEVICE pointers supplied by the caller
+ * (A [M,K], B [N,K], C [M,N], row-major, dense); the operand planes live in a fixed 16 MiB array inside the
+ * library image, which every GPU that loads the library holds until the process exits.  Limit:
+ * 2*(M+N)*roundup4(K) <= 4 Mi floats, else GN_ERR_INVALID_ARG.  The entry point calls no cudaMalloc / cudaFree.
+ * The first call on each device resolves the array's device address; make it before any stream capture.
+ * All calls on one GPU share the array (it keeps the last call's planes; each call rewrites what it reads):
+ * calls that overlap on the GPU race, so issue them one after the other. */
+int gn_op_gemm_nt_static(gn_ctx* ctx, int M, int N, int K, const float* A_dev, const float* B_dev,
+                         const float* bias_dev, float* C_dev);
+
 #ifdef __cplusplus
 }
 #endif
