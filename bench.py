@@ -196,11 +196,10 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    from goneuron_b200.sharding import shard_bounds
     GB = workload["global_batch"]
-    if GB % world:
-        raise SystemExit(f"global batch {GB} not divisible by {world} ranks")
-    B = GB // world
-    first = rank * B
+    first, last = shard_bounds(GB, rank, world)
+    B = last - first
     layers, loss_kind, _, lr = configs.build(workload["name"], **workload["kw"])
     rng = np.random.Generator(np.random.PCG64(configs.SEEDS[workload["name"]]))
     params = configs.init_params(layers, rng)

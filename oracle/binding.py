@@ -35,7 +35,7 @@ def lib():
         L.gno_param_count.argtypes = [C.c_void_p, C.c_int, i64p, i64p, i64p]
         L.gno_train_batch.argtypes = [C.c_void_p, C.c_int, C.c_int, f32p, f32p, f32p, f32p, C.POINTER(C.c_int),
                                       C.c_float, C.c_float, C.c_float, C.c_float, f32p, f32p, C.c_int, C.c_int,
-                                      C.c_int, C.c_int, C.c_int, f32p, C.POINTER(C.c_double)]
+                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.POINTER(C.c_double)]
         L.gno_forward_batch.argtypes = [C.c_void_p, C.c_int, f32p, f32p, C.c_int, f32p, C.c_int, C.c_int]
         L.gno_activation.argtypes = [C.c_int, f32p, C.c_int]
         L.gno_activation_deriv.argtypes = [C.c_int, f32p, C.c_int]
@@ -79,7 +79,7 @@ class OracleState:
         self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
         self.seconds = 0.0
 
-    def train_batch(self, x, y, W=1, threads=1, precision=64, step=True):
+    def train_batch(self, x, y, W=1, threads=1, precision=64, step=True, global_batch=0, first_sample=0):
         x, y = _f32(x), _f32(y)
         batch = x.shape[0]
         arr = layers_to_array(self.layers)
@@ -88,7 +88,7 @@ class OracleState:
         sec = C.c_double()
         rc = lib().gno_train_batch(arr, len(self.layers), self.loss_kind, _p(self.params), _p(self.grads), _p(self.m),
                                    _p(self.v), C.byref(ts), self.lr, self.beta1, self.beta2, self.eps, _p(x), _p(y), batch,
-                                   W, threads, precision, 1 if step else 0, C.byref(loss), C.byref(sec))
+                                   W, threads, precision, 1 if step else 0, global_batch, first_sample, C.byref(loss), C.byref(sec))
         if rc:
             raise ValueError(lib().gno_last_error().decode())
         self.timestep = ts.value

@@ -702,6 +702,7 @@ struct TrainArgs {
   float* params; float* grads_out; float* m; float* v; int* timestep;
   float lr, b1, b2, eps;
   const float* x; const float* y; int batch; int W; int threads; int do_step;
+  int global_batch; int first_sample;   // this call's samples are [first_sample, first_sample+batch) of a global batch (one rank's shard)
   float* mean_loss; double* seconds;
 };
 
@@ -711,12 +712,18 @@ template <class R> int train_batch_impl(const TrainArgs& a) {
   Net<R> proto;
   if (!Net<R>::build(a.layers, a.n_layers, proto)) return GN_ERR_INVALID_ARG;
   const int64_t P = proto.n_params; const int B = a.batch, in = proto.in_size, out = proto.out_size;
-  int W = std::max(1, std::min(a.W, B));
+  const int GB = a.global_batch > 0 ? a.global_batch : B, first = a.global_batch > 0 ? a.first_sample : 0;
+  int W = std::max(1, std::min(a.W, GB));
   std::vector<R> params(P); for (int64_t i = 0; i < P; i++) params[i] = (R)a.params[i];
-  // virtual-worker chunks (net.go:621-633)
-  struct Chunk { int s, e; };
-  std::vector<Chunk> chunks; int cs = (B + W - 1) / W;
-  for (int w = 0; w < W; w++) { int s = w * cs, e = std::min(B, s + cs); if (s < e) chunks.push_back({s, e}); }
+  // virtual-worker chunks (net.go:621-633) are laid out on the GLOBAL batch; this call owns the part of each
+  // chunk that falls inside [first, first + B)
+  struct Chunk { int s, e, gend; };   // local range, and the global index one past the chunk's last sample
+  std::vector<Chunk> chunks; int cs = (GB + W - 1) / W;
+  for (int w = 0; w < W; w++) {
+    int gs = w * cs, ge = std::min(GB, gs + cs); if (gs >= ge) continue;
+    int s = std::max(gs, first) - first, e = std::min(ge, first + B) - first;
+    if (s < e) chunks.push_back({s, e, ge - first});
+  }
   // Optional sub-division of a chunk over OS threads.  It changes nothing but the order in
   // which per-sample gradients are added (private buffers summed afterwards); it is not used
   // for a model with an LSTM, whose clipping depends on the order within the chunk.
@@ -727,7 +734,7 @@ template <class R> int train_batch_impl(const TrainArgs& a) {
     int parts = 1;
     if (!proto.has_lstm && (int)chunks.size() < threads) parts = std::min(c.e - c.s, std::max(1, threads / (int)chunks.size()));
     int ps = (c.e - c.s + parts - 1) / parts;
-    for (int s = c.s; s < c.e; s += ps) jobs.push_back({s, std::min(c.e, s + ps), c.e});
+    for (int s = c.s; s < c.e; s += ps) jobs.push_back({s, std::min(c.e, s + ps), c.gend});
   }
   std::vector<std::vector<R>> jgrads(jobs.size());
   std::vector<R> jloss(jobs.size(), R(0));
@@ -758,11 +765,11 @@ template <class R> int train_batch_impl(const TrainArgs& a) {
   else { std::vector<std::thread> th; for (int i = 0; i < nt; i++) th.emplace_back(worker); for (auto& t : th) t.join(); }
   std::vector<R> grads(P, R(0));
   for (auto& jg : jgrads) for (int64_t i = 0; i < P; i++) grads[i] += jg[i];       // net.go:694-700
-  R inv = (R)(1.0 / (double)B);                                                     // net.go:703
-  if (sizeof(R) == sizeof(float)) inv = (R)(float)(1.0 / (double)B);
+  R inv = (R)(1.0 / (double)GB);                                                    // net.go:703
+  if (sizeof(R) == sizeof(float)) inv = (R)(float)(1.0 / (double)GB);
   for (int64_t i = 0; i < P; i++) grads[i] *= inv;
   R total = 0; for (R l : jloss) total += l;
-  if (a.mean_loss) *a.mean_loss = (float)(total / (R)B);                            // net.go:711-716
+  if (a.mean_loss) *a.mean_loss = (float)(total / (R)GB);                            // net.go:711-716
   if (a.grads_out) for (int64_t i = 0; i < P; i++) a.grads_out[i] = (float)grads[i];
   if (a.do_step) {
     // Network.Step (net.go:260-284): NewStep() increments the counter, StepInPlace uses counter+1,
@@ -808,13 +815,15 @@ int gno_param_count(const gn_layer_desc* layers, int n_layers, int64_t* n, int64
   if (n) *n = net.n_params; if (in_size) *in_size = net.in_size; if (out_size) *out_size = net.out_size; return GN_OK;
 }
 
-// One Network.TrainBatch.  precision: 32 = literal fp32, 64 = double twin.  `W` = the reference's
+// One Network.TrainBatch.  With global_batch > 0 the call is ONE RANK's shard of a larger batch: gradients and
+// loss are this shard's contribution (already scaled by 1/global_batch), to be summed over ranks; pass do_step = 0.
+// precision: 32 = literal fp32, 64 = double twin.  `W` = the reference's
 // worker count (1 = trainBatchSequential); `threads` = OS threads used to run it.
 int gno_train_batch(const gn_layer_desc* layers, int n_layers, int loss_kind, float* params, float* grads_out,
                     float* m, float* v, int* timestep, float lr, float b1, float b2, float eps,
                     const float* x, const float* y, int batch, int W, int threads, int precision, int do_step,
-                    float* mean_loss, double* seconds) {
-  TrainArgs a{layers, n_layers, loss_kind, params, grads_out, m, v, timestep, lr, b1, b2, eps, x, y, batch, W, threads, do_step, mean_loss, seconds};
+                    int global_batch, int first_sample, float* mean_loss, double* seconds) {
+  TrainArgs a{layers, n_layers, loss_kind, params, grads_out, m, v, timestep, lr, b1, b2, eps, x, y, batch, W, threads, do_step, global_batch, first_sample, mean_loss, seconds};
   return precision == 64 ? train_batch_impl<double>(a) : train_batch_impl<float>(a);
 }
 

@@ -1,0 +1,65 @@
+"""The N > 1 host logic on CPU, world_size 2 over gloo: contiguous sharding, per-rank partial gradients scaled by
+1/global_batch, one sum all-reduce of the flat gradient buffer and of the loss, identical Adam on every rank.
+The per-rank arithmetic here is the CPU checker standing in for the device; what is under test is the data flow
+of goneuron_b200.sharding + the all-reduce, which must reproduce the single-process full-batch step (including
+the embedding rule, which depends on the GLOBAL sample index)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CASES = [("mlp", dict(in_size=20, hidden=9, classes=4), 8, 1),
+         ("transformer_small", dict(vocab=64, dim=16, seq_len=6, heads=2, ff_dim=24, n_blocks=1), 6, 1),
+         ("transformer_small", dict(vocab=64, dim=16, seq_len=6, heads=2, ff_dim=24, n_blocks=1), 8, 4)]
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from goneuron_b200 import configs
+    from goneuron_b200.sharding import shard_bounds
+    from oracle import binding as oracle
+    for ci, (name, kw, gb, W) in enumerate(CASES):
+        layers, loss_kind, params, x, y, lr = configs.make_case(name, batch=gb, **kw)
+        s, e = shard_bounds(gb, rank, world)
+        st = oracle.OracleState(layers, loss_kind, params, lr=lr)
+        part_loss = st.train_batch(x[s:e], y[s:e], W=W, precision=64, step=False, global_batch=gb, first_sample=s)
+        g = torch.from_numpy(st.grads.astype(np.float64))
+        l = torch.tensor([part_loss], dtype=torch.float64)
+        dist.all_reduce(g)
+        dist.all_reduce(l)
+        p, m, v = oracle.adam(params, g.numpy().astype(np.float32), np.zeros_like(params), np.zeros_like(params), lr, 0.9, 0.999, 1e-8, 2, precision=64)
+        np.savez(os.path.join(out_dir, f"r{rank}_c{ci}.npz"), grads=g.numpy(), loss=l.numpy(), params=p)
+    dist.destroy_process_group()
+
+
+def test_two_rank_step_equals_full_batch_step(tmp_path, oracle):
+    from goneuron_b200 import configs
+    port = 29500 + os.getpid() % 2000
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for ci, (name, kw, gb, W) in enumerate(CASES):
+        layers, loss_kind, params, x, y, lr = configs.make_case(name, batch=gb, **kw)
+        ref = oracle.OracleState(layers, loss_kind, params, lr=lr)
+        ref_loss = ref.train_batch(x, y, W=W, precision=64)
+        r0, r1 = (np.load(tmp_path / f"r{r}_c{ci}.npz") for r in (0, 1))
+        assert np.array_equal(r0["grads"], r1["grads"]) and np.array_equal(r0["params"], r1["params"])   # replicas stay identical
+        np.testing.assert_allclose(r0["grads"], ref.grads, rtol=0, atol=2e-6 * max(1.0, np.abs(ref.grads).max()))
+        assert abs(float(r0["loss"][0]) - ref_loss) <= 1e-5 * max(1.0, abs(ref_loss))
+        gmax = np.abs(ref.grads).max()
+        resolved = np.abs(ref.grads) > 1e-3 * gmax
+        np.testing.assert_allclose(r0["params"][resolved], ref.params[resolved], rtol=0, atol=1e-6)
+
+
+def test_shard_bounds():
+    from goneuron_b200.sharding import shard_bounds
+    assert [shard_bounds(256, r, 8) for r in (0, 3, 7)] == [(0, 32), (96, 128), (224, 256)]
+    with pytest.raises(ValueError):
+        shard_bounds(10, 0, 4)
+    with pytest.raises(ValueError):
+        shard_bounds(8, 2, 2)
