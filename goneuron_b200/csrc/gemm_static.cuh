@@ -59,15 +59,11 @@ extern "C" int gn_op_gemm_nt_static(gn_ctx* ctx, int M, int N, int K, const floa
   GN_CUDA(cudaSetDevice(c->device));
   float* base = nullptr; GN_TRY(static_scratch_ptr(c->device, &base));
   float *a_hi = base, *a_lo = a_hi + (long)M * ldp, *b_hi = a_lo + (long)M * ldp, *b_lo = b_hi + (long)N * ldp;
-  const long na = (long)M * ldp, nb = (long)N * ldp;
-  GN_LAUNCH(c, split_tf32_kernel, (unsigned)std::min<long>((na + 255) / 256, (long)c->sm_count * 32), 256, 0, A_dev, (long)K, M, K, a_hi, a_lo, (int)ldp);
-  GN_LAUNCH(c, split_tf32_kernel, (unsigned)std::min<long>((nb + 255) / 256, (long)c->sm_count * 32), 256, 0, B_dev, (long)K, N, K, b_hi, b_lo, (int)ldp);
-  CUtensorMap mAh, mAl, mBh, mBl;
-  GN_TRY(tc_make_map(c, &mAh, a_hi, M, K, (int)ldp, TC_BM)); GN_TRY(tc_make_map(c, &mAl, a_lo, M, K, (int)ldp, TC_BM));
-  GN_TRY(tc_make_map(c, &mBh, b_hi, N, K, (int)ldp, TC_BN)); GN_TRY(tc_make_map(c, &mBl, b_lo, N, K, (int)ldp, TC_BN));
-  TcEpilogue ep{C_dev, (long)N, bias_dev, nullptr, 0, GN_ACT_LINEAR, M, N, K, c->d_status};
-  GN_LAUNCH(c, gemm_tc_kernel, dim3(cdiv(N, TC_BN), cdiv(M, TC_BM)), TC_THREADS, TC_SMEM_BYTES, mAh, mAl, mBh, mBl, ep);
-  GN_TRY(check_launch("gemm_nt_static"));
+  TcPlanes PA{a_hi, a_lo, M, K, (int)ldp, 1}, PB{b_hi, b_lo, N, K, (int)ldp, 1};
+  GN_TRY(tc_split(c, TcSrc{A_dev, (long)K, 1, 0, 0, 1}, PA));
+  GN_TRY(tc_split(c, TcSrc{B_dev, (long)K, 1, 0, 0, 1}, PB));
+  TcParams ep{C_dev, (long)N, 0, 0, bias_dev, nullptr, 0, 0, 0, GN_ACT_LINEAR, M, N, K, 1, 0, c->d_status};
+  GN_TRY(tc_launch(c, PA, PB, ep));
   GN_CUDA(cudaStreamSynchronize(c->stream));
   int st = 0; GN_CUDA(cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost));
   if (st != 0) { cudaMemset(c->d_status, 0, sizeof(int)); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }

@@ -8,13 +8,14 @@
 // memory-bound pass (split_tf32_kernel / split_tf32_transpose_kernel) into K-major planes, so the
 // contraction kernel itself is a pure TMA -> shared memory -> tcgen05.mma pipeline:
 //
-//   warp 0   TMA producer: 4 tiled bulk copies per stage (A_hi, A_lo, B_hi, B_lo; 128-byte swizzle)
+//   warp 0   TMA producer: 4 tiled bulk copies per stage (A_hi, A_lo, B_hi, B_lo; 128-byte swizzle; 3-D maps,
+//            third coordinate = problem index of a batch)
 //   warp 1   allocates TMEM, issues tcgen05.mma.kind::tf32 (one elected lane), commits to mbarriers
 //   warps 2-5  epilogue: tcgen05.ld of the accumulator, bias / residual / ReLU, transposed through
 //              shared memory so that global stores are 128-byte coalesced
 //
-// Tile 128 x 256 x 32, 2 stages of 96 KB.  Two accumulators of 128 lanes x 256 columns fill the 512 TMEM
-// columns: the hi*hi products go to one, the small cross terms (hi*lo, lo*hi) to the other, and the epilogue
+// Tile 128 x BN x 32 with BN = 256 (2 stages of 96 KB), 128 (3 x 64 KB) or 64 (4 x 48 KB, for head-width
+// outputs).  Two accumulators of 128 lanes x BN columns in TMEM (all 512 columns at BN = 256): the hi*hi products go to one, the small cross terms (hi*lo, lo*hi) to the other, and the epilogue
 // adds them.  The tensor core truncates when it aligns a product sum to the running accumulator, an error
 // proportional to the accumulator's magnitude per MMA; keeping the cross terms out of the large accumulator
 // cuts the number of such truncations on it by three.
@@ -27,11 +28,16 @@
 
 namespace gn {
 
-constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 32, TC_STAGES = 2, TC_THREADS = 192;
-constexpr int TC_A_BYTES = TC_BM * TC_BK * 4, TC_B_BYTES = TC_BN * TC_BK * 4;
-constexpr int TC_STAGE_BYTES = 2 * TC_A_BYTES + 2 * TC_B_BYTES;        // 96 KB
-constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr int TC_BM = 128, TC_BK = 32, TC_THREADS = 192;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 4;
 constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
+template <int BN> struct TcCfg {
+  static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
+  static constexpr int B_BYTES = BN * TC_BK * 4;
+  static constexpr int STAGE_BYTES = 2 * TC_A_BYTES + 2 * B_BYTES;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = 2 * BN;
+};
 
 // ------------------------------------------------------------------ PTX wrappers
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -48,9 +54,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   }
   return false;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -81,29 +87,41 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr) : "memory");
 }
 
-struct TcEpilogue {
-  float* C; long ldc; const float* bias; const float* R; long ldr; int act; int M, N, K; int* status;
+// Output side of one launch.  Batched problems: problem z = blockIdx.z -> (z / batch2, z % batch2) selects the
+// output (and residual) sub-matrix; the operand planes of problem z are slice z of the 3-D tensor maps.
+struct TcParams {
+  float* C; long ldc, c_b1, c_b2; const float* bias; const float* R; long ldr, r_b1, r_b2;
+  int act, M, N, K, batch2, flags; int* status;
 };
 
+template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
-               const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo, TcEpilogue ep) {
+               const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo, TcParams ep) {
+  using Cfg = TcCfg<BN>;
+  constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, B_BYTES = Cfg::B_BYTES;
+  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN, z = blockIdx.z;
+  // causal attention products: tiles above the diagonal do not exist; the contraction range is clipped to the diagonal
+  if ((ep.flags & GEMM_SKIP_UPPER) && n0 > m0 + TC_BM - 1) return;
+  int kbeg = 0, kend = ep.K;
+  if (ep.flags & GEMM_KBEG_AT_M0) kbeg = (m0 / TC_BK) * TC_BK;
+  if (ep.flags & GEMM_KEND_AT_M0) kend = min(ep.K, m0 + TC_BM);
+  const int kb0 = kbeg / TC_BK, nkb = (kend - kbeg + TC_BK - 1) / TC_BK;
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);      // 128B-swizzle tiles need 1024-byte alignment
-  uint64_t* bars = (uint64_t*)(smem + TC_STAGES * TC_STAGE_BYTES);                   // full[S], empty[S], accum
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * TC_STAGES + 1);
-  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + TC_STAGES), accum = smem_u32(bars + 2 * TC_STAGES);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);                         // full[S], empty[S], accum
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), accum = smem_u32(bars + 2 * STAGES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
-  const int nkb = (ep.K + TC_BK - 1) / TC_BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < TC_STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     mbar_init(accum, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)(2 * TC_BN)) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -114,40 +132,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true;
-      for (int kb = 0; kb < nkb; kb++) {
-        const int s = kb % TC_STAGES, use = kb / TC_STAGES;
+      for (int i = 0; i < nkb; i++) {
+        const int s = i % STAGES, use = i / STAGES, kc = (kb0 + i) * TC_BK;
         if (use > 0) ok &= mbar_wait(empty0 + 8 * s, (use - 1) & 1);
-        const uint32_t base = smem_u32(smem + s * TC_STAGE_BYTES), bar = full0 + 8 * s;
-        mbar_expect_tx(bar, TC_STAGE_BYTES);
-        tma_load_2d(base, &mapAhi, kb * TC_BK, m0, bar);
-        tma_load_2d(base + TC_A_BYTES, &mapAlo, kb * TC_BK, m0, bar);
-        tma_load_2d(base + 2 * TC_A_BYTES, &mapBhi, kb * TC_BK, n0, bar);
-        tma_load_2d(base + 2 * TC_A_BYTES + TC_B_BYTES, &mapBlo, kb * TC_BK, n0, bar);
+        const uint32_t base = smem_u32(smem + s * STAGE_BYTES), bar = full0 + 8 * s;
+        mbar_expect_tx(bar, STAGE_BYTES);
+        tma_load_3d(base, &mapAhi, kc, m0, z, bar);
+        tma_load_3d(base + TC_A_BYTES, &mapAlo, kc, m0, z, bar);
+        tma_load_3d(base + 2 * TC_A_BYTES, &mapBhi, kc, n0, z, bar);
+        tma_load_3d(base + 2 * TC_A_BYTES + B_BYTES, &mapBlo, kc, n0, z, bar);
       }
       if (!ok) atomicExch(ep.status, 1);
     }
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true;
-      constexpr uint32_t idesc = make_idesc(TC_BM, TC_BN);
-      for (int kb = 0; kb < nkb; kb++) {
-        const int s = kb % TC_STAGES, use = kb / TC_STAGES;
+      constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+      for (int i = 0; i < nkb; i++) {
+        const int s = i % STAGES, use = i / STAGES;
         ok &= mbar_wait(full0 + 8 * s, use & 1);
         tc_fence_after();
-        const uint32_t base = smem_u32(smem + s * TC_STAGE_BYTES);
+        const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
         const uint64_t ahi = make_desc(base), alo = make_desc(base + TC_A_BYTES);
-        const uint64_t bhi = make_desc(base + 2 * TC_A_BYTES), blo = make_desc(base + 2 * TC_A_BYTES + TC_B_BYTES);
+        const uint64_t bhi = make_desc(base + 2 * TC_A_BYTES), blo = make_desc(base + 2 * TC_A_BYTES + B_BYTES);
 #pragma unroll
         for (int k = 0; k < TC_BK / 8; k++) {
           const uint64_t adv = (uint64_t)((k * 8 * 4) >> 4);          // 8 tf32 = 32 bytes along K inside the swizzle atom
-          const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-          tc_mma_tf32(tmem_base + TC_BN, alo + adv, bhi + adv, idesc, acc);     // cross terms -> second accumulator
-          tc_mma_tf32(tmem_base + TC_BN, ahi + adv, blo + adv, idesc, 1u);
+          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          tc_mma_tf32(tmem_base + BN, alo + adv, bhi + adv, idesc, acc);        // cross terms -> second accumulator
+          tc_mma_tf32(tmem_base + BN, ahi + adv, blo + adv, idesc, 1u);
           tc_mma_tf32(tmem_base, ahi + adv, bhi + adv, idesc, acc);             // main term
         }
         tc_commit(empty0 + 8 * s);           // frees this stage once the MMAs above have read it
       }
-      tc_commit(accum);                      // accumulator complete
+      tc_commit(accum);                      // accumulator complete (fires at once when nkb == 0)
       if (!ok) atomicExch(ep.status, 2);
     }
   } else {
@@ -159,21 +177,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
     if (!ok && lane == 0) atomicExch(ep.status, 3);
     __syncwarp();
     tc_fence_after();
+    const int z1 = z / ep.batch2, z2 = z % ep.batch2;
+    float* C = ep.C + z1 * ep.c_b1 + z2 * ep.c_b2;
+    const float* R = ep.R ? ep.R + z1 * ep.r_b1 + z2 * ep.r_b2 : nullptr;
     // the pipeline stages are idle once the accumulator barrier fired: reuse stage memory as a per-warp 32x33 transpose tile
     float* tile = (float*)smem + (warp - 2) * (32 * 33);
     const int row_base = m0 + quad * 32;
-    for (int c = 0; c < TC_BN / 32; c++) {
+    for (int c = 0; c < BN / 32; c++) {
       const int col0 = n0 + c * 32;
       if (col0 >= ep.N) break;
       uint32_t r[32], q[32];
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
-      tmem_ld32(taddr, r);
-      tmem_ld32(taddr + TC_BN, q);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      if (nkb > 0) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
+        tmem_ld32(taddr, r);
+        tmem_ld32(taddr + BN, q);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-      for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
+        for (int j = 0; j < 32; j++) tile[lane * 33 + j] = __uint_as_float(r[j]) + __uint_as_float(q[j]);     // thread = row, conflict-free (stride 33)
+      } else {
 #pragma unroll
-      for (int j = 0; j < 32; j++) tile[lane * 33 + j] = __uint_as_float(r[j]);     // thread = row, conflict-free (stride 33)
+        for (int j = 0; j < 32; j++) tile[lane * 33 + j] = 0.f;
+      }
       __syncwarp();
       const int col = col0 + lane;
       const float bv = (ep.bias && col < ep.N) ? ep.bias[col] : 0.f;
@@ -182,9 +206,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
           const int row = row_base + rr;
           if (row >= ep.M) break;
           float v = tile[rr * 33 + lane] + bv;
-          if (ep.R) v += ep.R[(long)row * ep.ldr + col];
+          if (R) v += R[(long)row * ep.ldr + col];
           if (ep.act == GN_ACT_RELU) v = v > 0.f ? v : 0.f;
-          ep.C[(long)row * ep.ldc + col] = v;
+          C[(long)row * ep.ldc + col] = v;
         }
       }
       __syncwarp();
@@ -193,36 +217,43 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * TC_BN)) : "memory");
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
 }
 
 // ------------------------------------------------------------------ operand split (memory-bound)
 __device__ __forceinline__ float tf32_round(float x) { uint32_t u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x)); return __uint_as_float(u); }
-// hi/lo planes [rows, ldp] of a K-major source [rows, cols] (row stride ld); columns cols..ldp-1 are zero-filled
-__global__ void split_tf32_kernel(const float* __restrict__ src, long ld, int rows, int cols, float* __restrict__ hi, float* __restrict__ lo, int ldp) {
-  long total = (long)rows * ldp;
+// Batched, strided split: planes[z][r][c] (row stride ldp, c < ldp, zero beyond cols) of the source element
+// (z, r, c) at p + (z / batch2) * b1 + (z % batch2) * b2 + r * s_r + c * s_c.  One of s_r, s_c is 1:
+// s_c == 1 reads rows directly; s_r == 1 (the operand is the transpose of what is stored) goes through a shared tile.
+struct TcSrc { const float* p; long s_r, s_c, b1, b2; int batch2; };
+__global__ void split_rows_kernel(TcSrc s, int rows, int cols, long total, float* __restrict__ hi, float* __restrict__ lo, int ldp) {
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-    int c = (int)(i % ldp); long r = i / ldp;
-    float x = c < cols ? src[r * ld + c] : 0.f;
+    int c = (int)(i % ldp); long q = i / ldp; int r = (int)(q % rows); int z = (int)(q / rows);
+    float x = c < cols ? s.p[(z / s.batch2) * s.b1 + (z % s.batch2) * s.b2 + r * s.s_r + c] : 0.f;
     float h = tf32_round(x);
     hi[i] = h; lo[i] = x - h;
   }
 }
-// planes of the TRANSPOSE: source [rows, cols] (row stride ld) -> hi/lo [cols, ldp] (ldp >= rows), through a 32x32 shared tile
-__global__ void split_tf32_transpose_kernel(const float* __restrict__ src, long ld, int rows, int cols, float* __restrict__ hi, float* __restrict__ lo, int ldp) {
+__global__ void split_cols_kernel(TcSrc s, int rows, int cols, float* __restrict__ hi, float* __restrict__ lo, int ldp) {
   __shared__ float t[32][33];
-  int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
-  for (int j = threadIdx.y; j < 32; j += blockDim.y) { int r = r0 + j, c = c0 + threadIdx.x; t[j][threadIdx.x] = (r < rows && c < cols) ? src[(long)r * ld + c] : 0.f; }
+  const int z = blockIdx.z, c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const float* src = s.p + (z / s.batch2) * s.b1 + (z % s.batch2) * s.b2;
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) { int c = c0 + j, r = r0 + threadIdx.x; t[j][threadIdx.x] = (r < rows && c < cols) ? src[r + c * s.s_c] : 0.f; }
   __syncthreads();
+  float* ph = hi + (long)z * rows * ldp; float* pl = lo + (long)z * rows * ldp;
   for (int j = threadIdx.y; j < 32; j += blockDim.y) {
-    int c = c0 + j, r = r0 + threadIdx.x;
-    if (c < cols && r < ldp) { float x = t[threadIdx.x][j]; float h = tf32_round(x); hi[(long)c * ldp + r] = h; lo[(long)c * ldp + r] = x - h; }
+    int r = r0 + j, c = c0 + threadIdx.x;
+    if (r < rows && c < ldp) { float x = t[threadIdx.x][j]; float h = tf32_round(x); ph[(long)r * ldp + c] = h; pl[(long)r * ldp + c] = x - h; }
   }
 }
 
 // ------------------------------------------------------------------ host side
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                     CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// hi/lo planes of one operand: [nbatch][rows][ldp] fp32 each, K valid columns
+struct TcPlanes { float* hi; float* lo; int rows, K, ldp, nbatch; };
+inline int tc_ldp(int K) { return ((K + 3) / 4) * 4; }              // plane row stride: a multiple of 16 bytes for TMA
 
 struct TcScratch { DevBuf a_hi, a_lo, b_hi, b_lo; };
 inline TcScratch& tc_scratch(Ctx* ctx) { static thread_local std::vector<std::pair<Ctx*, TcScratch*>> tab; for (auto& e : tab) if (e.first == ctx) return *e.second; tab.push_back({ctx, new TcScratch()}); return *tab.back().second; }
@@ -231,16 +262,57 @@ inline void tc_init(Ctx* ctx) {
   ctx->tc_ok = false;
   void* fn = nullptr; cudaDriverEntryPointQueryResult q;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn || q != cudaDriverEntryPointSuccess) { cudaGetLastError(); return; }
-  if (cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return; }
+  if (cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256>::SMEM_BYTES) != cudaSuccess ||
+      cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128>::SMEM_BYTES) != cudaSuccess ||
+      cudaFuncSetAttribute(gemm_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64>::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return; }
   ctx->encode_tiled = fn; ctx->tc_ok = true;
 }
 
-// Can the engine run this contraction at all?  A must be K-major; B either K-major (X W^T) or N-major (dZ W, via the
-// transposing split); single problem; no causal tile flags; fp32 alpha of 1.
+inline int tc_make_map(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const float* base, int box_rows) {
+  cuuint64_t dims[3] = {(cuuint64_t)p.K, (cuuint64_t)p.rows, (cuuint64_t)p.nbatch};
+  cuuint64_t strides[2] = {(cuuint64_t)p.ldp * 4, (cuuint64_t)p.rows * p.ldp * 4};
+  cuuint32_t box[3] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = ((PFN_encodeTiled)ctx->encode_tiled)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(GN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows %d K %d ld %d batch %d)", (int)r, p.rows, p.K, p.ldp, p.nbatch);
+  return GN_OK;
+}
+
+// Writes the planes of an operand.
+inline int tc_split(Ctx* ctx, const TcSrc& src, const TcPlanes& p) {
+  if (src.s_c == 1) {
+    long total = (long)p.nbatch * p.rows * p.ldp;
+    GN_LAUNCH(ctx, split_rows_kernel, (unsigned)std::min<long>((total + 255) / 256, (long)ctx->sm_count * 32), 256, 0, src, p.rows, p.K, total, p.hi, p.lo, p.ldp);
+  } else if (src.s_r == 1) {
+    GN_LAUNCH(ctx, split_cols_kernel, dim3(cdiv(p.ldp, 32), cdiv(p.rows, 32), p.nbatch), dim3(32, 8), 0, src, p.rows, p.K, p.hi, p.lo, p.ldp);
+  } else return fail(GN_ERR_UNSUPPORTED, "tc_split: neither stride of the operand is 1");
+  return check_launch("tc_split");
+}
+
+template <int BN>
+inline int tc_launch_bn(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep) {
+  CUtensorMap mAh, mAl, mBh, mBl;
+  GN_TRY(tc_make_map(ctx, &mAh, A, A.hi, TC_BM)); GN_TRY(tc_make_map(ctx, &mAl, A, A.lo, TC_BM));
+  GN_TRY(tc_make_map(ctx, &mBh, B, B.hi, BN)); GN_TRY(tc_make_map(ctx, &mBl, B, B.lo, BN));
+  dim3 grid(cdiv(ep.N, BN), cdiv(ep.M, TC_BM), A.nbatch);
+  GN_LAUNCH(ctx, gemm_tc_kernel<BN>, grid, TC_THREADS, TcCfg<BN>::SMEM_BYTES, mAh, mAl, mBh, mBl, ep);
+  return check_launch("gemm_tc");
+}
+// C[z] = A[z] * B[z]^T from prepared planes; the N tile follows the output width.
+inline int tc_launch(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep) {
+  if (!ctx->tc_ok) return fail(GN_ERR_UNSUPPORTED, "tcgen05 engine unavailable");
+  if (A.K != B.K || A.nbatch != B.nbatch || A.rows != ep.M || B.rows != ep.N || A.K != ep.K) return fail(GN_ERR_INVALID_ARG, "tc_launch: operand shapes disagree");
+  if (ep.N <= 64) return tc_launch_bn<64>(ctx, A, B, ep);
+  if (ep.N <= 128) return tc_launch_bn<128>(ctx, A, B, ep);
+  return tc_launch_bn<256>(ctx, A, B, ep);
+}
+
+// Can the engine run this contraction at all?  One of each operand's strides must be 1; LINEAR/RELU epilogue; alpha 1.
 inline bool gemm_tc_supported(Ctx* ctx, const GemmDesc& g) {
   if (!ctx->tc_ok) return false;
-  if (g.batch1 * g.batch2 != 1 || g.flags != 0 || g.alpha != 1.f) return false;
-  if (g.sa_k != 1) return false;
+  if (g.alpha != 1.f) return false;
+  if (!(g.sa_k == 1 || g.sa_m == 1)) return false;
   if (!(g.sb_k == 1 || g.sb_n == 1)) return false;
   if (g.act != GN_ACT_LINEAR && g.act != GN_ACT_RELU) return false;
   return g.M > 0 && g.N > 0 && g.K > 0;
@@ -248,44 +320,22 @@ inline bool gemm_tc_supported(Ctx* ctx, const GemmDesc& g) {
 // Is it worth it?  Small or skinny problems stay on the SIMT engine.
 inline bool gemm_tc_eligible(Ctx* ctx, const GemmDesc& g) {
   if (!gemm_tc_supported(ctx, g)) return false;
-  return g.M >= 128 && g.N >= 64 && g.K >= 64 && (double)g.M * g.N * g.K >= 1.0e8;
+  return g.M >= 64 && g.N >= 32 && g.K >= 32 && (double)g.M * g.N * g.K * g.batch1 * g.batch2 >= 1.0e8;
 }
 
-inline int tc_make_map(Ctx* ctx, CUtensorMap* map, const float* base, int rows, int cols, int ldp, int box_rows) {
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ldp * 4};
-  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = ((PFN_encodeTiled)ctx->encode_tiled)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(GN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows %d cols %d ld %d)", (int)r, rows, cols, ldp);
-  return GN_OK;
-}
-
+// General entry: splits both operands into the context's scratch planes, then runs the contraction.
 inline int gemm_tc(Ctx* ctx, const GemmDesc& g) {
   if (!gemm_tc_supported(ctx, g)) return fail(GN_ERR_UNSUPPORTED, "tcgen05 engine cannot run this contraction");
   TcScratch& sc = tc_scratch(ctx);
-  const int ldp = ((g.K + 3) / 4) * 4;                    // plane row stride: a multiple of 16 bytes for TMA
-  size_t na = (size_t)g.M * ldp, nb = (size_t)g.N * ldp;
+  const int nb = g.batch1 * g.batch2, ldp = tc_ldp(g.K);
+  size_t na = (size_t)nb * g.M * ldp, nbb = (size_t)nb * g.N * ldp;
   if (sc.a_hi.n < na) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.a_hi.alloc(na)); GN_TRY(sc.a_lo.alloc(na)); }
-  if (sc.b_hi.n < nb) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.b_hi.alloc(nb)); GN_TRY(sc.b_lo.alloc(nb)); }
-  long ga = std::min<long>(((long)na + 255) / 256, (long)ctx->sm_count * 32);
-  GN_LAUNCH(ctx, split_tf32_kernel, (unsigned)ga, 256, 0, g.A, g.sa_m, g.M, g.K, sc.a_hi.p, sc.a_lo.p, ldp);
-  if (g.sb_k == 1) {
-    long gb = std::min<long>(((long)nb + 255) / 256, (long)ctx->sm_count * 32);
-    GN_LAUNCH(ctx, split_tf32_kernel, (unsigned)gb, 256, 0, g.B, g.sb_n, g.N, g.K, sc.b_hi.p, sc.b_lo.p, ldp);
-  } else {
-    // B(k,n) = src[k*sb_k + n]: source is [K rows, N cols]; planes hold its transpose [N, K]
-    dim3 grid(cdiv(g.N, 32), cdiv(ldp, 32)), block(32, 8);
-    GN_LAUNCH(ctx, split_tf32_transpose_kernel, grid, block, 0, g.B, g.sb_k, g.K, g.N, sc.b_hi.p, sc.b_lo.p, ldp);
-  }
-  CUtensorMap mAh, mAl, mBh, mBl;
-  GN_TRY(tc_make_map(ctx, &mAh, sc.a_hi.p, g.M, g.K, ldp, TC_BM)); GN_TRY(tc_make_map(ctx, &mAl, sc.a_lo.p, g.M, g.K, ldp, TC_BM));
-  GN_TRY(tc_make_map(ctx, &mBh, sc.b_hi.p, g.N, g.K, ldp, TC_BN)); GN_TRY(tc_make_map(ctx, &mBl, sc.b_lo.p, g.N, g.K, ldp, TC_BN));
-  TcEpilogue ep{g.C, g.ldc, g.bias, g.R, g.ldr, g.act, g.M, g.N, g.K, ctx->d_status};
-  dim3 grid(cdiv(g.N, TC_BN), cdiv(g.M, TC_BM));
-  GN_LAUNCH(ctx, gemm_tc_kernel, grid, TC_THREADS, TC_SMEM_BYTES, mAh, mAl, mBh, mBl, ep);
-  return check_launch("gemm_tc");
+  if (sc.b_hi.n < nbb) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.b_hi.alloc(nbb)); GN_TRY(sc.b_lo.alloc(nbb)); }
+  TcPlanes A{sc.a_hi.p, sc.a_lo.p, g.M, g.K, ldp, nb}, B{sc.b_hi.p, sc.b_lo.p, g.N, g.K, ldp, nb};
+  GN_TRY(tc_split(ctx, TcSrc{g.A, g.sa_m, g.sa_k, g.a_b1, g.a_b2, g.batch2}, A));
+  GN_TRY(tc_split(ctx, TcSrc{g.B, g.sb_n, g.sb_k, g.b_b1, g.b_b2, g.batch2}, B));
+  TcParams ep{g.C, g.ldc, g.c_b1, g.c_b2, g.bias, g.R, g.ldr, g.r_b1, g.r_b2, g.act, g.M, g.N, g.K, g.batch2, g.flags, ctx->d_status};
+  return tc_launch(ctx, A, B, ep);
 }
 
 }  // namespace gn
