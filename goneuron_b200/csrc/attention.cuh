@@ -1,0 +1,157 @@
+// attention.cuh -- fused causal multi-head attention, forward and backward, without materialising the
+// [T, T] score matrices in HBM.
+//
+// reference: internal/layer/transformer.go:470-503 (forward: scores = q.k / sqrt(hd), masked entries -1e9,
+// row softmax, weighted sum of v) and :589-657 (backward: probabilities recomputed from q and k, explicit
+// softmax Jacobian, dQ / dK / dV).  The Jacobian row term sum_k dP_k P_k equals dO . O (O = P V), which is
+// what the backward kernels use; the row maximum and the row sum of the forward softmax are kept per row.
+//
+// Arithmetic: every product runs as 3xTF32 (hi*hi + hi*lo + lo*hi with fp32 accumulation) on warp-level
+// tensor-core MMAs, the operands being split in registers, so accuracy is fp32-level.  One CTA = 64 query
+// (or key) rows of one head, 4 warps x 16 rows, key (query) blocks of 64 streamed through shared memory;
+// causal blocks above the diagonal are never visited.
+//
+// Q, K, V, O, dO and the outputs are [batch*T, D] row-major with head h in columns [h*HD, (h+1)*HD).
+#pragma once
+#include "common.cuh"
+
+namespace gn {
+
+constexpr int AT_BLK = 64, AT_THREADS = 128;
+
+struct FragA { uint32_t hi[4], lo[4]; };
+struct FragB { uint32_t hi[2], lo[2]; };
+
+__device__ __forceinline__ void split32(float x, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  lo = __float_as_uint(x - __uint_as_float(hi));
+}
+__device__ __forceinline__ void mma8(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void mma3(float (&d)[4], const FragA& a, const FragB& b) { mma8(d, a.lo, b.hi); mma8(d, a.hi, b.lo); mma8(d, a.hi, b.hi); }
+
+// A(r, k) = s[(row0 + r) * LD + k0 + k], 16 x 8.  Fragment order: (g,t) (g+8,t) (g,t+4) (g+8,t+4).
+__device__ __forceinline__ void load_a(FragA& f, const float* s, int LD, int row0, int k0, int g, int t) {
+  const float* p = s + (row0 + g) * LD + k0 + t;
+  split32(p[0], f.hi[0], f.lo[0]); split32(p[8 * LD], f.hi[1], f.lo[1]); split32(p[4], f.hi[2], f.lo[2]); split32(p[8 * LD + 4], f.hi[3], f.lo[3]);
+}
+// B(k, n) = s[(n0 + n) * LD + k0 + k], 8 x 8: the contraction runs along the shared-memory row.
+__device__ __forceinline__ void load_b_nk(FragB& f, const float* s, int LD, int n0, int k0, int g, int t) {
+  const float* p = s + (n0 + g) * LD + k0 + t;
+  split32(p[0], f.hi[0], f.lo[0]); split32(p[4], f.hi[1], f.lo[1]);
+}
+// B(k, n) = s[(k0 + k') * LD + n0 + n] with the contraction index permuted: MMA k-index t <-> row k0 + 2t,
+// t + 4 <-> row k0 + 2t + 1.  This is the order in which an accumulator fragment holds its 8 columns
+// (thread t owns columns 2t and 2t+1), so an accumulator can be fed back as the A operand without shuffles.
+__device__ __forceinline__ void load_b_kn2(FragB& f, const float* s, int LD, int k0, int n0, int g, int t) {
+  const float* p = s + (k0 + 2 * t) * LD + n0 + g;
+  split32(p[0], f.hi[0], f.lo[0]); split32(p[LD], f.hi[1], f.lo[1]);
+}
+// accumulator fragment (rows g, g+8; columns 2t, 2t+1) as A operand in the permuted order above
+__device__ __forceinline__ void acc_to_a(FragA& f, const float (&c)[4]) {
+  split32(c[0], f.hi[0], f.lo[0]); split32(c[2], f.hi[1], f.lo[1]); split32(c[1], f.hi[2], f.lo[2]); split32(c[3], f.hi[3], f.lo[3]);
+}
+// 64 x HD tile of a [*, D] tensor into shared memory (row stride LD), rows >= T zero-filled
+template <int HD>
+__device__ __forceinline__ void load_tile(float* s, const float* src, long base, int row0, int T, int D) {
+  constexpr int LD = HD + 4, V4 = HD / 4;
+  for (int e = threadIdx.x; e < AT_BLK * V4; e += AT_THREADS) {
+    int r = e / V4, c4 = e - r * V4, row = row0 + r;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (row < T) v = *reinterpret_cast<const float4*>(src + base + (long)row * D + c4 * 4);
+    *reinterpret_cast<float4*>(s + r * LD + c4 * 4) = v;
+  }
+}
+__device__ __forceinline__ float quad_max(float v) { v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1)); return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2)); }
+__device__ __forceinline__ float quad_sum(float v) { v += __shfl_xor_sync(0xffffffffu, v, 1); return v + __shfl_xor_sync(0xffffffffu, v, 2); }
+
+// ---------------------------------------------------------------- forward
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS) attn_fwd_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                                                               float* __restrict__ O, float* __restrict__ Mst, float* __restrict__ Lst,
+                                                               int T, int D, int H, int causal, float inv_scale) {
+  constexpr int LD = HD + 4, NT = HD / 8;
+  extern __shared__ __align__(16) float sm[];
+  float* Qs = sm; float* Ks = Qs + AT_BLK * LD; float* Vs = Ks + AT_BLK * LD;
+  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z, q0 = qb * AT_BLK;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const long base = (long)b * T * D + (long)h * HD;
+  load_tile<HD>(Qs, Q, base, q0, T, D);
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; i++) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
+  const int nkb = causal ? qb + 1 : (T + AT_BLK - 1) / AT_BLK;
+  const int r0 = warp * 16, i0 = q0 + r0 + g, i1 = i0 + 8;
+  for (int kb = 0; kb < nkb; kb++) {
+    __syncthreads();
+    load_tile<HD>(Ks, K, base, kb * AT_BLK, T, D);
+    load_tile<HD>(Vs, V, base, kb * AT_BLK, T, D);
+    __syncthreads();
+    float s[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; n++) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < NT; ks++) {
+      FragA a; load_a(a, Qs, LD, r0, ks * 8, g, t);
+#pragma unroll
+      for (int n = 0; n < 8; n++) { FragB bf; load_b_nk(bf, Ks, LD, n * 8, ks * 8, g, t); mma3(s[n], a, bf); }
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < 8; n++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        int j = kb * AT_BLK + n * 8 + 2 * t + (e & 1), i = (e < 2) ? i0 : i1;
+        float v = s[n][e] * inv_scale;
+        if (j >= T || (causal && j > i)) v = -INFINITY;
+        s[n][e] = v;
+        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    mx0 = quad_max(mx0); mx1 = quad_max(mx1);
+    const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+    const float c0 = expf(m[0] - mn0), c1 = expf(m[1] - mn1);
+    float rs0 = 0.f, rs1 = 0.f;
+#pragma unroll
+    for (int n = 0; n < 8; n++) {
+      s[n][0] = expf(s[n][0] - mn0); s[n][1] = expf(s[n][1] - mn0); s[n][2] = expf(s[n][2] - mn1); s[n][3] = expf(s[n][3] - mn1);
+      rs0 += s[n][0] + s[n][1]; rs1 += s[n][2] + s[n][3];
+    }
+    rs0 = quad_sum(rs0); rs1 = quad_sum(rs1);
+    l[0] = l[0] * c0 + rs0; l[1] = l[1] * c1 + rs1; m[0] = mn0; m[1] = mn1;
+#pragma unroll
+    for (int d = 0; d < NT; d++) { o[d][0] *= c0; o[d][1] *= c0; o[d][2] *= c1; o[d][3] *= c1; }
+#pragma unroll
+    for (int kt = 0; kt < 8; kt++) {
+      FragA a; acc_to_a(a, s[kt]);
+#pragma unroll
+      for (int d = 0; d < NT; d++) { FragB bf; load_b_kn2(bf, Vs, LD, kt * 8, d * 8, g, t); mma3(o[d], a, bf); }
+    }
+  }
+  const float il0 = 1.f / l[0], il1 = 1.f / l[1];
+#pragma unroll
+  for (int d = 0; d < NT; d++) {
+    if (i0 < T) *reinterpret_cast<float2*>(O + base + (long)i0 * D + d * 8 + 2 * t) = make_float2(o[d][0] * il0, o[d][1] * il0);
+    if (i1 < T) *reinterpret_cast<float2*>(O + base + (long)i1 * D + d * 8 + 2 * t) = make_float2(o[d][2] * il1, o[d][3] * il1);
+  }
+  if (t == 0) {
+    const long sb = ((long)b * H + h) * T;
+    if (i0 < T) { Mst[sb + i0] = m[0]; Lst[sb + i0] = l[0]; }
+    if (i1 < T) { Mst[sb + i1] = m[1]; Lst[sb + i1] = l[1]; }
+  }
+}
+
+// Dv[b,h,i] = sum_d dO[b,i,h*HD+d] * O[b,i,h*HD+d]   (= sum_k dP_ik P_ik, the softmax-Jacobian row term)
+__global__ void attn_rowdot_kernel(const float* __restrict__ dO, const float* __restrict__ O, float* __restrict__ Dv, int T, int D, int H, int HD, long rows) {
+  long w = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if (w >= rows) return;     // w = (b*T + i)*H + h
+  int lane = threadIdx.x & 31; int h = (int)(w % H); long tok = w / H; int i = (int)(tok % T); long b = tok / T;
+  const float* p = dO + tok * D + (long)h * HD; const float* q = O + tok * D + (long)h * HD;
+  float s = 0.f;
+  for (int d = lane; d < HD; d += 32) s = fmaf(p[d], q[d], s);
+  s = warp_sum(s);
+  if (lane == 0) Dv[(b * H + h) * T + i] = s;
+}
+
+}  // namespace gn

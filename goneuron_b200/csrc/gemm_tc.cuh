@@ -226,13 +226,20 @@ __device__ __forceinline__ float tf32_round(float x) { uint32_t u; asm("cvt.rna.
 // (z, r, c) at p + (z / batch2) * b1 + (z % batch2) * b2 + r * s_r + c * s_c.  One of s_r, s_c is 1:
 // s_c == 1 reads rows directly; s_r == 1 (the operand is the transpose of what is stored) goes through a shared tile.
 struct TcSrc { const float* p; long s_r, s_c, b1, b2; int batch2; };
-__global__ void split_rows_kernel(TcSrc s, int rows, int cols, long total, float* __restrict__ hi, float* __restrict__ lo, int ldp) {
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
-    int c = (int)(i % ldp); long q = i / ldp; int r = (int)(q % rows); int z = (int)(q / rows);
-    float x = c < cols ? s.p[(z / s.batch2) * s.b1 + (z % s.batch2) * s.b2 + r * s.s_r + c] : 0.f;
-    float h = tf32_round(x);
-    hi[i] = h; lo[i] = x - h;
-  }
+__global__ void split_rows_kernel(TcSrc s, int rows, int cols, float* __restrict__ hi, float* __restrict__ lo, int ldp) {
+  // one float4 per thread; blockIdx.y = problem index
+  const int z = blockIdx.y, ldp4 = ldp >> 2;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * ldp4) return;
+  const int r = idx / ldp4, c = (idx - r * ldp4) << 2;
+  const float* src = s.p + (z / s.batch2) * s.b1 + (z % s.batch2) * s.b2 + (long)r * s.s_r + c;
+  float4 x;
+  if (c + 3 < cols && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) x = *reinterpret_cast<const float4*>(src);
+  else { x.x = c < cols ? src[0] : 0.f; x.y = c + 1 < cols ? src[1] : 0.f; x.z = c + 2 < cols ? src[2] : 0.f; x.w = c + 3 < cols ? src[3] : 0.f; }
+  float4 h = make_float4(tf32_round(x.x), tf32_round(x.y), tf32_round(x.z), tf32_round(x.w));
+  float4 l = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+  const long o = ((long)z * rows + r) * ldp + c;
+  *reinterpret_cast<float4*>(hi + o) = h; *reinterpret_cast<float4*>(lo + o) = l;
 }
 __global__ void split_cols_kernel(TcSrc s, int rows, int cols, float* __restrict__ hi, float* __restrict__ lo, int ldp) {
   __shared__ float t[32][33];
@@ -282,8 +289,8 @@ inline int tc_make_map(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const floa
 // Writes the planes of an operand.
 inline int tc_split(Ctx* ctx, const TcSrc& src, const TcPlanes& p) {
   if (src.s_c == 1) {
-    long total = (long)p.nbatch * p.rows * p.ldp;
-    GN_LAUNCH(ctx, split_rows_kernel, (unsigned)std::min<long>((total + 255) / 256, (long)ctx->sm_count * 32), 256, 0, src, p.rows, p.K, total, p.hi, p.lo, p.ldp);
+    if (p.nbatch > 65535) return fail(GN_ERR_UNSUPPORTED, "tc_split: more than 65535 problems in a batch");
+    GN_LAUNCH(ctx, split_rows_kernel, dim3(cdiv((long)p.rows * (p.ldp >> 2), 256), p.nbatch), 256, 0, src, p.rows, p.K, p.hi, p.lo, p.ldp);
   } else if (src.s_r == 1) {
     GN_LAUNCH(ctx, split_cols_kernel, dim3(cdiv(p.ldp, 32), cdiv(p.rows, 32), p.nbatch), dim3(32, 8), 0, src, p.rows, p.K, p.hi, p.lo, p.ldp);
   } else return fail(GN_ERR_UNSUPPORTED, "tc_split: neither stride of the operand is 1");
