@@ -154,4 +154,177 @@ __global__ void attn_rowdot_kernel(const float* __restrict__ dO, const float* __
   if (lane == 0) Dv[(b * H + h) * T + i] = s;
 }
 
+
+// ---------------------------------------------------------------- backward: dQ
+// One CTA = 64 query rows; for every key block at or below the diagonal: S = Q K^T, P = exp(S/sqrt(hd) - m) / l,
+// dP = dO V^T, dS = P (dP - Dv) / sqrt(hd), dQ += dS K.
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS) attn_bwd_dq_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                                                                  const float* __restrict__ dO, const float* __restrict__ Mst, const float* __restrict__ Lst,
+                                                                  const float* __restrict__ Dv, float* __restrict__ dQ, int T, int D, int H, int causal, float inv_scale) {
+  constexpr int LD = HD + 4, NT = HD / 8;
+  extern __shared__ __align__(16) float sm[];
+  float* Qs = sm; float* Gs = Qs + AT_BLK * LD; float* Ks = Gs + AT_BLK * LD; float* Vs = Ks + AT_BLK * LD;
+  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z, q0 = qb * AT_BLK;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const long base = (long)b * T * D + (long)h * HD, sb = ((long)b * H + h) * T;
+  load_tile<HD>(Qs, Q, base, q0, T, D);
+  load_tile<HD>(Gs, dO, base, q0, T, D);
+  const int r0 = warp * 16, i0 = q0 + r0 + g, i1 = i0 + 8;
+  const float m0 = i0 < T ? Mst[sb + i0] : 0.f, m1 = i1 < T ? Mst[sb + i1] : 0.f;
+  const float il0 = i0 < T ? 1.f / Lst[sb + i0] : 0.f, il1 = i1 < T ? 1.f / Lst[sb + i1] : 0.f;
+  const float d0 = i0 < T ? Dv[sb + i0] : 0.f, d1 = i1 < T ? Dv[sb + i1] : 0.f;
+  float acc[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+  const int nkb = causal ? qb + 1 : (T + AT_BLK - 1) / AT_BLK;
+  for (int kb = 0; kb < nkb; kb++) {
+    __syncthreads();
+    load_tile<HD>(Ks, K, base, kb * AT_BLK, T, D);
+    load_tile<HD>(Vs, V, base, kb * AT_BLK, T, D);
+    __syncthreads();
+    float s[8][4], dp[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; n++) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; dp[n][0] = dp[n][1] = dp[n][2] = dp[n][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < NT; ks++) {
+      FragA a, ga; load_a(a, Qs, LD, r0, ks * 8, g, t); load_a(ga, Gs, LD, r0, ks * 8, g, t);
+#pragma unroll
+      for (int n = 0; n < 8; n++) {
+        FragB bf; load_b_nk(bf, Ks, LD, n * 8, ks * 8, g, t); mma3(s[n], a, bf);
+        load_b_nk(bf, Vs, LD, n * 8, ks * 8, g, t); mma3(dp[n], ga, bf);
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < 8; n++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int j = kb * AT_BLK + n * 8 + 2 * t + (e & 1), i = (e < 2) ? i0 : i1;
+        const bool masked = j >= T || i >= T || (causal && j > i);
+        const float p = masked ? 0.f : expf(s[n][e] * inv_scale - (e < 2 ? m0 : m1)) * (e < 2 ? il0 : il1);
+        s[n][e] = p * (dp[n][e] - (e < 2 ? d0 : d1)) * inv_scale;        // dS
+      }
+#pragma unroll
+    for (int kt = 0; kt < 8; kt++) {
+      FragA a; acc_to_a(a, s[kt]);
+#pragma unroll
+      for (int d = 0; d < NT; d++) { FragB bf; load_b_kn2(bf, Ks, LD, kt * 8, d * 8, g, t); mma3(acc[d], a, bf); }
+    }
+  }
+#pragma unroll
+  for (int d = 0; d < NT; d++) {
+    if (i0 < T) *reinterpret_cast<float2*>(dQ + base + (long)i0 * D + d * 8 + 2 * t) = make_float2(acc[d][0], acc[d][1]);
+    if (i1 < T) *reinterpret_cast<float2*>(dQ + base + (long)i1 * D + d * 8 + 2 * t) = make_float2(acc[d][2], acc[d][3]);
+  }
+}
+
+// ---------------------------------------------------------------- backward: dK, dV
+// One CTA = 64 key rows; for every query block at or above the diagonal the TRANSPOSED tiles are formed directly:
+// S^T = K Q^T, P^T, dP^T = V dO^T, dS^T = P^T (dP^T - Dv[query]) / sqrt(hd); dK += dS^T Q, dV += P^T dO.
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS) attn_bwd_dkv_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                                                                   const float* __restrict__ dO, const float* __restrict__ Mst, const float* __restrict__ Lst,
+                                                                   const float* __restrict__ Dv, float* __restrict__ dK, float* __restrict__ dV,
+                                                                   int T, int D, int H, int causal, float inv_scale) {
+  constexpr int LD = HD + 4, NT = HD / 8;
+  extern __shared__ __align__(16) float sm[];
+  float* Ks = sm; float* Vs = Ks + AT_BLK * LD; float* Qs = Vs + AT_BLK * LD; float* Gs = Qs + AT_BLK * LD;
+  float* st_m = Gs + AT_BLK * LD; float* st_il = st_m + AT_BLK; float* st_d = st_il + AT_BLK;
+  const int kbk = blockIdx.x, h = blockIdx.y, b = blockIdx.z, k0 = kbk * AT_BLK;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const long base = (long)b * T * D + (long)h * HD, sb = ((long)b * H + h) * T;
+  load_tile<HD>(Ks, K, base, k0, T, D);
+  load_tile<HD>(Vs, V, base, k0, T, D);
+  const int r0 = warp * 16, j0 = k0 + r0 + g, j1 = j0 + 8;
+  float ak[NT][4], av[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; i++) { ak[i][0] = ak[i][1] = ak[i][2] = ak[i][3] = 0.f; av[i][0] = av[i][1] = av[i][2] = av[i][3] = 0.f; }
+  const int nqb = (T + AT_BLK - 1) / AT_BLK;
+  for (int qb = causal ? kbk : 0; qb < nqb; qb++) {
+    __syncthreads();
+    load_tile<HD>(Qs, Q, base, qb * AT_BLK, T, D);
+    load_tile<HD>(Gs, dO, base, qb * AT_BLK, T, D);
+    if (threadIdx.x < AT_BLK) {
+      const int i = qb * AT_BLK + threadIdx.x;
+      st_m[threadIdx.x] = i < T ? Mst[sb + i] : 0.f; st_il[threadIdx.x] = i < T ? 1.f / Lst[sb + i] : 0.f; st_d[threadIdx.x] = i < T ? Dv[sb + i] : 0.f;
+    }
+    __syncthreads();
+    float s[8][4], dp[8][4];
+#pragma unroll
+    for (int n = 0; n < 8; n++) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; dp[n][0] = dp[n][1] = dp[n][2] = dp[n][3] = 0.f; }
+#pragma unroll
+    for (int ks = 0; ks < NT; ks++) {
+      FragA a, va; load_a(a, Ks, LD, r0, ks * 8, g, t); load_a(va, Vs, LD, r0, ks * 8, g, t);
+#pragma unroll
+      for (int n = 0; n < 8; n++) {
+        FragB bf; load_b_nk(bf, Qs, LD, n * 8, ks * 8, g, t); mma3(s[n], a, bf);
+        load_b_nk(bf, Gs, LD, n * 8, ks * 8, g, t); mma3(dp[n], va, bf);
+      }
+    }
+    // rows = keys j (g, g+8), columns = queries i (2t, 2t+1 of n-tile n)
+#pragma unroll
+    for (int n = 0; n < 8; n++)
+#pragma unroll
+      for (int e = 0; e < 4; e++) {
+        const int ci = n * 8 + 2 * t + (e & 1), i = qb * AT_BLK + ci, j = (e < 2) ? j0 : j1;
+        const bool masked = j >= T || i >= T || (causal && j > i);
+        const float p = masked ? 0.f : expf(s[n][e] * inv_scale - st_m[ci]) * st_il[ci];
+        dp[n][e] = p * (dp[n][e] - st_d[ci]) * inv_scale;                 // dS^T
+        s[n][e] = p;                                                     // P^T
+      }
+#pragma unroll
+    for (int kt = 0; kt < 8; kt++) {
+      FragA ap, ads; acc_to_a(ap, s[kt]); acc_to_a(ads, dp[kt]);
+#pragma unroll
+      for (int d = 0; d < NT; d++) {
+        FragB bf; load_b_kn2(bf, Qs, LD, kt * 8, d * 8, g, t); mma3(ak[d], ads, bf);
+        load_b_kn2(bf, Gs, LD, kt * 8, d * 8, g, t); mma3(av[d], ap, bf);
+      }
+    }
+  }
+#pragma unroll
+  for (int d = 0; d < NT; d++) {
+    if (j0 < T) { *reinterpret_cast<float2*>(dK + base + (long)j0 * D + d * 8 + 2 * t) = make_float2(ak[d][0], ak[d][1]);
+                  *reinterpret_cast<float2*>(dV + base + (long)j0 * D + d * 8 + 2 * t) = make_float2(av[d][0], av[d][1]); }
+    if (j1 < T) { *reinterpret_cast<float2*>(dK + base + (long)j1 * D + d * 8 + 2 * t) = make_float2(ak[d][2], ak[d][3]);
+                  *reinterpret_cast<float2*>(dV + base + (long)j1 * D + d * 8 + 2 * t) = make_float2(av[d][2], av[d][3]); }
+  }
+}
+
+// ---------------------------------------------------------------- launchers
+inline bool attn_fused_supported(int hd, int D) { return (hd == 16 || hd == 32 || hd == 64) && D % 4 == 0; }
+
+template <int HD>
+inline int attn_fwd_launch(Ctx* ctx, const float* Q, const float* K, const float* V, float* O, float* M, float* L, int B, int T, int D, int H, int causal) {
+  size_t smem = (size_t)3 * AT_BLK * (HD + 4) * sizeof(float);
+  GN_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  GN_LAUNCH(ctx, attn_fwd_kernel<HD>, dim3(cdiv(T, AT_BLK), H, B), AT_THREADS, smem, Q, K, V, O, M, L, T, D, H, causal, 1.f / sqrtf((float)HD));
+  return check_launch("attn_fwd");
+}
+template <int HD>
+inline int attn_bwd_launch(Ctx* ctx, const float* Q, const float* K, const float* V, const float* O, const float* dO, const float* M, const float* L, float* Dv,
+                           float* dQ, float* dK, float* dV, int B, int T, int D, int H, int causal) {
+  const float inv_scale = 1.f / sqrtf((float)HD);
+  long rows = (long)B * T * H;
+  GN_LAUNCH(ctx, attn_rowdot_kernel, cdiv(rows, 8), 256, 0, dO, O, Dv, T, D, H, HD, rows);
+  size_t smem_q = (size_t)4 * AT_BLK * (HD + 4) * sizeof(float), smem_kv = smem_q + 3 * AT_BLK * sizeof(float);
+  GN_CUDA(cudaFuncSetAttribute(attn_bwd_dq_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q));
+  GN_CUDA(cudaFuncSetAttribute(attn_bwd_dkv_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv));
+  dim3 grid(cdiv(T, AT_BLK), H, B);
+  GN_LAUNCH(ctx, attn_bwd_dq_kernel<HD>, grid, AT_THREADS, smem_q, Q, K, V, dO, M, L, Dv, dQ, T, D, H, causal, inv_scale);
+  GN_LAUNCH(ctx, attn_bwd_dkv_kernel<HD>, grid, AT_THREADS, smem_kv, Q, K, V, dO, M, L, Dv, dK, dV, T, D, H, causal, inv_scale);
+  return check_launch("attn_bwd");
+}
+inline int attn_fwd(Ctx* ctx, int hd, const float* Q, const float* K, const float* V, float* O, float* M, float* L, int B, int T, int D, int H, int causal) {
+  if (hd == 64) return attn_fwd_launch<64>(ctx, Q, K, V, O, M, L, B, T, D, H, causal);
+  if (hd == 32) return attn_fwd_launch<32>(ctx, Q, K, V, O, M, L, B, T, D, H, causal);
+  return attn_fwd_launch<16>(ctx, Q, K, V, O, M, L, B, T, D, H, causal);
+}
+inline int attn_bwd(Ctx* ctx, int hd, const float* Q, const float* K, const float* V, const float* O, const float* dO, const float* M, const float* L, float* Dv,
+                    float* dQ, float* dK, float* dV, int B, int T, int D, int H, int causal) {
+  if (hd == 64) return attn_bwd_launch<64>(ctx, Q, K, V, O, dO, M, L, Dv, dQ, dK, dV, B, T, D, H, causal);
+  if (hd == 32) return attn_bwd_launch<32>(ctx, Q, K, V, O, dO, M, L, Dv, dQ, dK, dV, B, T, D, H, causal);
+  return attn_bwd_launch<16>(ctx, Q, K, V, O, dO, M, L, Dv, dQ, dK, dV, B, T, D, H, causal);
+}
+
 }  // namespace gn

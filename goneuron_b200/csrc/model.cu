@@ -23,6 +23,7 @@
 #include "gemm_tc.cuh"
 #include "rowops.cuh"
 #include "conv_lstm.cuh"
+#include "attention.cuh"
 #include "nccl_dl.cuh"
 
 namespace gn {
@@ -74,6 +75,7 @@ struct LayerRT {
   // forward state kept for backward
   DevBuf out, z;                       // activation / pre-activation  [cap, out_size]
   DevBuf q, k, v, att, r1, n1, mid, r2, stat;   // TransformerBlock
+  DevBuf att_m, att_l, att_d;          // fused attention: per-row softmax maximum, sum, and dO.O  [batch*heads*T]
   DevBuf pre_i, c_all, h_all, dgate;   // LSTM
   DevBuf idx;                          // int32 payload: MaxPool argmax / embedding token ids
   const float* fin = nullptr;          // input of the last forward call (device pointer, not owned)
@@ -189,7 +191,8 @@ static int alloc_activations(gn_model* m, int cap) {
       case GN_LAYER_TRANSFORMER_BLOCK: {
         size_t nd = c * d.seq_len * d.dim, nf = c * d.seq_len * d.ff_dim, nt = c * d.seq_len;
         GN_TRY(l.q.alloc(nd)); GN_TRY(l.k.alloc(nd)); GN_TRY(l.v.alloc(nd)); GN_TRY(l.att.alloc(nd)); GN_TRY(l.r1.alloc(nd)); GN_TRY(l.n1.alloc(nd));
-        GN_TRY(l.mid.alloc(nf)); GN_TRY(l.r2.alloc(nd)); GN_TRY(l.out.alloc(nd)); GN_TRY(l.stat.alloc(4 * nt)); break; }
+        GN_TRY(l.mid.alloc(nf)); GN_TRY(l.r2.alloc(nd)); GN_TRY(l.out.alloc(nd)); GN_TRY(l.stat.alloc(4 * nt));
+        GN_TRY(l.att_m.alloc(nt * d.heads)); GN_TRY(l.att_l.alloc(nt * d.heads)); GN_TRY(l.att_d.alloc(nt * d.heads)); break; }
       case GN_LAYER_CLS_POOLING: GN_TRY(l.out.alloc(c * l.out_size)); break;
       case GN_LAYER_LAYERNORM: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.stat.alloc(2 * c * (l.in_size / d.dim))); break;
     }
@@ -207,6 +210,13 @@ static int colsum(gn_model* m, const float* in, long ld, int R, int C, float* ou
   GN_LAUNCH(ctx, colsum_partial_kernel, dim3(cdiv(C, 128), chunks), 128, 0, in, ld, R, C, part);
   GN_LAUNCH(ctx, colsum_final_kernel, cdiv(C, 128), 128, 0, part, chunks, C, out, accumulate ? 1 : 0);
   return check_launch("colsum");
+}
+
+// The fused kernels (attention.cuh) are the default; GONEURON_CUDA_ATTENTION=unfused selects the path that
+// materialises the score matrices and runs the five products as batched contractions on the tcgen05 engine.
+static bool use_fused_attention(const gn_layer_desc& d) {
+  static const bool unfused = [] { const char* e = getenv("GONEURON_CUDA_ATTENTION"); return e && strcmp(e, "unfused") == 0; }();
+  return !unfused && attn_fused_supported(d.dim / d.heads, d.dim);
 }
 
 // ---------------------------------------------------------------- forward
@@ -290,8 +300,12 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out) {
         GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wq, bp.bq, l.q.p, D));
         GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wk, bp.bk, l.k.p, D));
         GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wv, bp.bv, l.v.p, D));
-        float* P; GN_TRY(ensure(m, S_ATT0, (size_t)B * d.heads * T * T, &P));
-        GN_TRY(attention_forward(m, l, B, P));
+        if (use_fused_attention(d)) {
+          GN_TRY(attn_fwd(ctx, D / d.heads, l.q.p, l.k.p, l.v.p, l.att.p, l.att_m.p, l.att_l.p, B, T, D, d.heads, d.causal));
+        } else {
+          float* P; GN_TRY(ensure(m, S_ATT0, (size_t)B * d.heads * T * T, &P));
+          GN_TRY(attention_forward(m, l, B, P));
+        }
         GN_TRY(gemm_nt(ctx, N, D, D, l.att.p, D, bp.wo, bp.bo, l.r1.p, D, GN_ACT_LINEAR, cur, D));          // res1 = x + att
         float* st = l.stat.p;
         GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(N, 8), 256, 0, l.r1.p, bp.g1, bp.be1, l.n1.p, st, st + N, (long)N, D, 1e-5f);
@@ -325,10 +339,11 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
   Ctx* ctx = &m->ctx->c; const gn_layer_desc& d = l.d;
   const int T = d.seq_len, D = d.dim, F = d.ff_dim, Hh = d.heads, hd = D / Hh; const int N = B * T; const long ND = (long)N * D;
   BlockParams bp = block_params(m->params.p + l.p_off, D, F); BlockParams gp = block_params(m->grads.p + l.p_off, D, F);
-  float *dR2, *dM, *comb, *dR1, *dA, *P, *dP; float* st = l.stat.p;
+  float *dR2, *dM, *comb, *dR1, *dA, *P = nullptr, *dP = nullptr; float* st = l.stat.p;
+  const bool fused = use_fused_attention(d);
   GN_TRY(ensure(m, S_ND0, ND, &dR2)); GN_TRY(ensure(m, S_NFF, (size_t)N * F, &dM)); GN_TRY(ensure(m, S_ND1, ND, &comb));
   GN_TRY(ensure(m, S_ND2, ND, &dR1)); GN_TRY(ensure(m, S_ND3, ND, &dA));
-  GN_TRY(ensure(m, S_ATT0, (size_t)B * Hh * T * T, &P)); GN_TRY(ensure(m, S_ATT1, (size_t)B * Hh * T * T, &dP));
+  if (!fused) { GN_TRY(ensure(m, S_ATT0, (size_t)B * Hh * T * T, &P)); GN_TRY(ensure(m, S_ATT1, (size_t)B * Hh * T * T, &dP)); }
   float* part; int chunks = std::max(1, std::min(N / 64, 128)); GN_TRY(ensure(m, S_PART2, (size_t)chunks * 2 * std::max(D, F), &part));
   // LayerNorm 2
   GN_LAUNCH(ctx, layernorm_pgrad_partial_kernel, dim3(cdiv(D, 128), chunks), 128, 0, gout, l.r2.p, st + 2 * N, st + 3 * N, (long)N, D, part);
@@ -348,23 +363,23 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
   GN_TRY(inner_dense_param_grads(m, dR1, B, T, D, l.att.p, D, (float*)gp.wo, (float*)gp.bo));
   GN_TRY(gemm_nn(ctx, N, D, D, dR1, D, bp.wo, dA, D));
   // attention: recompute P (transformer.go:610-622), then dP, dS, dQ, dK, dV
-  const long TD = (long)T * D, TT = (long)T * T; const float inv_scale = 1.f / sqrtf((float)hd); const long rows = (long)B * Hh * T;
-  {
+  float *dQ, *dK, *dV;
+  GN_TRY(ensure(m, S_ND0, ND, &dQ)); GN_TRY(ensure(m, S_ND1, ND, &dK)); GN_TRY(ensure(m, S_ND4, ND, &dV));   // dR2 / comb are dead by now
+  if (fused) {
+    GN_TRY(attn_bwd(ctx, hd, l.q.p, l.k.p, l.v.p, l.att.p, dA, l.att_m.p, l.att_l.p, l.att_d.p, dQ, dK, dV, B, T, D, Hh, d.causal));
+  } else {
+    const long TD = (long)T * D, TT = (long)T * T; const float inv_scale = 1.f / sqrtf((float)hd); const long rows = (long)B * Hh * T;
     GemmDesc g; g.M = T; g.N = T; g.K = hd; g.A = l.q.p; g.sa_m = D; g.sa_k = 1; g.B = l.k.p; g.sb_k = 1; g.sb_n = D;
     g.C = P; g.ldc = T; g.batch1 = B; g.batch2 = Hh; g.a_b1 = TD; g.a_b2 = hd; g.b_b1 = TD; g.b_b2 = hd; g.c_b1 = Hh * TT; g.c_b2 = TT;
     g.flags = d.causal ? GEMM_SKIP_UPPER : 0; GN_TRY(gemm(ctx, g));
     GN_LAUNCH(ctx, attn_softmax_kernel, cdiv(rows, 8), 256, 0, P, T, inv_scale, d.causal, rows);
     g.A = dA; g.B = l.v.p; g.C = dP; GN_TRY(gemm(ctx, g));                               // dP = dA V^T
     GN_LAUNCH(ctx, attn_ds_kernel, cdiv(rows, 8), 256, 0, P, dP, T, inv_scale, d.causal, rows);   // dP <- dS (scaled)
-  }
-  float *dQ, *dK, *dV;
-  GN_TRY(ensure(m, S_ND0, ND, &dQ)); GN_TRY(ensure(m, S_ND1, ND, &dK)); GN_TRY(ensure(m, S_ND4, ND, &dV));   // dR2 / comb are dead by now
-  {
-    GemmDesc g; g.M = T; g.N = hd; g.K = T; g.batch1 = B; g.batch2 = Hh; g.a_b1 = Hh * TT; g.a_b2 = TT; g.b_b1 = TD; g.b_b2 = hd; g.c_b1 = TD; g.c_b2 = hd; g.ldc = D;
-    g.sb_k = D; g.sb_n = 1;
-    g.A = dP; g.sa_m = T; g.sa_k = 1; g.B = l.k.p; g.C = dQ; g.flags = d.causal ? GEMM_KEND_AT_M0 : 0; GN_TRY(gemm(ctx, g));     // dQ = dS K
-    g.A = dP; g.sa_m = 1; g.sa_k = T; g.B = l.q.p; g.C = dK; g.flags = d.causal ? GEMM_KBEG_AT_M0 : 0; GN_TRY(gemm(ctx, g));     // dK = dS^T Q
-    g.A = P; g.B = dA; g.C = dV; GN_TRY(gemm(ctx, g));                                                                          // dV = P^T dA
+    GemmDesc q; q.M = T; q.N = hd; q.K = T; q.batch1 = B; q.batch2 = Hh; q.a_b1 = Hh * TT; q.a_b2 = TT; q.b_b1 = TD; q.b_b2 = hd; q.c_b1 = TD; q.c_b2 = hd; q.ldc = D;
+    q.sb_k = D; q.sb_n = 1;
+    q.A = dP; q.sa_m = T; q.sa_k = 1; q.B = l.k.p; q.C = dQ; q.flags = d.causal ? GEMM_KEND_AT_M0 : 0; GN_TRY(gemm(ctx, q));     // dQ = dS K
+    q.A = dP; q.sa_m = 1; q.sa_k = T; q.B = l.q.p; q.C = dK; q.flags = d.causal ? GEMM_KBEG_AT_M0 : 0; GN_TRY(gemm(ctx, q));     // dK = dS^T Q
+    q.A = P; q.B = dA; q.C = dV; GN_TRY(gemm(ctx, q));                                                                          // dV = P^T dA
   }
   // q, k, v projections; gradIn = dq + dk + dv, block input gradient = gradRes1 + gradIn
   GN_TRY(inner_dense_param_grads(m, dQ, B, T, D, xin, D, (float*)gp.wq, (float*)gp.bq));

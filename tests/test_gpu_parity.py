@@ -31,6 +31,9 @@ CASES = [
     ("transformer_small", dict(vocab=300, dim=48, seq_len=20, heads=3, ff_dim=100, n_blocks=1), 5, 2),
     ("transformer_small", {}, 64, 1),                               # the full small-transformer config
     ("transformer_large", dict(vocab=2000, dim=256, seq_len=64, heads=16, ff_dim=1024, n_blocks=2), 16, 1),
+    ("transformer_large", dict(vocab=1000, dim=128, seq_len=80, heads=2, ff_dim=256, n_blocks=1), 6, 1),    # head width 64, T not a multiple of the 64-row block
+    ("transformer_small", dict(vocab=700, dim=96, seq_len=150, heads=3, ff_dim=192, n_blocks=1), 4, 1),     # head width 32, three key blocks, ragged tail
+    ("transformer_small", dict(vocab=300, dim=40, seq_len=20, heads=5, ff_dim=64, n_blocks=1), 4, 1),       # head width 8: the unfused attention path
 ]
 
 
@@ -147,3 +150,17 @@ def test_gemm_simt(device, oracle, M, N, K):
     _lib.check(_lib.load().gn_op_gemm_nt(device.handle, 0, M, N, K, f(A), f(B), f(bias), f(out)))
     ref = A.astype(np.float64) @ B.astype(np.float64).T + bias
     assert norm_err(out, ref) <= 1e-5
+
+
+def test_unfused_attention_path_in_subprocess():
+    """GONEURON_CUDA_ATTENTION=unfused selects the batched-contraction attention (score matrices in HBM, products on the
+    tcgen05 engine); it must give the same parity.  The switch is read once per process, hence the child process."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, GONEURON_CUDA_ATTENTION="unfused")
+    ids = "transformer_small-8 or transformer_small-10 or transformer_large-12"
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_parity.py"), "-q", "-x", "-m", "gpu", "-k", ids],
+                       env=env, cwd=root, capture_output=True, text=True)
+    assert r.returncode == 0 and " passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
