@@ -22,8 +22,10 @@ constexpr int AT_BLK = 64, AT_THREADS = 128;
 struct FragA { uint32_t hi[4], lo[4]; };
 struct FragB { uint32_t hi[2], lo[2]; };
 
+// hi = x with the 13 low mantissa bits cleared (exactly a TF32 value; a logic op, full rate -- the cvt.rna
+// conversion runs on a slow pipe), lo = x - hi (exact; the MMA reads its leading 10 mantissa bits).
 __device__ __forceinline__ void split32(float x, uint32_t& hi, uint32_t& lo) {
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(x));
+  hi = __float_as_uint(x) & 0xffffe000u;
   lo = __float_as_uint(x - __uint_as_float(hi));
 }
 __device__ __forceinline__ void mma8(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
@@ -112,11 +114,11 @@ __global__ void __launch_bounds__(AT_THREADS) attn_fwd_kernel(const float* __res
       }
     mx0 = quad_max(mx0); mx1 = quad_max(mx1);
     const float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
-    const float c0 = expf(m[0] - mn0), c1 = expf(m[1] - mn1);
+    const float c0 = __expf(m[0] - mn0), c1 = __expf(m[1] - mn1);
     float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
     for (int n = 0; n < 8; n++) {
-      s[n][0] = expf(s[n][0] - mn0); s[n][1] = expf(s[n][1] - mn0); s[n][2] = expf(s[n][2] - mn1); s[n][3] = expf(s[n][3] - mn1);
+      s[n][0] = __expf(s[n][0] - mn0); s[n][1] = __expf(s[n][1] - mn0); s[n][2] = __expf(s[n][2] - mn1); s[n][3] = __expf(s[n][3] - mn1);
       rs0 += s[n][0] + s[n][1]; rs1 += s[n][2] + s[n][3];
     }
     rs0 = quad_sum(rs0); rs1 = quad_sum(rs1);
@@ -201,7 +203,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_bwd_dq_kernel(const float* __
       for (int e = 0; e < 4; e++) {
         const int j = kb * AT_BLK + n * 8 + 2 * t + (e & 1), i = (e < 2) ? i0 : i1;
         const bool masked = j >= T || i >= T || (causal && j > i);
-        const float p = masked ? 0.f : expf(s[n][e] * inv_scale - (e < 2 ? m0 : m1)) * (e < 2 ? il0 : il1);
+        const float p = masked ? 0.f : __expf(s[n][e] * inv_scale - (e < 2 ? m0 : m1)) * (e < 2 ? il0 : il1);
         s[n][e] = p * (dp[n][e] - (e < 2 ? d0 : d1)) * inv_scale;        // dS
       }
 #pragma unroll
@@ -268,7 +270,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_bwd_dkv_kernel(const float* _
       for (int e = 0; e < 4; e++) {
         const int ci = n * 8 + 2 * t + (e & 1), i = qb * AT_BLK + ci, j = (e < 2) ? j0 : j1;
         const bool masked = j >= T || i >= T || (causal && j > i);
-        const float p = masked ? 0.f : expf(s[n][e] * inv_scale - st_m[ci]) * st_il[ci];
+        const float p = masked ? 0.f : __expf(s[n][e] * inv_scale - st_m[ci]) * st_il[ci];
         dp[n][e] = p * (dp[n][e] - st_d[ci]) * inv_scale;                 // dS^T
         s[n][e] = p;                                                     // P^T
       }
