@@ -21,6 +21,9 @@ struct GemmDesc {
   const float* bias = nullptr;                          // [N]
   const float* R = nullptr; long ldr = 0;               // residual added to the result (may alias C)
   int act = GN_ACT_LINEAR;                              // LINEAR or RELU
+  // optional gate: result(m,n) is zeroed unless mask[(m / mask_group) * mask_ld + n] > 0 (the ReLU pattern of the
+  // last token of row m's sequence, see relu_mask semantics in model.cu)
+  const float* mask = nullptr; long mask_ld = 0; int mask_group = 1;
   float alpha = 1.f;
   int batch1 = 1, batch2 = 1;                           // batch index b -> (b / batch2, b % batch2)
   long a_b1 = 0, a_b2 = 0, b_b1 = 0, b_b2 = 0, c_b1 = 0, c_b2 = 0, r_b1 = 0, r_b2 = 0;
@@ -99,6 +102,7 @@ __global__ void __launch_bounds__(SG_THREADS) gemm_simt_kernel(GemmDesc g) {
       if (g.bias) v += g.bias[n];
       if (R) v += R[m * g.ldr + n];
       if (g.act == GN_ACT_RELU) v = v > 0.f ? v : 0.f;
+      if (g.mask && !(g.mask[(long)(m / g.mask_group) * g.mask_ld + n] > 0.f)) v = 0.f;
       C[m * g.ldc + n] = v;
     }
   }

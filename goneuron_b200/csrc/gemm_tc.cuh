@@ -23,18 +23,22 @@
 // still runs to its end (TMEM is always released).
 #pragma once
 #include <cuda.h>
+#include <cstdlib>
 #include "common.cuh"
 #include "gemm_simt.cuh"
 
 namespace gn {
 
-constexpr int TC_BM = 128, TC_BK = 32, TC_THREADS = 192;
-constexpr int TC_A_BYTES = TC_BM * TC_BK * 4;
+constexpr int TC_BM = 128, TC_THREADS = 192;
 constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
-template <int BN> struct TcCfg {
-  static constexpr int STAGES = BN == 256 ? 2 : (BN == 128 ? 3 : 4);
-  static constexpr int B_BYTES = BN * TC_BK * 4;
-  static constexpr int STAGE_BYTES = 2 * TC_A_BYTES + 2 * B_BYTES;
+constexpr int TC_FLAG_VEC = 4096;   // epilogue may use 16-byte accesses (set by the host when every pointer and stride allows it)
+// BK = 32 floats (one 128-byte swizzle row) or 16 (64-byte swizzle): same bytes per FLOP, but half-size stages keep
+// more of the shared memory in flight while one stage is being consumed.
+template <int BN, int BK> struct TcCfg {
+  static constexpr int A_BYTES = TC_BM * BK * 4;
+  static constexpr int B_BYTES = BN * BK * 4;
+  static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
   static constexpr int TMEM_COLS = 2 * BN;
 };
@@ -69,8 +73,11 @@ __device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t adesc, uin
 }
 // Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows are 128 bytes apart, groups of 8
 // rows 1024 bytes apart (stride byte offset), descriptor version 1 (sm_100), layout type 2 = SWIZZLE_128B.
+// With 64-byte rows (BK = 16): groups of 8 rows are 512 bytes apart and the layout type is 4 = SWIZZLE_64B.
+template <int BK>
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
-  return (uint64_t)((saddr >> 4) & 0x3FFF) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+  constexpr uint64_t sbo = (8 * BK * 4) >> 4, layout = BK == 32 ? 2 : 4;
+  return (uint64_t)((saddr >> 4) & 0x3FFF) | (1ull << 16) | (sbo << 32) | (1ull << 46) | (layout << 61);
 }
 // Instruction descriptor: D = f32 (bits 4-5 = 1), A = B = tf32 (bits 7-9, 10-12 = 2), both K-major,
 // N >> 3 at bits 17-22, M >> 4 at bits 24-28.
@@ -92,14 +99,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 struct TcParams {
   float* C; long ldc, c_b1, c_b2; const float* bias; const float* R; long ldr, r_b1, r_b2;
   int act, M, N, K, batch2, flags; int* status;
+  const float* mask; long mask_ld; int mask_group;    // optional gate, see GemmDesc::mask
 };
 
-template <int BN>
+template <int BN, int BK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
                const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo, TcParams ep) {
-  using Cfg = TcCfg<BN>;
-  constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, B_BYTES = Cfg::B_BYTES;
+  using Cfg = TcCfg<BN, BK>;
+  constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, B_BYTES = Cfg::B_BYTES, TC_A_BYTES = Cfg::A_BYTES, TC_BK = BK;
   const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * BN, z = blockIdx.z;
   // causal attention products: tiles above the diagonal do not exist; the contraction range is clipped to the diagonal
   if ((ep.flags & GEMM_SKIP_UPPER) && n0 > m0 + TC_BM - 1) return;
@@ -129,8 +137,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  const bool noload = (ep.flags & 256) != 0;   // tuning aid: issue the MMAs without feeding them (results are meaningless)
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && !noload) {
       bool ok = true;
       for (int i = 0; i < nkb; i++) {
         const int s = i % STAGES, use = i / STAGES, kc = (kb0 + i) * TC_BK;
@@ -150,11 +159,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
       constexpr uint32_t idesc = make_idesc(TC_BM, BN);
       for (int i = 0; i < nkb; i++) {
         const int s = i % STAGES, use = i / STAGES;
-        ok &= mbar_wait(full0 + 8 * s, use & 1);
+        if (!noload) ok &= mbar_wait(full0 + 8 * s, use & 1);
         tc_fence_after();
         const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t ahi = make_desc(base), alo = make_desc(base + TC_A_BYTES);
-        const uint64_t bhi = make_desc(base + 2 * TC_A_BYTES), blo = make_desc(base + 2 * TC_A_BYTES + B_BYTES);
+        const uint64_t ahi = make_desc<BK>(base), alo = make_desc<BK>(base + TC_A_BYTES);
+        const uint64_t bhi = make_desc<BK>(base + 2 * TC_A_BYTES), blo = make_desc<BK>(base + 2 * TC_A_BYTES + B_BYTES);
 #pragma unroll
         for (int k = 0; k < TC_BK / 8; k++) {
           const uint64_t adv = (uint64_t)((k * 8 * 4) >> 4);          // 8 tf32 = 32 bytes along K inside the swizzle atom
@@ -180,38 +189,59 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
     const int z1 = z / ep.batch2, z2 = z % ep.batch2;
     float* C = ep.C + z1 * ep.c_b1 + z2 * ep.c_b2;
     const float* R = ep.R ? ep.R + z1 * ep.r_b1 + z2 * ep.r_b2 : nullptr;
-    // the pipeline stages are idle once the accumulator barrier fired: reuse stage memory as a per-warp 32x33 transpose tile
-    float* tile = (float*)smem + (warp - 2) * (32 * 33);
-    const int row_base = m0 + quad * 32;
+    // One output row per thread (TMEM lane = row): 32 consecutive columns per tcgen05.ld, written as 8 float4.
+    // Bias, residual and gate values of a chunk are fetched before the TMEM wait so their latency overlaps.
+    const int row = m0 + quad * 32 + lane;
+    const bool row_ok = row < ep.M;
+    const float* Rrow = (R && row_ok) ? R + (long)row * ep.ldr : nullptr;
+    const float* Mrow = (ep.mask && row_ok) ? ep.mask + (long)(row / ep.mask_group) * ep.mask_ld : nullptr;
+    float* Crow = C + (long)row * ep.ldc;
+    const bool vec = (ep.flags & TC_FLAG_VEC) != 0;
     for (int c = 0; c < BN / 32; c++) {
       const int col0 = n0 + c * 32;
-      if (col0 >= ep.N) break;
+      if (col0 >= ep.N || (ep.flags & 512)) break;     // 512: tuning aid, skip the epilogue
       uint32_t r[32], q[32];
       if (nkb > 0) {
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
         tmem_ld32(taddr, r);
         tmem_ld32(taddr + BN, q);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 32; j++) tile[lane * 33 + j] = __uint_as_float(r[j]) + __uint_as_float(q[j]);     // thread = row, conflict-free (stride 33)
-      } else {
-#pragma unroll
-        for (int j = 0; j < 32; j++) tile[lane * 33 + j] = 0.f;
       }
-      __syncwarp();
-      const int col = col0 + lane;
-      const float bv = (ep.bias && col < ep.N) ? ep.bias[col] : 0.f;
-      if (col < ep.N) {
-        for (int rr = 0; rr < 32; rr++) {
-          const int row = row_base + rr;
-          if (row >= ep.M) break;
-          float v = tile[rr * 33 + lane] + bv;
-          if (R) v += R[(long)row * ep.ldr + col];
-          if (ep.act == GN_ACT_RELU) v = v > 0.f ? v : 0.f;
-          C[(long)row * ep.ldc + col] = v;
+      if (vec) {
+        float4 rv[8], mv[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const bool in = col0 + 4 * j < ep.N;
+          rv[j] = (Rrow && in) ? *reinterpret_cast<const float4*>(Rrow + col0 + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+          mv[j] = (Mrow && in) ? *reinterpret_cast<const float4*>(Mrow + col0 + 4 * j) : make_float4(1.f, 1.f, 1.f, 1.f);
+        }
+        if (nkb > 0) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          if (!row_ok || col0 + 4 * j >= ep.N) continue;
+          float4 bv = ep.bias ? __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + 4 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          float4 v;
+          v.x = (nkb > 0 ? __uint_as_float(r[4 * j]) + __uint_as_float(q[4 * j]) : 0.f) + bv.x + rv[j].x;
+          v.y = (nkb > 0 ? __uint_as_float(r[4 * j + 1]) + __uint_as_float(q[4 * j + 1]) : 0.f) + bv.y + rv[j].y;
+          v.z = (nkb > 0 ? __uint_as_float(r[4 * j + 2]) + __uint_as_float(q[4 * j + 2]) : 0.f) + bv.z + rv[j].z;
+          v.w = (nkb > 0 ? __uint_as_float(r[4 * j + 3]) + __uint_as_float(q[4 * j + 3]) : 0.f) + bv.w + rv[j].w;
+          if (ep.act == GN_ACT_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+          if (!(mv[j].x > 0.f)) v.x = 0.f; if (!(mv[j].y > 0.f)) v.y = 0.f; if (!(mv[j].z > 0.f)) v.z = 0.f; if (!(mv[j].w > 0.f)) v.w = 0.f;
+          *reinterpret_cast<float4*>(Crow + col0 + 4 * j) = v;
+        }
+      } else {
+        if (nkb > 0) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+          const int col = col0 + j;
+          if (!row_ok || col >= ep.N) continue;
+          float v = nkb > 0 ? __uint_as_float(r[j]) + __uint_as_float(q[j]) : 0.f;
+          if (ep.bias) v += ep.bias[col];
+          if (Rrow) v += Rrow[col];
+          if (ep.act == GN_ACT_RELU) v = fmaxf(v, 0.f);
+          if (Mrow && !(Mrow[col] > 0.f)) v = 0.f;
+          Crow[col] = v;
         }
       }
-      __syncwarp();
     }
   }
   tc_fence_before();
@@ -269,19 +299,22 @@ inline void tc_init(Ctx* ctx) {
   ctx->tc_ok = false;
   void* fn = nullptr; cudaDriverEntryPointQueryResult q;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn || q != cudaDriverEntryPointSuccess) { cudaGetLastError(); return; }
-  if (cudaFuncSetAttribute(gemm_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256>::SMEM_BYTES) != cudaSuccess ||
-      cudaFuncSetAttribute(gemm_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128>::SMEM_BYTES) != cudaSuccess ||
-      cudaFuncSetAttribute(gemm_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64>::SMEM_BYTES) != cudaSuccess) { cudaGetLastError(); return; }
+  bool ok = true;
+  ok &= cudaFuncSetAttribute(gemm_tc_kernel<256, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256, 32>::SMEM_BYTES) == cudaSuccess;
+  ok &= cudaFuncSetAttribute(gemm_tc_kernel<128, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128, 32>::SMEM_BYTES) == cudaSuccess;
+  ok &= cudaFuncSetAttribute(gemm_tc_kernel<64, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64, 32>::SMEM_BYTES) == cudaSuccess;
+  ok &= cudaFuncSetAttribute(gemm_tc_kernel<256, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256, 16>::SMEM_BYTES) == cudaSuccess;
+  if (!ok) { cudaGetLastError(); return; }
   ctx->encode_tiled = fn; ctx->tc_ok = true;
 }
 
-inline int tc_make_map(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const float* base, int box_rows) {
+inline int tc_make_map(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const float* base, int box_rows, int bk = 32) {
   cuuint64_t dims[3] = {(cuuint64_t)p.K, (cuuint64_t)p.rows, (cuuint64_t)p.nbatch};
   cuuint64_t strides[2] = {(cuuint64_t)p.ldp * 4, (cuuint64_t)p.rows * p.ldp * 4};
-  cuuint32_t box[3] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t box[3] = {(cuuint32_t)bk, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = ((PFN_encodeTiled)ctx->encode_tiled)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                                                    bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(GN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows %d K %d ld %d batch %d)", (int)r, p.rows, p.K, p.ldp, p.nbatch);
   return GN_OK;
 }
@@ -297,21 +330,32 @@ inline int tc_split(Ctx* ctx, const TcSrc& src, const TcPlanes& p) {
   return check_launch("tc_split");
 }
 
-template <int BN>
+template <int BN, int BK = 32>
 inline int tc_launch_bn(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep) {
   CUtensorMap mAh, mAl, mBh, mBl;
-  GN_TRY(tc_make_map(ctx, &mAh, A, A.hi, TC_BM)); GN_TRY(tc_make_map(ctx, &mAl, A, A.lo, TC_BM));
-  GN_TRY(tc_make_map(ctx, &mBh, B, B.hi, BN)); GN_TRY(tc_make_map(ctx, &mBl, B, B.lo, BN));
+  GN_TRY(tc_make_map(ctx, &mAh, A, A.hi, TC_BM, BK)); GN_TRY(tc_make_map(ctx, &mAl, A, A.lo, TC_BM, BK));
+  GN_TRY(tc_make_map(ctx, &mBh, B, B.hi, BN, BK)); GN_TRY(tc_make_map(ctx, &mBl, B, B.lo, BN, BK));
   dim3 grid(cdiv(ep.N, BN), cdiv(ep.M, TC_BM), A.nbatch);
-  GN_LAUNCH(ctx, gemm_tc_kernel<BN>, grid, TC_THREADS, TcCfg<BN>::SMEM_BYTES, mAh, mAl, mBh, mBl, ep);
+  GN_LAUNCH(ctx, (gemm_tc_kernel<BN, BK>), grid, TC_THREADS, (TcCfg<BN, BK>::SMEM_BYTES), mAh, mAl, mBh, mBl, ep);
   return check_launch("gemm_tc");
 }
 // C[z] = A[z] * B[z]^T from prepared planes; the N tile follows the output width.
-inline int tc_launch(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep) {
+inline int tc_launch(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep_in) {
   if (!ctx->tc_ok) return fail(GN_ERR_UNSUPPORTED, "tcgen05 engine unavailable");
+  TcParams ep = ep_in;
   if (A.K != B.K || A.nbatch != B.nbatch || A.rows != ep.M || B.rows != ep.N || A.K != ep.K) return fail(GN_ERR_INVALID_ARG, "tc_launch: operand shapes disagree");
+  auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  bool vec = ep.N % 4 == 0 && ep.ldc % 4 == 0 && ep.c_b1 % 4 == 0 && ep.c_b2 % 4 == 0 && a16(ep.C) && (!ep.bias || a16(ep.bias));
+  if (ep.R) vec = vec && ep.ldr % 4 == 0 && ep.r_b1 % 4 == 0 && ep.r_b2 % 4 == 0 && a16(ep.R);
+  if (ep.mask) vec = vec && ep.mask_ld % 4 == 0 && a16(ep.mask);
+  if (vec) ep.flags |= TC_FLAG_VEC;
+  static const int force_bn = [] { const char* e = getenv("GONEURON_TC_BN"); return e ? atoi(e) : 0; }();   // tuning aids
+  static const int bk = [] { const char* e = getenv("GONEURON_TC_BK"); return e ? atoi(e) : 32; }();
+  if (force_bn == 128) return tc_launch_bn<128>(ctx, A, B, ep);
+  if (force_bn == 64) return tc_launch_bn<64>(ctx, A, B, ep);
   if (ep.N <= 64) return tc_launch_bn<64>(ctx, A, B, ep);
   if (ep.N <= 128) return tc_launch_bn<128>(ctx, A, B, ep);
+  if (bk == 16) return tc_launch_bn<256, 16>(ctx, A, B, ep);
   return tc_launch_bn<256>(ctx, A, B, ep);
 }
 
@@ -341,7 +385,8 @@ inline int gemm_tc(Ctx* ctx, const GemmDesc& g) {
   TcPlanes A{sc.a_hi.p, sc.a_lo.p, g.M, g.K, ldp, nb}, B{sc.b_hi.p, sc.b_lo.p, g.N, g.K, ldp, nb};
   GN_TRY(tc_split(ctx, TcSrc{g.A, g.sa_m, g.sa_k, g.a_b1, g.a_b2, g.batch2}, A));
   GN_TRY(tc_split(ctx, TcSrc{g.B, g.sb_n, g.sb_k, g.b_b1, g.b_b2, g.batch2}, B));
-  TcParams ep{g.C, g.ldc, g.c_b1, g.c_b2, g.bias, g.R, g.ldr, g.r_b1, g.r_b2, g.act, g.M, g.N, g.K, g.batch2, g.flags, ctx->d_status};
+  static const int noload = [] { const char* e = getenv("GONEURON_TC_NOLOAD"); return e ? atoi(e) * 256 : 0; }();
+  TcParams ep{g.C, g.ldc, g.c_b1, g.c_b2, g.bias, g.R, g.ldr, g.r_b1, g.r_b2, g.act, g.M, g.N, g.K, g.batch2, g.flags | noload, ctx->d_status, g.mask, g.mask_ld, g.mask_group};
   return tc_launch(ctx, A, B, ep);
 }
 

@@ -351,8 +351,12 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
   GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(N, 8), 256, 0, gout, l.r2.p, bp.g2, st + 2 * N, st + 3 * N, dR2, (long)N, D);
   // ff2 then ff1, token by token in the reference (transformer.go:1238-1250)
   GN_TRY(inner_dense_param_grads(m, dR2, B, T, D, l.mid.p, F, (float*)gp.w2, (float*)gp.b2));
-  GN_TRY(gemm_nn(ctx, N, D, F, dR2, D, bp.w2, dM, F));
-  { long n = (long)N * F; GN_LAUNCH(ctx, relu_mask_last_token_kernel, ew_grid(ctx, n), 256, 0, dM, l.mid.p, T, F, n); }
+  {
+    // dz1[s,t,:] = (W2^T dR2[s,t,:]) gated by the ReLU pattern of the LAST token of sequence s (fused into the epilogue)
+    GemmDesc g; g.M = N; g.N = F; g.K = D; g.A = dR2; g.sa_m = D; g.sa_k = 1; g.B = bp.w2; g.sb_k = F; g.sb_n = 1; g.C = dM; g.ldc = F;
+    g.mask = l.mid.p + (long)(T - 1) * F; g.mask_ld = (long)T * F; g.mask_group = T;
+    GN_TRY(gemm(ctx, g));
+  }
   GN_TRY(inner_dense_param_grads(m, dM, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1));
   GN_TRY(gemm_nn(ctx, N, F, D, dM, F, bp.w1, comb, D, dR2, D));                          // combined = gradRes2 + W1^T dz1
   // LayerNorm 1
