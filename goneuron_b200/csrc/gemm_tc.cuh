@@ -40,6 +40,7 @@ template <int BN, int BK> struct TcCfg {
   static constexpr int STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
   static constexpr int STAGES = (200 * 1024) / STAGE_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  static_assert(2 * STAGES + 5 <= 32, "barrier area");
   static constexpr int TMEM_COLS = 2 * BN;
 };
 
@@ -101,6 +102,70 @@ struct TcParams {
   int act, M, N, K, batch2, flags; int* status;
   const float* mask; long mask_ld; int mask_group;    // optional gate, see GemmDesc::mask
 };
+
+// Epilogue of one output tile, executed by one warp for its TMEM lane quadrant: one output row per thread
+// (TMEM lane = row), 32 consecutive columns per tcgen05.ld, written as 8 float4.  Bias, residual and gate values
+// of a chunk are fetched before the TMEM wait so that their latency overlaps.  `acc_main` / `acc_cross` are the
+// TMEM column offsets of the two accumulators of this tile.
+template <int BN>
+__device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tmem_base, uint32_t acc_main, uint32_t acc_cross,
+                                                 int m0, int n0, int z, int quad, int lane, int nkb) {
+    const int z1 = z / ep.batch2, z2 = z % ep.batch2;
+    float* C = ep.C + z1 * ep.c_b1 + z2 * ep.c_b2;
+    const float* R = ep.R ? ep.R + z1 * ep.r_b1 + z2 * ep.r_b2 : nullptr;
+    const int row = m0 + quad * 32 + lane;
+    const bool row_ok = row < ep.M;
+    const float* Rrow = (R && row_ok) ? R + (long)row * ep.ldr : nullptr;
+    const float* Mrow = (ep.mask && row_ok) ? ep.mask + (long)(row / ep.mask_group) * ep.mask_ld : nullptr;
+    float* Crow = C + (long)row * ep.ldc;
+    const bool vec = (ep.flags & TC_FLAG_VEC) != 0;
+    for (int c = 0; c < BN / 32; c++) {
+      const int col0 = n0 + c * 32;
+      if (col0 >= ep.N || (ep.flags & 512)) break;     // 512: tuning aid, skip the epilogue
+      uint32_t r[32], q[32];
+      if (nkb > 0) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
+        tmem_ld32(taddr + acc_main, r);
+        tmem_ld32(taddr + acc_cross, q);
+      }
+      if (vec) {
+        float4 rv[8], mv[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          const bool in = col0 + 4 * j < ep.N;
+          rv[j] = (Rrow && in) ? *reinterpret_cast<const float4*>(Rrow + col0 + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
+          mv[j] = (Mrow && in) ? *reinterpret_cast<const float4*>(Mrow + col0 + 4 * j) : make_float4(1.f, 1.f, 1.f, 1.f);
+        }
+        if (nkb > 0) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          if (!row_ok || col0 + 4 * j >= ep.N) continue;
+          float4 bv = ep.bias ? __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + 4 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          float4 v;
+          v.x = (nkb > 0 ? __uint_as_float(r[4 * j]) + __uint_as_float(q[4 * j]) : 0.f) + bv.x + rv[j].x;
+          v.y = (nkb > 0 ? __uint_as_float(r[4 * j + 1]) + __uint_as_float(q[4 * j + 1]) : 0.f) + bv.y + rv[j].y;
+          v.z = (nkb > 0 ? __uint_as_float(r[4 * j + 2]) + __uint_as_float(q[4 * j + 2]) : 0.f) + bv.z + rv[j].z;
+          v.w = (nkb > 0 ? __uint_as_float(r[4 * j + 3]) + __uint_as_float(q[4 * j + 3]) : 0.f) + bv.w + rv[j].w;
+          if (ep.act == GN_ACT_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+          if (!(mv[j].x > 0.f)) v.x = 0.f; if (!(mv[j].y > 0.f)) v.y = 0.f; if (!(mv[j].z > 0.f)) v.z = 0.f; if (!(mv[j].w > 0.f)) v.w = 0.f;
+          *reinterpret_cast<float4*>(Crow + col0 + 4 * j) = v;
+        }
+      } else {
+        if (nkb > 0) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+          const int col = col0 + j;
+          if (!row_ok || col >= ep.N) continue;
+          float v = nkb > 0 ? __uint_as_float(r[j]) + __uint_as_float(q[j]) : 0.f;
+          if (ep.bias) v += ep.bias[col];
+          if (Rrow) v += Rrow[col];
+          if (ep.act == GN_ACT_RELU) v = fmaxf(v, 0.f);
+          if (Mrow && !(Mrow[col] > 0.f)) v = 0.f;
+          Crow[col] = v;
+        }
+      }
+    }
+  }
 
 template <int BN, int BK>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -186,68 +251,133 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
     if (!ok && lane == 0) atomicExch(ep.status, 3);
     __syncwarp();
     tc_fence_after();
-    const int z1 = z / ep.batch2, z2 = z % ep.batch2;
-    float* C = ep.C + z1 * ep.c_b1 + z2 * ep.c_b2;
-    const float* R = ep.R ? ep.R + z1 * ep.r_b1 + z2 * ep.r_b2 : nullptr;
-    // One output row per thread (TMEM lane = row): 32 consecutive columns per tcgen05.ld, written as 8 float4.
-    // Bias, residual and gate values of a chunk are fetched before the TMEM wait so their latency overlaps.
-    const int row = m0 + quad * 32 + lane;
-    const bool row_ok = row < ep.M;
-    const float* Rrow = (R && row_ok) ? R + (long)row * ep.ldr : nullptr;
-    const float* Mrow = (ep.mask && row_ok) ? ep.mask + (long)(row / ep.mask_group) * ep.mask_ld : nullptr;
-    float* Crow = C + (long)row * ep.ldc;
-    const bool vec = (ep.flags & TC_FLAG_VEC) != 0;
-    for (int c = 0; c < BN / 32; c++) {
-      const int col0 = n0 + c * 32;
-      if (col0 >= ep.N || (ep.flags & 512)) break;     // 512: tuning aid, skip the epilogue
-      uint32_t r[32], q[32];
-      if (nkb > 0) {
-        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
-        tmem_ld32(taddr, r);
-        tmem_ld32(taddr + BN, q);
-      }
-      if (vec) {
-        float4 rv[8], mv[8];
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const bool in = col0 + 4 * j < ep.N;
-          rv[j] = (Rrow && in) ? *reinterpret_cast<const float4*>(Rrow + col0 + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
-          mv[j] = (Mrow && in) ? *reinterpret_cast<const float4*>(Mrow + col0 + 4 * j) : make_float4(1.f, 1.f, 1.f, 1.f);
-        }
-        if (nkb > 0) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-          if (!row_ok || col0 + 4 * j >= ep.N) continue;
-          float4 bv = ep.bias ? __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + 4 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
-          float4 v;
-          v.x = (nkb > 0 ? __uint_as_float(r[4 * j]) + __uint_as_float(q[4 * j]) : 0.f) + bv.x + rv[j].x;
-          v.y = (nkb > 0 ? __uint_as_float(r[4 * j + 1]) + __uint_as_float(q[4 * j + 1]) : 0.f) + bv.y + rv[j].y;
-          v.z = (nkb > 0 ? __uint_as_float(r[4 * j + 2]) + __uint_as_float(q[4 * j + 2]) : 0.f) + bv.z + rv[j].z;
-          v.w = (nkb > 0 ? __uint_as_float(r[4 * j + 3]) + __uint_as_float(q[4 * j + 3]) : 0.f) + bv.w + rv[j].w;
-          if (ep.act == GN_ACT_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
-          if (!(mv[j].x > 0.f)) v.x = 0.f; if (!(mv[j].y > 0.f)) v.y = 0.f; if (!(mv[j].z > 0.f)) v.z = 0.f; if (!(mv[j].w > 0.f)) v.w = 0.f;
-          *reinterpret_cast<float4*>(Crow + col0 + 4 * j) = v;
-        }
-      } else {
-        if (nkb > 0) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 32; j++) {
-          const int col = col0 + j;
-          if (!row_ok || col >= ep.N) continue;
-          float v = nkb > 0 ? __uint_as_float(r[j]) + __uint_as_float(q[j]) : 0.f;
-          if (ep.bias) v += ep.bias[col];
-          if (Rrow) v += Rrow[col];
-          if (ep.act == GN_ACT_RELU) v = fmaxf(v, 0.f);
-          if (Mrow && !(Mrow[col] > 0.f)) v = 0.f;
-          Crow[col] = v;
-        }
-      }
-    }
+    tc_epilogue_tile<BN>(ep, tmem_base, 0u, (uint32_t)BN, m0, n0, z, quad, lane, nkb);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::TMEM_COLS) : "memory");
+}
+
+// ------------------------------------------------------------------ persistent variant
+// One CTA per SM walks the output tiles (n fastest, so CTAs running together share A rows in L2).  TMEM holds two
+// accumulator slots of 2*BN columns (main + cross terms), so the epilogue warps drain tile i while the MMA warp already
+// accumulates tile i+1 and the TMA warp keeps the shared-memory ring full across tile boundaries:
+//   full[s]/empty[s]   TMA <-> MMA per shared-memory stage (running stage counter across tiles)
+//   tfull[b]/tempty[b] MMA <-> epilogue per TMEM slot
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+
+template <int BN, int BK>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
+                       const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo, TcParams ep,
+                       int tiles_m, int tiles_n, int total_tiles) {
+  using Cfg = TcCfg<BN, BK>;
+  static_assert(4 * BN <= 512, "two accumulator slots must fit the 512 TMEM columns");
+  constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, B_BYTES = Cfg::B_BYTES, A_BYTES = Cfg::A_BYTES;
+  constexpr uint32_t TMEM_COLS = 4 * BN;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);       // full[S], empty[S], tfull[2], tempty[2]
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+    for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // tile -> coordinates and contraction range (identical in every role)
+  auto decode = [&](int tile, int& m0, int& n0, int& z, int& kb0, int& nkb) -> bool {
+    const int nt = tile % tiles_n, q = tile / tiles_n, mt = q % tiles_m; z = q / tiles_m;
+    m0 = mt * TC_BM; n0 = nt * BN;
+    if ((ep.flags & GEMM_SKIP_UPPER) && n0 > m0 + TC_BM - 1) return false;
+    int kbeg = 0, kend = ep.K;
+    if (ep.flags & GEMM_KBEG_AT_M0) kbeg = (m0 / BK) * BK;
+    if (ep.flags & GEMM_KEND_AT_M0) kend = min(ep.K, m0 + TC_BM);
+    kb0 = kbeg / BK; nkb = (kend - kbeg + BK - 1) / BK;
+    return true;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true; uint32_t it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
+        for (int i = 0; i < nkb; i++, it++) {
+          const uint32_t s = it % STAGES, use = it / STAGES; const int kc = (kb0 + i) * BK;
+          if (use > 0) ok &= mbar_wait(empty0 + 8 * s, (use - 1) & 1);
+          const uint32_t base = smem_u32(smem + s * STAGE_BYTES), bar = full0 + 8 * s;
+          mbar_expect_tx(bar, STAGE_BYTES);
+          tma_load_3d(base, &mapAhi, kc, m0, z, bar);
+          tma_load_3d(base + A_BYTES, &mapAlo, kc, m0, z, bar);
+          tma_load_3d(base + 2 * A_BYTES, &mapBhi, kc, n0, z, bar);
+          tma_load_3d(base + 2 * A_BYTES + B_BYTES, &mapBlo, kc, n0, z, bar);
+        }
+      }
+      if (!ok) atomicExch(ep.status, 1);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true; uint32_t it = 0, lt = 0;
+      constexpr uint32_t idesc = make_idesc(TC_BM, BN);
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
+        const uint32_t slot = lt & 1, u = lt >> 1; lt++;
+        ok &= mbar_wait(tempty0 + 8 * slot, (u & 1) ^ 1);          // slot drained by the epilogue (passes at once the first time)
+        tc_fence_after();
+        const uint32_t acc_main = tmem_base + slot * 2 * BN, acc_cross = acc_main + BN;
+        for (int i = 0; i < nkb; i++, it++) {
+          const uint32_t s = it % STAGES, use = it / STAGES;
+          ok &= mbar_wait(full0 + 8 * s, use & 1);
+          tc_fence_after();
+          const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t ahi = make_desc<BK>(base), alo = make_desc<BK>(base + A_BYTES);
+          const uint64_t bhi = make_desc<BK>(base + 2 * A_BYTES), blo = make_desc<BK>(base + 2 * A_BYTES + B_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / 8; k++) {
+            const uint64_t adv = (uint64_t)((k * 8 * 4) >> 4);
+            const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+            tc_mma_tf32(acc_cross, alo + adv, bhi + adv, idesc, acc);
+            tc_mma_tf32(acc_cross, ahi + adv, blo + adv, idesc, 1u);
+            tc_mma_tf32(acc_main, ahi + adv, bhi + adv, idesc, acc);
+          }
+          tc_commit(empty0 + 8 * s);
+        }
+        tc_commit(tfull0 + 8 * slot);
+      }
+      if (!ok) atomicExch(ep.status, 2);
+    }
+  } else {
+    const int quad = warp & 3; uint32_t lt = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
+      const uint32_t slot = lt & 1, u = lt >> 1; lt++;
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait(tfull0 + 8 * slot, u & 1);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok && lane == 0) atomicExch(ep.status, 3);
+      tc_fence_after();
+      tc_epilogue_tile<BN>(ep, tmem_base, slot * 2 * BN, slot * 2 * BN + BN, m0, n0, z, quad, lane, nkb);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty0 + 8 * slot);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
 }
 
 // ------------------------------------------------------------------ operand split (memory-bound)
@@ -304,6 +434,8 @@ inline void tc_init(Ctx* ctx) {
   ok &= cudaFuncSetAttribute(gemm_tc_kernel<128, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128, 32>::SMEM_BYTES) == cudaSuccess;
   ok &= cudaFuncSetAttribute(gemm_tc_kernel<64, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64, 32>::SMEM_BYTES) == cudaSuccess;
   ok &= cudaFuncSetAttribute(gemm_tc_kernel<256, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256, 16>::SMEM_BYTES) == cudaSuccess;
+  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<128, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128, 32>::SMEM_BYTES) == cudaSuccess;
+  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<64, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64, 32>::SMEM_BYTES) == cudaSuccess;
   if (!ok) { cudaGetLastError(); return; }
   ctx->encode_tiled = fn; ctx->tc_ok = true;
 }
@@ -339,6 +471,17 @@ inline int tc_launch_bn(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const Tc
   GN_LAUNCH(ctx, (gemm_tc_kernel<BN, BK>), grid, TC_THREADS, (TcCfg<BN, BK>::SMEM_BYTES), mAh, mAl, mBh, mBl, ep);
   return check_launch("gemm_tc");
 }
+template <int BN, int BK = 32>
+inline int tc_launch_persist(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep) {
+  CUtensorMap mAh, mAl, mBh, mBl;
+  GN_TRY(tc_make_map(ctx, &mAh, A, A.hi, TC_BM, BK)); GN_TRY(tc_make_map(ctx, &mAl, A, A.lo, TC_BM, BK));
+  GN_TRY(tc_make_map(ctx, &mBh, B, B.hi, BN, BK)); GN_TRY(tc_make_map(ctx, &mBl, B, B.lo, BN, BK));
+  const int tiles_m = cdiv(ep.M, TC_BM), tiles_n = cdiv(ep.N, BN); const long total = (long)tiles_m * tiles_n * A.nbatch;
+  if (total > 0x7fffffffL) return fail(GN_ERR_UNSUPPORTED, "too many output tiles");
+  const unsigned grid = (unsigned)std::min<long>(total, ctx->sm_count);
+  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN, BK>), grid, TC_THREADS, (TcCfg<BN, BK>::SMEM_BYTES), mAh, mAl, mBh, mBl, ep, tiles_m, tiles_n, (int)total);
+  return check_launch("gemm_tc_persist");
+}
 // C[z] = A[z] * B[z]^T from prepared planes; the N tile follows the output width.
 inline int tc_launch(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep_in) {
   if (!ctx->tc_ok) return fail(GN_ERR_UNSUPPORTED, "tcgen05 engine unavailable");
@@ -351,6 +494,8 @@ inline int tc_launch(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcPar
   if (vec) ep.flags |= TC_FLAG_VEC;
   static const int force_bn = [] { const char* e = getenv("GONEURON_TC_BN"); return e ? atoi(e) : 0; }();   // tuning aids
   static const int bk = [] { const char* e = getenv("GONEURON_TC_BK"); return e ? atoi(e) : 32; }();
+  static const int persist = [] { const char* e = getenv("GONEURON_TC_PERSIST"); return e ? atoi(e) : 1; }();
+  if (persist && !force_bn) return ep.N <= 64 ? tc_launch_persist<64>(ctx, A, B, ep) : tc_launch_persist<128>(ctx, A, B, ep);
   if (force_bn == 128) return tc_launch_bn<128>(ctx, A, B, ep);
   if (force_bn == 64) return tc_launch_bn<64>(ctx, A, B, ep);
   if (ep.N <= 64) return tc_launch_bn<64>(ctx, A, B, ep);
