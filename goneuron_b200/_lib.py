@@ -16,7 +16,7 @@ EXPORTS = [
     "gn_model_set_params", "gn_model_get_params", "gn_model_get_grads", "gn_adam_set", "gn_adam_get_state",
     "gn_adam_set_state", "gn_train_batch", "gn_train_batch_device", "gn_forward_batch", "gn_device_alloc",
     "gn_device_free", "gn_device_upload", "gn_device_download", "gn_model_last_stats", "gn_model_set_profiling",
-    "gn_op_gemm_nt", "gn_op_adam", "gn_op_gemm_nt_static",
+    "gn_op_gemm_nt", "gn_op_adam", "gn_op_gemm_nt_static", "gn_model_state_count", "gn_model_get_state", "gn_model_set_state",
 ]
 
 
@@ -73,6 +73,9 @@ def load():
     L.gn_model_set_profiling.argtypes = [vp, C.c_int]
     L.gn_op_gemm_nt.argtypes = [vp, C.c_int, C.c_int, C.c_int, C.c_int, f32p, f32p, f32p, f32p]
     L.gn_op_adam.argtypes = [vp, f32p, f32p, f32p, f32p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int, C.c_float]
+    L.gn_model_state_count.argtypes = [vp, i64p]
+    L.gn_model_get_state.argtypes = [vp, f32p, C.c_int64]
+    L.gn_model_set_state.argtypes = [vp, f32p, C.c_int64]
     L.gn_op_gemm_nt_static.argtypes = [vp, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp]
     _lib = L
     return L

@@ -23,6 +23,13 @@ def cnn(hw=32, c0=3, c1=16, c2=32, classes=10):
             D.Flatten(), D.Dense(c2 * h4 * h4, classes, D.SOFTMAX)], D.CROSS_ENTROPY
 
 
+def cnn_bn(hw=16, c0=3, c1=8, classes=5):
+    """Conv -> BatchNorm2D -> MaxPool -> Flatten -> Dense: exercises BatchNorm2D (used by the reference's CIFAR example)."""
+    h2 = hw // 2
+    return [D.Conv2D(c0, c1, 3, 1, 1, D.RELU, hw, hw), D.BatchNorm2D(c1, hw, hw), D.MaxPool2D(c1, 2, 2, 0, hw, hw),
+            D.Flatten(), D.Dense(c1 * h2 * h2, classes, D.SOFTMAX)], D.CROSS_ENTROPY
+
+
 def recurrent(in_size=16, hidden=128, seq_len=64):
     return [D.SequenceUnrollerLSTM(in_size, hidden, seq_len, False), D.Dense(hidden, 1, D.LINEAR)], D.MSE
 
@@ -38,11 +45,12 @@ CONFIGS = {
     # name: (builder, kwargs, batch, lr)
     "mlp": (mlp, {}, 64, 1e-3),
     "cnn": (cnn, {}, 128, 1e-3),
+    "cnn_bn": (cnn_bn, {}, 32, 1e-3),
     "lstm": (recurrent, {}, 256, 1e-3),
     "transformer_small": (transformer, dict(vocab=8192, dim=256, seq_len=128, heads=8, ff_dim=1024, n_blocks=4), 64, 3e-4),
     "transformer_large": (transformer, dict(vocab=32000, dim=1024, seq_len=512, heads=16, ff_dim=4096, n_blocks=8), 256, 1e-4),
 }
-SEEDS = {"mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
+SEEDS = {"cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
 
 
 def build(name, **override):
@@ -95,6 +103,8 @@ def init_params(layers, rng):
             parts += _dense_params(rng, f, d)
         elif k == D.LAYERNORM:
             parts += [np.ones(l.dim, np.float32), np.zeros(l.dim, np.float32)]
+        elif k == D.BATCHNORM2D:
+            parts += [rng.uniform(0.5, 1.5, size=l.in_size).astype(np.float32), rng.uniform(-0.5, 0.5, size=l.in_size).astype(np.float32)]
     return np.concatenate(parts) if parts else np.zeros(0, np.float32)
 
 

@@ -79,6 +79,8 @@ struct LayerRT {
   DevBuf pre_i, c_all, h_all, dgate;   // LSTM
   DevBuf idx;                          // int32 payload: MaxPool argmax / embedding token ids
   const float* fin = nullptr;          // input of the last forward call (device pointer, not owned)
+  int64_t s_off = 0, s_cnt = 0;        // BatchNorm2D: slice of the model's state buffer (running mean | running variance)
+  float bn_eps = 1e-5f, bn_mom = 0.1f;
 };
 
 }  // namespace gn
@@ -91,7 +93,7 @@ struct gn_model {
   std::vector<gn::LayerRT> L;
   int loss_kind = 0, W = 1;
   int64_t P = 0; int in_size = 0, out_size = 0;
-  gn::DevBuf params, grads, m1, v2;
+  gn::DevBuf params, grads, m1, v2, state; int64_t NS = 0;
   float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f; int timestep = 0;
   int cap = 0;                          // batch capacity of the activation buffers
   gn::DevBuf xin, yin, lossg, loss_s, loss_sum;
@@ -154,6 +156,10 @@ static int plan_layers(gn_model* m, const gn_layer_desc* layers, int n) {
       case GN_LAYER_CLS_POOLING:
         if (d.seq_len <= 0 || d.dim <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad CLSPooling descriptor", i);
         l.in_size = d.seq_len * d.dim; l.out_size = d.dim; break;
+      case GN_LAYER_BATCHNORM2D:
+        if (d.in_size <= 0 || d.in_h <= 0 || d.in_w <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad BatchNorm2D descriptor", i);
+        l.in_size = l.out_size = d.in_size * d.in_h * d.in_w; l.p_cnt = 2 * (int64_t)d.in_size; l.s_off = m->NS; l.s_cnt = 2 * (int64_t)d.in_size; m->NS += l.s_cnt;
+        if (d.reserved) memcpy(&l.bn_eps, &d.reserved, 4); if (d.dim) memcpy(&l.bn_mom, &d.dim, 4); break;
       case GN_LAYER_LAYERNORM:
         if (cur < 0 || d.dim <= 0 || cur % d.dim) return fail(GN_ERR_INVALID_ARG, "layer %d: LayerNorm width must divide the input size", i);
         l.in_size = l.out_size = cur; l.p_cnt = 2 * (int64_t)d.dim; break;
@@ -195,6 +201,7 @@ static int alloc_activations(gn_model* m, int cap) {
         GN_TRY(l.att_m.alloc(nt * d.heads)); GN_TRY(l.att_l.alloc(nt * d.heads)); GN_TRY(l.att_d.alloc(nt * d.heads)); break; }
       case GN_LAYER_CLS_POOLING: GN_TRY(l.out.alloc(c * l.out_size)); break;
       case GN_LAYER_LAYERNORM: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.stat.alloc(2 * c * (l.in_size / d.dim))); break;
+      case GN_LAYER_BATCHNORM2D: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.stat.alloc(3 * c * d.in_size)); break;
     }
   }
   m->cap = cap; return GN_OK;
@@ -244,7 +251,7 @@ static BlockParams block_params(const float* p, int D, int F) {
   b.w1 = p; b.b1 = p + (long)D * F; p += (long)D * F + F; b.w2 = p; b.b2 = p + (long)F * D; return b;
 }
 
-static int forward(gn_model* m, const float* x, int B, const float** y_out) {
+static int forward(gn_model* m, const float* x, int B, const float** y_out, bool training) {
   Ctx* ctx = &m->ctx->c;
   const float* cur = x;
   for (size_t li = 0; li < m->L.size(); li++) {
@@ -315,6 +322,16 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out) {
         cur = l.out.p; break; }
       case GN_LAYER_CLS_POOLING:
         GN_LAUNCH(ctx, cls_fwd_kernel, B, 128, 0, cur, l.out.p, d.seq_len, d.dim); cur = l.out.p; break;
+      case GN_LAYER_BATCHNORM2D: {
+        const int C = d.in_size, S = d.in_h * d.in_w; const long BC = (long)B * C; float* run = m->state.p + l.s_off;
+        if (training) {
+          if (ctx->world > 1) return fail(GN_ERR_UNSUPPORTED, "BatchNorm2D running statistics are single-GPU in this build");
+          GN_LAUNCH(ctx, bn_fwd_kernel, (unsigned)BC, 256, 0, cur, p, p + C, l.out.p, l.stat.p, C, S, BC, l.bn_eps);
+          GN_LAUNCH(ctx, bn_running_kernel, cdiv(C, 128), 128, 0, l.stat.p, run, B, C, BC, l.bn_mom);
+        } else {
+          long n = BC * S; GN_LAUNCH(ctx, bn_eval_kernel, ew_grid(ctx, n), 256, 0, cur, p, p + C, run, l.out.p, C, S, n, l.bn_eps);
+        }
+        cur = l.out.p; break; }
       case GN_LAYER_LAYERNORM: {
         long rows = (long)B * (l.in_size / d.dim);
         GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(rows, 8), 256, 0, cur, p, p + d.dim, l.out.p, l.stat.p, l.stat.p + rows, rows, d.dim, 1e-5f);
@@ -474,6 +491,12 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
       case GN_LAYER_CLS_POOLING: {
         long n = (long)B * l.in_size;
         GN_LAUNCH(ctx, cls_bwd_kernel, ew_grid(ctx, n), 256, 0, g, dx, d.seq_len, d.dim, n); g = dx; flip ^= 1; break; }
+      case GN_LAYER_BATCHNORM2D: {
+        const int C = d.in_size, S = d.in_h * d.in_w; const long BC = (long)B * C;
+        float* pg; GN_TRY(ensure(m, S_DELTA, (size_t)B * 2 * C, &pg));
+        GN_LAUNCH(ctx, bn_bwd_kernel, (unsigned)BC, 256, 0, g, xin, p, l.stat.p, dx, pg, C, S, BC);
+        GN_TRY(colsum(m, pg, 2 * C, B, 2 * C, gr, false));
+        g = dx; flip ^= 1; break; }
       case GN_LAYER_LAYERNORM: {
         long rows = (long)B * (l.in_size / d.dim); int chunks = (int)std::max<long>(1, std::min<long>(rows / 64, 128));
         float* part; GN_TRY(ensure(m, S_PART2, (size_t)chunks * 2 * d.dim, &part));
@@ -508,7 +531,7 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
   GN_CUDA(cudaEventRecord(m->ev0, ctx->stream));
   GN_CUDA(cudaMemsetAsync(m->grads.p, 0, (size_t)m->P * sizeof(float), ctx->stream));     // Network.ClearGradients, net.go:813-823
   const float* yp;
-  GN_TRY(forward(m, x_dev, B, &yp));
+  GN_TRY(forward(m, x_dev, B, &yp, true));
   GN_LAUNCH(ctx, loss_rows_kernel, B, 256, 0, yp, y_dev, m->lossg.p, m->loss_s.p, m->out_size, m->loss_kind);
   GN_LAUNCH(ctx, loss_total_kernel, 1, 32, 0, m->loss_s.p, B, m->loss_sum.p);
   GN_TRY(backward(m, x_dev, B, m->lossg.p, global_batch, first_sample));
@@ -637,6 +660,12 @@ int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int 
   size_t P = (size_t)std::max<int64_t>(m->P, 4);
   GN_TRY(m->params.alloc(P)); GN_TRY(m->grads.alloc(P)); GN_TRY(m->m1.alloc(P)); GN_TRY(m->v2.alloc(P));
   GN_CUDA(cudaMemset(m->params.p, 0, P * 4)); GN_CUDA(cudaMemset(m->grads.p, 0, P * 4)); GN_CUDA(cudaMemset(m->m1.p, 0, P * 4)); GN_CUDA(cudaMemset(m->v2.p, 0, P * 4));
+  if (m->NS > 0) {
+    GN_TRY(m->state.alloc((size_t)m->NS));
+    std::vector<float> init((size_t)m->NS, 0.f);     // running mean 0, running variance 1 (batchnorm2d.go:124-128)
+    for (auto& l : m->L) if (l.d.kind == GN_LAYER_BATCHNORM2D) for (int64_t k = l.s_cnt / 2; k < l.s_cnt; k++) init[l.s_off + k] = 1.f;
+    GN_CUDA(cudaMemcpy(m->state.p, init.data(), (size_t)m->NS * 4, cudaMemcpyHostToDevice));
+  }
   GN_CUDA(cudaEventCreate(&m->ev0)); GN_CUDA(cudaEventCreate(&m->ev1)); GN_CUDA(cudaEventCreate(&m->ar0)); GN_CUDA(cudaEventCreate(&m->ar1));
   m->scratch.resize(S_COUNT);
   *out = m.release(); return GN_OK;
@@ -647,7 +676,7 @@ int gn_model_destroy(gn_model* m) {
   std::lock_guard<std::mutex> lk(m->mu);
   cudaSetDevice(m->ctx->c.device);
   if (m->ctx->alive && m->ctx->c.stream) cudaStreamSynchronize(m->ctx->c.stream);
-  m->L.clear(); m->scratch.clear(); m->params.release(); m->grads.release(); m->m1.release(); m->v2.release();
+  m->L.clear(); m->scratch.clear(); m->state.release(); m->params.release(); m->grads.release(); m->m1.release(); m->v2.release();
   m->xin.release(); m->yin.release(); m->lossg.release(); m->loss_s.release(); m->loss_sum.release();
   if (m->ev0) cudaEventDestroy(m->ev0); if (m->ev1) cudaEventDestroy(m->ev1); if (m->ar0) cudaEventDestroy(m->ar0); if (m->ar1) cudaEventDestroy(m->ar1);
   m->ev0 = m->ev1 = m->ar0 = m->ar1 = nullptr; m->alive = false; return GN_OK;
@@ -679,6 +708,20 @@ int gn_model_get_grads(gn_model* m, float* host, int64_t n) {
   const float inv = m->last_inv_batch;
   for (int64_t i = 0; i < n; i++) host[i] *= inv;
   return GN_OK;
+}
+
+int gn_model_state_count(gn_model* m, int64_t* n) { CHECK_MODEL(m); if (!n) return fail(GN_ERR_INVALID_ARG, "n is null"); *n = m->NS; return GN_OK; }
+int gn_model_get_state(gn_model* m, float* host, int64_t n) {
+  CHECK_MODEL(m); if (n != m->NS || (n > 0 && !host)) return fail(GN_ERR_INVALID_ARG, "get_state: expected %lld floats, got %lld", (long long)m->NS, (long long)n);
+  if (n == 0) return GN_OK;
+  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); GN_CUDA(cudaMemcpy(host, m->state.p, (size_t)n * 4, cudaMemcpyDeviceToHost)); return GN_OK;
+}
+int gn_model_set_state(gn_model* m, const float* host, int64_t n) {
+  CHECK_MODEL(m); if (n != m->NS || (n > 0 && !host)) return fail(GN_ERR_INVALID_ARG, "set_state: expected %lld floats, got %lld", (long long)m->NS, (long long)n);
+  if (n == 0) return GN_OK;
+  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); GN_CUDA(cudaMemcpy(m->state.p, host, (size_t)n * 4, cudaMemcpyHostToDevice)); return GN_OK;
 }
 
 int gn_adam_set(gn_model* m, float lr, float beta1, float beta2, float eps, int timestep) {
@@ -723,7 +766,7 @@ int gn_forward_batch(gn_model* m, const float* x, int batch, float* out) {
   if (batch > m->cap) GN_TRY(alloc_activations(m, batch));
   cudaStream_t s = m->ctx->c.stream;
   GN_CUDA(cudaMemcpyAsync(m->xin.p, x, (size_t)batch * m->in_size * 4, cudaMemcpyHostToDevice, s));
-  const float* yp; GN_TRY(forward(m, m->xin.p, batch, &yp));
+  const float* yp; GN_TRY(forward(m, m->xin.p, batch, &yp, false));
   GN_CUDA(cudaMemcpyAsync(out, yp, (size_t)batch * m->out_size * 4, cudaMemcpyDeviceToHost, s));
   GN_CUDA(cudaStreamSynchronize(s)); return GN_OK;
 }

@@ -272,4 +272,56 @@ __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, 
   for (long i = (n4 << 2) + blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) upd(p[i], g[i], m[i], v[i]);
 }
 
+
+// ---------------------------------------------------------------- BatchNorm2D (NCHW)
+// The reference normalises ONE sample at a time, so the statistics of a (sample, channel) pair are taken over that
+// sample's S = H*W positions (batchnorm2d.go:336-377).  One block per (sample, channel).
+// stat layout: [B*C] mean | [B*C] std | [B*C] variance.
+__global__ void bn_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta, float* __restrict__ y,
+                              float* __restrict__ stat, int C, int S, long BC, float eps) {
+  __shared__ float red[33];
+  const long bc = blockIdx.x; const int c = (int)(bc % C);
+  const float* xp = x + bc * S; float* yp = y + bc * S;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < S; i += blockDim.x) s += xp[i];
+  const float mean = block_sum(s, red) * (1.f / (float)S);
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < S; i += blockDim.x) { float d = xp[i] - mean; ss += d * d; }
+  const float var = block_sum(ss, red) * (1.f / (float)S);
+  const float sd = sqrtf(var + eps), istd = 1.f / sd, g = gamma[c], b = beta[c];
+  for (int i = threadIdx.x; i < S; i += blockDim.x) yp[i] = g * ((xp[i] - mean) * istd) + b;
+  if (threadIdx.x == 0) { stat[bc] = mean; stat[BC + bc] = sd; stat[2 * BC + bc] = var; }
+}
+// running = (1 - momentum) * running + momentum * statistic, once per sample in batch order (batchnorm2d.go:352, :376)
+__global__ void bn_running_kernel(const float* __restrict__ stat, float* __restrict__ run, int B, int C, long BC, float mom) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= C) return;
+  float rm = run[c], rv = run[C + c];
+  for (int b = 0; b < B; b++) { rm = (1.f - mom) * rm + mom * stat[(long)b * C + c]; rv = (1.f - mom) * rv + mom * stat[2 * BC + (long)b * C + c]; }
+  run[c] = rm; run[C + c] = rv;
+}
+// inference mode: running statistics (batchnorm2d.go:492-509)
+__global__ void bn_eval_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta, const float* __restrict__ run,
+                               float* __restrict__ y, int C, int S, long total, float eps) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int c = (int)((i / S) % C);
+    y[i] = gamma[c] * ((x[i] - run[c]) / sqrtf(run[C + c] + eps)) + beta[c];
+  }
+}
+// reference: batchnorm2d.go:626-660, m = S.  pg: per (sample, channel) contributions [B, 2C] = gGamma | gBeta, summed over samples afterwards.
+__global__ void bn_bwd_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ stat,
+                              float* __restrict__ dx, float* __restrict__ pg, int C, int S, long BC) {
+  __shared__ float red[33];
+  const long bc = blockIdx.x; const int c = (int)(bc % C); const long b = bc / C;
+  const float* xp = x + bc * S; const float* gp = g + bc * S; float* dp = dx + bc * S;
+  const float mean = stat[bc], sd = stat[BC + bc], gm = gamma[c], m = (float)S;
+  float sg = 0.f, sgx = 0.f;
+  for (int i = threadIdx.x; i < S; i += blockDim.x) { float gg = gp[i]; sg += gg; sgx += gg * (xp[i] - mean); }
+  sg = block_sum(sg, red); sgx = block_sum(sgx, red);
+  for (int i = threadIdx.x; i < S; i += blockDim.x) {
+    float d = xp[i] - mean, gi = gp[i] * gm;
+    dp[i] = gi / sd - (sg * gm) / m / sd - d * (sgx * gm) / m / (sd * sd * sd);
+  }
+  if (threadIdx.x == 0) { pg[b * 2 * C + c] = sgx / sd; pg[b * 2 * C + C + c] = sg; }     // sum g*(x-mean)/std ; sum g
+}
+
 }  // namespace gn

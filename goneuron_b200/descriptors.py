@@ -3,7 +3,7 @@ constructors named after the reference's (goneuron/goneuron.go:59-340, internal/
 import ctypes as C
 
 # gn_layer_kind
-DENSE, CONV2D, MAXPOOL2D, FLATTEN, LSTM_UNROLLED, EMBEDDING, POSENC, TRANSFORMER_BLOCK, CLS_POOLING, LAYERNORM = range(1, 11)
+DENSE, CONV2D, MAXPOOL2D, FLATTEN, LSTM_UNROLLED, EMBEDDING, POSENC, TRANSFORMER_BLOCK, CLS_POOLING, LAYERNORM, BATCHNORM2D = range(1, 12)
 # gn_activation
 LINEAR, RELU, SIGMOID, TANH, SOFTMAX, LOGSOFTMAX = range(6)
 # gn_loss_kind
@@ -75,3 +75,13 @@ def CLSPooling(seq_len, dim):
 def LayerNorm(dim):
     """layer.NewLayerNorm(dim, 1e-5, true) applied to consecutive rows of `dim` -- layernorm.go:193-441."""
     return LayerDesc(kind=LAYERNORM, dim=dim)
+
+
+def _float_bits(v):
+    import struct
+    return struct.unpack("<i", struct.pack("<f", v))[0]
+
+
+def BatchNorm2D(num_features, in_h, in_w, eps=1e-5, momentum=0.1):
+    """layer.NewBatchNorm2D(C, eps, momentum, affine=true) + SetInputDimensions(h, w) -- batchnorm2d.go:67-160."""
+    return LayerDesc(kind=BATCHNORM2D, in_size=num_features, in_h=in_h, in_w=in_w, dim=_float_bits(momentum), reserved=_float_bits(eps))

@@ -123,6 +123,19 @@ class Sequential:
         m, v = _f32(m), _f32(v)
         _lib.check(_lib.load().gn_adam_set_state(self.handle, _p(m), _p(v), m.size, timestep))
 
+    def State(self):
+        """Non-parameter layer state (BatchNorm2D running mean | running variance per layer, in layer order)."""
+        n = C.c_int64()
+        _lib.check(_lib.load().gn_model_state_count(self.handle, C.byref(n)))
+        a = np.empty(n.value, np.float32)
+        if n.value:
+            _lib.check(_lib.load().gn_model_get_state(self.handle, _p(a), a.size))
+        return a
+
+    def SetState(self, state):
+        a = _f32(state)
+        _lib.check(_lib.load().gn_model_set_state(self.handle, _p(a), a.size))
+
     # -- training ---------------------------------------------------------------
     def _push_opt(self):
         o = self.opt   # re-read every step: schedulers mutate LearningRate on the host (opt/scheduler.go)

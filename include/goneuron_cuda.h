@@ -51,7 +51,8 @@ typedef enum gn_layer_kind {
   GN_LAYER_POSENC = 7,         /* layer.NewPositionalEncoding(T,dim)    internal/layer/transformer.go:12-84 */
   GN_LAYER_TRANSFORMER_BLOCK = 8, /* NewTransformerBlock(dim,heads,T,ff,causal) transformer.go:859-1279 */
   GN_LAYER_CLS_POOLING = 9,    /* layer.NewCLSPooling(T,dim)            internal/layer/transformer.go:1647-1777 */
-  GN_LAYER_LAYERNORM = 10      /* layer.NewLayerNorm(dim,eps,true) applied row-wise  layernorm.go:193-441 */
+  GN_LAYER_LAYERNORM = 10,     /* layer.NewLayerNorm(dim,eps,true) applied row-wise  layernorm.go:193-441 */
+  GN_LAYER_BATCHNORM2D = 11    /* layer.NewBatchNorm2D(C,eps,momentum,true) + SetInputDimensions  batchnorm2d.go:67-665 */
 } gn_layer_kind;
 
 /* Activations (reference: internal/activations/activations.go:22-236,342-352). */
@@ -79,12 +80,12 @@ typedef struct gn_layer_desc {
   int32_t in_h;        /* Conv2D / MaxPool2D input height (SetInputDimensions, conv2d.go:686-691) */
   int32_t in_w;
   int32_t seq_len;     /* unroller time steps; PosEnc / TransformerBlock / CLSPooling sequence length */
-  int32_t dim;         /* PosEnc / TransformerBlock / CLSPooling / LayerNorm model width */
+  int32_t dim;         /* PosEnc / TransformerBlock / CLSPooling / LayerNorm model width; BatchNorm2D: momentum as float bits (0 = 0.1) */
   int32_t heads;       /* TransformerBlock */
   int32_t ff_dim;      /* TransformerBlock */
   int32_t causal;      /* TransformerBlock */
   int32_t return_seq;  /* unroller: 0 = last hidden state only */
-  int32_t reserved;
+  int32_t reserved;    /* BatchNorm2D: eps as float bits (0 = 1e-5) */
 } gn_layer_desc;
 
 typedef struct gn_ctx gn_ctx;
@@ -169,6 +170,13 @@ int gn_device_alloc(gn_ctx* ctx, int64_t n_floats, float** dev);
 int gn_device_free(gn_ctx* ctx, float* dev);
 int gn_device_upload(gn_ctx* ctx, float* dev, const float* host, int64_t n_floats);
 int gn_device_download(gn_ctx* ctx, float* host, const float* dev, int64_t n_floats);
+
+/* Layer state that is not a parameter: BatchNorm2D running mean and variance (runningMean[C] | runningVar[C] per
+ * BatchNorm2D layer, in layer order; batchnorm2d.go:124-128, GetRunningMean/GetRunningVar :837-838).  Updated by
+ * gn_train_batch sample by sample in batch order, used by gn_forward_batch (inference mode, :472-509). */
+int gn_model_state_count(gn_model* m, int64_t* n);
+int gn_model_get_state(gn_model* m, float* host, int64_t n);
+int gn_model_set_state(gn_model* m, const float* host, int64_t n);
 
 /* Counters of the last gn_train_batch: kernels launched by this library, and
  * device time in ms of the whole step / of the gradient all-reduce (CUDA events

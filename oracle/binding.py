@@ -35,8 +35,9 @@ def lib():
         L.gno_param_count.argtypes = [C.c_void_p, C.c_int, i64p, i64p, i64p]
         L.gno_train_batch.argtypes = [C.c_void_p, C.c_int, C.c_int, f32p, f32p, f32p, f32p, C.POINTER(C.c_int),
                                       C.c_float, C.c_float, C.c_float, C.c_float, f32p, f32p, C.c_int, C.c_int,
-                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.POINTER(C.c_double)]
-        L.gno_forward_batch.argtypes = [C.c_void_p, C.c_int, f32p, f32p, C.c_int, f32p, C.c_int, C.c_int]
+                                      C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, f32p, C.POINTER(C.c_double), f32p]
+        L.gno_forward_batch.argtypes = [C.c_void_p, C.c_int, f32p, f32p, C.c_int, f32p, C.c_int, C.c_int, f32p, C.c_int]
+        L.gno_state_count.argtypes = [C.c_void_p, C.c_int, i64p]
         L.gno_activation.argtypes = [C.c_int, f32p, C.c_int]
         L.gno_activation_deriv.argtypes = [C.c_int, f32p, C.c_int]
         L.gno_loss.argtypes = [C.c_int, f32p, f32p, C.c_int]
@@ -75,6 +76,15 @@ class OracleState:
         self.m = np.zeros_like(self.params)
         self.v = np.zeros_like(self.params)
         self.grads = np.zeros_like(self.params)
+        n = C.c_int64()
+        lib().gno_state_count(layers_to_array(self.layers), len(self.layers), C.byref(n))
+        # BatchNorm2D running statistics: mean 0 | variance 1 per layer (batchnorm2d.go:124-128)
+        self.state = np.zeros(n.value, np.float32)
+        off = 0
+        for l in self.layers:
+            if l.kind == 11:
+                self.state[off + l.in_size:off + 2 * l.in_size] = 1.0
+                off += 2 * l.in_size
         self.timestep = 0
         self.lr, self.beta1, self.beta2, self.eps = lr, beta1, beta2, eps
         self.seconds = 0.0
@@ -88,19 +98,19 @@ class OracleState:
         sec = C.c_double()
         rc = lib().gno_train_batch(arr, len(self.layers), self.loss_kind, _p(self.params), _p(self.grads), _p(self.m),
                                    _p(self.v), C.byref(ts), self.lr, self.beta1, self.beta2, self.eps, _p(x), _p(y), batch,
-                                   W, threads, precision, 1 if step else 0, global_batch, first_sample, C.byref(loss), C.byref(sec))
+                                   W, threads, precision, 1 if step else 0, global_batch, first_sample, C.byref(loss), C.byref(sec), _p(self.state) if self.state.size else None)
         if rc:
             raise ValueError(lib().gno_last_error().decode())
         self.timestep = ts.value
         self.seconds = sec.value
         return loss.value
 
-    def forward_batch(self, x, threads=1, precision=64):
+    def forward_batch(self, x, threads=1, precision=64, training=False):
         x = _f32(x)
         _, _, out = param_count(self.layers)
         res = np.empty((x.shape[0], out), dtype=np.float32)
         arr = layers_to_array(self.layers)
-        rc = lib().gno_forward_batch(arr, len(self.layers), _p(self.params), _p(x), x.shape[0], _p(res), threads, precision)
+        rc = lib().gno_forward_batch(arr, len(self.layers), _p(self.params), _p(x), x.shape[0], _p(res), threads, precision, _p(self.state) if self.state.size else None, 1 if training else 0)
         if rc:
             raise ValueError(lib().gno_last_error().decode())
         return res

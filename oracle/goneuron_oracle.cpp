@@ -113,6 +113,12 @@ template <class R> struct Layer {
   virtual const R* forward(const R* x) = 0;
   // grad may be modified in place by the callee, as in the reference.
   virtual const R* backward(R* grad) = 0;
+  // non-parameter state (BatchNorm2D running statistics): count, eval-mode source, and the statistics of the last forward
+  virtual int64_t n_state() const { return 0; }
+  virtual void bind_state(const R* st) {}
+  virtual void last_stats(R* dst) const {}
+  virtual R momentum() const { return R(0); }
+  bool training = true;
   // set by the trainer: true when this sample is the last one of its worker chunk
   bool last_of_chunk = true;
   virtual void set_last_of_chunk(bool v) { last_of_chunk = v; }
@@ -478,6 +484,54 @@ template <class R> struct LayerNorm : Layer<R> {
   }
 };
 
+
+// reference: internal/layer/batchnorm2d.go:255-510 (forward; called per sample, so the statistics are those of ONE
+// sample's H*W positions per channel; running statistics updated after every sample, :350-377), :524-665 (backward)
+template <class R> struct BatchNorm2D : Layer<R> {
+  int C, S; R eps, mom; const R *gamma = nullptr, *beta = nullptr, *run = nullptr; R *gGamma = nullptr, *gBeta = nullptr;
+  std::vector<R> saved, mean, var, sd, out, gradIn;
+  BatchNorm2D(int C_, int S_, R eps_, R mom_) : C(C_), S(S_), eps(eps_), mom(mom_), saved((size_t)C_ * S_), mean(C_), var(C_), sd(C_), out(saved.size()), gradIn(saved.size()) {}
+  int64_t n_params() const override { return 2 * (int64_t)C; }
+  void bind(const R* p, R* g) override { gamma = p; beta = p + C; gGamma = g; gBeta = g ? g + C : nullptr; }
+  int64_t n_state() const override { return 2 * (int64_t)C; }
+  void bind_state(const R* st) override { run = st; }
+  void last_stats(R* dst) const override { for (int f = 0; f < C; f++) { dst[f] = mean[f]; dst[C + f] = var[f]; } }
+  R momentum() const override { return mom; }
+  int in_size() const override { return C * S; } int out_size() const override { return C * S; }
+  const R* forward(const R* x) override {
+    if (!this->training) {
+      for (int f = 0; f < C; f++) { R m = run[f], sdv = r_sqrt<R>(run[C + f] + eps); for (int s = 0; s < S; s++) out[(size_t)f * S + s] = gamma[f] * ((x[(size_t)f * S + s] - m) / sdv) + beta[f]; }
+      return out.data();
+    }
+    std::copy(x, x + saved.size(), saved.begin());
+    R invN = R(1) / (R)S;
+    for (int f = 0; f < C; f++) {
+      const R* xf = x + (size_t)f * S; R sum = 0;
+      for (int s = 0; s < S; s++) sum += xf[s];
+      R m = sum * invN; mean[f] = m;
+      R ss = 0; for (int s = 0; s < S; s++) { R d = xf[s] - m; ss += d * d; }
+      R v = ss * invN; var[f] = v; sd[f] = r_sqrt<R>(v + eps);
+      R istd = R(1) / sd[f];
+      for (int s = 0; s < S; s++) out[(size_t)f * S + s] = gamma[f] * ((xf[s] - m) * istd) + beta[f];
+    }
+    return out.data();
+  }
+  const R* backward(R* grad) override {
+    R m_ = (R)S;
+    for (int f = 0; f < C; f++) {
+      const R* xf = saved.data() + (size_t)f * S; const R* gf = grad + (size_t)f * S; R mu = mean[f], sdv = sd[f], g = gamma[f];
+      R sumG = 0, sumGX = 0;
+      for (int s = 0; s < S; s++) { R d = xf[s] - mu; sumG += gf[s]; sumGX += gf[s] * d; }
+      for (int s = 0; s < S; s++) {
+        R d = xf[s] - mu, nm = d / sdv, gi = gf[s] * g;
+        gradIn[(size_t)f * S + s] = (gi / sdv - (sumG * g) / m_ / sdv - d * (sumGX * g) / m_ / (sdv * sdv * sdv));
+        gGamma[f] += gf[s] * nm; gBeta[f] += gf[s];
+      }
+    }
+    return gradIn.data();
+  }
+};
+
 // reference: internal/layer/transformer.go:405-527 (forward), :557-690 (backward)
 template <class R> struct MHA : Layer<R> {
   int d, heads, hd, T; bool causal;
@@ -623,7 +677,7 @@ template <class R> struct CLS : Layer<R> {
 // ---- network -----------------------------------------------------------------
 template <class R> struct Net {
   std::vector<std::unique_ptr<Layer<R>>> layers;
-  int64_t n_params = 0;
+  int64_t n_params = 0, n_state = 0;
   int in_size = 0, out_size = 0;
   bool has_lstm = false;
 
@@ -648,13 +702,16 @@ template <class R> struct Net {
         case GN_LAYER_POSENC: p.reset(new PosEnc<R>(l.seq_len, l.dim)); break;
         case GN_LAYER_TRANSFORMER_BLOCK: p.reset(new Block<R>(l.dim, l.heads, l.seq_len, l.ff_dim, l.causal != 0)); break;
         case GN_LAYER_CLS_POOLING: p.reset(new CLS<R>(l.seq_len, l.dim)); break;
+        case GN_LAYER_BATCHNORM2D: {
+          float eps = 1e-5f, mom = 0.1f; if (l.reserved) memcpy(&eps, &l.reserved, 4); if (l.dim) memcpy(&mom, &l.dim, 4);
+          p.reset(new BatchNorm2D<R>(l.in_size, l.in_h * l.in_w, (R)eps, (R)mom)); break; }
         case GN_LAYER_LAYERNORM: { if (cur < 0 || l.dim <= 0 || cur % l.dim) { g_err = "LayerNorm shape"; return false; } p.reset(new LayerNorm<R>(cur / l.dim, l.dim)); break; }
         default: g_err = "unknown layer kind"; return false;
       }
       if (cur >= 0 && p->in_size() != cur) { g_err = "layer " + std::to_string(i) + " input size mismatch: expected " + std::to_string(p->in_size()) + " got " + std::to_string(cur); return false; }
       if (i == 0) net.in_size = p->in_size();
       cur = p->out_size();
-      net.n_params += p->n_params();
+      net.n_params += p->n_params(); net.n_state += p->n_state();
       net.layers.push_back(std::move(p));
       (void)curT;
     }
@@ -665,6 +722,9 @@ template <class R> struct Net {
     int64_t o = 0;
     for (auto& l : layers) { l->bind(params + o, grads ? grads + o : nullptr); o += l->n_params(); }
   }
+  void bind_state(const R* st) { int64_t o = 0; for (auto& l : layers) { l->bind_state(st + o); o += l->n_state(); } }
+  void last_stats(R* dst) const { int64_t o = 0; for (auto& l : layers) { l->last_stats(dst + o); o += l->n_state(); } }
+  void set_training(bool t) { for (auto& l : layers) l->training = t; }
   const R* forward(const R* x) { const R* c = x; for (auto& l : layers) c = l->forward(c); return c; }
   void backward(R* grad) { R* c = grad; for (int i = (int)layers.size() - 1; i >= 0; i--) c = const_cast<R*>(layers[i]->backward(c)); }
 };
@@ -704,6 +764,7 @@ struct TrainArgs {
   const float* x; const float* y; int batch; int W; int threads; int do_step;
   int global_batch; int first_sample;   // this call's samples are [first_sample, first_sample+batch) of a global batch (one rank's shard)
   float* mean_loss; double* seconds;
+  float* state;   // running statistics, updated sample by sample in batch order (may be null when the model has none)
 };
 
 // reference: internal/net/net.go:588-717 (worker pool: contiguous chunks of ceil(B/W), private
@@ -736,6 +797,8 @@ template <class R> int train_batch_impl(const TrainArgs& a) {
     int ps = (c.e - c.s + parts - 1) / parts;
     for (int s = c.s; s < c.e; s += ps) jobs.push_back({s, std::min(c.e, s + ps), c.gend});
   }
+  const int64_t NS = proto.n_state;
+  std::vector<R> sample_stats((size_t)NS * B);
   std::vector<std::vector<R>> jgrads(jobs.size());
   std::vector<R> jloss(jobs.size(), R(0));
   std::atomic<int> next{0};
@@ -753,6 +816,7 @@ template <class R> int train_batch_impl(const TrainArgs& a) {
         for (int k = 0; k < in; k++) xs[k] = (R)a.x[(size_t)i * in + k];
         for (int k = 0; k < out; k++) ys[k] = (R)a.y[(size_t)i * out + k];
         const R* yp = net.forward(xs.data());
+        if (NS) net.last_stats(sample_stats.data() + (size_t)i * NS);
         local += loss_forward<R>(a.loss_kind, yp, ys.data(), out);
         loss_backward<R>(a.loss_kind, yp, ys.data(), lg.data(), out);
         net.backward(lg.data());
@@ -771,6 +835,12 @@ template <class R> int train_batch_impl(const TrainArgs& a) {
   R total = 0; for (R l : jloss) total += l;
   if (a.mean_loss) *a.mean_loss = (float)(total / (R)GB);                            // net.go:711-716
   if (a.grads_out) for (int64_t i = 0; i < P; i++) a.grads_out[i] = (float)grads[i];
+  if (NS && a.state) {
+    // running = (1 - momentum) * running + momentum * statistic, once per sample, in batch order (batchnorm2d.go:352, :376)
+    std::vector<R> st(NS); for (int64_t k = 0; k < NS; k++) st[k] = (R)a.state[k];
+    for (int i = 0; i < B; i++) { int64_t o = 0; for (auto& l : proto.layers) { R mo = l->momentum(); for (int64_t k = 0; k < l->n_state(); k++) st[o + k] = (R(1) - mo) * st[o + k] + mo * sample_stats[(size_t)i * NS + o + k]; o += l->n_state(); } }
+    for (int64_t k = 0; k < NS; k++) a.state[k] = (float)st[k];
+  }
   if (a.do_step) {
     // Network.Step (net.go:260-284): NewStep() increments the counter, StepInPlace uses counter+1,
     // so the first optimiser step runs with t = 2.
@@ -784,12 +854,13 @@ template <class R> int train_batch_impl(const TrainArgs& a) {
   return GN_OK;
 }
 
-template <class R> int forward_batch_impl(const gn_layer_desc* L, int n, const float* params_f, const float* x, int batch, float* out_f, int threads) {
+template <class R> int forward_batch_impl(const gn_layer_desc* L, int n, const float* params_f, const float* x, int batch, float* out_f, int threads, const float* state_f, int training) {
   Net<R> proto; if (!Net<R>::build(L, n, proto)) return GN_ERR_INVALID_ARG;
   std::vector<R> params(proto.n_params); for (int64_t i = 0; i < proto.n_params; i++) params[i] = (R)params_f[i];
+  std::vector<R> state(proto.n_state + 1, R(0)); if (state_f) for (int64_t i = 0; i < proto.n_state; i++) state[i] = (R)state_f[i];
   std::atomic<int> next{0};
   auto worker = [&]() {
-    Net<R> net; Net<R>::build(L, n, net); net.bind(params.data(), nullptr);
+    Net<R> net; Net<R>::build(L, n, net); net.bind(params.data(), nullptr); net.bind_state(state.data()); net.set_training(training != 0);
     std::vector<R> xs(net.in_size);
     for (;;) {
       int i = next.fetch_add(1); if (i >= batch) break;
@@ -810,6 +881,10 @@ extern "C" {
 
 const char* gno_last_error() { return g_err.c_str(); }
 
+int gno_state_count(const gn_layer_desc* layers, int n_layers, int64_t* n) {
+  Net<float> net; if (!Net<float>::build(layers, n_layers, net)) return GN_ERR_INVALID_ARG;
+  *n = net.n_state; return GN_OK;
+}
 int gno_param_count(const gn_layer_desc* layers, int n_layers, int64_t* n, int64_t* in_size, int64_t* out_size) {
   Net<float> net; if (!Net<float>::build(layers, n_layers, net)) return GN_ERR_INVALID_ARG;
   if (n) *n = net.n_params; if (in_size) *in_size = net.in_size; if (out_size) *out_size = net.out_size; return GN_OK;
@@ -822,14 +897,15 @@ int gno_param_count(const gn_layer_desc* layers, int n_layers, int64_t* n, int64
 int gno_train_batch(const gn_layer_desc* layers, int n_layers, int loss_kind, float* params, float* grads_out,
                     float* m, float* v, int* timestep, float lr, float b1, float b2, float eps,
                     const float* x, const float* y, int batch, int W, int threads, int precision, int do_step,
-                    int global_batch, int first_sample, float* mean_loss, double* seconds) {
-  TrainArgs a{layers, n_layers, loss_kind, params, grads_out, m, v, timestep, lr, b1, b2, eps, x, y, batch, W, threads, do_step, global_batch, first_sample, mean_loss, seconds};
+                    int global_batch, int first_sample, float* mean_loss, double* seconds, float* state) {
+  TrainArgs a{layers, n_layers, loss_kind, params, grads_out, m, v, timestep, lr, b1, b2, eps, x, y, batch, W, threads, do_step, global_batch, first_sample, mean_loss, seconds, state};
   return precision == 64 ? train_batch_impl<double>(a) : train_batch_impl<float>(a);
 }
 
-int gno_forward_batch(const gn_layer_desc* layers, int n_layers, const float* params, const float* x, int batch, float* out, int threads, int precision) {
-  return precision == 64 ? forward_batch_impl<double>(layers, n_layers, params, x, batch, out, threads)
-                         : forward_batch_impl<float>(layers, n_layers, params, x, batch, out, threads);
+int gno_forward_batch(const gn_layer_desc* layers, int n_layers, const float* params, const float* x, int batch, float* out, int threads, int precision,
+                      const float* state, int training) {
+  return precision == 64 ? forward_batch_impl<double>(layers, n_layers, params, x, batch, out, threads, state, training)
+                         : forward_batch_impl<float>(layers, n_layers, params, x, batch, out, threads, state, training);
 }
 
 // ---- single operators, for the golden-vector tests ----------------------------

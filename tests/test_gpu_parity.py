@@ -34,6 +34,8 @@ CASES = [
     ("transformer_large", dict(vocab=1000, dim=128, seq_len=80, heads=2, ff_dim=256, n_blocks=1), 6, 1),    # head width 64, T not a multiple of the 64-row block
     ("transformer_small", dict(vocab=700, dim=96, seq_len=150, heads=3, ff_dim=192, n_blocks=1), 4, 1),     # head width 32, three key blocks, ragged tail
     ("transformer_small", dict(vocab=300, dim=40, seq_len=20, heads=5, ff_dim=64, n_blocks=1), 4, 1),       # head width 8: the unfused attention path
+    ("cnn_bn", {}, 32, 1),                                                                                  # BatchNorm2D
+    ("cnn_bn", dict(hw=10, c0=2, c1=5, classes=3), 7, 1),
 ]
 
 
@@ -164,3 +166,22 @@ def test_unfused_attention_path_in_subprocess():
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_parity.py"), "-q", "-x", "-m", "gpu", "-k", ids],
                        env=env, cwd=root, capture_output=True, text=True)
     assert r.returncode == 0 and " passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_batchnorm_running_statistics_and_inference(device, oracle):
+    """BatchNorm2D: running mean / variance follow the per-sample updates in batch order, and inference uses them."""
+    from goneuron_b200.sequential import Adam, Sequential
+    layers, loss_kind, params, x, y, lr = configs.make_case("cnn_bn", batch=12)
+    ref = oracle.OracleState(layers, loss_kind, params, lr=lr)
+    model = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+    model.SetParams(params)
+    assert np.array_equal(model.State(), ref.state)            # mean 0, variance 1
+    for _ in range(2):
+        ref.train_batch(x, y, precision=64)
+        model.TrainBatch(x, y)
+    assert norm_err(model.State(), ref.state) <= TOL
+    assert norm_err(model.PredictBatch(x[:5]), ref.forward_batch(x[:5], precision=64)) <= 1e-3   # weights carry two Adam steps
+    # state round-trip through the C ABI, then identical weights => inference parity at the strict tolerance
+    model.SetParams(ref.params); model.SetState(ref.state)
+    assert norm_err(model.PredictBatch(x[:5]), ref.forward_batch(x[:5], precision=64)) <= TOL
+    model.Close()
