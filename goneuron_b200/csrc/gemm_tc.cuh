@@ -263,19 +263,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
 // One CTA per SM walks the output tiles (n fastest, so CTAs running together share A rows in L2).  TMEM holds two
 // accumulator slots of 2*BN columns (main + cross terms), so the epilogue warps drain tile i while the MMA warp already
 // accumulates tile i+1 and the TMA warp keeps the shared-memory ring full across tile boundaries:
+// With BN = 256 one slot fills TMEM: the epilogue is then not overlapped, but it only has to read TMEM (stores are
+// not waited for) and the TMA warp already streams the next tile's operands meanwhile.
 //   full[s]/empty[s]   TMA <-> MMA per shared-memory stage (running stage counter across tiles)
 //   tfull[b]/tempty[b] MMA <-> epilogue per TMEM slot
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 
-template <int BN, int BK>
+template <int BN, int BK, int NSLOTS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
                        const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo, TcParams ep,
                        int tiles_m, int tiles_n, int total_tiles) {
   using Cfg = TcCfg<BN, BK>;
-  static_assert(4 * BN <= 512, "two accumulator slots must fit the 512 TMEM columns");
+  static_assert(NSLOTS * 2 * BN <= 512 && (NSLOTS == 1 || NSLOTS == 2), "accumulator slots must fit the 512 TMEM columns");
   constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, B_BYTES = Cfg::B_BYTES, A_BYTES = Cfg::A_BYTES;
-  constexpr uint32_t TMEM_COLS = 4 * BN;
+  constexpr uint32_t TMEM_COLS = NSLOTS * 2 * BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);       // full[S], empty[S], tfull[2], tempty[2]
@@ -333,7 +335,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_
       constexpr uint32_t idesc = make_idesc(TC_BM, BN);
       for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
         int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
-        const uint32_t slot = lt & 1, u = lt >> 1; lt++;
+        const uint32_t slot = NSLOTS == 2 ? (lt & 1) : 0, u = NSLOTS == 2 ? (lt >> 1) : lt; lt++;
         ok &= mbar_wait(tempty0 + 8 * slot, (u & 1) ^ 1);          // slot drained by the epilogue (passes at once the first time)
         tc_fence_after();
         const uint32_t acc_main = tmem_base + slot * 2 * BN, acc_cross = acc_main + BN;
@@ -362,7 +364,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_
     const int quad = warp & 3; uint32_t lt = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
-      const uint32_t slot = lt & 1, u = lt >> 1; lt++;
+      const uint32_t slot = NSLOTS == 2 ? (lt & 1) : 0, u = NSLOTS == 2 ? (lt >> 1) : lt; lt++;
       bool ok = true;
       if (lane == 0) ok = mbar_wait(tfull0 + 8 * slot, u & 1);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -434,8 +436,9 @@ inline void tc_init(Ctx* ctx) {
   ok &= cudaFuncSetAttribute(gemm_tc_kernel<128, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128, 32>::SMEM_BYTES) == cudaSuccess;
   ok &= cudaFuncSetAttribute(gemm_tc_kernel<64, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64, 32>::SMEM_BYTES) == cudaSuccess;
   ok &= cudaFuncSetAttribute(gemm_tc_kernel<256, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256, 16>::SMEM_BYTES) == cudaSuccess;
-  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<128, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128, 32>::SMEM_BYTES) == cudaSuccess;
-  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<64, 32>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64, 32>::SMEM_BYTES) == cudaSuccess;
+  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<256, 32, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256, 32>::SMEM_BYTES) == cudaSuccess;
+  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<128, 32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128, 32>::SMEM_BYTES) == cudaSuccess;
+  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<64, 32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64, 32>::SMEM_BYTES) == cudaSuccess;
   if (!ok) { cudaGetLastError(); return; }
   ctx->encode_tiled = fn; ctx->tc_ok = true;
 }
@@ -471,7 +474,7 @@ inline int tc_launch_bn(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const Tc
   GN_LAUNCH(ctx, (gemm_tc_kernel<BN, BK>), grid, TC_THREADS, (TcCfg<BN, BK>::SMEM_BYTES), mAh, mAl, mBh, mBl, ep);
   return check_launch("gemm_tc");
 }
-template <int BN, int BK = 32>
+template <int BN, int NSLOTS, int BK = 32>
 inline int tc_launch_persist(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep) {
   CUtensorMap mAh, mAl, mBh, mBl;
   GN_TRY(tc_make_map(ctx, &mAh, A, A.hi, TC_BM, BK)); GN_TRY(tc_make_map(ctx, &mAl, A, A.lo, TC_BM, BK));
@@ -479,7 +482,7 @@ inline int tc_launch_persist(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, con
   const int tiles_m = cdiv(ep.M, TC_BM), tiles_n = cdiv(ep.N, BN); const long total = (long)tiles_m * tiles_n * A.nbatch;
   if (total > 0x7fffffffL) return fail(GN_ERR_UNSUPPORTED, "too many output tiles");
   const unsigned grid = (unsigned)std::min<long>(total, ctx->sm_count);
-  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN, BK>), grid, TC_THREADS, (TcCfg<BN, BK>::SMEM_BYTES), mAh, mAl, mBh, mBl, ep, tiles_m, tiles_n, (int)total);
+  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN, BK, NSLOTS>), grid, TC_THREADS, (TcCfg<BN, BK>::SMEM_BYTES), mAh, mAl, mBh, mBl, ep, tiles_m, tiles_n, (int)total);
   return check_launch("gemm_tc_persist");
 }
 // C[z] = A[z] * B[z]^T from prepared planes; the N tile follows the output width.
@@ -495,7 +498,11 @@ inline int tc_launch(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcPar
   static const int force_bn = [] { const char* e = getenv("GONEURON_TC_BN"); return e ? atoi(e) : 0; }();   // tuning aids
   static const int bk = [] { const char* e = getenv("GONEURON_TC_BK"); return e ? atoi(e) : 32; }();
   static const int persist = [] { const char* e = getenv("GONEURON_TC_PERSIST"); return e ? atoi(e) : 1; }();
-  if (persist && !force_bn) return ep.N <= 64 ? tc_launch_persist<64>(ctx, A, B, ep) : tc_launch_persist<128>(ctx, A, B, ep);
+  if (persist && !force_bn) {
+    if (ep.N <= 64) return tc_launch_persist<64, 2>(ctx, A, B, ep);
+    if (ep.N <= 128 || persist != 3) return tc_launch_persist<128, 2>(ctx, A, B, ep);   // measured faster than the one-slot 256-wide tile
+    return tc_launch_persist<256, 1>(ctx, A, B, ep);
+  }
   if (force_bn == 128) return tc_launch_bn<128>(ctx, A, B, ep);
   if (force_bn == 64) return tc_launch_bn<64>(ctx, A, B, ep);
   if (ep.N <= 64) return tc_launch_bn<64>(ctx, A, B, ep);
