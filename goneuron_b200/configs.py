@@ -23,6 +23,11 @@ def cnn(hw=32, c0=3, c1=16, c2=32, classes=10):
             D.Flatten(), D.Dense(c2 * h4 * h4, classes, D.SOFTMAX)], D.CROSS_ENTROPY
 
 
+def mlp_ln(in_size=24, hidden=48, norm=16, classes=4):
+    """Dense -> LayerNorm over consecutive rows of `norm` -> Dense: exercises the stand-alone LayerNorm layer."""
+    return [D.Dense(in_size, hidden, D.TANH), D.LayerNorm(norm), D.Dense(hidden, classes, D.SOFTMAX)], D.CROSS_ENTROPY
+
+
 def cnn_bn(hw=16, c0=3, c1=8, classes=5):
     """Conv -> BatchNorm2D -> MaxPool -> Flatten -> Dense: exercises BatchNorm2D (used by the reference's CIFAR example)."""
     h2 = hw // 2
@@ -46,11 +51,12 @@ CONFIGS = {
     "mlp": (mlp, {}, 64, 1e-3),
     "cnn": (cnn, {}, 128, 1e-3),
     "cnn_bn": (cnn_bn, {}, 32, 1e-3),
+    "mlp_ln": (mlp_ln, {}, 16, 1e-3),
     "lstm": (recurrent, {}, 256, 1e-3),
     "transformer_small": (transformer, dict(vocab=8192, dim=256, seq_len=128, heads=8, ff_dim=1024, n_blocks=4), 64, 3e-4),
     "transformer_large": (transformer, dict(vocab=32000, dim=1024, seq_len=512, heads=16, ff_dim=4096, n_blocks=8), 256, 1e-4),
 }
-SEEDS = {"cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
+SEEDS = {"mlp_ln": 1241, "cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
 
 
 def build(name, **override):

@@ -62,7 +62,7 @@ extern "C" int gn_op_gemm_nt_static(gn_ctx* ctx, int M, int N, int K, const floa
   TcPlanes PA{a_hi, a_lo, M, K, (int)ldp, 1}, PB{b_hi, b_lo, N, K, (int)ldp, 1};
   GN_TRY(tc_split(c, TcSrc{A_dev, (long)K, 1, 0, 0, 1}, PA));
   GN_TRY(tc_split(c, TcSrc{B_dev, (long)K, 1, 0, 0, 1}, PB));
-  TcParams ep{C_dev, (long)N, 0, 0, bias_dev, nullptr, 0, 0, 0, GN_ACT_LINEAR, M, N, K, 1, 0, c->d_status, nullptr, 0, 1};
+  TcParams ep{C_dev, (long)N, 0, 0, bias_dev, nullptr, 0, 0, 0, GN_ACT_LINEAR, M, N, K, 1, 0, c->d_status, nullptr, 0, 1, nullptr, nullptr, 0};
   GN_TRY(tc_launch(c, PA, PB, ep));
   GN_CUDA(cudaStreamSynchronize(c->stream));
   int st = 0; GN_CUDA(cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost));

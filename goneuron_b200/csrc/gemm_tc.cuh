@@ -86,6 +86,7 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
+__device__ __forceinline__ float tf32_round(float x) { uint32_t u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x)); return __uint_as_float(u); }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -101,6 +102,7 @@ struct TcParams {
   float* C; long ldc, c_b1, c_b2; const float* bias; const float* R; long ldr, r_b1, r_b2;
   int act, M, N, K, batch2, flags; int* status;
   const float* mask; long mask_ld; int mask_group;    // optional gate, see GemmDesc::mask
+  float* Chi; float* Clo; long c_ldp;                 // optional: result also as hi/lo planes (single problem only)
 };
 
 // Epilogue of one output tile, executed by one warp for its TMEM lane quadrant: one output row per thread
@@ -149,6 +151,11 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
           if (ep.act == GN_ACT_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
           if (!(mv[j].x > 0.f)) v.x = 0.f; if (!(mv[j].y > 0.f)) v.y = 0.f; if (!(mv[j].z > 0.f)) v.z = 0.f; if (!(mv[j].w > 0.f)) v.w = 0.f;
           *reinterpret_cast<float4*>(Crow + col0 + 4 * j) = v;
+          if (ep.Chi) {
+            float4 h = make_float4(tf32_round(v.x), tf32_round(v.y), tf32_round(v.z), tf32_round(v.w));
+            *reinterpret_cast<float4*>(ep.Chi + (long)row * ep.c_ldp + col0 + 4 * j) = h;
+            *reinterpret_cast<float4*>(ep.Clo + (long)row * ep.c_ldp + col0 + 4 * j) = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+          }
         }
       } else {
         if (nkb > 0) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -162,6 +169,7 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
           if (ep.act == GN_ACT_RELU) v = fmaxf(v, 0.f);
           if (Mrow && !(Mrow[col] > 0.f)) v = 0.f;
           Crow[col] = v;
+          if (ep.Chi) { float h = tf32_round(v); ep.Chi[(long)row * ep.c_ldp + col] = h; ep.Clo[(long)row * ep.c_ldp + col] = v - h; }
         }
       }
     }
@@ -383,7 +391,6 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_
 }
 
 // ------------------------------------------------------------------ operand split (memory-bound)
-__device__ __forceinline__ float tf32_round(float x) { uint32_t u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x)); return __uint_as_float(u); }
 // Batched, strided split: planes[z][r][c] (row stride ldp, c < ldp, zero beyond cols) of the source element
 // (z, r, c) at p + (z / batch2) * b1 + (z % batch2) * b2 + r * s_r + c * s_c.  One of s_r, s_c is 1:
 // s_c == 1 reads rows directly; s_r == 1 (the operand is the transpose of what is stored) goes through a shared tile.
@@ -424,7 +431,7 @@ typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_
 struct TcPlanes { float* hi; float* lo; int rows, K, ldp, nbatch; };
 inline int tc_ldp(int K) { return ((K + 3) / 4) * 4; }              // plane row stride: a multiple of 16 bytes for TMA
 
-struct TcScratch { DevBuf a_hi, a_lo, b_hi, b_lo; };
+struct TcScratch { DevBuf a_hi, a_lo, b_hi, b_lo; const float* last_a = nullptr; int last_m = 0, last_k = 0; long last_ld = 0; };
 inline TcScratch& tc_scratch(Ctx* ctx) { static thread_local std::vector<std::pair<Ctx*, TcScratch*>> tab; for (auto& e : tab) if (e.first == ctx) return *e.second; tab.push_back({ctx, new TcScratch()}); return *tab.back().second; }
 
 inline void tc_init(Ctx* ctx) {
@@ -494,6 +501,7 @@ inline int tc_launch(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcPar
   bool vec = ep.N % 4 == 0 && ep.ldc % 4 == 0 && ep.c_b1 % 4 == 0 && ep.c_b2 % 4 == 0 && a16(ep.C) && (!ep.bias || a16(ep.bias));
   if (ep.R) vec = vec && ep.ldr % 4 == 0 && ep.r_b1 % 4 == 0 && ep.r_b2 % 4 == 0 && a16(ep.R);
   if (ep.mask) vec = vec && ep.mask_ld % 4 == 0 && a16(ep.mask);
+  if (ep.Chi) vec = vec && ep.c_ldp % 4 == 0 && a16(ep.Chi) && a16(ep.Clo);
   if (vec) ep.flags |= TC_FLAG_VEC;
   static const int force_bn = [] { const char* e = getenv("GONEURON_TC_BN"); return e ? atoi(e) : 0; }();   // tuning aids
   static const int bk = [] { const char* e = getenv("GONEURON_TC_BK"); return e ? atoi(e) : 32; }();
@@ -532,13 +540,21 @@ inline int gemm_tc(Ctx* ctx, const GemmDesc& g) {
   TcScratch& sc = tc_scratch(ctx);
   const int nb = g.batch1 * g.batch2, ldp = tc_ldp(g.K);
   size_t na = (size_t)nb * g.M * ldp, nbb = (size_t)nb * g.N * ldp;
-  if (sc.a_hi.n < na) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.a_hi.alloc(na)); GN_TRY(sc.a_lo.alloc(na)); }
+  if (!g.a_hi && sc.a_hi.n < na) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.a_hi.alloc(na)); GN_TRY(sc.a_lo.alloc(na)); sc.last_a = nullptr; }
   if (sc.b_hi.n < nbb) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.b_hi.alloc(nbb)); GN_TRY(sc.b_lo.alloc(nbb)); }
   TcPlanes A{sc.a_hi.p, sc.a_lo.p, g.M, g.K, ldp, nb}, B{sc.b_hi.p, sc.b_lo.p, g.N, g.K, ldp, nb};
-  GN_TRY(tc_split(ctx, TcSrc{g.A, g.sa_m, g.sa_k, g.a_b1, g.a_b2, g.batch2}, A));
+  if (g.a_hi) {                                       // planes written by the producing contraction's epilogue
+    A.hi = const_cast<float*>(g.a_hi); A.lo = const_cast<float*>(g.a_lo); A.ldp = g.a_ldp;
+  } else if (g.reuse_a_planes && nb == 1 && sc.last_a == g.A && sc.last_m == g.M && sc.last_k == g.K && sc.last_ld == g.sa_m && g.sa_k == 1) {
+    // same tensor as the previous call (the Q, K and V projections share their input): planes still valid
+  } else {
+    GN_TRY(tc_split(ctx, TcSrc{g.A, g.sa_m, g.sa_k, g.a_b1, g.a_b2, g.batch2}, A));
+    sc.last_a = (nb == 1 && g.sa_k == 1) ? g.A : nullptr; sc.last_m = g.M; sc.last_k = g.K; sc.last_ld = g.sa_m;
+  }
   GN_TRY(tc_split(ctx, TcSrc{g.B, g.sb_n, g.sb_k, g.b_b1, g.b_b2, g.batch2}, B));
   static const int noload = [] { const char* e = getenv("GONEURON_TC_NOLOAD"); return e ? atoi(e) * 256 : 0; }();
-  TcParams ep{g.C, g.ldc, g.c_b1, g.c_b2, g.bias, g.R, g.ldr, g.r_b1, g.r_b2, g.act, g.M, g.N, g.K, g.batch2, g.flags | noload, ctx->d_status, g.mask, g.mask_ld, g.mask_group};
+  TcParams ep{g.C, g.ldc, g.c_b1, g.c_b2, g.bias, g.R, g.ldr, g.r_b1, g.r_b2, g.act, g.M, g.N, g.K, g.batch2, g.flags | noload, ctx->d_status, g.mask, g.mask_ld, g.mask_group,
+              nb == 1 ? g.c_hi : nullptr, nb == 1 ? g.c_lo : nullptr, g.c_ldp};
   return tc_launch(ctx, A, B, ep);
 }
 

@@ -29,6 +29,10 @@
 namespace gn {
 
 // ------------------------------------------------------------------ contraction dispatch
+static bool force_simt_engine() { static const bool f = [] { const char* e = getenv("GONEURON_CUDA_ENGINE"); return e && strcmp(e, "simt") == 0; }(); return f; }
+// Both contractions of a producer -> consumer pair run on the tensor-core engine (so operand planes can be handed over).
+static bool tc_chain_ok(Ctx* ctx, const GemmDesc& a, const GemmDesc& b) { return !force_simt_engine() && gemm_tc_eligible(ctx, a) && gemm_tc_eligible(ctx, b); }
+
 // Chooses the tensor-core engine for large K-major x K-major products and the SIMT engine for the rest.
 static int gemm(Ctx* ctx, const GemmDesc& g) {
   cudaEvent_t e0 = nullptr, e1 = nullptr;
@@ -40,8 +44,7 @@ static int gemm(Ctx* ctx, const GemmDesc& g) {
     GN_CUDA(cudaEventRecord(e0, ctx->stream));
   }
   int rc;
-  static const bool force_simt = [] { const char* e = getenv("GONEURON_CUDA_ENGINE"); return e && strcmp(e, "simt") == 0; }();
-  if (!force_simt && gemm_tc_eligible(ctx, g)) rc = gemm_tc(ctx, g);
+  if (!force_simt_engine() && gemm_tc_eligible(ctx, g)) rc = gemm_tc(ctx, g);
   else rc = gemm_simt(ctx, g);
   if (ctx->profile) { GN_CUDA(cudaEventRecord(e1, ctx->stream)); }
   double nb = (double)g.batch1 * g.batch2;
@@ -107,7 +110,7 @@ struct gn_model {
 
 namespace gn {
 
-enum Slot { S_G0 = 0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+enum Slot { S_PL_HI = 0, S_PL_LO, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
 
 static int ensure(gn_model* m, int slot, size_t n, float** out) {
   if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
@@ -305,8 +308,11 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
       case GN_LAYER_TRANSFORMER_BLOCK: {
         const int T = d.seq_len, D = d.dim, F = d.ff_dim; const int N = B * T; BlockParams bp = block_params(p, D, F);
         GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wq, bp.bq, l.q.p, D));
-        GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wk, bp.bk, l.k.p, D));
-        GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wv, bp.bv, l.v.p, D));
+        {   // the K and V projections read the same input: its operand planes are still in the engine's scratch
+          GemmDesc g; g.M = N; g.N = D; g.K = D; g.A = cur; g.sa_m = D; g.sa_k = 1; g.sb_k = 1; g.sb_n = D; g.ldc = D; g.reuse_a_planes = true;
+          g.B = bp.wk; g.bias = bp.bk; g.C = l.k.p; GN_TRY(gemm(ctx, g));
+          g.B = bp.wv; g.bias = bp.bv; g.C = l.v.p; GN_TRY(gemm(ctx, g));
+        }
         if (use_fused_attention(d)) {
           GN_TRY(attn_fwd(ctx, D / d.heads, l.q.p, l.k.p, l.v.p, l.att.p, l.att_m.p, l.att_l.p, B, T, D, d.heads, d.causal));
         } else {
@@ -316,8 +322,15 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         GN_TRY(gemm_nt(ctx, N, D, D, l.att.p, D, bp.wo, bp.bo, l.r1.p, D, GN_ACT_LINEAR, cur, D));          // res1 = x + att
         float* st = l.stat.p;
         GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(N, 8), 256, 0, l.r1.p, bp.g1, bp.be1, l.n1.p, st, st + N, (long)N, D, 1e-5f);
-        GN_TRY(gemm_nt(ctx, N, F, D, l.n1.p, D, bp.w1, bp.b1, l.mid.p, F, GN_ACT_RELU));
-        GN_TRY(gemm_nt(ctx, N, D, F, l.mid.p, F, bp.w2, bp.b2, l.r2.p, D, GN_ACT_LINEAR, l.n1.p, D));        // res2 = norm1 + ff
+        {   // ff1 (ReLU) -> ff2; on the tensor-core engine ff1's epilogue also writes the operand planes ff2 consumes
+          GemmDesc g1; g1.M = N; g1.N = F; g1.K = D; g1.A = l.n1.p; g1.sa_m = D; g1.sa_k = 1; g1.B = bp.w1; g1.sb_k = 1; g1.sb_n = D; g1.C = l.mid.p; g1.ldc = F; g1.bias = bp.b1; g1.act = GN_ACT_RELU;
+          GemmDesc g2; g2.M = N; g2.N = D; g2.K = F; g2.A = l.mid.p; g2.sa_m = F; g2.sa_k = 1; g2.B = bp.w2; g2.sb_k = 1; g2.sb_n = F; g2.C = l.r2.p; g2.ldc = D; g2.bias = bp.b2; g2.R = l.n1.p; g2.ldr = D;   // res2 = norm1 + ff
+          if (tc_chain_ok(ctx, g1, g2) && F % 4 == 0) {
+            float *ph, *pl; GN_TRY(ensure(m, S_PL_HI, (size_t)N * F, &ph)); GN_TRY(ensure(m, S_PL_LO, (size_t)N * F, &pl));
+            g1.c_hi = ph; g1.c_lo = pl; g1.c_ldp = F; g2.a_hi = ph; g2.a_lo = pl; g2.a_ldp = F;
+          }
+          GN_TRY(gemm(ctx, g1)); GN_TRY(gemm(ctx, g2));
+        }
         GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(N, 8), 256, 0, l.r2.p, bp.g2, bp.be2, l.out.p, st + 2 * N, st + 3 * N, (long)N, D, 1e-5f);
         cur = l.out.p; break; }
       case GN_LAYER_CLS_POOLING:
@@ -342,6 +355,25 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
   *y_out = cur; return GN_OK;
 }
 
+// LayerNorm backward: dx, and gGamma / gBeta accumulated into the gradient slice.
+static int layernorm_backward(gn_model* m, const float* g, const float* x, const float* gamma, const float* mean, const float* sd, float* dx,
+                              float* gGamma, float* gBeta, long rows, int n) {
+  Ctx* ctx = &m->ctx->c;
+  if (n <= 32 * LN_MAXC) {
+    const int blocks = (int)std::min<long>((rows + 7) / 8, (long)ctx->sm_count), warps = blocks * 8;
+    float* part; GN_TRY(ensure(m, S_PART2, (size_t)warps * 2 * n, &part));
+    GN_LAUNCH(ctx, layernorm_bwd_fused_kernel, blocks, 256, 0, g, x, gamma, mean, sd, dx, part, rows, n);
+    GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(n, 128), 128, 0, part, warps, n, gGamma, gBeta);
+  } else {
+    const int chunks = (int)std::max<long>(1, std::min<long>(rows / 64, 128));
+    float* part; GN_TRY(ensure(m, S_PART2, (size_t)chunks * 2 * n, &part));
+    GN_LAUNCH(ctx, layernorm_pgrad_partial_kernel, dim3(cdiv(n, 128), chunks), 128, 0, g, x, mean, sd, rows, n, part);
+    GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(n, 128), 128, 0, part, chunks, n, gGamma, gBeta);
+    GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows, n);
+  }
+  return check_launch("layernorm_backward");
+}
+
 // ---------------------------------------------------------------- backward
 // Gradient of one inner Dense of a TransformerBlock at batch level:
 //   gb = sum over all tokens of dz ; gW = Delta^T * X_last with Delta[s] = sum_t dz[s,t], X_last[s] = x[s,T-1]
@@ -361,25 +393,25 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
   GN_TRY(ensure(m, S_ND0, ND, &dR2)); GN_TRY(ensure(m, S_NFF, (size_t)N * F, &dM)); GN_TRY(ensure(m, S_ND1, ND, &comb));
   GN_TRY(ensure(m, S_ND2, ND, &dR1)); GN_TRY(ensure(m, S_ND3, ND, &dA));
   if (!fused) { GN_TRY(ensure(m, S_ATT0, (size_t)B * Hh * T * T, &P)); GN_TRY(ensure(m, S_ATT1, (size_t)B * Hh * T * T, &dP)); }
-  float* part; int chunks = std::max(1, std::min(N / 64, 128)); GN_TRY(ensure(m, S_PART2, (size_t)chunks * 2 * std::max(D, F), &part));
   // LayerNorm 2
-  GN_LAUNCH(ctx, layernorm_pgrad_partial_kernel, dim3(cdiv(D, 128), chunks), 128, 0, gout, l.r2.p, st + 2 * N, st + 3 * N, (long)N, D, part);
-  GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(D, 128), 128, 0, part, chunks, D, (float*)gp.g2, (float*)gp.be2);
-  GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(N, 8), 256, 0, gout, l.r2.p, bp.g2, st + 2 * N, st + 3 * N, dR2, (long)N, D);
+  GN_TRY(layernorm_backward(m, gout, l.r2.p, bp.g2, st + 2 * N, st + 3 * N, dR2, (float*)gp.g2, (float*)gp.be2, (long)N, D));
   // ff2 then ff1, token by token in the reference (transformer.go:1238-1250)
   GN_TRY(inner_dense_param_grads(m, dR2, B, T, D, l.mid.p, F, (float*)gp.w2, (float*)gp.b2));
   {
     // dz1[s,t,:] = (W2^T dR2[s,t,:]) gated by the ReLU pattern of the LAST token of sequence s (fused into the epilogue)
     GemmDesc g; g.M = N; g.N = F; g.K = D; g.A = dR2; g.sa_m = D; g.sa_k = 1; g.B = bp.w2; g.sb_k = F; g.sb_n = 1; g.C = dM; g.ldc = F;
     g.mask = l.mid.p + (long)(T - 1) * F; g.mask_ld = (long)T * F; g.mask_group = T;
+    GemmDesc h; h.M = N; h.N = D; h.K = F; h.A = dM; h.sa_m = F; h.sa_k = 1; h.B = bp.w1; h.sb_k = D; h.sb_n = 1; h.C = comb; h.ldc = D; h.R = dR2; h.ldr = D;   // combined = gradRes2 + W1^T dz1
+    if (tc_chain_ok(ctx, g, h) && F % 4 == 0) {
+      float *ph, *pl; GN_TRY(ensure(m, S_PL_HI, (size_t)N * F, &ph)); GN_TRY(ensure(m, S_PL_LO, (size_t)N * F, &pl));
+      g.c_hi = ph; g.c_lo = pl; g.c_ldp = F; h.a_hi = ph; h.a_lo = pl; h.a_ldp = F;
+    }
     GN_TRY(gemm(ctx, g));
+    GN_TRY(inner_dense_param_grads(m, dM, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1));
+    GN_TRY(gemm(ctx, h));
   }
-  GN_TRY(inner_dense_param_grads(m, dM, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1));
-  GN_TRY(gemm_nn(ctx, N, F, D, dM, F, bp.w1, comb, D, dR2, D));                          // combined = gradRes2 + W1^T dz1
   // LayerNorm 1
-  GN_LAUNCH(ctx, layernorm_pgrad_partial_kernel, dim3(cdiv(D, 128), chunks), 128, 0, comb, l.r1.p, st, st + N, (long)N, D, part);
-  GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(D, 128), 128, 0, part, chunks, D, (float*)gp.g1, (float*)gp.be1);
-  GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(N, 8), 256, 0, comb, l.r1.p, bp.g1, st, st + N, dR1, (long)N, D);
+  GN_TRY(layernorm_backward(m, comb, l.r1.p, bp.g1, st, st + N, dR1, (float*)gp.g1, (float*)gp.be1, (long)N, D));
   // output projection
   GN_TRY(inner_dense_param_grads(m, dR1, B, T, D, l.att.p, D, (float*)gp.wo, (float*)gp.bo));
   GN_TRY(gemm_nn(ctx, N, D, D, dR1, D, bp.wo, dA, D));
@@ -498,11 +530,8 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         GN_TRY(colsum(m, pg, 2 * C, B, 2 * C, gr, false));
         g = dx; flip ^= 1; break; }
       case GN_LAYER_LAYERNORM: {
-        long rows = (long)B * (l.in_size / d.dim); int chunks = (int)std::max<long>(1, std::min<long>(rows / 64, 128));
-        float* part; GN_TRY(ensure(m, S_PART2, (size_t)chunks * 2 * d.dim, &part));
-        GN_LAUNCH(ctx, layernorm_pgrad_partial_kernel, dim3(cdiv(d.dim, 128), chunks), 128, 0, g, xin, l.stat.p, l.stat.p + rows, rows, d.dim, part);
-        GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(d.dim, 128), 128, 0, part, chunks, d.dim, gr, gr + d.dim);
-        GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(rows, 8), 256, 0, g, xin, p, l.stat.p, l.stat.p + rows, dx, rows, d.dim);
+        long rows = (long)B * (l.in_size / d.dim);
+        GN_TRY(layernorm_backward(m, g, xin, p, l.stat.p, l.stat.p + rows, dx, gr, gr + d.dim, rows, d.dim));
         g = dx; flip ^= 1; break; }
     }
     GN_TRY(check_launch("backward"));

@@ -36,6 +36,8 @@ CASES = [
     ("transformer_small", dict(vocab=300, dim=40, seq_len=20, heads=5, ff_dim=64, n_blocks=1), 4, 1),       # head width 8: the unfused attention path
     ("cnn_bn", {}, 32, 1),                                                                                  # BatchNorm2D
     ("cnn_bn", dict(hw=10, c0=2, c1=5, classes=3), 7, 1),
+    ("mlp_ln", {}, 16, 1),                                                                                  # stand-alone LayerNorm, sigmoid-family activation
+    ("mlp_ln", dict(in_size=10, hidden=2200, norm=1100, classes=3), 5, 1),                                  # rows wider than the fused kernel holds
 ]
 
 
