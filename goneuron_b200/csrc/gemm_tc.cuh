@@ -531,7 +531,7 @@ inline bool gemm_tc_supported(Ctx* ctx, const GemmDesc& g) {
 // Is it worth it?  Small or skinny problems stay on the SIMT engine.
 inline bool gemm_tc_eligible(Ctx* ctx, const GemmDesc& g) {
   if (!gemm_tc_supported(ctx, g)) return false;
-  return g.M >= 64 && g.N >= 32 && g.K >= 32 && (double)g.M * g.N * g.K * g.batch1 * g.batch2 >= 1.0e8;
+  return g.M >= 16 && g.N >= 32 && g.K >= 32 && (double)g.M * g.N * g.K * g.batch1 * g.batch2 >= 1.0e8;
 }
 
 // General entry: splits both operands into the context's scratch planes, then runs the contraction.

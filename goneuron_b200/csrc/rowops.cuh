@@ -150,37 +150,6 @@ __global__ void layernorm_bwd_kernel(const float* __restrict__ g, const float* _
     dr[i] = v;
   }
 }
-// Fused backward: dx and the per-warp partial sums of gGamma / gBeta in one pass over g and x.  Each warp walks rows
-// gw, gw + W, ... and keeps the column partials of its lanes in registers (n <= 32 * LN_MAXC); the partials
-// [warp][2][n] are reduced by layernorm_pgrad_final_kernel.  dx may alias g.
-constexpr int LN_MAXC = 32;
-__global__ void __launch_bounds__(256) layernorm_bwd_fused_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
-                                                                  const float* __restrict__ mean_in, const float* __restrict__ std_in, float* dx,
-                                                                  float* __restrict__ part, long rows, int n) {
-  const int lane = threadIdx.x & 31; const long gw = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), W = (long)gridDim.x * (blockDim.x >> 5);
-  float pg[LN_MAXC], pb[LN_MAXC];
-#pragma unroll
-  for (int k = 0; k < LN_MAXC; k++) { pg[k] = 0.f; pb[k] = 0.f; }
-  const float fn = (float)n;
-  for (long row = gw; row < rows; row += W) {
-    const float* xr = x + row * n; const float* gr = g + row * n; float* dr = dx + row * n;
-    const float mean = mean_in[row], sd = std_in[row];
-    float sg = 0.f, sgx = 0.f;
-#pragma unroll
-    for (int k = 0; k < LN_MAXC; k++) {
-      const int i = lane + 32 * k;
-      if (i < n) { const float gg = gr[i], d = xr[i] - mean, q = gg * gamma[i]; sg += q; sgx += q * d; pg[k] += gg * (d / sd); pb[k] += gg; }
-    }
-    sg = warp_sum(sg); sgx = warp_sum(sgx);
-#pragma unroll
-    for (int k = 0; k < LN_MAXC; k++) {
-      const int i = lane + 32 * k;
-      if (i < n) { const float q = gr[i] * gamma[i], d = xr[i] - mean; float v = (q - sg / fn) / sd; v -= (d * sgx) / (fn * sd * sd); dr[i] = v; }
-    }
-  }
-#pragma unroll
-  for (int k = 0; k < LN_MAXC; k++) { const int i = lane + 32 * k; if (i < n) { part[(gw * 2) * n + i] = pg[k]; part[(gw * 2 + 1) * n + i] = pb[k]; } }
-}
 // gGamma[c] += sum_r g*(x-mean)/std ; gBeta[c] += sum_r g     (layernorm.go:421-433)
 __global__ void layernorm_pgrad_partial_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ mean_in,
                                                const float* __restrict__ std_in, long rows, int n, float* __restrict__ part) {
