@@ -29,6 +29,7 @@ struct NcclApi;   // resolved at run time from libnccl.so.2 (nccl_dl.cuh)
 struct Ctx {
   int device = 0;
   cudaStream_t stream = nullptr;
+  cudaStream_t comm_stream = nullptr;   // gradient all-reduces run here, overlapped with the rest of the backward pass
   int rank = 0, world = 1;
   void* comm = nullptr;            // ncclComm_t
   NcclApi* nccl = nullptr;

@@ -108,7 +108,8 @@ struct gn_model {
   std::vector<gn::DevBuf> scratch;      // growable shared scratch, by slot
   float last_inv_batch = 1.f;
   gn_step_stats stats{};
-  cudaEvent_t ev0 = nullptr, ev1 = nullptr, ar0 = nullptr, ar1 = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr, ar0 = nullptr, ar1 = nullptr, comm_done = nullptr;
+  std::vector<cudaEvent_t> layer_ev;    // gradient of layer i complete (multi-GPU: releases its all-reduce)
   bool alive = true;
   bool has_lstm = false;
 };
@@ -379,7 +380,7 @@ static int layernorm_backward(gn_model* m, const float* g, const float* x, const
 //   gb = sum over all tokens of dz ; gW = Delta^T * X_last with Delta[s] = sum_t dz[s,t], X_last[s] = x[s,T-1]
 static int inner_dense_param_grads(gn_model* m, const float* dz, int B, int T, int out, const float* x, int in, float* gW, float* gb) {
   Ctx* ctx = &m->ctx->c; float* delta; GN_TRY(ensure(m, S_DELTA, (size_t)B * out, &delta));
-  GN_LAUNCH(ctx, token_sum_kernel, dim3(cdiv(out, 128), B), 128, 0, dz, T, out, delta);
+  GN_LAUNCH(ctx, token_sum_kernel, dim3(cdiv(out, 128), B), dim3(128, 4), 0, dz, T, out, delta);
   GN_TRY(colsum(m, delta, out, B, out, gb, false));
   return gemm_tn(ctx, B, out, in, delta, out, x + (long)(T - 1) * in, (long)T * in, gW);
 }
@@ -535,6 +536,13 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         g = dx; flip ^= 1; break; }
     }
     GN_TRY(check_launch("backward"));
+    if (ctx->world > 1 && l.p_cnt > 0) {
+      // this layer's slice of the flat gradient buffer is final: sum it over the ranks while earlier layers still compute
+      GN_CUDA(cudaEventRecord(m->layer_ev[li], ctx->stream));
+      GN_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->layer_ev[li], 0));
+      int rc = ctx->nccl->AllReduce(gr, gr, (size_t)l.p_cnt, NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->comm_stream);
+      if (rc) return fail(GN_ERR_NCCL, "ncclAllReduce(grads of layer %d): %s", li, ctx->nccl->GetErrorString(rc));
+    }
   }
   return GN_OK;
 }
@@ -565,11 +573,15 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
   GN_LAUNCH(ctx, loss_total_kernel, 1, 32, 0, m->loss_s.p, B, m->loss_sum.p);
   GN_TRY(backward(m, x_dev, B, m->lossg.p, global_batch, first_sample));
   if (ctx->world > 1) {
-    GN_CUDA(cudaEventRecord(m->ar0, ctx->stream));
-    int rc = ctx->nccl->AllReduce(m->grads.p, m->grads.p, (size_t)m->P, NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->stream);
-    if (rc) return fail(GN_ERR_NCCL, "ncclAllReduce(grads): %s", ctx->nccl->GetErrorString(rc));
-    rc = ctx->nccl->AllReduce(m->loss_sum.p, m->loss_sum.p, 1, NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->stream);
+    // loss sum over the ranks, then the main stream waits for the communication stream (per-layer gradient
+    // all-reduces were issued during the backward pass); ar0..ar1 brackets the exposed wait
+    GN_CUDA(cudaEventRecord(m->layer_ev.back(), ctx->stream));
+    GN_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->layer_ev.back(), 0));
+    int rc = ctx->nccl->AllReduce(m->loss_sum.p, m->loss_sum.p, 1, NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->comm_stream);
     if (rc) return fail(GN_ERR_NCCL, "ncclAllReduce(loss): %s", ctx->nccl->GetErrorString(rc));
+    GN_CUDA(cudaEventRecord(m->comm_done, ctx->comm_stream));
+    GN_CUDA(cudaEventRecord(m->ar0, ctx->stream));
+    GN_CUDA(cudaStreamWaitEvent(ctx->stream, m->comm_done, 0));
     GN_CUDA(cudaEventRecord(m->ar1, ctx->stream));
   }
   // Network.Step (net.go:260-284): NewStep() then StepInPlace with t = timestep + 1
@@ -611,6 +623,7 @@ static int make_ctx(int device, int rank, int world, const unsigned char* id, gn
     int rc = api->CommInitRank(&c->c.comm, world, uid, rank);
     if (rc) return fail(GN_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString(rc));
     c->c.nccl = api;
+    GN_CUDA(cudaStreamCreateWithFlags(&c->c.comm_stream, cudaStreamNonBlocking));
   }
   *out = c.release(); return GN_OK;
 }
@@ -645,12 +658,15 @@ int gn_shutdown(gn_ctx* ctx) {
   if (!ctx || !ctx->alive) return GN_OK;
   cudaSetDevice(ctx->c.device);
   if (ctx->c.stream) cudaStreamSynchronize(ctx->c.stream);
+  if (ctx->c.comm_stream) { cudaStreamSynchronize(ctx->c.comm_stream); }
   if (ctx->c.comm && ctx->c.nccl) ctx->c.nccl->CommDestroy(ctx->c.comm);
   for (auto& e : ctx->c.ev_pool) { cudaEventDestroy(e.first); cudaEventDestroy(e.second); }
   ctx->c.ev_pool.clear();
   if (ctx->c.d_status) cudaFree(ctx->c.d_status);
   if (ctx->c.t0) { cudaEventDestroy(ctx->c.t0); cudaEventDestroy(ctx->c.t1); ctx->c.t0 = ctx->c.t1 = nullptr; }
   if (ctx->c.stream) cudaStreamDestroy(ctx->c.stream);
+  if (ctx->c.comm_stream) cudaStreamDestroy(ctx->c.comm_stream);
+  ctx->c.comm_stream = nullptr;
   ctx->c.comm = nullptr; ctx->c.d_status = nullptr; ctx->c.stream = nullptr; ctx->alive = false;
   return GN_OK;   // the handle itself stays allocated so that a second call is harmless
 }
@@ -696,6 +712,9 @@ int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int 
     GN_CUDA(cudaMemcpy(m->state.p, init.data(), (size_t)m->NS * 4, cudaMemcpyHostToDevice));
   }
   GN_CUDA(cudaEventCreate(&m->ev0)); GN_CUDA(cudaEventCreate(&m->ev1)); GN_CUDA(cudaEventCreate(&m->ar0)); GN_CUDA(cudaEventCreate(&m->ar1));
+  GN_CUDA(cudaEventCreateWithFlags(&m->comm_done, cudaEventDisableTiming));
+  m->layer_ev.resize(m->L.size() + 1);
+  for (auto& e : m->layer_ev) GN_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   m->scratch.resize(S_COUNT);
   *out = m.release(); return GN_OK;
 }
@@ -708,7 +727,8 @@ int gn_model_destroy(gn_model* m) {
   m->L.clear(); m->scratch.clear(); m->state.release(); m->params.release(); m->grads.release(); m->m1.release(); m->v2.release();
   m->xin.release(); m->yin.release(); m->lossg.release(); m->loss_s.release(); m->loss_sum.release();
   if (m->ev0) cudaEventDestroy(m->ev0); if (m->ev1) cudaEventDestroy(m->ev1); if (m->ar0) cudaEventDestroy(m->ar0); if (m->ar1) cudaEventDestroy(m->ar1);
-  m->ev0 = m->ev1 = m->ar0 = m->ar1 = nullptr; m->alive = false; return GN_OK;
+  if (m->comm_done) cudaEventDestroy(m->comm_done); for (auto e : m->layer_ev) cudaEventDestroy(e); m->layer_ev.clear();
+  m->ev0 = m->ev1 = m->ar0 = m->ar1 = m->comm_done = nullptr; m->alive = false; return GN_OK;
 }
 
 int gn_model_param_count(gn_model* m, int64_t* n) { CHECK_MODEL(m); if (!n) return fail(GN_ERR_INVALID_ARG, "n is null"); *n = m->P; return GN_OK; }

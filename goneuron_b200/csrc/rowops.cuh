@@ -107,11 +107,22 @@ __global__ void colsum_final_kernel(const float* __restrict__ part, int chunks, 
 }
 // delta[s, c] = sum_t in[s, t, c]   ([B,T,C] -> [B,C]); the reference adds per-token terms one token after another.
 __global__ void token_sum_kernel(const float* __restrict__ in, int T, int C, float* __restrict__ out) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= C) return;
-  const float* p = in + (long)blockIdx.y * T * C + c;
+  // block = 128 columns x 4 groups of tokens; each group adds every 4th token, four loads in flight per thread
+  __shared__ float part[4][128];
+  const int c = blockIdx.x * 128 + threadIdx.x, grp = threadIdx.y;
   float s = 0.f;
-  for (int t = 0; t < T; t++) s += p[(long)t * C];
-  out[(long)blockIdx.y * C + c] = s;
+  if (c < C) {
+    const float* p = in + (long)blockIdx.y * T * C + c;
+    int t = grp;
+    for (; t + 12 < T; t += 16) {
+      float a0 = p[(long)t * C], a1 = p[(long)(t + 4) * C], a2 = p[(long)(t + 8) * C], a3 = p[(long)(t + 12) * C];
+      s += (a0 + a1) + (a2 + a3);
+    }
+    for (; t < T; t += 4) s += p[(long)t * C];
+  }
+  part[grp][threadIdx.x] = s;
+  __syncthreads();
+  if (grp == 0 && c < C) out[(long)blockIdx.y * C + c] = (part[0][threadIdx.x] + part[1][threadIdx.x]) + (part[2][threadIdx.x] + part[3][threadIdx.x]);
 }
 
 // ---------------------------------------------------------------- LayerNorm

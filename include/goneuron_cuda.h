@@ -179,8 +179,9 @@ int gn_model_get_state(gn_model* m, float* host, int64_t n);
 int gn_model_set_state(gn_model* m, const float* host, int64_t n);
 
 /* Counters of the last gn_train_batch: kernels launched by this library, and
- * device time in ms of the whole step / of the gradient all-reduce (CUDA events
- * on the context's stream). */
+ * device time in ms of the whole step / of the part of the gradient all-reduce that
+ * the compute stream had to wait for (the per-layer all-reduces run on a second
+ * stream under the rest of the backward pass); CUDA events on the context's stream. */
 typedef struct gn_step_stats {
   int64_t kernel_launches;
   float step_ms;
