@@ -57,6 +57,16 @@ inline int check_launch(const char* what) {
   return GN_OK;
 }
 
+// Host <-> device copies always go through the context's own stream and wait for it.  (The synchronous cudaMemcpy /
+// cudaMemset run on the legacy default stream, which a non-blocking stream does not wait for, and may return before
+// the transfer has landed: work issued that way can overtake, or be overtaken by, kernels of the context's stream.)
+inline cudaError_t copy_h2d(Ctx* c, void* dst, const void* src, size_t bytes) {
+  cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->stream); return e != cudaSuccess ? e : cudaStreamSynchronize(c->stream);
+}
+inline cudaError_t copy_d2h(Ctx* c, void* dst, const void* src, size_t bytes) {
+  cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream); return e != cudaSuccess ? e : cudaStreamSynchronize(c->stream);
+}
+
 // Owning device buffer.
 struct DevBuf {
   float* p = nullptr; size_t n = 0;

@@ -250,4 +250,124 @@ __global__ void __launch_bounds__(SCAN_THREADS) lstm_grad_scan_kernel(
   cluster.sync();
 }
 
+
+// ---------------------------------------------------------------- the same recurrence through Gram matrices
+// Every update is rank one, u_k = d_k (x) z_k, so the gradient after any number of clipped updates is a weighted sum
+// g = sum_j w_j u_j, and the only thing the clipping needs is the norm:
+//     |g + u_k|^2 = |g|^2 + 2 <g, u_k> + |u_k|^2,   <u_j, u_k> = <d_j, d_k> <z_j, z_k> =: G[j,k].
+// With f_k the clip factor of update k and S_k = f_0 ... f_k, the coefficient of u_j after update k is S_k / S_{j-1},
+// hence <g_{k-1}, u_k> = S_{k-1} sum_{j<k} G[j,k] / S_{j-1}.  The two Gram products and the final g = (diag(w) D)^T Z
+// are contractions (tensor cores); what stays sequential is one dot product of length k per update.
+//
+// Rows of Dm [n, 4H] and Zm [n, in+H+1] in update order: chunk by chunk, samples ascending, time descending.
+__global__ void lstm_gather_updates_kernel(const float* __restrict__ D, const float* __restrict__ x, const float* __restrict__ h_all,
+                                           float* __restrict__ Dm, float* __restrict__ Zm, int T, int in, int H, long n_updates) {
+  const int R4 = 4 * H, ZW = in + H + 1;
+  const long k = blockIdx.x; if (k >= n_updates) return;
+  const int s = (int)(k / T), t = T - 1 - (int)(k % T);
+  for (int e = threadIdx.x; e < R4 + ZW; e += blockDim.x) {
+    if (e < R4) Dm[k * R4 + e] = D[((long)s * T + t) * R4 + e];
+    else {
+      const int c = e - R4; float v;
+      if (c < in) v = x[(long)s * T * in + (long)(T - 1) * in + c];                 // input of the LAST forward call (lstm.go:592-621)
+      else if (c < in + H) v = t > 0 ? h_all[((long)s * T + (t - 1)) * H + (c - in)] : 0.f;
+      else v = 1.f;
+      Zm[k * ZW + c] = v;
+    }
+  }
+}
+// G <- G (.) G2 on the lower triangles (row k, columns j <= k) of `nb` matrices of size Kc x Kc
+__global__ void lstm_gram_mul_kernel(float* __restrict__ G, const float* __restrict__ G2, int Kc, long total) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int j = (int)(i % Kc), k = (int)((i / Kc) % Kc);
+    if (j <= k) G[i] *= G2[i];
+  }
+}
+// One block per worker chunk walks its updates in groups of GRAM_BS; w[j] = final coefficient of update j.
+// For a group starting at k0 the part of every dot product that involves EARLIER groups,
+//     v[r] = sum_{j<k0} t[j] G[k0+r, j],
+// does not depend on the group's own clip factors, so all threads compute it at once (a [GRAM_BS x k0] matrix-vector
+// product, coalesced rows of G); only the GRAM_BS x GRAM_BS diagonal block is walked sequentially, by one warp, from
+// shared memory.  t[j] = 1 / S_{j-1} relative to a reference that is re-based before the running product of clip
+// factors S underflows; the norm recurrence and S are kept in double.
+constexpr int GRAM_THREADS = 1024, GRAM_BS = 64, GRAM_MAX_K = 49152;
+__global__ void __launch_bounds__(GRAM_THREADS) lstm_gram_scan_kernel(const float* __restrict__ G, int Kc, long n_total, float* __restrict__ w) {
+  extern __shared__ float tco[];                     // [Kc]
+  __shared__ float Gd[GRAM_BS][GRAM_BS + 1];
+  __shared__ double v[GRAM_BS];
+  __shared__ double red8[8][GRAM_THREADS / 32];
+  __shared__ double state[2];                        // S, n2
+  const int chunk = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const long first = (long)chunk * Kc; const int n = (int)max(0L, min((long)Kc, n_total - first));
+  const float* Gc = G + (long)chunk * Kc * Kc;
+  if (tid == 0) { state[0] = 1.0; state[1] = 0.0; }
+  __syncthreads();
+  for (int k0 = 0; k0 < n; k0 += GRAM_BS) {
+    const int nb = min(GRAM_BS, n - k0);
+    // phase 1: contributions of earlier groups.  Thread (warp, lane) owns columns j = tid, tid + 1024, ... of ALL rows of
+    // the group, eight rows at a time, so that many independent loads are in flight; products are summed in fp32 per
+    // thread (at most k0 / 1024 terms) and across threads in double.
+    for (int r0 = 0; r0 < nb; r0 += 8) {
+      float acc[8];
+#pragma unroll
+      for (int q = 0; q < 8; q++) acc[q] = 0.f;
+      for (int j = tid; j < k0; j += GRAM_THREADS) {
+        const float tj = tco[j];
+#pragma unroll
+        for (int q = 0; q < 8; q++) if (r0 + q < nb) acc[q] = fmaf(tj, Gc[(long)(k0 + r0 + q) * Kc + j], acc[q]);
+      }
+#pragma unroll
+      for (int q = 0; q < 8; q++) {
+        double a = (double)acc[q];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0) red8[q][warp] = a;
+      }
+      __syncthreads();
+      if (tid < 8 && r0 + tid < nb) { double a = 0.0; for (int q = 0; q < GRAM_THREADS / 32; q++) a += red8[tid][q]; v[r0 + tid] = a; }
+      __syncthreads();
+    }
+    for (int e = tid; e < nb * GRAM_BS; e += GRAM_THREADS) { const int r = e / GRAM_BS, c = e % GRAM_BS; if (c <= r) Gd[r][c] = Gc[(long)(k0 + r) * Kc + k0 + c]; }   // diagonal block
+    __syncthreads();
+    // phase 2: the group's own updates, sequential, one warp
+    if (warp == 0) {
+      double S = state[0], n2 = state[1];
+      for (int r = 0; r < nb; r++) {
+        float p = 0.f;
+        if (lane < r) p = tco[k0 + lane] * Gd[r][lane];
+        if (lane + 32 < r) p = fmaf(tco[k0 + lane + 32], Gd[r][lane + 32], p);
+        p = warp_sum(p);
+        const double dot = v[r] + (double)p;
+        const double np = n2 + 2.0 * S * dot + (double)Gd[r][r];
+        if (lane == 0) tco[k0 + r] = (float)(1.0 / S);
+        if (np > 1.0) { S *= 1.0 / sqrt(np); n2 = 1.0; } else n2 = np;       // clip to norm 1 (lstm.go:738-750)
+        if (S < 1e-12) {                                                      // re-base: stored coefficients and pending sums scale with S
+          __syncwarp();
+          const float fs = (float)S;
+          for (int j = lane; j <= k0 + r; j += 32) tco[j] *= fs;
+          for (int q = r + 1 + lane; q < nb; q += 32) v[q] *= S;
+          S = 1.0;
+        }
+        __syncwarp();
+      }
+      if (lane == 0) { state[0] = S; state[1] = n2; }
+    }
+    __syncthreads();
+  }
+  const double S = state[0];
+  for (int j = tid; j < n; j += GRAM_THREADS) w[first + j] = (float)(S * (double)tco[j]);
+}
+__global__ void lstm_scale_rows_kernel(float* __restrict__ Dm, const float* __restrict__ w, int R4, long total) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) Dm[i] *= w[i / R4];
+}
+// chunk results [nchunks][4H][in+H+1] -> flat layout gWx[4H,in] | gWh[4H,H] | gb[4H], chunks added in worker order
+__global__ void lstm_scatter_grad_kernel(const float* __restrict__ Gc, int nchunks, int in, int H, float* __restrict__ out) {
+  const int R4 = 4 * H, ZW = in + H + 1; const long total = (long)R4 * ZW;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / ZW), c = (int)(i % ZW);
+    float v = 0.f; for (int q = 0; q < nchunks; q++) v += Gc[(long)q * total + i];
+    if (c < in) out[(long)r * in + c] = v; else if (c < in + H) out[(long)R4 * in + (long)r * H + (c - in)] = v; else out[(long)R4 * in + (long)R4 * H + r] = v;
+  }
+}
+
 }  // namespace gn

@@ -65,7 +65,7 @@ extern "C" int gn_op_gemm_nt_static(gn_ctx* ctx, int M, int N, int K, const floa
   TcParams ep{C_dev, (long)N, 0, 0, bias_dev, nullptr, 0, 0, 0, GN_ACT_LINEAR, M, N, K, 1, 0, c->d_status, nullptr, 0, 1, nullptr, nullptr, 0};
   GN_TRY(tc_launch(c, PA, PB, ep));
   GN_CUDA(cudaStreamSynchronize(c->stream));
-  int st = 0; GN_CUDA(cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost));
-  if (st != 0) { cudaMemset(c->d_status, 0, sizeof(int)); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
+  int st = 0; GN_CUDA(copy_d2h(c, &st, c->d_status, sizeof(int)));
+  if (st != 0) { cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream); cudaStreamSynchronize(c->stream); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
   return GN_OK;
 }

@@ -116,7 +116,7 @@ struct gn_model {
 
 namespace gn {
 
-enum Slot { S_PL_HI = 0, S_PL_LO, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+enum Slot { S_PL_HI = 0, S_PL_LO, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
 
 static int ensure(gn_model* m, int slot, size_t n, float** out) {
   if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
@@ -454,6 +454,37 @@ static int lstm_backward(gn_model* m, LayerRT& l, size_t li, int B, const float*
   if (m->ctx->c.world > 1) return fail(GN_ERR_UNSUPPORTED, "LSTM gradient scan is single-GPU in this build");
   (void)first_sample;
   int chunk = (global_batch + m->W - 1) / m->W, nchunks = (B + chunk - 1) / chunk;
+  {
+    // Gram-matrix form of the clipping recurrence (conv_lstm.cuh): the default whenever its matrices fit.  The
+    // cluster kernel below runs only for chunks too long for it, or when GONEURON_CUDA_LSTM_SCAN=cluster asks for it.
+    static const int mode = [] { const char* e = getenv("GONEURON_CUDA_LSTM_SCAN"); return !e ? 0 : (strcmp(e, "cluster") == 0 ? 1 : (strcmp(e, "gram") == 0 ? 2 : 0)); }();
+    const long Kc = (long)chunk * T, n_updates = (long)B * T; const int R4g = 4 * H, ZWg = in + H + 1;
+    const bool fits = Kc <= GRAM_MAX_K && (double)nchunks * Kc * Kc * 8 <= 8.0e9;
+    if (mode != 1 && fits) {
+      float *G0, *G1, *Dm, *Zm, *wv, *res;
+      GN_TRY(ensure(m, S_GRAM0, (size_t)nchunks * Kc * Kc, &G0)); GN_TRY(ensure(m, S_GRAM1, (size_t)nchunks * Kc * Kc, &G1));
+      GN_TRY(ensure(m, S_DM, (size_t)nchunks * Kc * R4g, &Dm)); GN_TRY(ensure(m, S_ZM, (size_t)nchunks * Kc * ZWg, &Zm));
+      GN_TRY(ensure(m, S_W, (size_t)nchunks * Kc, &wv)); GN_TRY(ensure(m, S_SCAN, (size_t)nchunks * R4g * ZWg, &res));
+      if ((long)nchunks * Kc > n_updates) {     // the last chunk is short: its unused rows must be zero for the final contraction
+        GN_CUDA(cudaMemsetAsync(Dm, 0, (size_t)nchunks * Kc * R4g * 4, ctx->stream)); GN_CUDA(cudaMemsetAsync(Zm, 0, (size_t)nchunks * Kc * ZWg * 4, ctx->stream));
+        GN_CUDA(cudaMemsetAsync(wv, 0, (size_t)nchunks * Kc * 4, ctx->stream));
+      }
+      GN_LAUNCH(ctx, lstm_gather_updates_kernel, (unsigned)n_updates, 128, 0, (const float*)l.dgate.p, xin, (const float*)l.h_all.p, Dm, Zm, T, in, H, n_updates);
+      GemmDesc g; g.M = (int)Kc; g.N = (int)Kc; g.batch1 = nchunks; g.c_b1 = Kc * Kc; g.ldc = Kc; g.flags = GEMM_SKIP_UPPER;
+      g.K = R4g; g.A = Dm; g.sa_m = R4g; g.sa_k = 1; g.B = Dm; g.sb_k = 1; g.sb_n = R4g; g.a_b1 = g.b_b1 = Kc * R4g; g.C = G0; GN_TRY(gemm(ctx, g));
+      g.K = ZWg; g.A = Zm; g.sa_m = ZWg; g.B = Zm; g.sb_n = ZWg; g.a_b1 = g.b_b1 = Kc * ZWg; g.C = G1; GN_TRY(gemm(ctx, g));
+      const long tot = (long)nchunks * Kc * Kc;
+      GN_LAUNCH(ctx, lstm_gram_mul_kernel, ew_grid(ctx, tot), 256, 0, G0, (const float*)G1, (int)Kc, tot);
+      GN_CUDA(cudaFuncSetAttribute(lstm_gram_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(Kc * sizeof(float))));
+      GN_LAUNCH(ctx, lstm_gram_scan_kernel, nchunks, GRAM_THREADS, (size_t)Kc * sizeof(float), (const float*)G0, (int)Kc, n_updates, wv);
+      const long dtot = (long)nchunks * Kc * R4g;
+      GN_LAUNCH(ctx, lstm_scale_rows_kernel, ew_grid(ctx, dtot), 256, 0, Dm, (const float*)wv, R4g, dtot);
+      GemmDesc f; f.M = R4g; f.N = ZWg; f.K = (int)Kc; f.batch1 = nchunks; f.A = Dm; f.sa_m = 1; f.sa_k = R4g; f.a_b1 = Kc * R4g;
+      f.B = Zm; f.sb_k = ZWg; f.sb_n = 1; f.b_b1 = Kc * ZWg; f.C = res; f.ldc = ZWg; f.c_b1 = (long)R4g * ZWg; GN_TRY(gemm(ctx, f));
+      GN_LAUNCH(ctx, lstm_scatter_grad_kernel, cdiv((long)R4g * ZWg, 256), 256, 0, (const float*)res, nchunks, in, H, m->grads.p + l.p_off);
+      return check_launch("lstm_backward(gram)");
+    }
+  }
   const int R4 = 4 * H, ZW = in + H + 1, rpc = (R4 + SCAN_CLUSTER - 1) / SCAN_CLUSTER;
   size_t smem = ((size_t)rpc * ZW + rpc + ZW + 33) * sizeof(float);
   if (smem > 220 * 1024) return fail(GN_ERR_UNSUPPORTED, "LSTM gradient of %d x %d per cluster CTA exceeds shared memory", rpc, ZW);
@@ -599,8 +630,8 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
   m->stats.allreduce_ms = 0.f; if (ctx->world > 1) cudaEventElapsedTime(&m->stats.allreduce_ms, m->ar0, m->ar1);
   m->stats.gemm_flops = ctx->gemm_flops; m->stats.gemm_launches = ctx->gemm_launches; m->stats.gemm_ms = 0.f;
   if (ctx->profile) { float tot = 0.f; for (size_t i = 0; i < ctx->ev_used; i++) { float ms = 0.f; cudaEventElapsedTime(&ms, ctx->ev_pool[i].first, ctx->ev_pool[i].second); tot += ms; } m->stats.gemm_ms = tot; }
-  int st = 0; GN_CUDA(cudaMemcpy(&st, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
-  if (st != 0) { cudaMemset(ctx->d_status, 0, sizeof(int)); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
+  int st = 0; GN_CUDA(copy_d2h(ctx, &st, ctx->d_status, sizeof(int)));
+  if (st != 0) { cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream); cudaStreamSynchronize(ctx->stream); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
   return GN_OK;
 }
 
@@ -615,7 +646,8 @@ static int make_ctx(int device, int rank, int world, const unsigned char* id, gn
   std::unique_ptr<gn_ctx> c(new gn_ctx());
   c->c.device = device; c->c.rank = rank; c->c.world = world; c->c.sm_count = prop.multiProcessorCount;
   GN_CUDA(cudaStreamCreateWithFlags(&c->c.stream, cudaStreamNonBlocking));
-  GN_CUDA(cudaMalloc(&c->c.d_status, sizeof(int))); GN_CUDA(cudaMemset(c->c.d_status, 0, sizeof(int)));
+  GN_CUDA(cudaMalloc(&c->c.d_status, sizeof(int)));
+  GN_CUDA(cudaMemsetAsync(c->c.d_status, 0, sizeof(int), c->c.stream)); GN_CUDA(cudaStreamSynchronize(c->c.stream));
   tc_init(&c->c);
   if (world > 1) {
     NcclApi* api = nccl_api(); if (!api) return fail(GN_ERR_NCCL, "libnccl.so.2 could not be loaded");
@@ -704,12 +736,20 @@ int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int 
   GN_TRY(plan_layers(m.get(), layers, n_layers));
   size_t P = (size_t)std::max<int64_t>(m->P, 4);
   GN_TRY(m->params.alloc(P)); GN_TRY(m->grads.alloc(P)); GN_TRY(m->m1.alloc(P)); GN_TRY(m->v2.alloc(P));
-  GN_CUDA(cudaMemset(m->params.p, 0, P * 4)); GN_CUDA(cudaMemset(m->grads.p, 0, P * 4)); GN_CUDA(cudaMemset(m->m1.p, 0, P * 4)); GN_CUDA(cudaMemset(m->v2.p, 0, P * 4));
+  // cudaMemset is asynchronous to the host and runs on the legacy default stream, which the context's non-blocking
+  // stream does not wait for: a memset issued that way can land AFTER the first training step has written its
+  // gradients (seen as all-zero LSTM gradients after the GPU had been idle).  So: the context's own stream, then wait.
+  {
+    cudaStream_t st = ctx->c.stream;
+    GN_CUDA(cudaMemsetAsync(m->params.p, 0, P * 4, st)); GN_CUDA(cudaMemsetAsync(m->grads.p, 0, P * 4, st));
+    GN_CUDA(cudaMemsetAsync(m->m1.p, 0, P * 4, st)); GN_CUDA(cudaMemsetAsync(m->v2.p, 0, P * 4, st));
+    GN_CUDA(cudaStreamSynchronize(st));
+  }
   if (m->NS > 0) {
     GN_TRY(m->state.alloc((size_t)m->NS));
     std::vector<float> init((size_t)m->NS, 0.f);     // running mean 0, running variance 1 (batchnorm2d.go:124-128)
     for (auto& l : m->L) if (l.d.kind == GN_LAYER_BATCHNORM2D) for (int64_t k = l.s_cnt / 2; k < l.s_cnt; k++) init[l.s_off + k] = 1.f;
-    GN_CUDA(cudaMemcpy(m->state.p, init.data(), (size_t)m->NS * 4, cudaMemcpyHostToDevice));
+    GN_CUDA(copy_h2d(&ctx->c, m->state.p, init.data(), (size_t)m->NS * 4));
   }
   GN_CUDA(cudaEventCreate(&m->ev0)); GN_CUDA(cudaEventCreate(&m->ev1)); GN_CUDA(cudaEventCreate(&m->ar0)); GN_CUDA(cudaEventCreate(&m->ar1));
   GN_CUDA(cudaEventCreateWithFlags(&m->comm_done, cudaEventDisableTiming));
@@ -764,13 +804,13 @@ int gn_model_get_state(gn_model* m, float* host, int64_t n) {
   CHECK_MODEL(m); if (n != m->NS || (n > 0 && !host)) return fail(GN_ERR_INVALID_ARG, "get_state: expected %lld floats, got %lld", (long long)m->NS, (long long)n);
   if (n == 0) return GN_OK;
   std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
-  GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); GN_CUDA(cudaMemcpy(host, m->state.p, (size_t)n * 4, cudaMemcpyDeviceToHost)); return GN_OK;
+  GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); GN_CUDA(copy_d2h(&m->ctx->c, host, m->state.p, (size_t)n * 4)); return GN_OK;
 }
 int gn_model_set_state(gn_model* m, const float* host, int64_t n) {
   CHECK_MODEL(m); if (n != m->NS || (n > 0 && !host)) return fail(GN_ERR_INVALID_ARG, "set_state: expected %lld floats, got %lld", (long long)m->NS, (long long)n);
   if (n == 0) return GN_OK;
   std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
-  GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); GN_CUDA(cudaMemcpy(m->state.p, host, (size_t)n * 4, cudaMemcpyHostToDevice)); return GN_OK;
+  GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); GN_CUDA(copy_h2d(&m->ctx->c, m->state.p, host, (size_t)n * 4)); return GN_OK;
 }
 
 int gn_adam_set(gn_model* m, float lr, float beta1, float beta2, float eps, int timestep) {
@@ -782,14 +822,14 @@ int gn_adam_set(gn_model* m, float lr, float beta1, float beta2, float eps, int 
 int gn_adam_get_state(gn_model* m, float* m1, float* v, int64_t n, int* timestep) {
   CHECK_MODEL(m); if (n != m->P) return fail(GN_ERR_INVALID_ARG, "adam state: expected %lld floats", (long long)m->P);
   std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
-  if (m1) GN_CUDA(cudaMemcpy(m1, m->m1.p, (size_t)n * 4, cudaMemcpyDeviceToHost));
-  if (v) GN_CUDA(cudaMemcpy(v, m->v2.p, (size_t)n * 4, cudaMemcpyDeviceToHost));
+  if (m1) GN_CUDA(copy_d2h(&m->ctx->c, m1, m->m1.p, (size_t)n * 4));
+  if (v) GN_CUDA(copy_d2h(&m->ctx->c, v, m->v2.p, (size_t)n * 4));
   if (timestep) *timestep = m->timestep; return GN_OK;
 }
 int gn_adam_set_state(gn_model* m, const float* m1, const float* v, int64_t n, int timestep) {
   CHECK_MODEL(m); if (n != m->P || !m1 || !v) return fail(GN_ERR_INVALID_ARG, "adam state: expected %lld floats", (long long)m->P);
   std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
-  GN_CUDA(cudaMemcpy(m->m1.p, m1, (size_t)n * 4, cudaMemcpyHostToDevice)); GN_CUDA(cudaMemcpy(m->v2.p, v, (size_t)n * 4, cudaMemcpyHostToDevice));
+  GN_CUDA(copy_h2d(&m->ctx->c, m->m1.p, m1, (size_t)n * 4)); GN_CUDA(copy_h2d(&m->ctx->c, m->v2.p, v, (size_t)n * 4));
   if (timestep >= 0) m->timestep = timestep; return GN_OK;
 }
 
@@ -848,8 +888,8 @@ int gn_op_gemm_nt(gn_ctx* ctx, int engine, int M, int N, int K, const float* A, 
   if (engine == 1) { if (!gemm_tc_supported(c, g)) return fail(GN_ERR_UNSUPPORTED, "tcgen05 engine cannot run this shape (M=%d N=%d K=%d)", M, N, K); GN_TRY(gemm_tc(c, g)); }
   else GN_TRY(gemm_simt(c, g));
   GN_CUDA(cudaMemcpyAsync(C, dC.p, (size_t)M * N * 4, cudaMemcpyDeviceToHost, c->stream)); GN_CUDA(cudaStreamSynchronize(c->stream));
-  int st = 0; GN_CUDA(cudaMemcpy(&st, c->d_status, sizeof(int), cudaMemcpyDeviceToHost));
-  if (st != 0) { cudaMemset(c->d_status, 0, sizeof(int)); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
+  int st = 0; GN_CUDA(copy_d2h(c, &st, c->d_status, sizeof(int)));
+  if (st != 0) { cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream); cudaStreamSynchronize(c->stream); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
   return GN_OK;
 }
 
@@ -857,11 +897,11 @@ int gn_op_adam(gn_ctx* ctx, float* params, const float* grads, float* m1, float*
   if (!ctx || !ctx->alive || !params || !grads || !m1 || !v || n <= 0) return fail(GN_ERR_INVALID_ARG, "op_adam: bad argument");
   Ctx* c = &ctx->c; GN_CUDA(cudaSetDevice(c->device));
   DevBuf dp, dg, dm, dv; size_t nn = (size_t)n; GN_TRY(dp.alloc(nn + 4)); GN_TRY(dg.alloc(nn + 4)); GN_TRY(dm.alloc(nn + 4)); GN_TRY(dv.alloc(nn + 4));
-  GN_CUDA(cudaMemcpy(dp.p, params, nn * 4, cudaMemcpyHostToDevice)); GN_CUDA(cudaMemcpy(dg.p, grads, nn * 4, cudaMemcpyHostToDevice));
-  GN_CUDA(cudaMemcpy(dm.p, m1, nn * 4, cudaMemcpyHostToDevice)); GN_CUDA(cudaMemcpy(dv.p, v, nn * 4, cudaMemcpyHostToDevice));
+  GN_CUDA(copy_h2d(c, dp.p, params, nn * 4)); GN_CUDA(copy_h2d(c, dg.p, grads, nn * 4));
+  GN_CUDA(copy_h2d(c, dm.p, m1, nn * 4)); GN_CUDA(copy_h2d(c, dv.p, v, nn * 4));
   GN_TRY(adam_launch(c, dp.p, dg.p, dm.p, dv.p, n, lr, beta1, beta2, eps, t, grad_scale));
   GN_CUDA(cudaStreamSynchronize(c->stream));
-  GN_CUDA(cudaMemcpy(params, dp.p, nn * 4, cudaMemcpyDeviceToHost)); GN_CUDA(cudaMemcpy(m1, dm.p, nn * 4, cudaMemcpyDeviceToHost)); GN_CUDA(cudaMemcpy(v, dv.p, nn * 4, cudaMemcpyDeviceToHost));
+  GN_CUDA(copy_d2h(c, params, dp.p, nn * 4)); GN_CUDA(copy_d2h(c, m1, dm.p, nn * 4)); GN_CUDA(copy_d2h(c, v, dv.p, nn * 4));
   return GN_OK;
 }
 

@@ -187,3 +187,18 @@ def test_batchnorm_running_statistics_and_inference(device, oracle):
     model.SetParams(ref.params); model.SetState(ref.state)
     assert norm_err(model.PredictBatch(x[:5]), ref.forward_batch(x[:5], precision=64)) <= TOL
     model.Close()
+
+
+@pytest.mark.parametrize("mode", ["gram", "cluster"])
+def test_lstm_scan_variants_in_subprocess(mode):
+    """The LSTM gradient-clipping recurrence has two implementations: a thread-block-cluster kernel that applies
+    the updates one by one, and the Gram-matrix form used when a worker chunk has many updates.  The switch
+    GONEURON_CUDA_LSTM_SCAN forces one of them for every size; both must give the same parity."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, GONEURON_CUDA_LSTM_SCAN=mode)
+    r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_parity.py"), "-q", "-x", "-m", "gpu", "-k", "lstm-5 or lstm-6 or lstm-7"],
+                       env=env, cwd=root, capture_output=True, text=True)
+    assert r.returncode == 0 and " passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
