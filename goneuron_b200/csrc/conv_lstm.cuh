@@ -283,79 +283,77 @@ __global__ void lstm_gram_mul_kernel(float* __restrict__ G, const float* __restr
     if (j <= k) G[i] *= G2[i];
   }
 }
-// One block per worker chunk walks its updates in groups of GRAM_BS; w[j] = final coefficient of update j.
-// For a group starting at k0 the part of every dot product that involves EARLIER groups,
-//     v[r] = sum_{j<k0} t[j] G[k0+r, j],
-// does not depend on the group's own clip factors, so all threads compute it at once (a [GRAM_BS x k0] matrix-vector
-// product, coalesced rows of G); only the GRAM_BS x GRAM_BS diagonal block is walked sequentially, by one warp, from
-// shared memory.  t[j] = 1 / S_{j-1} relative to a reference that is re-based before the running product of clip
-// factors S underflows; the norm recurrence and S are kept in double.
-constexpr int GRAM_THREADS = 1024, GRAM_BS = 64, GRAM_MAX_K = 49152;
-__global__ void __launch_bounds__(GRAM_THREADS) lstm_gram_scan_kernel(const float* __restrict__ G, int Kc, long n_total, float* __restrict__ w) {
-  extern __shared__ float tco[];                     // [Kc]
+// The updates of a worker chunk are walked in groups of GRAM_BS.  cw[j] holds the CURRENT coefficient of update j (the
+// product of all clip factors applied since it was added: at most 1, and free to underflow to 0, which is then also
+// what the literal recurrence has made of that update).  For the group starting at k0,
+//     v[r] = sum_{j<k0} cw[j] G[k0+r, j] = <g_{k0-1}, u_{k0+r}>
+// is a matrix-vector product over all SMs (lstm_gram_prefix_kernel, one block per row and chunk); inside the group the
+// earlier updates only get scaled by s = product of the group's clip factors so far, and the group's own GRAM_BS
+// coefficients live in shared memory and are walked sequentially by one warp (lstm_gram_group_kernel), which finally
+// scales cw[0..k0) by s and appends its own.  The two kernels are launched once per group; the stream orders them.
+// The norm recurrence and the coefficients are kept in double.  n2[chunk] = |g|^2.
+constexpr int GRAM_BS = 64, GRAM_MAX_K = 1 << 20;
+__global__ void lstm_gram_prefix_kernel(const float* __restrict__ G, const double* __restrict__ cw, double* __restrict__ v, int Kc, long n_total, int k0) {
+  __shared__ double red[8];
+  const int chunk = blockIdx.y, r = blockIdx.x, tid = threadIdx.x;
+  const long first = (long)chunk * Kc; const int n = (int)max(0L, min((long)Kc, n_total - first));
+  if (k0 + r >= n) return;
+  const float* row = G + (long)chunk * Kc * Kc + (long)(k0 + r) * Kc; const double* c = cw + first;
+  double acc = 0.0;
+  int j = tid;
+  for (; j + 3 * 256 < k0; j += 4 * 256)
+    acc += (c[j] * (double)row[j] + c[j + 256] * (double)row[j + 256]) + (c[j + 512] * (double)row[j + 512] + c[j + 768] * (double)row[j + 768]);
+  for (; j < k0; j += 256) acc += c[j] * (double)row[j];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if ((tid & 31) == 0) red[tid >> 5] = acc;
+  __syncthreads();
+  if (tid == 0) { double a = 0.0; for (int q = 0; q < 8; q++) a += red[q]; v[(long)chunk * GRAM_BS + r] = a; }
+}
+__global__ void __launch_bounds__(256) lstm_gram_group_kernel(const float* __restrict__ G, double* __restrict__ cw, const double* __restrict__ v,
+                                                              double* __restrict__ n2buf, int Kc, long n_total, int k0) {
   __shared__ float Gd[GRAM_BS][GRAM_BS + 1];
-  __shared__ double v[GRAM_BS];
-  __shared__ double red8[8][GRAM_THREADS / 32];
-  __shared__ double state[2];                        // S, n2
+  __shared__ double om[GRAM_BS];                 // current coefficients of this group's updates
+  __shared__ double s_shared;
   const int chunk = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const long first = (long)chunk * Kc; const int n = (int)max(0L, min((long)Kc, n_total - first));
-  const float* Gc = G + (long)chunk * Kc * Kc;
-  if (tid == 0) { state[0] = 1.0; state[1] = 0.0; }
+  if (k0 >= n) return;
+  const int nb = min(GRAM_BS, n - k0);
+  const float* Gc = G + (long)chunk * Kc * Kc; double* c = cw + first;
+  for (int e = tid; e < nb * GRAM_BS; e += 256) { const int r = e / GRAM_BS, q = e % GRAM_BS; if (q <= r) Gd[r][q] = Gc[(long)(k0 + r) * Kc + k0 + q]; }
   __syncthreads();
-  for (int k0 = 0; k0 < n; k0 += GRAM_BS) {
-    const int nb = min(GRAM_BS, n - k0);
-    // phase 1: contributions of earlier groups.  Thread (warp, lane) owns columns j = tid, tid + 1024, ... of ALL rows of
-    // the group, eight rows at a time, so that many independent loads are in flight; products are summed in fp32 per
-    // thread (at most k0 / 1024 terms) and across threads in double.
-    for (int r0 = 0; r0 < nb; r0 += 8) {
-      float acc[8];
+  if (warp == 0) {
+    double n2 = k0 == 0 ? 0.0 : n2buf[chunk];
+    double s = 1.0;
+    for (int r = 0; r < nb; r++) {
+      double p = 0.0;
+      if (lane < r) p = om[lane] * (double)Gd[r][lane];
+      if (lane + 32 < r) p += om[lane + 32] * (double)Gd[r][lane + 32];
 #pragma unroll
-      for (int q = 0; q < 8; q++) acc[q] = 0.f;
-      for (int j = tid; j < k0; j += GRAM_THREADS) {
-        const float tj = tco[j];
-#pragma unroll
-        for (int q = 0; q < 8; q++) if (r0 + q < nb) acc[q] = fmaf(tj, Gc[(long)(k0 + r0 + q) * Kc + j], acc[q]);
-      }
-#pragma unroll
-      for (int q = 0; q < 8; q++) {
-        double a = (double)acc[q];
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        if (lane == 0) red8[q][warp] = a;
-      }
-      __syncthreads();
-      if (tid < 8 && r0 + tid < nb) { double a = 0.0; for (int q = 0; q < GRAM_THREADS / 32; q++) a += red8[tid][q]; v[r0 + tid] = a; }
-      __syncthreads();
+      for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+      const double vr = k0 == 0 ? 0.0 : v[(long)chunk * GRAM_BS + r];
+      const double np = n2 + 2.0 * (s * vr + p) + (double)Gd[r][r];
+      double f = 1.0;
+      if (np > 1.0) { f = 1.0 / sqrt(np); n2 = 1.0; } else n2 = np;             // clip to norm 1 (lstm.go:738-750)
+      if (lane < r) om[lane] *= f;
+      if (lane + 32 < r) om[lane + 32] *= f;
+      if (lane == 0) om[r] = f;
+      s *= f;
+      __syncwarp();
     }
-    for (int e = tid; e < nb * GRAM_BS; e += GRAM_THREADS) { const int r = e / GRAM_BS, c = e % GRAM_BS; if (c <= r) Gd[r][c] = Gc[(long)(k0 + r) * Kc + k0 + c]; }   // diagonal block
-    __syncthreads();
-    // phase 2: the group's own updates, sequential, one warp
-    if (warp == 0) {
-      double S = state[0], n2 = state[1];
-      for (int r = 0; r < nb; r++) {
-        float p = 0.f;
-        if (lane < r) p = tco[k0 + lane] * Gd[r][lane];
-        if (lane + 32 < r) p = fmaf(tco[k0 + lane + 32], Gd[r][lane + 32], p);
-        p = warp_sum(p);
-        const double dot = v[r] + (double)p;
-        const double np = n2 + 2.0 * S * dot + (double)Gd[r][r];
-        if (lane == 0) tco[k0 + r] = (float)(1.0 / S);
-        if (np > 1.0) { S *= 1.0 / sqrt(np); n2 = 1.0; } else n2 = np;       // clip to norm 1 (lstm.go:738-750)
-        if (S < 1e-12) {                                                      // re-base: stored coefficients and pending sums scale with S
-          __syncwarp();
-          const float fs = (float)S;
-          for (int j = lane; j <= k0 + r; j += 32) tco[j] *= fs;
-          for (int q = r + 1 + lane; q < nb; q += 32) v[q] *= S;
-          S = 1.0;
-        }
-        __syncwarp();
-      }
-      if (lane == 0) { state[0] = S; state[1] = n2; }
-    }
-    __syncthreads();
+    if (lane == 0) { s_shared = s; n2buf[chunk] = n2; }
   }
-  const double S = state[0];
-  for (int j = tid; j < n; j += GRAM_THREADS) w[first + j] = (float)(S * (double)tco[j]);
+  __syncthreads();
+  const double sg = s_shared;
+  for (int j = tid; j < k0; j += 256) c[j] *= sg;
+  if (tid < nb) c[k0 + tid] = om[tid];
+}
+// w[j] = (float) cw[j], zero beyond the chunk's last update
+__global__ void lstm_gram_weights_kernel(const double* __restrict__ cw, float* __restrict__ w, int Kc, long n_total, long total) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const long chunk = i / Kc; const long n = max(0L, min((long)Kc, n_total - chunk * Kc));
+    w[i] = (i - chunk * Kc) < n ? (float)cw[i] : 0.f;
+  }
 }
 __global__ void lstm_scale_rows_kernel(float* __restrict__ Dm, const float* __restrict__ w, int R4, long total) {
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) Dm[i] *= w[i / R4];

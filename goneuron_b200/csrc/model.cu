@@ -116,7 +116,7 @@ struct gn_model {
 
 namespace gn {
 
-enum Slot { S_PL_HI = 0, S_PL_LO, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+enum Slot { S_PL_HI = 0, S_PL_LO, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
 
 static int ensure(gn_model* m, int slot, size_t n, float** out) {
   if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
@@ -475,8 +475,15 @@ static int lstm_backward(gn_model* m, LayerRT& l, size_t li, int B, const float*
       g.K = ZWg; g.A = Zm; g.sa_m = ZWg; g.B = Zm; g.sb_n = ZWg; g.a_b1 = g.b_b1 = Kc * ZWg; g.C = G1; GN_TRY(gemm(ctx, g));
       const long tot = (long)nchunks * Kc * Kc;
       GN_LAUNCH(ctx, lstm_gram_mul_kernel, ew_grid(ctx, tot), 256, 0, G0, (const float*)G1, (int)Kc, tot);
-      GN_CUDA(cudaFuncSetAttribute(lstm_gram_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(Kc * sizeof(float))));
-      GN_LAUNCH(ctx, lstm_gram_scan_kernel, nchunks, GRAM_THREADS, (size_t)Kc * sizeof(float), (const float*)G0, (int)Kc, n_updates, wv);
+      // cw (double) | v (double, one group) | |g|^2 per chunk (double) live in one scratch slot
+      float* tv; GN_TRY(ensure(m, S_TV, (size_t)2 * ((size_t)nchunks * Kc + (size_t)nchunks * GRAM_BS + 2 * nchunks + 2), &tv));
+      double* tco = reinterpret_cast<double*>(tv); double* vbuf = tco + (size_t)nchunks * Kc; double* state = vbuf + (size_t)nchunks * GRAM_BS;
+      for (int k0 = 0; k0 < Kc; k0 += GRAM_BS) {
+        if (k0 > 0) GN_LAUNCH(ctx, lstm_gram_prefix_kernel, dim3(GRAM_BS, nchunks), 256, 0, (const float*)G0, (const double*)tco, vbuf, (int)Kc, n_updates, k0);
+        GN_LAUNCH(ctx, lstm_gram_group_kernel, nchunks, 256, 0, (const float*)G0, tco, (const double*)vbuf, state, (int)Kc, n_updates, k0);
+      }
+      const long wtot = (long)nchunks * Kc;
+      GN_LAUNCH(ctx, lstm_gram_weights_kernel, ew_grid(ctx, wtot), 256, 0, (const double*)tco, wv, (int)Kc, n_updates, wtot);
       const long dtot = (long)nchunks * Kc * R4g;
       GN_LAUNCH(ctx, lstm_scale_rows_kernel, ew_grid(ctx, dtot), 256, 0, Dm, (const float*)wv, R4g, dtot);
       GemmDesc f; f.M = R4g; f.N = ZWg; f.K = (int)Kc; f.batch1 = nchunks; f.A = Dm; f.sa_m = 1; f.sa_k = R4g; f.a_b1 = Kc * R4g;
