@@ -292,7 +292,8 @@ __global__ void lstm_gram_mul_kernel(float* __restrict__ G, const float* __restr
 // coefficients live in shared memory and are walked sequentially by one warp (lstm_gram_group_kernel), which finally
 // scales cw[0..k0) by s and appends its own.  The two kernels are launched once per group; the stream orders them.
 // The norm recurrence and the coefficients are kept in double.  n2[chunk] = |g|^2.
-constexpr int GRAM_BS = 64, GRAM_MAX_K = 1 << 20;
+constexpr int GRAM_BS = 128, GRAM_MAX_K = 1 << 20;
+constexpr size_t GRAM_GROUP_SMEM = (size_t)GRAM_BS * (GRAM_BS + 1) * sizeof(float);
 __global__ void lstm_gram_prefix_kernel(const float* __restrict__ G, const double* __restrict__ cw, double* __restrict__ v, int Kc, long n_total, int k0) {
   __shared__ double red[8];
   const int chunk = blockIdx.y, r = blockIdx.x, tid = threadIdx.x;
@@ -310,41 +311,71 @@ __global__ void lstm_gram_prefix_kernel(const float* __restrict__ G, const doubl
   __syncthreads();
   if (tid == 0) { double a = 0.0; for (int q = 0; q < 8; q++) a += red[q]; v[(long)chunk * GRAM_BS + r] = a; }
 }
+// One warp walks the group.  Lane l owns rows l, l+32, ... of the diagonal block and keeps for each of them
+//     q[r'] = <g, u_{k0+r'}>  under the gradient g as it stands after the steps done so far,
+// which starts at v[r'] and follows q <- f (q + G[r'][r]) when step r adds u_r and scales by the clip factor f.  Step r
+// therefore needs one broadcast of q[r] and no reduction.  The factors are kept, and the group's coefficients are
+// their suffix products.
 __global__ void __launch_bounds__(256) lstm_gram_group_kernel(const float* __restrict__ G, double* __restrict__ cw, const double* __restrict__ v,
                                                               double* __restrict__ n2buf, int Kc, long n_total, int k0) {
-  __shared__ float Gd[GRAM_BS][GRAM_BS + 1];
-  __shared__ double om[GRAM_BS];                 // current coefficients of this group's updates
-  __shared__ double s_shared;
+  constexpr int QN = GRAM_BS / 32;
+  extern __shared__ __align__(16) float gram_smem[];
+  float (*Gd)[GRAM_BS + 1] = reinterpret_cast<float (*)[GRAM_BS + 1]>(gram_smem);
+  __shared__ double fr[GRAM_BS], om[GRAM_BS];
   const int chunk = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const long first = (long)chunk * Kc; const int n = (int)max(0L, min((long)Kc, n_total - first));
   if (k0 >= n) return;
   const int nb = min(GRAM_BS, n - k0);
   const float* Gc = G + (long)chunk * Kc * Kc; double* c = cw + first;
-  for (int e = tid; e < nb * GRAM_BS; e += 256) { const int r = e / GRAM_BS, q = e % GRAM_BS; if (q <= r) Gd[r][q] = Gc[(long)(k0 + r) * Kc + k0 + q]; }
+  for (int e = tid; e < GRAM_BS * GRAM_BS; e += 256) {
+    const int r = e / GRAM_BS, q = e % GRAM_BS;
+    Gd[r][q] = (r < nb && q < nb) ? Gc[(long)(k0 + r) * Kc + k0 + q] : 0.f;
+  }
   __syncthreads();
   if (warp == 0) {
     double n2 = k0 == 0 ? 0.0 : n2buf[chunk];
-    double s = 1.0;
-    for (int r = 0; r < nb; r++) {
-      double p = 0.0;
-      if (lane < r) p = om[lane] * (double)Gd[r][lane];
-      if (lane + 32 < r) p += om[lane + 32] * (double)Gd[r][lane + 32];
+    double q[QN];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
-      const double vr = k0 == 0 ? 0.0 : v[(long)chunk * GRAM_BS + r];
-      const double np = n2 + 2.0 * (s * vr + p) + (double)Gd[r][r];
-      double f = 1.0;
-      if (np > 1.0) { f = 1.0 / sqrt(np); n2 = 1.0; } else n2 = np;             // clip to norm 1 (lstm.go:738-750)
-      if (lane < r) om[lane] *= f;
-      if (lane + 32 < r) om[lane + 32] *= f;
-      if (lane == 0) om[r] = f;
-      s *= f;
-      __syncwarp();
+    for (int i = 0; i < QN; i++) { const int r = lane + 32 * i; q[i] = (k0 > 0 && r < nb) ? v[(long)chunk * GRAM_BS + r] : 0.0; }
+    // the block's column r and its diagonal entry are fetched one step ahead, so that the step itself is only the
+    // broadcast, the norm update and the clip factor (single-precision reciprocal square root + one Newton step)
+    float gcol[QN], gdiag = Gd[0][0];
+#pragma unroll
+    for (int i2 = 0; i2 < QN; i2++) gcol[i2] = Gd[lane + 32 * i2][0];
+#pragma unroll
+    for (int i = 0; i < QN; i++) {
+      for (int rl = 0; rl < 32; rl++) {
+        const int r = 32 * i + rl;
+        if (r >= nb) break;
+        const double qr = __shfl_sync(0xffffffffu, q[i], rl);
+        float ncol[QN]; const int rn = min(r + 1, GRAM_BS - 1);
+#pragma unroll
+        for (int i2 = 0; i2 < QN; i2++) ncol[i2] = Gd[lane + 32 * i2][rn];
+        const float ndiag = Gd[rn][rn];
+        double qg[QN];
+#pragma unroll
+        for (int i2 = 0; i2 < QN; i2++) qg[i2] = q[i2] + (double)gcol[i2];
+        const double np = n2 + 2.0 * qr + (double)gdiag;
+        double f0 = (double)rsqrtf((float)np);
+        f0 = f0 * (1.5 - 0.5 * np * f0 * f0);
+        const bool clip = np > 1.0;                                               // clip to norm 1 (lstm.go:738-750)
+        const double f = clip ? f0 : 1.0;
+        n2 = clip ? 1.0 : np;
+#pragma unroll
+        for (int i2 = 0; i2 < QN; i2++) { q[i2] = f * qg[i2]; gcol[i2] = ncol[i2]; }
+        gdiag = ndiag;
+        if (lane == 0) fr[r] = f;
+      }
     }
-    if (lane == 0) { s_shared = s; n2buf[chunk] = n2; }
+    __syncwarp();
+    if (lane == 0) {
+      double a = 1.0;
+      for (int r = nb - 1; r >= 0; r--) { a *= fr[r]; om[r] = a; }
+      n2buf[chunk] = n2;
+    }
   }
   __syncthreads();
-  const double sg = s_shared;
+  const double sg = om[0];
   for (int j = tid; j < k0; j += 256) c[j] *= sg;
   if (tid < nb) c[k0 + tid] = om[tid];
 }

@@ -478,9 +478,10 @@ static int lstm_backward(gn_model* m, LayerRT& l, size_t li, int B, const float*
       // cw (double) | v (double, one group) | |g|^2 per chunk (double) live in one scratch slot
       float* tv; GN_TRY(ensure(m, S_TV, (size_t)2 * ((size_t)nchunks * Kc + (size_t)nchunks * GRAM_BS + 2 * nchunks + 2), &tv));
       double* tco = reinterpret_cast<double*>(tv); double* vbuf = tco + (size_t)nchunks * Kc; double* state = vbuf + (size_t)nchunks * GRAM_BS;
+      GN_CUDA(cudaFuncSetAttribute(lstm_gram_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GRAM_GROUP_SMEM));
       for (int k0 = 0; k0 < Kc; k0 += GRAM_BS) {
         if (k0 > 0) GN_LAUNCH(ctx, lstm_gram_prefix_kernel, dim3(GRAM_BS, nchunks), 256, 0, (const float*)G0, (const double*)tco, vbuf, (int)Kc, n_updates, k0);
-        GN_LAUNCH(ctx, lstm_gram_group_kernel, nchunks, 256, 0, (const float*)G0, tco, (const double*)vbuf, state, (int)Kc, n_updates, k0);
+        GN_LAUNCH(ctx, lstm_gram_group_kernel, nchunks, 256, GRAM_GROUP_SMEM, (const float*)G0, tco, (const double*)vbuf, state, (int)Kc, n_updates, k0);
       }
       const long wtot = (long)nchunks * Kc;
       GN_LAUNCH(ctx, lstm_gram_weights_kernel, ew_grid(ctx, wtot), 256, 0, (const double*)tco, wv, (int)Kc, n_updates, wtot);
