@@ -1,0 +1,539 @@
+// attention_tc.cuh -- multi-head attention (head size 64) on the tcgen05 tensor cores with the score tile, the
+// probabilities and the output accumulator resident in tensor memory.
+//
+// reference: internal/layer/transformer.go:470-503 (forward) -- same arithmetic as attention.cuh: scores =
+// q.k / sqrt(hd), masked entries removed, row softmax, weighted sum of v; row maximum and row sum kept per row.
+//
+// Operands: hi/lo planes (3xTF32) written by the split kernels of gemm_tc.cuh, one problem per (batch, head):
+//   Qp, Kp : [B*H][T][64]   (contraction over the head dimension is along the row)
+//   Vt     : [B*H][64][T]   (transposed, so that the contraction over the keys is along the row as well)
+// and fetched by TMA into 128-byte-swizzled tiles.  One CTA = 128 query rows of one head; key blocks of 64.
+//   warp 0    : TMA producer (Q once; K and Vt blocks through two stages each)
+//   warp 1    : MMA issuer.  S_j = Q K_j^T (both operands in shared memory) into one of two 64-column TMEM buffers;
+//               O += P_j V_j with P read from TMEM as the A operand and Vt_j from shared memory.
+//   warps 2-5 : one query row per thread (TMEM lane = row): tcgen05.ld of S_j, running maximum and sum,
+//               p = exp(s - m), hi written over S_j in place and lo into a second buffer (tcgen05.st); when a row
+//               maximum moved, the output accumulator is rescaled in TMEM after the previous P V has completed.
+// The issue order S_0, S_1, PV_0, S_2, PV_1, ... keeps the tensor pipe busy with S_{j+1} (and PV_{j-1}) while the
+// softmax of block j runs.  Every wait is bounded; a wait that gives up sets the status word.
+#pragma once
+#include "attention.cuh"
+#include "gemm_tc.cuh"
+
+namespace gn {
+
+constexpr int ATC_BQ = 128, ATC_BK = 64, ATC_HD = 64, ATC_THREADS = 192;
+constexpr int ATC_Q_BYTES = 4 * ATC_BQ * 128;   // hi, lo x two chunks of 32 floats: 64 KB
+constexpr int ATC_K_BYTES = 4 * ATC_BK * 128;   // 32 KB
+constexpr int ATC_V_BYTES = 4 * ATC_HD * 128;   // 32 KB
+constexpr int ATC_FWD_SMEM = ATC_Q_BYTES + 2 * (ATC_K_BYTES + ATC_V_BYTES) + 1024 + 256;
+// TMEM columns: S / P_hi buffers [0,128), P_lo buffers [128,256), O [256,320)
+constexpr uint32_t ATC_COL_S = 0, ATC_COL_PLO = 128, ATC_COL_O = 256, ATC_TMEM_COLS = 512;
+
+__device__ __forceinline__ void tc_mma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+        "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+        "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// one lane polls, the warp gets the verdict
+__device__ __forceinline__ bool warp_mbar_wait(uint32_t bar, uint32_t parity, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+__global__ void __launch_bounds__(ATC_THREADS, 1)
+attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constant__ CUtensorMap mQl, const __grid_constant__ CUtensorMap mKh,
+                   const __grid_constant__ CUtensorMap mKl, const __grid_constant__ CUtensorMap mVh, const __grid_constant__ CUtensorMap mVl,
+                   float* __restrict__ O, float* __restrict__ Mst, float* __restrict__ Lst, int T, int D, int H, int causal, float inv_scale, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sK = smem + ATC_Q_BYTES;                                   // two stages of ATC_K_BYTES
+  uint8_t* sV = sK + 2 * ATC_K_BYTES;                                 // two stages of ATC_V_BYTES
+  uint64_t* bars = (uint64_t*)(sV + 2 * ATC_V_BYTES);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+  // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 p_full | 13 pv_done
+  const uint32_t bar0 = smem_u32(bars);
+  auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x, z = blockIdx.y, q0 = qb * ATC_BQ;   // long tiles first
+  const int nblk = causal ? (q0 + ATC_BQ) / ATC_BK : T / ATC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 14; i++) mbar_init(BAR(i), (i == 11 || i == 12) ? 128 : 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(ATC_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(BAR(0), ATC_Q_BYTES);
+      for (int c = 0; c < 2; c++) {
+        tma_load_3d(smem_u32(sQ + c * 16384), &mQh, c * 32, q0, z, BAR(0));
+        tma_load_3d(smem_u32(sQ + 32768 + c * 16384), &mQl, c * 32, q0, z, BAR(0));
+      }
+      for (int j = 0; j < nblk; j++) {
+        const int s = j & 1, u = j >> 1;
+        if (u > 0) ok &= mbar_wait(BAR(3 + s), (u - 1) & 1);
+        mbar_expect_tx(BAR(1 + s), ATC_K_BYTES);
+        for (int c = 0; c < 2; c++) {
+          tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + c * 8192), &mKh, c * 32, j * ATC_BK, z, BAR(1 + s));
+          tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + 16384 + c * 8192), &mKl, c * 32, j * ATC_BK, z, BAR(1 + s));
+        }
+        if (u > 0) ok &= mbar_wait(BAR(7 + s), (u - 1) & 1);
+        mbar_expect_tx(BAR(5 + s), ATC_V_BYTES);
+        for (int c = 0; c < 2; c++) {
+          tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + c * 8192), &mVh, j * ATC_BK + c * 32, 0, z, BAR(5 + s));
+          tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + 16384 + c * 8192), &mVl, j * ATC_BK + c * 32, 0, z, BAR(5 + s));
+        }
+      }
+      if (!ok) atomicExch(status, 11);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      constexpr uint32_t idesc = make_idesc(ATC_BQ, 64);
+      auto issue_s = [&](int j) {
+        const int s = j & 1, u = j >> 1;
+        ok &= mbar_wait(BAR(1 + s), u & 1);
+        tc_fence_after();
+        const uint32_t acc = tmem_base + ATC_COL_S + s * 64;
+        const uint32_t kb = smem_u32(sK + s * ATC_K_BYTES), qa = smem_u32(sQ);
+#pragma unroll
+        for (int c = 0; c < 2; c++)
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            const uint64_t adv = (uint64_t)(2 * k);
+            const uint64_t ah = make_desc<32>(qa + c * 16384) + adv, al = make_desc<32>(qa + 32768 + c * 16384) + adv;
+            const uint64_t bh = make_desc<32>(kb + c * 8192) + adv, bl = make_desc<32>(kb + 16384 + c * 8192) + adv;
+            tc_mma_tf32(acc, al, bh, idesc, (c | k) ? 1u : 0u);
+            tc_mma_tf32(acc, ah, bl, idesc, 1u);
+            tc_mma_tf32(acc, ah, bh, idesc, 1u);
+          }
+        tc_commit(BAR(3 + s));
+        tc_commit(BAR(9 + s));
+      };
+      auto issue_pv = [&](int j) {
+        const int s = j & 1, u = j >> 1;
+        ok &= mbar_wait(BAR(11 + s), u & 1);
+        ok &= mbar_wait(BAR(5 + s), u & 1);
+        tc_fence_after();
+        const uint32_t vb = smem_u32(sV + s * ATC_V_BYTES);
+        const uint32_t ph = tmem_base + ATC_COL_S + s * 64, pl = tmem_base + ATC_COL_PLO + s * 64, acc = tmem_base + ATC_COL_O;
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++) {
+          const int c = kk >> 2; const uint64_t adv = (uint64_t)(2 * (kk & 3));
+          const uint64_t bh = make_desc<32>(vb + c * 8192) + adv, bl = make_desc<32>(vb + 16384 + c * 8192) + adv;
+          tc_mma_tf32_ts(acc, pl + kk * 8, bh, idesc, (j | kk) ? 1u : 0u);
+          tc_mma_tf32_ts(acc, ph + kk * 8, bl, idesc, 1u);
+          tc_mma_tf32_ts(acc, ph + kk * 8, bh, idesc, 1u);
+        }
+        tc_commit(BAR(7 + s));
+        tc_commit(BAR(13));
+      };
+      ok &= mbar_wait(BAR(0), 0);
+      issue_s(0);
+      if (nblk > 1) issue_s(1);
+      for (int j = 0; j < nblk; j++) {
+        issue_pv(j);
+        if (j + 2 < nblk) issue_s(j + 2);
+      }
+      if (!ok) atomicExch(status, 12);
+    }
+  } else {
+    const int quad = warp & 3, row = quad * 32 + lane, qi = q0 + row;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nblk; j++) {
+      const int s = j & 1, u = j >> 1, key0 = j * ATC_BK;
+      ok &= warp_mbar_wait(BAR(9 + s), u & 1, lane);
+      tc_fence_after();
+      uint32_t a[32], b[32];
+      tmem_ld32(lane_base + ATC_COL_S + s * 64, a);
+      tmem_ld32(lane_base + ATC_COL_S + s * 64 + 32, b);
+      tmem_wait_ld();
+      float bm = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < 32; e++) {
+        float va = __uint_as_float(a[e]) * inv_scale, vb = __uint_as_float(b[e]) * inv_scale;
+        if (causal && key0 + e > qi) va = -INFINITY;
+        if (causal && key0 + 32 + e > qi) vb = -INFINITY;
+        a[e] = __float_as_uint(va); b[e] = __float_as_uint(vb);
+        bm = fmaxf(bm, fmaxf(va, vb));
+      }
+      const float m_new = fmaxf(m_run, bm);
+      const float corr = __expf(m_run - m_new);
+      float rs = 0.f;
+      uint32_t lo[32];
+#pragma unroll
+      for (int e = 0; e < 32; e++) {
+        const float p = __expf(__uint_as_float(a[e]) - m_new); rs += p;
+        const uint32_t hi = __float_as_uint(p) & 0xffffe000u;
+        a[e] = hi; lo[e] = __float_as_uint(p - __uint_as_float(hi));
+      }
+      tmem_st32(lane_base + ATC_COL_S + s * 64, a);
+      tmem_st32(lane_base + ATC_COL_PLO + s * 64, lo);
+#pragma unroll
+      for (int e = 0; e < 32; e++) {
+        const float p = __expf(__uint_as_float(b[e]) - m_new); rs += p;
+        const uint32_t hi = __float_as_uint(p) & 0xffffe000u;
+        b[e] = hi; lo[e] = __float_as_uint(p - __uint_as_float(hi));
+      }
+      tmem_st32(lane_base + ATC_COL_S + s * 64 + 32, b);
+      tmem_st32(lane_base + ATC_COL_PLO + s * 64 + 32, lo);
+      l_run = l_run * corr + rs; m_run = m_new;
+      // The accumulator may only be touched between P V products.  The wait is unconditional: a parity wait is only
+      // unambiguous when no completion of this barrier has been skipped.
+      if (j > 0) ok &= warp_mbar_wait(BAR(13), (j - 1) & 1, lane);
+      if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+        tc_fence_after();
+        tmem_ld32(lane_base + ATC_COL_O, a);
+        tmem_ld32(lane_base + ATC_COL_O + 32, b);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e++) { a[e] = __float_as_uint(__uint_as_float(a[e]) * corr); b[e] = __float_as_uint(__uint_as_float(b[e]) * corr); }
+        tmem_st32(lane_base + ATC_COL_O, a);
+        tmem_st32(lane_base + ATC_COL_O + 32, b);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(BAR(11 + s));
+    }
+    ok &= warp_mbar_wait(BAR(13), (nblk - 1) & 1, lane);
+    tc_fence_after();
+    {
+      uint32_t a[32], b[32];
+      tmem_ld32(lane_base + ATC_COL_O, a);
+      tmem_ld32(lane_base + ATC_COL_O + 32, b);
+      tmem_wait_ld();
+      const float il = 1.f / l_run;
+      const int bz = z / H, h = z % H;
+      float* orow = O + ((long)bz * T + qi) * D + (long)h * ATC_HD;
+#pragma unroll
+      for (int e = 0; e < 8; e++)
+        *reinterpret_cast<float4*>(orow + 4 * e) = make_float4(__uint_as_float(a[4 * e]) * il, __uint_as_float(a[4 * e + 1]) * il, __uint_as_float(a[4 * e + 2]) * il, __uint_as_float(a[4 * e + 3]) * il);
+#pragma unroll
+      for (int e = 0; e < 8; e++)
+        *reinterpret_cast<float4*>(orow + 32 + 4 * e) = make_float4(__uint_as_float(b[4 * e]) * il, __uint_as_float(b[4 * e + 1]) * il, __uint_as_float(b[4 * e + 2]) * il, __uint_as_float(b[4 * e + 3]) * il);
+      Mst[(long)z * T + qi] = m_run; Lst[(long)z * T + qi] = l_run;
+    }
+    if (!ok && lane == 0) atomicExch(status, 13);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(ATC_TMEM_COLS) : "memory");
+}
+
+// ------------------------------------------------------------------ backward
+// reference: internal/layer/transformer.go:589-657.  One kernel template, three uses; each CTA owns a tile of 128
+// rows ("row tile", operand planes resident in shared memory) and walks 64-wide blocks of the other index:
+//   MODE 0 (dQ): rows = queries.  S = Q K_j^T, dP = dO V_j^T, dS = P (dP - Dv) / sqrt(hd), dQ += dS K_j
+//   MODE 1 (dK): rows = keys.     S^T = K Q_i^T, dP^T = V dO_i^T, dS^T likewise,         dK += dS^T Q_i
+//   MODE 2 (dV): rows = keys.     S^T = K Q_i^T, P^T,                                     dV += P^T dO_i
+// with P = exp(S / sqrt(hd) - m) / l recomputed from the saved row statistics (per row of the tile in MODE 0, per
+// column in MODES 1 and 2, staged in shared memory).  R1, R2 = row-tile operands; C1, C2 = block operands of the two
+// score-shaped products ([64 rows][64]); C3 = block operand of the accumulating product, taken from TRANSPOSED planes
+// ([64 head columns][T]) so that its contraction index runs along the row.  dS (P in MODE 2) goes back to tensor
+// memory as hi/lo and is the A operand of the accumulating product.  TMEM: two sets of {S, dP / dS_hi, dS_lo} so that
+// the score products of block n+1 run under the elementwise work of block n; accumulator in the last 64 columns.
+// Warps: 0 = TMA producer for R1, R2, C1, C2; 1 = MMA issuer; 2-5 = elementwise (one tile row per thread);
+// 6 = TMA producer for C3 (its buffer is released much later than C1 / C2, so it gets its own thread).
+constexpr int ATB_THREADS = 224;
+constexpr int ATB_R_BYTES = 4 * 128 * 128, ATB_C_BYTES = 4 * 64 * 128;      // 64 KB, 32 KB
+template <int MODE> struct AtbCfg {
+  static constexpr int NR = MODE == 2 ? 1 : 2;                                 // row-tile operands, score-shaped products
+  static constexpr int SMEM = NR * ATB_R_BYTES + (NR + 1) * ATB_C_BYTES + 1024 + 256 + 2 * 3 * 64 * 4;
+};
+constexpr uint32_t ATB_COL_S = 0, ATB_COL_DP = 128, ATB_COL_LO = 256, ATB_COL_ACC = 384;
+
+template <int MODE>
+__global__ void __launch_bounds__(ATB_THREADS, 1)
+attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_constant__ CUtensorMap mR1l, const __grid_constant__ CUtensorMap mR2h,
+                   const __grid_constant__ CUtensorMap mR2l, const __grid_constant__ CUtensorMap mC1h, const __grid_constant__ CUtensorMap mC1l,
+                   const __grid_constant__ CUtensorMap mC2h, const __grid_constant__ CUtensorMap mC2l, const __grid_constant__ CUtensorMap mC3h,
+                   const __grid_constant__ CUtensorMap mC3l, const float* __restrict__ Mst, const float* __restrict__ Lst, const float* __restrict__ Dv,
+                   float* __restrict__ Out, int T, int D, int H, int causal, float inv_scale, int* status) {
+  constexpr int NR = AtbCfg<MODE>::NR;
+  constexpr bool TRANS = MODE != 0;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* sR = smem;                                    // NR row-tile operands
+  uint8_t* sC = sR + NR * ATB_R_BYTES;                   // NR block operands of the score products
+  uint8_t* sC3 = sC + NR * ATB_C_BYTES;
+  uint64_t* bars = (uint64_t*)(sC3 + ATB_C_BYTES);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+  float* st = (float*)(bars + 32);                       // [2][3][64] column statistics (MODES 1, 2)
+  // barriers: 0 r_full | 1 c12_full | 2 c12_empty | 3 c3_full | 4 c3_empty | 5,6 sd_full | 7,8 ds_full | 9 all_done
+  const uint32_t bar0 = smem_u32(bars);
+  auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int z = blockIdx.y;
+  const int tile = TRANS ? (int)blockIdx.x : (int)gridDim.x - 1 - (int)blockIdx.x;      // long tiles first
+  const int r0 = tile * 128;
+  const int b0 = (TRANS && causal) ? r0 / 64 : 0;
+  const int nb = TRANS ? T / 64 - b0 : (causal ? (r0 + 128) / 64 : T / 64);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 10; i++) mbar_init(BAR(i), (i == 7 || i == 8) ? 128 : 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      bool ok = true;
+      mbar_expect_tx(BAR(0), NR * ATB_R_BYTES);
+      for (int c = 0; c < 2; c++) {
+        tma_load_3d(smem_u32(sR + c * 16384), &mR1h, c * 32, r0, z, BAR(0));
+        tma_load_3d(smem_u32(sR + 32768 + c * 16384), &mR1l, c * 32, r0, z, BAR(0));
+        if (NR == 2) {
+          tma_load_3d(smem_u32(sR + ATB_R_BYTES + c * 16384), &mR2h, c * 32, r0, z, BAR(0));
+          tma_load_3d(smem_u32(sR + ATB_R_BYTES + 32768 + c * 16384), &mR2l, c * 32, r0, z, BAR(0));
+        }
+      }
+      for (int n = 0; n < nb; n++) {
+        const int row = (b0 + n) * 64;
+        if (n > 0) ok &= mbar_wait(BAR(2), (n - 1) & 1);
+        mbar_expect_tx(BAR(1), NR * ATB_C_BYTES);
+        for (int c = 0; c < 2; c++) {
+          tma_load_3d(smem_u32(sC + c * 8192), &mC1h, c * 32, row, z, BAR(1));
+          tma_load_3d(smem_u32(sC + 16384 + c * 8192), &mC1l, c * 32, row, z, BAR(1));
+          if (NR == 2) {
+            tma_load_3d(smem_u32(sC + ATB_C_BYTES + c * 8192), &mC2h, c * 32, row, z, BAR(1));
+            tma_load_3d(smem_u32(sC + ATB_C_BYTES + 16384 + c * 8192), &mC2l, c * 32, row, z, BAR(1));
+          }
+        }
+      }
+      if (!ok) atomicExch(status, 21);
+    }
+  } else if (warp == 6) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int n = 0; n < nb; n++) {
+        const int col = (b0 + n) * 64;
+        if (n > 0) ok &= mbar_wait(BAR(4), (n - 1) & 1);
+        mbar_expect_tx(BAR(3), ATB_C_BYTES);
+        for (int c = 0; c < 2; c++) {
+          tma_load_3d(smem_u32(sC3 + c * 8192), &mC3h, col + c * 32, 0, z, BAR(3));
+          tma_load_3d(smem_u32(sC3 + 16384 + c * 8192), &mC3l, col + c * 32, 0, z, BAR(3));
+        }
+      }
+      if (!ok) atomicExch(status, 22);
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      constexpr uint32_t idesc = make_idesc(128, 64);
+      auto issue_sd = [&](int n) {
+        const int s = n & 1;
+        ok &= mbar_wait(BAR(1), n & 1);
+        tc_fence_after();
+#pragma unroll
+        for (int prod = 0; prod < NR; prod++) {
+          const uint32_t acc = tmem_base + (prod == 0 ? ATB_COL_S : ATB_COL_DP) + s * 64;
+          const uint32_t ra = smem_u32(sR + prod * ATB_R_BYTES), cb = smem_u32(sC + prod * ATB_C_BYTES);
+#pragma unroll
+          for (int c = 0; c < 2; c++)
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+              const uint64_t adv = (uint64_t)(2 * k);
+              const uint64_t ah = make_desc<32>(ra + c * 16384) + adv, al = make_desc<32>(ra + 32768 + c * 16384) + adv;
+              const uint64_t bh = make_desc<32>(cb + c * 8192) + adv, bl = make_desc<32>(cb + 16384 + c * 8192) + adv;
+              tc_mma_tf32(acc, al, bh, idesc, (c | k) ? 1u : 0u);
+              tc_mma_tf32(acc, ah, bl, idesc, 1u);
+              tc_mma_tf32(acc, ah, bh, idesc, 1u);
+            }
+        }
+        tc_commit(BAR(2));
+        tc_commit(BAR(5 + s));
+      };
+      auto issue_acc = [&](int n) {
+        const int s = n & 1, u = n >> 1;
+        ok &= mbar_wait(BAR(7 + s), u & 1);
+        ok &= mbar_wait(BAR(3), n & 1);
+        tc_fence_after();
+        const uint32_t cb = smem_u32(sC3);
+        const uint32_t ph = tmem_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, pl = tmem_base + ATB_COL_LO + s * 64, acc = tmem_base + ATB_COL_ACC;
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++) {
+          const int c = kk >> 2; const uint64_t adv = (uint64_t)(2 * (kk & 3));
+          const uint64_t bh = make_desc<32>(cb + c * 8192) + adv, bl = make_desc<32>(cb + 16384 + c * 8192) + adv;
+          tc_mma_tf32_ts(acc, pl + kk * 8, bh, idesc, (n | kk) ? 1u : 0u);
+          tc_mma_tf32_ts(acc, ph + kk * 8, bl, idesc, 1u);
+          tc_mma_tf32_ts(acc, ph + kk * 8, bh, idesc, 1u);
+        }
+        tc_commit(BAR(4));
+        if (n == nb - 1) tc_commit(BAR(9));
+      };
+      ok &= mbar_wait(BAR(0), 0);
+      issue_sd(0);
+      if (nb > 1) issue_sd(1);
+      for (int n = 0; n < nb; n++) {
+        issue_acc(n);
+        if (n + 2 < nb) issue_sd(n + 2);
+      }
+      if (!ok) atomicExch(status, 23);
+    }
+  } else {
+    const int quad = warp & 3, row = quad * 32 + lane, ri = r0 + row, et = (warp - 2) * 32 + lane;   // et: 0..127 among the elementwise threads
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const long sb = (long)z * T;
+    float m_r = 0.f, il_r = 0.f, d_r = 0.f;
+    if (!TRANS) { m_r = Mst[sb + ri]; il_r = 1.f / Lst[sb + ri]; d_r = Dv[sb + ri]; }
+    bool ok = true;
+    for (int n = 0; n < nb; n++) {
+      const int s = n & 1, u = n >> 1, c0 = (b0 + n) * 64;
+      float* stm = st + s * 192; float* stl = stm + 64; float* std_ = stm + 128;
+      if (TRANS) {
+        if (et < 64) { stm[et] = Mst[sb + c0 + et]; stl[et] = 1.f / Lst[sb + c0 + et]; if (MODE == 1) std_[et] = Dv[sb + c0 + et]; }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+      ok &= warp_mbar_wait(BAR(5 + s), u & 1, lane);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 2; c++) {
+        uint32_t a[32], b[32], lo[32];
+        tmem_ld32(lane_base + ATB_COL_S + s * 64 + 32 * c, a);
+        if (MODE != 2) tmem_ld32(lane_base + ATB_COL_DP + s * 64 + 32 * c, b);
+        tmem_wait_ld();
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          const int col = 32 * c + e, ci = c0 + col;
+          const bool masked = causal && (TRANS ? ri > ci : ci > ri);
+          const float mm = TRANS ? stm[col] : m_r, il = TRANS ? stl[col] : il_r;
+          float v = masked ? 0.f : __expf(__uint_as_float(a[e]) * inv_scale - mm) * il;          // P
+          if (MODE != 2) v = v * (__uint_as_float(b[e]) - (TRANS ? std_[col] : d_r)) * inv_scale;   // dS
+          const uint32_t hi = __float_as_uint(v) & 0xffffe000u;
+          a[e] = hi; lo[e] = __float_as_uint(v - __uint_as_float(hi));
+        }
+        tmem_st32(lane_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64 + 32 * c, a);
+        tmem_st32(lane_base + ATB_COL_LO + s * 64 + 32 * c, lo);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(BAR(7 + s));
+    }
+    ok &= warp_mbar_wait(BAR(9), 0, lane);
+    tc_fence_after();
+    {
+      uint32_t a[32], b[32];
+      tmem_ld32(lane_base + ATB_COL_ACC, a);
+      tmem_ld32(lane_base + ATB_COL_ACC + 32, b);
+      tmem_wait_ld();
+      const int bz = z / H, h = z % H;
+      float* orow = Out + ((long)bz * T + ri) * D + (long)h * ATC_HD;
+#pragma unroll
+      for (int e = 0; e < 8; e++)
+        *reinterpret_cast<float4*>(orow + 4 * e) = make_float4(__uint_as_float(a[4 * e]), __uint_as_float(a[4 * e + 1]), __uint_as_float(a[4 * e + 2]), __uint_as_float(a[4 * e + 3]));
+#pragma unroll
+      for (int e = 0; e < 8; e++)
+        *reinterpret_cast<float4*>(orow + 32 + 4 * e) = make_float4(__uint_as_float(b[4 * e]), __uint_as_float(b[4 * e + 1]), __uint_as_float(b[4 * e + 2]), __uint_as_float(b[4 * e + 3]));
+    }
+    if (!ok && lane == 0) atomicExch(status, 24);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+}
+
+// ------------------------------------------------------------------ host side
+struct AttnTcScratch { DevBuf buf[16]; };
+inline AttnTcScratch& attn_tc_scratch(Ctx* ctx) {
+  static thread_local std::vector<std::pair<Ctx*, AttnTcScratch*>> tab;
+  for (auto& e : tab) if (e.first == ctx) return *e.second;
+  tab.push_back({ctx, new AttnTcScratch()}); return *tab.back().second;
+}
+inline int attn_tc_buf(Ctx* ctx, int i, size_t n, float** out) {
+  DevBuf& b = attn_tc_scratch(ctx).buf[i];
+  if (b.n < n) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(b.alloc(n)); }
+  *out = b.p; return GN_OK;
+}
+inline bool attn_tc_supported(Ctx* ctx, int hd, int T, int B, int H, int D) {
+  static const bool off = [] { const char* e = getenv("GONEURON_CUDA_ATTENTION"); return e && !strcmp(e, "mma"); }();
+  return !off && ctx->tc_ok && hd == ATC_HD && T % ATC_BQ == 0 && (long)B * H <= 65535 && D % 4 == 0;
+}
+// planes of a [B*T, D] tensor per (batch, head): rows [Z][T][64] or transposed [Z][64][T]
+inline int attn_tc_planes(Ctx* ctx, const float* X, int slot, bool transposed, int B, int T, int D, int H, TcPlanes* out) {
+  const int Z = B * H; const size_t n = (size_t)Z * T * ATC_HD;
+  float *hi, *lo; GN_TRY(attn_tc_buf(ctx, slot, n, &hi)); GN_TRY(attn_tc_buf(ctx, slot + 1, n, &lo));
+  TcSrc src; src.p = X; src.b1 = (long)T * D; src.b2 = ATC_HD; src.batch2 = H;
+  if (!transposed) { src.s_r = D; src.s_c = 1; *out = TcPlanes{hi, lo, T, ATC_HD, ATC_HD, Z}; }
+  else { src.s_r = 1; src.s_c = D; *out = TcPlanes{hi, lo, ATC_HD, T, T, Z}; }
+  return tc_split(ctx, src, *out);
+}
+inline int attn_tc_fwd(Ctx* ctx, const float* Q, const float* K, const float* V, float* O, float* M, float* L, int B, int T, int D, int H, int causal) {
+  TcPlanes pq, pk, pv;
+  GN_TRY(attn_tc_planes(ctx, Q, 0, false, B, T, D, H, &pq));
+  GN_TRY(attn_tc_planes(ctx, K, 2, false, B, T, D, H, &pk));
+  GN_TRY(attn_tc_planes(ctx, V, 4, true, B, T, D, H, &pv));
+  CUtensorMap mQh, mQl, mKh, mKl, mVh, mVl;
+  GN_TRY(tc_make_map(ctx, &mQh, pq, pq.hi, ATC_BQ)); GN_TRY(tc_make_map(ctx, &mQl, pq, pq.lo, ATC_BQ));
+  GN_TRY(tc_make_map(ctx, &mKh, pk, pk.hi, ATC_BK)); GN_TRY(tc_make_map(ctx, &mKl, pk, pk.lo, ATC_BK));
+  GN_TRY(tc_make_map(ctx, &mVh, pv, pv.hi, ATC_HD)); GN_TRY(tc_make_map(ctx, &mVl, pv, pv.lo, ATC_HD));
+  GN_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_FWD_SMEM));
+  GN_LAUNCH(ctx, attn_tc_fwd_kernel, dim3(T / ATC_BQ, B * H), ATC_THREADS, ATC_FWD_SMEM, mQh, mQl, mKh, mKl, mVh, mVl, O, M, L, T, D, H, causal,
+            1.f / sqrtf((float)ATC_HD), ctx->d_status);
+  return check_launch("attn_tc_fwd");
+}
+
+template <int MODE>
+inline int attn_tc_bwd_launch(Ctx* ctx, const TcPlanes& r1, const TcPlanes& r2, const TcPlanes& c1, const TcPlanes& c2, const TcPlanes& c3,
+                              const float* M, const float* L, const float* Dv, float* out, int B, int T, int D, int H, int causal) {
+  CUtensorMap m[10];
+  GN_TRY(tc_make_map(ctx, &m[0], r1, r1.hi, 128)); GN_TRY(tc_make_map(ctx, &m[1], r1, r1.lo, 128));
+  GN_TRY(tc_make_map(ctx, &m[2], r2, r2.hi, 128)); GN_TRY(tc_make_map(ctx, &m[3], r2, r2.lo, 128));
+  GN_TRY(tc_make_map(ctx, &m[4], c1, c1.hi, 64)); GN_TRY(tc_make_map(ctx, &m[5], c1, c1.lo, 64));
+  GN_TRY(tc_make_map(ctx, &m[6], c2, c2.hi, 64)); GN_TRY(tc_make_map(ctx, &m[7], c2, c2.lo, 64));
+  GN_TRY(tc_make_map(ctx, &m[8], c3, c3.hi, ATC_HD)); GN_TRY(tc_make_map(ctx, &m[9], c3, c3.lo, ATC_HD));
+  GN_CUDA(cudaFuncSetAttribute(attn_tc_bwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, AtbCfg<MODE>::SMEM));
+  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, dim3(T / 128, B * H), ATB_THREADS, AtbCfg<MODE>::SMEM, m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], m[8], m[9],
+            M, L, Dv, out, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ctx->d_status);
+  return check_launch("attn_tc_bwd");
+}
+// dQ, dK, dV from Q, K, V, O, dO and the forward's row statistics; Dv receives the row products dO . O
+inline int attn_tc_bwd(Ctx* ctx, const float* Q, const float* K, const float* V, const float* O, const float* dO, const float* M, const float* L, float* Dv,
+                       float* dQ, float* dK, float* dV, int B, int T, int D, int H, int causal) {
+  const long rows = (long)B * T * H;
+  GN_LAUNCH(ctx, attn_rowdot_kernel, cdiv(rows, 8), 256, 0, dO, O, Dv, T, D, H, ATC_HD, rows);
+  TcPlanes qp, kp, vp, gp, qt, kt, gt;
+  GN_TRY(attn_tc_planes(ctx, Q, 0, false, B, T, D, H, &qp));
+  GN_TRY(attn_tc_planes(ctx, K, 2, false, B, T, D, H, &kp));
+  GN_TRY(attn_tc_planes(ctx, V, 6, false, B, T, D, H, &vp));
+  GN_TRY(attn_tc_planes(ctx, dO, 8, false, B, T, D, H, &gp));
+  GN_TRY(attn_tc_planes(ctx, Q, 10, true, B, T, D, H, &qt));
+  GN_TRY(attn_tc_planes(ctx, K, 12, true, B, T, D, H, &kt));
+  GN_TRY(attn_tc_planes(ctx, dO, 14, true, B, T, D, H, &gt));
+  GN_TRY(attn_tc_bwd_launch<0>(ctx, qp, gp, kp, vp, kt, M, L, Dv, dQ, B, T, D, H, causal));
+  GN_TRY(attn_tc_bwd_launch<1>(ctx, kp, vp, qp, gp, qt, M, L, Dv, dK, B, T, D, H, causal));
+  GN_TRY(attn_tc_bwd_launch<2>(ctx, kp, kp, qp, qp, gt, M, L, Dv, dV, B, T, D, H, causal));
+  return GN_OK;
+}
+
+}  // namespace gn

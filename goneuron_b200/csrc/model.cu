@@ -24,6 +24,7 @@
 #include "rowops.cuh"
 #include "conv_lstm.cuh"
 #include "attention.cuh"
+#include "attention_tc.cuh"
 #include "nccl_dl.cuh"
 
 namespace gn {
@@ -320,7 +321,8 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
           g.B = bp.wv; g.bias = bp.bv; g.C = l.v.p; GN_TRY(gemm(ctx, g));
         }
         if (use_fused_attention(d)) {
-          GN_TRY(attn_fwd(ctx, D / d.heads, l.q.p, l.k.p, l.v.p, l.att.p, l.att_m.p, l.att_l.p, B, T, D, d.heads, d.causal));
+          if (attn_tc_supported(ctx, D / d.heads, T, B, d.heads, D)) GN_TRY(attn_tc_fwd(ctx, l.q.p, l.k.p, l.v.p, l.att.p, l.att_m.p, l.att_l.p, B, T, D, d.heads, d.causal));
+          else GN_TRY(attn_fwd(ctx, D / d.heads, l.q.p, l.k.p, l.v.p, l.att.p, l.att_m.p, l.att_l.p, B, T, D, d.heads, d.causal));
         } else {
           float* P; GN_TRY(ensure(m, S_ATT0, (size_t)B * d.heads * T * T, &P));
           GN_TRY(attention_forward(m, l, B, P));
@@ -420,7 +422,9 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
   float *dQ, *dK, *dV;
   GN_TRY(ensure(m, S_ND0, ND, &dQ)); GN_TRY(ensure(m, S_ND1, ND, &dK)); GN_TRY(ensure(m, S_ND4, ND, &dV));   // dR2 / comb are dead by now
   if (fused) {
-    GN_TRY(attn_bwd(ctx, hd, l.q.p, l.k.p, l.v.p, l.att.p, dA, l.att_m.p, l.att_l.p, l.att_d.p, dQ, dK, dV, B, T, D, Hh, d.causal));
+    static const bool tc_bwd = [] { const char* e = getenv("GONEURON_CUDA_ATTENTION_BWD"); return !(e && !strcmp(e, "mma")); }();
+    if (tc_bwd && attn_tc_supported(ctx, hd, T, B, Hh, D)) GN_TRY(attn_tc_bwd(ctx, l.q.p, l.k.p, l.v.p, l.att.p, dA, l.att_m.p, l.att_l.p, l.att_d.p, dQ, dK, dV, B, T, D, Hh, d.causal));
+    else GN_TRY(attn_bwd(ctx, hd, l.q.p, l.k.p, l.v.p, l.att.p, dA, l.att_m.p, l.att_l.p, l.att_d.p, dQ, dK, dV, B, T, D, Hh, d.causal));
   } else {
     const long TD = (long)T * D, TT = (long)T * T; const float inv_scale = 1.f / sqrtf((float)hd); const long rows = (long)B * Hh * T;
     GemmDesc g; g.M = T; g.N = T; g.K = hd; g.A = l.q.p; g.sa_m = D; g.sa_k = 1; g.B = l.k.p; g.sb_k = 1; g.sb_n = D;
@@ -910,6 +914,34 @@ int gn_op_adam(gn_ctx* ctx, float* params, const float* grads, float* m1, float*
   GN_TRY(adam_launch(c, dp.p, dg.p, dm.p, dv.p, n, lr, beta1, beta2, eps, t, grad_scale));
   GN_CUDA(cudaStreamSynchronize(c->stream));
   GN_CUDA(copy_d2h(c, params, dp.p, nn * 4)); GN_CUDA(copy_d2h(c, m1, dm.p, nn * 4)); GN_CUDA(copy_d2h(c, v, dv.p, nn * 4));
+  return GN_OK;
+}
+
+int gn_op_attention(gn_ctx* ctx, int engine, int B, int T, int D, int H, int causal, const float* Q, const float* K, const float* V, const float* dO,
+                    float* O, float* M, float* L, float* dQ, float* dK, float* dV) {
+  if (!ctx || !ctx->alive || !Q || !K || !V || !O || B <= 0 || T <= 0 || D <= 0 || H <= 0 || D % H) return fail(GN_ERR_INVALID_ARG, "op_attention: bad argument");
+  if (dO && (!dQ || !dK || !dV)) return fail(GN_ERR_INVALID_ARG, "op_attention: dO given without dQ, dK, dV");
+  Ctx* c = &ctx->c; GN_CUDA(cudaSetDevice(c->device));
+  const int hd = D / H; const size_t n = (size_t)B * T * D, ns = (size_t)B * H * T;
+  if (!attn_fused_supported(hd, D)) return fail(GN_ERR_UNSUPPORTED, "op_attention: head size %d", hd);
+  if (engine == 1 && !attn_tc_supported(c, hd, T, B, H, D)) return fail(GN_ERR_UNSUPPORTED, "tcgen05 attention cannot run this shape (head size %d, T=%d)", hd, T);
+  DevBuf q, k, v, o, m, l, g, dv_, dq, dk, dvv;
+  GN_TRY(q.alloc(n)); GN_TRY(k.alloc(n)); GN_TRY(v.alloc(n)); GN_TRY(o.alloc(n)); GN_TRY(m.alloc(ns)); GN_TRY(l.alloc(ns));
+  GN_CUDA(copy_h2d(c, q.p, Q, n * 4)); GN_CUDA(copy_h2d(c, k.p, K, n * 4)); GN_CUDA(copy_h2d(c, v.p, V, n * 4));
+  if (engine == 1) GN_TRY(attn_tc_fwd(c, q.p, k.p, v.p, o.p, m.p, l.p, B, T, D, H, causal));
+  else GN_TRY(attn_fwd(c, hd, q.p, k.p, v.p, o.p, m.p, l.p, B, T, D, H, causal));
+  if (dO) {
+    GN_TRY(g.alloc(n)); GN_TRY(dv_.alloc(ns)); GN_TRY(dq.alloc(n)); GN_TRY(dk.alloc(n)); GN_TRY(dvv.alloc(n));
+    GN_CUDA(copy_h2d(c, g.p, dO, n * 4));
+    if (engine == 1) GN_TRY(attn_tc_bwd(c, q.p, k.p, v.p, o.p, g.p, m.p, l.p, dv_.p, dq.p, dk.p, dvv.p, B, T, D, H, causal));
+    else GN_TRY(attn_bwd(c, hd, q.p, k.p, v.p, o.p, g.p, m.p, l.p, dv_.p, dq.p, dk.p, dvv.p, B, T, D, H, causal));
+    GN_CUDA(copy_d2h(c, dQ, dq.p, n * 4)); GN_CUDA(copy_d2h(c, dK, dk.p, n * 4)); GN_CUDA(copy_d2h(c, dV, dvv.p, n * 4));
+  }
+  GN_CUDA(copy_d2h(c, O, o.p, n * 4));
+  if (M) GN_CUDA(copy_d2h(c, M, m.p, ns * 4));
+  if (L) GN_CUDA(copy_d2h(c, L, l.p, ns * 4));
+  int st = 0; GN_CUDA(copy_d2h(c, &st, c->d_status, sizeof(int)));
+  if (st != 0) { cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream); cudaStreamSynchronize(c->stream); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
   return GN_OK;
 }
 

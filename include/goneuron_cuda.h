@@ -207,6 +207,15 @@ int gn_op_gemm_nt(gn_ctx* ctx, int engine, int M, int N, int K,
 int gn_op_adam(gn_ctx* ctx, float* params, const float* grads, float* m1, float* v,
                int64_t n, float lr, float beta1, float beta2, float eps, int t, float grad_scale);
 
+/* Multi-head attention of one TransformerBlock on host arrays: Q, K, V, O, dO, dQ, dK, dV are [B*T, D]
+ * row-major with head h in columns [h*D/H, (h+1)*D/H); M and L (may be NULL) receive the row maximum and the
+ * row sum of the softmax, [B*H*T].  Forward: scores q.k/sqrt(hd), causal mask, softmax, weighted sum of v
+ * (transformer.go:470-503); with dO != NULL also the backward pass (transformer.go:589-657).
+ * engine: 0 = warp-level tensor-core kernels, 1 = tcgen05 kernels (head size 64, T a multiple of 128). */
+int gn_op_attention(gn_ctx* ctx, int engine, int B, int T, int D, int H, int causal,
+                    const float* Q, const float* K, const float* V, const float* dO,
+                    float* O, float* M, float* L, float* dQ, float* dK, float* dV);
+
 /* The same product as gn_op_gemm_nt with engine 1 (C = A B^T + bias on the tensor cores), for callers that
  * must not allocate device memory: hosts whose own pool already owns all of HBM, and hosts with a per-step
  * latency budget (cudaMalloc / cudaFree lock the allocator, cudaFree waits for the device).  It has no

@@ -32,6 +32,7 @@ CASES = [
     ("transformer_small", {}, 64, 1),                               # the full small-transformer config
     ("transformer_large", dict(vocab=2000, dim=256, seq_len=64, heads=16, ff_dim=1024, n_blocks=2), 16, 1),
     ("transformer_large", dict(vocab=1000, dim=128, seq_len=80, heads=2, ff_dim=256, n_blocks=1), 6, 1),    # head width 64, T not a multiple of the 64-row block
+    ("transformer_large", dict(vocab=500, dim=128, seq_len=256, heads=2, ff_dim=256, n_blocks=2), 3, 1),    # head width 64, T a multiple of 128: tcgen05 attention
     ("transformer_small", dict(vocab=700, dim=96, seq_len=150, heads=3, ff_dim=192, n_blocks=1), 4, 1),     # head width 32, three key blocks, ragged tail
     ("transformer_small", dict(vocab=300, dim=40, seq_len=20, heads=5, ff_dim=64, n_blocks=1), 4, 1),       # head width 8: the unfused attention path
     ("cnn_bn", {}, 32, 1),                                                                                  # BatchNorm2D
