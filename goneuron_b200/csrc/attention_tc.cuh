@@ -11,9 +11,11 @@
 //   warp 0    : TMA producer (Q once; K and Vt blocks through two stages each)
 //   warp 1    : MMA issuer.  S_j = Q K_j^T (both operands in shared memory) into one of two 64-column TMEM buffers;
 //               O += P_j V_j with P read from TMEM as the A operand and Vt_j from shared memory.
-//   warps 2-5 : one query row per thread (TMEM lane = row): tcgen05.ld of S_j, running maximum and sum,
-//               p = exp(s - m), hi written over S_j in place and lo into a second buffer (tcgen05.st); when a row
-//               maximum moved, the output accumulator is rescaled in TMEM after the previous P V has completed.
+//   warps 2-9 : two threads per query row (TMEM lane = row, 32 of the 64 columns each): tcgen05.ld of S_j, running
+//               maximum (exchanged through shared memory) and sum, p = exp(s - m), hi written over S_j in place and
+//               lo into a second buffer (tcgen05.st); when a row maximum moved, the output accumulator is rescaled
+//               in TMEM after the previous P V has completed.  One warp per scheduler could not keep up with the
+//               tensor pipe (measured: 25 % tensor activity); two do.
 // The issue order S_0, S_1, PV_0, S_2, PV_1, ... keeps the tensor pipe busy with S_{j+1} (and PV_{j-1}) while the
 // softmax of block j runs.  Every wait is bounded; a wait that gives up sets the status word.
 #pragma once
@@ -22,11 +24,11 @@
 
 namespace gn {
 
-constexpr int ATC_BQ = 128, ATC_BK = 64, ATC_HD = 64, ATC_THREADS = 192;
+constexpr int ATC_BQ = 128, ATC_BK = 64, ATC_HD = 64, ATC_THREADS = 320;
 constexpr int ATC_Q_BYTES = 4 * ATC_BQ * 128;   // hi, lo x two chunks of 32 floats: 64 KB
 constexpr int ATC_K_BYTES = 4 * ATC_BK * 128;   // 32 KB
 constexpr int ATC_V_BYTES = 4 * ATC_HD * 128;   // 32 KB
-constexpr int ATC_FWD_SMEM = ATC_Q_BYTES + 2 * (ATC_K_BYTES + ATC_V_BYTES) + 1024 + 256;
+constexpr int ATC_FWD_SMEM = ATC_Q_BYTES + 2 * (ATC_K_BYTES + ATC_V_BYTES) + 1024 + 256 + 2 * 256 * 4;
 // TMEM columns: S / P_hi buffers [0,128), P_lo buffers [128,256), O [256,320)
 constexpr uint32_t ATC_COL_S = 0, ATC_COL_PLO = 128, ATC_COL_O = 256, ATC_TMEM_COLS = 512;
 
@@ -41,6 +43,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
         "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
 }
+__device__ __forceinline__ float fast_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // one lane polls, the warp gets the verdict
@@ -61,6 +64,7 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
   uint8_t* sV = sK + 2 * ATC_K_BYTES;                                 // two stages of ATC_V_BYTES
   uint64_t* bars = (uint64_t*)(sV + 2 * ATC_V_BYTES);
   uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+  float* xch = (float*)(bars + 32);                                   // [2][2][128] row maxima / sums exchanged between the two threads of a row
   // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 p_full | 13 pv_done
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
@@ -69,7 +73,7 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
   const int nblk = causal ? (q0 + ATC_BQ) / ATC_BK : T / ATC_BK;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 14; i++) mbar_init(BAR(i), (i == 11 || i == 12) ? 128 : 1);
+    for (int i = 0; i < 14; i++) mbar_init(BAR(i), (i == 11 || i == 12) ? 256 : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -158,60 +162,53 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
       if (!ok) atomicExch(status, 12);
     }
   } else {
-    const int quad = warp & 3, row = quad * 32 + lane, qi = q0 + row;
-    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
-    float m_run = -INFINITY, l_run = 0.f;
+    // two threads per query row: `half` selects 32 of the 64 columns of a block (and of the accumulator)
+    const int quad = warp & 3, half = (warp - 2) >> 2, row = quad * 32 + lane, qi = q0 + row;
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + 32 * half;
+    const float cs = inv_scale * 1.44269504088896341f;      // scores -> log2 units
+    float m_run = -INFINITY, l_part = 0.f;                  // running maximum (scaled scores, natural units), this thread's part of the row sum
     bool ok = true;
     for (int j = 0; j < nblk; j++) {
-      const int s = j & 1, u = j >> 1, key0 = j * ATC_BK;
+      const int s = j & 1, u = j >> 1, key0 = j * ATC_BK + 32 * half;
       ok &= warp_mbar_wait(BAR(9 + s), u & 1, lane);
       tc_fence_after();
-      uint32_t a[32], b[32];
+      uint32_t a[32], lo[32];
       tmem_ld32(lane_base + ATC_COL_S + s * 64, a);
-      tmem_ld32(lane_base + ATC_COL_S + s * 64 + 32, b);
       tmem_wait_ld();
+      if (causal && j * ATC_BK + ATC_BK - 1 > q0) {         // the block reaches above the diagonal for some row of the tile
+#pragma unroll
+        for (int e = 0; e < 32; e++) if (key0 + e > qi) a[e] = __float_as_uint(-INFINITY);
+      }
       float bm = -INFINITY;
 #pragma unroll
-      for (int e = 0; e < 32; e++) {
-        float va = __uint_as_float(a[e]) * inv_scale, vb = __uint_as_float(b[e]) * inv_scale;
-        if (causal && key0 + e > qi) va = -INFINITY;
-        if (causal && key0 + 32 + e > qi) vb = -INFINITY;
-        a[e] = __float_as_uint(va); b[e] = __float_as_uint(vb);
-        bm = fmaxf(bm, fmaxf(va, vb));
-      }
-      const float m_new = fmaxf(m_run, bm);
-      const float corr = __expf(m_run - m_new);
+      for (int e = 0; e < 32; e++) bm = fmaxf(bm, __uint_as_float(a[e]));
+      float* xb = xch + (j & 1) * 256;
+      xb[half * 128 + row] = bm;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      bm = fmaxf(bm, xb[(half ^ 1) * 128 + row]);
+      const float m_new = fmaxf(m_run, bm * inv_scale);
+      const float corr = fast_ex2((m_run - m_new) * 1.44269504088896341f);
+      const float mneg = -m_new * 1.44269504088896341f;
       float rs = 0.f;
-      uint32_t lo[32];
 #pragma unroll
       for (int e = 0; e < 32; e++) {
-        const float p = __expf(__uint_as_float(a[e]) - m_new); rs += p;
+        const float p = fast_ex2(fmaf(__uint_as_float(a[e]), cs, mneg)); rs += p;
         const uint32_t hi = __float_as_uint(p) & 0xffffe000u;
         a[e] = hi; lo[e] = __float_as_uint(p - __uint_as_float(hi));
       }
       tmem_st32(lane_base + ATC_COL_S + s * 64, a);
       tmem_st32(lane_base + ATC_COL_PLO + s * 64, lo);
-#pragma unroll
-      for (int e = 0; e < 32; e++) {
-        const float p = __expf(__uint_as_float(b[e]) - m_new); rs += p;
-        const uint32_t hi = __float_as_uint(p) & 0xffffe000u;
-        b[e] = hi; lo[e] = __float_as_uint(p - __uint_as_float(hi));
-      }
-      tmem_st32(lane_base + ATC_COL_S + s * 64 + 32, b);
-      tmem_st32(lane_base + ATC_COL_PLO + s * 64 + 32, lo);
-      l_run = l_run * corr + rs; m_run = m_new;
+      l_part = l_part * corr + rs; m_run = m_new;
       // The accumulator may only be touched between P V products.  The wait is unconditional: a parity wait is only
       // unambiguous when no completion of this barrier has been skipped.
       if (j > 0) ok &= warp_mbar_wait(BAR(13), (j - 1) & 1, lane);
       if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
         tc_fence_after();
         tmem_ld32(lane_base + ATC_COL_O, a);
-        tmem_ld32(lane_base + ATC_COL_O + 32, b);
         tmem_wait_ld();
 #pragma unroll
-        for (int e = 0; e < 32; e++) { a[e] = __float_as_uint(__uint_as_float(a[e]) * corr); b[e] = __float_as_uint(__uint_as_float(b[e]) * corr); }
+        for (int e = 0; e < 32; e++) a[e] = __float_as_uint(__uint_as_float(a[e]) * corr);
         tmem_st32(lane_base + ATC_COL_O, a);
-        tmem_st32(lane_base + ATC_COL_O + 32, b);
       }
       tmem_wait_st();
       tc_fence_before();
@@ -220,20 +217,20 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
     ok &= warp_mbar_wait(BAR(13), (nblk - 1) & 1, lane);
     tc_fence_after();
     {
-      uint32_t a[32], b[32];
+      uint32_t a[32];
       tmem_ld32(lane_base + ATC_COL_O, a);
-      tmem_ld32(lane_base + ATC_COL_O + 32, b);
+      float* xb = xch + (nblk & 1) * 256;
+      xb[half * 128 + row] = l_part;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      const float l_run = l_part + xb[(half ^ 1) * 128 + row];
       tmem_wait_ld();
       const float il = 1.f / l_run;
       const int bz = z / H, h = z % H;
-      float* orow = O + ((long)bz * T + qi) * D + (long)h * ATC_HD;
+      float* orow = O + ((long)bz * T + qi) * D + (long)h * ATC_HD + 32 * half;
 #pragma unroll
       for (int e = 0; e < 8; e++)
         *reinterpret_cast<float4*>(orow + 4 * e) = make_float4(__uint_as_float(a[4 * e]) * il, __uint_as_float(a[4 * e + 1]) * il, __uint_as_float(a[4 * e + 2]) * il, __uint_as_float(a[4 * e + 3]) * il);
-#pragma unroll
-      for (int e = 0; e < 8; e++)
-        *reinterpret_cast<float4*>(orow + 32 + 4 * e) = make_float4(__uint_as_float(b[4 * e]) * il, __uint_as_float(b[4 * e + 1]) * il, __uint_as_float(b[4 * e + 2]) * il, __uint_as_float(b[4 * e + 3]) * il);
-      Mst[(long)z * T + qi] = m_run; Lst[(long)z * T + qi] = l_run;
+      if (half == 0) { Mst[(long)z * T + qi] = m_run; Lst[(long)z * T + qi] = l_run; }
     }
     if (!ok && lane == 0) atomicExch(status, 13);
   }
@@ -255,9 +252,9 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
 // ([64 head columns][T]) so that its contraction index runs along the row.  dS (P in MODE 2) goes back to tensor
 // memory as hi/lo and is the A operand of the accumulating product.  TMEM: two sets of {S, dP / dS_hi, dS_lo} so that
 // the score products of block n+1 run under the elementwise work of block n; accumulator in the last 64 columns.
-// Warps: 0 = TMA producer for R1, R2, C1, C2; 1 = MMA issuer; 2-5 = elementwise (one tile row per thread);
-// 6 = TMA producer for C3 (its buffer is released much later than C1 / C2, so it gets its own thread).
-constexpr int ATB_THREADS = 224;
+// Warps: 0 = TMA producer for R1, R2, C1, C2; 1 = MMA issuer; 2-9 = elementwise (two threads per tile row);
+// 10 = TMA producer for C3 (its buffer is released much later than C1 / C2, so it gets its own thread).
+constexpr int ATB_THREADS = 352;
 constexpr int ATB_R_BYTES = 4 * 128 * 128, ATB_C_BYTES = 4 * 64 * 128;      // 64 KB, 32 KB
 template <int MODE> struct AtbCfg {
   static constexpr int NR = MODE == 2 ? 1 : 2;                                 // row-tile operands, score-shaped products
@@ -293,7 +290,7 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
   const int nb = TRANS ? T / 64 - b0 : (causal ? (r0 + 128) / 64 : T / 64);
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 10; i++) mbar_init(BAR(i), (i == 7 || i == 8) ? 128 : 1);
+    for (int i = 0; i < 10; i++) mbar_init(BAR(i), (i == 7 || i == 8) ? 256 : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -332,7 +329,7 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
       }
       if (!ok) atomicExch(status, 21);
     }
-  } else if (warp == 6) {
+  } else if (warp == 10) {
     if (lane == 0) {
       bool ok = true;
       for (int n = 0; n < nb; n++) {
@@ -401,40 +398,41 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
       if (!ok) atomicExch(status, 23);
     }
   } else {
-    const int quad = warp & 3, row = quad * 32 + lane, ri = r0 + row, et = (warp - 2) * 32 + lane;   // et: 0..127 among the elementwise threads
-    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+    // two threads per tile row: `half` selects 32 of the 64 columns of a block (and of the accumulator)
+    const int quad = warp & 3, half = (warp - 2) >> 2, row = quad * 32 + lane, ri = r0 + row, et = (warp - 2) * 32 + lane;   // et: 0..255
+    const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + 32 * half;
     const long sb = (long)z * T;
-    float m_r = 0.f, il_r = 0.f, d_r = 0.f;
-    if (!TRANS) { m_r = Mst[sb + ri]; il_r = 1.f / Lst[sb + ri]; d_r = Dv[sb + ri]; }
+    constexpr float LOG2E = 1.44269504088896341f;
+    const float cs = inv_scale * LOG2E, oscale = MODE == 2 ? 1.f : inv_scale;
+    float mneg_r = 0.f, il_r = 0.f, d_r = 0.f;        // -m log2(e), scale / l, Dv of this row (MODE 0)
+    if (!TRANS) { mneg_r = -Mst[sb + ri] * LOG2E; il_r = oscale / Lst[sb + ri]; d_r = Dv[sb + ri]; }
     bool ok = true;
     for (int n = 0; n < nb; n++) {
       const int s = n & 1, u = n >> 1, c0 = (b0 + n) * 64;
       float* stm = st + s * 192; float* stl = stm + 64; float* std_ = stm + 128;
       if (TRANS) {
-        if (et < 64) { stm[et] = Mst[sb + c0 + et]; stl[et] = 1.f / Lst[sb + c0 + et]; if (MODE == 1) std_[et] = Dv[sb + c0 + et]; }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et < 64) { stm[et] = -Mst[sb + c0 + et] * LOG2E; stl[et] = oscale / Lst[sb + c0 + et]; if (MODE == 1) std_[et] = Dv[sb + c0 + et]; }
+        asm volatile("bar.sync 1, 256;" ::: "memory");
       }
       ok &= warp_mbar_wait(BAR(5 + s), u & 1, lane);
       tc_fence_after();
+      uint32_t a[32], b[32], lo[32];
+      tmem_ld32(lane_base + ATB_COL_S + s * 64, a);
+      if (MODE != 2) tmem_ld32(lane_base + ATB_COL_DP + s * 64, b);
+      tmem_wait_ld();
+      // does the block reach across the diagonal for some row of the tile?
+      const bool diag = causal && (TRANS ? r0 + 127 > c0 : c0 + 63 > r0);
 #pragma unroll
-      for (int c = 0; c < 2; c++) {
-        uint32_t a[32], b[32], lo[32];
-        tmem_ld32(lane_base + ATB_COL_S + s * 64 + 32 * c, a);
-        if (MODE != 2) tmem_ld32(lane_base + ATB_COL_DP + s * 64 + 32 * c, b);
-        tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; e++) {
-          const int col = 32 * c + e, ci = c0 + col;
-          const bool masked = causal && (TRANS ? ri > ci : ci > ri);
-          const float mm = TRANS ? stm[col] : m_r, il = TRANS ? stl[col] : il_r;
-          float v = masked ? 0.f : __expf(__uint_as_float(a[e]) * inv_scale - mm) * il;          // P
-          if (MODE != 2) v = v * (__uint_as_float(b[e]) - (TRANS ? std_[col] : d_r)) * inv_scale;   // dS
-          const uint32_t hi = __float_as_uint(v) & 0xffffe000u;
-          a[e] = hi; lo[e] = __float_as_uint(v - __uint_as_float(hi));
-        }
-        tmem_st32(lane_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64 + 32 * c, a);
-        tmem_st32(lane_base + ATB_COL_LO + s * 64 + 32 * c, lo);
+      for (int e = 0; e < 32; e++) {
+        const int col = 32 * half + e;
+        float v = fast_ex2(fmaf(__uint_as_float(a[e]), cs, TRANS ? stm[col] : mneg_r)) * (TRANS ? stl[col] : il_r);   // P (times 1/sqrt(hd) for dS)
+        if (MODE != 2) v *= __uint_as_float(b[e]) - (TRANS ? std_[col] : d_r);                                        // dS
+        if (diag && (TRANS ? ri > c0 + col : c0 + col > ri)) v = 0.f;
+        const uint32_t hi = __float_as_uint(v) & 0xffffe000u;
+        a[e] = hi; lo[e] = __float_as_uint(v - __uint_as_float(hi));
       }
+      tmem_st32(lane_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, a);
+      tmem_st32(lane_base + ATB_COL_LO + s * 64, lo);
       tmem_wait_st();
       tc_fence_before();
       mbar_arrive(BAR(7 + s));
@@ -442,18 +440,14 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
     ok &= warp_mbar_wait(BAR(9), 0, lane);
     tc_fence_after();
     {
-      uint32_t a[32], b[32];
+      uint32_t a[32];
       tmem_ld32(lane_base + ATB_COL_ACC, a);
-      tmem_ld32(lane_base + ATB_COL_ACC + 32, b);
       tmem_wait_ld();
       const int bz = z / H, h = z % H;
-      float* orow = Out + ((long)bz * T + ri) * D + (long)h * ATC_HD;
+      float* orow = Out + ((long)bz * T + ri) * D + (long)h * ATC_HD + 32 * half;
 #pragma unroll
       for (int e = 0; e < 8; e++)
         *reinterpret_cast<float4*>(orow + 4 * e) = make_float4(__uint_as_float(a[4 * e]), __uint_as_float(a[4 * e + 1]), __uint_as_float(a[4 * e + 2]), __uint_as_float(a[4 * e + 3]));
-#pragma unroll
-      for (int e = 0; e < 8; e++)
-        *reinterpret_cast<float4*>(orow + 32 + 4 * e) = make_float4(__uint_as_float(b[4 * e]), __uint_as_float(b[4 * e + 1]), __uint_as_float(b[4 * e + 2]), __uint_as_float(b[4 * e + 3]));
     }
     if (!ok && lane == 0) atomicExch(status, 24);
   }
