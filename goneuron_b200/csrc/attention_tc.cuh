@@ -7,6 +7,7 @@
 // Operands: hi/lo planes (3xTF32) written by the split kernels of gemm_tc.cuh, one problem per (batch, head):
 //   Qp, Kp : [B*H][T][64]   (contraction over the head dimension is along the row)
 //   Vt     : [B*H][64][T]   (transposed, so that the contraction over the keys is along the row as well)
+// (attn_split_kernel writes both kinds from one read of the tensor)
 // and fetched by TMA into 128-byte-swizzled tiles.  One CTA = 128 query rows of one head; key blocks of 64.
 //   warp 0    : TMA producer (Q once; K and Vt blocks through two stages each)
 //   warp 1    : MMA issuer.  S_j = Q K_j^T (both operands in shared memory) into one of two 64-column TMEM buffers;
@@ -473,20 +474,59 @@ inline bool attn_tc_supported(Ctx* ctx, int hd, int T, int B, int H, int D) {
   static const bool off = [] { const char* e = getenv("GONEURON_CUDA_ATTENTION"); return e && !strcmp(e, "mma"); }();
   return !off && ctx->tc_ok && hd == ATC_HD && T % ATC_BQ == 0 && (long)B * H <= 65535 && D % 4 == 0;
 }
-// planes of a [B*T, D] tensor per (batch, head): rows [Z][T][64] or transposed [Z][64][T]
-inline int attn_tc_planes(Ctx* ctx, const float* X, int slot, bool transposed, int B, int T, int D, int H, TcPlanes* out) {
+// Operand planes of one [B*T, D] tensor for all (batch, head) problems, from ONE read of the tensor:
+//   row planes  [Z][T][64]  (ROWS)  and / or  transposed planes [Z][64][T]  (COLS),   z = batch * H + head.
+// One CTA = a 64 x 64 tile (64 tokens of one head); the transposition goes through shared memory.
+template <bool ROWS, bool COLS>
+__global__ void __launch_bounds__(256) attn_split_kernel(const float* __restrict__ X, float* __restrict__ rhi, float* __restrict__ rlo,
+                                                         float* __restrict__ chi, float* __restrict__ clo, int T, int D, int H) {
+  __shared__ float tile[64][65];
+  const int z = blockIdx.y, b = z / H, h = z % H, t0 = blockIdx.x * 64, i = threadIdx.x;
+  const int c4 = i & 15, r0 = i >> 4;
+  float4 x[4];
+#pragma unroll
+  for (int r = 0; r < 4; r++) x[r] = *reinterpret_cast<const float4*>(X + ((long)b * T + t0 + r0 + 16 * r) * D + (long)h * 64 + c4 * 4);
+#pragma unroll
+  for (int r = 0; r < 4; r++) {
+    const int row = r0 + 16 * r;
+    if (ROWS) {
+      const float4 hv = make_float4(tf32_round(x[r].x), tf32_round(x[r].y), tf32_round(x[r].z), tf32_round(x[r].w));
+      const long o = ((long)z * T + t0 + row) * 64 + c4 * 4;
+      *reinterpret_cast<float4*>(rhi + o) = hv;
+      *reinterpret_cast<float4*>(rlo + o) = make_float4(x[r].x - hv.x, x[r].y - hv.y, x[r].z - hv.z, x[r].w - hv.w);
+    }
+    if (COLS) { tile[row][c4 * 4] = x[r].x; tile[row][c4 * 4 + 1] = x[r].y; tile[row][c4 * 4 + 2] = x[r].z; tile[row][c4 * 4 + 3] = x[r].w; }
+  }
+  if (COLS) {
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < 4; r++) {
+      const int d = r0 + 16 * r;                          // head column -> plane row; c4 -> 4 consecutive tokens
+      const float4 v = make_float4(tile[c4 * 4][d], tile[c4 * 4 + 1][d], tile[c4 * 4 + 2][d], tile[c4 * 4 + 3][d]);
+      const float4 hv = make_float4(tf32_round(v.x), tf32_round(v.y), tf32_round(v.z), tf32_round(v.w));
+      const long o = ((long)z * 64 + d) * T + t0 + c4 * 4;
+      *reinterpret_cast<float4*>(chi + o) = hv;
+      *reinterpret_cast<float4*>(clo + o) = make_float4(v.x - hv.x, v.y - hv.y, v.z - hv.z, v.w - hv.w);
+    }
+  }
+}
+// slot / slot + 1 receive the row planes, cslot / cslot + 1 the transposed ones (a negative slot = not wanted)
+inline int attn_tc_planes(Ctx* ctx, const float* X, int slot, int cslot, int B, int T, int D, int H, TcPlanes* rows, TcPlanes* cols) {
   const int Z = B * H; const size_t n = (size_t)Z * T * ATC_HD;
-  float *hi, *lo; GN_TRY(attn_tc_buf(ctx, slot, n, &hi)); GN_TRY(attn_tc_buf(ctx, slot + 1, n, &lo));
-  TcSrc src; src.p = X; src.b1 = (long)T * D; src.b2 = ATC_HD; src.batch2 = H;
-  if (!transposed) { src.s_r = D; src.s_c = 1; *out = TcPlanes{hi, lo, T, ATC_HD, ATC_HD, Z}; }
-  else { src.s_r = 1; src.s_c = D; *out = TcPlanes{hi, lo, ATC_HD, T, T, Z}; }
-  return tc_split(ctx, src, *out);
+  float *rh = nullptr, *rl = nullptr, *ch = nullptr, *cl = nullptr;
+  if (slot >= 0) { GN_TRY(attn_tc_buf(ctx, slot, n, &rh)); GN_TRY(attn_tc_buf(ctx, slot + 1, n, &rl)); *rows = TcPlanes{rh, rl, T, ATC_HD, ATC_HD, Z}; }
+  if (cslot >= 0) { GN_TRY(attn_tc_buf(ctx, cslot, n, &ch)); GN_TRY(attn_tc_buf(ctx, cslot + 1, n, &cl)); *cols = TcPlanes{ch, cl, ATC_HD, T, T, Z}; }
+  const dim3 grid(T / 64, Z);
+  if (slot >= 0 && cslot >= 0) GN_LAUNCH(ctx, (attn_split_kernel<true, true>), grid, 256, 0, X, rh, rl, ch, cl, T, D, H);
+  else if (slot >= 0) GN_LAUNCH(ctx, (attn_split_kernel<true, false>), grid, 256, 0, X, rh, rl, ch, cl, T, D, H);
+  else GN_LAUNCH(ctx, (attn_split_kernel<false, true>), grid, 256, 0, X, rh, rl, ch, cl, T, D, H);
+  return check_launch("attn_split");
 }
 inline int attn_tc_fwd(Ctx* ctx, const float* Q, const float* K, const float* V, float* O, float* M, float* L, int B, int T, int D, int H, int causal) {
   TcPlanes pq, pk, pv;
-  GN_TRY(attn_tc_planes(ctx, Q, 0, false, B, T, D, H, &pq));
-  GN_TRY(attn_tc_planes(ctx, K, 2, false, B, T, D, H, &pk));
-  GN_TRY(attn_tc_planes(ctx, V, 4, true, B, T, D, H, &pv));
+  GN_TRY(attn_tc_planes(ctx, Q, 0, -1, B, T, D, H, &pq, nullptr));
+  GN_TRY(attn_tc_planes(ctx, K, 2, -1, B, T, D, H, &pk, nullptr));
+  GN_TRY(attn_tc_planes(ctx, V, -1, 4, B, T, D, H, nullptr, &pv));
   CUtensorMap mQh, mQl, mKh, mKl, mVh, mVl;
   GN_TRY(tc_make_map(ctx, &mQh, pq, pq.hi, ATC_BQ)); GN_TRY(tc_make_map(ctx, &mQl, pq, pq.lo, ATC_BQ));
   GN_TRY(tc_make_map(ctx, &mKh, pk, pk.hi, ATC_BK)); GN_TRY(tc_make_map(ctx, &mKl, pk, pk.lo, ATC_BK));
@@ -517,13 +557,10 @@ inline int attn_tc_bwd(Ctx* ctx, const float* Q, const float* K, const float* V,
   const long rows = (long)B * T * H;
   GN_LAUNCH(ctx, attn_rowdot_kernel, cdiv(rows, 8), 256, 0, dO, O, Dv, T, D, H, ATC_HD, rows);
   TcPlanes qp, kp, vp, gp, qt, kt, gt;
-  GN_TRY(attn_tc_planes(ctx, Q, 0, false, B, T, D, H, &qp));
-  GN_TRY(attn_tc_planes(ctx, K, 2, false, B, T, D, H, &kp));
-  GN_TRY(attn_tc_planes(ctx, V, 6, false, B, T, D, H, &vp));
-  GN_TRY(attn_tc_planes(ctx, dO, 8, false, B, T, D, H, &gp));
-  GN_TRY(attn_tc_planes(ctx, Q, 10, true, B, T, D, H, &qt));
-  GN_TRY(attn_tc_planes(ctx, K, 12, true, B, T, D, H, &kt));
-  GN_TRY(attn_tc_planes(ctx, dO, 14, true, B, T, D, H, &gt));
+  GN_TRY(attn_tc_planes(ctx, Q, 0, 10, B, T, D, H, &qp, &qt));
+  GN_TRY(attn_tc_planes(ctx, K, 2, 12, B, T, D, H, &kp, &kt));
+  GN_TRY(attn_tc_planes(ctx, V, 6, -1, B, T, D, H, &vp, nullptr));
+  GN_TRY(attn_tc_planes(ctx, dO, 8, 14, B, T, D, H, &gp, &gt));
   GN_TRY(attn_tc_bwd_launch<0>(ctx, qp, gp, kp, vp, kt, M, L, Dv, dQ, B, T, D, H, causal));
   GN_TRY(attn_tc_bwd_launch<1>(ctx, kp, vp, qp, gp, qt, M, L, Dv, dK, B, T, D, H, causal));
   GN_TRY(attn_tc_bwd_launch<2>(ctx, kp, kp, qp, qp, gt, M, L, Dv, dV, B, T, D, H, causal));

@@ -109,7 +109,7 @@ struct TcParams {
 // (TMEM lane = row), 32 consecutive columns per tcgen05.ld, written as 8 float4.  Bias, residual and gate values
 // of a chunk are fetched before the TMEM wait so that their latency overlaps.  `acc_main` / `acc_cross` are the
 // TMEM column offsets of the two accumulators of this tile.
-template <int BN>
+template <int BN, bool MERGED = false>
 __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tmem_base, uint32_t acc_main, uint32_t acc_cross,
                                                  int m0, int n0, int z, int quad, int lane, int nkb) {
     const int z1 = z / ep.batch2, z2 = z % ep.batch2;
@@ -128,7 +128,11 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
       if (nkb > 0) {
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
         tmem_ld32(taddr + acc_main, r);
-        tmem_ld32(taddr + acc_cross, q);
+        if (!MERGED) tmem_ld32(taddr + acc_cross, q);
+        else {
+#pragma unroll
+          for (int j = 0; j < 32; j++) q[j] = 0u;
+        }
       }
       if (vec) {
         float4 rv[8], mv[8];
@@ -277,15 +281,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant
 //   tfull[b]/tempty[b] MMA <-> epilogue per TMEM slot
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 
-template <int BN, int BK, int NSLOTS>
+template <int BN, int BK, int NSLOTS, bool MERGED = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAlo,
                        const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBlo, TcParams ep,
                        int tiles_m, int tiles_n, int total_tiles) {
   using Cfg = TcCfg<BN, BK>;
-  static_assert(NSLOTS * 2 * BN <= 512 && (NSLOTS == 1 || NSLOTS == 2), "accumulator slots must fit the 512 TMEM columns");
+  // MERGED: the three partial products of a tile share one accumulator (half the tensor memory per tile, so a 256-wide
+  // tile still has two slots; slightly larger truncation error, see the header)
+  constexpr int ACC_PER_TILE = MERGED ? 1 : 2;
+  static_assert(NSLOTS * ACC_PER_TILE * BN <= 512 && (NSLOTS == 1 || NSLOTS == 2), "accumulator slots must fit the 512 TMEM columns");
   constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, B_BYTES = Cfg::B_BYTES, A_BYTES = Cfg::A_BYTES;
-  constexpr uint32_t TMEM_COLS = NSLOTS * 2 * BN;
+  constexpr uint32_t TMEM_COLS = NSLOTS * ACC_PER_TILE * BN;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);       // full[S], empty[S], tfull[2], tempty[2]
@@ -346,7 +353,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_
         const uint32_t slot = NSLOTS == 2 ? (lt & 1) : 0, u = NSLOTS == 2 ? (lt >> 1) : lt; lt++;
         ok &= mbar_wait(tempty0 + 8 * slot, (u & 1) ^ 1);          // slot drained by the epilogue (passes at once the first time)
         tc_fence_after();
-        const uint32_t acc_main = tmem_base + slot * 2 * BN, acc_cross = acc_main + BN;
+        const uint32_t acc_main = tmem_base + slot * ACC_PER_TILE * BN, acc_cross = MERGED ? acc_main : acc_main + BN;
         for (int i = 0; i < nkb; i++, it++) {
           const uint32_t s = it % STAGES, use = it / STAGES;
           ok &= mbar_wait(full0 + 8 * s, use & 1);
@@ -360,7 +367,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_
             const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
             tc_mma_tf32(acc_cross, alo + adv, bhi + adv, idesc, acc);
             tc_mma_tf32(acc_cross, ahi + adv, blo + adv, idesc, 1u);
-            tc_mma_tf32(acc_main, ahi + adv, bhi + adv, idesc, acc);
+            tc_mma_tf32(acc_main, ahi + adv, bhi + adv, idesc, MERGED ? 1u : acc);
           }
           tc_commit(empty0 + 8 * s);
         }
@@ -378,7 +385,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok && lane == 0) atomicExch(ep.status, 3);
       tc_fence_after();
-      tc_epilogue_tile<BN>(ep, tmem_base, slot * 2 * BN, slot * 2 * BN + BN, m0, n0, z, quad, lane, nkb);
+      tc_epilogue_tile<BN, MERGED>(ep, tmem_base, slot * ACC_PER_TILE * BN, slot * ACC_PER_TILE * BN + BN, m0, n0, z, quad, lane, nkb);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * slot);
@@ -395,20 +402,30 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_
 // (z, r, c) at p + (z / batch2) * b1 + (z % batch2) * b2 + r * s_r + c * s_c.  One of s_r, s_c is 1:
 // s_c == 1 reads rows directly; s_r == 1 (the operand is the transpose of what is stored) goes through a shared tile.
 struct TcSrc { const float* p; long s_r, s_c, b1, b2; int batch2; };
-__global__ void split_rows_kernel(TcSrc s, int rows, int cols, float* __restrict__ hi, float* __restrict__ lo, int ldp) {
-  // one float4 per thread; blockIdx.y = problem index
-  const int z = blockIdx.y, ldp4 = ldp >> 2;
-  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= rows * ldp4) return;
-  const int r = idx / ldp4, c = (idx - r * ldp4) << 2;
-  const float* src = s.p + (z / s.batch2) * s.b1 + (z % s.batch2) * s.b2 + (long)r * s.s_r + c;
-  float4 x;
-  if (c + 3 < cols && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) x = *reinterpret_cast<const float4*>(src);
-  else { x.x = c < cols ? src[0] : 0.f; x.y = c + 1 < cols ? src[1] : 0.f; x.z = c + 2 < cols ? src[2] : 0.f; x.w = c + 3 < cols ? src[3] : 0.f; }
-  float4 h = make_float4(tf32_round(x.x), tf32_round(x.y), tf32_round(x.z), tf32_round(x.w));
-  float4 l = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
-  const long o = ((long)z * rows + r) * ldp + c;
-  *reinterpret_cast<float4*>(hi + o) = h; *reinterpret_cast<float4*>(lo + o) = l;
+__global__ void __launch_bounds__(256) split_rows_kernel(TcSrc s, int rows, int cols, float* __restrict__ hi, float* __restrict__ lo, int ldp) {
+  // four float4 per thread, all loads issued before the first store; blockIdx.y = problem index
+  const int z = blockIdx.y, ldp4 = ldp >> 2, total = rows * ldp4;
+  const float* base = s.p + (z / s.batch2) * s.b1 + (z % s.batch2) * s.b2;
+  const int idx0 = blockIdx.x * 1024 + threadIdx.x;
+  float4 x[4]; long o[4];
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    const int idx = idx0 + 256 * k;
+    o[k] = -1;
+    if (idx >= total) continue;
+    const int r = idx / ldp4, c = (idx - r * ldp4) << 2;
+    const float* src = base + (long)r * s.s_r + c;
+    if (c + 3 < cols && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) x[k] = *reinterpret_cast<const float4*>(src);
+    else { x[k].x = c < cols ? src[0] : 0.f; x[k].y = c + 1 < cols ? src[1] : 0.f; x[k].z = c + 2 < cols ? src[2] : 0.f; x[k].w = c + 3 < cols ? src[3] : 0.f; }
+    o[k] = ((long)z * rows + r) * ldp + c;
+  }
+#pragma unroll
+  for (int k = 0; k < 4; k++) {
+    if (o[k] < 0) continue;
+    const float4 h = make_float4(tf32_round(x[k].x), tf32_round(x[k].y), tf32_round(x[k].z), tf32_round(x[k].w));
+    *reinterpret_cast<float4*>(hi + o[k]) = h;
+    *reinterpret_cast<float4*>(lo + o[k]) = make_float4(x[k].x - h.x, x[k].y - h.y, x[k].z - h.z, x[k].w - h.w);
+  }
 }
 __global__ void split_cols_kernel(TcSrc s, int rows, int cols, float* __restrict__ hi, float* __restrict__ lo, int ldp) {
   __shared__ float t[32][33];
@@ -446,6 +463,8 @@ inline void tc_init(Ctx* ctx) {
   ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<256, 32, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256, 32>::SMEM_BYTES) == cudaSuccess;
   ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<128, 32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128, 32>::SMEM_BYTES) == cudaSuccess;
   ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<64, 32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64, 32>::SMEM_BYTES) == cudaSuccess;
+  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<256, 16, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256, 16>::SMEM_BYTES) == cudaSuccess;
+  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<256, 32, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<256, 32>::SMEM_BYTES) == cudaSuccess;
   if (!ok) { cudaGetLastError(); return; }
   ctx->encode_tiled = fn; ctx->tc_ok = true;
 }
@@ -465,7 +484,7 @@ inline int tc_make_map(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const floa
 inline int tc_split(Ctx* ctx, const TcSrc& src, const TcPlanes& p) {
   if (src.s_c == 1) {
     if (p.nbatch > 65535) return fail(GN_ERR_UNSUPPORTED, "tc_split: more than 65535 problems in a batch");
-    GN_LAUNCH(ctx, split_rows_kernel, dim3(cdiv((long)p.rows * (p.ldp >> 2), 256), p.nbatch), 256, 0, src, p.rows, p.K, p.hi, p.lo, p.ldp);
+    GN_LAUNCH(ctx, split_rows_kernel, dim3(cdiv((long)p.rows * (p.ldp >> 2), 1024), p.nbatch), 256, 0, src, p.rows, p.K, p.hi, p.lo, p.ldp);
   } else if (src.s_r == 1) {
     GN_LAUNCH(ctx, split_cols_kernel, dim3(cdiv(p.ldp, 32), cdiv(p.rows, 32), p.nbatch), dim3(32, 8), 0, src, p.rows, p.K, p.hi, p.lo, p.ldp);
   } else return fail(GN_ERR_UNSUPPORTED, "tc_split: neither stride of the operand is 1");
@@ -481,7 +500,7 @@ inline int tc_launch_bn(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const Tc
   GN_LAUNCH(ctx, (gemm_tc_kernel<BN, BK>), grid, TC_THREADS, (TcCfg<BN, BK>::SMEM_BYTES), mAh, mAl, mBh, mBl, ep);
   return check_launch("gemm_tc");
 }
-template <int BN, int NSLOTS, int BK = 32>
+template <int BN, int NSLOTS, int BK = 32, bool MERGED = false>
 inline int tc_launch_persist(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep) {
   CUtensorMap mAh, mAl, mBh, mBl;
   GN_TRY(tc_make_map(ctx, &mAh, A, A.hi, TC_BM, BK)); GN_TRY(tc_make_map(ctx, &mAl, A, A.lo, TC_BM, BK));
@@ -489,7 +508,7 @@ inline int tc_launch_persist(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, con
   const int tiles_m = cdiv(ep.M, TC_BM), tiles_n = cdiv(ep.N, BN); const long total = (long)tiles_m * tiles_n * A.nbatch;
   if (total > 0x7fffffffL) return fail(GN_ERR_UNSUPPORTED, "too many output tiles");
   const unsigned grid = (unsigned)std::min<long>(total, ctx->sm_count);
-  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN, BK, NSLOTS>), grid, TC_THREADS, (TcCfg<BN, BK>::SMEM_BYTES), mAh, mAl, mBh, mBl, ep, tiles_m, tiles_n, (int)total);
+  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN, BK, NSLOTS, MERGED>), grid, TC_THREADS, (TcCfg<BN, BK>::SMEM_BYTES), mAh, mAl, mBh, mBl, ep, tiles_m, tiles_n, (int)total);
   return check_launch("gemm_tc_persist");
 }
 // C[z] = A[z] * B[z]^T from prepared planes; the N tile follows the output width.
@@ -508,6 +527,8 @@ inline int tc_launch(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcPar
   static const int persist = [] { const char* e = getenv("GONEURON_TC_PERSIST"); return e ? atoi(e) : 1; }();
   if (persist && !force_bn) {
     if (ep.N <= 64) return tc_launch_persist<64, 2>(ctx, A, B, ep);
+    if (ep.N > 128 && persist == 4) return tc_launch_persist<256, 2, 16, true>(ctx, A, B, ep);
+    if (ep.N > 128 && persist == 5) return tc_launch_persist<256, 2, 32, true>(ctx, A, B, ep);
     if (ep.N <= 128 || persist != 3) return tc_launch_persist<128, 2>(ctx, A, B, ep);   // measured faster than the one-slot 256-wide tile
     return tc_launch_persist<256, 1>(ctx, A, B, ep);
   }
