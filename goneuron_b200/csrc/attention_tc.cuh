@@ -8,7 +8,7 @@
 //   Qp, Kp : [B*H][T][64]   (contraction over the head dimension is along the row)
 //   Vt     : [B*H][64][T]   (transposed, so that the contraction over the keys is along the row as well)
 // (attn_split_kernel writes both kinds from one read of the tensor)
-// and fetched by TMA into 128-byte-swizzled tiles.  One CTA = 128 query rows of one head; key blocks of 64.
+// and fetched by TMA into 128-byte-swizzled tiles.  One tile = 128 query rows of one head; key blocks of 64.
 //   warp 0    : TMA producer (Q once; K and Vt blocks through two stages each)
 //   warp 1    : MMA issuer.  S_j = Q K_j^T (both operands in shared memory) into one of two 64-column TMEM buffers;
 //               O += P_j V_j with P read from TMEM as the A operand and Vt_j from shared memory.
@@ -30,7 +30,7 @@ constexpr int ATC_Q_BYTES = 4 * ATC_BQ * 128;   // hi, lo x two chunks of 32 flo
 constexpr int ATC_K_BYTES = 4 * ATC_BK * 128;   // 32 KB
 constexpr int ATC_V_BYTES = 4 * ATC_HD * 128;   // 32 KB
 constexpr int ATC_FWD_SMEM = ATC_Q_BYTES + 2 * (ATC_K_BYTES + ATC_V_BYTES) + 1024 + 256 + 2 * 256 * 4;
-// TMEM columns: S / P_hi buffers [0,128), P_lo buffers [128,256), O [256,320)
+// TMEM columns: S / P_hi buffers [0,128), P_lo buffers [128,256), two output accumulators [256,384)
 constexpr uint32_t ATC_COL_S = 0, ATC_COL_PLO = 128, ATC_COL_O = 256, ATC_TMEM_COLS = 512;
 
 __device__ __forceinline__ void tc_mma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -54,27 +54,39 @@ __device__ __forceinline__ bool warp_mbar_wait(uint32_t bar, uint32_t parity, in
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
+// Persistent: gridDim.x CTAs (one per SM) walk the tiles; tile id = blockIdx.x + i * gridDim.x names (batch*head, query
+// block), the query block being rotated by i so that every CTA sees short and long causal tiles alike (gridDim.x is a
+// multiple of the number of query blocks).  All counters below run across tiles, so the barriers' phases simply continue:
+// the producer prefetches the next tile's Q as soon as the last score product of the current tile has completed, and
+// the first score products of the next tile run while the elementwise warps finish the current tile and write it out
+// (the output accumulator is double-buffered for that).
 __global__ void __launch_bounds__(ATC_THREADS, 1)
 attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constant__ CUtensorMap mQl, const __grid_constant__ CUtensorMap mKh,
                    const __grid_constant__ CUtensorMap mKl, const __grid_constant__ CUtensorMap mVh, const __grid_constant__ CUtensorMap mVl,
-                   float* __restrict__ O, float* __restrict__ Mst, float* __restrict__ Lst, int T, int D, int H, int causal, float inv_scale, int* status) {
+                   float* __restrict__ O, float* __restrict__ Mst, float* __restrict__ Lst, int T, int D, int H, int causal, float inv_scale,
+                   int ntiles, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
   uint8_t* sK = smem + ATC_Q_BYTES;                                   // two stages of ATC_K_BYTES
   uint8_t* sV = sK + 2 * ATC_K_BYTES;                                 // two stages of ATC_V_BYTES
   uint64_t* bars = (uint64_t*)(sV + 2 * ATC_V_BYTES);
-  uint32_t* tmem_slot = (uint32_t*)(bars + 16);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 20);
   float* xch = (float*)(bars + 32);                                   // [2][2][128] row maxima / sums exchanged between the two threads of a row
   // barriers: 0 q_full | 1,2 k_full | 3,4 k_empty | 5,6 v_full | 7,8 v_empty | 9,10 s_full | 11,12 p_full | 13 pv_done
+  //           14 q_empty | 15,16 o_free
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = (int)gridDim.x - 1 - (int)blockIdx.x, z = blockIdx.y, q0 = qb * ATC_BQ;   // long tiles first
-  const int nblk = causal ? (q0 + ATC_BQ) / ATC_BK : T / ATC_BK;
+  const int ntq = T / ATC_BQ;
+  // tile -> problem z, first query row, number of key blocks
+  auto decode = [&](int id, int i, int& z, int& q0, int& nblk) {
+    z = id / ntq; q0 = ((id % ntq + i) % ntq) * ATC_BQ;
+    nblk = causal ? (q0 + ATC_BQ) / ATC_BK : T / ATC_BK;
+  };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 14; i++) mbar_init(BAR(i), (i == 11 || i == 12) ? 256 : 1);
+    for (int i = 0; i < 17; i++) mbar_init(BAR(i), (i == 11 || i == 12 || i == 15 || i == 16) ? 256 : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -88,150 +100,169 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
-      bool ok = true;
-      mbar_expect_tx(BAR(0), ATC_Q_BYTES);
-      for (int c = 0; c < 2; c++) {
-        tma_load_3d(smem_u32(sQ + c * 16384), &mQh, c * 32, q0, z, BAR(0));
-        tma_load_3d(smem_u32(sQ + 32768 + c * 16384), &mQl, c * 32, q0, z, BAR(0));
-      }
-      for (int j = 0; j < nblk; j++) {
-        const int s = j & 1, u = j >> 1;
-        if (u > 0) ok &= mbar_wait(BAR(3 + s), (u - 1) & 1);
-        mbar_expect_tx(BAR(1 + s), ATC_K_BYTES);
+      bool ok = true; uint32_t g = 0;
+      for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+        int z, q0, nblk; decode(id, tt, z, q0, nblk);
+        if (tt > 0) ok &= mbar_wait(BAR(14), (tt - 1) & 1);
+        mbar_expect_tx(BAR(0), ATC_Q_BYTES);
         for (int c = 0; c < 2; c++) {
-          tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + c * 8192), &mKh, c * 32, j * ATC_BK, z, BAR(1 + s));
-          tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + 16384 + c * 8192), &mKl, c * 32, j * ATC_BK, z, BAR(1 + s));
+          tma_load_3d(smem_u32(sQ + c * 16384), &mQh, c * 32, q0, z, BAR(0));
+          tma_load_3d(smem_u32(sQ + 32768 + c * 16384), &mQl, c * 32, q0, z, BAR(0));
         }
-        if (u > 0) ok &= mbar_wait(BAR(7 + s), (u - 1) & 1);
-        mbar_expect_tx(BAR(5 + s), ATC_V_BYTES);
-        for (int c = 0; c < 2; c++) {
-          tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + c * 8192), &mVh, j * ATC_BK + c * 32, 0, z, BAR(5 + s));
-          tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + 16384 + c * 8192), &mVl, j * ATC_BK + c * 32, 0, z, BAR(5 + s));
+        for (int j = 0; j < nblk; j++, g++) {
+          const uint32_t s = g & 1, u = g >> 1;
+          if (u > 0) ok &= mbar_wait(BAR(3 + s), (u - 1) & 1);
+          mbar_expect_tx(BAR(1 + s), ATC_K_BYTES);
+          for (int c = 0; c < 2; c++) {
+            tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + c * 8192), &mKh, c * 32, j * ATC_BK, z, BAR(1 + s));
+            tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + 16384 + c * 8192), &mKl, c * 32, j * ATC_BK, z, BAR(1 + s));
+          }
+          if (u > 0) ok &= mbar_wait(BAR(7 + s), (u - 1) & 1);
+          mbar_expect_tx(BAR(5 + s), ATC_V_BYTES);
+          for (int c = 0; c < 2; c++) {
+            tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + c * 8192), &mVh, j * ATC_BK + c * 32, 0, z, BAR(5 + s));
+            tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + 16384 + c * 8192), &mVl, j * ATC_BK + c * 32, 0, z, BAR(5 + s));
+          }
         }
       }
       if (!ok) atomicExch(status, 11);
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      bool ok = true;
+      bool ok = true; uint32_t g0 = 0;
       constexpr uint32_t idesc = make_idesc(ATC_BQ, 64);
-      auto issue_s = [&](int j) {
-        const int s = j & 1, u = j >> 1;
-        ok &= mbar_wait(BAR(1 + s), u & 1);
-        tc_fence_after();
-        const uint32_t acc = tmem_base + ATC_COL_S + s * 64;
-        const uint32_t kb = smem_u32(sK + s * ATC_K_BYTES), qa = smem_u32(sQ);
+      for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+        int z, q0, nblk; decode(id, tt, z, q0, nblk);
+        const uint32_t ob = tt & 1;
+        auto issue_s = [&](int j) {
+          const uint32_t g = g0 + j, s = g & 1, u = g >> 1;
+          ok &= mbar_wait(BAR(1 + s), u & 1);
+          tc_fence_after();
+          const uint32_t acc = tmem_base + ATC_COL_S + s * 64;
+          const uint32_t kb = smem_u32(sK + s * ATC_K_BYTES), qa = smem_u32(sQ);
 #pragma unroll
-        for (int c = 0; c < 2; c++)
+          for (int c = 0; c < 2; c++)
 #pragma unroll
-          for (int k = 0; k < 4; k++) {
-            const uint64_t adv = (uint64_t)(2 * k);
-            const uint64_t ah = make_desc<32>(qa + c * 16384) + adv, al = make_desc<32>(qa + 32768 + c * 16384) + adv;
-            const uint64_t bh = make_desc<32>(kb + c * 8192) + adv, bl = make_desc<32>(kb + 16384 + c * 8192) + adv;
-            tc_mma_tf32(acc, al, bh, idesc, (c | k) ? 1u : 0u);
-            tc_mma_tf32(acc, ah, bl, idesc, 1u);
-            tc_mma_tf32(acc, ah, bh, idesc, 1u);
+            for (int k = 0; k < 4; k++) {
+              const uint64_t adv = (uint64_t)(2 * k);
+              const uint64_t ah = make_desc<32>(qa + c * 16384) + adv, al = make_desc<32>(qa + 32768 + c * 16384) + adv;
+              const uint64_t bh = make_desc<32>(kb + c * 8192) + adv, bl = make_desc<32>(kb + 16384 + c * 8192) + adv;
+              tc_mma_tf32(acc, al, bh, idesc, (c | k) ? 1u : 0u);
+              tc_mma_tf32(acc, ah, bl, idesc, 1u);
+              tc_mma_tf32(acc, ah, bh, idesc, 1u);
+            }
+          tc_commit(BAR(3 + s));
+          tc_commit(BAR(9 + s));
+          if (j == nblk - 1) tc_commit(BAR(14));             // Q may be replaced
+        };
+        auto issue_pv = [&](int j) {
+          const uint32_t g = g0 + j, s = g & 1, u = g >> 1;
+          ok &= mbar_wait(BAR(11 + s), u & 1);
+          ok &= mbar_wait(BAR(5 + s), u & 1);
+          tc_fence_after();
+          const uint32_t vb = smem_u32(sV + s * ATC_V_BYTES);
+          const uint32_t ph = tmem_base + ATC_COL_S + s * 64, pl = tmem_base + ATC_COL_PLO + s * 64, acc = tmem_base + ATC_COL_O + ob * 64;
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++) {
+            const int c = kk >> 2; const uint64_t adv = (uint64_t)(2 * (kk & 3));
+            const uint64_t bh = make_desc<32>(vb + c * 8192) + adv, bl = make_desc<32>(vb + 16384 + c * 8192) + adv;
+            tc_mma_tf32_ts(acc, pl + kk * 8, bh, idesc, (j | kk) ? 1u : 0u);
+            tc_mma_tf32_ts(acc, ph + kk * 8, bl, idesc, 1u);
+            tc_mma_tf32_ts(acc, ph + kk * 8, bh, idesc, 1u);
           }
-        tc_commit(BAR(3 + s));
-        tc_commit(BAR(9 + s));
-      };
-      auto issue_pv = [&](int j) {
-        const int s = j & 1, u = j >> 1;
-        ok &= mbar_wait(BAR(11 + s), u & 1);
-        ok &= mbar_wait(BAR(5 + s), u & 1);
-        tc_fence_after();
-        const uint32_t vb = smem_u32(sV + s * ATC_V_BYTES);
-        const uint32_t ph = tmem_base + ATC_COL_S + s * 64, pl = tmem_base + ATC_COL_PLO + s * 64, acc = tmem_base + ATC_COL_O;
-#pragma unroll
-        for (int kk = 0; kk < 8; kk++) {
-          const int c = kk >> 2; const uint64_t adv = (uint64_t)(2 * (kk & 3));
-          const uint64_t bh = make_desc<32>(vb + c * 8192) + adv, bl = make_desc<32>(vb + 16384 + c * 8192) + adv;
-          tc_mma_tf32_ts(acc, pl + kk * 8, bh, idesc, (j | kk) ? 1u : 0u);
-          tc_mma_tf32_ts(acc, ph + kk * 8, bl, idesc, 1u);
-          tc_mma_tf32_ts(acc, ph + kk * 8, bh, idesc, 1u);
+          tc_commit(BAR(7 + s));
+          tc_commit(BAR(13));
+        };
+        ok &= mbar_wait(BAR(0), tt & 1);
+        if (tt >= 2) ok &= mbar_wait(BAR(15 + ob), ((tt >> 1) - 1) & 1);     // this accumulator has been written out
+        issue_s(0);
+        if (nblk > 1) issue_s(1);
+        for (int j = 0; j < nblk; j++) {
+          issue_pv(j);
+          if (j + 2 < nblk) issue_s(j + 2);
         }
-        tc_commit(BAR(7 + s));
-        tc_commit(BAR(13));
-      };
-      ok &= mbar_wait(BAR(0), 0);
-      issue_s(0);
-      if (nblk > 1) issue_s(1);
-      for (int j = 0; j < nblk; j++) {
-        issue_pv(j);
-        if (j + 2 < nblk) issue_s(j + 2);
+        g0 += nblk;
       }
       if (!ok) atomicExch(status, 12);
     }
   } else {
     // two threads per query row: `half` selects 32 of the 64 columns of a block (and of the accumulator)
-    const int quad = warp & 3, half = (warp - 2) >> 2, row = quad * 32 + lane, qi = q0 + row;
+    const int quad = warp & 3, half = (warp - 2) >> 2, row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + 32 * half;
     const float cs = inv_scale * 1.44269504088896341f;      // scores -> log2 units
-    float m_run = -INFINITY, l_part = 0.f;                  // running maximum (scaled scores, natural units), this thread's part of the row sum
-    bool ok = true;
-    for (int j = 0; j < nblk; j++) {
-      const int s = j & 1, u = j >> 1, key0 = j * ATC_BK + 32 * half;
-      ok &= warp_mbar_wait(BAR(9 + s), u & 1, lane);
-      tc_fence_after();
-      uint32_t a[32], lo[32];
-      tmem_ld32(lane_base + ATC_COL_S + s * 64, a);
-      tmem_wait_ld();
-      if (causal && j * ATC_BK + ATC_BK - 1 > q0) {         // the block reaches above the diagonal for some row of the tile
-#pragma unroll
-        for (int e = 0; e < 32; e++) if (key0 + e > qi) a[e] = __float_as_uint(-INFINITY);
-      }
-      float bm = -INFINITY;
-#pragma unroll
-      for (int e = 0; e < 32; e++) bm = fmaxf(bm, __uint_as_float(a[e]));
-      float* xb = xch + (j & 1) * 256;
-      xb[half * 128 + row] = bm;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      bm = fmaxf(bm, xb[(half ^ 1) * 128 + row]);
-      const float m_new = fmaxf(m_run, bm * inv_scale);
-      const float corr = fast_ex2((m_run - m_new) * 1.44269504088896341f);
-      const float mneg = -m_new * 1.44269504088896341f;
-      float rs = 0.f;
-#pragma unroll
-      for (int e = 0; e < 32; e++) {
-        const float p = fast_ex2(fmaf(__uint_as_float(a[e]), cs, mneg)); rs += p;
-        const uint32_t hi = __float_as_uint(p) & 0xffffe000u;
-        a[e] = hi; lo[e] = __float_as_uint(p - __uint_as_float(hi));
-      }
-      tmem_st32(lane_base + ATC_COL_S + s * 64, a);
-      tmem_st32(lane_base + ATC_COL_PLO + s * 64, lo);
-      l_part = l_part * corr + rs; m_run = m_new;
-      // The accumulator may only be touched between P V products.  The wait is unconditional: a parity wait is only
-      // unambiguous when no completion of this barrier has been skipped.
-      if (j > 0) ok &= warp_mbar_wait(BAR(13), (j - 1) & 1, lane);
-      if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+    bool ok = true; uint32_t g0 = 0, xc = 0;
+    for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+      int z, q0, nblk; decode(id, tt, z, q0, nblk);
+      const int qi = q0 + row; const uint32_t ob = tt & 1;
+      float m_run = -INFINITY, l_part = 0.f;                // running maximum (scaled scores), this thread's part of the row sum
+      for (int j = 0; j < nblk; j++) {
+        const uint32_t g = g0 + j, s = g & 1, u = g >> 1; const int key0 = j * ATC_BK + 32 * half;
+        ok &= warp_mbar_wait(BAR(9 + s), u & 1, lane);
         tc_fence_after();
-        tmem_ld32(lane_base + ATC_COL_O, a);
+        uint32_t a[32], lo[32];
+        tmem_ld32(lane_base + ATC_COL_S + s * 64, a);
         tmem_wait_ld();
+        if (causal && j * ATC_BK + ATC_BK - 1 > q0) {       // the block reaches above the diagonal for some row of the tile
 #pragma unroll
-        for (int e = 0; e < 32; e++) a[e] = __float_as_uint(__uint_as_float(a[e]) * corr);
-        tmem_st32(lane_base + ATC_COL_O, a);
+          for (int e = 0; e < 32; e++) if (key0 + e > qi) a[e] = __float_as_uint(-INFINITY);
+        }
+        float bm = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 32; e++) bm = fmaxf(bm, __uint_as_float(a[e]));
+        float* xb = xch + (xc++ & 1) * 256;
+        xb[half * 128 + row] = bm;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        bm = fmaxf(bm, xb[(half ^ 1) * 128 + row]);
+        const float m_new = fmaxf(m_run, bm * inv_scale);
+        const float corr = fast_ex2((m_run - m_new) * 1.44269504088896341f);
+        const float mneg = -m_new * 1.44269504088896341f;
+        float rs = 0.f;
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          const float p = fast_ex2(fmaf(__uint_as_float(a[e]), cs, mneg)); rs += p;
+          const uint32_t hi = __float_as_uint(p) & 0xffffe000u;
+          a[e] = hi; lo[e] = __float_as_uint(p - __uint_as_float(hi));
+        }
+        tmem_st32(lane_base + ATC_COL_S + s * 64, a);
+        tmem_st32(lane_base + ATC_COL_PLO + s * 64, lo);
+        l_part = l_part * corr + rs; m_run = m_new;
+        // The accumulator may only be touched between P V products.  The wait is unconditional: a parity wait is only
+        // unambiguous when no completion of this barrier has been skipped (the first block of a tile skips none: the
+        // previous tile's write-out has waited for its last product).
+        if (j > 0) ok &= warp_mbar_wait(BAR(13), (g - 1) & 1, lane);
+        if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+          tc_fence_after();
+          tmem_ld32(lane_base + ATC_COL_O + ob * 64, a);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; e++) a[e] = __float_as_uint(__uint_as_float(a[e]) * corr);
+          tmem_st32(lane_base + ATC_COL_O + ob * 64, a);
+        }
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(BAR(11 + s));
       }
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(BAR(11 + s));
-    }
-    ok &= warp_mbar_wait(BAR(13), (nblk - 1) & 1, lane);
-    tc_fence_after();
-    {
-      uint32_t a[32];
-      tmem_ld32(lane_base + ATC_COL_O, a);
-      float* xb = xch + (nblk & 1) * 256;
-      xb[half * 128 + row] = l_part;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      const float l_run = l_part + xb[(half ^ 1) * 128 + row];
-      tmem_wait_ld();
-      const float il = 1.f / l_run;
-      const int bz = z / H, h = z % H;
-      float* orow = O + ((long)bz * T + qi) * D + (long)h * ATC_HD + 32 * half;
+      ok &= warp_mbar_wait(BAR(13), (g0 + nblk - 1) & 1, lane);
+      tc_fence_after();
+      {
+        uint32_t a[32];
+        tmem_ld32(lane_base + ATC_COL_O + ob * 64, a);
+        float* xb = xch + (xc++ & 1) * 256;
+        xb[half * 128 + row] = l_part;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        const float l_run = l_part + xb[(half ^ 1) * 128 + row];
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(BAR(15 + ob));                          // the accumulator is in registers: the MMA warp may reuse it
+        const float il = 1.f / l_run;
+        const int bz = z / H, h = z % H;
+        float* orow = O + ((long)bz * T + qi) * D + (long)h * ATC_HD + 32 * half;
 #pragma unroll
-      for (int e = 0; e < 8; e++)
-        *reinterpret_cast<float4*>(orow + 4 * e) = make_float4(__uint_as_float(a[4 * e]) * il, __uint_as_float(a[4 * e + 1]) * il, __uint_as_float(a[4 * e + 2]) * il, __uint_as_float(a[4 * e + 3]) * il);
-      if (half == 0) { Mst[(long)z * T + qi] = m_run; Lst[(long)z * T + qi] = l_run; }
+        for (int e = 0; e < 8; e++)
+          *reinterpret_cast<float4*>(orow + 4 * e) = make_float4(__uint_as_float(a[4 * e]) * il, __uint_as_float(a[4 * e + 1]) * il, __uint_as_float(a[4 * e + 2]) * il, __uint_as_float(a[4 * e + 3]) * il);
+        if (half == 0) { Mst[(long)z * T + qi] = m_run; Lst[(long)z * T + qi] = l_run; }
+      }
+      g0 += nblk;
     }
     if (!ok && lane == 0) atomicExch(status, 13);
   }
@@ -252,7 +283,8 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
 // score-shaped products ([64 rows][64]); C3 = block operand of the accumulating product, taken from TRANSPOSED planes
 // ([64 head columns][T]) so that its contraction index runs along the row.  dS (P in MODE 2) goes back to tensor
 // memory as hi/lo and is the A operand of the accumulating product.  TMEM: two sets of {S, dP / dS_hi, dS_lo} so that
-// the score products of block n+1 run under the elementwise work of block n; accumulator in the last 64 columns.
+// the score products of block n+1 run under the elementwise work of block n; two accumulators in the last 128 columns
+// (the kernel is persistent: the next tile starts while the previous one is written out).
 // Warps: 0 = TMA producer for R1, R2, C1, C2; 1 = MMA issuer; 2-9 = elementwise (two threads per tile row);
 // 10 = TMA producer for C3 (its buffer is released much later than C1 / C2, so it gets its own thread).
 constexpr int ATB_THREADS = 352;
@@ -261,7 +293,7 @@ template <int MODE> struct AtbCfg {
   static constexpr int NR = MODE == 2 ? 1 : 2;                                 // row-tile operands, score-shaped products
   static constexpr int SMEM = NR * ATB_R_BYTES + (NR + 1) * ATB_C_BYTES + 1024 + 256 + 2 * 3 * 64 * 4;
 };
-constexpr uint32_t ATB_COL_S = 0, ATB_COL_DP = 128, ATB_COL_LO = 256, ATB_COL_ACC = 384;
+constexpr uint32_t ATB_COL_S = 0, ATB_COL_DP = 128, ATB_COL_LO = 256, ATB_COL_ACC = 384;      // two accumulators of 64 columns
 
 template <int MODE>
 __global__ void __launch_bounds__(ATB_THREADS, 1)
@@ -269,7 +301,7 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
                    const __grid_constant__ CUtensorMap mR2l, const __grid_constant__ CUtensorMap mC1h, const __grid_constant__ CUtensorMap mC1l,
                    const __grid_constant__ CUtensorMap mC2h, const __grid_constant__ CUtensorMap mC2l, const __grid_constant__ CUtensorMap mC3h,
                    const __grid_constant__ CUtensorMap mC3l, const float* __restrict__ Mst, const float* __restrict__ Lst, const float* __restrict__ Dv,
-                   float* __restrict__ Out, int T, int D, int H, int causal, float inv_scale, int* status) {
+                   float* __restrict__ Out, int T, int D, int H, int causal, float inv_scale, int ntiles, int* status) {
   constexpr int NR = AtbCfg<MODE>::NR;
   constexpr bool TRANS = MODE != 0;
   extern __shared__ uint8_t smem_raw[];
@@ -280,18 +312,21 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
   uint64_t* bars = (uint64_t*)(sC3 + ATB_C_BYTES);
   uint32_t* tmem_slot = (uint32_t*)(bars + 16);
   float* st = (float*)(bars + 32);                       // [2][3][64] column statistics (MODES 1, 2)
-  // barriers: 0 r_full | 1 c12_full | 2 c12_empty | 3 c3_full | 4 c3_empty | 5,6 sd_full | 7,8 ds_full | 9 all_done
+  // barriers: 0 r_full | 1 c12_full | 2 c12_empty | 3 c3_full | 4 c3_empty | 5,6 sd_full | 7,8 ds_full | 9 tile_done
+  //           10 r_empty | 11,12 acc_free
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int z = blockIdx.y;
-  const int tile = TRANS ? (int)blockIdx.x : (int)gridDim.x - 1 - (int)blockIdx.x;      // long tiles first
-  const int r0 = tile * 128;
-  const int b0 = (TRANS && causal) ? r0 / 64 : 0;
-  const int nb = TRANS ? T / 64 - b0 : (causal ? (r0 + 128) / 64 : T / 64);
+  const int ntr = T / 128;
+  // persistent, as in the forward kernel: tile id -> problem z, first row of the tile, first block and number of blocks
+  auto decode = [&](int id, int i, int& z, int& r0, int& b0, int& nb) {
+    z = id / ntr; r0 = ((id % ntr + i) % ntr) * 128;
+    b0 = (TRANS && causal) ? r0 / 64 : 0;
+    nb = TRANS ? T / 64 - b0 : (causal ? (r0 + 128) / 64 : T / 64);
+  };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 10; i++) mbar_init(BAR(i), (i == 7 || i == 8) ? 256 : 1);
+    for (int i = 0; i < 13; i++) mbar_init(BAR(i), (i == 7 || i == 8 || i == 11 || i == 12) ? 256 : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -305,26 +340,30 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
 
   if (warp == 0) {
     if (lane == 0) {
-      bool ok = true;
-      mbar_expect_tx(BAR(0), NR * ATB_R_BYTES);
-      for (int c = 0; c < 2; c++) {
-        tma_load_3d(smem_u32(sR + c * 16384), &mR1h, c * 32, r0, z, BAR(0));
-        tma_load_3d(smem_u32(sR + 32768 + c * 16384), &mR1l, c * 32, r0, z, BAR(0));
-        if (NR == 2) {
-          tma_load_3d(smem_u32(sR + ATB_R_BYTES + c * 16384), &mR2h, c * 32, r0, z, BAR(0));
-          tma_load_3d(smem_u32(sR + ATB_R_BYTES + 32768 + c * 16384), &mR2l, c * 32, r0, z, BAR(0));
-        }
-      }
-      for (int n = 0; n < nb; n++) {
-        const int row = (b0 + n) * 64;
-        if (n > 0) ok &= mbar_wait(BAR(2), (n - 1) & 1);
-        mbar_expect_tx(BAR(1), NR * ATB_C_BYTES);
+      bool ok = true; uint32_t g = 0;
+      for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+        int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
+        if (tt > 0) ok &= mbar_wait(BAR(10), (tt - 1) & 1);
+        mbar_expect_tx(BAR(0), NR * ATB_R_BYTES);
         for (int c = 0; c < 2; c++) {
-          tma_load_3d(smem_u32(sC + c * 8192), &mC1h, c * 32, row, z, BAR(1));
-          tma_load_3d(smem_u32(sC + 16384 + c * 8192), &mC1l, c * 32, row, z, BAR(1));
+          tma_load_3d(smem_u32(sR + c * 16384), &mR1h, c * 32, r0, z, BAR(0));
+          tma_load_3d(smem_u32(sR + 32768 + c * 16384), &mR1l, c * 32, r0, z, BAR(0));
           if (NR == 2) {
-            tma_load_3d(smem_u32(sC + ATB_C_BYTES + c * 8192), &mC2h, c * 32, row, z, BAR(1));
-            tma_load_3d(smem_u32(sC + ATB_C_BYTES + 16384 + c * 8192), &mC2l, c * 32, row, z, BAR(1));
+            tma_load_3d(smem_u32(sR + ATB_R_BYTES + c * 16384), &mR2h, c * 32, r0, z, BAR(0));
+            tma_load_3d(smem_u32(sR + ATB_R_BYTES + 32768 + c * 16384), &mR2l, c * 32, r0, z, BAR(0));
+          }
+        }
+        for (int n = 0; n < nb; n++, g++) {
+          const int row = (b0 + n) * 64;
+          if (g > 0) ok &= mbar_wait(BAR(2), (g - 1) & 1);
+          mbar_expect_tx(BAR(1), NR * ATB_C_BYTES);
+          for (int c = 0; c < 2; c++) {
+            tma_load_3d(smem_u32(sC + c * 8192), &mC1h, c * 32, row, z, BAR(1));
+            tma_load_3d(smem_u32(sC + 16384 + c * 8192), &mC1l, c * 32, row, z, BAR(1));
+            if (NR == 2) {
+              tma_load_3d(smem_u32(sC + ATB_C_BYTES + c * 8192), &mC2h, c * 32, row, z, BAR(1));
+              tma_load_3d(smem_u32(sC + ATB_C_BYTES + 16384 + c * 8192), &mC2l, c * 32, row, z, BAR(1));
+            }
           }
         }
       }
@@ -332,123 +371,140 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
     }
   } else if (warp == 10) {
     if (lane == 0) {
-      bool ok = true;
-      for (int n = 0; n < nb; n++) {
-        const int col = (b0 + n) * 64;
-        if (n > 0) ok &= mbar_wait(BAR(4), (n - 1) & 1);
-        mbar_expect_tx(BAR(3), ATB_C_BYTES);
-        for (int c = 0; c < 2; c++) {
-          tma_load_3d(smem_u32(sC3 + c * 8192), &mC3h, col + c * 32, 0, z, BAR(3));
-          tma_load_3d(smem_u32(sC3 + 16384 + c * 8192), &mC3l, col + c * 32, 0, z, BAR(3));
+      bool ok = true; uint32_t g = 0;
+      for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+        int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
+        for (int n = 0; n < nb; n++, g++) {
+          const int col = (b0 + n) * 64;
+          if (g > 0) ok &= mbar_wait(BAR(4), (g - 1) & 1);
+          mbar_expect_tx(BAR(3), ATB_C_BYTES);
+          for (int c = 0; c < 2; c++) {
+            tma_load_3d(smem_u32(sC3 + c * 8192), &mC3h, col + c * 32, 0, z, BAR(3));
+            tma_load_3d(smem_u32(sC3 + 16384 + c * 8192), &mC3l, col + c * 32, 0, z, BAR(3));
+          }
         }
       }
       if (!ok) atomicExch(status, 22);
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      bool ok = true;
+      bool ok = true; uint32_t g0 = 0;
       constexpr uint32_t idesc = make_idesc(128, 64);
-      auto issue_sd = [&](int n) {
-        const int s = n & 1;
-        ok &= mbar_wait(BAR(1), n & 1);
-        tc_fence_after();
+      for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+        int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
+        const uint32_t ab = tt & 1;
+        auto issue_sd = [&](int n) {
+          const uint32_t g = g0 + n, s = g & 1;
+          ok &= mbar_wait(BAR(1), g & 1);
+          tc_fence_after();
 #pragma unroll
-        for (int prod = 0; prod < NR; prod++) {
-          const uint32_t acc = tmem_base + (prod == 0 ? ATB_COL_S : ATB_COL_DP) + s * 64;
-          const uint32_t ra = smem_u32(sR + prod * ATB_R_BYTES), cb = smem_u32(sC + prod * ATB_C_BYTES);
+          for (int prod = 0; prod < NR; prod++) {
+            const uint32_t acc = tmem_base + (prod == 0 ? ATB_COL_S : ATB_COL_DP) + s * 64;
+            const uint32_t ra = smem_u32(sR + prod * ATB_R_BYTES), cb = smem_u32(sC + prod * ATB_C_BYTES);
 #pragma unroll
-          for (int c = 0; c < 2; c++)
+            for (int c = 0; c < 2; c++)
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-              const uint64_t adv = (uint64_t)(2 * k);
-              const uint64_t ah = make_desc<32>(ra + c * 16384) + adv, al = make_desc<32>(ra + 32768 + c * 16384) + adv;
-              const uint64_t bh = make_desc<32>(cb + c * 8192) + adv, bl = make_desc<32>(cb + 16384 + c * 8192) + adv;
-              tc_mma_tf32(acc, al, bh, idesc, (c | k) ? 1u : 0u);
-              tc_mma_tf32(acc, ah, bl, idesc, 1u);
-              tc_mma_tf32(acc, ah, bh, idesc, 1u);
-            }
+              for (int k = 0; k < 4; k++) {
+                const uint64_t adv = (uint64_t)(2 * k);
+                const uint64_t ah = make_desc<32>(ra + c * 16384) + adv, al = make_desc<32>(ra + 32768 + c * 16384) + adv;
+                const uint64_t bh = make_desc<32>(cb + c * 8192) + adv, bl = make_desc<32>(cb + 16384 + c * 8192) + adv;
+                tc_mma_tf32(acc, al, bh, idesc, (c | k) ? 1u : 0u);
+                tc_mma_tf32(acc, ah, bl, idesc, 1u);
+                tc_mma_tf32(acc, ah, bh, idesc, 1u);
+              }
+          }
+          tc_commit(BAR(2));
+          tc_commit(BAR(5 + s));
+          if (n == nb - 1) tc_commit(BAR(10));               // the row tile may be replaced
+        };
+        auto issue_acc = [&](int n) {
+          const uint32_t g = g0 + n, s = g & 1, u = g >> 1;
+          ok &= mbar_wait(BAR(7 + s), u & 1);
+          ok &= mbar_wait(BAR(3), g & 1);
+          tc_fence_after();
+          const uint32_t cb = smem_u32(sC3);
+          const uint32_t ph = tmem_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, pl = tmem_base + ATB_COL_LO + s * 64,
+                         acc = tmem_base + ATB_COL_ACC + ab * 64;
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++) {
+            const int c = kk >> 2; const uint64_t adv = (uint64_t)(2 * (kk & 3));
+            const uint64_t bh = make_desc<32>(cb + c * 8192) + adv, bl = make_desc<32>(cb + 16384 + c * 8192) + adv;
+            tc_mma_tf32_ts(acc, pl + kk * 8, bh, idesc, (n | kk) ? 1u : 0u);
+            tc_mma_tf32_ts(acc, ph + kk * 8, bl, idesc, 1u);
+            tc_mma_tf32_ts(acc, ph + kk * 8, bh, idesc, 1u);
+          }
+          tc_commit(BAR(4));
+          if (n == nb - 1) tc_commit(BAR(9));
+        };
+        ok &= mbar_wait(BAR(0), tt & 1);
+        if (tt >= 2) ok &= mbar_wait(BAR(11 + ab), ((tt >> 1) - 1) & 1);     // this accumulator has been written out
+        issue_sd(0);
+        if (nb > 1) issue_sd(1);
+        for (int n = 0; n < nb; n++) {
+          issue_acc(n);
+          if (n + 2 < nb) issue_sd(n + 2);
         }
-        tc_commit(BAR(2));
-        tc_commit(BAR(5 + s));
-      };
-      auto issue_acc = [&](int n) {
-        const int s = n & 1, u = n >> 1;
-        ok &= mbar_wait(BAR(7 + s), u & 1);
-        ok &= mbar_wait(BAR(3), n & 1);
-        tc_fence_after();
-        const uint32_t cb = smem_u32(sC3);
-        const uint32_t ph = tmem_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, pl = tmem_base + ATB_COL_LO + s * 64, acc = tmem_base + ATB_COL_ACC;
-#pragma unroll
-        for (int kk = 0; kk < 8; kk++) {
-          const int c = kk >> 2; const uint64_t adv = (uint64_t)(2 * (kk & 3));
-          const uint64_t bh = make_desc<32>(cb + c * 8192) + adv, bl = make_desc<32>(cb + 16384 + c * 8192) + adv;
-          tc_mma_tf32_ts(acc, pl + kk * 8, bh, idesc, (n | kk) ? 1u : 0u);
-          tc_mma_tf32_ts(acc, ph + kk * 8, bl, idesc, 1u);
-          tc_mma_tf32_ts(acc, ph + kk * 8, bh, idesc, 1u);
-        }
-        tc_commit(BAR(4));
-        if (n == nb - 1) tc_commit(BAR(9));
-      };
-      ok &= mbar_wait(BAR(0), 0);
-      issue_sd(0);
-      if (nb > 1) issue_sd(1);
-      for (int n = 0; n < nb; n++) {
-        issue_acc(n);
-        if (n + 2 < nb) issue_sd(n + 2);
+        g0 += nb;
       }
       if (!ok) atomicExch(status, 23);
     }
   } else {
     // two threads per tile row: `half` selects 32 of the 64 columns of a block (and of the accumulator)
-    const int quad = warp & 3, half = (warp - 2) >> 2, row = quad * 32 + lane, ri = r0 + row, et = (warp - 2) * 32 + lane;   // et: 0..255
+    const int quad = warp & 3, half = (warp - 2) >> 2, row = quad * 32 + lane, et = (warp - 2) * 32 + lane;   // et: 0..255
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + 32 * half;
-    const long sb = (long)z * T;
     constexpr float LOG2E = 1.44269504088896341f;
     const float cs = inv_scale * LOG2E, oscale = MODE == 2 ? 1.f : inv_scale;
-    float mneg_r = 0.f, il_r = 0.f, d_r = 0.f;        // -m log2(e), scale / l, Dv of this row (MODE 0)
-    if (!TRANS) { mneg_r = -Mst[sb + ri] * LOG2E; il_r = oscale / Lst[sb + ri]; d_r = Dv[sb + ri]; }
-    bool ok = true;
-    for (int n = 0; n < nb; n++) {
-      const int s = n & 1, u = n >> 1, c0 = (b0 + n) * 64;
-      float* stm = st + s * 192; float* stl = stm + 64; float* std_ = stm + 128;
-      if (TRANS) {
-        if (et < 64) { stm[et] = -Mst[sb + c0 + et] * LOG2E; stl[et] = oscale / Lst[sb + c0 + et]; if (MODE == 1) std_[et] = Dv[sb + c0 + et]; }
-        asm volatile("bar.sync 1, 256;" ::: "memory");
+    bool ok = true; uint32_t g0 = 0;
+    for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+      int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
+      const int ri = r0 + row; const long sb = (long)z * T; const uint32_t ab = tt & 1;
+      float mneg_r = 0.f, il_r = 0.f, d_r = 0.f;        // -m log2(e), scale / l, Dv of this row (MODE 0)
+      if (!TRANS) { mneg_r = -Mst[sb + ri] * LOG2E; il_r = oscale / Lst[sb + ri]; d_r = Dv[sb + ri]; }
+      for (int n = 0; n < nb; n++) {
+        const uint32_t g = g0 + n, s = g & 1, u = g >> 1; const int c0 = (b0 + n) * 64;
+        float* stm = st + s * 192; float* stl = stm + 64; float* std_ = stm + 128;
+        if (TRANS) {
+          if (et < 64) { stm[et] = -Mst[sb + c0 + et] * LOG2E; stl[et] = oscale / Lst[sb + c0 + et]; if (MODE == 1) std_[et] = Dv[sb + c0 + et]; }
+          asm volatile("bar.sync 1, 256;" ::: "memory");
+        }
+        ok &= warp_mbar_wait(BAR(5 + s), u & 1, lane);
+        tc_fence_after();
+        uint32_t a[32], b[32], lo[32];
+        tmem_ld32(lane_base + ATB_COL_S + s * 64, a);
+        if (MODE != 2) tmem_ld32(lane_base + ATB_COL_DP + s * 64, b);
+        tmem_wait_ld();
+        // does the block reach across the diagonal for some row of the tile?
+        const bool diag = causal && (TRANS ? r0 + 127 > c0 : c0 + 63 > r0);
+#pragma unroll
+        for (int e = 0; e < 32; e++) {
+          const int col = 32 * half + e;
+          float v = fast_ex2(fmaf(__uint_as_float(a[e]), cs, TRANS ? stm[col] : mneg_r)) * (TRANS ? stl[col] : il_r);   // P (times 1/sqrt(hd) for dS)
+          if (MODE != 2) v *= __uint_as_float(b[e]) - (TRANS ? std_[col] : d_r);                                        // dS
+          if (diag && (TRANS ? ri > c0 + col : c0 + col > ri)) v = 0.f;
+          const uint32_t hi = __float_as_uint(v) & 0xffffe000u;
+          a[e] = hi; lo[e] = __float_as_uint(v - __uint_as_float(hi));
+        }
+        tmem_st32(lane_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, a);
+        tmem_st32(lane_base + ATB_COL_LO + s * 64, lo);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(BAR(7 + s));
       }
-      ok &= warp_mbar_wait(BAR(5 + s), u & 1, lane);
+      ok &= warp_mbar_wait(BAR(9), tt & 1, lane);
       tc_fence_after();
-      uint32_t a[32], b[32], lo[32];
-      tmem_ld32(lane_base + ATB_COL_S + s * 64, a);
-      if (MODE != 2) tmem_ld32(lane_base + ATB_COL_DP + s * 64, b);
-      tmem_wait_ld();
-      // does the block reach across the diagonal for some row of the tile?
-      const bool diag = causal && (TRANS ? r0 + 127 > c0 : c0 + 63 > r0);
+      {
+        uint32_t a[32];
+        tmem_ld32(lane_base + ATB_COL_ACC + ab * 64, a);
+        tmem_wait_ld();
+        tc_fence_before();
+        mbar_arrive(BAR(11 + ab));                          // the accumulator is in registers: the MMA warp may reuse it
+        const int bz = z / H, h = z % H;
+        float* orow = Out + ((long)bz * T + ri) * D + (long)h * ATC_HD + 32 * half;
 #pragma unroll
-      for (int e = 0; e < 32; e++) {
-        const int col = 32 * half + e;
-        float v = fast_ex2(fmaf(__uint_as_float(a[e]), cs, TRANS ? stm[col] : mneg_r)) * (TRANS ? stl[col] : il_r);   // P (times 1/sqrt(hd) for dS)
-        if (MODE != 2) v *= __uint_as_float(b[e]) - (TRANS ? std_[col] : d_r);                                        // dS
-        if (diag && (TRANS ? ri > c0 + col : c0 + col > ri)) v = 0.f;
-        const uint32_t hi = __float_as_uint(v) & 0xffffe000u;
-        a[e] = hi; lo[e] = __float_as_uint(v - __uint_as_float(hi));
+        for (int e = 0; e < 8; e++)
+          *reinterpret_cast<float4*>(orow + 4 * e) = make_float4(__uint_as_float(a[4 * e]), __uint_as_float(a[4 * e + 1]), __uint_as_float(a[4 * e + 2]), __uint_as_float(a[4 * e + 3]));
       }
-      tmem_st32(lane_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, a);
-      tmem_st32(lane_base + ATB_COL_LO + s * 64, lo);
-      tmem_wait_st();
-      tc_fence_before();
-      mbar_arrive(BAR(7 + s));
-    }
-    ok &= warp_mbar_wait(BAR(9), 0, lane);
-    tc_fence_after();
-    {
-      uint32_t a[32];
-      tmem_ld32(lane_base + ATB_COL_ACC, a);
-      tmem_wait_ld();
-      const int bz = z / H, h = z % H;
-      float* orow = Out + ((long)bz * T + ri) * D + (long)h * ATC_HD + 32 * half;
-#pragma unroll
-      for (int e = 0; e < 8; e++)
-        *reinterpret_cast<float4*>(orow + 4 * e) = make_float4(__uint_as_float(a[4 * e]), __uint_as_float(a[4 * e + 1]), __uint_as_float(a[4 * e + 2]), __uint_as_float(a[4 * e + 3]));
+      g0 += nb;
     }
     if (!ok && lane == 0) atomicExch(status, 24);
   }
@@ -532,8 +588,10 @@ inline int attn_tc_fwd(Ctx* ctx, const float* Q, const float* K, const float* V,
   GN_TRY(tc_make_map(ctx, &mKh, pk, pk.hi, ATC_BK)); GN_TRY(tc_make_map(ctx, &mKl, pk, pk.lo, ATC_BK));
   GN_TRY(tc_make_map(ctx, &mVh, pv, pv.hi, ATC_HD)); GN_TRY(tc_make_map(ctx, &mVl, pv, pv.lo, ATC_HD));
   GN_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_FWD_SMEM));
-  GN_LAUNCH(ctx, attn_tc_fwd_kernel, dim3(T / ATC_BQ, B * H), ATC_THREADS, ATC_FWD_SMEM, mQh, mQl, mKh, mKl, mVh, mVl, O, M, L, T, D, H, causal,
-            1.f / sqrtf((float)ATC_HD), ctx->d_status);
+  const int ntq = T / ATC_BQ, ntiles = ntq * B * H;
+  const int grid = std::min(ntiles, std::max(1, ctx->sm_count / ntq) * ntq);      // a multiple of the query blocks per problem
+  GN_LAUNCH(ctx, attn_tc_fwd_kernel, grid, ATC_THREADS, ATC_FWD_SMEM, mQh, mQl, mKh, mKl, mVh, mVl, O, M, L, T, D, H, causal,
+            1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status);
   return check_launch("attn_tc_fwd");
 }
 
@@ -547,8 +605,10 @@ inline int attn_tc_bwd_launch(Ctx* ctx, const TcPlanes& r1, const TcPlanes& r2, 
   GN_TRY(tc_make_map(ctx, &m[6], c2, c2.hi, 64)); GN_TRY(tc_make_map(ctx, &m[7], c2, c2.lo, 64));
   GN_TRY(tc_make_map(ctx, &m[8], c3, c3.hi, ATC_HD)); GN_TRY(tc_make_map(ctx, &m[9], c3, c3.lo, ATC_HD));
   GN_CUDA(cudaFuncSetAttribute(attn_tc_bwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, AtbCfg<MODE>::SMEM));
-  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, dim3(T / 128, B * H), ATB_THREADS, AtbCfg<MODE>::SMEM, m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], m[8], m[9],
-            M, L, Dv, out, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ctx->d_status);
+  const int ntr = T / 128, ntiles = ntr * B * H;
+  const int grid = std::min(ntiles, std::max(1, ctx->sm_count / ntr) * ntr);      // a multiple of the row tiles per problem
+  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, grid, ATB_THREADS, AtbCfg<MODE>::SMEM, m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], m[8], m[9],
+            M, L, Dv, out, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status);
   return check_launch("attn_tc_bwd");
 }
 // dQ, dK, dV from Q, K, V, O, dO and the forward's row statistics; Dv receives the row products dO . O

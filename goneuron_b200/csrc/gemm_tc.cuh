@@ -31,6 +31,7 @@ namespace gn {
 
 constexpr int TC_BM = 128, TC_THREADS = 192;
 constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
+constexpr int TC_KSLICE = 4096;     // longest accumulator run, see gemm_tc()
 constexpr int TC_FLAG_VEC = 4096;   // epilogue may use 16-byte accesses (set by the host when every pointer and stride allows it)
 // BK = 32 floats (one 128-byte swizzle row) or 16 (64-byte swizzle): same bytes per FLOP, but half-size stages keep
 // more of the shared memory in flight while one stage is being consumed.
@@ -576,7 +577,20 @@ inline int gemm_tc(Ctx* ctx, const GemmDesc& g) {
   static const int noload = [] { const char* e = getenv("GONEURON_TC_NOLOAD"); return e ? atoi(e) * 256 : 0; }();
   TcParams ep{g.C, g.ldc, g.c_b1, g.c_b2, g.bias, g.R, g.ldr, g.r_b1, g.r_b2, g.act, g.M, g.N, g.K, g.batch2, g.flags | noload, ctx->d_status, g.mask, g.mask_ld, g.mask_group,
               nb == 1 ? g.c_hi : nullptr, nb == 1 ? g.c_lo : nullptr, g.c_ldp};
-  return tc_launch(ctx, A, B, ep);
+  // The tensor core truncates when it adds a product group to the accumulator, so the error of one accumulator run grows
+  // with its length (measured 3e-6 at K = 1024, 1.2e-5 at K = 4096, normalised).  Long contractions (weight gradients
+  // over all tokens of a batch) are therefore cut into slices of TC_KSLICE, each slice adding its result to C through
+  // the epilogue's residual path, i.e. in properly rounded fp32.
+  if (g.K <= TC_KSLICE || (g.flags & (GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return tc_launch(ctx, A, B, ep);
+  for (int k0 = 0; k0 < g.K; k0 += TC_KSLICE) {
+    const int kl = std::min(TC_KSLICE, g.K - k0); const bool first = k0 == 0, last = k0 + kl >= g.K;
+    TcPlanes As = A, Bs = B; As.hi += k0; As.lo += k0; As.K = kl; Bs.hi += k0; Bs.lo += k0; Bs.K = kl;
+    TcParams es = ep; es.K = kl;
+    if (!first) { es.bias = nullptr; es.R = g.C; es.ldr = g.ldc; es.r_b1 = g.c_b1; es.r_b2 = g.c_b2; }
+    if (!last) { es.act = GN_ACT_LINEAR; es.mask = nullptr; es.Chi = nullptr; es.Clo = nullptr; }
+    GN_TRY(tc_launch(ctx, As, Bs, es));
+  }
+  return GN_OK;
 }
 
 }  // namespace gn

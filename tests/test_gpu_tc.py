@@ -27,7 +27,8 @@ def _gemm(device, engine, A, B, bias):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 32), (128, 256, 64), (256, 512, 256), (300, 520, 100), (129, 70, 70), (1, 8, 5),
-                                   (2048, 1024, 1024), (4096, 256, 4096)])
+                                   (2048, 1024, 1024), (4096, 256, 4096),
+                                   (256, 384, 70000)])          # a weight-gradient shape: contraction over all tokens, cut into slices
 def test_tc_gemm_matches_fp64(device, M, N, K):
     rng = np.random.default_rng(M * 7 + N * 3 + K)
     A = rng.standard_normal((M, K)).astype(np.float32)
