@@ -229,6 +229,19 @@ static int colsum(gn_model* m, const float* in, long ld, int R, int C, float* ou
   return check_launch("colsum");
 }
 
+// LayerNorm forward: the row-in-registers kernel when the row length allows it.
+static int layernorm_forward(Ctx* ctx, const float* x, const float* gamma, const float* beta, float* y, float* mean, float* sd, long rows, int n) {
+  const bool vec = n % 128 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta)) & 15) == 0;
+  switch (vec ? n / 128 : 0) {
+    case 1: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<1>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f); break;
+    case 2: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<2>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f); break;
+    case 4: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<4>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f); break;
+    case 8: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<8>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f); break;
+    default: GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, n, 1e-5f);
+  }
+  return check_launch("layernorm_forward");
+}
+
 // The fused kernels (attention.cuh) are the default; GONEURON_CUDA_ATTENTION=unfused selects the path that
 // materialises the score matrices and runs the five products as batched contractions on the tcgen05 engine.
 static bool use_fused_attention(const gn_layer_desc& d) {
@@ -329,7 +342,7 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         }
         GN_TRY(gemm_nt(ctx, N, D, D, l.att.p, D, bp.wo, bp.bo, l.r1.p, D, GN_ACT_LINEAR, cur, D));          // res1 = x + att
         float* st = l.stat.p;
-        GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(N, 8), 256, 0, l.r1.p, bp.g1, bp.be1, l.n1.p, st, st + N, (long)N, D, 1e-5f);
+        GN_TRY(layernorm_forward(ctx, l.r1.p, bp.g1, bp.be1, l.n1.p, st, st + N, (long)N, D));
         {   // ff1 (ReLU) -> ff2; on the tensor-core engine ff1's epilogue also writes the operand planes ff2 consumes
           GemmDesc g1; g1.M = N; g1.N = F; g1.K = D; g1.A = l.n1.p; g1.sa_m = D; g1.sa_k = 1; g1.B = bp.w1; g1.sb_k = 1; g1.sb_n = D; g1.C = l.mid.p; g1.ldc = F; g1.bias = bp.b1; g1.act = GN_ACT_RELU;
           GemmDesc g2; g2.M = N; g2.N = D; g2.K = F; g2.A = l.mid.p; g2.sa_m = F; g2.sa_k = 1; g2.B = bp.w2; g2.sb_k = 1; g2.sb_n = F; g2.C = l.r2.p; g2.ldc = D; g2.bias = bp.b2; g2.R = l.n1.p; g2.ldr = D;   // res2 = norm1 + ff
@@ -339,7 +352,7 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
           }
           GN_TRY(gemm(ctx, g1)); GN_TRY(gemm(ctx, g2));
         }
-        GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(N, 8), 256, 0, l.r2.p, bp.g2, bp.be2, l.out.p, st + 2 * N, st + 3 * N, (long)N, D, 1e-5f);
+        GN_TRY(layernorm_forward(ctx, l.r2.p, bp.g2, bp.be2, l.out.p, st + 2 * N, st + 3 * N, (long)N, D));
         cur = l.out.p; break; }
       case GN_LAYER_CLS_POOLING:
         GN_LAUNCH(ctx, cls_fwd_kernel, B, 128, 0, cur, l.out.p, d.seq_len, d.dim); cur = l.out.p; break;
@@ -355,7 +368,7 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         cur = l.out.p; break; }
       case GN_LAYER_LAYERNORM: {
         long rows = (long)B * (l.in_size / d.dim);
-        GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(rows, 8), 256, 0, cur, p, p + d.dim, l.out.p, l.stat.p, l.stat.p + rows, rows, d.dim, 1e-5f);
+        GN_TRY(layernorm_forward(ctx, cur, p, p + d.dim, l.out.p, l.stat.p, l.stat.p + rows, rows, d.dim));
         cur = l.out.p; break; }
     }
     GN_TRY(check_launch("forward"));
@@ -367,12 +380,24 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
 static int layernorm_backward(gn_model* m, const float* g, const float* x, const float* gamma, const float* mean, const float* sd, float* dx,
                               float* gGamma, float* gBeta, long rows, int n) {
   Ctx* ctx = &m->ctx->c;
-  {
+  const bool vec = n % 128 == 0 && ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(gamma)) & 15) == 0;
+  if (vec) {
+    const int chunks = (int)std::max<long>(1, std::min<long>(rows / 32, 4L * ctx->sm_count));
+    float* part; GN_TRY(ensure(m, S_PART2, (size_t)chunks * 2 * n, &part));
+    GN_LAUNCH(ctx, layernorm_pgrad_partial_vec_kernel, dim3(cdiv(n, 1024), chunks), 256, 0, g, x, mean, sd, rows, n, part);
+    GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(n, 32), 1024, 0, part, chunks, n, gGamma, gBeta);
+  } else {
     const int chunks = (int)std::max<long>(1, std::min<long>(rows / 64, 128));
     float* part; GN_TRY(ensure(m, S_PART2, (size_t)chunks * 2 * n, &part));
     GN_LAUNCH(ctx, layernorm_pgrad_partial_kernel, dim3(cdiv(n, 128), chunks), 128, 0, g, x, mean, sd, rows, n, part);
-    GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(n, 128), 128, 0, part, chunks, n, gGamma, gBeta);
-    GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows, n);
+    GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(n, 32), 1024, 0, part, chunks, n, gGamma, gBeta);
+  }
+  switch (vec ? n / 128 : 0) {
+    case 1: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<1>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows); break;
+    case 2: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<2>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows); break;
+    case 4: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<4>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows); break;
+    case 8: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<8>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows); break;
+    default: GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows, n);
   }
   return check_launch("layernorm_backward");
 }

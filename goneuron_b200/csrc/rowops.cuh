@@ -170,11 +170,94 @@ __global__ void layernorm_pgrad_partial_kernel(const float* __restrict__ g, cons
   for (long r = r0; r < r1; r++) { float gg = g[r * n + c]; sgam += gg * ((x[r * n + c] - mean_in[r]) / std_in[r]); sbet += gg; }
   part[((long)blockIdx.y * 2) * n + c] = sgam; part[((long)blockIdx.y * 2 + 1) * n + c] = sbet;
 }
-__global__ void layernorm_pgrad_final_kernel(const float* __restrict__ part, int chunks, int n, float* __restrict__ gGamma, float* __restrict__ gBeta) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= n) return;
+// block = 32 columns x 32 groups of chunks (1024 threads); the groups are combined through shared memory in a fixed order
+__global__ void __launch_bounds__(1024) layernorm_pgrad_final_kernel(const float* __restrict__ part, int chunks, int n, float* __restrict__ gGamma, float* __restrict__ gBeta) {
+  __shared__ float sa[32][33], sb[32][33];
+  const int tx = threadIdx.x & 31, grp = threadIdx.x >> 5, c = blockIdx.x * 32 + tx;
   float a = 0.f, b = 0.f;
-  for (int k = 0; k < chunks; k++) { a += part[((long)k * 2) * n + c]; b += part[((long)k * 2 + 1) * n + c]; }
-  gGamma[c] += a; gBeta[c] += b;
+  if (c < n) for (int k = grp; k < chunks; k += 32) { a += part[((long)k * 2) * n + c]; b += part[((long)k * 2 + 1) * n + c]; }
+  sa[grp][tx] = a; sb[grp][tx] = b;
+  __syncthreads();
+  if (grp == 0 && c < n) {
+    float ta = 0.f, tb = 0.f;
+    for (int k = 0; k < 32; k++) { ta += sa[k][tx]; tb += sb[k][tx]; }
+    gGamma[c] += ta; gBeta[c] += tb;
+  }
+}
+
+// Row-in-registers variants for n = 128 * NV (NV <= 16): one warp per row, the row is read once with 16-byte loads
+// and kept in registers between the reduction and the output pass.  Same arithmetic as the kernels above.
+template <int NV>
+__global__ void __launch_bounds__(256) layernorm_fwd_vec_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                                float* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ std_out, long rows, float eps) {
+  constexpr int n = 128 * NV;
+  const long row = (long)blockIdx.x * 8 + (threadIdx.x >> 5); if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float4* xr = reinterpret_cast<const float4*>(x + row * n) + lane;
+  float4 v[NV];
+#pragma unroll
+  for (int k = 0; k < NV; k++) v[k] = xr[32 * k];
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; k++) s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+  const float mean = warp_sum(s) / (float)n;
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; k++) { float a = v[k].x - mean, b = v[k].y - mean, c = v[k].z - mean, d = v[k].w - mean; ss += (a * a + b * b) + (c * c + d * d); }
+  const float sd = sqrtf(warp_sum(ss) / (float)n + eps), isd = 1.f / sd;     // one reciprocal per row instead of a division per element
+  float4* yr = reinterpret_cast<float4*>(y + row * n) + lane;
+#pragma unroll
+  for (int k = 0; k < NV; k++) {
+    const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma) + lane + 32 * k), be = __ldg(reinterpret_cast<const float4*>(beta) + lane + 32 * k);
+    yr[32 * k] = make_float4(ga.x * ((v[k].x - mean) * isd) + be.x, ga.y * ((v[k].y - mean) * isd) + be.y, ga.z * ((v[k].z - mean) * isd) + be.z, ga.w * ((v[k].w - mean) * isd) + be.w);
+  }
+  if (lane == 0) { mean_out[row] = mean; std_out[row] = sd; }
+}
+template <int NV>
+__global__ void __launch_bounds__(256) layernorm_bwd_vec_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
+                                                                const float* __restrict__ mean_in, const float* __restrict__ std_in, float* dx, long rows) {
+  constexpr int n = 128 * NV;
+  const long row = (long)blockIdx.x * 8 + (threadIdx.x >> 5); if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const float4* xr = reinterpret_cast<const float4*>(x + row * n) + lane;
+  const float4* gr = reinterpret_cast<const float4*>(g + row * n) + lane;
+  float4 q[NV], d[NV];
+#pragma unroll
+  for (int k = 0; k < NV; k++) { q[k] = gr[32 * k]; d[k] = xr[32 * k]; }
+  const float mean = mean_in[row], sd = std_in[row];
+  float sg = 0.f, sgx = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; k++) {
+    const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma) + lane + 32 * k);
+    q[k].x *= ga.x; q[k].y *= ga.y; q[k].z *= ga.z; q[k].w *= ga.w;
+    d[k].x -= mean; d[k].y -= mean; d[k].z -= mean; d[k].w -= mean;
+    sg += (q[k].x + q[k].y) + (q[k].z + q[k].w);
+    sgx += (q[k].x * d[k].x + q[k].y * d[k].y) + (q[k].z * d[k].z + q[k].w * d[k].w);
+  }
+  sg = warp_sum(sg); sgx = warp_sum(sgx);
+  const float fn = (float)n, sgn = sg / fn, isd = 1.f / sd, w = sgx / (fn * sd * sd);     // reciprocals per row, not per element
+  float4* dr = reinterpret_cast<float4*>(dx + row * n) + lane;
+#pragma unroll
+  for (int k = 0; k < NV; k++)
+    dr[32 * k] = make_float4((q[k].x - sgn) * isd - d[k].x * w, (q[k].y - sgn) * isd - d[k].y * w,
+                             (q[k].z - sgn) * isd - d[k].z * w, (q[k].w - sgn) * isd - d[k].w * w);
+}
+// Partial column sums for gGamma / gBeta with 16-byte loads: block = 256 threads = up to 1024 columns, grid.x covers the
+// columns, grid.y the row chunks; part layout as in layernorm_pgrad_partial_kernel.
+__global__ void __launch_bounds__(256) layernorm_pgrad_partial_vec_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ mean_in,
+                                                                          const float* __restrict__ std_in, long rows, int n, float* __restrict__ part) {
+  const int c = (blockIdx.x * 256 + threadIdx.x) * 4; if (c >= n) return;
+  const long chunks = gridDim.y, per = (rows + chunks - 1) / chunks, r0 = blockIdx.y * per, r1 = min(rows, r0 + per);
+  float4 sgam = make_float4(0.f, 0.f, 0.f, 0.f), sbet = sgam;
+#pragma unroll 4
+  for (long r = r0; r < r1; r++) {
+    const float4 gg = *reinterpret_cast<const float4*>(g + r * n + c), xx = *reinterpret_cast<const float4*>(x + r * n + c);
+    const float mean = mean_in[r], isd = 1.f / std_in[r];
+    sgam.x += gg.x * ((xx.x - mean) * isd); sgam.y += gg.y * ((xx.y - mean) * isd); sgam.z += gg.z * ((xx.z - mean) * isd); sgam.w += gg.w * ((xx.w - mean) * isd);
+    sbet.x += gg.x; sbet.y += gg.y; sbet.z += gg.z; sbet.w += gg.w;
+  }
+  *reinterpret_cast<float4*>(part + ((long)blockIdx.y * 2) * n + c) = sgam;
+  *reinterpret_cast<float4*>(part + ((long)blockIdx.y * 2 + 1) * n + c) = sbet;
 }
 
 // ---------------------------------------------------------------- embedding / positional / CLS

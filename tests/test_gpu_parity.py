@@ -39,6 +39,8 @@ CASES = [
     ("cnn_bn", dict(hw=10, c0=2, c1=5, classes=3), 7, 1),
     ("mlp_ln", {}, 16, 1),                                                                                  # stand-alone LayerNorm, sigmoid-family activation
     ("mlp_ln", dict(in_size=10, hidden=2200, norm=1100, classes=3), 5, 1),                                  # rows wider than the fused kernel holds
+    ("mlp_ln", dict(in_size=12, hidden=2048, norm=1024, classes=3), 9, 1),                                   # row-in-registers LayerNorm kernels, 8 x 128 columns
+    ("mlp_ln", dict(in_size=12, hidden=1024, norm=512, classes=3), 9, 1),                                   # ... 4 x 128 columns
 ]
 
 
