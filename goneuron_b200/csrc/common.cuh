@@ -67,6 +67,18 @@ inline cudaError_t copy_d2h(Ctx* c, void* dst, const void* src, size_t bytes) {
   cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream); return e != cudaSuccess ? e : cudaStreamSynchronize(c->stream);
 }
 
+// Contraction profiling (gn_model_set_profiling): one CUDA-event pair around each contraction KERNEL launch (the operand
+// split passes are separate, memory-bound kernels and are not inside the bracket).
+struct ProfScope {
+  Ctx* c; cudaEvent_t e1 = nullptr;
+  explicit ProfScope(Ctx* ctx) : c(ctx) {
+    if (!c->profile) return;
+    if (c->ev_used == c->ev_pool.size()) { cudaEvent_t a, b; if (cudaEventCreate(&a) != cudaSuccess || cudaEventCreate(&b) != cudaSuccess) return; c->ev_pool.push_back({a, b}); }
+    cudaEventRecord(c->ev_pool[c->ev_used].first, c->stream); e1 = c->ev_pool[c->ev_used].second; c->ev_used++;
+  }
+  ~ProfScope() { if (e1) cudaEventRecord(e1, c->stream); }
+};
+
 // Owning device buffer.
 struct DevBuf {
   float* p = nullptr; size_t n = 0;

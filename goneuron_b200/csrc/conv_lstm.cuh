@@ -77,6 +77,77 @@ __global__ void conv2d_wgrad_kernel(const float* __restrict__ g, const float* __
   }
 }
 
+// Weight gradient, tiled: one block per (oc, ic) pair and batch slice, so the K*K taps of the pair share every load of
+// g and the input plane is read from L1; partial sums go to part[slice][nW + outC] (bias partials from the ic == 0
+// blocks) and conv2d_wgrad_final_kernel adds the slices in order.  Same sums as conv2d_wgrad_kernel.
+template <int K>
+__global__ void __launch_bounds__(256) conv2d_wgrad_tile_kernel(const float* __restrict__ g, const float* __restrict__ x, float* __restrict__ part, ConvShape c, int slices) {
+  __shared__ float red[8][K * K + 1];
+  const int pair = blockIdx.x, oc = pair / c.inC, ic = pair % c.inC, sl = blockIdx.y;
+  const int bper = (c.B + slices - 1) / slices, b0 = sl * bper, b1 = min(c.B, b0 + bper);
+  const int npos = c.oH * c.oW, nW = c.outC * c.inC * K * K;
+  float acc[K * K], sb = 0.f;
+#pragma unroll
+  for (int t = 0; t < K * K; t++) acc[t] = 0.f;
+  const long span = (long)max(0, b1 - b0) * npos;
+  for (long i = threadIdx.x; i < span; i += 256) {
+    const int b = b0 + (int)(i / npos), pos = (int)(i % npos), oh = pos / c.oW, ow = pos - oh * c.oW;
+    const float gv = g[(((long)b * c.outC + oc) * c.oH + oh) * c.oW + ow];
+    sb += gv;
+    const float* xb = x + ((long)b * c.inC + ic) * c.H * c.W;
+#pragma unroll
+    for (int kh = 0; kh < K; kh++) {
+      const int ih = oh * c.s + kh - c.p; if (ih < 0 || ih >= c.H) continue;
+#pragma unroll
+      for (int kw = 0; kw < K; kw++) {
+        const int iw = ow * c.s + kw - c.p; if (iw < 0 || iw >= c.W) continue;
+        acc[kh * K + kw] = fmaf(gv, xb[ih * c.W + iw], acc[kh * K + kw]);
+      }
+    }
+  }
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+#pragma unroll
+  for (int t = 0; t < K * K; t++) { const float v = warp_sum(acc[t]); if (lane == 0) red[w][t] = v; }
+  sb = warp_sum(sb); if (lane == 0) red[w][K * K] = sb;
+  __syncthreads();
+  if (threadIdx.x <= K * K) {
+    float v = 0.f;
+    for (int q = 0; q < 8; q++) v += red[q][threadIdx.x];
+    float* prow = part + (long)sl * (nW + c.outC);
+    if (threadIdx.x < K * K) prow[(long)pair * K * K + threadIdx.x] = v;
+    else if (ic == 0) prow[nW + oc] = v;
+  }
+}
+__global__ void conv2d_wgrad_final_kernel(const float* __restrict__ part, int slices, int n, float* __restrict__ dW) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x; if (i >= n) return;
+  float s = 0.f;
+  for (int k = 0; k < slices; k++) s += part[(long)k * n + i];
+  dW[i] += s;                                             // weights, then biases: the gradient slice is laid out W | b
+}
+// Input gradient for stride 1 (no division in the tap loops); same sum as conv2d_dgrad_kernel.
+template <int K>
+__global__ void __launch_bounds__(256) conv2d_dgrad_s1_kernel(const float* __restrict__ g, const float* __restrict__ Wt, float* __restrict__ dx, ConvShape c) {
+  const long total = (long)c.B * c.inC * c.H * c.W;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    const int iw = (int)(i % c.W); long r = i / c.W; const int ih = (int)(r % c.H); r /= c.H; const int ic = (int)(r % c.inC), b = (int)(r / c.inC);
+    const float* gb = g + (long)b * c.outC * c.oH * c.oW;
+    float acc = 0.f;
+    for (int oc = 0; oc < c.outC; oc++) {
+      const float* gp = gb + (long)oc * c.oH * c.oW; const float* wp = Wt + ((long)oc * c.inC + ic) * K * K;
+#pragma unroll
+      for (int kh = 0; kh < K; kh++) {
+        const int oh = ih + c.p - kh; if (oh < 0 || oh >= c.oH) continue;
+#pragma unroll
+        for (int kw = 0; kw < K; kw++) {
+          const int ow = iw + c.p - kw; if (ow < 0 || ow >= c.oW) continue;
+          acc = fmaf(gp[oh * c.oW + ow], __ldg(wp + kh * K + kw), acc);
+        }
+      }
+    }
+    dx[i] = acc;
+  }
+}
+
 struct PoolShape { int B, C, k, s, p, H, W, oH, oW; };
 // reference: maxpool2d.go:192-221 (init -inf, strict '>', first maximum wins, argmax = flat CHW index)
 __global__ void maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int* __restrict__ arg, PoolShape c) {

@@ -113,8 +113,43 @@ __global__ void __launch_bounds__(SG_THREADS) gemm_simt_kernel(GemmDesc g) {
   }
 }
 
+// Skinny outputs (N <= 16, both operands K-major, one problem): the tiled kernel would run a handful of CTAs over a
+// long K loop.  Here one block owns one output row: its threads stride over K with all N sums in registers, then
+// combine through shared memory.  C(m,n) = act(sum_k A(m,k) B(n,k) + bias[n] + R(m,n)).
+constexpr int SKINNY_N = 16;
+__global__ void __launch_bounds__(256) gemm_skinny_kernel(GemmDesc g) {
+  __shared__ float red[8][SKINNY_N];
+  const int m = blockIdx.x, lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const float* a = g.A + (long)m * g.sa_m;
+  float acc[SKINNY_N];
+#pragma unroll
+  for (int n = 0; n < SKINNY_N; n++) acc[n] = 0.f;
+  for (int k = threadIdx.x; k < g.K; k += 256) {
+    const float av = a[k];
+#pragma unroll
+    for (int n = 0; n < SKINNY_N; n++) if (n < g.N) acc[n] = fmaf(av, g.B[(long)n * g.sb_n + k], acc[n]);
+  }
+#pragma unroll
+  for (int n = 0; n < SKINNY_N; n++) { const float v = warp_sum(acc[n]); if (lane == 0) red[w][n] = v; }
+  __syncthreads();
+  if (threadIdx.x < g.N) {
+    const int n = threadIdx.x;
+    float v = 0.f;
+    for (int q = 0; q < 8; q++) v += red[q][n];
+    if (g.bias) v += g.bias[n];
+    if (g.R) v += g.R[(long)m * g.ldr + n];
+    if (g.act == GN_ACT_RELU) v = v > 0.f ? v : 0.f;
+    g.C[(long)m * g.ldc + n] = v;
+  }
+}
+inline bool gemm_skinny_ok(const GemmDesc& g) {
+  return g.batch1 * g.batch2 == 1 && g.N <= SKINNY_N && g.K >= 256 && g.sa_k == 1 && g.sb_k == 1 && !g.mask && g.alpha == 1.f && g.flags == 0 &&
+         (g.act == GN_ACT_LINEAR || g.act == GN_ACT_RELU);
+}
+
 inline int gemm_simt(Ctx* ctx, const GemmDesc& g) {
   if (g.M <= 0 || g.N <= 0) return GN_OK;
+  if (gemm_skinny_ok(g)) { GN_LAUNCH(ctx, gemm_skinny_kernel, g.M, 256, 0, g); return check_launch("gemm_skinny"); }
   dim3 grid(cdiv(g.N, SG_BN), cdiv(g.M, SG_BM), g.batch1 * g.batch2);
   bool ak = (g.sa_k == 1), bn = (g.sb_n == 1);
   if (ak && bn) GN_LAUNCH(ctx, (gemm_simt_kernel<true, true>), grid, SG_THREADS, 0, g);

@@ -523,6 +523,7 @@ inline int tc_launch(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcPar
   if (ep.mask) vec = vec && ep.mask_ld % 4 == 0 && a16(ep.mask);
   if (ep.Chi) vec = vec && ep.c_ldp % 4 == 0 && a16(ep.Chi) && a16(ep.Clo);
   if (vec) ep.flags |= TC_FLAG_VEC;
+  ProfScope prof(ctx);
   static const int force_bn = [] { const char* e = getenv("GONEURON_TC_BN"); return e ? atoi(e) : 0; }();   // tuning aids
   static const int bk = [] { const char* e = getenv("GONEURON_TC_BK"); return e ? atoi(e) : 32; }();
   static const int persist = [] { const char* e = getenv("GONEURON_TC_PERSIST"); return e ? atoi(e) : 1; }();

@@ -41,18 +41,9 @@ static bool tc_chain_ok(Ctx* ctx, const GemmDesc& a, const GemmDesc& b) {
 
 // Chooses the tensor-core engine for large K-major x K-major products and the SIMT engine for the rest.
 static int gemm(Ctx* ctx, const GemmDesc& g) {
-  cudaEvent_t e0 = nullptr, e1 = nullptr;
-  if (ctx->profile) {
-    if (ctx->ev_used == ctx->ev_pool.size()) {
-      cudaEvent_t a, b; GN_CUDA(cudaEventCreate(&a)); GN_CUDA(cudaEventCreate(&b)); ctx->ev_pool.push_back({a, b});
-    }
-    e0 = ctx->ev_pool[ctx->ev_used].first; e1 = ctx->ev_pool[ctx->ev_used].second; ctx->ev_used++;
-    GN_CUDA(cudaEventRecord(e0, ctx->stream));
-  }
   int rc;
-  if (!force_simt_engine() && gemm_tc_eligible(ctx, g)) rc = gemm_tc(ctx, g);
-  else rc = gemm_simt(ctx, g);
-  if (ctx->profile) { GN_CUDA(cudaEventRecord(e1, ctx->stream)); }
+  if (!force_simt_engine() && gemm_tc_eligible(ctx, g)) rc = gemm_tc(ctx, g);          // brackets its kernel launches itself
+  else { ProfScope prof(ctx); rc = gemm_simt(ctx, g); }
   double nb = (double)g.batch1 * g.batch2;
   double flops = 2.0 * g.M * (double)g.N * g.K * nb;
   if (g.flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0)) flops *= 0.5;   // causal: about half the tiles exist
@@ -568,8 +559,21 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         long n = (long)B * l.out_size; float* dzb; GN_TRY(ensure(m, S_DZ, (size_t)n, &dzb));
         GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, l.z.p, dzb, n, d.activation);
         int nW = d.out_size * d.in_size * d.kernel * d.kernel;
-        GN_LAUNCH(ctx, conv2d_wgrad_kernel, nW + d.out_size, 256, 0, dzb, xin, gr, gr + nW, c);
-        if (need_dx) { long ni = (long)B * l.in_size; GN_LAUNCH(ctx, conv2d_dgrad_kernel, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c); g = dx; flip ^= 1; }
+        if (d.kernel == 3 || d.kernel == 5 || d.kernel == 1) {
+          const int pairs = d.out_size * d.in_size, slices = std::max(1, std::min(B, (4 * ctx->sm_count + pairs - 1) / pairs)), ng = nW + d.out_size;
+          float* part; GN_TRY(ensure(m, S_PART, (size_t)slices * ng, &part));
+          if (d.kernel == 3) GN_LAUNCH(ctx, conv2d_wgrad_tile_kernel<3>, dim3(pairs, slices), 256, 0, dzb, xin, part, c, slices);
+          else if (d.kernel == 5) GN_LAUNCH(ctx, conv2d_wgrad_tile_kernel<5>, dim3(pairs, slices), 256, 0, dzb, xin, part, c, slices);
+          else GN_LAUNCH(ctx, conv2d_wgrad_tile_kernel<1>, dim3(pairs, slices), 256, 0, dzb, xin, part, c, slices);
+          GN_LAUNCH(ctx, conv2d_wgrad_final_kernel, cdiv(ng, 256), 256, 0, part, slices, ng, gr);
+        } else GN_LAUNCH(ctx, conv2d_wgrad_kernel, nW + d.out_size, 256, 0, dzb, xin, gr, gr + nW, c);
+        if (need_dx) {
+          long ni = (long)B * l.in_size;
+          if (d.stride == 1 && d.kernel == 3) GN_LAUNCH(ctx, conv2d_dgrad_s1_kernel<3>, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
+          else if (d.stride == 1 && d.kernel == 5) GN_LAUNCH(ctx, conv2d_dgrad_s1_kernel<5>, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
+          else GN_LAUNCH(ctx, conv2d_dgrad_kernel, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
+          g = dx; flip ^= 1;
+        }
         break; }
       case GN_LAYER_MAXPOOL2D: {
         PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,

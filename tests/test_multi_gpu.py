@@ -9,7 +9,8 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-CASES = [("mlp", {}, 64), ("transformer_small", dict(vocab=512, dim=64, seq_len=16, heads=4, ff_dim=128, n_blocks=2), 8)]
+CASES = [("mlp", {}, 64), ("transformer_small", dict(vocab=512, dim=64, seq_len=16, heads=4, ff_dim=128, n_blocks=2), 8),
+         ("transformer_large", dict(vocab=500, dim=128, seq_len=256, heads=2, ff_dim=256, n_blocks=1), 4)]      # tcgen05 attention on each shard
 
 
 def _rank(rank, world, uid, out_dir):
