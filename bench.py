@@ -259,9 +259,9 @@ def main():
     achieved = gfl / (gms / 1e3) / 1e12 if gms > 0 else 0.0
     roofline = {"bound": "tensor", "achieved": achieved, "peak": pk["bf16_tflops_sustained"], "unit": "TFLOP/s",
                 "frac": achieved / pk["bf16_tflops_sustained"], "traffic": None,
-                "kernel": "contraction kernel launches of the step (gemm_tc_persist_kernel: 3xTF32 on tcgen05; small shapes on the fp32 SIMT kernel), CUDA events around each launch",
+                "kernel": "contraction kernel launches of the step (gemm_tc_persist_kernel: split-operand TF32 + 2 x BF16 on tcgen05; small shapes on the fp32 SIMT kernel), CUDA events around each launch",
                 "flops_per_step": gfl / 2, "launches_per_step": gl // 2, "ms_per_step": gms / 2, "allreduce_ms_per_step": ar_ms / 2,
-                "peak_source": pk["source"] + " cuBLAS bf16 (sustained); a 3xTF32 contraction issues 3 TF32 MMAs per product, so its ceiling is 1/6 of this"}
+                "peak_source": pk["source"] + " cuBLAS bf16 (sustained); an fp32-accurate product here is one TF32 MMA (half the bf16 rate) plus two BF16 MMAs, so its arithmetic ceiling is 1/4 of this"}
 
     # ---- end to end through the host-buffer entry point ---------------------------------------
     e2e = None

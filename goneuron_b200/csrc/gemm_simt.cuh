@@ -25,10 +25,6 @@ struct GemmDesc {
   // last token of row m's sequence, see relu_mask semantics in model.cu)
   const float* mask = nullptr; long mask_ld = 0; int mask_group = 1;
   float alpha = 1.f;
-  // tensor-core engine only: the result is ALSO written as hi/lo operand planes (row stride c_ldp) for a following
-  // contraction, and/or the A operand is taken from planes prepared that way instead of being split again
-  float *c_hi = nullptr, *c_lo = nullptr; long c_ldp = 0;
-  const float *a_hi = nullptr, *a_lo = nullptr; int a_ldp = 0;
   bool reuse_a_planes = false;                          // A is the same tensor as in the previous tensor-core call of this context
   int batch1 = 1, batch2 = 1;                           // batch index b -> (b / batch2, b % batch2)
   long a_b1 = 0, a_b2 = 0, b_b1 = 0, b_b2 = 0, c_b1 = 0, c_b2 = 0, r_b1 = 0, r_b2 = 0;

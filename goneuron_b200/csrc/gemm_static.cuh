@@ -4,12 +4,12 @@
 // Who that is: a host that has already handed every byte of HBM to its own pool (a later cudaMalloc can
 // only fail or fragment it), and a host with a latency budget per step, because cudaMalloc / cudaFree take
 // the driver's allocator lock and cudaFree waits for the device.  The regular path (gemm_tc) keeps its
-// hi/lo operand planes in buffers that grow on demand with cudaMalloc; this variant keeps them in one
+// operand planes in buffers that grow on demand with cudaMalloc; this variant keeps them in one
 // fixed array that is part of the library image instead.
 //
 // Cost and limit: GN_STATIC_SCRATCH_BYTES (16 MiB) of device memory are held on every GPU that loads the
 // library, from load until the process exits, whether or not this entry point is ever called.  A problem
-// needs 2 * (M + N) * roundup4(K) floats of it; larger problems are rejected with GN_ERR_INVALID_ARG.
+// needs 2 * (M + N) * roundup8(K) floats of it; larger problems are rejected with GN_ERR_INVALID_ARG.
 //
 // Sharing: there is ONE array per GPU.  Every call on that GPU uses it and leaves its operand planes behind;
 // each call rewrites all of the part it reads (padding columns included), so nothing needs clearing
@@ -51,10 +51,10 @@ extern "C" int gn_op_gemm_nt_static(gn_ctx* ctx, int M, int N, int K, const floa
   if (!ctx || !ctx->alive || !A_dev || !B_dev || !C_dev || M <= 0 || N <= 0 || K <= 0) return fail(GN_ERR_INVALID_ARG, "op_gemm_nt_static: bad argument");
   Ctx* c = &ctx->c;
   if (!c->tc_ok) return fail(GN_ERR_UNSUPPORTED, "the tensor-core engine is not available on this context");
-  const long ldp = ((long)K + 3) / 4 * 4;
+  const long ldp = tc_ldp(K);
   const long need = 2 * ((long)M + N) * ldp;
   if (need > GN_STATIC_SCRATCH_FLOATS)
-    return fail(GN_ERR_INVALID_ARG, "op_gemm_nt_static: M=%d N=%d K=%d needs %ld scratch floats, the fixed array holds %ld (2*(M+N)*roundup4(K) must not exceed it)",
+    return fail(GN_ERR_INVALID_ARG, "op_gemm_nt_static: M=%d N=%d K=%d needs %ld scratch floats, the fixed array holds %ld (2*(M+N)*roundup8(K) must not exceed it)",
                 M, N, K, need, GN_STATIC_SCRATCH_FLOATS);
   GN_CUDA(cudaSetDevice(c->device));
   float* base = nullptr; GN_TRY(static_scratch_ptr(c->device, &base));
@@ -62,7 +62,7 @@ extern "C" int gn_op_gemm_nt_static(gn_ctx* ctx, int M, int N, int K, const floa
   TcPlanes PA{a_hi, a_lo, M, K, (int)ldp, 1}, PB{b_hi, b_lo, N, K, (int)ldp, 1};
   GN_TRY(tc_split(c, TcSrc{A_dev, (long)K, 1, 0, 0, 1}, PA));
   GN_TRY(tc_split(c, TcSrc{B_dev, (long)K, 1, 0, 0, 1}, PB));
-  TcParams ep{C_dev, (long)N, 0, 0, bias_dev, nullptr, 0, 0, 0, GN_ACT_LINEAR, M, N, K, 1, 0, c->d_status, nullptr, 0, 1, nullptr, nullptr, 0};
+  TcParams ep{C_dev, (long)N, 0, 0, bias_dev, nullptr, 0, 0, 0, GN_ACT_LINEAR, M, N, K, 1, 0, c->d_status, nullptr, 0, 1};
   GN_TRY(tc_launch(c, PA, PB, ep));
   GN_CUDA(cudaStreamSynchronize(c->stream));
   int st = 0; GN_CUDA(copy_d2h(c, &st, c->d_status, sizeof(int)));

@@ -31,14 +31,6 @@ namespace gn {
 
 // ------------------------------------------------------------------ contraction dispatch
 static bool force_simt_engine() { static const bool f = [] { const char* e = getenv("GONEURON_CUDA_ENGINE"); return e && strcmp(e, "simt") == 0; }(); return f; }
-// Both contractions of a producer -> consumer pair run on the tensor-core engine (so operand planes can be handed over).
-static bool tc_chain_ok(Ctx* ctx, const GemmDesc& a, const GemmDesc& b) {
-  // measured: the extra plane stores in the producer's epilogue cost more (419 ms / step) than the split pass they save
-  // (401 ms), so the hand-over is off unless GONEURON_TC_CHAIN=1
-  static const bool on = [] { const char* e = getenv("GONEURON_TC_CHAIN"); return e && atoi(e) == 1; }();
-  return on && !force_simt_engine() && gemm_tc_eligible(ctx, a) && gemm_tc_eligible(ctx, b);
-}
-
 // Chooses the tensor-core engine for large K-major x K-major products and the SIMT engine for the rest.
 static int gemm(Ctx* ctx, const GemmDesc& g) {
   int rc;
@@ -334,13 +326,9 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         GN_TRY(gemm_nt(ctx, N, D, D, l.att.p, D, bp.wo, bp.bo, l.r1.p, D, GN_ACT_LINEAR, cur, D));          // res1 = x + att
         float* st = l.stat.p;
         GN_TRY(layernorm_forward(ctx, l.r1.p, bp.g1, bp.be1, l.n1.p, st, st + N, (long)N, D));
-        {   // ff1 (ReLU) -> ff2; on the tensor-core engine ff1's epilogue also writes the operand planes ff2 consumes
+        {   // ff1 (ReLU) -> ff2
           GemmDesc g1; g1.M = N; g1.N = F; g1.K = D; g1.A = l.n1.p; g1.sa_m = D; g1.sa_k = 1; g1.B = bp.w1; g1.sb_k = 1; g1.sb_n = D; g1.C = l.mid.p; g1.ldc = F; g1.bias = bp.b1; g1.act = GN_ACT_RELU;
           GemmDesc g2; g2.M = N; g2.N = D; g2.K = F; g2.A = l.mid.p; g2.sa_m = F; g2.sa_k = 1; g2.B = bp.w2; g2.sb_k = 1; g2.sb_n = F; g2.C = l.r2.p; g2.ldc = D; g2.bias = bp.b2; g2.R = l.n1.p; g2.ldr = D;   // res2 = norm1 + ff
-          if (tc_chain_ok(ctx, g1, g2) && F % 4 == 0) {
-            float *ph, *pl; GN_TRY(ensure(m, S_PL_HI, (size_t)N * F, &ph)); GN_TRY(ensure(m, S_PL_LO, (size_t)N * F, &pl));
-            g1.c_hi = ph; g1.c_lo = pl; g1.c_ldp = F; g2.a_hi = ph; g2.a_lo = pl; g2.a_ldp = F;
-          }
           GN_TRY(gemm(ctx, g1)); GN_TRY(gemm(ctx, g2));
         }
         GN_TRY(layernorm_forward(ctx, l.r2.p, bp.g2, bp.be2, l.out.p, st + 2 * N, st + 3 * N, (long)N, D));
@@ -421,10 +409,6 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
     GemmDesc g; g.M = N; g.N = F; g.K = D; g.A = dR2; g.sa_m = D; g.sa_k = 1; g.B = bp.w2; g.sb_k = F; g.sb_n = 1; g.C = dM; g.ldc = F;
     g.mask = l.mid.p + (long)(T - 1) * F; g.mask_ld = (long)T * F; g.mask_group = T;
     GemmDesc h; h.M = N; h.N = D; h.K = F; h.A = dM; h.sa_m = F; h.sa_k = 1; h.B = bp.w1; h.sb_k = D; h.sb_n = 1; h.C = comb; h.ldc = D; h.R = dR2; h.ldr = D;   // combined = gradRes2 + W1^T dz1
-    if (tc_chain_ok(ctx, g, h) && F % 4 == 0) {
-      float *ph, *pl; GN_TRY(ensure(m, S_PL_HI, (size_t)N * F, &ph)); GN_TRY(ensure(m, S_PL_LO, (size_t)N * F, &pl));
-      g.c_hi = ph; g.c_lo = pl; g.c_ldp = F; h.a_hi = ph; h.a_lo = pl; h.a_ldp = F;
-    }
     GN_TRY(gemm(ctx, g));
     GN_TRY(inner_dense_param_grads(m, dM, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1));
     GN_TRY(gemm(ctx, h));

@@ -222,7 +222,7 @@ int gn_op_attention(gn_ctx* ctx, int engine, int B, int T, int D, int H, int cau
  * counterpart in the reference.  A, B, bias (may be NULL) and C are DEVICE pointers supplied by the caller
  * (A [M,K], B [N,K], C [M,N], row-major, dense); the operand planes live in a fixed 16 MiB array inside the
  * library image, which every GPU that loads the library holds until the process exits.  Limit:
- * 2*(M+N)*roundup4(K) <= 4 Mi floats, else GN_ERR_INVALID_ARG.  The entry point calls no cudaMalloc / cudaFree.
+ * 2*(M+N)*roundup8(K) <= 4 Mi floats, else GN_ERR_INVALID_ARG.  The entry point calls no cudaMalloc / cudaFree.
  * The first call on each device resolves the array's device address; make it before any stream capture.
  * All calls on one GPU share the array (it keeps the last call's planes; each call rewrites what it reads):
  * calls that overlap on the GPU race, so issue them one after the other. */
