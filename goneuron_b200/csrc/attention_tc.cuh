@@ -4,7 +4,8 @@
 // reference: internal/layer/transformer.go:470-503 (forward) -- same arithmetic as attention.cuh: scores =
 // q.k / sqrt(hd), masked entries removed, row softmax, weighted sum of v; row maximum and row sum kept per row.
 //
-// Operands: hi/lo planes (3xTF32) written by the split kernels of gemm_tc.cuh, one problem per (batch, head):
+// Operands: the split planes of gemm_tc.cuh's scheme (hi = tf32(x) as fp32, bf16(x), bf16(x - hi); every product is one
+// TF32 MMA on hi x hi plus two BF16 MMAs for the cross terms), one problem per (batch, head):
 //   Qp, Kp : [B*H][T][64]   (contraction over the head dimension is along the row)
 //   Vt     : [B*H][64][T]   (transposed, so that the contraction over the keys is along the row as well)
 // (attn_split_kernel writes both kinds from one read of the tensor)
@@ -14,7 +15,7 @@
 //               O += P_j V_j with P read from TMEM as the A operand and Vt_j from shared memory.
 //   warps 2-9 : two threads per query row (TMEM lane = row, 32 of the 64 columns each): tcgen05.ld of S_j, running
 //               maximum (exchanged through shared memory) and sum, p = exp(s - m), hi written over S_j in place and
-//               lo into a second buffer (tcgen05.st); when a row maximum moved, the output accumulator is rescaled
+//               bf16(p), bf16(p - hi) packed two per column into a second buffer (tcgen05.st); when a row maximum moved, the output accumulator is rescaled
 //               in TMEM after the previous P V has completed.  One warp per scheduler could not keep up with the
 //               tensor pipe (measured: 25 % tensor activity); two do.
 // The issue order S_0, S_1, PV_0, S_2, PV_1, ... keeps the tensor pipe busy with S_{j+1} (and PV_{j-1}) while the
@@ -44,6 +45,25 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
         "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
 }
+__device__ __forceinline__ void tc_mma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]),
+                 "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+// 32 fp32 values -> hi (TF32, in place) and the packed bf16 pairs of the value and of value - hi (16 words each)
+__device__ __forceinline__ void split_pack32(uint32_t (&v)[32], uint32_t (&xb)[16], uint32_t (&lob)[16]) {
+#pragma unroll
+  for (int e = 0; e < 16; e++) {
+    const float a = __uint_as_float(v[2 * e]), b = __uint_as_float(v[2 * e + 1]);
+    const uint32_t ha = v[2 * e] & 0xffffe000u, hb = v[2 * e + 1] & 0xffffe000u;
+    xb[e] = pack_bf16(a, b); lob[e] = pack_bf16(a - __uint_as_float(ha), b - __uint_as_float(hb));
+    v[2 * e] = ha; v[2 * e + 1] = hb;
+  }
+}
 __device__ __forceinline__ float fast_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -54,6 +74,9 @@ __device__ __forceinline__ bool warp_mbar_wait(uint32_t bar, uint32_t parity, in
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
+// Tensor maps of a launch: three per operand (hi fp32 | bf16 copy | bf16 lo).
+template <int N> struct AttnMaps { CUtensorMap m[N]; };
+
 // Persistent: gridDim.x CTAs (one per SM) walk the tiles; tile id = blockIdx.x + i * gridDim.x names (batch*head, query
 // block), the query block being rotated by i so that every CTA sees short and long causal tiles alike (gridDim.x is a
 // multiple of the number of query blocks).  All counters below run across tiles, so the barriers' phases simply continue:
@@ -61,9 +84,7 @@ __device__ __forceinline__ bool warp_mbar_wait(uint32_t bar, uint32_t parity, in
 // the first score products of the next tile run while the elementwise warps finish the current tile and write it out
 // (the output accumulator is double-buffered for that).
 __global__ void __launch_bounds__(ATC_THREADS, 1)
-attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constant__ CUtensorMap mQl, const __grid_constant__ CUtensorMap mKh,
-                   const __grid_constant__ CUtensorMap mKl, const __grid_constant__ CUtensorMap mVh, const __grid_constant__ CUtensorMap mVl,
-                   float* __restrict__ O, float* __restrict__ Mst, float* __restrict__ Lst, int T, int D, int H, int causal, float inv_scale,
+attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__ O, float* __restrict__ Mst, float* __restrict__ Lst, int T, int D, int H, int causal, float inv_scale,
                    int ntiles, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -105,24 +126,21 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
         int z, q0, nblk; decode(id, tt, z, q0, nblk);
         if (tt > 0) ok &= mbar_wait(BAR(14), (tt - 1) & 1);
         mbar_expect_tx(BAR(0), ATC_Q_BYTES);
-        for (int c = 0; c < 2; c++) {
-          tma_load_3d(smem_u32(sQ + c * 16384), &mQh, c * 32, q0, z, BAR(0));
-          tma_load_3d(smem_u32(sQ + 32768 + c * 16384), &mQl, c * 32, q0, z, BAR(0));
-        }
+        for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sQ + c * 16384), &maps.m[0], c * 32, q0, z, BAR(0));
+        tma_load_3d(smem_u32(sQ + 32768), &maps.m[1], 0, q0, z, BAR(0));
+        tma_load_3d(smem_u32(sQ + 49152), &maps.m[2], 0, q0, z, BAR(0));
         for (int j = 0; j < nblk; j++, g++) {
           const uint32_t s = g & 1, u = g >> 1;
           if (u > 0) ok &= mbar_wait(BAR(3 + s), (u - 1) & 1);
           mbar_expect_tx(BAR(1 + s), ATC_K_BYTES);
-          for (int c = 0; c < 2; c++) {
-            tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + c * 8192), &mKh, c * 32, j * ATC_BK, z, BAR(1 + s));
-            tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + 16384 + c * 8192), &mKl, c * 32, j * ATC_BK, z, BAR(1 + s));
-          }
+          for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + c * 8192), &maps.m[3], c * 32, j * ATC_BK, z, BAR(1 + s));
+          tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + 16384), &maps.m[4], 0, j * ATC_BK, z, BAR(1 + s));
+          tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + 24576), &maps.m[5], 0, j * ATC_BK, z, BAR(1 + s));
           if (u > 0) ok &= mbar_wait(BAR(7 + s), (u - 1) & 1);
           mbar_expect_tx(BAR(5 + s), ATC_V_BYTES);
-          for (int c = 0; c < 2; c++) {
-            tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + c * 8192), &mVh, j * ATC_BK + c * 32, 0, z, BAR(5 + s));
-            tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + 16384 + c * 8192), &mVl, j * ATC_BK + c * 32, 0, z, BAR(5 + s));
-          }
+          for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + c * 8192), &maps.m[6], j * ATC_BK + c * 32, 0, z, BAR(5 + s));
+          tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + 16384), &maps.m[7], j * ATC_BK, 0, z, BAR(5 + s));
+          tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + 24576), &maps.m[8], j * ATC_BK, 0, z, BAR(5 + s));
         }
       }
       if (!ok) atomicExch(status, 11);
@@ -130,7 +148,7 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true; uint32_t g0 = 0;
-      constexpr uint32_t idesc = make_idesc(ATC_BQ, 64);
+      constexpr uint32_t idesc = make_idesc(ATC_BQ, 64), idesc_bf = make_idesc_bf16(ATC_BQ, 64);
       for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
         int z, q0, nblk; decode(id, tt, z, q0, nblk);
         const uint32_t ob = tt & 1;
@@ -141,15 +159,17 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
           const uint32_t acc = tmem_base + ATC_COL_S + s * 64;
           const uint32_t kb = smem_u32(sK + s * ATC_K_BYTES), qa = smem_u32(sQ);
 #pragma unroll
+          for (int k = 0; k < 4; k++) {                      // cross terms: bf16, 16 head columns per instruction
+            const uint64_t adv = (uint64_t)(2 * k);
+            tc_mma_bf16(acc, make_desc<32>(qa + 49152) + adv, make_desc<32>(kb + 16384) + adv, idesc_bf, k ? 1u : 0u);
+            tc_mma_bf16(acc, make_desc<32>(qa + 32768) + adv, make_desc<32>(kb + 24576) + adv, idesc_bf, 1u);
+          }
+#pragma unroll
           for (int c = 0; c < 2; c++)
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
+            for (int k = 0; k < 4; k++) {                    // main term: tf32, 8 head columns per instruction
               const uint64_t adv = (uint64_t)(2 * k);
-              const uint64_t ah = make_desc<32>(qa + c * 16384) + adv, al = make_desc<32>(qa + 32768 + c * 16384) + adv;
-              const uint64_t bh = make_desc<32>(kb + c * 8192) + adv, bl = make_desc<32>(kb + 16384 + c * 8192) + adv;
-              tc_mma_tf32(acc, al, bh, idesc, (c | k) ? 1u : 0u);
-              tc_mma_tf32(acc, ah, bl, idesc, 1u);
-              tc_mma_tf32(acc, ah, bh, idesc, 1u);
+              tc_mma_tf32(acc, make_desc<32>(qa + c * 16384) + adv, make_desc<32>(kb + c * 8192) + adv, idesc, 1u);
             }
           tc_commit(BAR(3 + s));
           tc_commit(BAR(9 + s));
@@ -163,12 +183,15 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
           const uint32_t vb = smem_u32(sV + s * ATC_V_BYTES);
           const uint32_t ph = tmem_base + ATC_COL_S + s * 64, pl = tmem_base + ATC_COL_PLO + s * 64, acc = tmem_base + ATC_COL_O + ob * 64;
 #pragma unroll
-          for (int kk = 0; kk < 8; kk++) {
+          for (int k = 0; k < 4; k++) {                      // cross terms: packed bf16 P (16 keys = 8 columns per instruction)
+            const uint64_t adv = (uint64_t)(2 * k);
+            tc_mma_bf16_ts(acc, pl + 32 + k * 8, make_desc<32>(vb + 16384) + adv, idesc_bf, (j | k) ? 1u : 0u);
+            tc_mma_bf16_ts(acc, pl + k * 8, make_desc<32>(vb + 24576) + adv, idesc_bf, 1u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++) {                   // main term: tf32 P_hi (8 keys = 8 columns per instruction)
             const int c = kk >> 2; const uint64_t adv = (uint64_t)(2 * (kk & 3));
-            const uint64_t bh = make_desc<32>(vb + c * 8192) + adv, bl = make_desc<32>(vb + 16384 + c * 8192) + adv;
-            tc_mma_tf32_ts(acc, pl + kk * 8, bh, idesc, (j | kk) ? 1u : 0u);
-            tc_mma_tf32_ts(acc, ph + kk * 8, bl, idesc, 1u);
-            tc_mma_tf32_ts(acc, ph + kk * 8, bh, idesc, 1u);
+            tc_mma_tf32_ts(acc, ph + kk * 8, make_desc<32>(vb + c * 8192) + adv, idesc, 1u);
           }
           tc_commit(BAR(7 + s));
           tc_commit(BAR(13));
@@ -189,6 +212,7 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
     // two threads per query row: `half` selects 32 of the 64 columns of a block (and of the accumulator)
     const int quad = warp & 3, half = (warp - 2) >> 2, row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + 32 * half;
+    const uint32_t pk_base = tmem_base + ((uint32_t)(quad * 32) << 16) + 16 * half;     // packed bf16 planes: 16 columns per half
     const float cs = inv_scale * 1.44269504088896341f;      // scores -> log2 units
     bool ok = true; uint32_t g0 = 0, xc = 0;
     for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
@@ -199,7 +223,7 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
         const uint32_t g = g0 + j, s = g & 1, u = g >> 1; const int key0 = j * ATC_BK + 32 * half;
         ok &= warp_mbar_wait(BAR(9 + s), u & 1, lane);
         tc_fence_after();
-        uint32_t a[32], lo[32];
+        uint32_t a[32];
         tmem_ld32(lane_base + ATC_COL_S + s * 64, a);
         tmem_wait_ld();
         if (causal && j * ATC_BK + ATC_BK - 1 > q0) {       // the block reaches above the diagonal for some row of the tile
@@ -218,13 +242,12 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap mQh, const __grid_constan
         const float mneg = -m_new * 1.44269504088896341f;
         float rs = 0.f;
 #pragma unroll
-        for (int e = 0; e < 32; e++) {
-          const float p = fast_ex2(fmaf(__uint_as_float(a[e]), cs, mneg)); rs += p;
-          const uint32_t hi = __float_as_uint(p) & 0xffffe000u;
-          a[e] = hi; lo[e] = __float_as_uint(p - __uint_as_float(hi));
-        }
-        tmem_st32(lane_base + ATC_COL_S + s * 64, a);
-        tmem_st32(lane_base + ATC_COL_PLO + s * 64, lo);
+        for (int e = 0; e < 32; e++) { const float p = fast_ex2(fmaf(__uint_as_float(a[e]), cs, mneg)); rs += p; a[e] = __float_as_uint(p); }
+        uint32_t pb[16], plb[16];
+        split_pack32(a, pb, plb);
+        tmem_st32(lane_base + ATC_COL_S + s * 64, a);                                // P_hi over S, 32-bit columns
+        tmem_st16(pk_base + ATC_COL_PLO + s * 64, pb);                               // bf16(P), two keys per column
+        tmem_st16(pk_base + ATC_COL_PLO + s * 64 + 32, plb);                         // bf16(P - P_hi)
         l_part = l_part * corr + rs; m_run = m_new;
         // The accumulator may only be touched between P V products.  The wait is unconditional: a parity wait is only
         // unambiguous when no completion of this barrier has been skipped (the first block of a tile skips none: the
@@ -297,10 +320,7 @@ constexpr uint32_t ATB_COL_S = 0, ATB_COL_DP = 128, ATB_COL_LO = 256, ATB_COL_AC
 
 template <int MODE>
 __global__ void __launch_bounds__(ATB_THREADS, 1)
-attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_constant__ CUtensorMap mR1l, const __grid_constant__ CUtensorMap mR2h,
-                   const __grid_constant__ CUtensorMap mR2l, const __grid_constant__ CUtensorMap mC1h, const __grid_constant__ CUtensorMap mC1l,
-                   const __grid_constant__ CUtensorMap mC2h, const __grid_constant__ CUtensorMap mC2l, const __grid_constant__ CUtensorMap mC3h,
-                   const __grid_constant__ CUtensorMap mC3l, const float* __restrict__ Mst, const float* __restrict__ Lst, const float* __restrict__ Dv,
+attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __restrict__ Mst, const float* __restrict__ Lst, const float* __restrict__ Dv,
                    float* __restrict__ Out, int T, int D, int H, int causal, float inv_scale, int ntiles, int* status) {
   constexpr int NR = AtbCfg<MODE>::NR;
   constexpr bool TRANS = MODE != 0;
@@ -345,25 +365,22 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
         int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
         if (tt > 0) ok &= mbar_wait(BAR(10), (tt - 1) & 1);
         mbar_expect_tx(BAR(0), NR * ATB_R_BYTES);
-        for (int c = 0; c < 2; c++) {
-          tma_load_3d(smem_u32(sR + c * 16384), &mR1h, c * 32, r0, z, BAR(0));
-          tma_load_3d(smem_u32(sR + 32768 + c * 16384), &mR1l, c * 32, r0, z, BAR(0));
-          if (NR == 2) {
-            tma_load_3d(smem_u32(sR + ATB_R_BYTES + c * 16384), &mR2h, c * 32, r0, z, BAR(0));
-            tma_load_3d(smem_u32(sR + ATB_R_BYTES + 32768 + c * 16384), &mR2l, c * 32, r0, z, BAR(0));
-          }
+        // maps: R1 = 0..2, R2 = 3..5, C1 = 6..8, C2 = 9..11, C3 = 12..14 (hi | bf16 copy | bf16 lo each)
+        for (int o = 0; o < NR; o++) {
+          const uint32_t base = smem_u32(sR + o * ATB_R_BYTES);
+          for (int c = 0; c < 2; c++) tma_load_3d(base + c * 16384, &maps.m[3 * o], c * 32, r0, z, BAR(0));
+          tma_load_3d(base + 32768, &maps.m[3 * o + 1], 0, r0, z, BAR(0));
+          tma_load_3d(base + 49152, &maps.m[3 * o + 2], 0, r0, z, BAR(0));
         }
         for (int n = 0; n < nb; n++, g++) {
           const int row = (b0 + n) * 64;
           if (g > 0) ok &= mbar_wait(BAR(2), (g - 1) & 1);
           mbar_expect_tx(BAR(1), NR * ATB_C_BYTES);
-          for (int c = 0; c < 2; c++) {
-            tma_load_3d(smem_u32(sC + c * 8192), &mC1h, c * 32, row, z, BAR(1));
-            tma_load_3d(smem_u32(sC + 16384 + c * 8192), &mC1l, c * 32, row, z, BAR(1));
-            if (NR == 2) {
-              tma_load_3d(smem_u32(sC + ATB_C_BYTES + c * 8192), &mC2h, c * 32, row, z, BAR(1));
-              tma_load_3d(smem_u32(sC + ATB_C_BYTES + 16384 + c * 8192), &mC2l, c * 32, row, z, BAR(1));
-            }
+          for (int o = 0; o < NR; o++) {
+            const uint32_t base = smem_u32(sC + o * ATB_C_BYTES);
+            for (int c = 0; c < 2; c++) tma_load_3d(base + c * 8192, &maps.m[6 + 3 * o], c * 32, row, z, BAR(1));
+            tma_load_3d(base + 16384, &maps.m[7 + 3 * o], 0, row, z, BAR(1));
+            tma_load_3d(base + 24576, &maps.m[8 + 3 * o], 0, row, z, BAR(1));
           }
         }
       }
@@ -378,10 +395,9 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
           const int col = (b0 + n) * 64;
           if (g > 0) ok &= mbar_wait(BAR(4), (g - 1) & 1);
           mbar_expect_tx(BAR(3), ATB_C_BYTES);
-          for (int c = 0; c < 2; c++) {
-            tma_load_3d(smem_u32(sC3 + c * 8192), &mC3h, col + c * 32, 0, z, BAR(3));
-            tma_load_3d(smem_u32(sC3 + 16384 + c * 8192), &mC3l, col + c * 32, 0, z, BAR(3));
-          }
+          for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sC3 + c * 8192), &maps.m[12], col + c * 32, 0, z, BAR(3));
+          tma_load_3d(smem_u32(sC3 + 16384), &maps.m[13], col, 0, z, BAR(3));
+          tma_load_3d(smem_u32(sC3 + 24576), &maps.m[14], col, 0, z, BAR(3));
         }
       }
       if (!ok) atomicExch(status, 22);
@@ -389,7 +405,7 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true; uint32_t g0 = 0;
-      constexpr uint32_t idesc = make_idesc(128, 64);
+      constexpr uint32_t idesc = make_idesc(128, 64), idesc_bf = make_idesc_bf16(128, 64);
       for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
         int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
         const uint32_t ab = tt & 1;
@@ -402,15 +418,17 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
             const uint32_t acc = tmem_base + (prod == 0 ? ATB_COL_S : ATB_COL_DP) + s * 64;
             const uint32_t ra = smem_u32(sR + prod * ATB_R_BYTES), cb = smem_u32(sC + prod * ATB_C_BYTES);
 #pragma unroll
+            for (int k = 0; k < 4; k++) {                    // cross terms: bf16, 16 head columns per instruction
+              const uint64_t adv = (uint64_t)(2 * k);
+              tc_mma_bf16(acc, make_desc<32>(ra + 49152) + adv, make_desc<32>(cb + 16384) + adv, idesc_bf, k ? 1u : 0u);
+              tc_mma_bf16(acc, make_desc<32>(ra + 32768) + adv, make_desc<32>(cb + 24576) + adv, idesc_bf, 1u);
+            }
+#pragma unroll
             for (int c = 0; c < 2; c++)
 #pragma unroll
-              for (int k = 0; k < 4; k++) {
+              for (int k = 0; k < 4; k++) {                  // main term: tf32, 8 head columns per instruction
                 const uint64_t adv = (uint64_t)(2 * k);
-                const uint64_t ah = make_desc<32>(ra + c * 16384) + adv, al = make_desc<32>(ra + 32768 + c * 16384) + adv;
-                const uint64_t bh = make_desc<32>(cb + c * 8192) + adv, bl = make_desc<32>(cb + 16384 + c * 8192) + adv;
-                tc_mma_tf32(acc, al, bh, idesc, (c | k) ? 1u : 0u);
-                tc_mma_tf32(acc, ah, bl, idesc, 1u);
-                tc_mma_tf32(acc, ah, bh, idesc, 1u);
+                tc_mma_tf32(acc, make_desc<32>(ra + c * 16384) + adv, make_desc<32>(cb + c * 8192) + adv, idesc, 1u);
               }
           }
           tc_commit(BAR(2));
@@ -426,12 +444,15 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
           const uint32_t ph = tmem_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, pl = tmem_base + ATB_COL_LO + s * 64,
                          acc = tmem_base + ATB_COL_ACC + ab * 64;
 #pragma unroll
-          for (int kk = 0; kk < 8; kk++) {
+          for (int k = 0; k < 4; k++) {                      // cross terms: packed bf16 (16 block columns = 8 TMEM columns per instruction)
+            const uint64_t adv = (uint64_t)(2 * k);
+            tc_mma_bf16_ts(acc, pl + 32 + k * 8, make_desc<32>(cb + 16384) + adv, idesc_bf, (n | k) ? 1u : 0u);
+            tc_mma_bf16_ts(acc, pl + k * 8, make_desc<32>(cb + 24576) + adv, idesc_bf, 1u);
+          }
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++) {                   // main term: tf32 hi (8 columns per instruction)
             const int c = kk >> 2; const uint64_t adv = (uint64_t)(2 * (kk & 3));
-            const uint64_t bh = make_desc<32>(cb + c * 8192) + adv, bl = make_desc<32>(cb + 16384 + c * 8192) + adv;
-            tc_mma_tf32_ts(acc, pl + kk * 8, bh, idesc, (n | kk) ? 1u : 0u);
-            tc_mma_tf32_ts(acc, ph + kk * 8, bl, idesc, 1u);
-            tc_mma_tf32_ts(acc, ph + kk * 8, bh, idesc, 1u);
+            tc_mma_tf32_ts(acc, ph + kk * 8, make_desc<32>(cb + c * 8192) + adv, idesc, 1u);
           }
           tc_commit(BAR(4));
           if (n == nb - 1) tc_commit(BAR(9));
@@ -452,6 +473,7 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
     // two threads per tile row: `half` selects 32 of the 64 columns of a block (and of the accumulator)
     const int quad = warp & 3, half = (warp - 2) >> 2, row = quad * 32 + lane, et = (warp - 2) * 32 + lane;   // et: 0..255
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + 32 * half;
+    const uint32_t pk_base = tmem_base + ((uint32_t)(quad * 32) << 16) + 16 * half;     // packed bf16 planes: 16 columns per half
     constexpr float LOG2E = 1.44269504088896341f;
     const float cs = inv_scale * LOG2E, oscale = MODE == 2 ? 1.f : inv_scale;
     bool ok = true; uint32_t g0 = 0;
@@ -469,7 +491,7 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
         }
         ok &= warp_mbar_wait(BAR(5 + s), u & 1, lane);
         tc_fence_after();
-        uint32_t a[32], b[32], lo[32];
+        uint32_t a[32], b[32];
         tmem_ld32(lane_base + ATB_COL_S + s * 64, a);
         if (MODE != 2) tmem_ld32(lane_base + ATB_COL_DP + s * 64, b);
         tmem_wait_ld();
@@ -481,11 +503,13 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap mR1h, const __grid_consta
           float v = fast_ex2(fmaf(__uint_as_float(a[e]), cs, TRANS ? stm[col] : mneg_r)) * (TRANS ? stl[col] : il_r);   // P (times 1/sqrt(hd) for dS)
           if (MODE != 2) v *= __uint_as_float(b[e]) - (TRANS ? std_[col] : d_r);                                        // dS
           if (diag && (TRANS ? ri > c0 + col : c0 + col > ri)) v = 0.f;
-          const uint32_t hi = __float_as_uint(v) & 0xffffe000u;
-          a[e] = hi; lo[e] = __float_as_uint(v - __uint_as_float(hi));
+          a[e] = __float_as_uint(v);
         }
-        tmem_st32(lane_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, a);
-        tmem_st32(lane_base + ATB_COL_LO + s * 64, lo);
+        uint32_t xb[16], lob[16];
+        split_pack32(a, xb, lob);
+        tmem_st32(lane_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, a);      // hi, 32-bit columns
+        tmem_st16(pk_base + ATB_COL_LO + s * 64, xb);                                 // bf16 copy, two block columns per TMEM column
+        tmem_st16(pk_base + ATB_COL_LO + s * 64 + 32, lob);                           // bf16 lo
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(BAR(7 + s));
@@ -531,11 +555,13 @@ inline bool attn_tc_supported(Ctx* ctx, int hd, int T, int B, int H, int D) {
   return !off && ctx->tc_ok && hd == ATC_HD && T % ATC_BQ == 0 && (long)B * H <= 65535 && D % 4 == 0;
 }
 // Operand planes of one [B*T, D] tensor for all (batch, head) problems, from ONE read of the tensor:
-//   row planes  [Z][T][64]  (ROWS)  and / or  transposed planes [Z][64][T]  (COLS),   z = batch * H + head.
+//   row planes  [Z][T][64]  (ROWS)  and / or  transposed planes [Z][64][T]  (COLS),   z = batch * H + head,
+// three planes each: hi = tf32(x) as fp32, bf16(x), bf16(x - hi).
 // One CTA = a 64 x 64 tile (64 tokens of one head); the transposition goes through shared memory.
 template <bool ROWS, bool COLS>
-__global__ void __launch_bounds__(256) attn_split_kernel(const float* __restrict__ X, float* __restrict__ rhi, float* __restrict__ rlo,
-                                                         float* __restrict__ chi, float* __restrict__ clo, int T, int D, int H) {
+__global__ void __launch_bounds__(256) attn_split_kernel(const float* __restrict__ X, float* __restrict__ rhi, __nv_bfloat16* __restrict__ rxb,
+                                                         __nv_bfloat16* __restrict__ rlo, float* __restrict__ chi, __nv_bfloat16* __restrict__ cxb,
+                                                         __nv_bfloat16* __restrict__ clo, int T, int D, int H) {
   __shared__ float tile[64][65];
   const int z = blockIdx.y, b = z / H, h = z % H, t0 = blockIdx.x * 64, i = threadIdx.x;
   const int c4 = i & 15, r0 = i >> 4;
@@ -549,7 +575,8 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const float* __restrict
       const float4 hv = make_float4(tf32_round(x[r].x), tf32_round(x[r].y), tf32_round(x[r].z), tf32_round(x[r].w));
       const long o = ((long)z * T + t0 + row) * 64 + c4 * 4;
       *reinterpret_cast<float4*>(rhi + o) = hv;
-      *reinterpret_cast<float4*>(rlo + o) = make_float4(x[r].x - hv.x, x[r].y - hv.y, x[r].z - hv.z, x[r].w - hv.w);
+      *reinterpret_cast<uint2*>(rxb + o) = make_uint2(pack_bf16(x[r].x, x[r].y), pack_bf16(x[r].z, x[r].w));
+      *reinterpret_cast<uint2*>(rlo + o) = make_uint2(pack_bf16(x[r].x - hv.x, x[r].y - hv.y), pack_bf16(x[r].z - hv.z, x[r].w - hv.w));
     }
     if (COLS) { tile[row][c4 * 4] = x[r].x; tile[row][c4 * 4 + 1] = x[r].y; tile[row][c4 * 4 + 2] = x[r].z; tile[row][c4 * 4 + 3] = x[r].w; }
   }
@@ -562,53 +589,55 @@ __global__ void __launch_bounds__(256) attn_split_kernel(const float* __restrict
       const float4 hv = make_float4(tf32_round(v.x), tf32_round(v.y), tf32_round(v.z), tf32_round(v.w));
       const long o = ((long)z * 64 + d) * T + t0 + c4 * 4;
       *reinterpret_cast<float4*>(chi + o) = hv;
-      *reinterpret_cast<float4*>(clo + o) = make_float4(v.x - hv.x, v.y - hv.y, v.z - hv.z, v.w - hv.w);
+      *reinterpret_cast<uint2*>(cxb + o) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+      *reinterpret_cast<uint2*>(clo + o) = make_uint2(pack_bf16(v.x - hv.x, v.y - hv.y), pack_bf16(v.z - hv.z, v.w - hv.w));
     }
   }
 }
-// slot / slot + 1 receive the row planes, cslot / cslot + 1 the transposed ones (a negative slot = not wanted)
+// slot / slot + 1 receive the row planes (hi | the two bf16 planes), cslot / cslot + 1 the transposed ones (a negative
+// slot = not wanted)
 inline int attn_tc_planes(Ctx* ctx, const float* X, int slot, int cslot, int B, int T, int D, int H, TcPlanes* rows, TcPlanes* cols) {
   const int Z = B * H; const size_t n = (size_t)Z * T * ATC_HD;
-  float *rh = nullptr, *rl = nullptr, *ch = nullptr, *cl = nullptr;
-  if (slot >= 0) { GN_TRY(attn_tc_buf(ctx, slot, n, &rh)); GN_TRY(attn_tc_buf(ctx, slot + 1, n, &rl)); *rows = TcPlanes{rh, rl, T, ATC_HD, ATC_HD, Z}; }
-  if (cslot >= 0) { GN_TRY(attn_tc_buf(ctx, cslot, n, &ch)); GN_TRY(attn_tc_buf(ctx, cslot + 1, n, &cl)); *cols = TcPlanes{ch, cl, ATC_HD, T, T, Z}; }
+  TcPlanes r{nullptr, nullptr, T, ATC_HD, ATC_HD, Z}, c{nullptr, nullptr, ATC_HD, T, T, Z};
+  if (slot >= 0) { GN_TRY(attn_tc_buf(ctx, slot, n, &r.hi)); GN_TRY(attn_tc_buf(ctx, slot + 1, n, &r.lo)); *rows = r; }
+  if (cslot >= 0) { GN_TRY(attn_tc_buf(ctx, cslot, n, &c.hi)); GN_TRY(attn_tc_buf(ctx, cslot + 1, n, &c.lo)); *cols = c; }
   const dim3 grid(T / 64, Z);
-  if (slot >= 0 && cslot >= 0) GN_LAUNCH(ctx, (attn_split_kernel<true, true>), grid, 256, 0, X, rh, rl, ch, cl, T, D, H);
-  else if (slot >= 0) GN_LAUNCH(ctx, (attn_split_kernel<true, false>), grid, 256, 0, X, rh, rl, ch, cl, T, D, H);
-  else GN_LAUNCH(ctx, (attn_split_kernel<false, true>), grid, 256, 0, X, rh, rl, ch, cl, T, D, H);
+  __nv_bfloat16* nb = nullptr;
+  if (slot >= 0 && cslot >= 0) GN_LAUNCH(ctx, (attn_split_kernel<true, true>), grid, 256, 0, X, r.hi, r.xb(), r.lob(), c.hi, c.xb(), c.lob(), T, D, H);
+  else if (slot >= 0) GN_LAUNCH(ctx, (attn_split_kernel<true, false>), grid, 256, 0, X, r.hi, r.xb(), r.lob(), (float*)nullptr, nb, nb, T, D, H);
+  else GN_LAUNCH(ctx, (attn_split_kernel<false, true>), grid, 256, 0, X, (float*)nullptr, nb, nb, c.hi, c.xb(), c.lob(), T, D, H);
   return check_launch("attn_split");
+}
+// the three tensor maps of one operand: hi (fp32, 32 columns per copy), bf16 copy and bf16 lo (64 columns per copy)
+inline int attn_tc_maps(Ctx* ctx, CUtensorMap* m, const TcPlanes& p, int box_rows) {
+  GN_TRY(tc_make_map(ctx, &m[0], p, p.hi, box_rows));
+  GN_TRY(tc_make_map_bf16(ctx, &m[1], p, p.xb(), box_rows, 64));
+  return tc_make_map_bf16(ctx, &m[2], p, p.lob(), box_rows, 64);
 }
 inline int attn_tc_fwd(Ctx* ctx, const float* Q, const float* K, const float* V, float* O, float* M, float* L, int B, int T, int D, int H, int causal) {
   TcPlanes pq, pk, pv;
   GN_TRY(attn_tc_planes(ctx, Q, 0, -1, B, T, D, H, &pq, nullptr));
   GN_TRY(attn_tc_planes(ctx, K, 2, -1, B, T, D, H, &pk, nullptr));
   GN_TRY(attn_tc_planes(ctx, V, -1, 4, B, T, D, H, nullptr, &pv));
-  CUtensorMap mQh, mQl, mKh, mKl, mVh, mVl;
-  GN_TRY(tc_make_map(ctx, &mQh, pq, pq.hi, ATC_BQ)); GN_TRY(tc_make_map(ctx, &mQl, pq, pq.lo, ATC_BQ));
-  GN_TRY(tc_make_map(ctx, &mKh, pk, pk.hi, ATC_BK)); GN_TRY(tc_make_map(ctx, &mKl, pk, pk.lo, ATC_BK));
-  GN_TRY(tc_make_map(ctx, &mVh, pv, pv.hi, ATC_HD)); GN_TRY(tc_make_map(ctx, &mVl, pv, pv.lo, ATC_HD));
+  AttnMaps<9> maps;
+  GN_TRY(attn_tc_maps(ctx, &maps.m[0], pq, ATC_BQ)); GN_TRY(attn_tc_maps(ctx, &maps.m[3], pk, ATC_BK)); GN_TRY(attn_tc_maps(ctx, &maps.m[6], pv, ATC_HD));
   GN_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_FWD_SMEM));
   const int ntq = T / ATC_BQ, ntiles = ntq * B * H;
   const int grid = std::min(ntiles, std::max(1, ctx->sm_count / ntq) * ntq);      // a multiple of the query blocks per problem
-  GN_LAUNCH(ctx, attn_tc_fwd_kernel, grid, ATC_THREADS, ATC_FWD_SMEM, mQh, mQl, mKh, mKl, mVh, mVl, O, M, L, T, D, H, causal,
-            1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status);
+  GN_LAUNCH(ctx, attn_tc_fwd_kernel, grid, ATC_THREADS, ATC_FWD_SMEM, maps, O, M, L, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status);
   return check_launch("attn_tc_fwd");
 }
 
 template <int MODE>
 inline int attn_tc_bwd_launch(Ctx* ctx, const TcPlanes& r1, const TcPlanes& r2, const TcPlanes& c1, const TcPlanes& c2, const TcPlanes& c3,
                               const float* M, const float* L, const float* Dv, float* out, int B, int T, int D, int H, int causal) {
-  CUtensorMap m[10];
-  GN_TRY(tc_make_map(ctx, &m[0], r1, r1.hi, 128)); GN_TRY(tc_make_map(ctx, &m[1], r1, r1.lo, 128));
-  GN_TRY(tc_make_map(ctx, &m[2], r2, r2.hi, 128)); GN_TRY(tc_make_map(ctx, &m[3], r2, r2.lo, 128));
-  GN_TRY(tc_make_map(ctx, &m[4], c1, c1.hi, 64)); GN_TRY(tc_make_map(ctx, &m[5], c1, c1.lo, 64));
-  GN_TRY(tc_make_map(ctx, &m[6], c2, c2.hi, 64)); GN_TRY(tc_make_map(ctx, &m[7], c2, c2.lo, 64));
-  GN_TRY(tc_make_map(ctx, &m[8], c3, c3.hi, ATC_HD)); GN_TRY(tc_make_map(ctx, &m[9], c3, c3.lo, ATC_HD));
+  AttnMaps<15> maps;
+  GN_TRY(attn_tc_maps(ctx, &maps.m[0], r1, 128)); GN_TRY(attn_tc_maps(ctx, &maps.m[3], r2, 128));
+  GN_TRY(attn_tc_maps(ctx, &maps.m[6], c1, 64)); GN_TRY(attn_tc_maps(ctx, &maps.m[9], c2, 64)); GN_TRY(attn_tc_maps(ctx, &maps.m[12], c3, ATC_HD));
   GN_CUDA(cudaFuncSetAttribute(attn_tc_bwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, AtbCfg<MODE>::SMEM));
   const int ntr = T / 128, ntiles = ntr * B * H;
   const int grid = std::min(ntiles, std::max(1, ctx->sm_count / ntr) * ntr);      // a multiple of the row tiles per problem
-  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, grid, ATB_THREADS, AtbCfg<MODE>::SMEM, m[0], m[1], m[2], m[3], m[4], m[5], m[6], m[7], m[8], m[9],
-            M, L, Dv, out, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status);
+  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, grid, ATB_THREADS, AtbCfg<MODE>::SMEM, maps, M, L, Dv, out, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status);
   return check_launch("attn_tc_bwd");
 }
 // dQ, dK, dV from Q, K, V, O, dO and the forward's row statistics; Dv receives the row products dO . O

@@ -400,14 +400,16 @@ inline int tc_make_map(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const floa
   if (r != CUDA_SUCCESS) return fail(GN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows %d K %d ld %d batch %d)", (int)r, p.rows, p.K, p.ldp, p.nbatch);
   return GN_OK;
 }
-// bf16 plane, 32 columns (64 bytes, 64-byte swizzle) x box_rows per copy
-inline int tc_make_map_bf16(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const __nv_bfloat16* base, int box_rows) {
+// bf16 plane, box_cols columns x box_rows per copy: 32 columns = 64 bytes with the 64-byte swizzle (contraction engine),
+// 64 columns = 128 bytes with the 128-byte swizzle (attention tiles)
+inline int tc_make_map_bf16(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const __nv_bfloat16* base, int box_rows, int box_cols = TC_BK) {
   cuuint64_t dims[3] = {(cuuint64_t)p.K, (cuuint64_t)p.rows, (cuuint64_t)p.nbatch};
   cuuint64_t strides[2] = {(cuuint64_t)p.ldp * 2, (cuuint64_t)p.rows * p.ldp * 2};
-  cuuint32_t box[3] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = ((PFN_encodeTiled)ctx->encode_tiled)(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)(base + p.koff), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                                    CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                                                    box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(GN_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed with %d (rows %d K %d ld %d batch %d)", (int)r, p.rows, p.K, p.ldp, p.nbatch);
   return GN_OK;
 }

@@ -136,6 +136,26 @@ class Sequential:
         a = _f32(state)
         _lib.check(_lib.load().gn_model_set_state(self.handle, _p(a), a.size))
 
+    # -- checkpoints ------------------------------------------------------------
+    def Checkpoint(self):
+        """Everything a resumed run needs: parameters (Network.Save, net.go:863-1075), the optimiser's moments and
+        step counter (which the reference does not checkpoint, opt.go:312-322) and the non-parameter layer state."""
+        m, v, t = self.AdamState()
+        return {"params": self.Params(), "adam_m": m, "adam_v": v, "adam_timestep": np.int64(t), "state": self.State()}
+
+    def Restore(self, ckpt):
+        self.SetParams(ckpt["params"])
+        self.SetAdamState(ckpt["adam_m"], ckpt["adam_v"], int(ckpt["adam_timestep"]))
+        if np.asarray(ckpt["state"]).size:
+            self.SetState(ckpt["state"])
+
+    def Save(self, path):
+        np.savez(path, **self.Checkpoint())
+
+    def Load(self, path):
+        with np.load(path) as f:
+            self.Restore({k: f[k] for k in f.files})
+
     # -- training ---------------------------------------------------------------
     def _push_opt(self):
         o = self.opt   # re-read every step: schedulers mutate LearningRate on the host (opt/scheduler.go)

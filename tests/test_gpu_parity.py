@@ -205,3 +205,46 @@ def test_lstm_scan_variants_in_subprocess(mode):
     r = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_parity.py"), "-q", "-x", "-m", "gpu", "-k", "lstm-5 or lstm-6 or lstm-7"],
                        env=env, cwd=root, capture_output=True, text=True)
     assert r.returncode == 0 and " passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.parametrize("name,kw,batch", [("cnn_bn", {}, 32), ("transformer_small", dict(vocab=512, dim=64, seq_len=16, heads=4, ff_dim=128, n_blocks=2), 8)])
+def test_resume_from_checkpoint_is_bit_exact(device, tmp_path, name, kw, batch):
+    """Parameters + Adam moments + step counter + running statistics, saved after two steps and loaded into a fresh
+    model, continue exactly like the uninterrupted run (the reference loses the Adam state on Save, opt.go:312-322)."""
+    from goneuron_b200.sequential import Adam, Sequential
+    layers, loss_kind, params, x, y, lr = configs.make_case(name, batch=batch, **kw)
+    a = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+    a.SetParams(params)
+    for _ in range(2):
+        a.TrainBatch(x, y)
+    a.Save(tmp_path / "ckpt.npz")
+    b = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+    b.Load(tmp_path / "ckpt.npz")
+    la, lb = a.TrainBatch(x, y), b.TrainBatch(x, y)
+    assert la == lb
+    assert np.array_equal(a.Params(), b.Params()) and np.array_equal(a.State(), b.State())
+    ma, va, ta = a.AdamState(); mb, vb, tb = b.AdamState()
+    assert ta == tb == 3 and np.array_equal(ma, mb) and np.array_equal(va, vb)
+    a.Close(); b.Close()
+
+
+def test_learning_rate_schedule_is_followed(device, oracle):
+    """Schedulers mutate Adam.LearningRate on the host between steps (opt/scheduler.go:19-149); the library re-reads it
+    at every step.  Three steps with a decaying rate against the CPU checker stepping with the same rates."""
+    from goneuron_b200.sequential import Adam, Sequential
+    layers, loss_kind, params, x, y, lr = configs.make_case("mlp", batch=16)
+    ref = oracle.OracleState(layers, loss_kind, params, lr=lr)
+    opt = Adam(lr)
+    model = Sequential(layers, device).Compile(opt, loss_kind)
+    model.SetParams(params)
+    for step in range(3):
+        opt.LearningRate = ref.lr = lr * (0.5 ** step)
+        l_gpu, l_ref = model.TrainBatch(x, y), ref.train_batch(x, y, precision=64)
+        assert abs(l_gpu - l_ref) <= TOL * max(1.0, abs(l_ref))
+    d = np.abs(model.Params() - ref.params).max()
+    assert d <= 3 * lr * 1e-2, d      # three Adam steps move a weight by at most about 3 lr; agreement to a percent of that
+    fixed = oracle.OracleState(layers, loss_kind, params, lr=lr)
+    for _ in range(3):
+        fixed.train_batch(x, y, precision=64)
+    assert np.abs(model.Params() - fixed.params).max() > 10 * d      # and the schedule really changed the trajectory
+    model.Close()
