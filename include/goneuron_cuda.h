@@ -198,7 +198,7 @@ int gn_model_set_profiling(gn_model* m, int level);
  *      restatement; all pointers are HOST memory, copied in and out) --------- */
 
 /* C[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) ; row-major, fp32 in/out.
- * engine: 0 = SIMT fp32, 1 = tcgen05 3xTF32.  (Dense forward, layer.go:406 /
+ * engine: 0 = SIMT fp32, 1 = tcgen05 split-operand (TF32 + 2 x BF16, fp32-level accuracy).  (Dense forward, layer.go:406 /
  * matmul_optimized.go:18-152 at batch level.) */
 int gn_op_gemm_nt(gn_ctx* ctx, int engine, int M, int N, int K,
                   const float* A, const float* B, const float* bias, float* C);

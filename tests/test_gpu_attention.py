@@ -10,7 +10,7 @@ from tests.parity import norm_err
 
 pytestmark = pytest.mark.gpu
 
-TOL = 1e-4   # normalised max error; both engines run 3xTF32 and land near 1e-6
+TOL = 1e-4   # normalised max error; both engines run split-operand products and land near 1e-6
 
 
 @pytest.fixture(scope="module")

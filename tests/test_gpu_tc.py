@@ -1,4 +1,4 @@
-"""The tcgen05 3xTF32 contraction engine against float64 numpy and against the exact-fp32 SIMT engine,
+"""The tcgen05 split-operand (TF32 + 2 x BF16) contraction engine against float64 numpy and against the exact-fp32 SIMT engine,
 through the C ABI: C = A B^T + bias, ragged and tile-aligned shapes."""
 import ctypes as C
 
