@@ -156,6 +156,26 @@ __global__ void attn_rowdot_kernel(const float* __restrict__ dO, const float* __
   if (lane == 0) Dv[(b * H + h) * T + i] = s;
 }
 
+// The same for head size 64 and D = 64 H (rows of all heads are then consecutive 64-float segments): 16 threads per row,
+// 16-byte loads, two rows in flight per thread.
+__global__ void __launch_bounds__(256) attn_rowdot64_kernel(const float* __restrict__ dO, const float* __restrict__ O, float* __restrict__ Dv, int T, int H, long rows) {
+  const long gid = (long)blockIdx.x * 256 + threadIdx.x, half = (long)gridDim.x * 16;      // rows per pass of the grid
+  const int l16 = threadIdx.x & 15;
+  for (long w = gid >> 4; w < rows; w += 2 * half) {
+    const long w2 = w + half;
+    const float4 a = *reinterpret_cast<const float4*>(dO + w * 64 + l16 * 4), b = *reinterpret_cast<const float4*>(O + w * 64 + l16 * 4);
+    float4 c = make_float4(0.f, 0.f, 0.f, 0.f), d = c;
+    if (w2 < rows) { c = *reinterpret_cast<const float4*>(dO + w2 * 64 + l16 * 4); d = *reinterpret_cast<const float4*>(O + w2 * 64 + l16 * 4); }
+    float s = (a.x * b.x + a.y * b.y) + (a.z * b.z + a.w * b.w), s2 = (c.x * d.x + c.y * d.y) + (c.z * d.z + c.w * d.w);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) { s += __shfl_xor_sync(0xffffffffu, s, o); s2 += __shfl_xor_sync(0xffffffffu, s2, o); }
+    if (l16 == 0) {
+      { const int h = (int)(w % H); const long tok = w / H; Dv[((tok / T) * H + h) * T + tok % T] = s; }
+      if (w2 < rows) { const int h = (int)(w2 % H); const long tok = w2 / H; Dv[((tok / T) * H + h) * T + tok % T] = s2; }
+    }
+  }
+}
+
 
 // ---------------------------------------------------------------- backward: dQ
 // One CTA = 64 query rows; for every key block at or below the diagonal: S = Q K^T, P = exp(S/sqrt(hd) - m) / l,

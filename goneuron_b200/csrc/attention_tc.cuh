@@ -15,9 +15,9 @@
 //               O += P_j V_j with P read from TMEM as the A operand and Vt_j from shared memory.
 //   warps 2-9 : two threads per query row (TMEM lane = row, 32 of the 64 columns each): tcgen05.ld of S_j, running
 //               maximum (exchanged through shared memory) and sum, p = exp(s - m), hi written over S_j in place and
-//               bf16(p), bf16(p - hi) packed two per column into a second buffer (tcgen05.st); when a row maximum moved, the output accumulator is rescaled
-//               in TMEM after the previous P V has completed.  One warp per scheduler could not keep up with the
-//               tensor pipe (measured: 25 % tensor activity); two do.
+//               bf16(p), bf16(p - hi) packed two per column into a second buffer (tcgen05.st); when a row maximum
+//               moved, the output accumulator is rescaled in TMEM after the previous P V has completed.  One warp per
+//               scheduler could not keep up with the tensor pipe (measured: 25 % tensor activity); two do.
 // The issue order S_0, S_1, PV_0, S_2, PV_1, ... keeps the tensor pipe busy with S_{j+1} (and PV_{j-1}) while the
 // softmax of block j runs.  Every wait is bounded; a wait that gives up sets the status word.
 #pragma once
@@ -27,11 +27,11 @@
 namespace gn {
 
 constexpr int ATC_BQ = 128, ATC_BK = 64, ATC_HD = 64, ATC_THREADS = 320;
-constexpr int ATC_Q_BYTES = 4 * ATC_BQ * 128;   // hi, lo x two chunks of 32 floats: 64 KB
+constexpr int ATC_Q_BYTES = 4 * ATC_BQ * 128;   // hi (two chunks of 32 floats) + bf16 copy + bf16 lo: 64 KB
 constexpr int ATC_K_BYTES = 4 * ATC_BK * 128;   // 32 KB
 constexpr int ATC_V_BYTES = 4 * ATC_HD * 128;   // 32 KB
 constexpr int ATC_FWD_SMEM = ATC_Q_BYTES + 2 * (ATC_K_BYTES + ATC_V_BYTES) + 1024 + 256 + 2 * 256 * 4;
-// TMEM columns: S / P_hi buffers [0,128), P_lo buffers [128,256), two output accumulators [256,384)
+// TMEM columns: S / P_hi buffers [0,128), packed bf16 P | P_lo buffers [128,256), two output accumulators [256,384)
 constexpr uint32_t ATC_COL_S = 0, ATC_COL_PLO = 128, ATC_COL_O = 256, ATC_TMEM_COLS = 512;
 
 __device__ __forceinline__ void tc_mma_tf32_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -644,7 +644,9 @@ inline int attn_tc_bwd_launch(Ctx* ctx, const TcPlanes& r1, const TcPlanes& r2, 
 inline int attn_tc_bwd(Ctx* ctx, const float* Q, const float* K, const float* V, const float* O, const float* dO, const float* M, const float* L, float* Dv,
                        float* dQ, float* dK, float* dV, int B, int T, int D, int H, int causal) {
   const long rows = (long)B * T * H;
-  GN_LAUNCH(ctx, attn_rowdot_kernel, cdiv(rows, 8), 256, 0, dO, O, Dv, T, D, H, ATC_HD, rows);
+  if (D == H * ATC_HD && ((reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(O)) & 15) == 0)
+    GN_LAUNCH(ctx, attn_rowdot64_kernel, (unsigned)std::min<long>(cdiv(rows, 32), (long)ctx->sm_count * 16), 256, 0, dO, O, Dv, T, H, rows);
+  else GN_LAUNCH(ctx, attn_rowdot_kernel, cdiv(rows, 8), 256, 0, dO, O, Dv, T, D, H, ATC_HD, rows);
   TcPlanes qp, kp, vp, gp, qt, kt, gt;
   GN_TRY(attn_tc_planes(ctx, Q, 0, 10, B, T, D, H, &qp, &qt));
   GN_TRY(attn_tc_planes(ctx, K, 2, 12, B, T, D, H, &kp, &kt));

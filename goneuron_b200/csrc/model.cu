@@ -386,7 +386,9 @@ static int layernorm_backward(gn_model* m, const float* g, const float* x, const
 //   gb = sum over all tokens of dz ; gW = Delta^T * X_last with Delta[s] = sum_t dz[s,t], X_last[s] = x[s,T-1]
 static int inner_dense_param_grads(gn_model* m, const float* dz, int B, int T, int out, const float* x, int in, float* gW, float* gb) {
   Ctx* ctx = &m->ctx->c; float* delta; GN_TRY(ensure(m, S_DELTA, (size_t)B * out, &delta));
-  GN_LAUNCH(ctx, token_sum_kernel, dim3(cdiv(out, 128), B), dim3(128, 4), 0, dz, T, out, delta);
+  if (out % 4 == 0 && ((reinterpret_cast<uintptr_t>(dz) | reinterpret_cast<uintptr_t>(delta)) & 15) == 0)
+    GN_LAUNCH(ctx, token_sum_vec_kernel, dim3(cdiv(out, 128), B), dim3(32, 8), 0, dz, T, out, delta);
+  else GN_LAUNCH(ctx, token_sum_kernel, dim3(cdiv(out, 128), B), dim3(128, 4), 0, dz, T, out, delta);
   GN_TRY(colsum(m, delta, out, B, out, gb, false));
   return gemm_tn(ctx, B, out, in, delta, out, x + (long)(T - 1) * in, (long)T * in, gW);
 }

@@ -125,6 +125,31 @@ __global__ void token_sum_kernel(const float* __restrict__ in, int T, int C, flo
   if (grp == 0 && c < C) out[(long)blockIdx.y * C + c] = (part[0][threadIdx.x] + part[1][threadIdx.x]) + (part[2][threadIdx.x] + part[3][threadIdx.x]);
 }
 
+// The same sum with 16-byte loads: block = 32 column groups of 4 x 8 groups of tokens (C a multiple of 4, aligned rows).
+__global__ void __launch_bounds__(256) token_sum_vec_kernel(const float* __restrict__ in, int T, int C, float* __restrict__ out) {
+  __shared__ float4 part[8][32];
+  const int c = (blockIdx.x * 32 + threadIdx.x) * 4, grp = threadIdx.y;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c < C) {
+    const float* p = in + (long)blockIdx.y * T * C + c;
+    int t = grp;
+    for (; t + 24 < T; t += 32) {
+      const float4 a0 = *reinterpret_cast<const float4*>(p + (long)t * C), a1 = *reinterpret_cast<const float4*>(p + (long)(t + 8) * C);
+      const float4 a2 = *reinterpret_cast<const float4*>(p + (long)(t + 16) * C), a3 = *reinterpret_cast<const float4*>(p + (long)(t + 24) * C);
+      s.x += (a0.x + a1.x) + (a2.x + a3.x); s.y += (a0.y + a1.y) + (a2.y + a3.y); s.z += (a0.z + a1.z) + (a2.z + a3.z); s.w += (a0.w + a1.w) + (a2.w + a3.w);
+    }
+    for (; t < T; t += 8) { const float4 a = *reinterpret_cast<const float4*>(p + (long)t * C); s.x += a.x; s.y += a.y; s.z += a.z; s.w += a.w; }
+  }
+  part[grp][threadIdx.x] = s;
+  __syncthreads();
+  if (grp == 0 && c < C) {
+    float4 r = part[0][threadIdx.x];
+#pragma unroll
+    for (int g = 1; g < 8; g++) { const float4 q = part[g][threadIdx.x]; r.x += q.x; r.y += q.y; r.z += q.z; r.w += q.w; }
+    *reinterpret_cast<float4*>(out + (long)blockIdx.y * C + c) = r;
+  }
+}
+
 // ---------------------------------------------------------------- LayerNorm
 // One warp per row.  reference: layernorm.go:268-301
 __global__ void layernorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
