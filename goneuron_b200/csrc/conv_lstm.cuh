@@ -171,6 +171,45 @@ __global__ void maxpool_bwd_kernel(const float* __restrict__ g, const int* __res
   }
 }
 
+// Average pooling: mean over the taps inside the input (padded taps are not counted; a window with no valid tap
+// gives 0).  reference: avgpool2d.go:172-228
+__global__ void avgpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, PoolShape c) {
+  long total = (long)c.B * c.C * c.oH * c.oW;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int ow = (int)(i % c.oW); long r = i / c.oW; int oh = (int)(r % c.oH); r /= c.oH;      // r = b * C + ch
+    const float* xp = x + r * c.H * c.W;
+    float sum = 0.f; int cnt = 0;
+    for (int kh = 0; kh < c.k; kh++) for (int kw = 0; kw < c.k; kw++) {
+      int ih = oh * c.s + kh - c.p, iw = ow * c.s + kw - c.p;
+      if (ih >= 0 && ih < c.H && iw >= 0 && iw < c.W) { sum += xp[ih * c.W + iw]; cnt++; }
+    }
+    y[i] = cnt > 0 ? sum * (1.f / (float)cnt) : 0.f;
+  }
+}
+// Backward in gather form (one thread per input element, no atomics): dx = sum over the windows that contain the element
+// of g / count(window), windows visited in the reference's (oh, ow) order.  reference: avgpool2d.go:441-468
+__global__ void avgpool_bwd_kernel(const float* __restrict__ g, float* __restrict__ dx, PoolShape c) {
+  long total = (long)c.B * c.C * c.H * c.W;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int iw = (int)(i % c.W); long r = i / c.W; int ih = (int)(r % c.H); r /= c.H;          // r = b * C + ch
+    const float* gp = g + r * c.oH * c.oW;
+    float acc = 0.f;
+    for (int oh = 0; oh < c.oH; oh++) {
+      int kh = ih - oh * c.s + c.p; if (kh < 0 || kh >= c.k) continue;
+      for (int ow = 0; ow < c.oW; ow++) {
+        int kw = iw - ow * c.s + c.p; if (kw < 0 || kw >= c.k) continue;
+        int cnt = 0;
+        for (int a = 0; a < c.k; a++) for (int b = 0; b < c.k; b++) {
+          int h2 = oh * c.s + a - c.p, w2 = ow * c.s + b - c.p;
+          if (h2 >= 0 && h2 < c.H && w2 >= 0 && w2 < c.W) cnt++;
+        }
+        acc += gp[oh * c.oW + ow] * (1.f / (float)cnt);
+      }
+    }
+    dx[i] = acc;
+  }
+}
+
 // ---------------------------------------------------------------- LSTM
 // Forward recurrence of one sample per block, thread i = hidden unit i.
 // reference: lstm.go:276-407.  The reference's gate helpers (lstm.go:1065-1101) run over the first H of the

@@ -123,8 +123,9 @@ static int plan_layers(gn_model* m, const gn_layer_desc* layers, int n) {
         int oh = (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, ow = (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1;
         l.in_size = d.in_size * d.in_h * d.in_w; l.out_size = d.out_size * oh * ow;
         l.p_cnt = (int64_t)d.out_size * d.in_size * d.kernel * d.kernel + d.out_size; break; }
-      case GN_LAYER_MAXPOOL2D: {
-        if (d.in_size <= 0 || d.kernel <= 0 || d.stride <= 0 || d.in_h <= 0 || d.in_w <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad MaxPool2D descriptor", i);
+      case GN_LAYER_MAXPOOL2D:
+      case GN_LAYER_AVGPOOL2D: {
+        if (d.in_size <= 0 || d.kernel <= 0 || d.stride <= 0 || d.padding < 0 || d.in_h <= 0 || d.in_w <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad pooling descriptor", i);
         int oh = (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, ow = (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1;
         l.in_size = d.in_size * d.in_h * d.in_w; l.out_size = d.in_size * oh * ow; break; }
       case GN_LAYER_FLATTEN:
@@ -181,6 +182,7 @@ static int alloc_activations(gn_model* m, int cap) {
         break;
       case GN_LAYER_CONV2D: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.z.alloc(c * l.out_size)); break;
       case GN_LAYER_MAXPOOL2D: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.idx.alloc(c * l.out_size)); break;
+      case GN_LAYER_AVGPOOL2D: GN_TRY(l.out.alloc(c * l.out_size)); break;
       case GN_LAYER_FLATTEN: break;
       case GN_LAYER_LSTM_UNROLLED: {
         size_t th = c * d.seq_len * d.out_size;
@@ -286,6 +288,12 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
                     (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
         long n = (long)B * l.out_size;
         GN_LAUNCH(ctx, maxpool_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, l.out.p, (int*)l.idx.p, c);
+        cur = l.out.p; break; }
+      case GN_LAYER_AVGPOOL2D: {
+        PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
+                    (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
+        long n = (long)B * l.out_size;
+        GN_LAUNCH(ctx, avgpool_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, l.out.p, c);
         cur = l.out.p; break; }
       case GN_LAYER_FLATTEN: break;
       case GN_LAYER_LSTM_UNROLLED: {
@@ -568,6 +576,11 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         long n = (long)B * l.out_size;
         GN_LAUNCH(ctx, maxpool_bwd_kernel, ew_grid(ctx, n), 256, 0, g, (const int*)l.idx.p, dx, c);
         g = dx; flip ^= 1; break; }
+      case GN_LAYER_AVGPOOL2D: {
+        PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
+                    (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
+        if (need_dx) { long n = (long)B * l.in_size; GN_LAUNCH(ctx, avgpool_bwd_kernel, ew_grid(ctx, n), 256, 0, g, dx, c); g = dx; flip ^= 1; }
+        break; }
       case GN_LAYER_FLATTEN: break;
       case GN_LAYER_LSTM_UNROLLED:
         GN_TRY(lstm_backward(m, l, li, B, xin, g, global_batch, first_sample, dx)); if (need_dx) { g = dx; flip ^= 1; } break;

@@ -52,7 +52,8 @@ typedef enum gn_layer_kind {
   GN_LAYER_TRANSFORMER_BLOCK = 8, /* NewTransformerBlock(dim,heads,T,ff,causal) transformer.go:859-1279 */
   GN_LAYER_CLS_POOLING = 9,    /* layer.NewCLSPooling(T,dim)            internal/layer/transformer.go:1647-1777 */
   GN_LAYER_LAYERNORM = 10,     /* layer.NewLayerNorm(dim,eps,true) applied row-wise  layernorm.go:193-441 */
-  GN_LAYER_BATCHNORM2D = 11    /* layer.NewBatchNorm2D(C,eps,momentum,true) + SetInputDimensions  batchnorm2d.go:67-665 */
+  GN_LAYER_BATCHNORM2D = 11,   /* layer.NewBatchNorm2D(C,eps,momentum,true) + SetInputDimensions  batchnorm2d.go:67-665 */
+  GN_LAYER_AVGPOOL2D = 12      /* layer.NewAvgPool2D(inC,k,s,p) + input dimensions   internal/layer/avgpool2d.go:43-228, 401-468 */
 } gn_layer_kind;
 
 /* Activations (reference: internal/activations/activations.go:22-236,342-352). */
@@ -74,7 +75,7 @@ typedef struct gn_layer_desc {
   int32_t activation;  /* gn_activation (Dense, Conv2D) */
   int32_t in_size;     /* Dense in; Conv2D/MaxPool in-channels; LSTM input size; Embedding vocab */
   int32_t out_size;    /* Dense out; Conv2D out-channels; LSTM hidden size; Embedding dim */
-  int32_t kernel;      /* Conv2D / MaxPool2D window */
+  int32_t kernel;      /* Conv2D / MaxPool2D / AvgPool2D window */
   int32_t stride;
   int32_t padding;
   int32_t in_h;        /* Conv2D / MaxPool2D input height (SetInputDimensions, conv2d.go:686-691) */

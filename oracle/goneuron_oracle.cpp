@@ -301,6 +301,46 @@ template <class R> struct MaxPool2D : Layer<R> {
   }
 };
 
+// reference: internal/layer/avgpool2d.go:172-228 (mean over the taps that fall inside the input: padded taps are not
+// counted; a window without any valid tap gives 0), :401-468 (backward: grad / count to every valid tap, accumulated).
+template <class R> struct AvgPool2D : Layer<R> {
+  int C, k, s, p, H, Wd, oH, oW;
+  std::vector<R> output, gradIn; std::vector<int> count;
+  AvgPool2D(int C_, int k_, int s_, int p_, int H_, int W_) : C(C_), k(k_), s(s_), p(p_), H(H_), Wd(W_) {
+    oH = (H + 2 * p - k) / s + 1; oW = (Wd + 2 * p - k) / s + 1;
+    output.resize((size_t)C * oH * oW); count.resize((size_t)oH * oW); gradIn.resize((size_t)C * H * Wd);
+  }
+  int in_size() const override { return C * H * Wd; }
+  int out_size() const override { return C * oH * oW; }
+  bool valid(int oh, int ow, int kh, int kw, int& ih, int& iw) const { ih = oh * s + kh - p; iw = ow * s + kw - p; return ih >= 0 && ih < H && iw >= 0 && iw < Wd; }
+  const R* forward(const R* x) override {
+    for (int oh = 0; oh < oH; oh++) for (int ow = 0; ow < oW; ow++) {
+      int pos = oh * oW + ow, cnt = 0, ih, iw;
+      for (int kh = 0; kh < k; kh++) for (int kw = 0; kw < k; kw++) if (valid(oh, ow, kh, kw, ih, iw)) cnt++;
+      count[pos] = cnt;
+      const R inv = cnt > 0 ? R(1) / R(cnt) : R(0);
+      for (int c = 0; c < C; c++) {
+        R sum = 0;
+        for (int kh = 0; kh < k; kh++) for (int kw = 0; kw < k; kw++) if (valid(oh, ow, kh, kw, ih, iw)) sum += x[((size_t)c * H + ih) * Wd + iw];
+        output[(size_t)c * oH * oW + pos] = cnt > 0 ? sum * inv : R(0);
+      }
+    }
+    return output.data();
+  }
+  const R* backward(R* grad) override {
+    std::fill(gradIn.begin(), gradIn.end(), R(0));
+    for (int oh = 0; oh < oH; oh++) for (int ow = 0; ow < oW; ow++) {
+      int pos = oh * oW + ow, ih, iw; if (count[pos] <= 0) continue;
+      const R per = R(1) / R(count[pos]);
+      for (int c = 0; c < C; c++) {
+        const R gv = grad[(size_t)c * oH * oW + pos] * per;
+        for (int kh = 0; kh < k; kh++) for (int kw = 0; kw < k; kw++) if (valid(oh, ow, kh, kw, ih, iw)) gradIn[((size_t)c * H + ih) * Wd + iw] += gv;
+      }
+    }
+    return gradIn.data();
+  }
+};
+
 // reference: internal/layer/reshape.go:64-96 (copy forward, identity backward)
 template <class R> struct Flatten : Layer<R> {
   int n; std::vector<R> buf;
@@ -691,6 +731,7 @@ template <class R> struct Net {
         case GN_LAYER_DENSE: p.reset(new Dense<R>(l.in_size, l.out_size, l.activation)); break;
         case GN_LAYER_CONV2D: p.reset(new Conv2D<R>(l.in_size, l.out_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w, l.activation)); break;
         case GN_LAYER_MAXPOOL2D: p.reset(new MaxPool2D<R>(l.in_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w)); break;
+        case GN_LAYER_AVGPOOL2D: p.reset(new AvgPool2D<R>(l.in_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w)); break;
         case GN_LAYER_FLATTEN: if (cur < 0) { g_err = "Flatten cannot be first"; return false; } p.reset(new Flatten<R>(cur)); break;
         case GN_LAYER_LSTM_UNROLLED: p.reset(new LSTMUnrolled<R>(l.in_size, l.out_size, l.seq_len, l.return_seq != 0)); net.has_lstm = true; break;
         case GN_LAYER_EMBEDDING: {

@@ -41,6 +41,8 @@ CASES = [
     ("mlp_ln", dict(in_size=10, hidden=2200, norm=1100, classes=3), 5, 1),                                  # rows wider than the fused kernel holds
     ("mlp_ln", dict(in_size=12, hidden=2048, norm=1024, classes=3), 9, 1),                                   # row-in-registers LayerNorm kernels, 8 x 128 columns
     ("mlp_ln", dict(in_size=12, hidden=1024, norm=512, classes=3), 9, 1),                                   # ... 4 x 128 columns
+    ("cnn_avg", {}, 16, 1),                                                                                 # AvgPool2D, overlapping padded windows
+    ("cnn_avg", dict(hw=9, c0=1, c1=3, classes=2), 5, 1),
 ]
 
 

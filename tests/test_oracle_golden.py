@@ -109,3 +109,22 @@ def test_conv2d_simple(oracle):
     st = oracle.OracleState(layers, D.MSE, params)
     out = st.forward_batch(np.array(f["input"], np.float32).reshape(1, 9), precision=32)
     np.testing.assert_allclose(out.ravel(), np.array(f["output"], np.float32).ravel(), atol=1e-4, rtol=0)
+
+
+def test_avgpool2d_known_answers(oracle):
+    """internal/layer/avgpool2d_test.go:8-35 (2x2 stride 2 on 4x4), :37-65 (2x2 stride 1 on 3x3), :84-114 (backward:
+    a unit output gradient spreads 0.25 to every input of its window)."""
+    st = oracle.OracleState([D.AvgPool2D(1, 2, 2, 0, 4, 4)], D.MSE, np.zeros(0, np.float32))
+    out = st.forward_batch(np.arange(1, 17, dtype=np.float32).reshape(1, 16), precision=32)
+    assert np.array_equal(out.ravel(), np.array([3.5, 5.5, 11.5, 13.5], np.float32))
+    st = oracle.OracleState([D.AvgPool2D(1, 2, 1, 0, 3, 3)], D.MSE, np.zeros(0, np.float32))
+    out = st.forward_batch(np.arange(1, 10, dtype=np.float32).reshape(1, 9), precision=32)
+    assert np.array_equal(out.ravel(), np.array([3, 4, 6, 7], np.float32))
+    # backward: an identity Dense in front makes the pooled layer's input gradient visible as the Dense bias gradient
+    layers = [D.Dense(16, 16, D.LINEAR), D.AvgPool2D(1, 2, 2, 0, 4, 4)]
+    params = np.concatenate([np.eye(16, dtype=np.float32).ravel(), np.zeros(16, np.float32)])
+    st = oracle.OracleState(layers, D.MSE, params)
+    x = np.arange(1, 17, dtype=np.float32).reshape(1, 16)
+    y = np.array([[3.5, 5.5, 11.5, 13.5]], np.float32) - 2.0          # MSE gradient 2/n (p - y) = 1 for n = 4
+    st.train_batch(x, y, precision=32, step=False)
+    assert np.allclose(st.grads[256:], 0.25, atol=1e-7)
