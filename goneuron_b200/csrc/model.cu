@@ -86,6 +86,7 @@ struct gn_model {
   int loss_kind = 0, W = 1;
   int64_t P = 0; int in_size = 0, out_size = 0;
   gn::DevBuf params, grads, m1, v2, state; int64_t NS = 0;
+  int cur_first_sample = 0;             // global index of the first sample of the batch being processed (Dropout's stream position)
   float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f; int timestep = 0;
   int cap = 0;                          // batch capacity of the activation buffers
   gn::DevBuf xin, yin, lossg, loss_s, loss_sum;
@@ -150,6 +151,12 @@ static int plan_layers(gn_model* m, const gn_layer_desc* layers, int n) {
       case GN_LAYER_CLS_POOLING:
         if (d.seq_len <= 0 || d.dim <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad CLSPooling descriptor", i);
         l.in_size = d.seq_len * d.dim; l.out_size = d.dim; break;
+      case GN_LAYER_DROPOUT: {
+        float pr = 0.f; memcpy(&pr, &d.dim, 4);
+        if (d.in_size <= 0 || !(pr >= 0.f && pr < 1.f)) return fail(GN_ERR_INVALID_ARG, "layer %d: bad Dropout descriptor", i);
+        if (cur >= 0 && cur != d.in_size) return fail(GN_ERR_INVALID_ARG, "layer %d: Dropout size %d does not match its input %lld", i, d.in_size, (long long)cur);
+        if (m->W > 1) return fail(GN_ERR_UNSUPPORTED, "layer %d: Dropout with more than one virtual worker (every worker clone restarts the random stream)", i);
+        l.in_size = l.out_size = d.in_size; l.s_off = m->NS; l.s_cnt = 2; m->NS += 2; l.bn_mom = pr; break; }
       case GN_LAYER_BATCHNORM2D:
         if (d.in_size <= 0 || d.in_h <= 0 || d.in_w <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad BatchNorm2D descriptor", i);
         l.in_size = l.out_size = d.in_size * d.in_h * d.in_w; l.p_cnt = 2 * (int64_t)d.in_size; l.s_off = m->NS; l.s_cnt = 2 * (int64_t)d.in_size; m->NS += l.s_cnt;
@@ -183,6 +190,7 @@ static int alloc_activations(gn_model* m, int cap) {
       case GN_LAYER_CONV2D: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.z.alloc(c * l.out_size)); break;
       case GN_LAYER_MAXPOOL2D: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.idx.alloc(c * l.out_size)); break;
       case GN_LAYER_AVGPOOL2D: GN_TRY(l.out.alloc(c * l.out_size)); break;
+      case GN_LAYER_DROPOUT: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.z.alloc(c * l.out_size)); break;      // z = the mask
       case GN_LAYER_FLATTEN: break;
       case GN_LAYER_LSTM_UNROLLED: {
         size_t th = c * d.seq_len * d.out_size;
@@ -289,6 +297,14 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         long n = (long)B * l.out_size;
         GN_LAUNCH(ctx, maxpool_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, l.out.p, (int*)l.idx.p, c);
         cur = l.out.p; break; }
+      case GN_LAYER_DROPOUT:
+        if (training) {
+          const long tot = (long)B * l.in_size;
+          GN_LAUNCH(ctx, dropout_fwd_kernel, ew_grid(ctx, cdiv(tot, DROP_RUN)), 256, 0, cur, l.out.p, l.z.p, (const float*)(m->state.p + l.s_off), tot, l.in_size, l.bn_mom,
+                    (long)m->cur_first_sample * l.in_size);
+          cur = l.out.p;
+        }
+        break;
       case GN_LAYER_AVGPOOL2D: {
         PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
                     (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
@@ -576,6 +592,9 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         long n = (long)B * l.out_size;
         GN_LAUNCH(ctx, maxpool_bwd_kernel, ew_grid(ctx, n), 256, 0, g, (const int*)l.idx.p, dx, c);
         g = dx; flip ^= 1; break; }
+      case GN_LAYER_DROPOUT:
+        if (need_dx) { long n = (long)B * l.in_size; GN_LAUNCH(ctx, dropout_bwd_kernel, ew_grid(ctx, n), 256, 0, g, (const float*)l.z.p, dx, n, l.bn_mom); g = dx; flip ^= 1; }
+        break;
       case GN_LAYER_AVGPOOL2D: {
         PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
                     (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
@@ -639,7 +658,10 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
   GN_CUDA(cudaEventRecord(m->ev0, ctx->stream));
   GN_CUDA(cudaMemsetAsync(m->grads.p, 0, (size_t)m->P * sizeof(float), ctx->stream));     // Network.ClearGradients, net.go:813-823
   const float* yp;
+  m->cur_first_sample = first_sample;
   GN_TRY(forward(m, x_dev, B, &yp, true));
+  for (auto& l : m->L) if (l.d.kind == GN_LAYER_DROPOUT)          // every rank moves the stream on by the whole global batch
+    GN_LAUNCH(ctx, dropout_advance_kernel, 1, 1, 0, m->state.p + l.s_off, (unsigned long long)global_batch * (unsigned long long)l.in_size);
   GN_LAUNCH(ctx, loss_rows_kernel, B, 256, 0, yp, y_dev, m->lossg.p, m->loss_s.p, m->out_size, m->loss_kind);
   GN_LAUNCH(ctx, loss_total_kernel, 1, 32, 0, m->loss_s.p, B, m->loss_sum.p);
   GN_TRY(backward(m, x_dev, B, m->lossg.p, global_batch, first_sample));

@@ -285,6 +285,44 @@ __global__ void __launch_bounds__(256) layernorm_pgrad_partial_vec_kernel(const 
   *reinterpret_cast<float4*>(part + ((long)blockIdx.y * 2 + 1) * n + c) = sbet;
 }
 
+// ---------------------------------------------------------------- Dropout
+// The reference's generator (layer.go:61-75): s <- s * 6364136223846793005 + 1, value = float32(s >> 33) / 2^31, one
+// stream per layer seeded with 42 and consumed element by element, sample by sample (dropout.go:139-152).  Draw k of the
+// stream is reached by composing the affine map k times (square and multiply), so every thread can enter the stream at
+// its own elements: element i of global sample g of a batch that starts after `count` draws uses draw count + g n + i + 1.
+// `cnt` = the two state floats (count mod 2^20, count >> 20).
+__device__ __forceinline__ unsigned long long lcg_jump(unsigned long long s0, unsigned long long k) {
+  unsigned long long A = 1, C = 0, a = 6364136223846793005ull, c = 1;
+  while (k) { if (k & 1) { A = A * a; C = C * a + c; } c = c * (a + 1); a = a * a; k >>= 1; }
+  return A * s0 + C;
+}
+constexpr int DROP_RUN = 8;      // consecutive elements per thread (one jump, then the recurrence)
+__global__ void dropout_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, float* __restrict__ mask, const float* __restrict__ cnt,
+                                   long total, int n, float p, long first_elem) {
+  const unsigned long long count = (unsigned long long)cnt[0] + ((unsigned long long)cnt[1] << 20);
+  const float scale = 1.0f / (1.0f - p);
+  for (long e0 = (blockIdx.x * (long)blockDim.x + threadIdx.x) * DROP_RUN; e0 < total; e0 += (long)gridDim.x * blockDim.x * DROP_RUN) {
+    unsigned long long s = lcg_jump(42ull, count + (unsigned long long)(first_elem + e0));
+#pragma unroll
+    for (int j = 0; j < DROP_RUN; j++) {
+      const long e = e0 + j; if (e >= total) break;
+      s = s * 6364136223846793005ull + 1ull;
+      const float r = (float)(s >> 33) / 2147483648.0f;
+      const bool keep = !(r < p);
+      mask[e] = keep ? 1.f : 0.f; y[e] = keep ? x[e] * scale : 0.f;
+    }
+  }
+}
+__global__ void dropout_bwd_kernel(const float* __restrict__ g, const float* __restrict__ mask, float* __restrict__ dx, long total, float p) {
+  const float scale = 1.0f / (1.0f - p);
+  for (long e = blockIdx.x * (long)blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) dx[e] = mask[e] > 0.f ? g[e] * scale : 0.f;
+}
+// after a training batch: the stream has moved on by `add` draws (global batch x elements per sample)
+__global__ void dropout_advance_kernel(float* __restrict__ cnt, unsigned long long add) {
+  const unsigned long long c = (unsigned long long)cnt[0] + ((unsigned long long)cnt[1] << 20) + add;
+  cnt[0] = (float)(c & 0xfffffull); cnt[1] = (float)(c >> 20);
+}
+
 // ---------------------------------------------------------------- embedding / positional / CLS
 // out[s,t,:] = E[floor(id)] (+ P[t,:])   reference: embedding.go:120-136, transformer.go:80-82
 __global__ void embedding_fwd_kernel(const float* __restrict__ ids, const float* __restrict__ E, const float* __restrict__ P,

@@ -3,7 +3,7 @@ constructors named after the reference's (goneuron/goneuron.go:59-340, internal/
 import ctypes as C
 
 # gn_layer_kind
-DENSE, CONV2D, MAXPOOL2D, FLATTEN, LSTM_UNROLLED, EMBEDDING, POSENC, TRANSFORMER_BLOCK, CLS_POOLING, LAYERNORM, BATCHNORM2D, AVGPOOL2D = range(1, 13)
+DENSE, CONV2D, MAXPOOL2D, FLATTEN, LSTM_UNROLLED, EMBEDDING, POSENC, TRANSFORMER_BLOCK, CLS_POOLING, LAYERNORM, BATCHNORM2D, AVGPOOL2D, DROPOUT = range(1, 14)
 # gn_activation
 LINEAR, RELU, SIGMOID, TANH, SOFTMAX, LOGSOFTMAX = range(6)
 # gn_loss_kind
@@ -35,6 +35,11 @@ def Conv2D(in_channels, out_channels, kernel, stride, padding, activation, in_h,
     """layer.NewConv2D(inC, outC, k, stride, pad, act) + SetInputDimensions(h, w) -- conv2d.go:60-140, :686-691."""
     return LayerDesc(kind=CONV2D, in_size=in_channels, out_size=out_channels, kernel=kernel, stride=stride,
                      padding=padding, activation=activation, in_h=in_h, in_w=in_w)
+
+
+def Dropout(p, in_size):
+    """layer.NewDropout(p, inSize) -- dropout.go:36."""
+    return LayerDesc(kind=DROPOUT, in_size=in_size, dim=_float_bits(p))
 
 
 def AvgPool2D(in_channels, kernel, stride, padding, in_h, in_w):

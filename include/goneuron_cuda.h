@@ -53,7 +53,9 @@ typedef enum gn_layer_kind {
   GN_LAYER_CLS_POOLING = 9,    /* layer.NewCLSPooling(T,dim)            internal/layer/transformer.go:1647-1777 */
   GN_LAYER_LAYERNORM = 10,     /* layer.NewLayerNorm(dim,eps,true) applied row-wise  layernorm.go:193-441 */
   GN_LAYER_BATCHNORM2D = 11,   /* layer.NewBatchNorm2D(C,eps,momentum,true) + SetInputDimensions  batchnorm2d.go:67-665 */
-  GN_LAYER_AVGPOOL2D = 12      /* layer.NewAvgPool2D(inC,k,s,p) + input dimensions   internal/layer/avgpool2d.go:43-228, 401-468 */
+  GN_LAYER_AVGPOOL2D = 12,     /* layer.NewAvgPool2D(inC,k,s,p) + input dimensions   internal/layer/avgpool2d.go:43-228, 401-468 */
+  GN_LAYER_DROPOUT = 13        /* layer.NewDropout(p, inSize): in_size = inSize, dim = bits of float p;  internal/layer/dropout.go:36-155, 241-293.
+                                  State: two floats = number of random draws consumed so far (low 20 bits | the rest). */
 } gn_layer_kind;
 
 /* Activations (reference: internal/activations/activations.go:22-236,342-352). */

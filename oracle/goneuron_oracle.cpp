@@ -122,6 +122,8 @@ template <class R> struct Layer {
   // set by the trainer: true when this sample is the last one of its worker chunk
   bool last_of_chunk = true;
   virtual void set_last_of_chunk(bool v) { last_of_chunk = v; }
+  // set by the trainer: index of the sample in the global batch (Dropout's position in its random stream)
+  virtual void set_sample(int64_t) {}
 };
 
 // reference: internal/layer/layer.go:346-456 (ForwardWithArena), :488-667 (Backward),
@@ -337,6 +339,48 @@ template <class R> struct AvgPool2D : Layer<R> {
         for (int kh = 0; kh < k; kh++) for (int kw = 0; kw < k; kw++) if (valid(oh, ow, kh, kw, ih, iw)) gradIn[((size_t)c * H + ih) * Wd + iw] += gv;
       }
     }
+    return gradIn.data();
+  }
+};
+
+// The reference's generator (layer.go:61-75): s <- s * 6364136223846793005 + 1, value = float32(s >> 33) / 2^31.
+// Draw number k (1-based) of a stream seeded with s0 is reached by composing the affine map k times (square and multiply).
+static inline uint64_t lcg_jump(uint64_t s0, uint64_t k) {
+  uint64_t A = 1, C = 0, a = 6364136223846793005ull, c = 1;
+  while (k) { if (k & 1) { A = A * a; C = C * a + c; } c = c * (a + 1); a = a * a; k >>= 1; }
+  return A * s0 + C;
+}
+// reference: internal/layer/dropout.go:85-155 (training: one draw per element, draw < p zeroes it, the rest is scaled by
+// 1 / (1 - p) in float32; otherwise identity), :241-293 (backward through the same mask).  One generator per layer, seeded
+// with 42 (dropout.go:63) and never reset, so the element i of global sample g of a batch that starts after `count`
+// draws uses draw count + g * n + i + 1.  State: count as two exactly representable floats (count mod 2^20, count >> 20).
+template <class R> struct Dropout : Layer<R> {
+  int n; float p; const R* st = nullptr; int64_t sample = 0;
+  std::vector<R> output, gradIn; std::vector<uint8_t> mask;
+  Dropout(int n_, float p_) : n(n_), p(p_), output(n_), gradIn(n_), mask(n_) {}
+  int in_size() const override { return n; } int out_size() const override { return n; }
+  int64_t n_state() const override { return 2; }
+  void bind_state(const R* s) override { st = s; }
+  R momentum() const override { return R(1); }            // "running" value := value after this sample
+  void set_sample(int64_t g) override { sample = g; }
+  uint64_t count() const { return st ? (uint64_t)st[0] + ((uint64_t)st[1] << 20) : 0; }
+  void last_stats(R* dst) const override { uint64_t c = count() + (uint64_t)(sample + 1) * n; dst[0] = (R)(c & 0xfffffu); dst[1] = (R)(c >> 20); }
+  const R* forward(const R* x) override {
+    if (!this->training) { std::copy(x, x + n, output.begin()); return output.data(); }
+    const float keep = 1.0f - p, scale = 1.0f / keep;
+    uint64_t s = lcg_jump(42, count() + (uint64_t)sample * n);
+    for (int i = 0; i < n; i++) {
+      s = s * 6364136223846793005ull + 1;
+      const float r = (float)(s >> 33) / 2147483648.0f;
+      mask[i] = r < p ? 0 : 1;
+      output[i] = mask[i] ? x[i] * (R)scale : R(0);
+    }
+    return output.data();
+  }
+  const R* backward(R* grad) override {
+    if (!this->training) return grad;
+    const float keep = 1.0f - p, scale = 1.0f / keep;
+    for (int i = 0; i < n; i++) gradIn[i] = mask[i] ? grad[i] * (R)scale : R(0);
     return gradIn.data();
   }
 };
@@ -731,6 +775,7 @@ template <class R> struct Net {
         case GN_LAYER_DENSE: p.reset(new Dense<R>(l.in_size, l.out_size, l.activation)); break;
         case GN_LAYER_CONV2D: p.reset(new Conv2D<R>(l.in_size, l.out_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w, l.activation)); break;
         case GN_LAYER_MAXPOOL2D: p.reset(new MaxPool2D<R>(l.in_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w)); break;
+        case GN_LAYER_DROPOUT: { float pr = 0.f; memcpy(&pr, &l.dim, 4); if (l.in_size <= 0 || pr < 0.f || pr >= 1.f) { g_err = "Dropout descriptor"; return false; } p.reset(new Dropout<R>(l.in_size, pr)); break; }
         case GN_LAYER_AVGPOOL2D: p.reset(new AvgPool2D<R>(l.in_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w)); break;
         case GN_LAYER_FLATTEN: if (cur < 0) { g_err = "Flatten cannot be first"; return false; } p.reset(new Flatten<R>(cur)); break;
         case GN_LAYER_LSTM_UNROLLED: p.reset(new LSTMUnrolled<R>(l.in_size, l.out_size, l.seq_len, l.return_seq != 0)); net.has_lstm = true; break;
@@ -840,12 +885,14 @@ template <class R> int train_batch_impl(const TrainArgs& a) {
   }
   const int64_t NS = proto.n_state;
   std::vector<R> sample_stats((size_t)NS * B);
+  std::vector<R> state0(NS + 1, R(0));                       // state at the start of the batch (read-only for the workers)
+  if (NS && a.state) for (int64_t k = 0; k < NS; k++) state0[k] = (R)a.state[k];
   std::vector<std::vector<R>> jgrads(jobs.size());
   std::vector<R> jloss(jobs.size(), R(0));
   std::atomic<int> next{0};
   auto t0 = std::chrono::steady_clock::now();
   auto worker = [&]() {
-    Net<R> net; Net<R>::build(a.layers, a.n_layers, net);
+    Net<R> net; Net<R>::build(a.layers, a.n_layers, net); net.bind_state(state0.data());
     std::vector<R> xs(in), ys(out), lg(out);
     for (;;) {
       int j = next.fetch_add(1); if (j >= (int)jobs.size()) break;
@@ -853,7 +900,7 @@ template <class R> int train_batch_impl(const TrainArgs& a) {
       net.bind(params.data(), jgrads[j].data());
       R local = 0;
       for (int i = jobs[j].s; i < jobs[j].e; i++) {
-        for (auto& l : net.layers) { l->reset(); l->set_last_of_chunk(i == jobs[j].chunk_end - 1); }
+        for (auto& l : net.layers) { l->reset(); l->set_last_of_chunk(i == jobs[j].chunk_end - 1); l->set_sample((int64_t)first + i); }
         for (int k = 0; k < in; k++) xs[k] = (R)a.x[(size_t)i * in + k];
         for (int k = 0; k < out; k++) ys[k] = (R)a.y[(size_t)i * out + k];
         const R* yp = net.forward(xs.data());

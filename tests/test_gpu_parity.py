@@ -43,6 +43,8 @@ CASES = [
     ("mlp_ln", dict(in_size=12, hidden=1024, norm=512, classes=3), 9, 1),                                   # ... 4 x 128 columns
     ("cnn_avg", {}, 16, 1),                                                                                 # AvgPool2D, overlapping padded windows
     ("cnn_avg", dict(hw=9, c0=1, c1=3, classes=2), 5, 1),
+    ("mlp_drop", {}, 24, 1),                                                                                # Dropout: mask from the reference's generator
+    ("mlp_drop", dict(in_size=9, hidden=21, classes=3, p=0.6), 7, 1),
 ]
 
 
@@ -209,7 +211,8 @@ def test_lstm_scan_variants_in_subprocess(mode):
     assert r.returncode == 0 and " passed" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
 
 
-@pytest.mark.parametrize("name,kw,batch", [("cnn_bn", {}, 32), ("transformer_small", dict(vocab=512, dim=64, seq_len=16, heads=4, ff_dim=128, n_blocks=2), 8)])
+@pytest.mark.parametrize("name,kw,batch", [("cnn_bn", {}, 32), ("mlp_drop", {}, 24),
+                                           ("transformer_small", dict(vocab=512, dim=64, seq_len=16, heads=4, ff_dim=128, n_blocks=2), 8)])
 def test_resume_from_checkpoint_is_bit_exact(device, tmp_path, name, kw, batch):
     """Parameters + Adam moments + step counter + running statistics, saved after two steps and loaded into a fresh
     model, continue exactly like the uninterrupted run (the reference loses the Adam state on Save, opt.go:312-322)."""
@@ -250,3 +253,25 @@ def test_learning_rate_schedule_is_followed(device, oracle):
         fixed.train_batch(x, y, precision=64)
     assert np.abs(model.Params() - fixed.params).max() > 10 * d      # and the schedule really changed the trajectory
     model.Close()
+
+
+def test_dropout_stream_continues_across_batches(device, oracle):
+    """The layer's generator is never reset (dropout.go:63): the second batch continues where the first one stopped, a
+    batch of another size shifts everything after it, and inference is the identity."""
+    from goneuron_b200.sequential import Adam, Sequential
+    layers, loss_kind, params, x, y, lr = configs.make_case("mlp_drop", batch=24)
+    ref = oracle.OracleState(layers, loss_kind, params, lr=lr)
+    model = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+    model.SetParams(params)
+    for lo, hi in ((0, 24), (0, 10), (10, 24)):
+        l_ref = ref.train_batch(x[lo:hi], y[lo:hi], precision=64)
+        l_gpu = model.TrainBatch(x[lo:hi], y[lo:hi])
+        assert abs(l_gpu - l_ref) <= TOL * max(1.0, abs(l_ref))
+        assert_grads_close(layers, model.Gradients(), ref.grads)
+    assert np.array_equal(model.State(), ref.state) and model.State()[0] == (24 + 10 + 14) * 64
+    # inference: no mask, no scaling
+    nodrop = [layers[0], layers[2]]
+    plain = Sequential(nodrop, device).Compile(Adam(lr), loss_kind)
+    plain.SetParams(model.Params())
+    assert np.array_equal(model.PredictBatch(x), plain.PredictBatch(x))
+    model.Close(); plain.Close()
