@@ -28,6 +28,11 @@ def mlp_ln(in_size=24, hidden=48, norm=16, classes=4):
     return [D.Dense(in_size, hidden, D.TANH), D.LayerNorm(norm), D.Dense(hidden, classes, D.SOFTMAX)], D.CROSS_ENTROPY
 
 
+def mlp_act(act=D.GELU, alpha=None, in_size=20, hidden=32, classes=4):
+    """Dense(act) -> Dense(act) -> Dense(softmax): exercises the element-wise activations (activations.go)."""
+    return [D.Dense(in_size, hidden, act, alpha), D.Dense(hidden, hidden, act, alpha), D.Dense(hidden, classes, D.SOFTMAX)], D.CROSS_ENTROPY
+
+
 def mlp_drop(in_size=40, hidden=64, classes=5, p=0.3):
     """Dense -> Dropout -> Dense: exercises Dropout's mask stream (dropout.go)."""
     return [D.Dense(in_size, hidden, D.RELU), D.Dropout(p, hidden), D.Dense(hidden, classes, D.SOFTMAX)], D.CROSS_ENTROPY
@@ -65,12 +70,13 @@ CONFIGS = {
     "cnn_bn": (cnn_bn, {}, 32, 1e-3),
     "cnn_avg": (cnn_avg, {}, 16, 1e-3),
     "mlp_drop": (mlp_drop, {}, 24, 1e-3),
+    "mlp_act": (mlp_act, {}, 12, 1e-3),
     "mlp_ln": (mlp_ln, {}, 16, 1e-3),
     "lstm": (recurrent, {}, 256, 1e-3),
     "transformer_small": (transformer, dict(vocab=8192, dim=256, seq_len=128, heads=8, ff_dim=1024, n_blocks=4), 64, 3e-4),
     "transformer_large": (transformer, dict(vocab=32000, dim=1024, seq_len=512, heads=16, ff_dim=4096, n_blocks=8), 256, 1e-4),
 }
-SEEDS = {"mlp_drop": 1243, "cnn_avg": 1242, "mlp_ln": 1241, "cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
+SEEDS = {"mlp_act": 1244, "mlp_drop": 1243, "cnn_avg": 1242, "mlp_ln": 1241, "cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
 
 
 def build(name, **override):

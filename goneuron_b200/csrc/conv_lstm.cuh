@@ -12,7 +12,7 @@ struct ConvShape { int B, inC, outC, k, s, p, H, W, oH, oW; };
 // z[b,oc,oh,ow] = bias[oc] + sum_{ic,kh,kw} W[oc,ic,kh,kw] x[b,ic,oh*s+kh-p,ow*s+kw-p]; a = act(z)
 // reference: conv2d.go:716-959 (zero padding = out-of-range taps skipped; bias added last)
 __global__ void conv2d_fwd_kernel(const float* __restrict__ x, const float* __restrict__ Wt, const float* __restrict__ bias,
-                                  float* __restrict__ z, float* __restrict__ a, ConvShape c, int act) {
+                                  float* __restrict__ z, float* __restrict__ a, ConvShape c, int act, float alpha) {
   long total = (long)c.B * c.outC * c.oH * c.oW;
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
     int ow = (int)(i % c.oW); long r = i / c.oW; int oh = (int)(r % c.oH); r /= c.oH; int oc = (int)(r % c.outC); int b = (int)(r / c.outC);
@@ -28,7 +28,7 @@ __global__ void conv2d_fwd_kernel(const float* __restrict__ x, const float* __re
         }
       }
     acc += bias[oc];
-    z[i] = acc; a[i] = act_fwd(act, acc);
+    z[i] = acc; a[i] = act_fwd(act, acc, alpha);
   }
 }
 // dx[b,ic,ih,iw] = sum_{oc,kh,kw} g[b,oc,oh,ow] W[oc,ic,kh,kw] with oh*s+kh-p = ih   (conv2d.go:1151-1162)

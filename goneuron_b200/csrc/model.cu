@@ -117,10 +117,12 @@ static int plan_layers(gn_model* m, const gn_layer_desc* layers, int n) {
     switch (d.kind) {
       case GN_LAYER_DENSE:
         if (d.in_size <= 0 || d.out_size <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: Dense sizes must be positive", i);
+        if (d.activation < GN_ACT_LINEAR || d.activation > GN_ACT_ELU) return fail(GN_ERR_UNSUPPORTED, "layer %d: activation %d", i, d.activation);
         l.in_size = d.in_size; l.out_size = d.out_size; l.p_cnt = (int64_t)d.in_size * d.out_size + d.out_size; break;
       case GN_LAYER_CONV2D: {
         if (d.in_size <= 0 || d.out_size <= 0 || d.kernel <= 0 || d.stride <= 0 || d.in_h <= 0 || d.in_w <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad Conv2D descriptor", i);
         if (d.activation == GN_ACT_SOFTMAX || d.activation == GN_ACT_LOGSOFTMAX) return fail(GN_ERR_UNSUPPORTED, "layer %d: Conv2D with a softmax activation", i);
+        if (d.activation < GN_ACT_LINEAR || d.activation > GN_ACT_ELU) return fail(GN_ERR_UNSUPPORTED, "layer %d: activation %d", i, d.activation);
         int oh = (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, ow = (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1;
         l.in_size = d.in_size * d.in_h * d.in_w; l.out_size = d.out_size * oh * ow;
         l.p_cnt = (int64_t)d.out_size * d.in_size * d.kernel * d.kernel + d.out_size; break; }
@@ -282,14 +284,14 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
           GN_TRY(gemm_nt(ctx, B, d.out_size, d.in_size, cur, d.in_size, W, bias, l.z.p, d.out_size));
           if (d.activation == GN_ACT_SOFTMAX || d.activation == GN_ACT_LOGSOFTMAX)
             GN_LAUNCH(ctx, softmax_rows_kernel, B, 256, 0, l.z.p, l.out.p, d.out_size, d.activation == GN_ACT_LOGSOFTMAX ? 1 : 0);
-          else { long n = (long)B * d.out_size; GN_LAUNCH(ctx, act_forward_kernel, ew_grid(ctx, n), 256, 0, l.z.p, l.out.p, n, d.activation); }
+          else { long n = (long)B * d.out_size; GN_LAUNCH(ctx, act_forward_kernel, ew_grid(ctx, n), 256, 0, l.z.p, l.out.p, n, d.activation, act_alpha_of(d.activation, d.reserved)); }
         }
         cur = l.out.p; break; }
       case GN_LAYER_CONV2D: {
         ConvShape c{B, d.in_size, d.out_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
                     (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
         long n = (long)B * l.out_size;
-        GN_LAUNCH(ctx, conv2d_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, p, p + (long)d.out_size * d.in_size * d.kernel * d.kernel, l.z.p, l.out.p, c, d.activation);
+        GN_LAUNCH(ctx, conv2d_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, p, p + (long)d.out_size * d.in_size * d.kernel * d.kernel, l.z.p, l.out.p, c, d.activation, act_alpha_of(d.activation, d.reserved));
         cur = l.out.p; break; }
       case GN_LAYER_MAXPOOL2D: {
         PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
@@ -556,7 +558,7 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
           float* dzb; GN_TRY(ensure(m, S_DZ, (size_t)B * d.out_size, &dzb)); long n = (long)B * d.out_size;
           if (d.activation == GN_ACT_SOFTMAX || d.activation == GN_ACT_LOGSOFTMAX)
             GN_LAUNCH(ctx, head_jacobian_kernel, B, 256, 0, g, l.out.p, dzb, d.out_size, d.activation == GN_ACT_LOGSOFTMAX ? 1 : 0);
-          else GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, d.activation == GN_ACT_RELU ? l.out.p : l.z.p, dzb, n, d.activation);
+          else GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, d.activation == GN_ACT_RELU ? l.out.p : l.z.p, dzb, n, d.activation, act_alpha_of(d.activation, d.reserved));
           dz = dzb;
         }
         GN_TRY(colsum(m, dz, d.out_size, B, d.out_size, gr + wn, false));
@@ -567,7 +569,7 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         ConvShape c{B, d.in_size, d.out_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
                     (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
         long n = (long)B * l.out_size; float* dzb; GN_TRY(ensure(m, S_DZ, (size_t)n, &dzb));
-        GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, l.z.p, dzb, n, d.activation);
+        GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, l.z.p, dzb, n, d.activation, act_alpha_of(d.activation, d.reserved));
         int nW = d.out_size * d.in_size * d.kernel * d.kernel;
         if (d.kernel == 3 || d.kernel == 5 || d.kernel == 1) {
           const int pairs = d.out_size * d.in_size, slices = std::max(1, std::min(B, (4 * ctx->sm_count + pairs - 1) / pairs)), ng = nW + d.out_size;

@@ -9,29 +9,46 @@
 namespace gn {
 
 // ---------------------------------------------------------------- activations
-// reference: internal/activations/activations.go:25-58, :135-143 (float64 libm then rounded)
-__device__ __forceinline__ float act_fwd(int act, float x) {
+// reference: internal/activations/activations.go:25-58, :135-143 (float64 libm then rounded), :62-82 (LeakyReLU),
+// :241-275 (GELU, tanh form: Activate in float32 around a float64 tanh, Derivative in float64), :277-309 (SiLU), :311-340 (ELU)
+__host__ __device__ inline float act_alpha_of(int act, int bits) {
+  float a = 0.f; memcpy(&a, &bits, 4);
+  if (bits == 0) a = act == GN_ACT_LEAKY_RELU ? 0.01f : (act == GN_ACT_ELU ? 1.0f : 0.f);
+  return a;
+}
+__device__ __forceinline__ float act_fwd(int act, float x, float alpha = 0.f) {
   switch (act) {
     case GN_ACT_RELU: return x > 0.f ? x : 0.f;
     case GN_ACT_SIGMOID: return 1.f / (1.f + (float)exp((double)-x));
     case GN_ACT_TANH: return (float)tanh((double)x);
+    case GN_ACT_LEAKY_RELU: return x > 0.f ? x : alpha * x;
+    case GN_ACT_ELU: return x > 0.f ? x : alpha * ((float)exp((double)x) - 1.f);
+    case GN_ACT_GELU: { float x3 = x * x * x; float arg = 0.7978845608028654f * (x + 0.044715f * x3); return 0.5f * x * (1.f + (float)tanh((double)arg)); }
+    case GN_ACT_SILU: { if (x >= 0.f) return x * (1.f / (1.f + (float)exp((double)-x))); float e = (float)exp((double)x); return x * e / (1.f + e); }
     default: return x;
   }
 }
-__device__ __forceinline__ float act_der(int act, float x) {
+__device__ __forceinline__ float act_der(int act, float x, float alpha = 0.f) {
   switch (act) {
     case GN_ACT_RELU: return x > 0.f ? 1.f : 0.f;
     case GN_ACT_SIGMOID: { float s = 1.f / (1.f + (float)exp((double)-x)); return s * (1.f - s); }
     case GN_ACT_TANH: { float t = (float)tanh((double)x); return 1.f - t * t; }
+    case GN_ACT_LEAKY_RELU: return x > 0.f ? 1.f : alpha;
+    case GN_ACT_ELU: return x > 0.f ? 1.f : alpha * (float)exp((double)x);
+    case GN_ACT_GELU: {
+      const double c = 0.044715, k = 0.7978845608028654, xd = (double)x, x2 = xd * xd, t = tanh(k * (xd + c * xd * x2));
+      return (float)(0.5 * (1.0 + t) + 0.5 * xd * (1.0 - t * t) * k * (1.0 + 3.0 * c * x2));
+    }
+    case GN_ACT_SILU: { float sg; if (x >= 0.f) sg = 1.f / (1.f + (float)exp((double)-x)); else { float e = (float)exp((double)x); sg = e / (1.f + e); } return sg + x * sg * (1.f - sg); }
     default: return 1.f;
   }
 }
-__global__ void act_forward_kernel(const float* __restrict__ z, float* __restrict__ a, long n, int act) {
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) a[i] = act_fwd(act, z[i]);
+__global__ void act_forward_kernel(const float* __restrict__ z, float* __restrict__ a, long n, int act, float alpha = 0.f) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) a[i] = act_fwd(act, z[i], alpha);
 }
 // dz = dA * act'(z)   (Dense.Backward default branch, layer.go:563-567; Conv2D.Backward conv2d.go:1133)
-__global__ void act_backward_kernel(const float* __restrict__ dA, const float* __restrict__ z, float* __restrict__ dz, long n, int act) {
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) dz[i] = dA[i] * act_der(act, z[i]);
+__global__ void act_backward_kernel(const float* __restrict__ dA, const float* __restrict__ z, float* __restrict__ dz, long n, int act, float alpha = 0.f) {
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) dz[i] = dA[i] * act_der(act, z[i], alpha);
 }
 
 // ---------------------------------------------------------------- softmax heads

@@ -5,7 +5,7 @@ import ctypes as C
 # gn_layer_kind
 DENSE, CONV2D, MAXPOOL2D, FLATTEN, LSTM_UNROLLED, EMBEDDING, POSENC, TRANSFORMER_BLOCK, CLS_POOLING, LAYERNORM, BATCHNORM2D, AVGPOOL2D, DROPOUT = range(1, 14)
 # gn_activation
-LINEAR, RELU, SIGMOID, TANH, SOFTMAX, LOGSOFTMAX = range(6)
+LINEAR, RELU, SIGMOID, TANH, SOFTMAX, LOGSOFTMAX, GELU, SILU, LEAKY_RELU, ELU = range(10)
 # gn_loss_kind
 MSE, CROSS_ENTROPY = 0, 1
 
@@ -26,15 +26,16 @@ def layers_to_array(layers):
     return arr
 
 
-def Dense(in_size, out_size, activation=LINEAR):
-    """layer.NewDense(in, out, act) -- internal/layer/layer.go:224-340."""
-    return LayerDesc(kind=DENSE, in_size=in_size, out_size=out_size, activation=activation)
+def Dense(in_size, out_size, activation=LINEAR, alpha=None):
+    """layer.NewDense(in, out, act) -- internal/layer/layer.go:224-340.  `alpha`: slope / scale of LEAKY_RELU / ELU
+    (activations.NewLeakyReLU, NewELU); None selects 0.01 / 1."""
+    return LayerDesc(kind=DENSE, in_size=in_size, out_size=out_size, activation=activation, reserved=0 if alpha is None else _float_bits(alpha))
 
 
-def Conv2D(in_channels, out_channels, kernel, stride, padding, activation, in_h, in_w):
+def Conv2D(in_channels, out_channels, kernel, stride, padding, activation, in_h, in_w, alpha=None):
     """layer.NewConv2D(inC, outC, k, stride, pad, act) + SetInputDimensions(h, w) -- conv2d.go:60-140, :686-691."""
     return LayerDesc(kind=CONV2D, in_size=in_channels, out_size=out_channels, kernel=kernel, stride=stride,
-                     padding=padding, activation=activation, in_h=in_h, in_w=in_w)
+                     padding=padding, activation=activation, in_h=in_h, in_w=in_w, reserved=0 if alpha is None else _float_bits(alpha))
 
 
 def Dropout(p, in_size):

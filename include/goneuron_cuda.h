@@ -65,7 +65,11 @@ typedef enum gn_activation {
   GN_ACT_SIGMOID = 2,
   GN_ACT_TANH = 3,
   GN_ACT_SOFTMAX = 4,      /* the ActTypeSoftmax branch, layer.go:504-529 (reached with &activations.Softmax{}) */
-  GN_ACT_LOGSOFTMAX = 5    /* the ActTypeLogSoftmax branch, layer.go:530-560 */
+  GN_ACT_LOGSOFTMAX = 5,   /* the ActTypeLogSoftmax branch, layer.go:530-560 */
+  GN_ACT_GELU = 6,         /* activations.GELU (tanh form), activations.go:241-275 */
+  GN_ACT_SILU = 7,         /* activations.SiLU, activations.go:277-309 */
+  GN_ACT_LEAKY_RELU = 8,   /* activations.NewLeakyReLU(alpha), activations.go:62-82; alpha = bits of `reserved` (0 selects 0.01) */
+  GN_ACT_ELU = 9           /* activations.NewELU(alpha), activations.go:311-340; alpha = bits of `reserved` (0 selects 1, as NewELU) */
 } gn_activation;
 
 /* Losses (reference: internal/loss/loss.go:53-105 MSE, :120-178 CrossEntropy). */
@@ -88,7 +92,7 @@ typedef struct gn_layer_desc {
   int32_t ff_dim;      /* TransformerBlock */
   int32_t causal;      /* TransformerBlock */
   int32_t return_seq;  /* unroller: 0 = last hidden state only */
-  int32_t reserved;    /* BatchNorm2D: eps as float bits (0 = 1e-5) */
+  int32_t reserved;    /* BatchNorm2D: eps as float bits (0 = 1e-5); Dense / Conv2D: alpha of LEAKY_RELU / ELU as float bits */
 } gn_layer_desc;
 
 typedef struct gn_ctx gn_ctx;

@@ -66,20 +66,37 @@ template <class R> inline R r_tanh(R x) { return (R)std::tanh((double)x); }
 template <class R> inline R r_sqrt(R x) { return (R)std::sqrt((double)x); }
 template <class R> inline R sigmoid(R x) { return R(1) / (R(1) + r_exp<R>(-x)); }
 
-// reference: activations.go:25-38 (ReLU), :342-352 (Linear), :45-58, :135-143
-template <class R> inline R act_apply(int act, R x) {
+// reference: activations.go:25-38 (ReLU), :342-352 (Linear), :45-58, :135-143, :62-82 (LeakyReLU), :241-275 (GELU, tanh form;
+// Activate in float32 with a float64 tanh, Derivative entirely in float64), :277-309 (SiLU), :311-340 (ELU)
+inline float act_default_alpha(int act, uint32_t bits) {
+  float a = 0.f; memcpy(&a, &bits, 4);
+  if (bits == 0) a = act == GN_ACT_LEAKY_RELU ? 0.01f : (act == GN_ACT_ELU ? 1.0f : 0.f);
+  return a;
+}
+template <class R> inline R act_apply(int act, R x, R alpha = R(0)) {
   switch (act) {
     case GN_ACT_RELU: return x > 0 ? x : R(0);
     case GN_ACT_SIGMOID: return sigmoid<R>(x);
     case GN_ACT_TANH: return r_tanh<R>(x);
+    case GN_ACT_LEAKY_RELU: return x > 0 ? x : alpha * x;
+    case GN_ACT_ELU: return x > 0 ? x : alpha * (r_exp<R>(x) - R(1));
+    case GN_ACT_GELU: { R x3 = x * x * x; R arg = R(0.7978845608028654) * (x + R(0.044715) * x3); return R(0.5) * x * (R(1) + r_tanh<R>(arg)); }
+    case GN_ACT_SILU: { if (x >= 0) return x * (R(1) / (R(1) + r_exp<R>(-x))); R e = r_exp<R>(x); return x * e / (R(1) + e); }
     default: return x;
   }
 }
-template <class R> inline R act_deriv(int act, R x) {
+template <class R> inline R act_deriv(int act, R x, R alpha = R(0)) {
   switch (act) {
     case GN_ACT_RELU: return x > 0 ? R(1) : R(0);
     case GN_ACT_SIGMOID: { R s = sigmoid<R>(x); return s * (R(1) - s); }
     case GN_ACT_TANH: { R t = r_tanh<R>(x); return R(1) - t * t; }
+    case GN_ACT_LEAKY_RELU: return x > 0 ? R(1) : alpha;
+    case GN_ACT_ELU: return x > 0 ? R(1) : alpha * r_exp<R>(x);
+    case GN_ACT_GELU: {
+      const double c = 0.044715, k = 0.7978845608028654, xd = (double)x, x2 = xd * xd, t = std::tanh(k * (xd + c * xd * x2));
+      return (R)(0.5 * (1.0 + t) + 0.5 * xd * (1.0 - t * t) * k * (1.0 + 3.0 * c * x2));
+    }
+    case GN_ACT_SILU: { R sg; if (x >= 0) sg = R(1) / (R(1) + r_exp<R>(-x)); else { R e = r_exp<R>(x); sg = e / (R(1) + e); } return sg + x * sg * (R(1) - sg); }
     default: return R(1);
   }
 }
@@ -134,6 +151,7 @@ template <class R> struct Dense : Layer<R> {
   const R *W = nullptr, *b = nullptr;
   R *gW = nullptr, *gb = nullptr;
   std::vector<R> inputBuf, preAct, output, savedOutput, dz, gradIn;
+  R alpha = R(0);
   Dense(int in_, int out_, int act_) : in(in_), out(out_), act(act_),
       inputBuf(in_), preAct(out_), output(out_), savedOutput(out_), dz(out_), gradIn(in_) {}
   int64_t n_params() const override { return (int64_t)in * out + out; }
@@ -150,7 +168,7 @@ template <class R> struct Dense : Layer<R> {
     }
     if (act == GN_ACT_SOFTMAX) { output = preAct; softmax_inplace<R>(output.data(), out); }
     else if (act == GN_ACT_LOGSOFTMAX) { output = preAct; logsoftmax_inplace<R>(output.data(), out); }
-    else for (int o = 0; o < out; o++) output[o] = act_apply<R>(act, preAct[o]);
+    else for (int o = 0; o < out; o++) output[o] = act_apply<R>(act, preAct[o], alpha);
     savedOutput = output;
     return output.data();
   }
@@ -185,7 +203,7 @@ template <class R> struct Dense : Layer<R> {
       }
     } else {
       // layer.go:563-567: derivative taken at the layer's LAST pre-activation buffer
-      for (int o = 0; o < out; o++) { dz[o] = grad[o] * act_deriv<R>(act, preAct[o]); gb[o] += dz[o]; }
+      for (int o = 0; o < out; o++) { dz[o] = grad[o] * act_deriv<R>(act, preAct[o], alpha); gb[o] += dz[o]; }
     }
     // layer.go:591-625: gradW += dz (x) inputBuf  (inputBuf = last forward's input)
     for (int o = 0; o < out; o++) {
@@ -206,7 +224,7 @@ template <class R> struct Dense : Layer<R> {
 // each kernel row's three products before adding them to the accumulator; bias is
 // added after all input channels :930-956), :1113-1168 (backward).
 template <class R> struct Conv2D : Layer<R> {
-  int inC, outC, k, s, p, H, Wd, oH, oW, act;
+  int inC, outC, k, s, p, H, Wd, oH, oW, act; R alpha = R(0);
   const R *W = nullptr, *b = nullptr; R *gW = nullptr, *gb = nullptr;
   std::vector<R> saved, preAct, output, gradIn;
   Conv2D(int inC_, int outC_, int k_, int s_, int p_, int H_, int W_, int act_)
@@ -249,7 +267,7 @@ template <class R> struct Conv2D : Layer<R> {
           }
         }
       }
-      for (int i = 0; i < oH * oW; i++) { z[i] += b[oc]; output[(size_t)oc * oH * oW + i] = act_apply<R>(act, z[i]); }
+      for (int i = 0; i < oH * oW; i++) { z[i] += b[oc]; output[(size_t)oc * oH * oW + i] = act_apply<R>(act, z[i], alpha); }
     }
     return output.data();
   }
@@ -257,7 +275,7 @@ template <class R> struct Conv2D : Layer<R> {
     std::fill(gradIn.begin(), gradIn.end(), R(0));
     for (int oc = 0; oc < outC; oc++) for (int oh = 0; oh < oH; oh++) for (int ow = 0; ow < oW; ow++) {
       size_t pos = ((size_t)oc * oH + oh) * oW + ow;
-      R g = grad[pos] * act_deriv<R>(act, preAct[pos]);
+      R g = grad[pos] * act_deriv<R>(act, preAct[pos], alpha);
       gb[oc] += g;
       for (int ic = 0; ic < inC; ic++) for (int kh = 0; kh < k; kh++) {
         int ih = oh * s + kh - p; if (ih < 0 || ih >= H) continue;
@@ -772,8 +790,8 @@ template <class R> struct Net {
       const gn_layer_desc& l = L[i];
       std::unique_ptr<Layer<R>> p;
       switch (l.kind) {
-        case GN_LAYER_DENSE: p.reset(new Dense<R>(l.in_size, l.out_size, l.activation)); break;
-        case GN_LAYER_CONV2D: p.reset(new Conv2D<R>(l.in_size, l.out_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w, l.activation)); break;
+        case GN_LAYER_DENSE: { auto* dl = new Dense<R>(l.in_size, l.out_size, l.activation); dl->alpha = (R)act_default_alpha(l.activation, (uint32_t)l.reserved); p.reset(dl); break; }
+        case GN_LAYER_CONV2D: { auto* cl = new Conv2D<R>(l.in_size, l.out_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w, l.activation); cl->alpha = (R)act_default_alpha(l.activation, (uint32_t)l.reserved); p.reset(cl); break; }
         case GN_LAYER_MAXPOOL2D: p.reset(new MaxPool2D<R>(l.in_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w)); break;
         case GN_LAYER_DROPOUT: { float pr = 0.f; memcpy(&pr, &l.dim, 4); if (l.in_size <= 0 || pr < 0.f || pr >= 1.f) { g_err = "Dropout descriptor"; return false; } p.reset(new Dropout<R>(l.in_size, pr)); break; }
         case GN_LAYER_AVGPOOL2D: p.reset(new AvgPool2D<R>(l.in_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w)); break;
@@ -1000,9 +1018,9 @@ int gno_forward_batch(const gn_layer_desc* layers, int n_layers, const float* pa
 void gno_activation(int act, float* x, int n) {
   if (act == GN_ACT_SOFTMAX) softmax_inplace<float>(x, n);
   else if (act == GN_ACT_LOGSOFTMAX) logsoftmax_inplace<float>(x, n);
-  else for (int i = 0; i < n; i++) x[i] = act_apply<float>(act, x[i]);
+  else for (int i = 0; i < n; i++) x[i] = act_apply<float>(act, x[i], act_default_alpha(act, 0));
 }
-void gno_activation_deriv(int act, float* x, int n) { for (int i = 0; i < n; i++) x[i] = act_deriv<float>(act, x[i]); }
+void gno_activation_deriv(int act, float* x, int n) { for (int i = 0; i < n; i++) x[i] = act_deriv<float>(act, x[i], act_default_alpha(act, 0)); }
 float gno_loss(int kind, const float* p, const float* y, int n) { return loss_forward<float>(kind, p, y, n); }
 void gno_loss_grad(int kind, const float* p, const float* y, float* g, int n) { loss_backward<float>(kind, p, y, g, n); }
 // direct Adam.StepInPlace with explicit exponent t (a fresh optimiser called directly uses t = 1)

@@ -29,7 +29,7 @@ def main(ref):
         meta = json.load(open(os.path.join(d, "metadata.json")))
         out[case] = {k: read(d, k, meta["inputs"][k]["shape"]) for k in ("input", "weights", "biases")}
         out[case]["output"] = read(d, "output", meta["outputs"]["output"]["shape"])
-    for act in ("relu", "sigmoid", "tanh", "softmax", "log_softmax"):
+    for act in ("relu", "sigmoid", "tanh", "softmax", "log_softmax", "leaky_relu", "elu"):   # leaky_relu: slope 0.01; elu: alpha 1
         d = os.path.join(root, "activation_" + act)
         meta = json.load(open(os.path.join(d, "metadata.json")))
         out["activation_" + act] = {"input": read(d, "input", meta["inputs"]["input"]["shape"]),

@@ -45,6 +45,9 @@ CASES = [
     ("cnn_avg", dict(hw=9, c0=1, c1=3, classes=2), 5, 1),
     ("mlp_drop", {}, 24, 1),                                                                                # Dropout: mask from the reference's generator
     ("mlp_drop", dict(in_size=9, hidden=21, classes=3, p=0.6), 7, 1),
+    ("mlp_act", dict(act=D.GELU), 12, 1), ("mlp_act", dict(act=D.SILU), 12, 1),                             # element-wise activations beyond the benchmark configs
+    ("mlp_act", dict(act=D.LEAKY_RELU), 12, 1), ("mlp_act", dict(act=D.LEAKY_RELU, alpha=0.2), 12, 1),
+    ("mlp_act", dict(act=D.ELU), 12, 1), ("mlp_act", dict(act=D.ELU, alpha=0.7), 12, 1),
 ]
 
 

@@ -28,7 +28,8 @@ def test_dense_simple_literal():
     np.testing.assert_allclose(np.array(FX["dense_simple"]["output"]).ravel(), [3.0674953, 0.60423696, 1.6263502], rtol=1e-6)
 
 
-@pytest.mark.parametrize("name,act,tol", [("relu", D.RELU, 1e-5), ("sigmoid", D.SIGMOID, 1e-5), ("tanh", D.TANH, 1e-5)])
+@pytest.mark.parametrize("name,act,tol", [("relu", D.RELU, 1e-5), ("sigmoid", D.SIGMOID, 1e-5), ("tanh", D.TANH, 1e-5),
+                                          ("leaky_relu", D.LEAKY_RELU, 1e-6), ("elu", D.ELU, 1e-6)])
 def test_scalar_activations(oracle, name, act, tol):
     f = FX["activation_" + name]
     np.testing.assert_allclose(oracle.activation(act, np.array(f["input"]).ravel()), np.array(f["output"], np.float32).ravel(), atol=tol, rtol=0)
@@ -128,3 +129,16 @@ def test_avgpool2d_known_answers(oracle):
     y = np.array([[3.5, 5.5, 11.5, 13.5]], np.float32) - 2.0          # MSE gradient 2/n (p - y) = 1 for n = 4
     st.train_batch(x, y, precision=32, step=False)
     assert np.allclose(st.grads[256:], 0.25, atol=1e-7)
+
+
+def test_gelu_silu_follow_their_formulas(oracle):
+    """The reference holds no stored vector for GELU (tanh form, activations.go:241-275) or SiLU (:277-309): the checker is
+    compared with the formulas evaluated in float64, value and derivative (by central differences)."""
+    x = np.linspace(-4, 4, 41).astype(np.float32)
+    xd = x.astype(np.float64)
+    gelu = lambda v: 0.5 * v * (1 + np.tanh(0.7978845608028654 * (v + 0.044715 * v ** 3)))
+    silu = lambda v: v / (1 + np.exp(-v))
+    for act, f in ((D.GELU, gelu), (D.SILU, silu)):
+        np.testing.assert_allclose(oracle.activation(act, x), f(xd), atol=2e-6, rtol=0)
+        h = 1e-5
+        np.testing.assert_allclose(oracle.activation_deriv(act, x), (f(xd + h) - f(xd - h)) / (2 * h), atol=2e-5, rtol=0)
