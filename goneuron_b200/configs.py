@@ -28,6 +28,11 @@ def mlp_ln(in_size=24, hidden=48, norm=16, classes=4):
     return [D.Dense(in_size, hidden, D.TANH), D.LayerNorm(norm), D.Dense(hidden, classes, D.SOFTMAX)], D.CROSS_ENTROPY
 
 
+def mlp_rms(in_size=24, hidden=48, norm=16, classes=4):
+    """Dense -> RMSNorm over consecutive rows of `norm` -> Dense: exercises RMSNorm (rmsnorm.go)."""
+    return [D.Dense(in_size, hidden, D.TANH), D.RMSNorm(norm), D.Dense(hidden, classes, D.SOFTMAX)], D.CROSS_ENTROPY
+
+
 def mlp_act(act=D.GELU, alpha=None, in_size=20, hidden=32, classes=4):
     """Dense(act) -> Dense(act) -> Dense(softmax): exercises the element-wise activations (activations.go)."""
     return [D.Dense(in_size, hidden, act, alpha), D.Dense(hidden, hidden, act, alpha), D.Dense(hidden, classes, D.SOFTMAX)], D.CROSS_ENTROPY
@@ -71,12 +76,13 @@ CONFIGS = {
     "cnn_avg": (cnn_avg, {}, 16, 1e-3),
     "mlp_drop": (mlp_drop, {}, 24, 1e-3),
     "mlp_act": (mlp_act, {}, 12, 1e-3),
+    "mlp_rms": (mlp_rms, {}, 16, 1e-3),
     "mlp_ln": (mlp_ln, {}, 16, 1e-3),
     "lstm": (recurrent, {}, 256, 1e-3),
     "transformer_small": (transformer, dict(vocab=8192, dim=256, seq_len=128, heads=8, ff_dim=1024, n_blocks=4), 64, 3e-4),
     "transformer_large": (transformer, dict(vocab=32000, dim=1024, seq_len=512, heads=16, ff_dim=4096, n_blocks=8), 256, 1e-4),
 }
-SEEDS = {"mlp_act": 1244, "mlp_drop": 1243, "cnn_avg": 1242, "mlp_ln": 1241, "cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
+SEEDS = {"mlp_rms": 1245, "mlp_act": 1244, "mlp_drop": 1243, "cnn_avg": 1242, "mlp_ln": 1241, "cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
 
 
 def build(name, **override):
@@ -129,6 +135,8 @@ def init_params(layers, rng):
             parts += _dense_params(rng, f, d)
         elif k == D.LAYERNORM:
             parts += [np.ones(l.dim, np.float32), np.zeros(l.dim, np.float32)]
+        elif k == D.RMSNORM:
+            parts.append(rng.uniform(0.5, 1.5, size=l.dim).astype(np.float32))
         elif k == D.BATCHNORM2D:
             parts += [rng.uniform(0.5, 1.5, size=l.in_size).astype(np.float32), rng.uniform(-0.5, 0.5, size=l.in_size).astype(np.float32)]
     return np.concatenate(parts) if parts else np.zeros(0, np.float32)

@@ -166,6 +166,9 @@ static int plan_layers(gn_model* m, const gn_layer_desc* layers, int n) {
       case GN_LAYER_LAYERNORM:
         if (cur < 0 || d.dim <= 0 || cur % d.dim) return fail(GN_ERR_INVALID_ARG, "layer %d: LayerNorm width must divide the input size", i);
         l.in_size = l.out_size = cur; l.p_cnt = 2 * (int64_t)d.dim; break;
+      case GN_LAYER_RMSNORM:
+        if (cur < 0 || d.dim <= 0 || cur % d.dim) return fail(GN_ERR_INVALID_ARG, "layer %d: RMSNorm width must divide the input size", i);
+        l.in_size = l.out_size = cur; l.p_cnt = d.dim; l.bn_eps = 1e-5f; if (d.reserved) memcpy(&l.bn_eps, &d.reserved, 4); break;
       default: return fail(GN_ERR_UNSUPPORTED, "layer %d: unknown layer kind %d", i, d.kind);
     }
     if (cur >= 0 && l.in_size != cur) return fail(GN_ERR_INVALID_ARG, "layer %d: input size mismatch: expected %d, got %d", i, l.in_size, cur);
@@ -206,6 +209,7 @@ static int alloc_activations(gn_model* m, int cap) {
         GN_TRY(l.att_m.alloc(nt * d.heads)); GN_TRY(l.att_l.alloc(nt * d.heads)); GN_TRY(l.att_d.alloc(nt * d.heads)); break; }
       case GN_LAYER_CLS_POOLING: GN_TRY(l.out.alloc(c * l.out_size)); break;
       case GN_LAYER_LAYERNORM: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.stat.alloc(2 * c * (l.in_size / d.dim))); break;
+      case GN_LAYER_RMSNORM: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.stat.alloc(c * (l.in_size / d.dim))); break;
       case GN_LAYER_BATCHNORM2D: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.stat.alloc(3 * c * d.in_size)); break;
     }
   }
@@ -374,6 +378,10 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
       case GN_LAYER_LAYERNORM: {
         long rows = (long)B * (l.in_size / d.dim);
         GN_TRY(layernorm_forward(ctx, cur, p, p + d.dim, l.out.p, l.stat.p, l.stat.p + rows, rows, d.dim));
+        cur = l.out.p; break; }
+      case GN_LAYER_RMSNORM: {
+        long rows = (long)B * (l.in_size / d.dim);
+        GN_LAUNCH(ctx, rmsnorm_fwd_kernel, cdiv(rows, 8), 256, 0, cur, p, l.out.p, l.stat.p, rows, d.dim, l.bn_eps);
         cur = l.out.p; break; }
     }
     GN_TRY(check_launch("forward"));
@@ -626,6 +634,14 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         long rows = (long)B * (l.in_size / d.dim);
         GN_TRY(layernorm_backward(m, g, xin, p, l.stat.p, l.stat.p + rows, dx, gr, gr + d.dim, rows, d.dim));
         g = dx; flip ^= 1; break; }
+      case GN_LAYER_RMSNORM: {
+        long rows = (long)B * (l.in_size / d.dim);
+        const int chunks = (int)std::max<long>(1, std::min<long>(rows / 64, 128));
+        float* part; GN_TRY(ensure(m, S_PART2, (size_t)chunks * d.dim, &part));
+        GN_LAUNCH(ctx, rmsnorm_pgrad_partial_kernel, dim3(cdiv(d.dim, 128), chunks), 128, 0, g, xin, (const float*)l.stat.p, rows, d.dim, part);
+        GN_LAUNCH(ctx, rmsnorm_pgrad_final_kernel, cdiv(d.dim, 128), 128, 0, part, chunks, d.dim, gr);
+        if (need_dx) { GN_LAUNCH(ctx, rmsnorm_bwd_kernel, cdiv(rows, 8), 256, 0, g, xin, p, (const float*)l.stat.p, dx, rows, d.dim); g = dx; flip ^= 1; }
+        break; }
     }
     GN_TRY(check_launch("backward"));
     if (ctx->world > 1 && l.p_cnt > 0) {

@@ -302,6 +302,45 @@ __global__ void __launch_bounds__(256) layernorm_pgrad_partial_vec_kernel(const 
   *reinterpret_cast<float4*>(part + ((long)blockIdx.y * 2 + 1) * n + c) = sbet;
 }
 
+// ---------------------------------------------------------------- RMSNorm
+// One warp per row.  reference: rmsnorm.go:222-240 (forward), :301-330 (backward); the row's rms is kept for the backward.
+__global__ void rmsnorm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ gamma, float* __restrict__ y, float* __restrict__ rms_out, long rows, int n, float eps) {
+  long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if (row >= rows) return;
+  int lane = threadIdx.x & 31;
+  const float* xr = x + row * n; float* yr = y + row * n;
+  float ss = 0.f;
+  for (int i = lane; i < n; i += 32) ss += xr[i] * xr[i];
+  const float r = (float)sqrt((double)(warp_sum(ss) / (float)n + eps));
+  for (int i = lane; i < n; i += 32) yr[i] = (xr[i] / r) * gamma[i];
+  if (lane == 0) rms_out[row] = r;
+}
+// dx may alias g.
+__global__ void rmsnorm_bwd_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ rms_in,
+                                   float* dx, long rows, int n) {
+  long row = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); if (row >= rows) return;
+  int lane = threadIdx.x & 31;
+  const float* xr = x + row * n; const float* gr = g + row * n; float* dr = dx + row * n;
+  const float r = rms_in[row], inv = 1.f / r;
+  float s = 0.f;
+  for (int i = lane; i < n; i += 32) s += gr[i] * gamma[i] * xr[i];
+  const float factor = warp_sum(s) / ((float)n * r * r);
+  for (int i = lane; i < n; i += 32) dr[i] = (gamma[i] * inv) * (gr[i] - xr[i] * factor);
+}
+// gGamma[c] partial sums over a chunk of rows: sum_r g * (x / rms)    (rmsnorm.go:322-330); part[chunk][n]
+__global__ void rmsnorm_pgrad_partial_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ rms_in, long rows, int n, float* __restrict__ part) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= n) return;
+  long chunks = gridDim.y, per = (rows + chunks - 1) / chunks, r0 = blockIdx.y * per, r1 = min(rows, r0 + per);
+  float s = 0.f;
+  for (long r = r0; r < r1; r++) s += g[r * n + c] * (x[r * n + c] * (1.f / rms_in[r]));
+  part[(long)blockIdx.y * n + c] = s;
+}
+__global__ void rmsnorm_pgrad_final_kernel(const float* __restrict__ part, int chunks, int n, float* __restrict__ gGamma) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= n) return;
+  float a = 0.f;
+  for (int k = 0; k < chunks; k++) a += part[(long)k * n + c];
+  gGamma[c] += a;
+}
+
 // ---------------------------------------------------------------- Dropout
 // The reference's generator (layer.go:61-75): s <- s * 6364136223846793005 + 1, value = float32(s >> 33) / 2^31, one
 // stream per layer seeded with 42 and consumed element by element, sample by sample (dropout.go:139-152).  Draw k of the

@@ -403,6 +403,38 @@ template <class R> struct Dropout : Layer<R> {
   }
 };
 
+// reference: internal/layer/rmsnorm.go:222-240 (rms = sqrt(mean(x^2) + eps) through float64, y = (x / rms) * gamma),
+// :301-330 (factor = sum(g gamma x) / (n rms^2); dx = (gamma / rms) (g - x factor); dgamma += g x / rms).
+template <class R> struct RMSNorm : Layer<R> {
+  int rows, n; R eps; const R* gamma = nullptr; R* gGamma = nullptr;
+  std::vector<R> saved, rms, out, gradIn;
+  RMSNorm(int rows_, int n_, R eps_) : rows(rows_), n(n_), eps(eps_), saved((size_t)rows_ * n_), rms(rows_), out((size_t)rows_ * n_), gradIn((size_t)rows_ * n_) {}
+  int64_t n_params() const override { return n; }
+  void bind(const R* p, R* g) override { gamma = p; gGamma = g; }
+  int in_size() const override { return rows * n; } int out_size() const override { return rows * n; }
+  const R* forward(const R* x) override {
+    std::copy(x, x + (size_t)rows * n, saved.begin());
+    for (int s = 0; s < rows; s++) {
+      const R* xr = x + (size_t)s * n; R sumSq = 0;
+      for (int i = 0; i < n; i++) sumSq += xr[i] * xr[i];
+      const R r = r_sqrt<R>(sumSq / R(n) + eps); rms[s] = r;
+      for (int i = 0; i < n; i++) out[(size_t)s * n + i] = (xr[i] / r) * gamma[i];
+    }
+    return out.data();
+  }
+  const R* backward(R* grad) override {
+    for (int s = 0; s < rows; s++) {
+      const R* xr = saved.data() + (size_t)s * n; const R* g = grad + (size_t)s * n; const R r = rms[s], inv = R(1) / r;
+      R sum = 0;
+      for (int i = 0; i < n; i++) sum += g[i] * gamma[i] * xr[i];
+      const R factor = sum / (R(n) * r * r);
+      for (int i = 0; i < n; i++) gradIn[(size_t)s * n + i] = (gamma[i] * inv) * (g[i] - xr[i] * factor);
+    }
+    if (gGamma) for (int s = 0; s < rows; s++) { const R inv = R(1) / rms[s]; for (int i = 0; i < n; i++) gGamma[i] += grad[(size_t)s * n + i] * (saved[(size_t)s * n + i] * inv); }
+    return gradIn.data();
+  }
+};
+
 // reference: internal/layer/reshape.go:64-96 (copy forward, identity backward)
 template <class R> struct Flatten : Layer<R> {
   int n; std::vector<R> buf;
@@ -810,6 +842,7 @@ template <class R> struct Net {
           float eps = 1e-5f, mom = 0.1f; if (l.reserved) memcpy(&eps, &l.reserved, 4); if (l.dim) memcpy(&mom, &l.dim, 4);
           p.reset(new BatchNorm2D<R>(l.in_size, l.in_h * l.in_w, (R)eps, (R)mom)); break; }
         case GN_LAYER_LAYERNORM: { if (cur < 0 || l.dim <= 0 || cur % l.dim) { g_err = "LayerNorm shape"; return false; } p.reset(new LayerNorm<R>(cur / l.dim, l.dim)); break; }
+        case GN_LAYER_RMSNORM: { if (cur < 0 || l.dim <= 0 || cur % l.dim) { g_err = "RMSNorm shape"; return false; } float e = 1e-5f; if (l.reserved) memcpy(&e, &l.reserved, 4); p.reset(new RMSNorm<R>(cur / l.dim, l.dim, (R)e)); break; }
         default: g_err = "unknown layer kind"; return false;
       }
       if (cur >= 0 && p->in_size() != cur) { g_err = "layer " + std::to_string(i) + " input size mismatch: expected " + std::to_string(p->in_size()) + " got " + std::to_string(cur); return false; }

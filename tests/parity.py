@@ -37,6 +37,8 @@ def tensor_slices(layers):
             add(f"{i}.blk.ff1.W", d * f); add(f"{i}.blk.ff1.b", f); add(f"{i}.blk.ff2.W", f * d); add(f"{i}.blk.ff2.b", d)
         elif k == D.LAYERNORM:
             add(f"{i}.ln.g", l.dim); add(f"{i}.ln.b", l.dim)
+        elif k == D.RMSNORM:
+            add(f"{i}.rms.g", l.dim)
         elif k == D.BATCHNORM2D:
             add(f"{i}.bn.g", l.in_size); add(f"{i}.bn.b", l.in_size)
     return out

@@ -48,6 +48,7 @@ CASES = [
     ("mlp_act", dict(act=D.GELU), 12, 1), ("mlp_act", dict(act=D.SILU), 12, 1),                             # element-wise activations beyond the benchmark configs
     ("mlp_act", dict(act=D.LEAKY_RELU), 12, 1), ("mlp_act", dict(act=D.LEAKY_RELU, alpha=0.2), 12, 1),
     ("mlp_act", dict(act=D.ELU), 12, 1), ("mlp_act", dict(act=D.ELU, alpha=0.7), 12, 1),
+    ("mlp_rms", {}, 16, 1), ("mlp_rms", dict(in_size=10, hidden=300, norm=100, classes=3), 5, 1),            # RMSNorm
 ]
 
 

@@ -142,3 +142,13 @@ def test_gelu_silu_follow_their_formulas(oracle):
         np.testing.assert_allclose(oracle.activation(act, x), f(xd), atol=2e-6, rtol=0)
         h = 1e-5
         np.testing.assert_allclose(oracle.activation_deriv(act, x), (f(xd + h) - f(xd - h)) / (2 * h), atol=2e-5, rtol=0)
+
+
+def test_rmsnorm_known_answer(oracle):
+    """internal/layer/rmsnorm_test.go:8-28: x = [1, 2, 3, 4], eps = 1e-5, gamma = 1 -> x / sqrt(30 / 4 + 1e-5)."""
+    # (a normalisation layer takes its row count from the layer in front of it: an identity Dense supplies it)
+    params = np.concatenate([np.eye(4, dtype=np.float32).ravel(), np.zeros(4, np.float32), np.ones(4, np.float32)])
+    st = oracle.OracleState([D.Dense(4, 4, D.LINEAR), D.RMSNorm(4, 1e-5)], D.MSE, params)
+    x = np.array([[1, 2, 3, 4]], np.float32)
+    rms = np.float32(np.sqrt(np.float64(np.float32(30.0) / np.float32(4.0) + np.float32(1e-5))))
+    np.testing.assert_allclose(st.forward_batch(x, precision=32).ravel(), x.ravel() / rms, atol=1e-6, rtol=0)
