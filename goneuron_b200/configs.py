@@ -28,6 +28,14 @@ def mlp_ln(in_size=24, hidden=48, norm=16, classes=4):
     return [D.Dense(in_size, hidden, D.TANH), D.LayerNorm(norm), D.Dense(hidden, classes, D.SOFTMAX)], D.CROSS_ENTROPY
 
 
+def cnn1d(length=40, c0=3, c1=8, c2=6, classes=4, act=D.RELU):
+    """Conv1D -> Conv1D (stride 2) -> Flatten -> Dense: exercises Conv1D (conv1d.go), whose backward pass ignores the
+    activation's derivative."""
+    l2 = (length + 2 - 3) // 2 + 1
+    return [D.Conv1D(c0, c1, 5, 1, 2, act, length), D.Conv1D(c1, c2, 3, 2, 1, D.TANH, length), D.Flatten(),
+            D.Dense(c2 * l2, classes, D.SOFTMAX)], D.CROSS_ENTROPY
+
+
 def mlp_rms(in_size=24, hidden=48, norm=16, classes=4):
     """Dense -> RMSNorm over consecutive rows of `norm` -> Dense: exercises RMSNorm (rmsnorm.go)."""
     return [D.Dense(in_size, hidden, D.TANH), D.RMSNorm(norm), D.Dense(hidden, classes, D.SOFTMAX)], D.CROSS_ENTROPY
@@ -77,12 +85,13 @@ CONFIGS = {
     "mlp_drop": (mlp_drop, {}, 24, 1e-3),
     "mlp_act": (mlp_act, {}, 12, 1e-3),
     "mlp_rms": (mlp_rms, {}, 16, 1e-3),
+    "cnn1d": (cnn1d, {}, 12, 1e-3),
     "mlp_ln": (mlp_ln, {}, 16, 1e-3),
     "lstm": (recurrent, {}, 256, 1e-3),
     "transformer_small": (transformer, dict(vocab=8192, dim=256, seq_len=128, heads=8, ff_dim=1024, n_blocks=4), 64, 3e-4),
     "transformer_large": (transformer, dict(vocab=32000, dim=1024, seq_len=512, heads=16, ff_dim=4096, n_blocks=8), 256, 1e-4),
 }
-SEEDS = {"mlp_rms": 1245, "mlp_act": 1244, "mlp_drop": 1243, "cnn_avg": 1242, "mlp_ln": 1241, "cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
+SEEDS = {"cnn1d": 1246, "mlp_rms": 1245, "mlp_act": 1244, "mlp_drop": 1243, "cnn_avg": 1242, "mlp_ln": 1241, "cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
 
 
 def build(name, **override):
@@ -115,6 +124,9 @@ def init_params(layers, rng):
             kk = l.kernel * l.kernel
             parts += [_glorot(rng, (l.out_size, l.in_size, l.kernel, l.kernel), l.in_size * kk, l.out_size * kk).ravel(),
                       np.zeros(l.out_size, np.float32)]
+        elif k == D.CONV1D:
+            parts += [_glorot(rng, (l.out_size, l.in_size, l.kernel), l.in_size * l.kernel, l.out_size * l.kernel).ravel(),
+                      rng.uniform(-0.1, 0.1, size=l.out_size).astype(np.float32)]
         elif k == D.LSTM_UNROLLED:
             H, i = l.out_size, l.in_size
             b = np.zeros(4 * H, np.float32)
@@ -154,6 +166,11 @@ def make_inputs(name, layers, batch, rng):
     elif first.kind == D.LSTM_UNROLLED:
         x = rng.standard_normal((batch, first.seq_len * first.in_size)).astype(np.float32)
         y = rng.standard_normal((batch, last.out_size)).astype(np.float32)
+    elif first.kind == D.CONV1D:
+        x = rng.standard_normal((batch, first.in_size * first.in_w)).astype(np.float32)
+        tgt = rng.integers(0, last.out_size, size=batch)
+        y = np.zeros((batch, last.out_size), np.float32)
+        y[np.arange(batch), tgt] = 1.0
     elif first.kind == D.CONV2D:
         x = rng.standard_normal((batch, first.in_size * first.in_h * first.in_w)).astype(np.float32)
         tgt = rng.integers(0, last.out_size, size=batch)

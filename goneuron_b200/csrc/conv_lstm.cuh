@@ -148,6 +148,59 @@ __global__ void __launch_bounds__(256) conv2d_dgrad_s1_kernel(const float* __res
   }
 }
 
+// ---------------------------------------------------------------- Conv1D
+// Input [B, inC, L], output [B, outC, oL], weights [outC, inC, k].  reference: conv1d.go:178-216 (the sum starts from the
+// bias), :254-288 (the backward pass uses the incoming gradient as it is: no activation derivative).
+struct Conv1Shape { int B, inC, outC, k, s, p, L, oL; };
+__global__ void conv1d_fwd_kernel(const float* __restrict__ x, const float* __restrict__ Wt, const float* __restrict__ bias, float* __restrict__ y,
+                                  Conv1Shape c, int act, float alpha) {
+  long total = (long)c.B * c.outC * c.oL;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int ol = (int)(i % c.oL); long r = i / c.oL; int oc = (int)(r % c.outC); int b = (int)(r / c.outC);
+    const float* xb = x + (long)b * c.inC * c.L; const float* w = Wt + (long)oc * c.inC * c.k;
+    float sum = bias[oc];
+    for (int ic = 0; ic < c.inC; ic++) for (int k = 0; k < c.k; k++) {
+      int pos = ol * c.s + k - c.p;
+      if (pos >= 0 && pos < c.L) sum = fmaf(xb[(long)ic * c.L + pos], __ldg(w + ic * c.k + k), sum);
+    }
+    y[i] = act_fwd(act, sum, alpha);
+  }
+}
+__global__ void conv1d_dgrad_kernel(const float* __restrict__ g, const float* __restrict__ Wt, float* __restrict__ dx, Conv1Shape c) {
+  long total = (long)c.B * c.inC * c.L;
+  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+    int pos = (int)(i % c.L); long r = i / c.L; int ic = (int)(r % c.inC); int b = (int)(r / c.inC);
+    const float* gb = g + (long)b * c.outC * c.oL;
+    float acc = 0.f;
+    for (int oc = 0; oc < c.outC; oc++) for (int k = 0; k < c.k; k++) {
+      int t = pos + c.p - k; if (t < 0 || t % c.s) continue; int ol = t / c.s; if (ol >= c.oL) continue;
+      acc = fmaf(gb[(long)oc * c.oL + ol], __ldg(Wt + ((long)oc * c.inC + ic) * c.k + k), acc);
+    }
+    dx[i] = acc;
+  }
+}
+// One block per weight: dW[oc,ic,k] += sum_{b,ol} g x ; blocks >= nW reduce one bias each.
+__global__ void conv1d_wgrad_kernel(const float* __restrict__ g, const float* __restrict__ x, float* __restrict__ dW, float* __restrict__ db, Conv1Shape c) {
+  __shared__ float red[33];
+  const int nW = c.outC * c.inC * c.k, wi = blockIdx.x; const long span = (long)c.B * c.oL;
+  float s = 0.f;
+  if (wi < nW) {
+    const int k = wi % c.k; int r = wi / c.k; const int ic = r % c.inC, oc = r / c.inC;
+    for (long i = threadIdx.x; i < span; i += blockDim.x) {
+      const int ol = (int)(i % c.oL), b = (int)(i / c.oL), pos = ol * c.s + k - c.p;
+      if (pos < 0 || pos >= c.L) continue;
+      s = fmaf(g[((long)b * c.outC + oc) * c.oL + ol], x[((long)b * c.inC + ic) * c.L + pos], s);
+    }
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) dW[wi] += s;
+  } else {
+    const int oc = wi - nW;
+    for (long i = threadIdx.x; i < span; i += blockDim.x) s += g[((long)(i / c.oL) * c.outC + oc) * c.oL + i % c.oL];
+    s = block_sum(s, red);
+    if (threadIdx.x == 0) db[oc] += s;
+  }
+}
+
 struct PoolShape { int B, C, k, s, p, H, W, oH, oW; };
 // reference: maxpool2d.go:192-221 (init -inf, strict '>', first maximum wins, argmax = flat CHW index)
 __global__ void maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int* __restrict__ arg, PoolShape c) {

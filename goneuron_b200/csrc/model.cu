@@ -126,6 +126,13 @@ static int plan_layers(gn_model* m, const gn_layer_desc* layers, int n) {
         int oh = (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, ow = (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1;
         l.in_size = d.in_size * d.in_h * d.in_w; l.out_size = d.out_size * oh * ow;
         l.p_cnt = (int64_t)d.out_size * d.in_size * d.kernel * d.kernel + d.out_size; break; }
+      case GN_LAYER_CONV1D: {
+        if (d.in_size <= 0 || d.out_size <= 0 || d.kernel <= 0 || d.stride <= 0 || d.padding < 0 || d.in_w <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad Conv1D descriptor", i);
+        if (d.activation < GN_ACT_LINEAR || d.activation > GN_ACT_ELU || d.activation == GN_ACT_SOFTMAX || d.activation == GN_ACT_LOGSOFTMAX)
+          return fail(GN_ERR_UNSUPPORTED, "layer %d: Conv1D activation %d", i, d.activation);
+        const int ol = (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1;
+        if (ol <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: Conv1D output length %d", i, ol);
+        l.in_size = d.in_size * d.in_w; l.out_size = d.out_size * ol; l.p_cnt = (int64_t)d.out_size * d.in_size * d.kernel + d.out_size; break; }
       case GN_LAYER_MAXPOOL2D:
       case GN_LAYER_AVGPOOL2D: {
         if (d.in_size <= 0 || d.kernel <= 0 || d.stride <= 0 || d.padding < 0 || d.in_h <= 0 || d.in_w <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad pooling descriptor", i);
@@ -195,6 +202,7 @@ static int alloc_activations(gn_model* m, int cap) {
       case GN_LAYER_CONV2D: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.z.alloc(c * l.out_size)); break;
       case GN_LAYER_MAXPOOL2D: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.idx.alloc(c * l.out_size)); break;
       case GN_LAYER_AVGPOOL2D: GN_TRY(l.out.alloc(c * l.out_size)); break;
+      case GN_LAYER_CONV1D: GN_TRY(l.out.alloc(c * l.out_size)); break;
       case GN_LAYER_DROPOUT: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.z.alloc(c * l.out_size)); break;      // z = the mask
       case GN_LAYER_FLATTEN: break;
       case GN_LAYER_LSTM_UNROLLED: {
@@ -302,6 +310,11 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
                     (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
         long n = (long)B * l.out_size;
         GN_LAUNCH(ctx, maxpool_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, l.out.p, (int*)l.idx.p, c);
+        cur = l.out.p; break; }
+      case GN_LAYER_CONV1D: {
+        Conv1Shape c{B, d.in_size, d.out_size, d.kernel, d.stride, d.padding, d.in_w, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
+        long n = (long)B * l.out_size;
+        GN_LAUNCH(ctx, conv1d_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, p, p + (long)d.out_size * d.in_size * d.kernel, l.out.p, c, d.activation, act_alpha_of(d.activation, d.reserved));
         cur = l.out.p; break; }
       case GN_LAYER_DROPOUT:
         if (training) {
@@ -602,6 +615,12 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         long n = (long)B * l.out_size;
         GN_LAUNCH(ctx, maxpool_bwd_kernel, ew_grid(ctx, n), 256, 0, g, (const int*)l.idx.p, dx, c);
         g = dx; flip ^= 1; break; }
+      case GN_LAYER_CONV1D: {
+        Conv1Shape c{B, d.in_size, d.out_size, d.kernel, d.stride, d.padding, d.in_w, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
+        const int nW = d.out_size * d.in_size * d.kernel;
+        GN_LAUNCH(ctx, conv1d_wgrad_kernel, nW + d.out_size, 256, 0, g, xin, gr, gr + nW, c);
+        if (need_dx) { long ni = (long)B * l.in_size; GN_LAUNCH(ctx, conv1d_dgrad_kernel, ew_grid(ctx, ni), 256, 0, g, p, dx, c); g = dx; flip ^= 1; }
+        break; }
       case GN_LAYER_DROPOUT:
         if (need_dx) { long n = (long)B * l.in_size; GN_LAUNCH(ctx, dropout_bwd_kernel, ew_grid(ctx, n), 256, 0, g, (const float*)l.z.p, dx, n, l.bn_mom); g = dx; flip ^= 1; }
         break;

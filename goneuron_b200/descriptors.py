@@ -3,7 +3,7 @@ constructors named after the reference's (goneuron/goneuron.go:59-340, internal/
 import ctypes as C
 
 # gn_layer_kind
-DENSE, CONV2D, MAXPOOL2D, FLATTEN, LSTM_UNROLLED, EMBEDDING, POSENC, TRANSFORMER_BLOCK, CLS_POOLING, LAYERNORM, BATCHNORM2D, AVGPOOL2D, DROPOUT, RMSNORM = range(1, 15)
+DENSE, CONV2D, MAXPOOL2D, FLATTEN, LSTM_UNROLLED, EMBEDDING, POSENC, TRANSFORMER_BLOCK, CLS_POOLING, LAYERNORM, BATCHNORM2D, AVGPOOL2D, DROPOUT, RMSNORM, CONV1D = range(1, 16)
 # gn_activation
 LINEAR, RELU, SIGMOID, TANH, SOFTMAX, LOGSOFTMAX, GELU, SILU, LEAKY_RELU, ELU = range(10)
 # gn_loss_kind
@@ -36,6 +36,12 @@ def Conv2D(in_channels, out_channels, kernel, stride, padding, activation, in_h,
     """layer.NewConv2D(inC, outC, k, stride, pad, act) + SetInputDimensions(h, w) -- conv2d.go:60-140, :686-691."""
     return LayerDesc(kind=CONV2D, in_size=in_channels, out_size=out_channels, kernel=kernel, stride=stride,
                      padding=padding, activation=activation, in_h=in_h, in_w=in_w, reserved=0 if alpha is None else _float_bits(alpha))
+
+
+def Conv1D(in_channels, out_channels, kernel, stride, padding, activation, length, alpha=None):
+    """layer.NewConv1D(inC, outC, k, stride, pad, act) on inputs of `length` positions -- conv1d.go:65."""
+    return LayerDesc(kind=CONV1D, in_size=in_channels, out_size=out_channels, kernel=kernel, stride=stride, padding=padding,
+                     activation=activation, in_w=length, reserved=0 if alpha is None else _float_bits(alpha))
 
 
 def RMSNorm(dim, eps=1e-5):

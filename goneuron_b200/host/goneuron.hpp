@@ -18,6 +18,7 @@ inline void check(int rc) { if (rc != GN_OK) throw std::runtime_error(std::strin
 inline gn_layer_desc Dense(int in, int out, gn_activation act = GN_ACT_LINEAR) { gn_layer_desc d{}; d.kind = GN_LAYER_DENSE; d.in_size = in; d.out_size = out; d.activation = act; return d; }
 inline gn_layer_desc Conv2D(int inC, int outC, int k, int stride, int pad, gn_activation act, int h, int w) {
   gn_layer_desc d{}; d.kind = GN_LAYER_CONV2D; d.in_size = inC; d.out_size = outC; d.kernel = k; d.stride = stride; d.padding = pad; d.activation = act; d.in_h = h; d.in_w = w; return d; }
+inline gn_layer_desc Conv1D(int inC, int outC, int k, int stride, int pad, int act, int length) { gn_layer_desc d{}; d.kind = GN_LAYER_CONV1D; d.in_size = inC; d.out_size = outC; d.kernel = k; d.stride = stride; d.padding = pad; d.activation = act; d.in_w = length; return d; }
 inline gn_layer_desc RMSNorm(int dim, float eps = 1e-5f) { gn_layer_desc d{}; d.kind = GN_LAYER_RMSNORM; d.dim = dim; memcpy(&d.reserved, &eps, 4); return d; }
 inline gn_layer_desc Dropout(float p, int inSize) { gn_layer_desc d{}; d.kind = GN_LAYER_DROPOUT; d.in_size = inSize; memcpy(&d.dim, &p, 4); return d; }
 inline gn_layer_desc AvgPool2D(int inC, int k, int stride, int pad, int h, int w) { gn_layer_desc d{}; d.kind = GN_LAYER_AVGPOOL2D; d.in_size = inC; d.kernel = k; d.stride = stride; d.padding = pad; d.in_h = h; d.in_w = w; return d; }

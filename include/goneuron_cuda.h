@@ -56,7 +56,9 @@ typedef enum gn_layer_kind {
   GN_LAYER_AVGPOOL2D = 12,     /* layer.NewAvgPool2D(inC,k,s,p) + input dimensions   internal/layer/avgpool2d.go:43-228, 401-468 */
   GN_LAYER_DROPOUT = 13,       /* layer.NewDropout(p, inSize): in_size = inSize, dim = bits of float p;  internal/layer/dropout.go:36-155, 241-293.
                                   State: two floats = number of random draws consumed so far (low 20 bits | the rest). */
-  GN_LAYER_RMSNORM = 14        /* layer.NewRMSNorm(dim, eps) applied row-wise: dim = dim, reserved = bits of eps (0 selects 1e-5)  rmsnorm.go:157-336 */
+  GN_LAYER_RMSNORM = 14,       /* layer.NewRMSNorm(dim, eps) applied row-wise: dim = dim, reserved = bits of eps (0 selects 1e-5)  rmsnorm.go:157-336 */
+  GN_LAYER_CONV1D = 15         /* layer.NewConv1D(inC,outC,k,stride,pad,act): in_size = inC, out_size = outC, in_w = input length;
+                                  the backward pass does not apply the activation's derivative  conv1d.go:128-288 */
 } gn_layer_kind;
 
 /* Activations (reference: internal/activations/activations.go:22-236,342-352). */

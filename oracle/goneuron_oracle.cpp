@@ -435,6 +435,45 @@ template <class R> struct RMSNorm : Layer<R> {
   }
 };
 
+// reference: internal/layer/conv1d.go:178-216 (sum starts from the bias, then ic-major, k-minor over the taps inside the
+// input), :168-172 (activation), :254-288 (backward: the incoming gradient is used AS IS -- no activation derivative --
+// db += g, dW += g x, dx += g W).  Input [inC, L], output [outC, oL], weights [outC, inC, k] then biases.
+template <class R> struct Conv1D : Layer<R> {
+  int inC, outC, k, s, p, L, oL, act; R alpha = R(0);
+  const R *W = nullptr, *b = nullptr; R *gW = nullptr, *gb = nullptr;
+  std::vector<R> saved, output, gradIn;
+  Conv1D(int inC_, int outC_, int k_, int s_, int p_, int L_, int act_) : inC(inC_), outC(outC_), k(k_), s(s_), p(p_), L(L_), act(act_) {
+    oL = (L + 2 * p - k) / s + 1; saved.resize((size_t)inC * L); output.resize((size_t)outC * oL); gradIn.resize((size_t)inC * L);
+  }
+  int64_t n_params() const override { return (int64_t)outC * inC * k + outC; }
+  void bind(const R* pp, R* g) override { W = pp; b = pp + (size_t)outC * inC * k; gW = g; gb = g ? g + (size_t)outC * inC * k : nullptr; }
+  int in_size() const override { return inC * L; } int out_size() const override { return outC * oL; }
+  const R* forward(const R* x) override {
+    std::copy(x, x + (size_t)inC * L, saved.begin());
+    for (int oc = 0; oc < outC; oc++) for (int ol = 0; ol < oL; ol++) {
+      R sum = b[oc];
+      for (int ic = 0; ic < inC; ic++) for (int kk = 0; kk < k; kk++) {
+        int pos = ol * s + kk - p;
+        if (pos >= 0 && pos < L) sum += x[(size_t)ic * L + pos] * W[((size_t)oc * inC + ic) * k + kk];
+      }
+      output[(size_t)oc * oL + ol] = act_apply<R>(act, sum, alpha);
+    }
+    return output.data();
+  }
+  const R* backward(R* grad) override {
+    std::fill(gradIn.begin(), gradIn.end(), R(0));
+    for (int oc = 0; oc < outC; oc++) for (int ol = 0; ol < oL; ol++) {
+      const R g = grad[(size_t)oc * oL + ol];
+      if (gb) gb[oc] += g;
+      for (int ic = 0; ic < inC; ic++) for (int kk = 0; kk < k; kk++) {
+        int pos = ol * s + kk - p;
+        if (pos >= 0 && pos < L) { if (gW) gW[((size_t)oc * inC + ic) * k + kk] += g * saved[(size_t)ic * L + pos]; gradIn[(size_t)ic * L + pos] += g * W[((size_t)oc * inC + ic) * k + kk]; }
+      }
+    }
+    return gradIn.data();
+  }
+};
+
 // reference: internal/layer/reshape.go:64-96 (copy forward, identity backward)
 template <class R> struct Flatten : Layer<R> {
   int n; std::vector<R> buf;
@@ -826,6 +865,7 @@ template <class R> struct Net {
         case GN_LAYER_CONV2D: { auto* cl = new Conv2D<R>(l.in_size, l.out_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w, l.activation); cl->alpha = (R)act_default_alpha(l.activation, (uint32_t)l.reserved); p.reset(cl); break; }
         case GN_LAYER_MAXPOOL2D: p.reset(new MaxPool2D<R>(l.in_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w)); break;
         case GN_LAYER_DROPOUT: { float pr = 0.f; memcpy(&pr, &l.dim, 4); if (l.in_size <= 0 || pr < 0.f || pr >= 1.f) { g_err = "Dropout descriptor"; return false; } p.reset(new Dropout<R>(l.in_size, pr)); break; }
+        case GN_LAYER_CONV1D: { auto* cl = new Conv1D<R>(l.in_size, l.out_size, l.kernel, l.stride, l.padding, l.in_w, l.activation); cl->alpha = (R)act_default_alpha(l.activation, (uint32_t)l.reserved); p.reset(cl); break; }
         case GN_LAYER_AVGPOOL2D: p.reset(new AvgPool2D<R>(l.in_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w)); break;
         case GN_LAYER_FLATTEN: if (cur < 0) { g_err = "Flatten cannot be first"; return false; } p.reset(new Flatten<R>(cur)); break;
         case GN_LAYER_LSTM_UNROLLED: p.reset(new LSTMUnrolled<R>(l.in_size, l.out_size, l.seq_len, l.return_seq != 0)); net.has_lstm = true; break;

@@ -21,6 +21,8 @@ def tensor_slices(layers):
             add(f"{i}.dense.W", l.in_size * l.out_size); add(f"{i}.dense.b", l.out_size)
         elif k == D.CONV2D:
             add(f"{i}.conv.W", l.out_size * l.in_size * l.kernel ** 2); add(f"{i}.conv.b", l.out_size)
+        elif k == D.CONV1D:
+            add(f"{i}.conv1d.W", l.out_size * l.in_size * l.kernel); add(f"{i}.conv1d.b", l.out_size)
         elif k == D.LSTM_UNROLLED:
             H = l.out_size
             add(f"{i}.lstm.Wx", 4 * H * l.in_size); add(f"{i}.lstm.Wh", 4 * H * H); add(f"{i}.lstm.b", 4 * H)

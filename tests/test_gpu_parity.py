@@ -49,6 +49,7 @@ CASES = [
     ("mlp_act", dict(act=D.LEAKY_RELU), 12, 1), ("mlp_act", dict(act=D.LEAKY_RELU, alpha=0.2), 12, 1),
     ("mlp_act", dict(act=D.ELU), 12, 1), ("mlp_act", dict(act=D.ELU, alpha=0.7), 12, 1),
     ("mlp_rms", {}, 16, 1), ("mlp_rms", dict(in_size=10, hidden=300, norm=100, classes=3), 5, 1),            # RMSNorm
+    ("cnn1d", {}, 12, 1), ("cnn1d", dict(length=17, c0=2, c1=5, c2=3, classes=3, act=D.GELU), 7, 1),           # Conv1D
 ]
 
 

@@ -152,3 +152,11 @@ def test_rmsnorm_known_answer(oracle):
     x = np.array([[1, 2, 3, 4]], np.float32)
     rms = np.float32(np.sqrt(np.float64(np.float32(30.0) / np.float32(4.0) + np.float32(1e-5))))
     np.testing.assert_allclose(st.forward_batch(x, precision=32).ravel(), x.ravel() / rms, atol=1e-6, rtol=0)
+
+
+def test_conv1d_known_answer(oracle):
+    """internal/layer/conv1d_test.go:69-84: one channel, kernel [1, 0, 1], bias 0, padding 1 on [0, 1, 2, 3, 4]:
+    the worked example in the test gives 1 and 2 for the first two positions; the definition gives [1, 2, 4, 6, 3]."""
+    st = oracle.OracleState([D.Conv1D(1, 1, 3, 1, 1, D.LINEAR, 5)], D.MSE, np.array([1, 0, 1, 0], np.float32))
+    out = st.forward_batch(np.array([[0, 1, 2, 3, 4]], np.float32), precision=32)
+    assert np.array_equal(out.ravel(), np.array([1, 2, 4, 6, 3], np.float32))
