@@ -543,7 +543,7 @@ struct AttnTcScratch { DevBuf buf[16]; };
 inline AttnTcScratch& attn_tc_scratch(Ctx* ctx) {
   static thread_local std::vector<std::pair<Ctx*, AttnTcScratch*>> tab;
   for (auto& e : tab) if (e.first == ctx) return *e.second;
-  tab.push_back({ctx, new AttnTcScratch()}); return *tab.back().second;
+  tab.push_back({ctx, ctx->own(new AttnTcScratch())}); return *tab.back().second;
 }
 inline int attn_tc_buf(Ctx* ctx, int i, size_t n, float** out) {
   DevBuf& b = attn_tc_scratch(ctx).buf[i];

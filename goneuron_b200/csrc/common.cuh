@@ -43,6 +43,11 @@ struct Ctx {
   bool tc_ok = false;              // tcgen05 engine usable (driver entry point for tensor maps found)
   void* encode_tiled = nullptr;    // cuTensorMapEncodeTiled
   cudaEvent_t t0 = nullptr, t1 = nullptr;   // gn_timer_start / gn_timer_stop
+  // Scratch objects created on demand for this context (operand planes of the contraction and attention engines): one
+  // per host thread that uses the context, all released by gn_shutdown.
+  std::vector<std::pair<void*, void (*)(void*)>> owned; std::mutex owned_mu;
+  template <class T> T* own(T* p) { std::lock_guard<std::mutex> lk(owned_mu); owned.push_back({p, [](void* q) { delete static_cast<T*>(q); }}); return p; }
+  void release_owned() { std::lock_guard<std::mutex> lk(owned_mu); for (auto& e : owned) e.second(e.first); owned.clear(); }
 };
 
 inline unsigned cdiv(long a, long b) { return (unsigned)((a + b - 1) / b); }

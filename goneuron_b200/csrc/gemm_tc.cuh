@@ -376,7 +376,7 @@ struct TcPlanes {
 inline int tc_ldp(int K) { return ((K + 7) / 8) * 8; }              // plane row stride: a multiple of 16 bytes for TMA in bf16 too
 
 struct TcScratch { DevBuf a_hi, a_lo, b_hi, b_lo; const float* last_a = nullptr; int last_m = 0, last_k = 0; long last_ld = 0; };
-inline TcScratch& tc_scratch(Ctx* ctx) { static thread_local std::vector<std::pair<Ctx*, TcScratch*>> tab; for (auto& e : tab) if (e.first == ctx) return *e.second; tab.push_back({ctx, new TcScratch()}); return *tab.back().second; }
+inline TcScratch& tc_scratch(Ctx* ctx) { static thread_local std::vector<std::pair<Ctx*, TcScratch*>> tab; for (auto& e : tab) if (e.first == ctx) return *e.second; tab.push_back({ctx, ctx->own(new TcScratch())}); return *tab.back().second; }
 
 inline void tc_init(Ctx* ctx) {
   ctx->tc_ok = false;

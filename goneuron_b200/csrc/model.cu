@@ -793,6 +793,7 @@ int gn_shutdown(gn_ctx* ctx) {
   if (ctx->c.comm && ctx->c.nccl) ctx->c.nccl->CommDestroy(ctx->c.comm);
   for (auto& e : ctx->c.ev_pool) { cudaEventDestroy(e.first); cudaEventDestroy(e.second); }
   ctx->c.ev_pool.clear();
+  ctx->c.release_owned();                               // operand-plane scratch of the contraction and attention engines
   if (ctx->c.d_status) cudaFree(ctx->c.d_status);
   if (ctx->c.t0) { cudaEventDestroy(ctx->c.t0); cudaEventDestroy(ctx->c.t1); ctx->c.t0 = ctx->c.t1 = nullptr; }
   if (ctx->c.stream) cudaStreamDestroy(ctx->c.stream);
