@@ -11,7 +11,7 @@ UNIQUE_ID_BYTES = 128
 
 # every symbol include/goneuron_cuda.h declares
 EXPORTS = [
-    "gn_init", "gn_get_unique_id", "gn_init_rank", "gn_shutdown", "gn_ctx_world_size", "gn_synchronize", "gn_timer_start", "gn_timer_stop", "gn_last_error",
+    "gn_init", "gn_get_unique_id", "gn_init_rank", "gn_shutdown", "gn_ctx_world_size", "gn_ctx_set_spin_limit", "gn_synchronize", "gn_timer_start", "gn_timer_stop", "gn_last_error",
     "gn_model_create", "gn_model_destroy", "gn_model_param_count", "gn_model_in_size", "gn_model_out_size",
     "gn_model_set_params", "gn_model_get_params", "gn_model_get_grads", "gn_adam_set", "gn_adam_get_state",
     "gn_adam_set_state", "gn_train_batch", "gn_train_batch_device", "gn_forward_batch", "gn_device_alloc",
@@ -50,6 +50,7 @@ def load():
     L.gn_shutdown.argtypes = [vp]
     L.gn_ctx_world_size.argtypes = [vp, C.POINTER(C.c_int), C.POINTER(C.c_int)]
     L.gn_synchronize.argtypes = [vp]
+    L.gn_ctx_set_spin_limit.argtypes = [vp, C.c_uint]
     L.gn_timer_start.argtypes = [vp]
     L.gn_timer_stop.argtypes = [vp, f32p]
     L.gn_model_create.argtypes = [vp, C.POINTER(LayerDesc), C.c_int, C.c_int, C.c_int, C.POINTER(vp)]

@@ -541,9 +541,8 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
 // ------------------------------------------------------------------ host side
 struct AttnTcScratch { DevBuf buf[16]; };
 inline AttnTcScratch& attn_tc_scratch(Ctx* ctx) {
-  static thread_local std::vector<std::pair<Ctx*, AttnTcScratch*>> tab;
-  for (auto& e : tab) if (e.first == ctx) return *e.second;
-  tab.push_back({ctx, ctx->own(new AttnTcScratch())}); return *tab.back().second;
+  if (!ctx->attn_scratch) ctx->attn_scratch = ctx->own(new AttnTcScratch());
+  return *static_cast<AttnTcScratch*>(ctx->attn_scratch);
 }
 inline int attn_tc_buf(Ctx* ctx, int i, size_t n, float** out) {
   DevBuf& b = attn_tc_scratch(ctx).buf[i];

@@ -42,9 +42,14 @@ struct Ctx {
   int* d_status = nullptr;         // device word set by kernels whose bounded waits gave up
   bool tc_ok = false;              // tcgen05 engine usable (driver entry point for tensor maps found)
   void* encode_tiled = nullptr;    // cuTensorMapEncodeTiled
+  unsigned spin_limit = 1u << 24;  // polls per bounded device-side wait (gn_ctx_set_spin_limit)
+  int tc_force_bn = 0, tc_kslice = 0;   // experiment switches of the contraction engine (GONEURON_CUDA_TC_BN / _KSLICE); 0 = automatic
+  void* tc_scratch = nullptr;      // operand planes of the contraction engine (TcScratch, owned)
+  void* attn_scratch = nullptr;    // operand planes of the tcgen05 attention kernels (AttnTcScratch, owned)
+  std::mutex run_mu;               // serialises every entry point that launches work on this context (they share the scratch above)
   cudaEvent_t t0 = nullptr, t1 = nullptr;   // gn_timer_start / gn_timer_stop
-  // Scratch objects created on demand for this context (operand planes of the contraction and attention engines): one
-  // per host thread that uses the context, all released by gn_shutdown.
+  // Scratch objects created on demand for this context (operand planes of the contraction and attention engines),
+  // all released by gn_shutdown.
   std::vector<std::pair<void*, void (*)(void*)>> owned; std::mutex owned_mu;
   template <class T> T* own(T* p) { std::lock_guard<std::mutex> lk(owned_mu); owned.push_back({p, [](void* q) { delete static_cast<T*>(q); }}); return p; }
   void release_owned() { std::lock_guard<std::mutex> lk(owned_mu); for (auto& e : owned) e.second(e.first); owned.clear(); }

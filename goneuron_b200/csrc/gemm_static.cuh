@@ -9,7 +9,10 @@
 //
 // Cost and limit: GN_STATIC_SCRATCH_BYTES (16 MiB) of device memory are held on every GPU that loads the
 // library, from load until the process exits, whether or not this entry point is ever called.  A problem
-// needs 2 * (M + N) * roundup8(K) floats of it; larger problems are rejected with GN_ERR_INVALID_ARG.
+// needs (M + N) * (roundup8(K) + 1) floats of it (two fp16 planes per operand element and one scale per operand row);
+// larger problems are
+// rejected with GN_ERR_INVALID_ARG.  Long contractions are cut into accumulator runs exactly as in the regular
+// path (more launches, no allocation).
 //
 // Sharing: there is ONE array per GPU.  Every call on that GPU uses it and leaves its operand planes behind;
 // each call rewrites all of the part it reads (padding columns included), so nothing needs clearing
@@ -52,20 +55,21 @@ extern "C" int gn_op_gemm_nt_static(gn_ctx* ctx, int M, int N, int K, const floa
   Ctx* c = &ctx->c;
   if (!c->tc_ok) return fail(GN_ERR_UNSUPPORTED, "the tensor-core engine is not available on this context");
   const long ldp = tc_ldp(K);
-  const long need = 2 * ((long)M + N) * ldp;
+  const long need = ((long)M + N) * (ldp + 1);
   if (need > GN_STATIC_SCRATCH_FLOATS)
-    return fail(GN_ERR_INVALID_ARG, "op_gemm_nt_static: M=%d N=%d K=%d needs %ld scratch floats, the fixed array holds %ld (2*(M+N)*roundup8(K) must not exceed it)",
+    return fail(GN_ERR_INVALID_ARG, "op_gemm_nt_static: M=%d N=%d K=%d needs %ld scratch floats, the fixed array holds %ld ((M+N)*(roundup8(K)+1) must not exceed it)",
                 M, N, K, need, GN_STATIC_SCRATCH_FLOATS);
+  std::lock_guard<std::mutex> lk(c->run_mu);
   GN_CUDA(cudaSetDevice(c->device));
   float* base = nullptr; GN_TRY(static_scratch_ptr(c->device, &base));
-  float *a_hi = base, *a_lo = a_hi + (long)M * ldp, *b_hi = a_lo + (long)M * ldp, *b_lo = b_hi + (long)N * ldp;
-  TcPlanes PA{a_hi, a_lo, M, K, (int)ldp, 1}, PB{b_hi, b_lo, N, K, (int)ldp, 1};
-  GN_TRY(tc_split(c, TcSrc{A_dev, (long)K, 1, 0, 0, 1}, PA));
-  GN_TRY(tc_split(c, TcSrc{B_dev, (long)K, 1, 0, 0, 1}, PB));
+  float* scales = base + ((long)M + N) * ldp;          // [M] for A, then [N] for B; (M + N) * ldp is a multiple of 8 floats, so B's start is 16-byte aligned when M % 4 == 0
+  float* sb = scales + (((long)M + 3) & ~3L);
+  if (sb + N > base + GN_STATIC_SCRATCH_FLOATS) return fail(GN_ERR_INVALID_ARG, "op_gemm_nt_static: M=%d N=%d K=%d does not fit the fixed array", M, N, K);
+  BfPlanes PA{reinterpret_cast<__half*>(base), scales, M, K, (int)ldp, 1}, PB{reinterpret_cast<__half*>(base + (long)M * ldp), sb, N, K, (int)ldp, 1};
+  GN_TRY(tc_split(c, TcSrc{A_dev, (long)K, 1, 0, 0, 1}, PA, nullptr));
+  GN_TRY(tc_split(c, TcSrc{B_dev, (long)K, 1, 0, 0, 1}, PB, nullptr));
   TcParams ep{C_dev, (long)N, 0, 0, bias_dev, nullptr, 0, 0, 0, GN_ACT_LINEAR, M, N, K, 1, 0, c->d_status, nullptr, 0, 1};
-  GN_TRY(tc_launch(c, PA, PB, ep));
+  GN_TRY(tc_run(c, PA, PB, ep));
   GN_CUDA(cudaStreamSynchronize(c->stream));
-  int st = 0; GN_CUDA(copy_d2h(c, &st, c->d_status, sizeof(int)));
-  if (st != 0) { cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream); cudaStreamSynchronize(c->stream); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
-  return GN_OK;
+  return check_status_word(c);
 }

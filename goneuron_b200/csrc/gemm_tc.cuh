@@ -2,36 +2,46 @@
 //
 //   C[M,N] = act( A[M,K] * B[N,K]^T + bias[N] + R[M,N] )
 //
-// Split-operand scheme.  Every fp32 operand x is written as hi = tf32(x) and lo = x - hi (exact in fp32), and
-//     a*b  =  hi_a*hi_b  +  lo_a*b  +  a*lo_b      (the dropped lo*lo term is ~2^-22 relative).
-// The large term runs as one TF32 MMA (both factors are exact TF32 values, fp32 accumulation).  The two cross
-// terms are about 2^-11 of the product, so their factors only need a few bits: they run as BF16 MMAs on
-// lo (rounded to bf16) and on a bf16 copy of the other operand, which contributes a relative error of about
-// 2^-8 * 2^-11 = 2^-19 per product -- the size of the fp32 rounding noise of a long sum -- at half the tensor
-// time of a TF32 MMA.  Per 32 contraction indices that is 4 TF32 + 4 BF16 instructions of the same size
-// instead of the 12 TF32 instructions of the plain 3xTF32 scheme (which this file used first; measured
-// 228-238 TFLOP/s fp32-equivalent, i.e. at the ceiling of one sixth of the bf16 rate).
-// The operand planes (hi as fp32, the bf16 copy, lo as bf16: 8 bytes per element) are written by a
-// memory-bound pass (split_rows_kernel / split_cols_kernel), K-major, so the contraction kernel itself is a
-// pure TMA -> shared memory -> tcgen05.mma pipeline:
+// Split-operand scheme (three half-precision products per fp32 product).  Every operand row (one output row's or
+// output column's K-vector) is first multiplied by a power of two s that brings its largest magnitude into
+// [2^14, 2^15), and each scaled element is written as
+//     x s = x0 + x1 + r,   x0 = fp16(x s),  x1 = fp16(x s - x0),  |r| <= 2^-22 |x s| + 2^-25
+// (fp16 carries 11 significant bits, so two planes hold 22 of the 24 bits of an fp32 mantissa; elements far below the
+// row's maximum land in fp16's subnormal range, where the absolute error 2^-25 is 2^-39 of the row's maximum).  Then
+//     a*b  =  ( a0*b0  +  a0*b1 + a1*b0 ) / (s_a s_b)      (dropped: a1*b1, r_a*b, a*r_b -- each about 2^-22 |a b|).
+// All three terms are tcgen05.mma.kind::f16 instructions with fp32 accumulation in tensor memory; a product of two
+// fp16 numbers is exact in fp32, and the division by the two powers of two in the epilogue is exact.  Against the
+// other ways of reaching fp32 accuracy on these tensor cores -- three TF32 instructions (6 units of tensor time per
+// product, 8-byte operand planes), or one TF32 and two BF16 instructions (4 units, 8 bytes; what this file did
+// before) -- this costs 3 units and the operand planes are 4 bytes per element, the size of the fp32 source.  That
+// halves what the kernel pulls through L2 and shared memory, which matters because the kernel is bound by
+// shared-memory bandwidth, not by the tensor pipe: with 128 x 128 tiles every MMA re-reads both operands from shared
+// memory (8 KB per 64 tensor cycles = the full 128 B/clk) while TMA writes the next stage into the same memory.  The
+// large-problem variant therefore uses 128 x 256 tiles (12 KB per 128 tensor cycles).
 //
-//   warp 0   TMA producer: 6 tiled bulk copies per stage (hi: 128-byte swizzle; bf16 planes: 64-byte
-//            swizzle; 3-D maps, third coordinate = problem index of a batch)
-//   warp 1   allocates TMEM, issues tcgen05.mma.kind::tf32 / kind::f16 (one elected lane), commits to mbarriers
-//   warps 2-5  epilogue: tcgen05.ld of the accumulators, bias / residual / ReLU / gate, one output row
+// The operand planes (K-major fp16, row stride a multiple of 8 elements) and the per-row inverse scales are written
+// by a memory-bound pass (split2_rows_kernel / split2_cols_kernel); the contraction kernel itself is a pure
+// TMA -> shared memory -> tcgen05.mma pipeline:
+//
+//   warp 0   TMA producer: 4 tiled bulk copies per stage (64-byte rows, 64-byte swizzle; 3-D maps, third
+//            coordinate = problem index of a batch)
+//   warp 1   allocates TMEM, issues the MMAs (one elected lane), commits to mbarriers
+//   warps 2-5  epilogue: tcgen05.ld of the accumulators, scales / bias / residual / ReLU / gate, one output row
 //              per thread with 16-byte stores
 //
-// Persistent: one CTA per SM walks 128 x BN output tiles (BN = 128, or 64 for narrow outputs), 3 stages of
-// 64 KB, and TMEM holds two accumulator slots so the epilogue of tile i runs under the mainloop of tile i+1.
-// Each slot has two accumulators: the hi*hi products go to one, the small cross terms to the other, and the
-// epilogue adds them.  The tensor core truncates when it aligns a product sum to the running accumulator, an
-// error proportional to the accumulator's magnitude per MMA; keeping the cross terms out of the large
-// accumulator keeps the number of such truncations on it at one per 8 contraction indices.
-// Every mbarrier wait is bounded; a wait that gives up sets the context's status word and the kernel
-// still runs to its end (TMEM is always released).
+// Persistent: one CTA per SM walks 128 x BN output tiles.  TMEM holds two accumulator slots, so the epilogue
+// of tile i runs under the mainloop of tile i+1.  The tensor core truncates when it adds a group of products
+// to the accumulator, an error proportional to the accumulator's magnitude per MMA instruction.  With BN = 64
+// or 128 each slot therefore has two accumulators -- the a0*b0 products go to one, the small cross terms to
+// the other, and the epilogue adds them -- and with BN = 256 (one accumulator per slot, 512 columns in all) the
+// host cuts long contractions into shorter accumulator runs instead.
+// Every mbarrier wait is bounded.  A wait that gives up sets the context's status word and a flag in shared
+// memory; every role of the CTA then leaves its loops without issuing further copies or MMAs, the producer
+// waits (bounded) for its copies in flight, the MMA role for its instructions in flight, and TMEM is released.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cstdlib>
 #include "common.cuh"
 #include "gemm_simt.cuh"
@@ -39,19 +49,21 @@
 namespace gn {
 
 constexpr int TC_BM = 128, TC_THREADS = 192;
-constexpr unsigned TC_SPIN_LIMIT = 1u << 24;
-constexpr int TC_KSLICE = 4096;     // longest accumulator run, see gemm_tc()
+constexpr unsigned TC_SPIN_LIMIT = 1u << 24;    // default number of polls of one wait (Ctx::spin_limit overrides it)
+constexpr unsigned TC_DRAIN_LIMIT = 1u << 20;   // polls spent waiting for own work in flight after a wait gave up
 constexpr int TC_FLAG_VEC = 4096;   // epilogue may use 16-byte accesses (set by the host when every pointer and stride allows it)
-// One stage = 32 contraction indices of both operands: hi plane (fp32, 128-byte rows) + bf16 copy + bf16 lo (64-byte rows).
+// One stage = 32 contraction indices of both operands: two fp16 planes each, 64-byte rows.
 constexpr int TC_BK = 32;
 template <int BN> struct TcCfg {
-  static constexpr int A_HI = TC_BM * TC_BK * 4, A_BF = TC_BM * TC_BK * 2;       // 16 KB, 8 KB
-  static constexpr int B_HI = BN * TC_BK * 4, B_BF = BN * TC_BK * 2;
-  static constexpr int A_BYTES = A_HI + 2 * A_BF, B_BYTES = B_HI + 2 * B_BF;
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES;
+  static constexpr int A_PL = TC_BM * TC_BK * 2, B_PL = BN * TC_BK * 2;           // one plane of a stage: 8 KB, BN * 64 B
+  static constexpr int STAGE_BYTES = 2 * A_PL + 2 * B_PL;
+  static constexpr int STAGES = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
-  static_assert(2 * STAGES + 5 <= 32, "barrier area");
+  static constexpr bool MERGED = BN > 128;                                        // one accumulator per slot
+  static constexpr int SLOT_COLS = MERGED ? BN : 2 * BN;
+  static constexpr int TMEM_COLS = 2 * SLOT_COLS;
+  static_assert(2 * STAGES + 6 <= 30, "barrier area");
+  static_assert(TMEM_COLS <= 512, "accumulator slots must fit the 512 TMEM columns");
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -60,12 +72,25 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) { asm vo
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Bounded wait: returns false when it gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (unsigned it = 0; it < TC_SPIN_LIMIT; it++) {
+// Bounded wait: returns false when it gave up -- after `limit` polls, or as soon as `*abort_flag` (a word in
+// shared memory that a role of this CTA sets when one of its own waits gave up) is non-zero.  A poll is
+// mbarrier.try_wait, which may suspend the thread for a while by itself; limits below 4096 poll with the
+// non-suspending mbarrier.test_wait instead, so that a small limit really is a short time (the failure-detection
+// tests rely on that to make a wait run out).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned limit = TC_SPIN_LIMIT, const volatile int* abort_flag = nullptr) {
+  if (limit < 4096u) {
+    for (unsigned it = 0; it < limit; it++) {
+      uint32_t done;
+      asm volatile("{\n.reg .pred p;\nmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+      if (done) return true;
+    }
+    return false;
+  }
+  for (unsigned it = 0; it < limit; it++) {
     uint32_t done;
     asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}" : "=r"(done) : "r"(bar), "r"(parity) : "memory");
     if (done) return true;
+    if (abort_flag && (it & 63) == 63 && *abort_flag) return false;
   }
   return false;
 }
@@ -104,6 +129,10 @@ __host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
+// kind::f16 with A = B = fp16 (format code 0), D = f32.
+__host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N) {
+  return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
 
 __device__ __forceinline__ float tf32_round(float x) { uint32_t u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x)); return __uint_as_float(u); }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -115,19 +144,22 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "r"(taddr) : "memory");
 }
 
-// Output side of one launch.  Batched problems: problem z = blockIdx.z -> (z / batch2, z % batch2) selects the
+
+// Output side of one launch.  Batched problems: problem z -> (z / batch2, z % batch2) selects the
 // output (and residual) sub-matrix; the operand planes of problem z are slice z of the 3-D tensor maps.
 struct TcParams {
   float* C; long ldc, c_b1, c_b2; const float* bias; const float* R; long ldr, r_b1, r_b2;
   int act, M, N, K, batch2, flags; int* status;
   const float* mask; long mask_ld; int mask_group;    // optional gate, see GemmDesc::mask
+  const float* isa = nullptr; const float* isb = nullptr;   // inverse row scales of the operand planes: [nbatch][M], [nbatch][N]
+  unsigned spin_limit = TC_SPIN_LIMIT;                // polls per wait before the kernel gives up
 };
 
 // Epilogue of one output tile, executed by one warp for its TMEM lane quadrant: one output row per thread
 // (TMEM lane = row), 32 consecutive columns per tcgen05.ld, written as 8 float4.  Bias, residual and gate values
 // of a chunk are fetched before the TMEM wait so that their latency overlaps.  `acc_main` / `acc_cross` are the
-// TMEM column offsets of the two accumulators of this tile.
-template <int BN>
+// TMEM column offsets of the two accumulators of this tile (MERGED: there is only acc_main).
+template <int BN, bool MERGED>
 __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tmem_base, uint32_t acc_main, uint32_t acc_cross,
                                                  int m0, int n0, int z, int quad, int lane, int nkb) {
     const int z1 = z / ep.batch2, z2 = z % ep.batch2;
@@ -139,20 +171,27 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
     const float* Mrow = (ep.mask && row_ok) ? ep.mask + (long)(row / ep.mask_group) * ep.mask_ld : nullptr;
     float* Crow = C + (long)row * ep.ldc;
     const bool vec = (ep.flags & TC_FLAG_VEC) != 0;
+    const float isa = row_ok ? ep.isa[(long)z * ep.M + row] : 1.f;       // 1 / (scale of this output row's A vector), a power of two
+    const float* isb = ep.isb + (long)z * ep.N;
     for (int c = 0; c < BN / 32; c++) {
       const int col0 = n0 + c * 32;
       if (col0 >= ep.N) break;
-      uint32_t r[32], q[32];
+      uint32_t r[32], q[MERGED ? 1 : 32];
       if (nkb > 0) {
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
         tmem_ld32(taddr + acc_main, r);
-        tmem_ld32(taddr + acc_cross, q);
+        if constexpr (!MERGED) tmem_ld32(taddr + acc_cross, q);
       }
+      auto acc = [&](int j) -> float {
+        if (nkb <= 0) return 0.f;
+        if constexpr (MERGED) return __uint_as_float(r[j]); else return __uint_as_float(r[j]) + __uint_as_float(q[j]);
+      };
       if (vec) {
-        float4 rv[8], mv[8];
+        float4 rv[8], mv[8], sv[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) {
           const bool in = col0 + 4 * j < ep.N;
+          sv[j] = in ? __ldg(reinterpret_cast<const float4*>(isb + col0 + 4 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
           rv[j] = (Rrow && in) ? *reinterpret_cast<const float4*>(Rrow + col0 + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
           mv[j] = (Mrow && in) ? *reinterpret_cast<const float4*>(Mrow + col0 + 4 * j) : make_float4(1.f, 1.f, 1.f, 1.f);
         }
@@ -162,10 +201,8 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
           if (!row_ok || col0 + 4 * j >= ep.N) continue;
           float4 bv = ep.bias ? __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + 4 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
           float4 v;
-          v.x = (nkb > 0 ? __uint_as_float(r[4 * j]) + __uint_as_float(q[4 * j]) : 0.f) + bv.x + rv[j].x;
-          v.y = (nkb > 0 ? __uint_as_float(r[4 * j + 1]) + __uint_as_float(q[4 * j + 1]) : 0.f) + bv.y + rv[j].y;
-          v.z = (nkb > 0 ? __uint_as_float(r[4 * j + 2]) + __uint_as_float(q[4 * j + 2]) : 0.f) + bv.z + rv[j].z;
-          v.w = (nkb > 0 ? __uint_as_float(r[4 * j + 3]) + __uint_as_float(q[4 * j + 3]) : 0.f) + bv.w + rv[j].w;
+          v.x = acc(4 * j) * isa * sv[j].x + bv.x + rv[j].x; v.y = acc(4 * j + 1) * isa * sv[j].y + bv.y + rv[j].y;
+          v.z = acc(4 * j + 2) * isa * sv[j].z + bv.z + rv[j].z; v.w = acc(4 * j + 3) * isa * sv[j].w + bv.w + rv[j].w;
           if (ep.act == GN_ACT_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
           if (!(mv[j].x > 0.f)) v.x = 0.f; if (!(mv[j].y > 0.f)) v.y = 0.f; if (!(mv[j].z > 0.f)) v.z = 0.f; if (!(mv[j].w > 0.f)) v.w = 0.f;
           *reinterpret_cast<float4*>(Crow + col0 + 4 * j) = v;
@@ -176,7 +213,7 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
         for (int j = 0; j < 32; j++) {
           const int col = col0 + j;
           if (!row_ok || col >= ep.N) continue;
-          float v = nkb > 0 ? __uint_as_float(r[j]) + __uint_as_float(q[j]) : 0.f;
+          float v = acc(j) * isa * isb[col];
           if (ep.bias) v += ep.bias[col];
           if (Rrow) v += Rrow[col];
           if (ep.act == GN_ACT_RELU) v = fmaxf(v, 0.f);
@@ -189,27 +226,32 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 
-template <int BN, int NSLOTS>
+template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_constant__ CUtensorMap mapAxb, const __grid_constant__ CUtensorMap mapAlo,
-                       const __grid_constant__ CUtensorMap mapBhi, const __grid_constant__ CUtensorMap mapBxb, const __grid_constant__ CUtensorMap mapBlo,
+gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
+                       const __grid_constant__ CUtensorMap mapB0, const __grid_constant__ CUtensorMap mapB1,
                        TcParams ep, int tiles_m, int tiles_n, int total_tiles) {
   using Cfg = TcCfg<BN>;
-  static_assert(NSLOTS * 2 * BN <= 512 && (NSLOTS == 1 || NSLOTS == 2), "accumulator slots must fit the 512 TMEM columns");
   constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, BK = TC_BK;
-  constexpr uint32_t TMEM_COLS = NSLOTS * 2 * BN;
+  constexpr bool MERGED = Cfg::MERGED;
+  constexpr uint32_t TMEM_COLS = Cfg::TMEM_COLS, SLOT_COLS = Cfg::SLOT_COLS;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);       // full[S], empty[S], tfull[2], tempty[2]
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);       // full[S], empty[S], tfull[2], tempty[2], drain
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 5);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);       // set by the first role whose wait gave up
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
+  const uint32_t drain = smem_u32(bars + 2 * STAGES + 4);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // stage layout: A_hi | A_xb | A_lo | B_hi | B_xb | B_lo
-  constexpr uint32_t OFF_AXB = Cfg::A_HI, OFF_ALO = Cfg::A_HI + Cfg::A_BF, OFF_BHI = Cfg::A_BYTES, OFF_BXB = OFF_BHI + Cfg::B_HI, OFF_BLO = OFF_BXB + Cfg::B_BF;
+  // stage layout: A plane 0 | A plane 1 | B plane 0 | B plane 1
+  constexpr uint32_t OFF_A1 = Cfg::A_PL, OFF_B0 = 2 * Cfg::A_PL, OFF_B1 = OFF_B0 + Cfg::B_PL;
+  const unsigned limit = ep.spin_limit;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+    mbar_init(drain, 1);
+    *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -232,72 +274,80 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_
     kb0 = kbeg / BK; nkb = (kend - kbeg + BK - 1) / BK;
     return true;
   };
+  // a wait gave up: record which role, and tell the other roles of this CTA to stop
+  auto give_up = [&](int code) { atomicExch(ep.status, code); *abort_flag = 1; __threadfence_block(); };
 
+  uint32_t issued = 0;          // producer thread: stages whose copies it has started
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true; uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
         for (int i = 0; i < nkb; i++, it++) {
           const uint32_t s = it % STAGES, use = it / STAGES; const int kc = (kb0 + i) * BK;
-          if (use > 0) ok &= mbar_wait(empty0 + 8 * s, (use - 1) & 1);
+          if (use > 0 && !mbar_wait(empty0 + 8 * s, (use - 1) & 1, limit, abort_flag)) { ok = false; break; }
           const uint32_t base = smem_u32(smem + s * STAGE_BYTES), bar = full0 + 8 * s;
           mbar_expect_tx(bar, STAGE_BYTES);
-          tma_load_3d(base, &mapAhi, kc, m0, z, bar);
-          tma_load_3d(base + OFF_AXB, &mapAxb, kc, m0, z, bar);
-          tma_load_3d(base + OFF_ALO, &mapAlo, kc, m0, z, bar);
-          tma_load_3d(base + OFF_BHI, &mapBhi, kc, n0, z, bar);
-          tma_load_3d(base + OFF_BXB, &mapBxb, kc, n0, z, bar);
-          tma_load_3d(base + OFF_BLO, &mapBlo, kc, n0, z, bar);
+          tma_load_3d(base, &mapA0, kc, m0, z, bar);
+          tma_load_3d(base + OFF_A1, &mapA1, kc, m0, z, bar);
+          tma_load_3d(base + OFF_B0, &mapB0, kc, n0, z, bar);
+          tma_load_3d(base + OFF_B1, &mapB1, kc, n0, z, bar);
         }
       }
-      if (!ok) atomicExch(ep.status, 1);
+      if (!ok && !*abort_flag) give_up(1);
+      issued = it;
     }
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true; uint32_t it = 0, lt = 0;
-      constexpr uint32_t idesc = make_idesc(TC_BM, BN), idesc_bf = make_idesc_bf16(TC_BM, BN);
-      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      constexpr uint32_t idesc = make_idesc_f16(TC_BM, BN);
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
-        const uint32_t slot = NSLOTS == 2 ? (lt & 1) : 0, u = NSLOTS == 2 ? (lt >> 1) : lt; lt++;
-        ok &= mbar_wait(tempty0 + 8 * slot, (u & 1) ^ 1);          // slot drained by the epilogue (passes at once the first time)
+        const uint32_t slot = lt & 1, u = lt >> 1; lt++;
+        if (!mbar_wait(tempty0 + 8 * slot, (u & 1) ^ 1, limit, abort_flag)) { ok = false; break; }     // slot drained by the epilogue (passes at once the first time)
         tc_fence_after();
-        const uint32_t acc_main = tmem_base + slot * 2 * BN, acc_cross = acc_main + BN;
+        const uint32_t acc_main = tmem_base + slot * SLOT_COLS, acc_cross = MERGED ? acc_main : acc_main + BN;
         for (int i = 0; i < nkb; i++, it++) {
           const uint32_t s = it % STAGES, use = it / STAGES;
-          ok &= mbar_wait(full0 + 8 * s, use & 1);
+          if (!mbar_wait(full0 + 8 * s, use & 1, limit, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t base = smem_u32(smem + s * STAGE_BYTES);
-          const uint64_t ahi = make_desc<32>(base), axb = make_desc<16>(base + OFF_AXB), alo = make_desc<16>(base + OFF_ALO);
-          const uint64_t bhi = make_desc<32>(base + OFF_BHI), bxb = make_desc<16>(base + OFF_BXB), blo = make_desc<16>(base + OFF_BLO);
+          const uint64_t a0 = make_desc<16>(base), a1 = make_desc<16>(base + OFF_A1), b0 = make_desc<16>(base + OFF_B0), b1 = make_desc<16>(base + OFF_B1);
 #pragma unroll
-          for (int k = 0; k < 2; k++) {                      // bf16: 16 contraction indices = 32 bytes per instruction
+          for (int k = 0; k < 2; k++) {                      // 16 contraction indices = 32 bytes per instruction
             const uint64_t adv = (uint64_t)(2 * k);
-            tc_mma_bf16(acc_cross, alo + adv, bxb + adv, idesc_bf, (i > 0 || k > 0) ? 1u : 0u);
-            tc_mma_bf16(acc_cross, axb + adv, blo + adv, idesc_bf, 1u);
-          }
-#pragma unroll
-          for (int k = 0; k < 4; k++) {                      // tf32: 8 contraction indices = 32 bytes per instruction
-            const uint64_t adv = (uint64_t)(2 * k);
-            tc_mma_tf32(acc_main, ahi + adv, bhi + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            if constexpr (MERGED) {
+              // small terms first, so that they meet the accumulator before the large term of this group is added
+              tc_mma_bf16(acc_main, a1 + adv, b0 + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
+              tc_mma_bf16(acc_main, a0 + adv, b1 + adv, idesc, 1u);
+              tc_mma_bf16(acc_main, a0 + adv, b0 + adv, idesc, 1u);
+            } else {
+              tc_mma_bf16(acc_cross, a1 + adv, b0 + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
+              tc_mma_bf16(acc_cross, a0 + adv, b1 + adv, idesc, 1u);
+              tc_mma_bf16(acc_main, a0 + adv, b0 + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            }
           }
           tc_commit(empty0 + 8 * s);
         }
-        tc_commit(tfull0 + 8 * slot);
+        if (ok) tc_commit(tfull0 + 8 * slot);
       }
-      if (!ok) atomicExch(ep.status, 2);
+      if (!ok) {
+        if (!*abort_flag) give_up(2);
+        tc_commit(drain);                                   // own instructions in flight must finish before TMEM is released
+        mbar_wait(drain, 0, TC_DRAIN_LIMIT);
+      }
     }
   } else {
     const int quad = warp & 3; uint32_t lt = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
-      const uint32_t slot = NSLOTS == 2 ? (lt & 1) : 0, u = NSLOTS == 2 ? (lt >> 1) : lt; lt++;
-      bool ok = true;
-      if (lane == 0) ok = mbar_wait(tfull0 + 8 * slot, u & 1);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok && lane == 0) atomicExch(ep.status, 3);
+      const uint32_t slot = lt & 1, u = lt >> 1; lt++;
+      int ok = 1;
+      if (lane == 0) ok = mbar_wait(tfull0 + 8 * slot, u & 1, limit, abort_flag) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) { if (lane == 0 && !*abort_flag) give_up(3); break; }
       tc_fence_after();
-      tc_epilogue_tile<BN>(ep, tmem_base, slot * 2 * BN, slot * 2 * BN + BN, m0, n0, z, quad, lane, nkb);
+      tc_epilogue_tile<BN, MERGED>(ep, tmem_base, slot * SLOT_COLS, slot * SLOT_COLS + BN, m0, n0, z, quad, lane, nkb);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * slot);
@@ -306,6 +356,12 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (threadIdx.x == 0 && *abort_flag) {
+    // a wait gave up somewhere in this CTA: the producer's last copies may still be in flight and nobody consumes
+    // them any more; the CTA must not exit (and hand its shared memory on) before they have landed
+    const uint32_t n_back = issued < (uint32_t)STAGES ? issued : (uint32_t)STAGES;
+    for (uint32_t j = issued - n_back; j < issued; j++) mbar_wait(full0 + 8 * (j % STAGES), (j / STAGES) & 1, TC_DRAIN_LIMIT);
+  }
   if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
 }
 
@@ -313,50 +369,99 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapAhi, const __grid_
 // Batched, strided split: planes[z][r][c] (row stride ldp, c < ldp, zero beyond cols) of the source element
 // (z, r, c) at p + (z / batch2) * b1 + (z % batch2) * b2 + r * s_r + c * s_c.  One of s_r, s_c is 1:
 // s_c == 1 reads rows directly; s_r == 1 (the operand is the transpose of what is stored) goes through a shared tile.
-// Three planes per operand: hi = tf32(x) as fp32, xb = bf16(x), lo = bf16(x - hi).
+// Two fp16 planes per operand, p0 = fp16(x s), p1 = fp16(x s - p0), and the inverse 1/s of every plane row's scale.
 struct TcSrc { const float* p; long s_r, s_c, b1, b2; int batch2; };
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
   __nv_bfloat162 v = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&v);
 }
-__global__ void __launch_bounds__(256) split_rows_kernel(TcSrc s, int rows, int cols, float* __restrict__ hi, __nv_bfloat16* __restrict__ xb,
-                                                         __nv_bfloat16* __restrict__ lo, int ldp) {
-  // four float4 per thread, all loads issued before the first store; blockIdx.y = problem index
-  const int z = blockIdx.y, ldp4 = ldp >> 2, total = rows * ldp4;
-  const float* base = s.p + (z / s.batch2) * s.b1 + (z % s.batch2) * s.b2;
-  const int idx0 = blockIdx.x * 1024 + threadIdx.x;
-  float4 x[4]; long o[4];
-#pragma unroll
-  for (int k = 0; k < 4; k++) {
-    const int idx = idx0 + 256 * k;
-    o[k] = -1;
-    if (idx >= total) continue;
-    const int r = idx / ldp4, c = (idx - r * ldp4) << 2;
-    const float* src = base + (long)r * s.s_r + c;
-    if (c + 3 < cols && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) x[k] = *reinterpret_cast<const float4*>(src);
-    else { x[k].x = c < cols ? src[0] : 0.f; x[k].y = c + 1 < cols ? src[1] : 0.f; x[k].z = c + 2 < cols ? src[2] : 0.f; x[k].w = c + 3 < cols ? src[3] : 0.f; }
-    o[k] = ((long)z * rows + r) * ldp + c;
+// Power of two s that brings a row whose largest magnitude is mx into [2^14, 2^15) (fp16 overflows at 65504), and its
+// inverse.  s = 1 for a row of zeros (and for a row that holds an infinity or a NaN, which the products then carry on).
+__device__ __forceinline__ float row_scale(float mx, float* inv) {
+  if (!(mx > 0.f) || !(mx <= 3.0e38f)) { *inv = 1.f; return 1.f; }
+  int se = 14 - (((__float_as_int(mx) >> 23) & 0xff) - 127);
+  se = max(-100, min(100, se));
+  *inv = __int_as_float((127 - se) << 23); return __int_as_float((127 + se) << 23);
+}
+// (x s) -> (fp16(x s), fp16(x s - fp16(x s))) for two neighbouring elements, packed
+__device__ __forceinline__ void split2_pair(float a, float b, float s, uint32_t& p0, uint32_t& p1) {
+  a *= s; b *= s;
+  const __half2 h = __floats2half2_rn(a, b);
+  const float2 hf = __half22float2(h);
+  const __half2 l = __floats2half2_rn(a - hf.x, b - hf.y);
+  p0 = *reinterpret_cast<const uint32_t*>(&h); p1 = *reinterpret_cast<const uint32_t*>(&l);
+}
+// One warp per plane row: first the row's largest magnitude (the row is read a second time from L1 / L2 afterwards),
+// then eight elements per lane and step (two 16-byte loads, one 16-byte store per plane).  blockIdx.y = problem index.
+__global__ void __launch_bounds__(256) split2_rows_kernel(TcSrc s, int rows, int cols, __half* __restrict__ p0, __half* __restrict__ p1, float* __restrict__ inv_scale, int ldp) {
+  const int z = blockIdx.y, lane = threadIdx.x & 31;
+  const long r = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const float* src = s.p + (z / s.batch2) * s.b1 + (z % s.batch2) * s.b2 + r * s.s_r;
+  const bool vec = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
+  const int cols8 = vec ? (cols & ~7) : 0;                  // columns handled with 16-byte loads
+  float mx = 0.f;
+  for (int c = lane * 8; c < cols8; c += 256) {
+    const float4 a = *reinterpret_cast<const float4*>(src + c), b = *reinterpret_cast<const float4*>(src + c + 4);
+    mx = fmaxf(mx, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))), fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w)))));
   }
+  for (int c = cols8 + lane; c < cols; c += 32) mx = fmaxf(mx, fabsf(src[c]));
+  mx = warp_max(mx);
+  float inv; const float sc = row_scale(mx, &inv);
+  if (lane == 0) inv_scale[(long)z * rows + r] = inv;
+  const long o = ((long)z * rows + r) * ldp;
+  for (int c = lane * 8; c < ldp; c += 256) {
+    float t[8];
+    if (c + 7 < cols8) {
+      const float4 a = *reinterpret_cast<const float4*>(src + c), b = *reinterpret_cast<const float4*>(src + c + 4);
+      t[0] = a.x; t[1] = a.y; t[2] = a.z; t[3] = a.w; t[4] = b.x; t[5] = b.y; t[6] = b.z; t[7] = b.w;
+    } else {
 #pragma unroll
-  for (int k = 0; k < 4; k++) {
-    if (o[k] < 0) continue;
-    const float4 h = make_float4(tf32_round(x[k].x), tf32_round(x[k].y), tf32_round(x[k].z), tf32_round(x[k].w));
-    *reinterpret_cast<float4*>(hi + o[k]) = h;
-    *reinterpret_cast<uint2*>(xb + o[k]) = make_uint2(pack_bf16(x[k].x, x[k].y), pack_bf16(x[k].z, x[k].w));
-    *reinterpret_cast<uint2*>(lo + o[k]) = make_uint2(pack_bf16(x[k].x - h.x, x[k].y - h.y), pack_bf16(x[k].z - h.z, x[k].w - h.w));
+      for (int j = 0; j < 8; j++) t[j] = c + j < cols ? src[c + j] : 0.f;
+    }
+    uint4 a, b;
+    split2_pair(t[0], t[1], sc, a.x, b.x); split2_pair(t[2], t[3], sc, a.y, b.y);
+    split2_pair(t[4], t[5], sc, a.z, b.z); split2_pair(t[6], t[7], sc, a.w, b.w);
+    *reinterpret_cast<uint4*>(p0 + o + c) = a;
+    *reinterpret_cast<uint4*>(p1 + o + c) = b;
   }
 }
-__global__ void split_cols_kernel(TcSrc s, int rows, int cols, float* __restrict__ hi, __nv_bfloat16* __restrict__ xb, __nv_bfloat16* __restrict__ lo, int ldp) {
-  __shared__ float t[32][33];
-  const int z = blockIdx.z, c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+// Largest magnitude of every plane row of a transposed operand (= of every column of the stored matrix): a block covers
+// 64 plane rows x 256 contraction indices, reads run along the stored matrix's fast index, one atomicMax per row and block
+// on the bit pattern (non-negative floats order like integers).  `mx` must be zero on entry.
+__global__ void __launch_bounds__(256) colmax_kernel(TcSrc s, int rows, int cols, int* __restrict__ mx) {
+  __shared__ float red[4][64];
+  const int z = blockIdx.z, r = blockIdx.x * 64 + (threadIdx.x & 63), cy = threadIdx.x >> 6;
   const float* src = s.p + (z / s.batch2) * s.b1 + (z % s.batch2) * s.b2;
-  for (int j = threadIdx.y; j < 32; j += blockDim.y) { int c = c0 + j, r = r0 + threadIdx.x; t[j][threadIdx.x] = (r < rows && c < cols) ? src[r + c * s.s_c] : 0.f; }
+  float m = 0.f;
+  if (r < rows) for (int c = blockIdx.y * 256 + cy; c < min(cols, (int)(blockIdx.y + 1) * 256); c += 4) m = fmaxf(m, fabsf(src[r + (long)c * s.s_c]));
+  red[cy][threadIdx.x & 63] = m;
+  __syncthreads();
+  if (threadIdx.x < 64 && r < rows) {
+    m = fmaxf(fmaxf(red[0][threadIdx.x], red[1][threadIdx.x]), fmaxf(red[2][threadIdx.x], red[3][threadIdx.x]));
+    if (!(m <= 3.0e38f)) m = 3.4e38f;                       // an infinity or a NaN in the column: row_scale() then uses s = 1
+    atomicMax(mx + (long)z * rows + r, __float_as_int(m));
+  }
+}
+// Transposing split: 64 x 64 source tile through shared memory; reads run along the source's fast index (r), each
+// thread then writes two neighbouring contraction indices of one plane row as one 4-byte word.  `mx` = colmax_kernel's result.
+__global__ void __launch_bounds__(256) split2_cols_kernel(TcSrc s, int rows, int cols, __half* __restrict__ p0, __half* __restrict__ p1, const int* __restrict__ mx,
+                                                          float* __restrict__ inv_scale, int ldp) {
+  __shared__ float t[64][65];
+  const int z = blockIdx.z, c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
+  const float* src = s.p + (z / s.batch2) * s.b1 + (z % s.batch2) * s.b2;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  for (int j = ty; j < 64; j += 4) { const int c = c0 + j, r = r0 + tx; t[j][tx] = (r < rows && c < cols) ? src[r + (long)c * s.s_c] : 0.f; }
   __syncthreads();
   const long zo = (long)z * rows * ldp;
-  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
-    int r = r0 + j, c = c0 + threadIdx.x;
+  const int cx = (threadIdx.x & 31) * 2, ry = threadIdx.x >> 5;
+  for (int j = ry; j < 64; j += 8) {
+    const int r = r0 + j, c = c0 + cx;
     if (r < rows && c < ldp) {
-      const float x = t[threadIdx.x][j], h = tf32_round(x); const long o = zo + (long)r * ldp + c;
-      hi[o] = h; xb[o] = __float2bfloat16_rn(x); lo[o] = __float2bfloat16_rn(x - h);
+      float inv; const float sc = row_scale(__int_as_float(mx[(long)z * rows + r]), &inv);
+      if (c == 0) inv_scale[(long)z * rows + r] = inv;
+      uint32_t a, b; split2_pair(t[cx][j], t[cx + 1][j], sc, a, b);
+      const long o = zo + (long)r * ldp + c;
+      *reinterpret_cast<uint32_t*>(p0 + o) = a; *reinterpret_cast<uint32_t*>(p1 + o) = b;
     }
   }
 }
@@ -365,28 +470,38 @@ __global__ void split_cols_kernel(TcSrc s, int rows, int cols, float* __restrict
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                     CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// Operand planes, [nbatch][rows][ldp] each, K valid columns starting at column koff (a slice of a longer contraction):
-// `hi` fp32; `lo` is a buffer of the same size holding the two bf16 planes one after the other (bf16 copy, then lo).
-// The attention kernels use the same struct for their own fp32 hi / fp32 lo planes (tc_make_map on either pointer).
+// Operand planes of the attention kernels, [nbatch][rows][ldp] each, K valid columns starting at column koff:
+// `hi` fp32 (tf32-rounded values); `lo` is a buffer of the same size holding two bf16 planes one after the other
+// (bf16 copy, then bf16 of the remainder).
 struct TcPlanes {
   float* hi; float* lo; int rows, K, ldp, nbatch; int koff = 0;
   __nv_bfloat16* xb() const { return reinterpret_cast<__nv_bfloat16*>(lo); }
   __nv_bfloat16* lob() const { return xb() + (size_t)nbatch * rows * ldp; }
 };
-inline int tc_ldp(int K) { return ((K + 7) / 8) * 8; }              // plane row stride: a multiple of 16 bytes for TMA in bf16 too
+// Operand planes of the contraction engine: two fp16 planes [nbatch][rows][ldp] in one buffer, plane 1 after plane 0, and
+// the inverse scale of every plane row [nbatch][rows].
+struct BfPlanes {
+  __half* base; float* inv_scale; int rows, K, ldp, nbatch; int koff = 0;
+  size_t plane_elems() const { return (size_t)nbatch * rows * ldp; }
+  __half* p0() const { return base; }
+  __half* p1() const { return base + plane_elems(); }
+};
+inline int tc_ldp(int K) { return ((K + 7) / 8) * 8; }              // plane row stride: a multiple of 16 bytes for TMA
+inline size_t bf_plane_floats(long nbatch, long rows, long ldp) { return (size_t)nbatch * rows * ldp; }   // two fp16 planes = one float per element
 
-struct TcScratch { DevBuf a_hi, a_lo, b_hi, b_lo; const float* last_a = nullptr; int last_m = 0, last_k = 0; long last_ld = 0; };
-inline TcScratch& tc_scratch(Ctx* ctx) { static thread_local std::vector<std::pair<Ctx*, TcScratch*>> tab; for (auto& e : tab) if (e.first == ctx) return *e.second; tab.push_back({ctx, ctx->own(new TcScratch())}); return *tab.back().second; }
+// Per-context operand-plane scratch of the contraction engine (calls on a context are serialised by Ctx::run_mu).
+struct TcScratch { DevBuf a, b, sa, sb, mx; const float* last_a = nullptr; int last_m = 0, last_k = 0; long last_ld = 0; };
+inline TcScratch& tc_scratch(Ctx* ctx) { if (!ctx->tc_scratch) ctx->tc_scratch = ctx->own(new TcScratch()); return *static_cast<TcScratch*>(ctx->tc_scratch); }
 
+template <int BN> inline bool tc_set_smem() { return cudaFuncSetAttribute(gemm_tc_persist_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<BN>::SMEM_BYTES) == cudaSuccess; }
 inline void tc_init(Ctx* ctx) {
   ctx->tc_ok = false;
   void* fn = nullptr; cudaDriverEntryPointQueryResult q;
   if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || !fn || q != cudaDriverEntryPointSuccess) { cudaGetLastError(); return; }
-  bool ok = true;
-  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<128, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<128>::SMEM_BYTES) == cudaSuccess;
-  ok &= cudaFuncSetAttribute(gemm_tc_persist_kernel<64, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<64>::SMEM_BYTES) == cudaSuccess;
-  if (!ok) { cudaGetLastError(); return; }
+  if (!(tc_set_smem<64>() && tc_set_smem<128>() && tc_set_smem<256>())) { cudaGetLastError(); return; }
   ctx->encode_tiled = fn; ctx->tc_ok = true;
+  if (const char* e = getenv("GONEURON_CUDA_TC_BN")) ctx->tc_force_bn = atoi(e);
+  if (const char* e = getenv("GONEURON_CUDA_TC_KSLICE")) ctx->tc_kslice = atoi(e);
 }
 
 // fp32 plane, 32 columns (128 bytes, 128-byte swizzle) x box_rows per copy
@@ -400,55 +515,94 @@ inline int tc_make_map(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const floa
   if (r != CUDA_SUCCESS) return fail(GN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows %d K %d ld %d batch %d)", (int)r, p.rows, p.K, p.ldp, p.nbatch);
   return GN_OK;
 }
-// bf16 plane, box_cols columns x box_rows per copy: 32 columns = 64 bytes with the 64-byte swizzle (contraction engine),
-// 64 columns = 128 bytes with the 128-byte swizzle (attention tiles)
-inline int tc_make_map_bf16(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const __nv_bfloat16* base, int box_rows, int box_cols = TC_BK) {
-  cuuint64_t dims[3] = {(cuuint64_t)p.K, (cuuint64_t)p.rows, (cuuint64_t)p.nbatch};
-  cuuint64_t strides[2] = {(cuuint64_t)p.ldp * 2, (cuuint64_t)p.rows * p.ldp * 2};
+// bf16 plane [nbatch][rows][ldp], K valid columns from column koff, box_cols columns x box_rows per copy: 32 columns = 64
+// bytes with the 64-byte swizzle (contraction engine), 64 columns = 128 bytes with the 128-byte swizzle (attention tiles)
+inline int tc_make_map_bf16_raw(Ctx* ctx, CUtensorMap* map, const void* base_v, int K, int rows, int ldp, int nbatch, int koff, int box_rows, int box_cols,
+                                CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16) {
+  const uint16_t* base = static_cast<const uint16_t*>(base_v);
+  cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)nbatch};
+  cuuint64_t strides[2] = {(cuuint64_t)ldp * 2, (cuuint64_t)rows * ldp * 2};
   cuuint32_t box[3] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = ((PFN_encodeTiled)ctx->encode_tiled)(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, (void*)(base + p.koff), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = ((PFN_encodeTiled)ctx->encode_tiled)(map, dtype, 3, (void*)(base + koff), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                                                     box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(GN_ERR_CUDA, "cuTensorMapEncodeTiled (bf16) failed with %d (rows %d K %d ld %d batch %d)", (int)r, p.rows, p.K, p.ldp, p.nbatch);
+  if (r != CUDA_SUCCESS) return fail(GN_ERR_CUDA, "cuTensorMapEncodeTiled (16-bit) failed with %d (rows %d K %d ld %d batch %d)", (int)r, rows, K, ldp, nbatch);
   return GN_OK;
 }
+inline int tc_make_map_bf16(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const __nv_bfloat16* base, int box_rows, int box_cols = TC_BK) {
+  return tc_make_map_bf16_raw(ctx, map, base, p.K, p.rows, p.ldp, p.nbatch, p.koff, box_rows, box_cols);
+}
 
-// Writes the planes of an operand.
-inline int tc_split(Ctx* ctx, const TcSrc& src, const TcPlanes& p) {
+// Writes the planes and inverse row scales of an operand.  `mx` (only used by the transposing variant): nbatch * rows ints.
+inline int tc_split(Ctx* ctx, const TcSrc& src, const BfPlanes& p, int* mx) {
   if (src.s_c == 1) {
     if (p.nbatch > 65535) return fail(GN_ERR_UNSUPPORTED, "tc_split: more than 65535 problems in a batch");
-    GN_LAUNCH(ctx, split_rows_kernel, dim3(cdiv((long)p.rows * (p.ldp >> 2), 1024), p.nbatch), 256, 0, src, p.rows, p.K, p.hi, p.xb(), p.lob(), p.ldp);
+    GN_LAUNCH(ctx, split2_rows_kernel, dim3(cdiv(p.rows, 8), p.nbatch), 256, 0, src, p.rows, p.K, p.p0(), p.p1(), p.inv_scale, p.ldp);
   } else if (src.s_r == 1) {
-    GN_LAUNCH(ctx, split_cols_kernel, dim3(cdiv(p.ldp, 32), cdiv(p.rows, 32), p.nbatch), dim3(32, 8), 0, src, p.rows, p.K, p.hi, p.xb(), p.lob(), p.ldp);
+    if (p.nbatch > 65535 || cdiv(p.rows, 64) > 65535 || cdiv(p.K, 256) > 65535) return fail(GN_ERR_UNSUPPORTED, "tc_split: operand too large for the transposing split");
+    if (!mx) return fail(GN_ERR_INVALID_ARG, "tc_split: the transposing split needs a row-maximum buffer");
+    GN_CUDA(cudaMemsetAsync(mx, 0, (size_t)p.nbatch * p.rows * sizeof(int), ctx->stream));
+    GN_LAUNCH(ctx, colmax_kernel, dim3(cdiv(p.rows, 64), cdiv(p.K, 256), p.nbatch), 256, 0, src, p.rows, p.K, mx);
+    GN_LAUNCH(ctx, split2_cols_kernel, dim3(cdiv(p.ldp, 64), cdiv(p.rows, 64), p.nbatch), 256, 0, src, p.rows, p.K, p.p0(), p.p1(), (const int*)mx, p.inv_scale, p.ldp);
   } else return fail(GN_ERR_UNSUPPORTED, "tc_split: neither stride of the operand is 1");
   return check_launch("tc_split");
 }
 
 template <int BN>
-inline int tc_launch_persist(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep) {
-  CUtensorMap mAh, mAx, mAl, mBh, mBx, mBl;
-  GN_TRY(tc_make_map(ctx, &mAh, A, A.hi, TC_BM)); GN_TRY(tc_make_map_bf16(ctx, &mAx, A, A.xb(), TC_BM)); GN_TRY(tc_make_map_bf16(ctx, &mAl, A, A.lob(), TC_BM));
-  GN_TRY(tc_make_map(ctx, &mBh, B, B.hi, BN)); GN_TRY(tc_make_map_bf16(ctx, &mBx, B, B.xb(), BN)); GN_TRY(tc_make_map_bf16(ctx, &mBl, B, B.lob(), BN));
+inline int tc_launch_persist(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams& ep) {
+  CUtensorMap mA0, mA1, mB0, mB1;
+  constexpr CUtensorMapDataType F16 = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  GN_TRY(tc_make_map_bf16_raw(ctx, &mA0, A.p0(), A.K, A.rows, A.ldp, A.nbatch, A.koff, TC_BM, TC_BK, F16)); GN_TRY(tc_make_map_bf16_raw(ctx, &mA1, A.p1(), A.K, A.rows, A.ldp, A.nbatch, A.koff, TC_BM, TC_BK, F16));
+  GN_TRY(tc_make_map_bf16_raw(ctx, &mB0, B.p0(), B.K, B.rows, B.ldp, B.nbatch, B.koff, BN, TC_BK, F16)); GN_TRY(tc_make_map_bf16_raw(ctx, &mB1, B.p1(), B.K, B.rows, B.ldp, B.nbatch, B.koff, BN, TC_BK, F16));
   const int tiles_m = cdiv(ep.M, TC_BM), tiles_n = cdiv(ep.N, BN); const long total = (long)tiles_m * tiles_n * A.nbatch;
   if (total > 0x7fffffffL) return fail(GN_ERR_UNSUPPORTED, "too many output tiles");
   const unsigned grid = (unsigned)std::min<long>(total, ctx->sm_count);
   ProfScope prof(ctx);
-  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN, 2>), grid, TC_THREADS, (TcCfg<BN>::SMEM_BYTES), mAh, mAx, mAl, mBh, mBx, mBl, ep, tiles_m, tiles_n, (int)total);
+  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN>), grid, TC_THREADS, (TcCfg<BN>::SMEM_BYTES), mA0, mA1, mB0, mB1, ep, tiles_m, tiles_n, (int)total);
   return check_launch("gemm_tc_persist");
 }
-// C[z] = A[z] * B[z]^T from prepared planes; the N tile follows the output width.
-inline int tc_launch(Ctx* ctx, const TcPlanes& A, const TcPlanes& B, const TcParams& ep_in) {
+// Output tile width for a problem: 64 for narrow outputs; 256 (three quarters of the shared-memory traffic per MMA
+// cycle of the 128-wide tile) when the problem still fills the SMs evenly with tiles of that size.
+inline int tc_pick_bn(Ctx* ctx, int M, int N, long nbatch, int flags) {
+  if (ctx->tc_force_bn == 64 || ctx->tc_force_bn == 128 || ctx->tc_force_bn == 256) return ctx->tc_force_bn;
+  if (N <= 64) return 64;
+  if (N <= 128 || (flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return 128;
+  auto cost = [&](int bn, double rate) { const double tiles = (double)cdiv(M, TC_BM) * cdiv(N, bn) * nbatch; const double waves = std::ceil(tiles / ctx->sm_count); return waves * bn / rate; };
+  return cost(256, 1.3) < cost(128, 1.0) ? 256 : 128;
+}
+// C[z] = A[z] * B[z]^T from prepared planes, one accumulator run over the whole contraction.
+inline int tc_launch(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams& ep_in, int bn) {
   if (!ctx->tc_ok) return fail(GN_ERR_UNSUPPORTED, "tcgen05 engine unavailable");
-  TcParams ep = ep_in;
+  TcParams ep = ep_in; ep.spin_limit = ctx->spin_limit; ep.isa = A.inv_scale; ep.isb = B.inv_scale;
   if (A.K != B.K || A.nbatch != B.nbatch || A.rows != ep.M || B.rows != ep.N || A.K != ep.K) return fail(GN_ERR_INVALID_ARG, "tc_launch: operand shapes disagree");
   auto a16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  bool vec = ep.N % 4 == 0 && ep.ldc % 4 == 0 && ep.c_b1 % 4 == 0 && ep.c_b2 % 4 == 0 && a16(ep.C) && (!ep.bias || a16(ep.bias));
+  bool vec = ep.N % 4 == 0 && ep.ldc % 4 == 0 && ep.c_b1 % 4 == 0 && ep.c_b2 % 4 == 0 && a16(ep.C) && (!ep.bias || a16(ep.bias)) && a16(ep.isb);
   if (ep.R) vec = vec && ep.ldr % 4 == 0 && ep.r_b1 % 4 == 0 && ep.r_b2 % 4 == 0 && a16(ep.R);
   if (ep.mask) vec = vec && ep.mask_ld % 4 == 0 && a16(ep.mask);
   if (vec) ep.flags |= TC_FLAG_VEC;
-  if (ep.N <= 64) return tc_launch_persist<64>(ctx, A, B, ep);
+  if (bn == 64) return tc_launch_persist<64>(ctx, A, B, ep);
+  if (bn == 256) return tc_launch_persist<256>(ctx, A, B, ep);
   return tc_launch_persist<128>(ctx, A, B, ep);
+}
+// The tensor core truncates when it adds a product group to the accumulator, so the error of one accumulator run grows
+// with the number of MMA instructions that feed it (one per 16 contraction indices and term).  Long contractions (weight
+// gradients over all tokens of a batch) are therefore cut into slices, each slice adding its result to C through the
+// epilogue's residual path, i.e. in properly rounded fp32: 4096 indices per run with separate accumulators for the
+// large and the small terms, 2048 with the single accumulator of the 256-wide tile.
+inline int tc_run(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams& ep) {
+  const int bn = tc_pick_bn(ctx, ep.M, ep.N, A.nbatch, ep.flags);
+  const int kslice = ctx->tc_kslice > 0 ? ctx->tc_kslice : (bn == 256 ? 2048 : 4096);
+  if (ep.K <= kslice || (ep.flags & (GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return tc_launch(ctx, A, B, ep, bn);
+  for (int k0 = 0; k0 < ep.K; k0 += kslice) {
+    const int kl = std::min(kslice, ep.K - k0); const bool first = k0 == 0, last = k0 + kl >= ep.K;
+    BfPlanes As = A, Bs = B; As.koff = A.koff + k0; As.K = kl; Bs.koff = B.koff + k0; Bs.K = kl;
+    TcParams es = ep; es.K = kl;
+    if (!first) { es.bias = nullptr; es.R = ep.C; es.ldr = ep.ldc; es.r_b1 = ep.c_b1; es.r_b2 = ep.c_b2; }
+    if (!last) { es.act = GN_ACT_LINEAR; es.mask = nullptr; }
+    GN_TRY(tc_launch(ctx, As, Bs, es, bn));
+  }
+  return GN_OK;
 }
 
 // Can the engine run this contraction at all?  One of each operand's strides must be 1; LINEAR/RELU epilogue; alpha 1.
@@ -471,32 +625,23 @@ inline int gemm_tc(Ctx* ctx, const GemmDesc& g) {
   if (!gemm_tc_supported(ctx, g)) return fail(GN_ERR_UNSUPPORTED, "tcgen05 engine cannot run this contraction");
   TcScratch& sc = tc_scratch(ctx);
   const int nb = g.batch1 * g.batch2, ldp = tc_ldp(g.K);
-  size_t na = (size_t)nb * g.M * ldp, nbb = (size_t)nb * g.N * ldp;
-  if (sc.a_hi.n < na) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.a_hi.alloc(na)); GN_TRY(sc.a_lo.alloc(na)); sc.last_a = nullptr; }
-  if (sc.b_hi.n < nbb) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.b_hi.alloc(nbb)); GN_TRY(sc.b_lo.alloc(nbb)); }
-  TcPlanes A{sc.a_hi.p, sc.a_lo.p, g.M, g.K, ldp, nb}, B{sc.b_hi.p, sc.b_lo.p, g.N, g.K, ldp, nb};
+  const size_t na = bf_plane_floats(nb, g.M, ldp), nbb = bf_plane_floats(nb, g.N, ldp), nsa = (size_t)nb * g.M, nsb = (size_t)nb * g.N;
+  if (sc.a.n < na) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.a.alloc(na)); sc.last_a = nullptr; }
+  if (sc.b.n < nbb) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.b.alloc(nbb)); }
+  if (sc.sa.n < nsa) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.sa.alloc(nsa + 1024)); sc.last_a = nullptr; }
+  if (sc.sb.n < nsb) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.sb.alloc(nsb + 1024)); }
+  if (sc.mx.n < std::max(nsa, nsb)) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.mx.alloc(std::max(nsa, nsb) + 1024)); }
+  BfPlanes A{reinterpret_cast<__half*>(sc.a.p), sc.sa.p, g.M, g.K, ldp, nb}, B{reinterpret_cast<__half*>(sc.b.p), sc.sb.p, g.N, g.K, ldp, nb};
+  int* mx = reinterpret_cast<int*>(sc.mx.p);
   if (g.reuse_a_planes && nb == 1 && sc.last_a == g.A && sc.last_m == g.M && sc.last_k == g.K && sc.last_ld == g.sa_m && g.sa_k == 1) {
     // same tensor as the previous call (the Q, K and V projections share their input): planes still valid
   } else {
-    GN_TRY(tc_split(ctx, TcSrc{g.A, g.sa_m, g.sa_k, g.a_b1, g.a_b2, g.batch2}, A));
+    GN_TRY(tc_split(ctx, TcSrc{g.A, g.sa_m, g.sa_k, g.a_b1, g.a_b2, g.batch2}, A, mx));
     sc.last_a = (nb == 1 && g.sa_k == 1) ? g.A : nullptr; sc.last_m = g.M; sc.last_k = g.K; sc.last_ld = g.sa_m;
   }
-  GN_TRY(tc_split(ctx, TcSrc{g.B, g.sb_n, g.sb_k, g.b_b1, g.b_b2, g.batch2}, B));
+  GN_TRY(tc_split(ctx, TcSrc{g.B, g.sb_n, g.sb_k, g.b_b1, g.b_b2, g.batch2}, B, mx));
   TcParams ep{g.C, g.ldc, g.c_b1, g.c_b2, g.bias, g.R, g.ldr, g.r_b1, g.r_b2, g.act, g.M, g.N, g.K, g.batch2, g.flags, ctx->d_status, g.mask, g.mask_ld, g.mask_group};
-  // The tensor core truncates when it adds a product group to the accumulator, so the error of one accumulator run grows
-  // with its length (measured 3e-6 at K = 1024, 1.2e-5 at K = 4096, normalised).  Long contractions (weight gradients
-  // over all tokens of a batch) are therefore cut into slices of TC_KSLICE, each slice adding its result to C through
-  // the epilogue's residual path, i.e. in properly rounded fp32.
-  if (g.K <= TC_KSLICE || (g.flags & (GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return tc_launch(ctx, A, B, ep);
-  for (int k0 = 0; k0 < g.K; k0 += TC_KSLICE) {
-    const int kl = std::min(TC_KSLICE, g.K - k0); const bool first = k0 == 0, last = k0 + kl >= g.K;
-    TcPlanes As = A, Bs = B; As.koff = k0; As.K = kl; Bs.koff = k0; Bs.K = kl;
-    TcParams es = ep; es.K = kl;
-    if (!first) { es.bias = nullptr; es.R = g.C; es.ldr = g.ldc; es.r_b1 = g.c_b1; es.r_b2 = g.c_b2; }
-    if (!last) { es.act = GN_ACT_LINEAR; es.mask = nullptr; }
-    GN_TRY(tc_launch(ctx, As, Bs, es));
-  }
-  return GN_OK;
+  return tc_run(ctx, A, B, ep);
 }
 
 }  // namespace gn

@@ -72,6 +72,7 @@ struct LayerRT {
   DevBuf idx;                          // int32 payload: MaxPool argmax / embedding token ids
   const float* fin = nullptr;          // input of the last forward call (device pointer, not owned)
   int64_t s_off = 0, s_cnt = 0;        // BatchNorm2D: slice of the model's state buffer (running mean | running variance)
+  bool grad_replicated = false;        // multi-GPU: every rank already holds the gradient of the whole global batch (no all-reduce)
   float bn_eps = 1e-5f, bn_mom = 0.1f;
 };
 
@@ -87,13 +88,15 @@ struct gn_model {
   int64_t P = 0; int in_size = 0, out_size = 0;
   gn::DevBuf params, grads, m1, v2, state; int64_t NS = 0;
   int cur_first_sample = 0;             // global index of the first sample of the batch being processed (Dropout's stream position)
+  int cur_global_batch = 0;             // size of the global batch being processed (all ranks)
   float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f; int timestep = 0;
   int cap = 0;                          // batch capacity of the activation buffers
   gn::DevBuf xin, yin, lossg, loss_s, loss_sum;
   std::vector<gn::DevBuf> scratch;      // growable shared scratch, by slot
   float last_inv_batch = 1.f;
+  float* h_ret = nullptr;               // pinned host block: [0] loss sum, [1] status word (bits), read back once per step
   gn_step_stats stats{};
-  cudaEvent_t ev0 = nullptr, ev1 = nullptr, ar0 = nullptr, ar1 = nullptr, comm_done = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr, ar0 = nullptr, ar1 = nullptr, comm_done = nullptr, gather_ev = nullptr;
   std::vector<cudaEvent_t> layer_ev;    // gradient of layer i complete (multi-GPU: releases its all-reduce)
   bool alive = true;
   bool has_lstm = false;
@@ -101,13 +104,26 @@ struct gn_model {
 
 namespace gn {
 
-enum Slot { S_GRAM0 = 0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+enum Slot { S_BNG = 0, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
 
 static int ensure(gn_model* m, int slot, size_t n, float** out) {
   if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
   DevBuf& b = m->scratch[slot];
   if (b.n < n) { GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); GN_TRY(b.alloc(n)); }
   *out = b.p; return GN_OK;
+}
+
+// All-gather of equal per-rank pieces on the communication stream, ordered after everything queued on the main stream so
+// far; the main stream then waits for the result.  `send` may be the rank's own piece inside `recv` (in place).
+static int all_gather_on_comm(gn_model* m, const float* send, float* recv, size_t count_per_rank, const char* what) {
+  Ctx* ctx = &m->ctx->c;
+  GN_CUDA(cudaEventRecord(m->gather_ev, ctx->stream));
+  GN_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->gather_ev, 0));
+  int rc = ctx->nccl->AllGather(send, recv, count_per_rank, NCCL_FLOAT32, ctx->comm, ctx->comm_stream);
+  if (rc) return fail(GN_ERR_NCCL, "ncclAllGather(%s): %s", what, ctx->nccl->GetErrorString(rc));
+  GN_CUDA(cudaEventRecord(m->gather_ev, ctx->comm_stream));
+  GN_CUDA(cudaStreamWaitEvent(ctx->stream, m->gather_ev, 0));
+  return GN_OK;
 }
 
 static int plan_layers(gn_model* m, const gn_layer_desc* layers, int n) {
@@ -381,9 +397,17 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
       case GN_LAYER_BATCHNORM2D: {
         const int C = d.in_size, S = d.in_h * d.in_w; const long BC = (long)B * C; float* run = m->state.p + l.s_off;
         if (training) {
-          if (ctx->world > 1) return fail(GN_ERR_UNSUPPORTED, "BatchNorm2D running statistics are single-GPU in this build");
           GN_LAUNCH(ctx, bn_fwd_kernel, (unsigned)BC, 256, 0, cur, p, p + C, l.out.p, l.stat.p, C, S, BC, l.bn_eps);
-          GN_LAUNCH(ctx, bn_running_kernel, cdiv(C, 128), 128, 0, l.stat.p, run, B, C, BC, l.bn_mom);
+          if (ctx->world > 1) {
+            // the running statistics move once per sample in batch order (batchnorm2d.go:352, :376): every rank gathers the
+            // per-sample statistics of the whole global batch and walks them in that order, so the replicas stay identical
+            const int GB = m->cur_global_batch;
+            if (GB != B * ctx->world) return fail(GN_ERR_INVALID_ARG, "BatchNorm2D on %d ranks needs equal shards (global batch %d, this rank %d)", ctx->world, GB, B);
+            float* g; GN_TRY(ensure(m, S_BNG, (size_t)2 * GB * C, &g));
+            GN_TRY(all_gather_on_comm(m, l.stat.p, g, (size_t)BC, "BatchNorm2D means"));
+            GN_TRY(all_gather_on_comm(m, l.stat.p + 2 * BC, g + (size_t)GB * C, (size_t)BC, "BatchNorm2D variances"));
+            GN_LAUNCH(ctx, bn_running_gathered_kernel, cdiv(C, 128), 128, 0, (const float*)g, (const float*)(g + (size_t)GB * C), run, GB, C, l.bn_mom);
+          } else GN_LAUNCH(ctx, bn_running_kernel, cdiv(C, 128), 128, 0, l.stat.p, run, B, C, BC, l.bn_mom);
         } else {
           long n = BC * S; GN_LAUNCH(ctx, bn_eval_kernel, ew_grid(ctx, n), 256, 0, cur, p, p + C, run, l.out.p, C, S, n, l.bn_eps);
         }
@@ -504,15 +528,21 @@ static int lstm_backward(gn_model* m, LayerRT& l, size_t li, int B, const float*
   int threads = ((H + 31) / 32) * 32;
   GN_LAUNCH(ctx, lstm_bwd_kernel, B, threads, (size_t)4 * H * sizeof(float), gout, Wh, bias, l.pre_i.p, l.c_all.p, l.dgate.p, T, H, d.return_seq);
   if (li > 0) GN_TRY(gemm_nn(ctx, B * T, 4 * H, in, l.dgate.p, 4 * H, Wx, dx, in));   // dx_t = Wx^T d_t
-  if (m->ctx->c.world > 1) return fail(GN_ERR_UNSUPPORTED, "LSTM gradient scan is single-GPU in this build");
-  (void)first_sample;
-  int chunk = (global_batch + m->W - 1) / m->W, nchunks = (B + chunk - 1) / chunk;
+  // The clipping recurrence (lstm.go:694, :725-751) walks the rank-1 updates d_k z_k^T of a whole worker chunk in sample
+  // order, and a chunk may span ranks.  With more than one rank every rank therefore gathers the update factors of the
+  // whole global batch (rows in global sample order, all-gather over NVLink) and runs the identical scan over all chunks:
+  // each replica ends up with the complete LSTM gradient, and this layer's slice is not all-reduced.
+  const int world = ctx->world; const int GB = world > 1 ? global_batch : B; const int row0 = world > 1 ? first_sample : 0;
+  if (world > 1 && GB != B * world) return fail(GN_ERR_INVALID_ARG, "LSTM on %d ranks needs equal shards (global batch %d, this rank %d)", world, GB, B);
+  l.grad_replicated = world > 1;
+  int chunk = (global_batch + m->W - 1) / m->W, nchunks = (GB + chunk - 1) / chunk;
   {
     // Gram-matrix form of the clipping recurrence (conv_lstm.cuh): the default whenever its matrices fit.  The
     // cluster kernel below runs only for chunks too long for it, or when GONEURON_CUDA_LSTM_SCAN=cluster asks for it.
     static const int mode = [] { const char* e = getenv("GONEURON_CUDA_LSTM_SCAN"); return !e ? 0 : (strcmp(e, "cluster") == 0 ? 1 : (strcmp(e, "gram") == 0 ? 2 : 0)); }();
-    const long Kc = (long)chunk * T, n_updates = (long)B * T; const int R4g = 4 * H, ZWg = in + H + 1;
+    const long Kc = (long)chunk * T, n_updates = (long)GB * T, n_local = (long)B * T; const int R4g = 4 * H, ZWg = in + H + 1;
     const bool fits = Kc <= GRAM_MAX_K && (double)nchunks * Kc * Kc * 8 <= 8.0e9;
+    if (world > 1 && !(mode != 1 && fits)) return fail(GN_ERR_UNSUPPORTED, "LSTM on more than one GPU needs the Gram form of the clipping recurrence (worker chunk of %ld updates)", Kc);
     if (mode != 1 && fits) {
       float *G0, *G1, *Dm, *Zm, *wv, *res;
       GN_TRY(ensure(m, S_GRAM0, (size_t)nchunks * Kc * Kc, &G0)); GN_TRY(ensure(m, S_GRAM1, (size_t)nchunks * Kc * Kc, &G1));
@@ -522,7 +552,12 @@ static int lstm_backward(gn_model* m, LayerRT& l, size_t li, int B, const float*
         GN_CUDA(cudaMemsetAsync(Dm, 0, (size_t)nchunks * Kc * R4g * 4, ctx->stream)); GN_CUDA(cudaMemsetAsync(Zm, 0, (size_t)nchunks * Kc * ZWg * 4, ctx->stream));
         GN_CUDA(cudaMemsetAsync(wv, 0, (size_t)nchunks * Kc * 4, ctx->stream));
       }
-      GN_LAUNCH(ctx, lstm_gather_updates_kernel, (unsigned)n_updates, 128, 0, (const float*)l.dgate.p, xin, (const float*)l.h_all.p, Dm, Zm, T, in, H, n_updates);
+      float* Dloc = Dm + (size_t)row0 * T * R4g; float* Zloc = Zm + (size_t)row0 * T * ZWg;      // this rank's rows inside the global arrays
+      GN_LAUNCH(ctx, lstm_gather_updates_kernel, (unsigned)n_local, 128, 0, (const float*)l.dgate.p, xin, (const float*)l.h_all.p, Dloc, Zloc, T, in, H, n_local);
+      if (world > 1) {
+        GN_TRY(all_gather_on_comm(m, Dloc, Dm, (size_t)n_local * R4g, "LSTM update factors D"));
+        GN_TRY(all_gather_on_comm(m, Zloc, Zm, (size_t)n_local * ZWg, "LSTM update factors Z"));
+      }
       GemmDesc g; g.M = (int)Kc; g.N = (int)Kc; g.batch1 = nchunks; g.c_b1 = Kc * Kc; g.ldc = Kc; g.flags = GEMM_SKIP_UPPER;
       g.K = R4g; g.A = Dm; g.sa_m = R4g; g.sa_k = 1; g.B = Dm; g.sb_k = 1; g.sb_n = R4g; g.a_b1 = g.b_b1 = Kc * R4g; g.C = G0; GN_TRY(gemm(ctx, g));
       g.K = ZWg; g.A = Zm; g.sa_m = ZWg; g.B = Zm; g.sb_n = ZWg; g.a_b1 = g.b_b1 = Kc * ZWg; g.C = G1; GN_TRY(gemm(ctx, g));
@@ -663,7 +698,7 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         break; }
     }
     GN_TRY(check_launch("backward"));
-    if (ctx->world > 1 && l.p_cnt > 0) {
+    if (ctx->world > 1 && l.p_cnt > 0 && !l.grad_replicated) {
       // this layer's slice of the flat gradient buffer is final: sum it over the ranks while earlier layers still compute
       GN_CUDA(cudaEventRecord(m->layer_ev[li], ctx->stream));
       GN_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->layer_ev[li], 0));
@@ -681,21 +716,27 @@ static void adam_coeffs(float lr, float b1, float b2, int t, float* effLR) {
   float bias2 = (float)(1.0 - std::pow((double)b2, (double)t));
   *effLR = lr * (float)std::sqrt((double)bias2) / bias1;
 }
-static int adam_launch(Ctx* ctx, float* p, const float* g, float* m1, float* v, int64_t n, float lr, float b1, float b2, float eps, int t, float grad_scale) {
+static int adam_launch(Ctx* ctx, float* p, const float* g, float* m1, float* v, int64_t n, float lr, float b1, float b2, float eps, int t, float grad_scale,
+                       const int* status = nullptr) {
   float effLR; adam_coeffs(lr, b1, b2, t, &effLR);
-  GN_LAUNCH(ctx, adam_kernel, ew_grid(ctx, (n + 3) / 4), 256, 0, p, g, m1, v, (long)n, effLR, b1, b2, 1.f - b1, 1.f - b2, eps, grad_scale);
+  GN_LAUNCH(ctx, adam_kernel, ew_grid(ctx, (n + 3) / 4), 256, 0, p, g, m1, v, (long)n, effLR, b1, b2, 1.f - b1, 1.f - b2, eps, grad_scale, status);
   return check_launch("adam");
 }
+// Reads the status word; non-zero (a bounded device-side wait gave up) clears it and becomes GN_ERR_TIMEOUT.
+static int check_status_word(Ctx* c) {
+  int st = 0; GN_CUDA(copy_d2h(c, &st, c->d_status, sizeof(int)));
+  if (st != 0) { cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream); cudaStreamSynchronize(c->stream); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
+  return GN_OK;
+}
 
-static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B, int global_batch, int first_sample, float* mean_loss) {
+// The step proper.  Anything that fails after work has been queued must not leave that work running behind the caller's
+// back: train_step() below drains both streams before it reports the error.
+static int train_step_issue(gn_model* m, const float* x_dev, const float* y_dev, int B, int global_batch, int first_sample) {
   Ctx* ctx = &m->ctx->c;
-  if (global_batch <= 0) { global_batch = B; first_sample = 0; }
-  if (B > m->cap) GN_TRY(alloc_activations(m, B));
-  int64_t launches0 = ctx->launches; ctx->gemm_flops = 0; ctx->gemm_launches = 0; ctx->gemm_ms = 0; ctx->ev_used = 0;
   GN_CUDA(cudaEventRecord(m->ev0, ctx->stream));
   GN_CUDA(cudaMemsetAsync(m->grads.p, 0, (size_t)m->P * sizeof(float), ctx->stream));     // Network.ClearGradients, net.go:813-823
   const float* yp;
-  m->cur_first_sample = first_sample;
+  m->cur_first_sample = first_sample; m->cur_global_batch = global_batch;
   GN_TRY(forward(m, x_dev, B, &yp, true));
   for (auto& l : m->L) if (l.d.kind == GN_LAYER_DROPOUT)          // every rank moves the stream on by the whole global batch
     GN_LAUNCH(ctx, dropout_advance_kernel, 1, 1, 0, m->state.p + l.s_off, (unsigned long long)global_batch * (unsigned long long)l.in_size);
@@ -714,23 +755,44 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
     GN_CUDA(cudaStreamWaitEvent(ctx->stream, m->comm_done, 0));
     GN_CUDA(cudaEventRecord(m->ar1, ctx->stream));
   }
-  // Network.Step (net.go:260-284): NewStep() then StepInPlace with t = timestep + 1
-  m->timestep += 1;
+  // Network.Step (net.go:260-284): NewStep() then StepInPlace with t = timestep + 1.  The pass reads the status word
+  // first: after a bounded wait gave up it changes nothing.
   float inv = (float)(1.0 / (double)global_batch);                                        // net.go:703
   m->last_inv_batch = inv;
-  GN_TRY(adam_launch(ctx, m->params.p, m->grads.p, m->m1.p, m->v2.p, m->P, m->lr, m->b1, m->b2, m->eps, m->timestep + 1, inv));
+  GN_TRY(adam_launch(ctx, m->params.p, m->grads.p, m->m1.p, m->v2.p, m->P, m->lr, m->b1, m->b2, m->eps, m->timestep + 2, inv, ctx->d_status));
   GN_CUDA(cudaEventRecord(m->ev1, ctx->stream));
-  float hsum = 0.f;
-  GN_CUDA(cudaMemcpyAsync(&hsum, m->loss_sum.p, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  // one read-back for the caller: the loss sum and the status word land in the same pinned block, one wait
+  GN_CUDA(cudaMemcpyAsync(&m->h_ret[0], m->loss_sum.p, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+  GN_CUDA(cudaMemcpyAsync(&m->h_ret[1], ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
   GN_CUDA(cudaStreamSynchronize(ctx->stream));
-  if (mean_loss) *mean_loss = hsum / (float)global_batch;
+  return GN_OK;
+}
+
+static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B, int global_batch, int first_sample, float* mean_loss) {
+  Ctx* ctx = &m->ctx->c;
+  if (global_batch <= 0) { global_batch = B; first_sample = 0; }
+  if (B > m->cap) GN_TRY(alloc_activations(m, B));
+  int64_t launches0 = ctx->launches; ctx->gemm_flops = 0; ctx->gemm_launches = 0; ctx->gemm_ms = 0; ctx->ev_used = 0;
+  int rc = train_step_issue(m, x_dev, y_dev, B, global_batch, first_sample);
+  if (rc != GN_OK) {
+    // drain what was queued before the failure (both streams) so that nothing of this step runs after the call returned
+    const std::string msg = last_error();
+    if (ctx->comm_stream) cudaStreamSynchronize(ctx->comm_stream);
+    cudaStreamSynchronize(ctx->stream); cudaGetLastError();
+    last_error() = msg; return rc;
+  }
+  int st; memcpy(&st, &m->h_ret[1], sizeof(int));
+  if (st != 0) {    // the Adam pass saw the same word and left parameters, moments and the step counter alone
+    cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream); cudaStreamSynchronize(ctx->stream);
+    return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d); parameters and optimiser state are unchanged", st);
+  }
+  m->timestep += 1;
+  if (mean_loss) *mean_loss = m->h_ret[0] / (float)global_batch;
   m->stats.kernel_launches = ctx->launches - launches0;
   cudaEventElapsedTime(&m->stats.step_ms, m->ev0, m->ev1);
   m->stats.allreduce_ms = 0.f; if (ctx->world > 1) cudaEventElapsedTime(&m->stats.allreduce_ms, m->ar0, m->ar1);
   m->stats.gemm_flops = ctx->gemm_flops; m->stats.gemm_launches = ctx->gemm_launches; m->stats.gemm_ms = 0.f;
   if (ctx->profile) { float tot = 0.f; for (size_t i = 0; i < ctx->ev_used; i++) { float ms = 0.f; cudaEventElapsedTime(&ms, ctx->ev_pool[i].first, ctx->ev_pool[i].second); tot += ms; } m->stats.gemm_ms = tot; }
-  int st = 0; GN_CUDA(copy_d2h(ctx, &st, ctx->d_status, sizeof(int)));
-  if (st != 0) { cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream); cudaStreamSynchronize(ctx->stream); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
   return GN_OK;
 }
 
@@ -742,7 +804,14 @@ static int make_ctx(int device, int rank, int world, const unsigned char* id, gn
   GN_CUDA(cudaSetDevice(device));
   cudaDeviceProp prop; GN_CUDA(cudaGetDeviceProperties(&prop, device));
   if (prop.major != 10) return fail(GN_ERR_NO_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major, prop.minor);
-  std::unique_ptr<gn_ctx> c(new gn_ctx());
+  // a context that fails half way releases what it already holds
+  struct Guard { gn_ctx* c; ~Guard() { if (!c) return;
+      if (c->c.comm && c->c.nccl) c->c.nccl->CommDestroy(c->c.comm);
+      if (c->c.comm_stream) cudaStreamDestroy(c->c.comm_stream);
+      if (c->c.d_status) cudaFree(c->c.d_status);
+      if (c->c.stream) cudaStreamDestroy(c->c.stream);
+      delete c; } } guard{new gn_ctx()};
+  gn_ctx* c = guard.c;
   c->c.device = device; c->c.rank = rank; c->c.world = world; c->c.sm_count = prop.multiProcessorCount;
   GN_CUDA(cudaStreamCreateWithFlags(&c->c.stream, cudaStreamNonBlocking));
   GN_CUDA(cudaMalloc(&c->c.d_status, sizeof(int)));
@@ -751,12 +820,13 @@ static int make_ctx(int device, int rank, int world, const unsigned char* id, gn
   if (world > 1) {
     NcclApi* api = nccl_api(); if (!api) return fail(GN_ERR_NCCL, "libnccl.so.2 could not be loaded");
     NcclUniqueId uid; memcpy(uid.internal, id, GN_UNIQUE_ID_BYTES);
-    int rc = api->CommInitRank(&c->c.comm, world, uid, rank);
-    if (rc) return fail(GN_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString(rc));
     c->c.nccl = api;
+    int rc = api->CommInitRank(&c->c.comm, world, uid, rank);
+    if (rc) { c->c.comm = nullptr; return fail(GN_ERR_NCCL, "ncclCommInitRank: %s", api->GetErrorString(rc)); }
     GN_CUDA(cudaStreamCreateWithFlags(&c->c.comm_stream, cudaStreamNonBlocking));
   }
-  *out = c.release(); return GN_OK;
+  guard.c = nullptr;
+  *out = c; return GN_OK;
 }
 
 }  // namespace gn
@@ -808,6 +878,11 @@ int gn_ctx_world_size(gn_ctx* ctx, int* world_size, int* rank) {
   if (world_size) *world_size = ctx->c.world; if (rank) *rank = ctx->c.rank; return GN_OK;
 }
 
+int gn_ctx_set_spin_limit(gn_ctx* ctx, unsigned int polls) {
+  if (!ctx || !ctx->alive) return fail(GN_ERR_INVALID_ARG, "context is null or shut down");
+  ctx->c.spin_limit = polls == 0 ? TC_SPIN_LIMIT : polls; return GN_OK;
+}
+
 int gn_synchronize(gn_ctx* ctx) {
   if (!ctx || !ctx->alive) return fail(GN_ERR_INVALID_ARG, "context is null or shut down");
   GN_CUDA(cudaSetDevice(ctx->c.device)); GN_CUDA(cudaStreamSynchronize(ctx->c.stream)); return GN_OK;
@@ -852,10 +927,11 @@ int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int 
     GN_CUDA(copy_h2d(&ctx->c, m->state.p, init.data(), (size_t)m->NS * 4));
   }
   GN_CUDA(cudaEventCreate(&m->ev0)); GN_CUDA(cudaEventCreate(&m->ev1)); GN_CUDA(cudaEventCreate(&m->ar0)); GN_CUDA(cudaEventCreate(&m->ar1));
-  GN_CUDA(cudaEventCreateWithFlags(&m->comm_done, cudaEventDisableTiming));
+  GN_CUDA(cudaEventCreateWithFlags(&m->comm_done, cudaEventDisableTiming)); GN_CUDA(cudaEventCreateWithFlags(&m->gather_ev, cudaEventDisableTiming));
   m->layer_ev.resize(m->L.size() + 1);
   for (auto& e : m->layer_ev) GN_CUDA(cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
   m->scratch.resize(S_COUNT);
+  GN_CUDA(cudaHostAlloc((void**)&m->h_ret, 4 * sizeof(float), cudaHostAllocDefault));
   *out = m.release(); return GN_OK;
 }
 
@@ -867,7 +943,8 @@ int gn_model_destroy(gn_model* m) {
   m->L.clear(); m->scratch.clear(); m->state.release(); m->params.release(); m->grads.release(); m->m1.release(); m->v2.release();
   m->xin.release(); m->yin.release(); m->lossg.release(); m->loss_s.release(); m->loss_sum.release();
   if (m->ev0) cudaEventDestroy(m->ev0); if (m->ev1) cudaEventDestroy(m->ev1); if (m->ar0) cudaEventDestroy(m->ar0); if (m->ar1) cudaEventDestroy(m->ar1);
-  if (m->comm_done) cudaEventDestroy(m->comm_done); for (auto e : m->layer_ev) cudaEventDestroy(e); m->layer_ev.clear();
+  if (m->comm_done) cudaEventDestroy(m->comm_done); if (m->gather_ev) cudaEventDestroy(m->gather_ev); m->gather_ev = nullptr; for (auto e : m->layer_ev) cudaEventDestroy(e); m->layer_ev.clear();
+  if (m->h_ret) cudaFreeHost(m->h_ret); m->h_ret = nullptr;
   m->ev0 = m->ev1 = m->ar0 = m->ar1 = m->comm_done = nullptr; m->alive = false; return GN_OK;
 }
 
@@ -935,13 +1012,13 @@ int gn_adam_set_state(gn_model* m, const float* m1, const float* v, int64_t n, i
 
 int gn_train_batch_device(gn_model* m, const float* x_dev, const float* y_dev, int batch, int global_batch, int first_sample, float* mean_loss) {
   CHECK_MODEL(m); if (!x_dev || !y_dev || batch <= 0) return fail(GN_ERR_INVALID_ARG, "train_batch: null input or batch <= 0");
-  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  std::lock_guard<std::mutex> lk(m->mu); std::lock_guard<std::mutex> run_lk(m->ctx->c.run_mu); USE_DEVICE(m);
   return train_step(m, x_dev, y_dev, batch, global_batch, first_sample, mean_loss);
 }
 
 int gn_train_batch(gn_model* m, const float* x, const float* y, int batch, int global_batch, int first_sample, float* mean_loss) {
   CHECK_MODEL(m); if (!x || !y || batch <= 0) return fail(GN_ERR_INVALID_ARG, "train_batch: null input or batch <= 0");
-  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  std::lock_guard<std::mutex> lk(m->mu); std::lock_guard<std::mutex> run_lk(m->ctx->c.run_mu); USE_DEVICE(m);
   if (batch > m->cap) GN_TRY(alloc_activations(m, batch));
   cudaStream_t s = m->ctx->c.stream;
   GN_CUDA(cudaMemcpyAsync(m->xin.p, x, (size_t)batch * m->in_size * 4, cudaMemcpyHostToDevice, s));
@@ -951,13 +1028,13 @@ int gn_train_batch(gn_model* m, const float* x, const float* y, int batch, int g
 
 int gn_forward_batch(gn_model* m, const float* x, int batch, float* out) {
   CHECK_MODEL(m); if (!x || !out || batch <= 0) return fail(GN_ERR_INVALID_ARG, "forward_batch: null pointer or batch <= 0");
-  std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
+  std::lock_guard<std::mutex> lk(m->mu); std::lock_guard<std::mutex> run_lk(m->ctx->c.run_mu); USE_DEVICE(m);
   if (batch > m->cap) GN_TRY(alloc_activations(m, batch));
   cudaStream_t s = m->ctx->c.stream;
   GN_CUDA(cudaMemcpyAsync(m->xin.p, x, (size_t)batch * m->in_size * 4, cudaMemcpyHostToDevice, s));
   const float* yp; GN_TRY(forward(m, m->xin.p, batch, &yp, false));
   GN_CUDA(cudaMemcpyAsync(out, yp, (size_t)batch * m->out_size * 4, cudaMemcpyDeviceToHost, s));
-  GN_CUDA(cudaStreamSynchronize(s)); return GN_OK;
+  GN_CUDA(cudaStreamSynchronize(s)); return check_status_word(&m->ctx->c);
 }
 
 int gn_device_alloc(gn_ctx* ctx, int64_t n, float** dev) {
@@ -980,7 +1057,7 @@ int gn_model_set_profiling(gn_model* m, int level) { CHECK_MODEL(m); m->ctx->c.p
 
 int gn_op_gemm_nt(gn_ctx* ctx, int engine, int M, int N, int K, const float* A, const float* B, const float* bias, float* C) {
   if (!ctx || !ctx->alive || !A || !B || !C || M <= 0 || N <= 0 || K <= 0) return fail(GN_ERR_INVALID_ARG, "op_gemm_nt: bad argument");
-  Ctx* c = &ctx->c; GN_CUDA(cudaSetDevice(c->device));
+  Ctx* c = &ctx->c; std::lock_guard<std::mutex> run_lk(c->run_mu); GN_CUDA(cudaSetDevice(c->device));
   DevBuf dA, dB, dC, db; GN_TRY(dA.alloc((size_t)M * K)); GN_TRY(dB.alloc((size_t)N * K)); GN_TRY(dC.alloc((size_t)M * N)); if (bias) GN_TRY(db.alloc(N));
   GN_CUDA(cudaMemcpyAsync(dA.p, A, (size_t)M * K * 4, cudaMemcpyHostToDevice, c->stream)); GN_CUDA(cudaMemcpyAsync(dB.p, B, (size_t)N * K * 4, cudaMemcpyHostToDevice, c->stream));
   if (bias) GN_CUDA(cudaMemcpyAsync(db.p, bias, (size_t)N * 4, cudaMemcpyHostToDevice, c->stream));
@@ -988,14 +1065,12 @@ int gn_op_gemm_nt(gn_ctx* ctx, int engine, int M, int N, int K, const float* A, 
   if (engine == 1) { if (!gemm_tc_supported(c, g)) return fail(GN_ERR_UNSUPPORTED, "tcgen05 engine cannot run this shape (M=%d N=%d K=%d)", M, N, K); GN_TRY(gemm_tc(c, g)); }
   else GN_TRY(gemm_simt(c, g));
   GN_CUDA(cudaMemcpyAsync(C, dC.p, (size_t)M * N * 4, cudaMemcpyDeviceToHost, c->stream)); GN_CUDA(cudaStreamSynchronize(c->stream));
-  int st = 0; GN_CUDA(copy_d2h(c, &st, c->d_status, sizeof(int)));
-  if (st != 0) { cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream); cudaStreamSynchronize(c->stream); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
-  return GN_OK;
+  return check_status_word(c);
 }
 
 int gn_op_adam(gn_ctx* ctx, float* params, const float* grads, float* m1, float* v, int64_t n, float lr, float beta1, float beta2, float eps, int t, float grad_scale) {
   if (!ctx || !ctx->alive || !params || !grads || !m1 || !v || n <= 0) return fail(GN_ERR_INVALID_ARG, "op_adam: bad argument");
-  Ctx* c = &ctx->c; GN_CUDA(cudaSetDevice(c->device));
+  Ctx* c = &ctx->c; std::lock_guard<std::mutex> run_lk(c->run_mu); GN_CUDA(cudaSetDevice(c->device));
   DevBuf dp, dg, dm, dv; size_t nn = (size_t)n; GN_TRY(dp.alloc(nn + 4)); GN_TRY(dg.alloc(nn + 4)); GN_TRY(dm.alloc(nn + 4)); GN_TRY(dv.alloc(nn + 4));
   GN_CUDA(copy_h2d(c, dp.p, params, nn * 4)); GN_CUDA(copy_h2d(c, dg.p, grads, nn * 4));
   GN_CUDA(copy_h2d(c, dm.p, m1, nn * 4)); GN_CUDA(copy_h2d(c, dv.p, v, nn * 4));
@@ -1009,7 +1084,7 @@ int gn_op_attention(gn_ctx* ctx, int engine, int B, int T, int D, int H, int cau
                     float* O, float* M, float* L, float* dQ, float* dK, float* dV) {
   if (!ctx || !ctx->alive || !Q || !K || !V || !O || B <= 0 || T <= 0 || D <= 0 || H <= 0 || D % H) return fail(GN_ERR_INVALID_ARG, "op_attention: bad argument");
   if (dO && (!dQ || !dK || !dV)) return fail(GN_ERR_INVALID_ARG, "op_attention: dO given without dQ, dK, dV");
-  Ctx* c = &ctx->c; GN_CUDA(cudaSetDevice(c->device));
+  Ctx* c = &ctx->c; std::lock_guard<std::mutex> run_lk(c->run_mu); GN_CUDA(cudaSetDevice(c->device));
   const int hd = D / H; const size_t n = (size_t)B * T * D, ns = (size_t)B * H * T;
   if (!attn_fused_supported(hd, D)) return fail(GN_ERR_UNSUPPORTED, "op_attention: head size %d", hd);
   if (engine == 1 && !attn_tc_supported(c, hd, T, B, H, D)) return fail(GN_ERR_UNSUPPORTED, "tcgen05 attention cannot run this shape (head size %d, T=%d)", hd, T);
@@ -1028,9 +1103,7 @@ int gn_op_attention(gn_ctx* ctx, int engine, int B, int T, int D, int H, int cau
   GN_CUDA(copy_d2h(c, O, o.p, n * 4));
   if (M) GN_CUDA(copy_d2h(c, M, m.p, ns * 4));
   if (L) GN_CUDA(copy_d2h(c, L, l.p, ns * 4));
-  int st = 0; GN_CUDA(copy_d2h(c, &st, c->d_status, sizeof(int)));
-  if (st != 0) { cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream); cudaStreamSynchronize(c->stream); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
-  return GN_OK;
+  return check_status_word(c);
 }
 
 }  // extern "C"

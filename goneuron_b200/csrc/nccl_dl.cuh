@@ -14,6 +14,7 @@ struct NcclApi {
   int (*CommInitRank)(void** comm, int nranks, NcclUniqueId id, int rank) = nullptr;
   int (*CommDestroy)(void* comm) = nullptr;
   int (*AllReduce)(const void* send, void* recv, size_t count, int dtype, int op, void* comm, cudaStream_t s) = nullptr;
+  int (*AllGather)(const void* send, void* recv, size_t sendcount, int dtype, void* comm, cudaStream_t s) = nullptr;
   int (*CommGetAsyncError)(void* comm, int* err) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
 };
@@ -29,9 +30,10 @@ inline NcclApi* nccl_api() {
     api.CommInitRank = (decltype(api.CommInitRank))dlsym(api.handle, "ncclCommInitRank");
     api.CommDestroy = (decltype(api.CommDestroy))dlsym(api.handle, "ncclCommDestroy");
     api.AllReduce = (decltype(api.AllReduce))dlsym(api.handle, "ncclAllReduce");
+    api.AllGather = (decltype(api.AllGather))dlsym(api.handle, "ncclAllGather");
     api.CommGetAsyncError = (decltype(api.CommGetAsyncError))dlsym(api.handle, "ncclCommGetAsyncError");
     api.GetErrorString = (decltype(api.GetErrorString))dlsym(api.handle, "ncclGetErrorString");
-    ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.GetErrorString;
+    ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.AllGather && api.GetErrorString;
   });
   return ok ? &api : nullptr;
 }

@@ -466,8 +466,11 @@ __global__ void scale_kernel(float* __restrict__ x, long n, float s) {
 // code does, so that the update is bit-identical to the CPU path for identical gradients.
 //   g' = g * grad_scale (the 1/batch averaging of net.go:702-706, folded into this pass)
 //   m = b1*m + (1-b1)*g' ; v = b2*v + (1-b2)*g'*g' ; p -= effLR * m / (sqrt(v) + eps)
+// `status` (may be null): the context's status word; when a bounded wait of an earlier kernel of this step gave up, the
+// gradients are not trustworthy and the pass leaves the parameters and moments untouched.
 __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v, long n,
-                            float effLR, float b1, float b2, float omb1, float omb2, float eps, float grad_scale) {
+                            float effLR, float b1, float b2, float omb1, float omb2, float eps, float grad_scale, const int* __restrict__ status) {
+  if (status && *status != 0) return;
   long n4 = n >> 2;
   float4* p4 = reinterpret_cast<float4*>(p); const float4* g4 = reinterpret_cast<const float4*>(g);
   float4* m4 = reinterpret_cast<float4*>(m); float4* v4 = reinterpret_cast<float4*>(v);
@@ -510,6 +513,14 @@ __global__ void bn_running_kernel(const float* __restrict__ stat, float* __restr
   int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= C) return;
   float rm = run[c], rv = run[C + c];
   for (int b = 0; b < B; b++) { rm = (1.f - mom) * rm + mom * stat[(long)b * C + c]; rv = (1.f - mom) * rv + mom * stat[2 * BC + (long)b * C + c]; }
+  run[c] = rm; run[C + c] = rv;
+}
+// The same walk over per-sample statistics gathered from every rank (mean and variance as separate [B, C] arrays in
+// global sample order), so that every replica applies the updates of the whole global batch in the reference's order.
+__global__ void bn_running_gathered_kernel(const float* __restrict__ mean, const float* __restrict__ var, float* __restrict__ run, int B, int C, float mom) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x; if (c >= C) return;
+  float rm = run[c], rv = run[C + c];
+  for (int b = 0; b < B; b++) { rm = (1.f - mom) * rm + mom * mean[(long)b * C + c]; rv = (1.f - mom) * rv + mom * var[(long)b * C + c]; }
   run[c] = rm; run[C + c] = rv;
 }
 // inference mode: running statistics (batchnorm2d.go:492-509)

@@ -122,6 +122,12 @@ int gn_init_rank(int device, int rank, int world_size,
 int gn_shutdown(gn_ctx* ctx);                 /* idempotent; mirrors MetalDevice.Close */
 int gn_ctx_world_size(gn_ctx* ctx, int* world_size, int* rank);
 int gn_synchronize(gn_ctx* ctx);              /* drains the context's stream (metal.go:199 waitForMetal) */
+/* Number of polls a device-side wait (on an mbarrier of the tensor-core kernels) makes before it gives up; 0 restores
+ * the default (2^24).  A wait that gives up stops its kernel's pipeline, the call returns GN_ERR_TIMEOUT, and
+ * gn_train_batch leaves parameters and optimiser state unchanged; the context stays usable.  The failure-detection
+ * tests set a limit of 1 to make a wait run out without faulting the GPU.  No counterpart in the reference, whose
+ * Metal dispatch blocks without a bound (metal.go:199). */
+int gn_ctx_set_spin_limit(gn_ctx* ctx, unsigned int polls);
 /* CUDA-event stopwatch on the stream every kernel of this context is launched on: start records an
  * event, stop records a second one, waits for it and returns the device time between the two. */
 int gn_timer_start(gn_ctx* ctx);
@@ -208,7 +214,7 @@ int gn_model_set_profiling(gn_model* m, int level);
  *      restatement; all pointers are HOST memory, copied in and out) --------- */
 
 /* C[M,N] = A[M,K] * B[N,K]^T (+ bias[N]) ; row-major, fp32 in/out.
- * engine: 0 = SIMT fp32, 1 = tcgen05 split-operand (TF32 + 2 x BF16, fp32-level accuracy).  (Dense forward, layer.go:406 /
+ * engine: 0 = SIMT fp32, 1 = tcgen05 split-operand (three BF16 products per fp32 product, fp32-level accuracy).  (Dense forward, layer.go:406 /
  * matmul_optimized.go:18-152 at batch level.) */
 int gn_op_gemm_nt(gn_ctx* ctx, int engine, int M, int N, int K,
                   const float* A, const float* B, const float* bias, float* C);
@@ -232,7 +238,7 @@ int gn_op_attention(gn_ctx* ctx, int engine, int B, int T, int D, int H, int cau
  * counterpart in the reference.  A, B, bias (may be NULL) and C are DEVICE pointers supplied by the caller
  * (A [M,K], B [N,K], C [M,N], row-major, dense); the operand planes live in a fixed 16 MiB array inside the
  * library image, which every GPU that loads the library holds until the process exits.  Limit:
- * 2*(M+N)*roundup8(K) <= 4 Mi floats, else GN_ERR_INVALID_ARG.  The entry point calls no cudaMalloc / cudaFree.
+ * (M+N)*roundup8(K) <= 4 Mi floats, else GN_ERR_INVALID_ARG.  The entry point calls no cudaMalloc / cudaFree.
  * The first call on each device resolves the array's device address; make it before any stream capture.
  * All calls on one GPU share the array (it keeps the last call's planes; each call rewrites what it reads):
  * calls that overlap on the GPU race, so issue them one after the other. */

@@ -57,14 +57,19 @@ def assert_grads_close(layers, got, ref, tol=TOL, floor=None):
     """Every parameter tensor's gradient within `tol` normalised error of the reference value.
     `floor` (the literal-fp32 CPU path's own distance from the double twin) loosens the bound for tensors
     whose value the reference itself only resolves to fp32 cancellation noise."""
-    worst = []
+    worst, loosened = [], []
     for name, s, e in tensor_slices(layers):
         err = norm_err(got[s:e], ref[s:e])
         lim = tol
         if floor is not None:
             lim = max(tol, 4.0 * norm_err(floor[s:e], ref[s:e]))
+        if lim > tol:
+            loosened.append((name, err, lim))
         worst.append((err / lim, name, err, lim))
     worst.sort(reverse=True)
+    # every tensor whose bound was loosened is named in the test output, with the error it was allowed
+    for name, err, lim in loosened:
+        print(f"loosened bound: {name}: error {err:.3e}, bound {lim:.3e} (4 x the literal fp32 path's own distance from the double twin)")
     bad = [w for w in worst if w[0] > 1.0]
     assert not bad, "gradient tensors outside tolerance: " + ", ".join(f"{n}: {e:.3e} > {l:.1e}" for _, n, e, l in bad[:6])
     return worst[0]

@@ -50,6 +50,10 @@ CASES = [
     ("mlp_act", dict(act=D.ELU), 12, 1), ("mlp_act", dict(act=D.ELU, alpha=0.7), 12, 1),
     ("mlp_rms", {}, 16, 1), ("mlp_rms", dict(in_size=10, hidden=300, norm=100, classes=3), 5, 1),            # RMSNorm
     ("cnn1d", {}, 12, 1), ("cnn1d", dict(length=17, c0=2, c1=5, c2=3, classes=3, act=D.GELU), 7, 1),           # Conv1D
+    # the large Transformer at its real width (vocabulary 32000, width 1024, 16 heads of 64, 512 tokens, FFN 4096): the plan,
+    # the strides, the sliced head contraction and the block wiring at full size; small batches keep the CPU checker affordable
+    ("transformer_large", dict(n_blocks=2), 3, 1),
+    ("transformer_large", {}, 4, 2),                                # all eight blocks, two reference workers
 ]
 
 
@@ -71,7 +75,8 @@ def test_train_step_parity(device, oracle, name, kw, batch, W):
     model.Close()
 
     assert abs(loss - ref_loss) <= TOL * max(1.0, abs(ref_loss)), (loss, ref_loss)
-    assert_grads_close(layers, grads, ref.grads, floor=lit.grads if small else None)
+    worst = assert_grads_close(layers, grads, ref.grads, floor=lit.grads if small else None)
+    print(f"{name} batch {batch} W {W}: loss {loss:.6f} (cpu {ref_loss:.6f}); worst gradient tensor {worst[1]} at {worst[2]:.2e} of {worst[3]:.1e}")
     assert_weights_close(after, ref.params, params, ref.grads, lr)
     # the optimiser itself is bit-exact: the literal CPU Adam applied to the GPU's gradients
     p2, m2, v2 = oracle.adam(params, grads, np.zeros_like(params), np.zeros_like(params), lr, 0.9, 0.999, 1e-8, 2)
