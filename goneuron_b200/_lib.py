@@ -22,7 +22,8 @@ EXPORTS = [
 
 class StepStats(C.Structure):
     _fields_ = [("kernel_launches", C.c_int64), ("step_ms", C.c_float), ("allreduce_ms", C.c_float),
-                ("gemm_ms", C.c_float), ("gemm_launches", C.c_int64), ("gemm_flops", C.c_double)]
+                ("gemm_ms", C.c_float), ("gemm_launches", C.c_int64), ("gemm_flops", C.c_double),
+                ("gemm_bytes", C.c_double), ("split_bytes", C.c_double)]
 
 
 class GoNeuronCudaError(RuntimeError):

@@ -154,6 +154,88 @@ def init_params(layers, rng):
     return np.concatenate(parts) if parts else np.zeros(0, np.float32)
 
 
+class ReferenceRNG:
+    """The reference's own generator (internal/layer/layer.go:61-75): the 64-bit LCG s <- s * 6364136223846793005 + 1,
+    RandFloat() = float32(s >> 33) / float32(1 << 31).  Vectorised: n consecutive outputs by doubling (the m-step map of an
+    affine recurrence is again affine), in wrapping uint64 arithmetic."""
+    A = np.uint64(6364136223846793005)
+
+    def __init__(self, seed):
+        self.state = np.uint64(seed & 0xFFFFFFFFFFFFFFFF)
+
+    def rand_float(self, n):
+        """The next n values of RandFloat() as float32."""
+        if n <= 0:
+            return np.zeros(0, np.float32)
+        with np.errstate(over="ignore"):
+            st = np.empty(n, np.uint64)
+            st[0] = self.state * self.A + np.uint64(1)
+            am, cm, m = self.A, np.uint64(1), 1            # the m-step map s -> am * s + cm
+            while m < n:
+                k = min(m, n - m)
+                st[m:m + k] = st[:k] * am + cm
+                cm = am * cm + cm
+                am = am * am
+                m *= 2
+        self.state = st[-1]
+        return (st >> np.uint64(33)).astype(np.float32) / np.float32(1 << 31)
+
+
+def reference_init_params(layers):
+    """Flat parameter vector exactly as the reference's constructors initialise it, generator seeds included
+    (Dense: layer.go:312-319, seed in*1000 + out*100 + 42; Conv2D: conv2d.go:126-134, seed 42; LSTM: lstm.go:181-200, seed
+    in*1000 + out*100 + 142, forget-gate bias 1; Embedding: embedding.go:50-56, seed 42; positional table:
+    transformer.go:58-63, seed T + d + 42; LayerNorm gamma 1 / beta 0: layernorm.go:92-95).  Every expression is evaluated in
+    float32, operation by operation, as the Go code does.  Equal-shaped layers start identical, as in the reference.
+    TransformerBlock parameters are all zero after the reference's Build (transformer.go:367-379, :1035-1056): they are
+    returned as zeros here too, which is why the Transformer configs are always run with uploaded weights instead."""
+    f32 = np.float32
+    parts = []
+    for l in layers:
+        k = l.kind
+        if k == D.DENSE:
+            i, o = l.in_size, l.out_size
+            scale = f32(math.sqrt(2.0 / (float(i) + float(o))))
+            rng = ReferenceRNG(i * 1000 + o * 100 + 42)
+            w = rng.rand_float(o * i) * f32(2) * scale - scale
+            b = rng.rand_float(o) * f32(0.2) - f32(0.1)
+            parts += [w.astype(f32), b.astype(f32)]
+        elif k == D.CONV2D:
+            n = l.out_size * l.in_size * l.kernel * l.kernel
+            scale = f32(math.sqrt(2.0 / float(l.in_size * l.kernel * l.kernel)))
+            rng = ReferenceRNG(42)
+            w = rng.rand_float(n) * f32(2) * scale - scale
+            b = rng.rand_float(l.out_size) * f32(0.2) - f32(0.1)
+            parts += [w.astype(f32), b.astype(f32)]
+        elif k == D.LSTM_UNROLLED:
+            H, i = l.out_size, l.in_size
+            si = f32(math.sqrt(2.0 / float(i + 4 * H))); sr = f32(math.sqrt(2.0 / float(H + 4 * H)))
+            rng = ReferenceRNG(i * 1000 + H * 100 + 142)
+            r = rng.rand_float(4 * H * (i + H)).reshape(4 * H, i + H)        # per gate row: in input weights, then H recurrent weights
+            wx = r[:, :i] * f32(2) * si - si
+            wh = r[:, i:] * f32(2) * sr - sr
+            b = np.zeros(4 * H, f32); b[H:2 * H] = 1.0
+            parts += [np.ascontiguousarray(wx, f32).ravel(), np.ascontiguousarray(wh, f32).ravel(), b]
+        elif k == D.EMBEDDING:
+            scale = f32(math.sqrt(3.0 / float(l.out_size)))
+            parts.append((scale * (f32(2) * ReferenceRNG(42).rand_float(l.in_size * l.out_size) - f32(1))).astype(f32))
+        elif k == D.POSENC:
+            scale = f32(math.sqrt(1.0 / float(l.dim)))
+            parts.append((ReferenceRNG(l.seq_len + l.dim + 42).rand_float(l.seq_len * l.dim) * f32(2) * scale - scale).astype(f32))
+        elif k == D.TRANSFORMER_BLOCK:
+            d, f = l.dim, l.ff_dim
+            parts.append(np.zeros(4 * (d * d + d) + 4 * d + (d * f + f) + (f * d + d), f32))
+        elif k == D.LAYERNORM:
+            parts += [np.ones(l.dim, f32), np.zeros(l.dim, f32)]
+        elif k in (D.RMSNORM,):
+            parts.append(np.ones(l.dim, f32))
+        elif k == D.BATCHNORM2D:
+            parts += [np.ones(l.in_size, f32), np.zeros(l.in_size, f32)]
+        elif k == D.CONV1D:
+            raise ValueError("reference_init_params: Conv1D is not one of the layers whose reference initialiser is restated")
+    return np.concatenate(parts) if parts else np.zeros(0, f32)
+
+
 def make_inputs(name, layers, batch, rng):
     """Seeded synthetic batch with the shapes and value distributions the benchmark names."""
     first, last = layers[0], layers[-1]
@@ -184,11 +266,14 @@ def make_inputs(name, layers, batch, rng):
     return x, y
 
 
-def make_case(name, batch=None, seed=None, **override):
-    """(layers, loss, params, x, y, lr) for a named config; draw order weights -> inputs -> labels."""
+def make_case(name, batch=None, seed=None, init="glorot", **override):
+    """(layers, loss, params, x, y, lr) for a named config; draw order weights -> inputs -> labels.
+    init = "reference" replaces the seeded Glorot weights by the reference's own deterministic initialisation."""
     layers, loss, b, lr = build(name, **override)
     batch = batch or b
     rng = np.random.Generator(np.random.PCG64(seed if seed is not None else SEEDS[name]))
     params = init_params(layers, rng)
+    if init == "reference":
+        params = reference_init_params(layers)
     x, y = make_inputs(name, layers, batch, rng)
     return layers, loss, params, x, y, lr

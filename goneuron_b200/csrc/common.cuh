@@ -38,6 +38,7 @@ struct Ctx {
   // contraction profiling (gn_model_set_profiling)
   int profile = 0;
   double gemm_flops = 0; float gemm_ms = 0; int64_t gemm_launches = 0;
+  double gemm_bytes = 0, split_bytes = 0;   // algorithmic bytes of the step's contraction launches (operand planes + output + residual) / of its operand split passes
   std::vector<std::pair<cudaEvent_t, cudaEvent_t>> ev_pool; size_t ev_used = 0;
   int* d_status = nullptr;         // device word set by kernels whose bounded waits gave up
   bool tc_ok = false;              // tcgen05 engine usable (driver entry point for tensor maps found)

@@ -269,9 +269,11 @@ __global__ void avgpool_bwd_kernel(const float* __restrict__ g, float* __restric
 // 4H pre-activation rows, so only the input gate receives Wx*x + Wh*h; forget, cell and output gates see
 // their biases alone and are constant over time.
 // Saves per (sample, t): input-gate pre-activation, cell state, hidden state.
+// `xproj` != 0: pre_i already holds the input projection Wx[0:H] x_t of every (sample, t) (one tensor-core contraction
+// over all B*T rows, issued before this kernel); the kernel then only runs the recurrent part.
 __global__ void lstm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ Wx, const float* __restrict__ Wh, const float* __restrict__ bias,
                                 float* __restrict__ pre_i, float* __restrict__ c_all, float* __restrict__ h_all, float* __restrict__ out,
-                                int T, int in, int H, int return_seq) {
+                                int T, int in, int H, int return_seq, int xproj) {
   extern __shared__ float sm[];
   float* WhT = sm;                 // [H][H]  WhT[j*H+i] = Wh[i,j], rows 0..H-1 of the 4H
   float* WxT = WhT + (long)H * H;  // [in][H]
@@ -279,19 +281,20 @@ __global__ void lstm_fwd_kernel(const float* __restrict__ x, const float* __rest
   float* xbuf = hbuf + 2 * H;        // [in]
   const int s = blockIdx.x, i = threadIdx.x;
   for (int e = threadIdx.x; e < H * H; e += blockDim.x) { int r = e / H, j = e % H; WhT[j * H + r] = Wh[e]; }
-  for (int e = threadIdx.x; e < H * in; e += blockDim.x) { int r = e / in, j = e % in; WxT[j * H + r] = Wx[e]; }
+  if (!xproj) for (int e = threadIdx.x; e < H * in; e += blockDim.x) { int r = e / in, j = e % in; WxT[j * H + r] = Wx[e]; }
   if (i < H) { hbuf[i] = 0.f; hbuf[H + i] = 0.f; }
   float bi = 0.f, fg = 0.f, cg = 0.f, og = 0.f, c = 0.f;
   if (i < H) { bi = bias[i]; fg = act_fwd(GN_ACT_SIGMOID, bias[H + i]); cg = act_fwd(GN_ACT_TANH, bias[2 * H + i]); og = act_fwd(GN_ACT_SIGMOID, bias[3 * H + i]); }
   __syncthreads();
   const float* xs = x + (long)s * T * in;
   for (int t = 0; t < T; t++) {
-    for (int e = threadIdx.x; e < in; e += blockDim.x) xbuf[e] = xs[(long)t * in + e];
+    if (!xproj) { for (int e = threadIdx.x; e < in; e += blockDim.x) xbuf[e] = xs[(long)t * in + e]; }
     __syncthreads();
     const float* hp = hbuf + (t & 1) * H; float* hn = hbuf + ((t + 1) & 1) * H;
     if (i < H) {
       float sx = 0.f;
-      for (int j = 0; j < in; j++) sx = fmaf(WxT[j * H + i], xbuf[j], sx);
+      if (xproj) sx = pre_i[((long)s * T + t) * H + i];
+      else for (int j = 0; j < in; j++) sx = fmaf(WxT[j * H + i], xbuf[j], sx);
       float pre = bi + sx;
       for (int j = 0; j < H; j++) pre = fmaf(WhT[j * H + i], hp[j], pre);
       float ig = act_fwd(GN_ACT_SIGMOID, pre);

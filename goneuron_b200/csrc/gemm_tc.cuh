@@ -153,6 +153,7 @@ struct TcParams {
   const float* mask; long mask_ld; int mask_group;    // optional gate, see GemmDesc::mask
   const float* isa = nullptr; const float* isb = nullptr;   // inverse row scales of the operand planes: [nbatch][M], [nbatch][N]
   unsigned spin_limit = TC_SPIN_LIMIT;                // polls per wait before the kernel gives up
+  int nchw_P = 0;      // > 0: output row r = (sample r / P, position r % P) is stored as C[sample][col][position] (N channels of P positions)
 };
 
 // Epilogue of one output tile, executed by one warp for its TMEM lane quadrant: one output row per thread
@@ -218,7 +219,8 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
           if (Rrow) v += Rrow[col];
           if (ep.act == GN_ACT_RELU) v = fmaxf(v, 0.f);
           if (Mrow && !(Mrow[col] > 0.f)) v = 0.f;
-          Crow[col] = v;
+          if (ep.nchw_P > 0) C[((long)(row / ep.nchw_P) * ep.N + col) * ep.nchw_P + row % ep.nchw_P] = v;
+          else Crow[col] = v;
         }
       }
     }
@@ -493,6 +495,20 @@ inline size_t bf_plane_floats(long nbatch, long rows, long ldp) { return (size_t
 struct TcScratch { DevBuf a, b, sa, sb, mx; const float* last_a = nullptr; int last_m = 0, last_k = 0; long last_ld = 0; };
 inline TcScratch& tc_scratch(Ctx* ctx) { if (!ctx->tc_scratch) ctx->tc_scratch = ctx->own(new TcScratch()); return *static_cast<TcScratch*>(ctx->tc_scratch); }
 
+// Operand planes for `nbatch` problems of rows x K in the context's scratch (which = 0: A side, 1: B side).
+inline int tc_planes(Ctx* ctx, int which, long nbatch, long rows, int K, BfPlanes* out) {
+  TcScratch& sc = tc_scratch(ctx);
+  const int ldp = tc_ldp(K); const size_t n = bf_plane_floats(nbatch, rows, ldp), ns = (size_t)nbatch * rows;
+  if (rows > 0x7fffffffL || nbatch > 65535) return fail(GN_ERR_UNSUPPORTED, "tc_planes: operand too large");
+  DevBuf& pl = which == 0 ? sc.a : sc.b; DevBuf& scl = which == 0 ? sc.sa : sc.sb;
+  if (pl.n < n) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(pl.alloc(n)); }
+  if (scl.n < ns) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(scl.alloc(ns + 1024)); }
+  if (sc.mx.n < ns) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.mx.alloc(ns + 1024)); }
+  if (which == 0) sc.last_a = nullptr;
+  *out = BfPlanes{reinterpret_cast<__half*>(pl.p), scl.p, (int)rows, K, ldp, (int)nbatch}; return GN_OK;
+}
+inline int* tc_rowmax_buf(Ctx* ctx) { return reinterpret_cast<int*>(tc_scratch(ctx).mx.p); }
+
 template <int BN> inline bool tc_set_smem() { return cudaFuncSetAttribute(gemm_tc_persist_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcCfg<BN>::SMEM_BYTES) == cudaSuccess; }
 inline void tc_init(Ctx* ctx) {
   ctx->tc_ok = false;
@@ -546,6 +562,7 @@ inline int tc_split(Ctx* ctx, const TcSrc& src, const BfPlanes& p, int* mx) {
     GN_LAUNCH(ctx, colmax_kernel, dim3(cdiv(p.rows, 64), cdiv(p.K, 256), p.nbatch), 256, 0, src, p.rows, p.K, mx);
     GN_LAUNCH(ctx, split2_cols_kernel, dim3(cdiv(p.ldp, 64), cdiv(p.rows, 64), p.nbatch), 256, 0, src, p.rows, p.K, p.p0(), p.p1(), (const int*)mx, p.inv_scale, p.ldp);
   } else return fail(GN_ERR_UNSUPPORTED, "tc_split: neither stride of the operand is 1");
+  ctx->split_bytes += 8.0 * (double)p.nbatch * p.rows * p.K;
   return check_launch("tc_split");
 }
 
@@ -580,7 +597,13 @@ inline int tc_launch(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcPar
   bool vec = ep.N % 4 == 0 && ep.ldc % 4 == 0 && ep.c_b1 % 4 == 0 && ep.c_b2 % 4 == 0 && a16(ep.C) && (!ep.bias || a16(ep.bias)) && a16(ep.isb);
   if (ep.R) vec = vec && ep.ldr % 4 == 0 && ep.r_b1 % 4 == 0 && ep.r_b2 % 4 == 0 && a16(ep.R);
   if (ep.mask) vec = vec && ep.mask_ld % 4 == 0 && a16(ep.mask);
+  if (ep.nchw_P > 0) { if (ep.R || A.nbatch != 1) return fail(GN_ERR_UNSUPPORTED, "tc_launch: NCHW store with a residual or a batch"); vec = false; }
   if (vec) ep.flags |= TC_FLAG_VEC;
+  {
+    double by = 4.0 * ((double)ep.M + ep.N) * ep.K + 4.0 * (double)ep.M * ep.N * (ep.R ? 2 : 1);
+    if (ep.flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0)) by *= 0.5;
+    ctx->gemm_bytes += by * A.nbatch;
+  }
   if (bn == 64) return tc_launch_persist<64>(ctx, A, B, ep);
   if (bn == 256) return tc_launch_persist<256>(ctx, A, B, ep);
   return tc_launch_persist<128>(ctx, A, B, ep);
@@ -624,15 +647,11 @@ inline bool gemm_tc_eligible(Ctx* ctx, const GemmDesc& g) {
 inline int gemm_tc(Ctx* ctx, const GemmDesc& g) {
   if (!gemm_tc_supported(ctx, g)) return fail(GN_ERR_UNSUPPORTED, "tcgen05 engine cannot run this contraction");
   TcScratch& sc = tc_scratch(ctx);
-  const int nb = g.batch1 * g.batch2, ldp = tc_ldp(g.K);
-  const size_t na = bf_plane_floats(nb, g.M, ldp), nbb = bf_plane_floats(nb, g.N, ldp), nsa = (size_t)nb * g.M, nsb = (size_t)nb * g.N;
-  if (sc.a.n < na) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.a.alloc(na)); sc.last_a = nullptr; }
-  if (sc.b.n < nbb) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.b.alloc(nbb)); }
-  if (sc.sa.n < nsa) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.sa.alloc(nsa + 1024)); sc.last_a = nullptr; }
-  if (sc.sb.n < nsb) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.sb.alloc(nsb + 1024)); }
-  if (sc.mx.n < std::max(nsa, nsb)) { GN_CUDA(cudaStreamSynchronize(ctx->stream)); GN_TRY(sc.mx.alloc(std::max(nsa, nsb) + 1024)); }
-  BfPlanes A{reinterpret_cast<__half*>(sc.a.p), sc.sa.p, g.M, g.K, ldp, nb}, B{reinterpret_cast<__half*>(sc.b.p), sc.sb.p, g.N, g.K, ldp, nb};
-  int* mx = reinterpret_cast<int*>(sc.mx.p);
+  const int nb = g.batch1 * g.batch2;
+  const float* last_a = sc.last_a; const float* pa = sc.a.p; const float* psa = sc.sa.p;   // tc_planes() forgets the A planes' origin when it hands the buffer out
+  BfPlanes A, B; GN_TRY(tc_planes(ctx, 0, nb, g.M, g.K, &A)); GN_TRY(tc_planes(ctx, 1, nb, g.N, g.K, &B));
+  int* mx = tc_rowmax_buf(ctx);
+  sc.last_a = (sc.a.p == pa && sc.sa.p == psa) ? last_a : nullptr;                          // still valid unless a buffer was replaced
   if (g.reuse_a_planes && nb == 1 && sc.last_a == g.A && sc.last_m == g.M && sc.last_k == g.K && sc.last_ld == g.sa_m && g.sa_k == 1) {
     // same tensor as the previous call (the Q, K and V projections share their input): planes still valid
   } else {

@@ -25,6 +25,7 @@
 #include "conv_lstm.cuh"
 #include "attention.cuh"
 #include "attention_tc.cuh"
+#include "conv_tc.cuh"
 #include "nccl_dl.cuh"
 
 namespace gn {
@@ -104,7 +105,7 @@ struct gn_model {
 
 namespace gn {
 
-enum Slot { S_BNG = 0, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
 
 static int ensure(gn_model* m, int slot, size_t n, float** out) {
   if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
@@ -318,8 +319,13 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
       case GN_LAYER_CONV2D: {
         ConvShape c{B, d.in_size, d.out_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
                     (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
-        long n = (long)B * l.out_size;
-        GN_LAUNCH(ctx, conv2d_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, p, p + (long)d.out_size * d.in_size * d.kernel * d.kernel, l.z.p, l.out.p, c, d.activation, act_alpha_of(d.activation, d.reserved));
+        long n = (long)B * l.out_size; const float* bias = p + (long)d.out_size * d.in_size * d.kernel * d.kernel;
+        if (!force_simt_engine() && conv_tc_supported(ctx, c)) {
+          // implicit GEMM on the tensor cores; bias and ReLU in the epilogue, other activations from the kept pre-activation
+          const bool in_epilogue = d.activation == GN_ACT_LINEAR || d.activation == GN_ACT_RELU;
+          GN_TRY(conv_tc_forward(ctx, c, cur, p, bias, in_epilogue ? l.out.p : l.z.p, in_epilogue ? d.activation : GN_ACT_LINEAR));
+          if (!in_epilogue) GN_LAUNCH(ctx, act_forward_kernel, ew_grid(ctx, n), 256, 0, l.z.p, l.out.p, n, d.activation, act_alpha_of(d.activation, d.reserved));
+        } else GN_LAUNCH(ctx, conv2d_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, p, bias, l.z.p, l.out.p, c, d.activation, act_alpha_of(d.activation, d.reserved));
         cur = l.out.p; break; }
       case GN_LAYER_MAXPOOL2D: {
         PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
@@ -352,8 +358,16 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         size_t smem = ((size_t)H * H + (size_t)in * H + 2 * H + in) * sizeof(float);
         if (smem > 200 * 1024) return fail(GN_ERR_UNSUPPORTED, "LSTM of hidden size %d needs %zu bytes of shared memory", H, smem);
         GN_CUDA(cudaFuncSetAttribute(lstm_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // The input projection has no recurrence in it: Wx[0:H] x_t for all B*T rows is one contraction on the tensor cores
+        // (only the first H of the 4H gate rows receive it, lstm.go:319-326, :1065-1101); the kernel then adds the bias and
+        // the recurrent product step by step.
+        int xproj = 0;
+        {
+          GemmDesc g; g.M = B * d.seq_len; g.N = H; g.K = in; g.A = cur; g.sa_m = in; g.sa_k = 1; g.B = p; g.sb_k = 1; g.sb_n = in; g.C = l.pre_i.p; g.ldc = H;
+          if (!force_simt_engine() && gemm_tc_supported(ctx, g)) { GN_TRY(gemm_tc(ctx, g)); ctx->gemm_flops += 2.0 * g.M * (double)g.N * g.K; ctx->gemm_launches++; xproj = 1; }
+        }
         GN_LAUNCH(ctx, lstm_fwd_kernel, B, threads, smem, cur, p, p + (long)4 * H * in, p + (long)4 * H * in + (long)4 * H * H,
-                  l.pre_i.p, l.c_all.p, l.h_all.p, l.out.p, d.seq_len, in, H, d.return_seq);
+                  l.pre_i.p, l.c_all.p, l.h_all.p, l.out.p, d.seq_len, in, H, d.return_seq, xproj);
         cur = l.out.p; break; }
       case GN_LAYER_EMBEDDING: {
         // fused with a directly following PositionalEncoding
@@ -361,7 +375,7 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         bool fuse = li + 1 < m->L.size() && m->L[li + 1].d.kind == GN_LAYER_POSENC && m->L[li + 1].d.dim == d.out_size;
         if (fuse) P = m->params.p + m->L[li + 1].p_off;
         float* dst = fuse ? m->L[li + 1].out.p : l.out.p;
-        GN_LAUNCH(ctx, embedding_fwd_kernel, (unsigned)tokens, 128, 0, cur, p, P, dst, tokens, d.seq_len, d.out_size, d.in_size, (int*)l.idx.p);
+        GN_LAUNCH(ctx, embedding_fwd_kernel, (unsigned)tokens, 128, 0, cur, p, P, dst, tokens, d.seq_len, d.out_size, d.in_size, (int*)l.idx.p, ctx->d_status);
         cur = dst; if (fuse) li++; break; }
       case GN_LAYER_POSENC: {
         long n = (long)B * l.out_size;
@@ -625,9 +639,15 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         ConvShape c{B, d.in_size, d.out_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
                     (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
         long n = (long)B * l.out_size; float* dzb; GN_TRY(ensure(m, S_DZ, (size_t)n, &dzb));
-        GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, l.z.p, dzb, n, d.activation, act_alpha_of(d.activation, d.reserved));
+        // ReLU'(z) = [z > 0] = [a > 0], so ReLU (and the identity) work from the activation; the others need the pre-activation
+        const float* zsrc = (d.activation == GN_ACT_RELU || d.activation == GN_ACT_LINEAR) ? l.out.p : l.z.p;
+        GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, zsrc, dzb, n, d.activation, act_alpha_of(d.activation, d.reserved));
         int nW = d.out_size * d.in_size * d.kernel * d.kernel;
-        if (d.kernel == 3 || d.kernel == 5 || d.kernel == 1) {
+        const bool conv_tc = !force_simt_engine() && conv_tc_supported(ctx, c);
+        if (conv_tc) {
+          float* part; GN_TRY(ensure(m, S_PART, (size_t)B * (nW + d.out_size), &part));
+          GN_TRY(conv_tc_wgrad(ctx, c, dzb, xin, part, gr, gr + nW));
+        } else if (d.kernel == 3 || d.kernel == 5 || d.kernel == 1) {
           const int pairs = d.out_size * d.in_size, slices = std::max(1, std::min(B, (4 * ctx->sm_count + pairs - 1) / pairs)), ng = nW + d.out_size;
           float* part; GN_TRY(ensure(m, S_PART, (size_t)slices * ng, &part));
           if (d.kernel == 3) GN_LAUNCH(ctx, conv2d_wgrad_tile_kernel<3>, dim3(pairs, slices), 256, 0, dzb, xin, part, c, slices);
@@ -637,7 +657,8 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         } else GN_LAUNCH(ctx, conv2d_wgrad_kernel, nW + d.out_size, 256, 0, dzb, xin, gr, gr + nW, c);
         if (need_dx) {
           long ni = (long)B * l.in_size;
-          if (d.stride == 1 && d.kernel == 3) GN_LAUNCH(ctx, conv2d_dgrad_s1_kernel<3>, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
+          if (conv_tc && d.stride == 1) { float* wtmp; GN_TRY(ensure(m, S_DELTA, (size_t)nW, &wtmp)); GN_TRY(conv_tc_dgrad(ctx, c, dzb, p, wtmp, dx)); }
+          else if (d.stride == 1 && d.kernel == 3) GN_LAUNCH(ctx, conv2d_dgrad_s1_kernel<3>, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
           else if (d.stride == 1 && d.kernel == 5) GN_LAUNCH(ctx, conv2d_dgrad_s1_kernel<5>, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
           else GN_LAUNCH(ctx, conv2d_dgrad_kernel, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
           g = dx; flip ^= 1;
@@ -668,8 +689,41 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
       case GN_LAYER_LSTM_UNROLLED:
         GN_TRY(lstm_backward(m, l, li, B, xin, g, global_batch, first_sample, dx)); if (need_dx) { g = dx; flip ^= 1; } break;
       case GN_LAYER_EMBEDDING: {
-        int chunk = (global_batch + m->W - 1) / m->W;
-        GN_LAUNCH(ctx, embedding_bwd_kernel, dim3(d.seq_len, B), 128, 0, g, (const int*)l.idx.p, gr, d.seq_len, d.out_size, first_sample, global_batch, chunk);
+        // Only the last sample of every worker chunk reaches the table (embedding.go:151-154): global samples
+        // c*chunk + chunk - 1 and the very last one.
+        const int chunk = (global_batch + m->W - 1) / m->W, T = d.seq_len, dim = d.out_size;
+        const int nq = (global_batch + chunk - 1) / chunk;                       // qualifying samples of the global batch
+        auto q_sample = [&](int q) { return std::min(global_batch - 1, q * chunk + chunk - 1); };
+        const size_t smem = (size_t)T * sizeof(int);
+        if (smem > 48 * 1024) GN_CUDA(cudaFuncSetAttribute(embedding_bwd_sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const bool sparse = ctx->world > 1 && (double)nq * T * (dim + 1) < 0.5 * (double)l.p_cnt;
+        if (sparse) {
+          // few samples, large table: exchange those samples' rows (nq * T * (dim + 1) floats) instead of all-reducing the table;
+          // every rank then builds the complete table gradient itself
+          float* buf; GN_TRY(ensure(m, S_EMB, (size_t)nq * T * (dim + 1) + (size_t)nq * T, &buf));
+          float* rows = buf; float* idsf = buf + (size_t)nq * T * dim; int* idsi = reinterpret_cast<int*>(idsf + (size_t)nq * T);
+          GN_CUDA(cudaMemsetAsync(buf, 0, (size_t)nq * T * (dim + 1) * sizeof(float), ctx->stream));
+          for (int q = 0; q < nq; q++) {
+            const int sl = q_sample(q) - first_sample; if (sl < 0 || sl >= B) continue;
+            GN_LAUNCH(ctx, embedding_pack_kernel, T, 128, 0, g + (size_t)sl * T * dim, (const int*)l.idx.p + (size_t)sl * T, rows + (size_t)q * T * dim, idsf + (size_t)q * T, T, dim);
+          }
+          GN_CUDA(cudaEventRecord(m->gather_ev, ctx->stream));
+          GN_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->gather_ev, 0));
+          int rc = ctx->nccl->AllReduce(buf, buf, (size_t)nq * T * (dim + 1), NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->comm_stream);
+          if (rc) return fail(GN_ERR_NCCL, "ncclAllReduce(embedding rows): %s", ctx->nccl->GetErrorString(rc));
+          GN_CUDA(cudaEventRecord(m->gather_ev, ctx->comm_stream));
+          GN_CUDA(cudaStreamWaitEvent(ctx->stream, m->gather_ev, 0));
+          GN_LAUNCH(ctx, ids_to_int_kernel, cdiv((long)nq * T, 256), 256, 0, (const float*)idsf, idsi, nq * T);
+          for (int q = 0; q < nq; q++)
+            GN_LAUNCH(ctx, embedding_bwd_sample_kernel, T, 128, smem, (const float*)(rows + (size_t)q * T * dim), (const int*)(idsi + (size_t)q * T), gr, T, dim);
+          l.grad_replicated = true;
+        } else {
+          for (int q = 0; q < nq; q++) {
+            const int sl = q_sample(q) - first_sample; if (sl < 0 || sl >= B) continue;
+            GN_LAUNCH(ctx, embedding_bwd_sample_kernel, T, 128, smem, g + (size_t)sl * T * dim, (const int*)l.idx.p + (size_t)sl * T, gr, T, dim);
+          }
+          l.grad_replicated = false;
+        }
         break; }
       case GN_LAYER_POSENC:
         GN_TRY(colsum(m, g, l.out_size, B, l.out_size, gr, false)); break;     // gP = sum over samples; dx = g
@@ -722,10 +776,15 @@ static int adam_launch(Ctx* ctx, float* p, const float* g, float* m1, float* v, 
   GN_LAUNCH(ctx, adam_kernel, ew_grid(ctx, (n + 3) / 4), 256, 0, p, g, m1, v, (long)n, effLR, b1, b2, 1.f - b1, 1.f - b2, eps, grad_scale, status);
   return check_launch("adam");
 }
-// Reads the status word; non-zero (a bounded device-side wait gave up) clears it and becomes GN_ERR_TIMEOUT.
+// Meaning of a non-zero status word.
+static int status_error(int st) {
+  if (st == GN_STATUS_BAD_TOKEN) return fail(GN_ERR_INVALID_ARG, "a token id outside [0, vocabulary) was given to an Embedding layer (embedding.go:124-129); parameters and optimiser state are unchanged");
+  return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d); parameters and optimiser state are unchanged", st);
+}
+// Reads the status word; non-zero clears it and becomes an error (GN_ERR_TIMEOUT: a bounded device-side wait gave up).
 static int check_status_word(Ctx* c) {
   int st = 0; GN_CUDA(copy_d2h(c, &st, c->d_status, sizeof(int)));
-  if (st != 0) { cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream); cudaStreamSynchronize(c->stream); return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d)", st); }
+  if (st != 0) { cudaMemsetAsync(c->d_status, 0, sizeof(int), c->stream); cudaStreamSynchronize(c->stream); return status_error(st); }
   return GN_OK;
 }
 
@@ -772,7 +831,7 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
   Ctx* ctx = &m->ctx->c;
   if (global_batch <= 0) { global_batch = B; first_sample = 0; }
   if (B > m->cap) GN_TRY(alloc_activations(m, B));
-  int64_t launches0 = ctx->launches; ctx->gemm_flops = 0; ctx->gemm_launches = 0; ctx->gemm_ms = 0; ctx->ev_used = 0;
+  int64_t launches0 = ctx->launches; ctx->gemm_flops = 0; ctx->gemm_launches = 0; ctx->gemm_ms = 0; ctx->ev_used = 0; ctx->gemm_bytes = 0; ctx->split_bytes = 0;
   int rc = train_step_issue(m, x_dev, y_dev, B, global_batch, first_sample);
   if (rc != GN_OK) {
     // drain what was queued before the failure (both streams) so that nothing of this step runs after the call returned
@@ -784,7 +843,7 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
   int st; memcpy(&st, &m->h_ret[1], sizeof(int));
   if (st != 0) {    // the Adam pass saw the same word and left parameters, moments and the step counter alone
     cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream); cudaStreamSynchronize(ctx->stream);
-    return fail(GN_ERR_TIMEOUT, "a device-side bounded wait gave up (status word %d); parameters and optimiser state are unchanged", st);
+    return status_error(st);
   }
   m->timestep += 1;
   if (mean_loss) *mean_loss = m->h_ret[0] / (float)global_batch;
@@ -792,6 +851,7 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
   cudaEventElapsedTime(&m->stats.step_ms, m->ev0, m->ev1);
   m->stats.allreduce_ms = 0.f; if (ctx->world > 1) cudaEventElapsedTime(&m->stats.allreduce_ms, m->ar0, m->ar1);
   m->stats.gemm_flops = ctx->gemm_flops; m->stats.gemm_launches = ctx->gemm_launches; m->stats.gemm_ms = 0.f;
+  m->stats.gemm_bytes = ctx->gemm_bytes; m->stats.split_bytes = ctx->split_bytes;
   if (ctx->profile) { float tot = 0.f; for (size_t i = 0; i < ctx->ev_used; i++) { float ms = 0.f; cudaEventElapsedTime(&ms, ctx->ev_pool[i].first, ctx->ev_pool[i].second); tot += ms; } m->stats.gemm_ms = tot; }
   return GN_OK;
 }

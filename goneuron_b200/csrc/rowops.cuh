@@ -381,10 +381,15 @@ __global__ void dropout_advance_kernel(float* __restrict__ cnt, unsigned long lo
 
 // ---------------------------------------------------------------- embedding / positional / CLS
 // out[s,t,:] = E[floor(id)] (+ P[t,:])   reference: embedding.go:120-136, transformer.go:80-82
+// A token id outside [0, V) is an error in the reference (embedding.go:124-129): the kernel records it in the status
+// word (GN_STATUS_BAD_TOKEN; the host turns it into GN_ERR_INVALID_ARG and the step changes nothing) and carries on
+// with a clamped id, so that nothing is read out of bounds.
+constexpr int GN_STATUS_BAD_TOKEN = 100;
 __global__ void embedding_fwd_kernel(const float* __restrict__ ids, const float* __restrict__ E, const float* __restrict__ P,
-                                     float* __restrict__ out, long tokens, int T, int d, int V, int* __restrict__ idx_out) {
+                                     float* __restrict__ out, long tokens, int T, int d, int V, int* __restrict__ idx_out, int* __restrict__ status) {
   long tok = blockIdx.x; if (tok >= tokens) return;
-  int id = (int)floorf(ids[tok]); id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+  int id = (int)floorf(ids[tok]);
+  if (id < 0 || id >= V || !(ids[tok] == ids[tok])) { if (threadIdx.x == 0) atomicCAS(status, 0, GN_STATUS_BAD_TOKEN); id = id < 0 ? 0 : V - 1; }
   if (threadIdx.x == 0 && idx_out) idx_out[tok] = id;
   const float* e = E + (long)id * d; float* o = out + tok * d;
   if (P) { const float* p = P + (long)(tok % T) * d; for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = e[i] + p[i]; }
@@ -394,15 +399,40 @@ __global__ void posenc_fwd_kernel(const float* __restrict__ x, const float* __re
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) out[i] = x[i] + P[i % per_sample];
 }
 // Embedding.Backward zeroes its whole gradient at every call (embedding.go:151-154), so only the last
-// sample of each worker chunk reaches the table: scatter-add the rows of exactly those samples.
-__global__ void embedding_bwd_kernel(const float* __restrict__ g, const int* __restrict__ idx, float* __restrict__ gE, int T, int d,
-                                     int first_sample, int global_batch, int chunk) {
-  int s = blockIdx.y, gidx = first_sample + s;
-  bool last = ((gidx + 1) % chunk == 0) || (gidx == global_batch - 1);
-  if (!last) return;
-  int t = blockIdx.x; long tok = (long)s * T + t;
-  float* dst = gE + (long)idx[tok] * d; const float* src = g + tok * d;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) atomicAdd(dst + i, src[i]);
+// sample of each worker chunk reaches the table.  Gradient of ONE such sample, added to the table: block t handles
+// position t, and only if t is the first position of its token id; it then adds the rows of all positions with that
+// id in ascending order, exactly the sum the reference's loop forms for that table row (embedding.go:156-180), and adds
+// the result to the row.  No two blocks touch the same row, so there are no atomics and the result does not depend on
+// scheduling; the samples of a batch are processed by consecutive launches in sample order (the order in which the
+// reference adds its workers' gradients, net.go:694-700).
+__global__ void embedding_bwd_sample_kernel(const float* __restrict__ g, const int* __restrict__ ids, float* __restrict__ gE, int T, int d) {
+  extern __shared__ int same[];                 // positions after t that hold the same id
+  __shared__ int n_same, first;
+  const int t = blockIdx.x, id = ids[t];
+  if (threadIdx.x == 0) {
+    first = 1; n_same = 0;
+    for (int u = 0; u < t; u++) if (ids[u] == id) { first = 0; break; }
+    if (first) for (int u = t + 1; u < T; u++) if (ids[u] == id) same[n_same++] = u;
+  }
+  __syncthreads();
+  if (!first) return;
+  float* dst = gE + (long)id * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float s = g[(long)t * d + i];
+    for (int k = 0; k < n_same; k++) s += g[(long)same[k] * d + i];
+    dst[i] += s;
+  }
+}
+// Multi-GPU exchange of the few samples that reach the table: slot q of the buffers belongs to the q-th qualifying
+// sample of the global batch; the rank that owns it copies its gradient rows [T, d] and token ids (as floats) there,
+// every other rank leaves zeros, and a sum all-reduce of the small buffers gives every rank all of them.
+__global__ void embedding_pack_kernel(const float* __restrict__ g, const int* __restrict__ idx, float* __restrict__ rows, float* __restrict__ ids, int T, int d) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) rows[(long)t * d + i] = g[(long)t * d + i];
+  if (threadIdx.x == 0) ids[t] = (float)idx[t];
+}
+__global__ void ids_to_int_kernel(const float* __restrict__ f, int* __restrict__ out, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < n) out[i] = (int)f[i];
 }
 // CLSPooling: y[s,:] = x[s,0,:]; backward: zeros except token 0   transformer.go:1684, :1715-1724
 __global__ void cls_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, int T, int d) {

@@ -205,6 +205,8 @@ typedef struct gn_step_stats {
   float gemm_ms;          /* sum over the step's dense-contraction launches */
   int64_t gemm_launches;
   double gemm_flops;      /* 2*M*N*K summed over those launches */
+  double gemm_bytes;      /* bytes those launches must move: operand planes (4 B per element) + output (+ residual) */
+  double split_bytes;     /* bytes the operand split passes of the step move: 4 B read + 4 B written per element */
 } gn_step_stats;
 int gn_model_last_stats(gn_model* m, gn_step_stats* out);
 /* 0 = off (default); 1 = time every contraction launch with CUDA events. */

@@ -65,3 +65,37 @@ def test_large_transformer_param_count():
     d, f, v, t = 1024, 4096, 32000, 512
     per_block = 4 * (d * d + d) + 4 * d + d * f + f + f * d + d
     assert v * d + t * d + 8 * per_block + d * v + v == 166862080
+
+
+def test_reference_generator_and_initialisers():
+    """The reference's LCG (layer.go:61-75) restated with wrapping uint64 arithmetic, against plain Python integers; and the
+    shapes, seeds and fixed entries of the initialisers built on it."""
+    import numpy as np
+    from goneuron_b200 import configs
+
+    def lcg(seed, n):
+        s, out = seed, []
+        for _ in range(n):
+            s = (s * 6364136223846793005 + 1) % (1 << 64)
+            out.append(np.float32(s >> 33) / np.float32(1 << 31))
+        return np.array(out, np.float32)
+
+    rng = configs.ReferenceRNG(784 * 1000 + 128 * 100 + 42)
+    got = np.concatenate([rng.rand_float(1000), rng.rand_float(1), rng.rand_float(77)])      # state carries over between calls
+    assert np.array_equal(got, lcg(784 * 1000 + 128 * 100 + 42, 1078))
+    layers, _, _, _ = configs.build("mlp")
+    p = configs.reference_init_params(layers)
+    assert p.size == 101770
+    scale = np.float32(np.sqrt(2.0 / (784.0 + 128.0)))
+    r = lcg(784 * 1000 + 128 * 100 + 42, 784 * 128 + 128)
+    assert np.array_equal(p[:784 * 128], r[:784 * 128] * np.float32(2) * scale - scale)
+    assert np.array_equal(p[784 * 128:784 * 128 + 128], r[784 * 128:] * np.float32(0.2) - np.float32(0.1))
+    layers, _, _, _ = configs.build("lstm")
+    p = configs.reference_init_params(layers)
+    H, i = 128, 16
+    b = p[4 * H * i + 4 * H * H:4 * H * i + 4 * H * H + 4 * H]
+    assert p.size == 74369 and np.array_equal(b[H:2 * H], np.ones(H, np.float32)) and not b[:H].any() and not b[2 * H:].any()
+    # equal-shaped layers start identical (the seed depends only on the shape)
+    from goneuron_b200 import descriptors as D
+    q = configs.reference_init_params([D.Dense(8, 8, D.RELU), D.Dense(8, 8, D.RELU)])
+    assert np.array_equal(q[:72], q[72:])
