@@ -610,6 +610,9 @@ static int lstm_backward(gn_model* m, LayerRT& l, size_t li, int B, const float*
   return check_launch("lstm_backward");
 }
 
+static int adam_launch(Ctx* ctx, float* p, const float* g, float* m1, float* v, int64_t n, float lr, float b1, float b2, float eps, int t, float grad_scale,
+                       const int* status, cudaStream_t stream);
+
 static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, int global_batch, int first_sample) {
   Ctx* ctx = &m->ctx->c;
   const float* g = gloss;
@@ -752,12 +755,19 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
         break; }
     }
     GN_TRY(check_launch("backward"));
-    if (ctx->world > 1 && l.p_cnt > 0 && !l.grad_replicated) {
-      // this layer's slice of the flat gradient buffer is final: sum it over the ranks while earlier layers still compute
+    if (ctx->world > 1 && l.p_cnt > 0) {
+      // This layer's slice of the flat gradient buffer is final: sum it over the ranks while earlier layers still compute
+      // (unless every rank already holds the whole sum), and apply this slice's Adam update right behind it on the
+      // communication stream -- the layer's parameters are not read again in this step -- so that neither the exchange
+      // nor the optimiser pass is left over when the backward pass ends.
       GN_CUDA(cudaEventRecord(m->layer_ev[li], ctx->stream));
       GN_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->layer_ev[li], 0));
-      int rc = ctx->nccl->AllReduce(gr, gr, (size_t)l.p_cnt, NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->comm_stream);
-      if (rc) return fail(GN_ERR_NCCL, "ncclAllReduce(grads of layer %d): %s", li, ctx->nccl->GetErrorString(rc));
+      if (!l.grad_replicated) {
+        int rc = ctx->nccl->AllReduce(gr, gr, (size_t)l.p_cnt, NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->comm_stream);
+        if (rc) return fail(GN_ERR_NCCL, "ncclAllReduce(grads of layer %d): %s", li, ctx->nccl->GetErrorString(rc));
+      }
+      GN_TRY(adam_launch(ctx, m->params.p + l.p_off, gr, m->m1.p + l.p_off, m->v2.p + l.p_off, l.p_cnt, m->lr, m->b1, m->b2, m->eps, m->timestep + 2,
+                         (float)(1.0 / (double)global_batch), ctx->d_status, ctx->comm_stream));
     }
   }
   return GN_OK;
@@ -771,9 +781,10 @@ static void adam_coeffs(float lr, float b1, float b2, int t, float* effLR) {
   *effLR = lr * (float)std::sqrt((double)bias2) / bias1;
 }
 static int adam_launch(Ctx* ctx, float* p, const float* g, float* m1, float* v, int64_t n, float lr, float b1, float b2, float eps, int t, float grad_scale,
-                       const int* status = nullptr) {
+                       const int* status = nullptr, cudaStream_t stream = nullptr) {
   float effLR; adam_coeffs(lr, b1, b2, t, &effLR);
-  GN_LAUNCH(ctx, adam_kernel, ew_grid(ctx, (n + 3) / 4), 256, 0, p, g, m1, v, (long)n, effLR, b1, b2, 1.f - b1, 1.f - b2, eps, grad_scale, status);
+  adam_kernel<<<ew_grid(ctx, (n + 3) / 4), 256, 0, stream ? stream : ctx->stream>>>(p, g, m1, v, (long)n, effLR, b1, b2, 1.f - b1, 1.f - b2, eps, grad_scale, status);
+  ctx->launches++;
   return check_launch("adam");
 }
 // Meaning of a non-zero status word.
@@ -818,7 +829,8 @@ static int train_step_issue(gn_model* m, const float* x_dev, const float* y_dev,
   // first: after a bounded wait gave up it changes nothing.
   float inv = (float)(1.0 / (double)global_batch);                                        // net.go:703
   m->last_inv_batch = inv;
-  GN_TRY(adam_launch(ctx, m->params.p, m->grads.p, m->m1.p, m->v2.p, m->P, m->lr, m->b1, m->b2, m->eps, m->timestep + 2, inv, ctx->d_status));
+  if (ctx->world == 1) GN_TRY(adam_launch(ctx, m->params.p, m->grads.p, m->m1.p, m->v2.p, m->P, m->lr, m->b1, m->b2, m->eps, m->timestep + 2, inv, ctx->d_status));
+  // (with more than one rank the update was applied slice by slice behind each layer's all-reduce, see backward())
   GN_CUDA(cudaEventRecord(m->ev1, ctx->stream));
   // one read-back for the caller: the loss sum and the status word land in the same pinned block, one wait
   GN_CUDA(cudaMemcpyAsync(&m->h_ret[0], m->loss_sum.p, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));

@@ -501,21 +501,26 @@ __global__ void scale_kernel(float* __restrict__ x, long n, float s) {
 __global__ void adam_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m, float* __restrict__ v, long n,
                             float effLR, float b1, float b2, float omb1, float omb2, float eps, float grad_scale, const int* __restrict__ status) {
   if (status && *status != 0) return;
-  long n4 = n >> 2;
-  float4* p4 = reinterpret_cast<float4*>(p); const float4* g4 = reinterpret_cast<const float4*>(g);
-  float4* m4 = reinterpret_cast<float4*>(m); float4* v4 = reinterpret_cast<float4*>(v);
+  // The four arrays are slices of the flat buffers at the same offset, so they share their position relative to a
+  // 16-byte boundary: `head` leading elements are handled one by one, then float4s, then the tail.
+  const long head = min(n, (long)((4 - ((reinterpret_cast<uintptr_t>(p) >> 2) & 3)) & 3));
+  const long n4 = (n - head) >> 2;
+  float4* p4 = reinterpret_cast<float4*>(p + head); const float4* g4 = reinterpret_cast<const float4*>(g + head);
+  float4* m4 = reinterpret_cast<float4*>(m + head); float4* v4 = reinterpret_cast<float4*>(v + head);
   auto upd = [&](float& pp, float gg, float& mm, float& vv) {
     float gs = __fmul_rn(gg, grad_scale);
     mm = __fadd_rn(__fmul_rn(b1, mm), __fmul_rn(omb1, gs));
     vv = __fadd_rn(__fmul_rn(b2, vv), __fmul_rn(__fmul_rn(omb2, gs), gs));
     pp = __fsub_rn(pp, __fdiv_rn(__fmul_rn(effLR, mm), __fadd_rn(__fsqrt_rn(vv), eps)));
   };
-  for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n4; i += (long)gridDim.x * blockDim.x) {
+  const long tid = blockIdx.x * (long)blockDim.x + threadIdx.x, nthreads = (long)gridDim.x * blockDim.x;
+  for (long i = tid; i < n4; i += nthreads) {
     float4 P = p4[i], G = g4[i], M = m4[i], V = v4[i];
     upd(P.x, G.x, M.x, V.x); upd(P.y, G.y, M.y, V.y); upd(P.z, G.z, M.z, V.z); upd(P.w, G.w, M.w, V.w);
     p4[i] = P; m4[i] = M; v4[i] = V;
   }
-  for (long i = (n4 << 2) + blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) upd(p[i], g[i], m[i], v[i]);
+  if (tid < head) upd(p[tid], g[tid], m[tid], v[tid]);
+  for (long i = head + (n4 << 2) + tid; i < n; i += nthreads) upd(p[i], g[i], m[i], v[i]);
 }
 
 

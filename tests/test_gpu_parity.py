@@ -50,6 +50,7 @@ CASES = [
     ("mlp_act", dict(act=D.ELU), 12, 1), ("mlp_act", dict(act=D.ELU, alpha=0.7), 12, 1),
     ("mlp_rms", {}, 16, 1), ("mlp_rms", dict(in_size=10, hidden=300, norm=100, classes=3), 5, 1),            # RMSNorm
     ("cnn1d", {}, 12, 1), ("cnn1d", dict(length=17, c0=2, c1=5, c2=3, classes=3, act=D.GELU), 7, 1),           # Conv1D
+    ("transformer_small", dict(vocab=7, dim=16, seq_len=24, heads=2, ff_dim=32, n_blocks=1), 3, 1),          # every token id repeats: table rows summed in position order
     # the reference's own deterministic initialisation (LCG seeded from the layer shapes) instead of uploaded Glorot weights
     ("mlp", dict(init="reference"), 64, 1), ("cnn", dict(init="reference"), 128, 1), ("lstm", dict(init="reference"), 256, 1),
     # The large Transformer at its real width (vocabulary 32000, width 1024, 16 heads of 64, 512 tokens, FFN 4096): the plan,
@@ -151,6 +152,42 @@ def test_errors_are_status_codes(device):
         m.SetParams(np.zeros(3, np.float32))                                                # wrong length
     m.Close()
     m.Close()                                                                               # idempotent
+
+
+def test_invalid_token_id_is_an_error_and_changes_nothing(device):
+    """Embedding.Forward returns an error for an id outside [0, vocab) (embedding.go:124-129); here the step reports
+    GN_ERR_INVALID_ARG, leaves parameters and optimiser state alone, and the next valid step is unaffected."""
+    from goneuron_b200 import _lib
+    from goneuron_b200.sequential import Adam, Sequential
+    kw = dict(vocab=50, dim=16, seq_len=8, heads=2, ff_dim=32, n_blocks=1)
+    layers, loss_kind, params, x, y, lr = configs.make_case("transformer_small", batch=4, **kw)
+    fresh = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+    fresh.SetParams(params); fresh.TrainBatch(x, y); p_ref = fresh.Params(); fresh.Close()
+    model = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+    model.SetParams(params)
+    for bad in (50.0, -1.0):
+        xb = x.copy(); xb[2, 3] = bad
+        with pytest.raises(_lib.GoNeuronCudaError) as ei:
+            model.TrainBatch(xb, y)
+        assert ei.value.code == -1 and "token id" in str(ei.value)
+        assert np.array_equal(model.Params(), params) and model.AdamState()[2] == 0
+        with pytest.raises(_lib.GoNeuronCudaError):
+            model.PredictBatch(xb)
+    model.TrainBatch(x, y)
+    assert np.array_equal(model.Params(), p_ref)
+    model.Close()
+
+
+def test_repeated_token_ids_give_a_run_to_run_identical_gradient(device):
+    """The table gradient of a row that several positions share is summed in position order, not with atomics: two runs
+    of the same step are bit-identical."""
+    from goneuron_b200.sequential import Adam, Sequential
+    layers, loss_kind, params, x, y, lr = configs.make_case("transformer_small", batch=6, vocab=5, dim=32, seq_len=64, heads=2, ff_dim=64, n_blocks=1)
+    grads = []
+    for _ in range(2):
+        model = Sequential(layers, device, virtual_workers=3).Compile(Adam(lr), loss_kind)
+        model.SetParams(params); model.TrainBatch(x, y); grads.append(model.Gradients()); model.Close()
+    assert np.array_equal(grads[0], grads[1]) and np.abs(grads[0][:5 * 32]).max() > 0
 
 
 def test_adam_kernel_bit_exact(device, oracle):
