@@ -2,5 +2,5 @@
 
 The compute lives in csrc/ (CUDA kernels + the C ABI declared in include/goneuron_cuda.h);
 this package is the thin host-side mirror of the reference's Sequential API used by the
-tests and the benchmark (the Go binding is shown in INTEGRATION.md)."""
+tests and the benchmark; a Go host binds the same C ABI through cgo."""
 from . import descriptors  # noqa: F401

@@ -16,7 +16,7 @@ EXPORTS = [
     "gn_model_set_params", "gn_model_get_params", "gn_model_get_grads", "gn_adam_set", "gn_adam_get_state",
     "gn_adam_set_state", "gn_train_batch", "gn_train_batch_device", "gn_forward_batch", "gn_device_alloc",
     "gn_device_free", "gn_device_upload", "gn_device_download", "gn_model_last_stats", "gn_model_set_profiling",
-    "gn_op_gemm_nt", "gn_op_adam", "gn_op_gemm_nt_static", "gn_op_attention", "gn_model_state_count", "gn_model_get_state", "gn_model_set_state",
+    "gn_op_gemm_nt", "gn_op_adam", "gn_op_layernorm", "gn_op_conv2d", "gn_op_softmax_ce", "gn_op_lstm", "gn_op_gemm_nt_static", "gn_op_attention", "gn_model_state_count", "gn_model_get_state", "gn_model_set_state",
 ]
 
 
@@ -79,6 +79,10 @@ def load():
     L.gn_model_get_state.argtypes = [vp, f32p, C.c_int64]
     L.gn_model_set_state.argtypes = [vp, f32p, C.c_int64]
     L.gn_op_gemm_nt_static.argtypes = [vp, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp]
+    L.gn_op_layernorm.argtypes = [vp, C.c_int64, C.c_int] + [f32p] * 8
+    L.gn_op_conv2d.argtypes = [vp] + [C.c_int] * 10 + [f32p] * 8
+    L.gn_op_softmax_ce.argtypes = [vp, C.c_int, C.c_int, C.c_int] + [f32p] * 5
+    L.gn_op_lstm.argtypes = [vp] + [C.c_int] * 5 + [f32p] * 8
     L.gn_op_attention.argtypes = [vp] + [C.c_int] * 6 + [f32p] * 10
     _lib = L
     return L

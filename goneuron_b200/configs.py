@@ -69,6 +69,12 @@ def recurrent(in_size=16, hidden=128, seq_len=64):
     return [D.SequenceUnrollerLSTM(in_size, hidden, seq_len, False), D.Dense(hidden, 1, D.LINEAR)], D.MSE
 
 
+def recurrent_gru(in_size=16, hidden=64, seq_len=24, return_seq=False):
+    """SequenceUnroller(GRU) -> Dense: exercises the GRU layer (gru.go) with its literal backward pass."""
+    out = hidden * seq_len if return_seq else hidden
+    return [D.SequenceUnrollerGRU(in_size, hidden, seq_len, return_seq), D.Dense(out, 2, D.LINEAR)], D.MSE
+
+
 def transformer(vocab, dim, seq_len, heads, ff_dim, n_blocks):
     layers = [D.Embedding(vocab, dim, seq_len), D.PositionalEncoding(seq_len, dim)]
     layers += [D.TransformerBlock(dim, heads, seq_len, ff_dim, True) for _ in range(n_blocks)]
@@ -88,10 +94,11 @@ CONFIGS = {
     "cnn1d": (cnn1d, {}, 12, 1e-3),
     "mlp_ln": (mlp_ln, {}, 16, 1e-3),
     "lstm": (recurrent, {}, 256, 1e-3),
+    "gru": (recurrent_gru, {}, 32, 1e-3),
     "transformer_small": (transformer, dict(vocab=8192, dim=256, seq_len=128, heads=8, ff_dim=1024, n_blocks=4), 64, 3e-4),
     "transformer_large": (transformer, dict(vocab=32000, dim=1024, seq_len=512, heads=16, ff_dim=4096, n_blocks=8), 256, 1e-4),
 }
-SEEDS = {"cnn1d": 1246, "mlp_rms": 1245, "mlp_act": 1244, "mlp_drop": 1243, "cnn_avg": 1242, "mlp_ln": 1241, "cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
+SEEDS = {"gru": 1247, "cnn1d": 1246, "mlp_rms": 1245, "mlp_act": 1244, "mlp_drop": 1243, "cnn_avg": 1242, "mlp_ln": 1241, "cnn_bn": 1240, "mlp": 1235, "cnn": 1236, "lstm": 1237, "transformer_small": 1238, "transformer_large": 1239}
 
 
 def build(name, **override):
@@ -132,6 +139,9 @@ def init_params(layers, rng):
             b = np.zeros(4 * H, np.float32)
             b[H:2 * H] = 1.0
             parts += [_glorot(rng, (4 * H, i), i, H).ravel(), _glorot(rng, (4 * H, H), H, H).ravel(), b]
+        elif k == D.GRU_UNROLLED:
+            H, i = l.out_size, l.in_size
+            parts += [_glorot(rng, (3 * H, i), i, H).ravel(), _glorot(rng, (2 * H, H), H, H).ravel(), rng.uniform(-0.1, 0.1, size=3 * H).astype(np.float32)]
         elif k == D.EMBEDDING:
             a = math.sqrt(3.0 / l.out_size)
             parts.append(rng.uniform(-a, a, size=l.in_size * l.out_size).astype(np.float32))
@@ -216,6 +226,13 @@ def reference_init_params(layers):
             wh = r[:, i:] * f32(2) * sr - sr
             b = np.zeros(4 * H, f32); b[H:2 * H] = 1.0
             parts += [np.ascontiguousarray(wx, f32).ravel(), np.ascontiguousarray(wh, f32).ravel(), b]
+        elif k == D.GRU_UNROLLED:
+            H, i = l.out_size, l.in_size                                      # gru.go:126-147, seed in*1000 + out*100 + 242, biases zero
+            scale = f32(math.sqrt(2.0 / (float(i) + float(H))))
+            rng = ReferenceRNG(i * 1000 + H * 100 + 242)
+            wx = rng.rand_float(3 * H * i) * f32(2) * scale - scale
+            wh = rng.rand_float(2 * H * H) * f32(2) * scale - scale
+            parts += [wx.astype(f32), wh.astype(f32), np.zeros(3 * H, f32)]
         elif k == D.EMBEDDING:
             scale = f32(math.sqrt(3.0 / float(l.out_size)))
             parts.append((scale * (f32(2) * ReferenceRNG(42).rand_float(l.in_size * l.out_size) - f32(1))).astype(f32))
@@ -245,7 +262,7 @@ def make_inputs(name, layers, batch, rng):
         tgt = rng.integers(0, last.out_size, size=batch)
         y = np.zeros((batch, last.out_size), np.float32)
         y[np.arange(batch), tgt] = 1.0
-    elif first.kind == D.LSTM_UNROLLED:
+    elif first.kind in (D.LSTM_UNROLLED, D.GRU_UNROLLED):
         x = rng.standard_normal((batch, first.seq_len * first.in_size)).astype(np.float32)
         y = rng.standard_normal((batch, last.out_size)).astype(np.float32)
     elif first.kind == D.CONV1D:

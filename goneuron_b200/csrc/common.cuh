@@ -47,6 +47,7 @@ struct Ctx {
   int tc_force_bn = 0, tc_kslice = 0;   // experiment switches of the contraction engine (GONEURON_CUDA_TC_BN / _KSLICE); 0 = automatic
   void* tc_scratch = nullptr;      // operand planes of the contraction engine (TcScratch, owned)
   void* attn_scratch = nullptr;    // operand planes of the tcgen05 attention kernels (AttnTcScratch, owned)
+  const void* weight_planes = nullptr;   // the running model's table of prepared weight planes (WeightPlaneTable), or null
   std::mutex run_mu;               // serialises every entry point that launches work on this context (they share the scratch above)
   cudaEvent_t t0 = nullptr, t1 = nullptr;   // gn_timer_start / gn_timer_stop
   // Scratch objects created on demand for this context (operand planes of the contraction and attention engines),

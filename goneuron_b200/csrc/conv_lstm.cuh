@@ -307,6 +307,84 @@ __global__ void lstm_fwd_kernel(const float* __restrict__ x, const float* __rest
     __syncthreads();
   }
 }
+
+// ---------------------------------------------------------------- GRU
+// Forward recurrence of one sample per block, thread i = hidden unit i.  reference: gru.go:192-288.
+// `pre` [B, T, 3H] holds b + Wx x_t of every step on entry (one contraction over all B*T rows, issued before) and the
+// complete pre-activations (update | reset | candidate) on exit.  The layer has 2H recurrent rows: the candidate's
+// recurrent product uses the reset gate's rows on r (.) h_prev (gru.go:247-258).
+__global__ void gru_fwd_kernel(const float* __restrict__ Wh, float* __restrict__ pre, float* __restrict__ h_all, float* __restrict__ out, int T, int H, int return_seq) {
+  extern __shared__ float sm[];
+  float* WzT = sm;                   // [H][H]  WzT[j*H+i] = Wh[i, j]        (update rows)
+  float* WrT = WzT + (long)H * H;    // [H][H]  WrT[j*H+i] = Wh[H + i, j]    (reset rows)
+  float* hbuf = WrT + (long)H * H;   // [2][H]
+  float* rh = hbuf + 2 * H;          // [H]  r (.) h_prev
+  const int s = blockIdx.x, i = threadIdx.x;
+  for (int e = threadIdx.x; e < H * H; e += blockDim.x) { const int r = e / H, j = e % H; WzT[j * H + r] = Wh[e]; WrT[j * H + r] = Wh[(long)H * H + e]; }
+  if (i < H) { hbuf[i] = 0.f; hbuf[H + i] = 0.f; }
+  __syncthreads();
+  for (int t = 0; t < T; t++) {
+    const float* hp = hbuf + (t & 1) * H; float* hn = hbuf + ((t + 1) & 1) * H;
+    float* pr = pre + ((long)s * T + t) * 3 * H;
+    float pz = 0.f, prr = 0.f, z = 0.f, hprev = 0.f;
+    if (i < H) {
+      pz = pr[i]; prr = pr[H + i]; hprev = hp[i];
+      for (int j = 0; j < H; j++) { const float hj = hp[j]; pz = fmaf(WzT[j * H + i], hj, pz); prr = fmaf(WrT[j * H + i], hj, prr); }
+      z = act_fwd(GN_ACT_SIGMOID, pz);
+      rh[i] = act_fwd(GN_ACT_SIGMOID, prr) * hprev;
+    }
+    __syncthreads();
+    if (i < H) {
+      float pc = pr[2 * H + i];
+      for (int j = 0; j < H; j++) pc = fmaf(WrT[j * H + i], rh[j], pc);
+      const float c = act_fwd(GN_ACT_TANH, pc);
+      const float h = hprev + z * (c - hprev);
+      pr[i] = pz; pr[H + i] = prr; pr[2 * H + i] = pc;
+      const long o = ((long)s * T + t) * H + i;
+      h_all[o] = h; hn[i] = h;
+      if (return_seq) out[o] = h; else if (t == T - 1) out[(long)s * H + i] = h;
+    }
+    __syncthreads();
+  }
+}
+// Back-propagation through time of one sample per block.  reference: gru.go:360-534 with unroller.go:190-209, literal:
+// the reset gate's delta is never formed (stays zero), the candidate's gradient is scaled by (1 - z) and the
+// hidden-state pass-through by z, the candidate's contribution to dh_prev is indexed by the output unit's reset gate,
+// and dh_prev is ADDED to the incoming gradient before it is handed to the previous step.
+// Writes the gate deltas D [B,T,3H] (update | zero | candidate), h_{t-1} [B,T,H] and r (.) h_{t-1} [B,T,H] for the
+// weight-gradient contractions.
+__global__ void gru_bwd_kernel(const float* __restrict__ gout, const float* __restrict__ Wh, const float* __restrict__ pre, const float* __restrict__ h_all,
+                               float* __restrict__ D, float* __restrict__ hprev_all, float* __restrict__ rh_all, int T, int H, int return_seq) {
+  extern __shared__ float sm[];
+  float* dU = sm; float* dCr = sm + H;
+  const int s = blockIdx.x, i = threadIdx.x;
+  float cur = 0.f;
+  for (int t = T - 1; t >= 0; t--) {
+    float z = 0.f;
+    if (i < H) {
+      if (return_seq) cur += gout[((long)s * T + t) * H + i]; else if (t == T - 1) cur += gout[(long)s * H + i];
+      const float* pr = pre + ((long)s * T + t) * 3 * H;
+      z = act_fwd(GN_ACT_SIGMOID, pr[i]);
+      const float r = act_fwd(GN_ACT_SIGMOID, pr[H + i]), c = act_fwd(GN_ACT_TANH, pr[2 * H + i]);
+      const long o = ((long)s * T + t) * H + i;
+      const float hprev = t > 0 ? h_all[o - H] : 0.f;
+      const float du = cur * (c - hprev) * z * (1.f - z);
+      const float dc = cur * (1.f - z) * (1.f - c * c);
+      float* Dr = D + ((long)s * T + t) * 3 * H;
+      Dr[i] = du; Dr[H + i] = 0.f; Dr[2 * H + i] = dc;
+      hprev_all[o] = hprev; rh_all[o] = r * hprev;
+      dU[i] = du; dCr[i] = dc * r;
+    }
+    __syncthreads();
+    if (i < H) {
+      float sum = 0.f;
+      for (int j = 0; j < H; j++) sum = fmaf(Wh[(long)j * H + i], dU[j], sum);
+      for (int j = 0; j < H; j++) sum = fmaf(Wh[((long)H + j) * H + i], dCr[j], sum);
+      cur = cur + (sum + cur * z);
+    }
+    __syncthreads();
+  }
+}
 // Back-propagation through time of one sample per block; writes the gate deltas D[s,t,4H].
 // reference: lstm.go:476-698 + unroller.go:190-209: the hidden-state gradient handed to step t-1 is the
 // gradient of step t PLUS Wh^T d (a running sum), because LSTM.Backward adds dhPrev into its argument.

@@ -26,6 +26,7 @@ struct GemmDesc {
   const float* mask = nullptr; long mask_ld = 0; int mask_group = 1;
   float alpha = 1.f;
   bool reuse_a_planes = false;                          // A is the same tensor as in the previous tensor-core call of this context
+  const void* b_planes = nullptr;                       // tensor-core engine: prepared operand planes of B (a BfPlanes), e.g. of a weight matrix
   int batch1 = 1, batch2 = 1;                           // batch index b -> (b / batch2, b % batch2)
   long a_b1 = 0, a_b2 = 0, b_b1 = 0, b_b2 = 0, c_b1 = 0, c_b2 = 0, r_b1 = 0, r_b2 = 0;
   // Causal structure of attention: tiles that are entirely masked are never touched.

@@ -613,8 +613,7 @@ inline int tc_launch(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcPar
 // gradients over all tokens of a batch) are therefore cut into slices, each slice adding its result to C through the
 // epilogue's residual path, i.e. in properly rounded fp32: 4096 indices per run with separate accumulators for the
 // large and the small terms, 2048 with the single accumulator of the 256-wide tile.
-inline int tc_run(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams& ep) {
-  const int bn = tc_pick_bn(ctx, ep.M, ep.N, A.nbatch, ep.flags);
+inline int tc_run_rows(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams& ep, int bn) {
   const int kslice = ctx->tc_kslice > 0 ? ctx->tc_kslice : (bn == 256 ? 2048 : 4096);
   if (ep.K <= kslice || (ep.flags & (GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return tc_launch(ctx, A, B, ep, bn);
   for (int k0 = 0; k0 < ep.K; k0 += kslice) {
@@ -626,6 +625,111 @@ inline int tc_run(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams
     GN_TRY(tc_launch(ctx, As, Bs, es, bn));
   }
   return GN_OK;
+}
+inline int tc_run(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams& ep) {
+  // (Running the rows of a short last wave as a second launch with 128-wide tiles was measured at 16 384 rows: the second
+  // launch's fixed cost ate the 9 % it should have saved, so every product is one tiling.)
+  return tc_run_rows(ctx, A, B, ep, tc_pick_bn(ctx, ep.M, ep.N, A.nbatch, ep.flags));
+}
+
+// ------------------------------------------------------------------ prepared planes of weight matrices
+// A weight matrix W [out, in] is an operand twice per training step: as stored (rows = out, contraction over in) in the
+// forward product X W^T, and transposed (rows = in, contraction over out) in the input-gradient product dZ W.  Splitting it
+// at each use costs two small launches per orientation and matrix, work that does not shrink when the batch is sharded over
+// GPUs.  Instead all registered matrices are split once per parameter update, both orientations from one read, by two
+// launches in all: the matrices get ONE power-of-two scale each (their entries are of similar size, unlike activation
+// rows), found by wplanes_max_kernel, and wplanes_split_kernel writes every 64 x 64 tile as stored and transposed.
+struct WPlaneJob { const float* src; int out, in, ldp_r, ldp_c; __half *r0, *r1, *c0, *c1; float *inv_r, *inv_c; int tile0, tiles_in; };
+__device__ __forceinline__ int wplane_find(const WPlaneJob* jobs, int njobs, int tile) {
+  int lo = 0, hi = njobs - 1;
+  while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (jobs[mid].tile0 <= tile) lo = mid; else hi = mid - 1; }
+  return lo;
+}
+__global__ void __launch_bounds__(256) wplanes_max_kernel(const WPlaneJob* __restrict__ jobs, int njobs, int* __restrict__ mx) {
+  __shared__ float red[33];
+  const int j = wplane_find(jobs, njobs, blockIdx.x); const WPlaneJob jb = jobs[j];
+  const int t = blockIdx.x - jb.tile0, r0 = (t / jb.tiles_in) * 64, c0 = (t % jb.tiles_in) * 64;
+  float m = 0.f;
+  for (int e = threadIdx.x; e < 4096; e += 256) { const int r = r0 + (e >> 6), c = c0 + (e & 63); if (r < jb.out && c < jb.in) m = fmaxf(m, fabsf(jb.src[(long)r * jb.in + c])); }
+  m = block_max(m, red);
+  if (threadIdx.x == 0) { if (!(m <= 3.0e38f)) m = 3.4e38f; atomicMax(mx + j, __float_as_int(m)); }
+}
+__global__ void __launch_bounds__(256) wplanes_split_kernel(const WPlaneJob* __restrict__ jobs, int njobs, const int* __restrict__ mx) {
+  __shared__ float tl[64][65];
+  const int j = wplane_find(jobs, njobs, blockIdx.x); const WPlaneJob jb = jobs[j];
+  const int t = blockIdx.x - jb.tile0, r0 = (t / jb.tiles_in) * 64, c0 = (t % jb.tiles_in) * 64;
+  float inv; const float sc = row_scale(__int_as_float(mx[j]), &inv);
+  for (int e = threadIdx.x; e < 4096; e += 256) { const int rr = e >> 6, cc = e & 63; const int r = r0 + rr, c = c0 + cc; tl[rr][cc] = (r < jb.out && c < jb.in) ? jb.src[(long)r * jb.in + c] : 0.f; }
+  __syncthreads();
+  const int x2 = (threadIdx.x & 31) * 2, y = threadIdx.x >> 5;
+  for (int rr = y; rr < 64; rr += 8) {                        // as stored: plane row = out index, two neighbouring in indices per thread
+    const int r = r0 + rr, c = c0 + x2;
+    if (r < jb.out && c < jb.in) {                            // (in is even-padded by ldp_r; an odd last column writes its zero neighbour)
+      uint32_t a, b; split2_pair(tl[rr][x2], tl[rr][x2 + 1], sc, a, b);
+      const long o = (long)r * jb.ldp_r + c;
+      *reinterpret_cast<uint32_t*>(jb.r0 + o) = a; *reinterpret_cast<uint32_t*>(jb.r1 + o) = b;
+    }
+    if (c0 == 0 && x2 == 0 && r < jb.out) jb.inv_r[r] = inv;
+  }
+  for (int cc = y; cc < 64; cc += 8) {                        // transposed: plane row = in index, two neighbouring out indices per thread
+    const int c = c0 + cc, r = r0 + x2;
+    if (c < jb.in && r < jb.out) {
+      uint32_t a, b; split2_pair(tl[x2][cc], tl[x2 + 1][cc], sc, a, b);
+      const long o = (long)c * jb.ldp_c + r;
+      *reinterpret_cast<uint32_t*>(jb.c0 + o) = a; *reinterpret_cast<uint32_t*>(jb.c1 + o) = b;
+    }
+    if (r0 == 0 && x2 == 0 && c < jb.in) jb.inv_c[c] = inv;
+  }
+}
+// Host side of the table: one entry per registered matrix, looked up by the matrix's device address.
+struct WeightPlaneEntry { const float* src; int out, in; BfPlanes rows, cols; };
+struct WeightPlaneTable {
+  std::vector<WeightPlaneEntry> e; DevBuf planes, scales, mx, jobs; int total_tiles = 0; bool dirty = true;
+  const WeightPlaneEntry* find(const float* p) const { for (auto& x : e) if (x.src == p) return &x; return nullptr; }
+};
+// Lays the table out for the matrices (src, out, in) and allocates its buffers (planes zeroed once: the padding columns
+// of a plane row are never written afterwards and must read as zero).
+inline int wplanes_build(Ctx* ctx, WeightPlaneTable& t, const std::vector<WeightPlaneEntry>& mats) {
+  t.e = mats; size_t halves = 0, nscale = 0; int tiles = 0; std::vector<WPlaneJob> jobs;
+  for (auto& x : t.e) {
+    const int lr = tc_ldp(x.in), lc = tc_ldp(x.out);
+    halves += 2 * ((size_t)x.out * lr + (size_t)x.in * lc); nscale += (size_t)x.out + x.in + 8;
+  }
+  if (t.e.empty()) return GN_OK;
+  GN_TRY(t.planes.alloc(halves / 2 + 64)); GN_TRY(t.scales.alloc(nscale)); GN_TRY(t.mx.alloc(t.e.size() + 4));
+  GN_CUDA(cudaMemsetAsync(t.planes.p, 0, (halves / 2 + 64) * 4, ctx->stream));
+  __half* hp = reinterpret_cast<__half*>(t.planes.p); float* sp = t.scales.p;
+  for (auto& x : t.e) {
+    const int lr = tc_ldp(x.in), lc = tc_ldp(x.out);
+    x.rows = BfPlanes{hp, sp, x.out, x.in, lr, 1}; hp += 2 * (size_t)x.out * lr; sp += (x.out + 3) & ~3;
+    x.cols = BfPlanes{hp, sp, x.in, x.out, lc, 1}; hp += 2 * (size_t)x.in * lc; sp += (x.in + 3) & ~3;
+    WPlaneJob jb{x.src, x.out, x.in, lr, lc, x.rows.p0(), x.rows.p1(), x.cols.p0(), x.cols.p1(), x.rows.inv_scale, x.cols.inv_scale, tiles, (int)cdiv(x.in, 64)};
+    tiles += (int)cdiv(x.out, 64) * (int)cdiv(x.in, 64); jobs.push_back(jb);
+  }
+  t.total_tiles = tiles;
+  GN_TRY(t.jobs.alloc((jobs.size() * sizeof(WPlaneJob) + 3) / 4));
+  GN_CUDA(copy_h2d(ctx, t.jobs.p, jobs.data(), jobs.size() * sizeof(WPlaneJob)));
+  t.dirty = true; return GN_OK;
+}
+// Re-splits every registered matrix if the parameters changed since the last call.
+inline int wplanes_refresh(Ctx* ctx, WeightPlaneTable& t) {
+  if (t.e.empty() || !t.dirty) return GN_OK;
+  const int nj = (int)t.e.size();
+  GN_CUDA(cudaMemsetAsync(t.mx.p, 0, (size_t)nj * sizeof(int), ctx->stream));
+  GN_LAUNCH(ctx, wplanes_max_kernel, t.total_tiles, 256, 0, reinterpret_cast<const WPlaneJob*>(t.jobs.p), nj, reinterpret_cast<int*>(t.mx.p));
+  GN_LAUNCH(ctx, wplanes_split_kernel, t.total_tiles, 256, 0, reinterpret_cast<const WPlaneJob*>(t.jobs.p), nj, reinterpret_cast<const int*>(t.mx.p));
+  double elems = 0; for (auto& x : t.e) elems += (double)x.out * x.in;
+  ctx->split_bytes += 16.0 * elems;                          // 4 B read twice, 8 B written
+  t.dirty = false; return check_launch("wplanes_refresh");
+}
+// Prepared planes for B of this contraction, if B is a registered matrix used in one of its two orientations.
+inline const BfPlanes* wplanes_lookup(Ctx* ctx, const GemmDesc& g) {
+  const WeightPlaneTable* t = static_cast<const WeightPlaneTable*>(ctx->weight_planes);
+  if (!t || t->dirty || g.batch1 * g.batch2 != 1) return nullptr;
+  const WeightPlaneEntry* x = t->find(g.B); if (!x) return nullptr;
+  if (g.sb_k == 1 && g.sb_n == x->in && g.N == x->out && g.K == x->in) return &x->rows;     // B(k, n) = W[n, k]
+  if (g.sb_n == 1 && g.sb_k == x->in && g.N == x->in && g.K == x->out) return &x->cols;     // B(k, n) = W[k, n]
+  return nullptr;
 }
 
 // Can the engine run this contraction at all?  One of each operand's strides must be 1; LINEAR/RELU epilogue; alpha 1.
@@ -658,7 +762,10 @@ inline int gemm_tc(Ctx* ctx, const GemmDesc& g) {
     GN_TRY(tc_split(ctx, TcSrc{g.A, g.sa_m, g.sa_k, g.a_b1, g.a_b2, g.batch2}, A, mx));
     sc.last_a = (nb == 1 && g.sa_k == 1) ? g.A : nullptr; sc.last_m = g.M; sc.last_k = g.K; sc.last_ld = g.sa_m;
   }
-  GN_TRY(tc_split(ctx, TcSrc{g.B, g.sb_n, g.sb_k, g.b_b1, g.b_b2, g.batch2}, B, mx));
+  if (g.b_planes) {
+    B = *static_cast<const BfPlanes*>(g.b_planes);
+    if (B.rows != g.N || B.K != g.K || B.nbatch != nb) return fail(GN_ERR_INVALID_ARG, "gemm_tc: prepared planes of B do not match the contraction");
+  } else GN_TRY(tc_split(ctx, TcSrc{g.B, g.sb_n, g.sb_k, g.b_b1, g.b_b2, g.batch2}, B, mx));
   TcParams ep{g.C, g.ldc, g.c_b1, g.c_b2, g.bias, g.R, g.ldr, g.r_b1, g.r_b2, g.act, g.M, g.N, g.K, g.batch2, g.flags, ctx->d_status, g.mask, g.mask_ld, g.mask_group};
   return tc_run(ctx, A, B, ep);
 }

@@ -35,7 +35,10 @@ static bool force_simt_engine() { static const bool f = [] { const char* e = get
 // Chooses the tensor-core engine for large K-major x K-major products and the SIMT engine for the rest.
 static int gemm(Ctx* ctx, const GemmDesc& g) {
   int rc;
-  if (!force_simt_engine() && gemm_tc_eligible(ctx, g)) rc = gemm_tc(ctx, g);          // brackets its kernel launches itself
+  if (!force_simt_engine() && gemm_tc_eligible(ctx, g)) {                                 // brackets its kernel launches itself
+    GemmDesc h = g; if (!h.b_planes) h.b_planes = wplanes_lookup(ctx, g);                 // weight matrices come with prepared planes
+    rc = gemm_tc(ctx, h);
+  }
   else { ProfScope prof(ctx); rc = gemm_simt(ctx, g); }
   double nb = (double)g.batch1 * g.batch2;
   double flops = 2.0 * g.M * (double)g.N * g.K * nb;
@@ -101,6 +104,7 @@ struct gn_model {
   std::vector<cudaEvent_t> layer_ev;    // gradient of layer i complete (multi-GPU: releases its all-reduce)
   bool alive = true;
   bool has_lstm = false;
+  gn::WeightPlaneTable wplanes;         // prepared tensor-core operand planes of the Dense / TransformerBlock weight matrices
 };
 
 namespace gn {
@@ -163,6 +167,11 @@ static int plan_layers(gn_model* m, const gn_layer_desc* layers, int n) {
         if (d.out_size > 1024) return fail(GN_ERR_UNSUPPORTED, "layer %d: LSTM hidden size > 1024", i);
         l.in_size = d.seq_len * d.in_size; l.out_size = d.return_seq ? d.seq_len * d.out_size : d.out_size;
         l.p_cnt = (int64_t)4 * d.out_size * d.in_size + (int64_t)4 * d.out_size * d.out_size + 4 * d.out_size; m->has_lstm = true; break;
+      case GN_LAYER_GRU_UNROLLED:
+        if (d.in_size <= 0 || d.out_size <= 0 || d.seq_len <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad GRU descriptor", i);
+        if (((size_t)2 * d.out_size * d.out_size + 3 * (size_t)d.out_size) * sizeof(float) > 200 * 1024) return fail(GN_ERR_UNSUPPORTED, "layer %d: GRU hidden size %d (both recurrent matrices must fit shared memory)", i, d.out_size);
+        l.in_size = d.seq_len * d.in_size; l.out_size = d.return_seq ? d.seq_len * d.out_size : d.out_size;
+        l.p_cnt = (int64_t)3 * d.out_size * d.in_size + (int64_t)2 * d.out_size * d.out_size + 3 * d.out_size; break;
       case GN_LAYER_EMBEDDING: {
         int T = d.seq_len; for (int j = i + 1; j < n && T <= 0; j++) T = layers[j].seq_len;
         if (T <= 0 || d.in_size <= 0 || d.out_size <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: Embedding needs vocab, dim and a sequence length", i);
@@ -225,6 +234,9 @@ static int alloc_activations(gn_model* m, int cap) {
       case GN_LAYER_LSTM_UNROLLED: {
         size_t th = c * d.seq_len * d.out_size;
         GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.pre_i.alloc(th)); GN_TRY(l.c_all.alloc(th)); GN_TRY(l.h_all.alloc(th)); GN_TRY(l.dgate.alloc(4 * th)); break; }
+      case GN_LAYER_GRU_UNROLLED: {
+        size_t th = c * d.seq_len * d.out_size;     // pre_i: pre-activations [.,T,3H]; c_all: h_{t-1}; z: r (.) h_{t-1}; dgate: deltas [.,T,3H]
+        GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.pre_i.alloc(3 * th)); GN_TRY(l.c_all.alloc(th)); GN_TRY(l.h_all.alloc(th)); GN_TRY(l.z.alloc(th)); GN_TRY(l.dgate.alloc(3 * th)); break; }
       case GN_LAYER_EMBEDDING: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.idx.alloc(c * d.seq_len)); break;
       case GN_LAYER_POSENC: GN_TRY(l.out.alloc(c * l.out_size)); break;
       case GN_LAYER_TRANSFORMER_BLOCK: {
@@ -273,6 +285,49 @@ static bool use_fused_attention(const gn_layer_desc& d) {
   return !unfused && attn_fused_supported(d.dim / d.heads, d.dim);
 }
 
+// ---------------------------------------------------------------- Conv2D (both paths)
+// z / out: [B, outC, oH, oW].  Implicit GEMM on the tensor cores when `allow_tc` and the engine takes the shape (bias
+// and ReLU in the epilogue, other activations from the kept pre-activation z); else the direct kernel (writes z and out).
+static int conv_forward(Ctx* ctx, const ConvShape& c, int act, float alpha, const float* x, const float* p, float* z, float* out, bool allow_tc) {
+  const long n = (long)c.B * c.outC * c.oH * c.oW; const float* bias = p + (long)c.outC * c.inC * c.k * c.k;
+  if (allow_tc && conv_tc_supported(ctx, c)) {
+    const bool in_epilogue = act == GN_ACT_LINEAR || act == GN_ACT_RELU;
+    GN_TRY(conv_tc_forward(ctx, c, x, p, bias, in_epilogue ? out : z, in_epilogue ? act : GN_ACT_LINEAR));
+    if (!in_epilogue) GN_LAUNCH(ctx, act_forward_kernel, ew_grid(ctx, n), 256, 0, z, out, n, act, alpha);
+  } else GN_LAUNCH(ctx, conv2d_fwd_kernel, ew_grid(ctx, n), 256, 0, x, p, bias, z, out, c, act, alpha);
+  return check_launch("conv_forward");
+}
+// g: gradient with respect to the activation; gW / gb are added to; dx (may be null) is written.
+static int conv_backward(gn_model* m, const ConvShape& c, int act, float alpha, const float* g, const float* x, const float* p, const float* z, const float* out,
+                         float* gW, float* gb, float* dx, bool allow_tc) {
+  Ctx* ctx = &m->ctx->c;
+  const long n = (long)c.B * c.outC * c.oH * c.oW; float* dzb; GN_TRY(ensure(m, S_DZ, (size_t)n, &dzb));
+  // ReLU'(z) = [z > 0] = [a > 0], so ReLU (and the identity) work from the activation; the others need the pre-activation
+  const float* zsrc = (act == GN_ACT_RELU || act == GN_ACT_LINEAR) ? out : z;
+  GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, zsrc, dzb, n, act, alpha);
+  const int nW = c.outC * c.inC * c.k * c.k;
+  const bool conv_tc = allow_tc && conv_tc_supported(ctx, c);
+  if (conv_tc) {
+    float* part; GN_TRY(ensure(m, S_PART, (size_t)c.B * (nW + c.outC), &part));
+    GN_TRY(conv_tc_wgrad(ctx, c, dzb, x, part, gW, gb));
+  } else if (c.k == 3 || c.k == 5 || c.k == 1) {
+    const int pairs = c.outC * c.inC, slices = std::max(1, std::min(c.B, (4 * ctx->sm_count + pairs - 1) / pairs)), ng = nW + c.outC;
+    float* part; GN_TRY(ensure(m, S_PART, (size_t)slices * ng, &part));
+    if (c.k == 3) GN_LAUNCH(ctx, conv2d_wgrad_tile_kernel<3>, dim3(pairs, slices), 256, 0, dzb, x, part, c, slices);
+    else if (c.k == 5) GN_LAUNCH(ctx, conv2d_wgrad_tile_kernel<5>, dim3(pairs, slices), 256, 0, dzb, x, part, c, slices);
+    else GN_LAUNCH(ctx, conv2d_wgrad_tile_kernel<1>, dim3(pairs, slices), 256, 0, dzb, x, part, c, slices);
+    GN_LAUNCH(ctx, conv2d_wgrad_final_kernel, cdiv(ng, 256), 256, 0, part, slices, ng, gW);          // weights, then biases: gb follows gW
+  } else GN_LAUNCH(ctx, conv2d_wgrad_kernel, nW + c.outC, 256, 0, dzb, x, gW, gb, c);
+  if (dx) {
+    const long ni = (long)c.B * c.inC * c.H * c.W;
+    if (conv_tc && c.s == 1) { float* wtmp; GN_TRY(ensure(m, S_DELTA, (size_t)nW, &wtmp)); GN_TRY(conv_tc_dgrad(ctx, c, dzb, p, wtmp, dx)); }
+    else if (c.s == 1 && c.k == 3) GN_LAUNCH(ctx, conv2d_dgrad_s1_kernel<3>, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
+    else if (c.s == 1 && c.k == 5) GN_LAUNCH(ctx, conv2d_dgrad_s1_kernel<5>, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
+    else GN_LAUNCH(ctx, conv2d_dgrad_kernel, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
+  }
+  return check_launch("conv_backward");
+}
+
 // ---------------------------------------------------------------- forward
 static int attention_forward(gn_model* m, LayerRT& l, int B, float* P) {
   Ctx* ctx = &m->ctx->c; const gn_layer_desc& d = l.d;
@@ -300,6 +355,8 @@ static BlockParams block_params(const float* p, int D, int F) {
 
 static int forward(gn_model* m, const float* x, int B, const float** y_out, bool training) {
   Ctx* ctx = &m->ctx->c;
+  GN_TRY(wplanes_refresh(ctx, m->wplanes));          // no-op unless the parameters changed since the last pass
+  ctx->weight_planes = &m->wplanes;
   const float* cur = x;
   for (size_t li = 0; li < m->L.size(); li++) {
     LayerRT& l = m->L[li]; const gn_layer_desc& d = l.d; const float* p = m->params.p + l.p_off;
@@ -319,13 +376,7 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
       case GN_LAYER_CONV2D: {
         ConvShape c{B, d.in_size, d.out_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
                     (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
-        long n = (long)B * l.out_size; const float* bias = p + (long)d.out_size * d.in_size * d.kernel * d.kernel;
-        if (!force_simt_engine() && conv_tc_supported(ctx, c)) {
-          // implicit GEMM on the tensor cores; bias and ReLU in the epilogue, other activations from the kept pre-activation
-          const bool in_epilogue = d.activation == GN_ACT_LINEAR || d.activation == GN_ACT_RELU;
-          GN_TRY(conv_tc_forward(ctx, c, cur, p, bias, in_epilogue ? l.out.p : l.z.p, in_epilogue ? d.activation : GN_ACT_LINEAR));
-          if (!in_epilogue) GN_LAUNCH(ctx, act_forward_kernel, ew_grid(ctx, n), 256, 0, l.z.p, l.out.p, n, d.activation, act_alpha_of(d.activation, d.reserved));
-        } else GN_LAUNCH(ctx, conv2d_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, p, bias, l.z.p, l.out.p, c, d.activation, act_alpha_of(d.activation, d.reserved));
+        GN_TRY(conv_forward(ctx, c, d.activation, act_alpha_of(d.activation, d.reserved), cur, p, l.z.p, l.out.p, !force_simt_engine()));
         cur = l.out.p; break; }
       case GN_LAYER_MAXPOOL2D: {
         PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
@@ -368,6 +419,15 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         }
         GN_LAUNCH(ctx, lstm_fwd_kernel, B, threads, smem, cur, p, p + (long)4 * H * in, p + (long)4 * H * in + (long)4 * H * H,
                   l.pre_i.p, l.c_all.p, l.h_all.p, l.out.p, d.seq_len, in, H, d.return_seq, xproj);
+        cur = l.out.p; break; }
+      case GN_LAYER_GRU_UNROLLED: {
+        const int H = d.out_size, in = d.in_size, T = d.seq_len, threads = ((H + 31) / 32) * 32;
+        const float* Wx = p; const float* Wh = p + (long)3 * H * in; const float* bias = Wh + (long)2 * H * H;
+        // input projection of all three gates and all B*T rows as one contraction (bias in its epilogue), then the recurrence
+        GN_TRY(gemm_nt(ctx, B * T, 3 * H, in, cur, in, Wx, bias, l.pre_i.p, 3 * H));
+        const size_t smem = ((size_t)2 * H * H + 3 * (size_t)H) * sizeof(float);
+        GN_CUDA(cudaFuncSetAttribute(gru_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        GN_LAUNCH(ctx, gru_fwd_kernel, B, threads, smem, Wh, l.pre_i.p, l.h_all.p, l.out.p, T, H, d.return_seq);
         cur = l.out.p; break; }
       case GN_LAYER_EMBEDDING: {
         // fused with a directly following PositionalEncoding
@@ -641,31 +701,9 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
       case GN_LAYER_CONV2D: {
         ConvShape c{B, d.in_size, d.out_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
                     (d.in_h + 2 * d.padding - d.kernel) / d.stride + 1, (d.in_w + 2 * d.padding - d.kernel) / d.stride + 1};
-        long n = (long)B * l.out_size; float* dzb; GN_TRY(ensure(m, S_DZ, (size_t)n, &dzb));
-        // ReLU'(z) = [z > 0] = [a > 0], so ReLU (and the identity) work from the activation; the others need the pre-activation
-        const float* zsrc = (d.activation == GN_ACT_RELU || d.activation == GN_ACT_LINEAR) ? l.out.p : l.z.p;
-        GN_LAUNCH(ctx, act_backward_kernel, ew_grid(ctx, n), 256, 0, g, zsrc, dzb, n, d.activation, act_alpha_of(d.activation, d.reserved));
-        int nW = d.out_size * d.in_size * d.kernel * d.kernel;
-        const bool conv_tc = !force_simt_engine() && conv_tc_supported(ctx, c);
-        if (conv_tc) {
-          float* part; GN_TRY(ensure(m, S_PART, (size_t)B * (nW + d.out_size), &part));
-          GN_TRY(conv_tc_wgrad(ctx, c, dzb, xin, part, gr, gr + nW));
-        } else if (d.kernel == 3 || d.kernel == 5 || d.kernel == 1) {
-          const int pairs = d.out_size * d.in_size, slices = std::max(1, std::min(B, (4 * ctx->sm_count + pairs - 1) / pairs)), ng = nW + d.out_size;
-          float* part; GN_TRY(ensure(m, S_PART, (size_t)slices * ng, &part));
-          if (d.kernel == 3) GN_LAUNCH(ctx, conv2d_wgrad_tile_kernel<3>, dim3(pairs, slices), 256, 0, dzb, xin, part, c, slices);
-          else if (d.kernel == 5) GN_LAUNCH(ctx, conv2d_wgrad_tile_kernel<5>, dim3(pairs, slices), 256, 0, dzb, xin, part, c, slices);
-          else GN_LAUNCH(ctx, conv2d_wgrad_tile_kernel<1>, dim3(pairs, slices), 256, 0, dzb, xin, part, c, slices);
-          GN_LAUNCH(ctx, conv2d_wgrad_final_kernel, cdiv(ng, 256), 256, 0, part, slices, ng, gr);
-        } else GN_LAUNCH(ctx, conv2d_wgrad_kernel, nW + d.out_size, 256, 0, dzb, xin, gr, gr + nW, c);
-        if (need_dx) {
-          long ni = (long)B * l.in_size;
-          if (conv_tc && d.stride == 1) { float* wtmp; GN_TRY(ensure(m, S_DELTA, (size_t)nW, &wtmp)); GN_TRY(conv_tc_dgrad(ctx, c, dzb, p, wtmp, dx)); }
-          else if (d.stride == 1 && d.kernel == 3) GN_LAUNCH(ctx, conv2d_dgrad_s1_kernel<3>, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
-          else if (d.stride == 1 && d.kernel == 5) GN_LAUNCH(ctx, conv2d_dgrad_s1_kernel<5>, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
-          else GN_LAUNCH(ctx, conv2d_dgrad_kernel, ew_grid(ctx, ni), 256, 0, dzb, p, dx, c);
-          g = dx; flip ^= 1;
-        }
+        const int nW = d.out_size * d.in_size * d.kernel * d.kernel;
+        GN_TRY(conv_backward(m, c, d.activation, act_alpha_of(d.activation, d.reserved), g, xin, p, l.z.p, l.out.p, gr, gr + nW, need_dx ? dx : nullptr, !force_simt_engine()));
+        if (need_dx) { g = dx; flip ^= 1; }
         break; }
       case GN_LAYER_MAXPOOL2D: {
         PoolShape c{B, d.in_size, d.kernel, d.stride, d.padding, d.in_h, d.in_w,
@@ -691,6 +729,19 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
       case GN_LAYER_FLATTEN: break;
       case GN_LAYER_LSTM_UNROLLED:
         GN_TRY(lstm_backward(m, l, li, B, xin, g, global_batch, first_sample, dx)); if (need_dx) { g = dx; flip ^= 1; } break;
+      case GN_LAYER_GRU_UNROLLED: {
+        const int H = d.out_size, in = d.in_size, T = d.seq_len, threads = ((H + 31) / 32) * 32;
+        const float* Wx = p; const float* Wh = p + (long)3 * H * in;
+        float* gWx = gr; float* gWh = gr + (long)3 * H * in; float* gb = gWh + (long)2 * H * H;
+        GN_LAUNCH(ctx, gru_bwd_kernel, B, threads, (size_t)2 * H * sizeof(float), g, Wh, (const float*)l.pre_i.p, (const float*)l.h_all.p, l.dgate.p, l.c_all.p, l.z.p, T, H, d.return_seq);
+        // input weights and biases: every step's delta meets the input of the LAST forward call (gru.go:429-447), so per sample
+        // gWx = (sum_t d_t) (x) x_{T-1}: the same batch-level contraction as the inner Dense layers of a TransformerBlock
+        GN_TRY(inner_dense_param_grads(m, l.dgate.p, B, T, 3 * H, xin, in, gWx, gb));
+        // recurrent weights: update rows from h_{t-1}, reset rows from the candidate's delta and r (.) h_{t-1} (gru.go:450-476)
+        GN_TRY(gemm_tn(ctx, B * T, H, H, l.dgate.p, 3 * H, l.c_all.p, H, gWh));
+        GN_TRY(gemm_tn(ctx, B * T, H, H, l.dgate.p + 2 * H, 3 * H, l.z.p, H, gWh + (long)H * H));
+        if (need_dx) { GN_TRY(gemm_nn(ctx, B * T, 3 * H, in, l.dgate.p, 3 * H, Wx, dx, in)); g = dx; flip ^= 1; }
+        break; }
       case GN_LAYER_EMBEDDING: {
         // Only the last sample of every worker chunk reaches the table (embedding.go:151-154): global samples
         // c*chunk + chunk - 1 and the very last one.
@@ -857,7 +908,7 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
     cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream); cudaStreamSynchronize(ctx->stream);
     return status_error(st);
   }
-  m->timestep += 1;
+  m->timestep += 1; m->wplanes.dirty = true;        // the parameters moved: their operand planes are stale
   if (mean_loss) *mean_loss = m->h_ret[0] / (float)global_batch;
   m->stats.kernel_launches = ctx->launches - launches0;
   cudaEventElapsedTime(&m->stats.step_ms, m->ev0, m->ev1);
@@ -992,6 +1043,23 @@ int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int 
     GN_CUDA(cudaMemsetAsync(m->m1.p, 0, P * 4, st)); GN_CUDA(cudaMemsetAsync(m->v2.p, 0, P * 4, st));
     GN_CUDA(cudaStreamSynchronize(st));
   }
+  if (ctx->c.tc_ok && !force_simt_engine() && !getenv("GONEURON_CUDA_NO_WEIGHT_PLANES")) {
+    // weight matrices large enough to run on the tensor-core engine get prepared operand planes (both orientations)
+    std::vector<WeightPlaneEntry> mats;
+    auto add = [&](int64_t off, int out, int in) { if ((double)out * in >= 64.0 * 64.0) mats.push_back(WeightPlaneEntry{m->params.p + off, out, in, {}, {}}); };
+    for (auto& l : m->L) {
+      const gn_layer_desc& d = l.d;
+      if (d.kind == GN_LAYER_DENSE) add(l.p_off, d.out_size, d.in_size);
+      else if (d.kind == GN_LAYER_TRANSFORMER_BLOCK) {
+        const int64_t dd = (int64_t)d.dim * d.dim + d.dim; int64_t o = l.p_off;
+        for (int k = 0; k < 4; k++) { add(o, d.dim, d.dim); o += dd; }
+        o += 4 * (int64_t)d.dim;
+        add(o, d.ff_dim, d.dim); o += (int64_t)d.dim * d.ff_dim + d.ff_dim;
+        add(o, d.dim, d.ff_dim);
+      }
+    }
+    GN_TRY(wplanes_build(&ctx->c, m->wplanes, mats));
+  }
   if (m->NS > 0) {
     GN_TRY(m->state.alloc((size_t)m->NS));
     std::vector<float> init((size_t)m->NS, 0.f);     // running mean 0, running variance 1 (batchnorm2d.go:124-128)
@@ -1012,6 +1080,8 @@ int gn_model_destroy(gn_model* m) {
   std::lock_guard<std::mutex> lk(m->mu);
   cudaSetDevice(m->ctx->c.device);
   if (m->ctx->alive && m->ctx->c.stream) cudaStreamSynchronize(m->ctx->c.stream);
+  if (m->ctx->c.weight_planes == &m->wplanes) m->ctx->c.weight_planes = nullptr;
+  m->wplanes = gn::WeightPlaneTable();
   m->L.clear(); m->scratch.clear(); m->state.release(); m->params.release(); m->grads.release(); m->m1.release(); m->v2.release();
   m->xin.release(); m->yin.release(); m->lossg.release(); m->loss_s.release(); m->loss_sum.release();
   if (m->ev0) cudaEventDestroy(m->ev0); if (m->ev1) cudaEventDestroy(m->ev1); if (m->ar0) cudaEventDestroy(m->ar0); if (m->ar1) cudaEventDestroy(m->ar1);
@@ -1028,6 +1098,7 @@ int gn_model_set_params(gn_model* m, const float* host, int64_t n) {
   CHECK_MODEL(m); if (!host || n != m->P) return fail(GN_ERR_INVALID_ARG, "set_params: expected %lld floats, got %lld", (long long)m->P, (long long)n);
   std::lock_guard<std::mutex> lk(m->mu); USE_DEVICE(m);
   GN_CUDA(cudaMemcpyAsync(m->params.p, host, (size_t)n * 4, cudaMemcpyHostToDevice, m->ctx->c.stream));
+  m->wplanes.dirty = true;
   GN_CUDA(cudaStreamSynchronize(m->ctx->c.stream)); return GN_OK;
 }
 int gn_model_get_params(gn_model* m, float* host, int64_t n) {
@@ -1181,3 +1252,4 @@ int gn_op_attention(gn_ctx* ctx, int engine, int B, int T, int D, int H, int cau
 }  // extern "C"
 
 #include "gemm_static.cuh"
+#include "ops_tier.cuh"

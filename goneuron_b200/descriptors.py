@@ -3,7 +3,7 @@ constructors named after the reference's (goneuron/goneuron.go:59-340, internal/
 import ctypes as C
 
 # gn_layer_kind
-DENSE, CONV2D, MAXPOOL2D, FLATTEN, LSTM_UNROLLED, EMBEDDING, POSENC, TRANSFORMER_BLOCK, CLS_POOLING, LAYERNORM, BATCHNORM2D, AVGPOOL2D, DROPOUT, RMSNORM, CONV1D = range(1, 16)
+DENSE, CONV2D, MAXPOOL2D, FLATTEN, LSTM_UNROLLED, EMBEDDING, POSENC, TRANSFORMER_BLOCK, CLS_POOLING, LAYERNORM, BATCHNORM2D, AVGPOOL2D, DROPOUT, RMSNORM, CONV1D, GRU_UNROLLED = range(1, 17)
 # gn_activation
 LINEAR, RELU, SIGMOID, TANH, SOFTMAX, LOGSOFTMAX, GELU, SILU, LEAKY_RELU, ELU = range(10)
 # gn_loss_kind
@@ -72,6 +72,11 @@ def Flatten():
 def SequenceUnrollerLSTM(in_size, hidden, seq_len, return_seq=False):
     """layer.NewSequenceUnroller(layer.NewLSTM(in, hidden), T, returnSeq) -- unroller.go:57, lstm.go:276."""
     return LayerDesc(kind=LSTM_UNROLLED, in_size=in_size, out_size=hidden, seq_len=seq_len, return_seq=int(return_seq))
+
+
+def SequenceUnrollerGRU(in_size, hidden, seq_len, return_seq=False):
+    """layer.NewSequenceUnroller(layer.NewGRU(in, hidden), T, returnSeq) -- unroller.go:57, gru.go:81."""
+    return LayerDesc(kind=GRU_UNROLLED, in_size=in_size, out_size=hidden, seq_len=seq_len, return_seq=int(return_seq))
 
 
 def Embedding(vocab, dim, seq_len=0):

@@ -149,11 +149,18 @@ class Sequential:
         if np.asarray(ckpt["state"]).size:
             self.SetState(ckpt["state"])
 
+    @staticmethod
+    def _ckpt_path(path):
+        """np.savez appends ".npz" to a name without it; Save and Load agree on the file name by doing the same."""
+        path = str(path)
+        return path if path.endswith(".npz") else path + ".npz"
+
     def Save(self, path):
-        np.savez(path, **self.Checkpoint())
+        with open(self._ckpt_path(path), "wb") as f:
+            np.savez(f, **self.Checkpoint())
 
     def Load(self, path):
-        with np.load(path) as f:
+        with np.load(self._ckpt_path(path)) as f:
             self.Restore({k: f[k] for k in f.files})
 
     # -- training ---------------------------------------------------------------
@@ -205,12 +212,17 @@ class Sequential:
         return self.PredictBatch(_f32(x).reshape(1, -1))[0]
 
     def Evaluate(self, x, y):
-        """Sequential.Evaluate (sequential.go:172-183): mean per-sample loss without a weight update."""
+        """Sequential.Evaluate (sequential.go:172-183): mean per-sample loss without a weight update.  The forward pass
+        runs on the device; the per-sample loss of the few outputs is formed on the host in float32, term by term as
+        loss.go:53-69 (MSE) and :120-138 (CrossEntropy, probabilities clipped at 1e-10) do."""
         p = self.PredictBatch(x)
         y = _f32(y)
         if self.loss == 0:
-            return float(np.mean(np.mean((p - y) ** 2, axis=1)))
-        return float(np.mean(-np.sum(y * np.log(np.maximum(p, 1e-10)), axis=1)))
+            d = p - y
+            per = np.sum(d * d, axis=1, dtype=np.float32) / np.float32(p.shape[1])
+        else:
+            per = -np.sum(y * np.log(np.maximum(p, np.float32(1e-10)).astype(np.float64)).astype(np.float32), axis=1, dtype=np.float32)
+        return float(np.sum(per, dtype=np.float32) / np.float32(p.shape[0]))
 
     def stats(self):
         s = _lib.StepStats()

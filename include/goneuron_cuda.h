@@ -57,8 +57,10 @@ typedef enum gn_layer_kind {
   GN_LAYER_DROPOUT = 13,       /* layer.NewDropout(p, inSize): in_size = inSize, dim = bits of float p;  internal/layer/dropout.go:36-155, 241-293.
                                   State: two floats = number of random draws consumed so far (low 20 bits | the rest). */
   GN_LAYER_RMSNORM = 14,       /* layer.NewRMSNorm(dim, eps) applied row-wise: dim = dim, reserved = bits of eps (0 selects 1e-5)  rmsnorm.go:157-336 */
-  GN_LAYER_CONV1D = 15         /* layer.NewConv1D(inC,outC,k,stride,pad,act): in_size = inC, out_size = outC, in_w = input length;
+  GN_LAYER_CONV1D = 15,        /* layer.NewConv1D(inC,outC,k,stride,pad,act): in_size = inC, out_size = outC, in_w = input length;
                                   the backward pass does not apply the activation's derivative  conv1d.go:128-288 */
+  GN_LAYER_GRU_UNROLLED = 16   /* NewSequenceUnroller(NewGRU(in,H),T,returnSeq): in_size = in, out_size = H; parameters Wx [3H,in] |
+                                  Wh [2H,H] | b [3H], gates update, reset, candidate  gru.go:81-534, unroller.go:57-213 */
 } gn_layer_kind;
 
 /* Activations (reference: internal/activations/activations.go:22-236,342-352). */
@@ -233,6 +235,32 @@ int gn_op_adam(gn_ctx* ctx, float* params, const float* grads, float* m1, float*
 int gn_op_attention(gn_ctx* ctx, int engine, int B, int T, int D, int H, int causal,
                     const float* Q, const float* K, const float* V, const float* dO,
                     float* O, float* M, float* L, float* dQ, float* dK, float* dV);
+
+/* One LayerNorm over `rows` rows of width n on host arrays: y = gamma * (x - mean) / sqrt(var + 1e-5) + beta
+ * (layernorm.go:193-304); with dy != NULL also the backward pass with the reference's second term divided by
+ * N * std^2 (layernorm.go:385-441): dx [rows, n], dgamma [n], dbeta [n] (sums over the rows). */
+int gn_op_layernorm(gn_ctx* ctx, int64_t rows, int n, const float* x, const float* gamma, const float* beta, const float* dy,
+                    float* y, float* dx, float* dgamma, float* dbeta);
+
+/* One Conv2D layer (NCHW, zero padding) on host arrays: y = act(conv(x, w) + bias) (conv2d.go:716-959); with dy != NULL
+ * (gradient with respect to y) also dx, dw, db of one batch (conv2d.go:997-1174).  engine: 0 = direct CUDA-core kernels,
+ * 1 = implicit GEMM on the tensor-core engine (all three directions; the input gradient for stride 1). */
+int gn_op_conv2d(gn_ctx* ctx, int engine, int B, int in_c, int out_c, int kernel, int stride, int pad, int H, int W, int activation,
+                 const float* x, const float* w, const float* bias, const float* dy, float* y, float* dx, float* dw, float* db);
+
+/* The classification head after its Dense product, on host arrays [B, V]: out = softmax(z) or log-softmax(z)
+ * (activations.go:146-236); loss[B] = CrossEntropy(out, y) per sample (loss.go:120-138, probabilities clipped at 1e-10);
+ * dz = the gradient that reaches the pre-activations: CrossEntropy's (out - y) pushed through the head's Jacobian
+ * (loss.go:165-178, layer.go:504-560).  loss and dz may be NULL. */
+int gn_op_softmax_ce(gn_ctx* ctx, int B, int V, int log_softmax, const float* z, const float* y, float* out, float* loss, float* dz);
+
+/* The LSTM recurrence of SequenceUnroller(LSTM(in, H), T, returnSeq = false) on host arrays: x [B, T*in], wx [4H, in],
+ * wh [4H, H], bias [4H] (gate order i, f, g, o); h_all, c_all [B, T, H] receive every step's hidden and cell state
+ * (lstm.go:276-407: only the input-gate rows receive wx x + wh h).  With dh_last != NULL ([B, H], gradient of the last
+ * hidden state) also the gate deltas of back-propagation through time, dgate [B, T, 4H] (lstm.go:476-691).
+ * engine: 0 = input projection inside the recurrence kernel, 1 = as one tensor-core contraction over all B*T rows. */
+int gn_op_lstm(gn_ctx* ctx, int engine, int B, int T, int in_size, int H, const float* x, const float* wx, const float* wh, const float* bias,
+               const float* dh_last, float* h_all, float* c_all, float* dgate);
 
 /* The same product as gn_op_gemm_nt with engine 1 (C = A B^T + bias on the tensor cores), for callers that
  * must not allocate device memory: hosts whose own pool already owns all of HBM, and hosts with a per-step

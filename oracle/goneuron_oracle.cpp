@@ -575,6 +575,90 @@ template <class R> struct LSTMUnrolled : Layer<R> {
   }
 };
 
+// reference: internal/layer/gru.go:192-288 (forward), :360-534 (backward); internal/layer/unroller.go:57-127, :133-213.
+// Literal behaviours kept: the cell candidate's recurrent product uses the RESET gate's recurrent rows applied to
+// r (.) h_prev (gru.go:247-258; the layer has only 2H recurrent rows); the backward pass never computes the reset gate's
+// delta (dResetBuf stays zero, gru.go:413-476), scales the candidate's gradient by (1 - z) and the hidden-state
+// pass-through by z although the forward pass is h = h_prev + z (c - h_prev) (gru.go:395-399, :521), indexes the reset
+// gate by the OUTPUT unit in the candidate's contribution to dh_prev (gru.go:517), uses the input of the LAST forward
+// call for every time step's input-weight gradient (g.inputBuf, gru.go:429-447), and adds dh_prev INTO the incoming
+// gradient, which the unroller carries to the previous step (gru.go:524-527, unroller.go:190-209).  No gradient clipping.
+template <class R> struct GRUUnrolled : Layer<R> {
+  int in, H, T; bool returnSeq;
+  const R *Wx = nullptr, *Wh = nullptr, *b = nullptr; R *gWx = nullptr, *gWh = nullptr, *gb = nullptr;
+  std::vector<R> inputBuf, hidden, h_all, pre_all, outBuf, gradIn;
+  GRUUnrolled(int in_, int H_, int T_, bool rs) : in(in_), H(H_), T(T_), returnSeq(rs), inputBuf(in_), hidden(H_), h_all((size_t)T_ * H_),
+      pre_all((size_t)T_ * 3 * H_), outBuf(rs ? (size_t)T_ * H_ : (size_t)H_), gradIn((size_t)T_ * in_) {}
+  int64_t n_params() const override { return (int64_t)3 * H * in + (int64_t)2 * H * H + 3 * H; }
+  void bind(const R* p, R* g) override {
+    Wx = p; Wh = p + (int64_t)3 * H * in; b = Wh + (int64_t)2 * H * H;
+    gWx = g; gWh = g ? g + (int64_t)3 * H * in : nullptr; gb = g ? gWh + (int64_t)2 * H * H : nullptr;
+  }
+  int in_size() const override { return T * in; }
+  int out_size() const override { return returnSeq ? T * H : H; }
+  const R* forward(const R* x) override {
+    std::fill(hidden.begin(), hidden.end(), R(0));                          // unroller.go:66 base.Reset(), gru.go:180-188
+    std::vector<R> z(H), r(H), c(H);
+    for (int t = 0; t < T; t++) {
+      const R* xt = x + (size_t)t * in;
+      std::copy(xt, xt + in, inputBuf.begin());
+      R* pre = pre_all.data() + (size_t)t * 3 * H;
+      for (int i = 0; i < 3 * H; i++) pre[i] = b[i];
+      for (int g = 0; g < 3; g++) for (int i = 0; i < H; i++) { R sum = 0; for (int j = 0; j < in; j++) sum += Wx[((int64_t)g * H + i) * in + j] * xt[j]; pre[g * H + i] += sum; }
+      for (int g = 0; g < 2; g++) for (int i = 0; i < H; i++) { R sum = 0; for (int j = 0; j < H; j++) sum += Wh[((int64_t)g * H + i) * H + j] * hidden[j]; pre[g * H + i] += sum; }
+      for (int i = 0; i < H; i++) { z[i] = sigmoid<R>(pre[i]); r[i] = sigmoid<R>(pre[H + i]); }
+      for (int i = 0; i < H; i++) {
+        R sum = 0; for (int j = 0; j < H; j++) sum += Wh[((int64_t)H + i) * H + j] * (r[j] * hidden[j]);
+        pre[2 * H + i] += sum; c[i] = r_tanh<R>(pre[2 * H + i]);
+      }
+      for (int i = 0; i < H; i++) hidden[i] = hidden[i] + z[i] * (c[i] - hidden[i]);
+      std::copy(hidden.begin(), hidden.end(), h_all.begin() + (size_t)t * H);
+      if (returnSeq) std::copy(hidden.begin(), hidden.end(), outBuf.begin() + (size_t)t * H);
+      else if (t == T - 1) std::copy(hidden.begin(), hidden.end(), outBuf.begin());
+    }
+    return outBuf.data();
+  }
+  const R* backward(R* grad) override {
+    std::vector<R> dhNext(H, R(0)), cur(H), z(H), r(H), c(H), dU(H), dC(H), zeros(H, R(0));
+    for (int t = T - 1; t >= 0; t--) {
+      for (int i = 0; i < H; i++) cur[i] = dhNext[i];
+      if (returnSeq) { for (int i = 0; i < H; i++) cur[i] += grad[(size_t)t * H + i]; }
+      else if (t == T - 1) { for (int i = 0; i < H; i++) cur[i] += grad[i]; }
+      const R* pre = pre_all.data() + (size_t)t * 3 * H;
+      const R* hPrev = t > 0 ? h_all.data() + (size_t)(t - 1) * H : zeros.data();
+      for (int i = 0; i < H; i++) { z[i] = sigmoid<R>(pre[i]); r[i] = sigmoid<R>(pre[H + i]); c[i] = r_tanh<R>(pre[2 * H + i]); }
+      for (int i = 0; i < H; i++) {
+        R dhc = cur[i] * (R(1) - z[i]);                                     // gru.go:395-399
+        R du = cur[i] * (c[i] - hPrev[i]);                                  // :402-405
+        dU[i] = du * z[i] * (R(1) - z[i]);                                  // :409-411
+        dC[i] = dhc * (R(1) - c[i] * c[i]);                                 // :414-418
+      }
+      // :421-447 input weights and biases (reset-gate rows receive zero); :450-476 recurrent weights
+      for (int i = 0; i < H; i++) { for (int j = 0; j < in; j++) gWx[(int64_t)i * in + j] += dU[i] * inputBuf[j]; gb[i] += dU[i]; }
+      for (int i = 0; i < H; i++) { for (int j = 0; j < in; j++) gWx[((int64_t)2 * H + i) * in + j] += dC[i] * inputBuf[j]; gb[2 * H + i] += dC[i]; }
+      for (int i = 0; i < H; i++) for (int j = 0; j < H; j++) gWh[(int64_t)i * H + j] += dU[i] * hPrev[j];
+      for (int i = 0; i < H; i++) for (int j = 0; j < H; j++) gWh[((int64_t)H + i) * H + j] += dC[i] * (r[j] * hPrev[j]);
+      // :482-499 input gradient
+      for (int i = 0; i < in; i++) {
+        R sum = 0;
+        for (int j = 0; j < H; j++) sum += Wx[(int64_t)j * in + i] * dU[j];
+        for (int j = 0; j < H; j++) sum += Wx[((int64_t)H + j) * in + i] * R(0);
+        for (int j = 0; j < H; j++) sum += Wx[((int64_t)2 * H + j) * in + i] * dC[j];
+        gradIn[(size_t)t * in + i] = sum;
+      }
+      // :503-527 previous hidden state, added into the incoming gradient
+      for (int i = 0; i < H; i++) {
+        R sum = 0;
+        for (int j = 0; j < H; j++) sum += Wh[(int64_t)j * H + i] * dU[j];
+        for (int j = 0; j < H; j++) sum += Wh[((int64_t)H + j) * H + i] * dC[j] * r[j];
+        sum += cur[i] * z[i];
+        dhNext[i] = cur[i] + sum;
+      }
+    }
+    return gradIn.data();
+  }
+};
+
 // reference: internal/layer/embedding.go:79-139, :147-183
 template <class R> struct Embedding : Layer<R> {
   int V, d, T; const R* W = nullptr; R* gW = nullptr;
@@ -869,6 +953,7 @@ template <class R> struct Net {
         case GN_LAYER_AVGPOOL2D: p.reset(new AvgPool2D<R>(l.in_size, l.kernel, l.stride, l.padding, l.in_h, l.in_w)); break;
         case GN_LAYER_FLATTEN: if (cur < 0) { g_err = "Flatten cannot be first"; return false; } p.reset(new Flatten<R>(cur)); break;
         case GN_LAYER_LSTM_UNROLLED: p.reset(new LSTMUnrolled<R>(l.in_size, l.out_size, l.seq_len, l.return_seq != 0)); net.has_lstm = true; break;
+        case GN_LAYER_GRU_UNROLLED: p.reset(new GRUUnrolled<R>(l.in_size, l.out_size, l.seq_len, l.return_seq != 0)); break;
         case GN_LAYER_EMBEDDING: {
           // sequence length = input length of the sample; taken from the next layer that states it
           int T = l.seq_len;

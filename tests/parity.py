@@ -26,6 +26,9 @@ def tensor_slices(layers):
         elif k == D.LSTM_UNROLLED:
             H = l.out_size
             add(f"{i}.lstm.Wx", 4 * H * l.in_size); add(f"{i}.lstm.Wh", 4 * H * H); add(f"{i}.lstm.b", 4 * H)
+        elif k == D.GRU_UNROLLED:
+            H = l.out_size
+            add(f"{i}.gru.Wx", 3 * H * l.in_size); add(f"{i}.gru.Wh", 2 * H * H); add(f"{i}.gru.b", 3 * H)
         elif k == D.EMBEDDING:
             add(f"{i}.emb", l.in_size * l.out_size)
         elif k == D.POSENC:

@@ -51,6 +51,8 @@ CASES = [
     ("mlp_rms", {}, 16, 1), ("mlp_rms", dict(in_size=10, hidden=300, norm=100, classes=3), 5, 1),            # RMSNorm
     ("cnn1d", {}, 12, 1), ("cnn1d", dict(length=17, c0=2, c1=5, c2=3, classes=3, act=D.GELU), 7, 1),           # Conv1D
     ("transformer_small", dict(vocab=7, dim=16, seq_len=24, heads=2, ff_dim=32, n_blocks=1), 3, 1),          # every token id repeats: table rows summed in position order
+    ("gru", {}, 32, 1), ("gru", dict(in_size=5, hidden=24, seq_len=7), 11, 1),                                # GRU with its literal backward pass
+    ("gru", dict(in_size=6, hidden=20, seq_len=5, return_seq=True), 9, 1), ("gru", dict(init="reference"), 32, 1),
     # the reference's own deterministic initialisation (LCG seeded from the layer shapes) instead of uploaded Glorot weights
     ("mlp", dict(init="reference"), 64, 1), ("cnn", dict(init="reference"), 128, 1), ("lstm", dict(init="reference"), 256, 1),
     # The large Transformer at its real width (vocabulary 32000, width 1024, 16 heads of 64, 512 tokens, FFN 4096): the plan,
@@ -114,7 +116,7 @@ def test_three_steps(device, oracle, name, kw, batch):
 def test_predict_matches_forward(device, oracle):
     from goneuron_b200.sequential import Adam, Sequential
     for name, kw, batch in [("mlp", {}, 33), ("cnn", dict(hw=12, c0=2, c1=5, c2=7, classes=3), 6),
-                            ("lstm", dict(in_size=5, hidden=24, seq_len=7), 4),
+                            ("lstm", dict(in_size=5, hidden=24, seq_len=7), 4), ("gru", dict(in_size=5, hidden=24, seq_len=7), 4),
                             ("transformer_small", dict(vocab=300, dim=48, seq_len=20, heads=3, ff_dim=100, n_blocks=1), 5)]:
         layers, loss_kind, params, x, y, lr = configs.make_case(name, batch=batch, **kw)
         ref = oracle.OracleState(layers, loss_kind, params).forward_batch(x, threads=4, precision=64)
@@ -124,6 +126,26 @@ def test_predict_matches_forward(device, oracle):
         assert norm_err(out, ref) <= TOL, name
         assert np.array_equal(model.Predict(x[0]), out[0])
         model.Close()
+
+
+def test_evaluate_matches_the_cpu_path(device, oracle, tmp_path):
+    """Sequential.Evaluate (sequential.go:172-183): mean per-sample loss without a weight update, for both losses; and a
+    checkpoint path without extension round-trips through Save / Load."""
+    from goneuron_b200.sequential import Adam, Sequential
+    for name, kw, batch in [("mlp", {}, 33), ("lstm", dict(in_size=5, hidden=24, seq_len=7), 9)]:
+        layers, loss_kind, params, x, y, lr = configs.make_case(name, batch=batch, **kw)
+        model = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+        model.SetParams(params)
+        out = oracle.OracleState(layers, loss_kind, params).forward_batch(x, threads=2, precision=64)
+        want = float(np.mean([oracle.loss(loss_kind, out[i], y[i]) for i in range(batch)]))
+        got = model.Evaluate(x, y)
+        assert abs(got - want) <= TOL * max(1.0, abs(want)), (name, got, want)
+        assert np.array_equal(model.Params(), params)                 # no update
+        model.Save(tmp_path / f"{name}_ckpt")                          # no extension
+        other = Sequential(layers, device).Compile(Adam(lr), loss_kind)
+        other.Load(tmp_path / f"{name}_ckpt")
+        assert np.array_equal(other.Params(), params)
+        model.Close(); other.Close()
 
 
 def test_fit_short_last_batch(device, oracle):

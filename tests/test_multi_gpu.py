@@ -16,7 +16,8 @@ CASES = [("mlp", {}, 64, 1), ("transformer_small", dict(vocab=512, dim=64, seq_l
          ("cnn", dict(hw=12, c0=2, c1=5, c2=7, classes=3), 10, 1),
          ("lstm", dict(in_size=5, hidden=24, seq_len=7), 12, 1),       # one worker chunk spans both ranks: update factors gathered, scan replicated
          ("lstm", dict(in_size=5, hidden=24, seq_len=7), 12, 4),       # worker chunks inside the ranks' shards
-         ("cnn_bn", dict(hw=10, c0=2, c1=5, classes=3), 8, 1)]         # BatchNorm2D running statistics across ranks
+         ("cnn_bn", dict(hw=10, c0=2, c1=5, classes=3), 8, 1),         # BatchNorm2D running statistics across ranks
+         ("gru", dict(in_size=5, hidden=24, seq_len=7), 10, 1)]
 
 
 def _rank(rank, world, uid, out_dir):
