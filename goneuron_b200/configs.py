@@ -75,9 +75,11 @@ def recurrent_gru(in_size=16, hidden=64, seq_len=24, return_seq=False):
     return [D.SequenceUnrollerGRU(in_size, hidden, seq_len, return_seq), D.Dense(out, 2, D.LINEAR)], D.MSE
 
 
-def transformer(vocab, dim, seq_len, heads, ff_dim, n_blocks):
+def transformer(vocab, dim, seq_len, heads, ff_dim, n_blocks, ff_act=D.RELU, rms_norm=False, rope=False, causal=True):
+    """The benchmark Transformers are causal with CLS pooling of token 0, so only token 0 of a sequence ever receives a
+    gradient; causal=False lets every token contribute (used by the tests of the block variants)."""
     layers = [D.Embedding(vocab, dim, seq_len), D.PositionalEncoding(seq_len, dim)]
-    layers += [D.TransformerBlock(dim, heads, seq_len, ff_dim, True) for _ in range(n_blocks)]
+    layers += [D.TransformerBlock(dim, heads, seq_len, ff_dim, causal, ff_act, rms_norm, rope) for _ in range(n_blocks)]
     layers += [D.CLSPooling(seq_len, dim), D.Dense(dim, vocab, D.LOGSOFTMAX)]
     return layers, D.CROSS_ENTROPY
 
@@ -152,8 +154,14 @@ def init_params(layers, rng):
             d, f = l.dim, l.ff_dim
             for _ in range(4):
                 parts += _dense_params(rng, d, d)
-            parts += [np.ones(d, np.float32), np.zeros(d, np.float32)] * 2
-            parts += _dense_params(rng, d, f)
+            if l.kernel:                                   # RMSNorm: gain only
+                parts += [rng.uniform(0.8, 1.2, size=d).astype(np.float32) for _ in range(2)]
+            else:
+                parts += [np.ones(d, np.float32), np.zeros(d, np.float32)] * 2
+            if l.activation == D.SILU:                     # SwiGLU: gate and up projections, no biases
+                parts += [_glorot(rng, (f, d), d, f).ravel(), _glorot(rng, (f, d), d, f).ravel()]
+            else:
+                parts += _dense_params(rng, d, f)
             parts += _dense_params(rng, f, d)
         elif k == D.LAYERNORM:
             parts += [np.ones(l.dim, np.float32), np.zeros(l.dim, np.float32)]
@@ -241,7 +249,9 @@ def reference_init_params(layers):
             parts.append((ReferenceRNG(l.seq_len + l.dim + 42).rand_float(l.seq_len * l.dim) * f32(2) * scale - scale).astype(f32))
         elif k == D.TRANSFORMER_BLOCK:
             d, f = l.dim, l.ff_dim
-            parts.append(np.zeros(4 * (d * d + d) + 4 * d + (d * f + f) + (f * d + d), f32))
+            n_norm = 2 * d if l.kernel else 4 * d
+            n_ff1 = 2 * d * f if l.activation == D.SILU else d * f + f
+            parts.append(np.zeros(4 * (d * d + d) + n_norm + n_ff1 + (f * d + d), f32))
         elif k == D.LAYERNORM:
             parts += [np.ones(l.dim, f32), np.zeros(l.dim, f32)]
         elif k in (D.RMSNORM,):

@@ -72,6 +72,8 @@ struct LayerRT {
   DevBuf out, z;                       // activation / pre-activation  [cap, out_size]
   DevBuf q, k, v, att, r1, n1, mid, r2, stat;   // TransformerBlock
   DevBuf att_m, att_l, att_d;          // fused attention: per-row softmax maximum, sum, and dO.O  [batch*heads*T]
+  DevBuf gate, up, zlast, rope;        // TransformerBlock variants: SwiGLU projections [tokens, ff]; GELU: last token's pre-activation [batch, ff]; cos | sin table
+  int ff_act = GN_ACT_RELU; bool rms = false, use_rope = false;
   DevBuf pre_i, c_all, h_all, dgate;   // LSTM
   DevBuf idx;                          // int32 payload: MaxPool argmax / embedding token ids
   const float* fin = nullptr;          // input of the last forward call (device pointer, not owned)
@@ -109,7 +111,7 @@ struct gn_model {
 
 namespace gn {
 
-enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_NFF2, S_NFF3, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
 
 static int ensure(gn_model* m, int slot, size_t n, float** out) {
   if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
@@ -181,8 +183,12 @@ static int plan_layers(gn_model* m, const gn_layer_desc* layers, int n) {
         l.in_size = l.out_size = d.seq_len * d.dim; l.p_cnt = (int64_t)d.seq_len * d.dim; break;
       case GN_LAYER_TRANSFORMER_BLOCK:
         if (d.seq_len <= 0 || d.dim <= 0 || d.heads <= 0 || d.ff_dim <= 0 || d.dim % d.heads) return fail(GN_ERR_INVALID_ARG, "layer %d: bad TransformerBlock descriptor (dim must be divisible by heads)", i);
+        if (d.activation != 0 && d.activation != GN_ACT_RELU && d.activation != GN_ACT_GELU && d.activation != GN_ACT_SILU) return fail(GN_ERR_UNSUPPORTED, "layer %d: TransformerBlock feed-forward activation %d", i, d.activation);
+        l.ff_act = d.activation == 0 ? GN_ACT_RELU : d.activation; l.rms = d.kernel != 0; l.use_rope = d.stride != 0;
+        if (l.use_rope && (d.dim / d.heads) % 2) return fail(GN_ERR_INVALID_ARG, "layer %d: rotary embeddings need an even head size", i);
         l.in_size = l.out_size = d.seq_len * d.dim;
-        l.p_cnt = 4 * ((int64_t)d.dim * d.dim + d.dim) + 4 * (int64_t)d.dim + ((int64_t)d.dim * d.ff_dim + d.ff_dim) + ((int64_t)d.ff_dim * d.dim + d.dim); break;
+        l.p_cnt = 4 * ((int64_t)d.dim * d.dim + d.dim) + (l.rms ? 2 : 4) * (int64_t)d.dim
+                + (l.ff_act == GN_ACT_SILU ? 2 * (int64_t)d.dim * d.ff_dim : (int64_t)d.dim * d.ff_dim + d.ff_dim) + ((int64_t)d.ff_dim * d.dim + d.dim); break;
       case GN_LAYER_CLS_POOLING:
         if (d.seq_len <= 0 || d.dim <= 0) return fail(GN_ERR_INVALID_ARG, "layer %d: bad CLSPooling descriptor", i);
         l.in_size = d.seq_len * d.dim; l.out_size = d.dim; break;
@@ -243,7 +249,10 @@ static int alloc_activations(gn_model* m, int cap) {
         size_t nd = c * d.seq_len * d.dim, nf = c * d.seq_len * d.ff_dim, nt = c * d.seq_len;
         GN_TRY(l.q.alloc(nd)); GN_TRY(l.k.alloc(nd)); GN_TRY(l.v.alloc(nd)); GN_TRY(l.att.alloc(nd)); GN_TRY(l.r1.alloc(nd)); GN_TRY(l.n1.alloc(nd));
         GN_TRY(l.mid.alloc(nf)); GN_TRY(l.r2.alloc(nd)); GN_TRY(l.out.alloc(nd)); GN_TRY(l.stat.alloc(4 * nt));
-        GN_TRY(l.att_m.alloc(nt * d.heads)); GN_TRY(l.att_l.alloc(nt * d.heads)); GN_TRY(l.att_d.alloc(nt * d.heads)); break; }
+        GN_TRY(l.att_m.alloc(nt * d.heads)); GN_TRY(l.att_l.alloc(nt * d.heads)); GN_TRY(l.att_d.alloc(nt * d.heads));
+        if (l.ff_act == GN_ACT_SILU) { GN_TRY(l.gate.alloc(nf)); GN_TRY(l.up.alloc(nf)); }
+        if (l.ff_act == GN_ACT_GELU) GN_TRY(l.zlast.alloc(c * d.ff_dim));
+        break; }
       case GN_LAYER_CLS_POOLING: GN_TRY(l.out.alloc(c * l.out_size)); break;
       case GN_LAYER_LAYERNORM: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.stat.alloc(2 * c * (l.in_size / d.dim))); break;
       case GN_LAYER_RMSNORM: GN_TRY(l.out.alloc(c * l.out_size)); GN_TRY(l.stat.alloc(c * (l.in_size / d.dim))); break;
@@ -276,6 +285,41 @@ static int layernorm_forward(Ctx* ctx, const float* x, const float* gamma, const
     default: GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, n, 1e-5f);
   }
   return check_launch("layernorm_forward");
+}
+
+
+// The two norms of a TransformerBlock: LayerNorm (row mean and deviation in stat[0:rows], stat[rows:2 rows]) or RMSNorm
+// (row RMS in stat[0:rows]); rmsnorm.go:157-240, :246-336.
+static int block_norm_forward(Ctx* ctx, bool rms, const float* x, const float* gamma, const float* beta, float* y, float* stat, long rows, int n) {
+  if (!rms) return layernorm_forward(ctx, x, gamma, beta, y, stat, stat + rows, rows, n);
+  GN_LAUNCH(ctx, rmsnorm_fwd_kernel, cdiv(rows, 8), 256, 0, x, gamma, y, stat, rows, n, 1e-5f);
+  return check_launch("rmsnorm_forward");
+}
+static int layernorm_backward(gn_model* m, const float* g, const float* x, const float* gamma, const float* mean, const float* sd, float* dx,
+                              float* gGamma, float* gBeta, long rows, int n);
+static int block_norm_backward(gn_model* m, bool rms, const float* g, const float* x, const float* gamma, const float* stat, float* dx, float* gGamma, float* gBeta, long rows, int n) {
+  if (!rms) return layernorm_backward(m, g, x, gamma, stat, stat + rows, dx, gGamma, gBeta, rows, n);
+  Ctx* ctx = &m->ctx->c;
+  const int chunks = (int)std::max<long>(1, std::min<long>(rows / 64, 128));
+  float* part; GN_TRY(ensure(m, S_PART2, (size_t)chunks * n, &part));
+  GN_LAUNCH(ctx, rmsnorm_pgrad_partial_kernel, dim3(cdiv(n, 128), chunks), 128, 0, g, x, stat, rows, n, part);
+  GN_LAUNCH(ctx, rmsnorm_pgrad_final_kernel, cdiv(n, 128), 128, 0, part, chunks, n, gGamma);
+  GN_LAUNCH(ctx, rmsnorm_bwd_kernel, cdiv(rows, 8), 256, 0, g, x, gamma, stat, dx, rows, n);
+  return check_launch("rmsnorm_backward");
+}
+// cos | sin of the rotary embedding per (position, pair index), with the reference's conversions (transformer.go:217-221):
+// theta and position * theta are rounded to float32, cos and sin taken in float64 and rounded to float32.
+static int rope_table(Ctx* ctx, LayerRT& l) {
+  const int T = l.d.seq_len, hd = l.d.dim / l.d.heads, half = hd / 2;
+  if (l.rope.n >= (size_t)T * half * 2) return GN_OK;
+  std::vector<float> tab((size_t)T * half * 2);
+  for (int t = 0; t < T; t++) for (int i = 0; i < half; i++) {
+    const float theta = (float)std::pow(10000.0, -(double)(2 * i) / (double)hd);
+    const float mt = (float)t * theta;
+    tab[((size_t)t * half + i) * 2] = (float)std::cos((double)mt); tab[((size_t)t * half + i) * 2 + 1] = (float)std::sin((double)mt);
+  }
+  GN_TRY(l.rope.alloc(tab.size()));
+  GN_CUDA(copy_h2d(ctx, l.rope.p, tab.data(), tab.size() * 4)); return GN_OK;
 }
 
 // The fused kernels (attention.cuh) are the default; GONEURON_CUDA_ATTENTION=unfused selects the path that
@@ -345,12 +389,18 @@ static int attention_forward(gn_model* m, LayerRT& l, int B, float* P) {
   return gemm(ctx, o);
 }
 
-struct BlockParams { const float *wq, *bq, *wk, *bk, *wv, *bv, *wo, *bo, *g1, *be1, *g2, *be2, *w1, *b1, *w2, *b2; };
-static BlockParams block_params(const float* p, int D, int F) {
+// Views into a TransformerBlock's slice of a flat buffer: MHA (wQ, wK, wV, wOut, each W | b) | norm1 | norm2 | ff1 | ff2
+// (transformer.go:1038-1056).  RMSNorm has a gain only (be1 = be2 = null); a SwiGLU first layer is W (gate) | V (up) without
+// biases (w1 = W, v1 = V, b1 = null).
+struct BlockParams { const float *wq, *bq, *wk, *bk, *wv, *bv, *wo, *bo, *g1, *be1, *g2, *be2, *w1, *b1, *v1, *w2, *b2; };
+static BlockParams block_params(const float* p, int D, int F, bool rms = false, int ff_act = GN_ACT_RELU) {
   BlockParams b; long dd = (long)D * D;
   b.wq = p; b.bq = p + dd; p += dd + D; b.wk = p; b.bk = p + dd; p += dd + D; b.wv = p; b.bv = p + dd; p += dd + D; b.wo = p; b.bo = p + dd; p += dd + D;
-  b.g1 = p; b.be1 = p + D; p += 2 * D; b.g2 = p; b.be2 = p + D; p += 2 * D;
-  b.w1 = p; b.b1 = p + (long)D * F; p += (long)D * F + F; b.w2 = p; b.b2 = p + (long)F * D; return b;
+  if (rms) { b.g1 = p; b.be1 = nullptr; p += D; b.g2 = p; b.be2 = nullptr; p += D; }
+  else { b.g1 = p; b.be1 = p + D; p += 2 * D; b.g2 = p; b.be2 = p + D; p += 2 * D; }
+  if (ff_act == GN_ACT_SILU) { b.w1 = p; b.v1 = p + (long)D * F; b.b1 = nullptr; p += 2 * (long)D * F; }
+  else { b.w1 = p; b.b1 = p + (long)D * F; b.v1 = nullptr; p += (long)D * F + F; }
+  b.w2 = p; b.b2 = p + (long)F * D; return b;
 }
 
 static int forward(gn_model* m, const float* x, int B, const float** y_out, bool training) {
@@ -442,12 +492,18 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         GN_LAUNCH(ctx, posenc_fwd_kernel, ew_grid(ctx, n), 256, 0, cur, p, l.out.p, n, (long)l.out_size);
         cur = l.out.p; break; }
       case GN_LAYER_TRANSFORMER_BLOCK: {
-        const int T = d.seq_len, D = d.dim, F = d.ff_dim; const int N = B * T; BlockParams bp = block_params(p, D, F);
+        const int T = d.seq_len, D = d.dim, F = d.ff_dim; const int N = B * T; BlockParams bp = block_params(p, D, F, l.rms, l.ff_act);
         GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wq, bp.bq, l.q.p, D));
         {   // the K and V projections read the same input: its operand planes are still in the engine's scratch
           GemmDesc g; g.M = N; g.N = D; g.K = D; g.A = cur; g.sa_m = D; g.sa_k = 1; g.sb_k = 1; g.sb_n = D; g.ldc = D; g.reuse_a_planes = true;
           g.B = bp.wk; g.bias = bp.bk; g.C = l.k.p; GN_TRY(gemm(ctx, g));
           g.B = bp.wv; g.bias = bp.bv; g.C = l.v.p; GN_TRY(gemm(ctx, g));
+        }
+        if (l.use_rope) {   // rotary embeddings on q and k, in place: attention and its backward pass see the rotated tensors (transformer.go:457-461)
+          GN_TRY(rope_table(ctx, l));
+          const long tot = (long)N * (D / 2);
+          GN_LAUNCH(ctx, rope_kernel, ew_grid(ctx, tot), 256, 0, l.q.p, (const float*)l.rope.p, (long)N, T, D, D / d.heads, 1.f);
+          GN_LAUNCH(ctx, rope_kernel, ew_grid(ctx, tot), 256, 0, l.k.p, (const float*)l.rope.p, (long)N, T, D, D / d.heads, 1.f);
         }
         if (use_fused_attention(d)) {
           if (attn_tc_supported(ctx, D / d.heads, T, B, d.heads, D)) GN_TRY(attn_tc_fwd(ctx, l.q.p, l.k.p, l.v.p, l.att.p, l.att_m.p, l.att_l.p, B, T, D, d.heads, d.causal));
@@ -458,13 +514,25 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         }
         GN_TRY(gemm_nt(ctx, N, D, D, l.att.p, D, bp.wo, bp.bo, l.r1.p, D, GN_ACT_LINEAR, cur, D));          // res1 = x + att
         float* st = l.stat.p;
-        GN_TRY(layernorm_forward(ctx, l.r1.p, bp.g1, bp.be1, l.n1.p, st, st + N, (long)N, D));
-        {   // ff1 (ReLU) -> ff2
-          GemmDesc g1; g1.M = N; g1.N = F; g1.K = D; g1.A = l.n1.p; g1.sa_m = D; g1.sa_k = 1; g1.B = bp.w1; g1.sb_k = 1; g1.sb_n = D; g1.C = l.mid.p; g1.ldc = F; g1.bias = bp.b1; g1.act = GN_ACT_RELU;
-          GemmDesc g2; g2.M = N; g2.N = D; g2.K = F; g2.A = l.mid.p; g2.sa_m = F; g2.sa_k = 1; g2.B = bp.w2; g2.sb_k = 1; g2.sb_n = F; g2.C = l.r2.p; g2.ldc = D; g2.bias = bp.b2; g2.R = l.n1.p; g2.ldr = D;   // res2 = norm1 + ff
-          GN_TRY(gemm(ctx, g1)); GN_TRY(gemm(ctx, g2));
+        GN_TRY(block_norm_forward(ctx, l.rms, l.r1.p, bp.g1, bp.be1, l.n1.p, st, (long)N, D));
+        {   // feed-forward: ff1 -> ff2, res2 = norm1 + ff
+          GemmDesc g1; g1.M = N; g1.N = F; g1.K = D; g1.A = l.n1.p; g1.sa_m = D; g1.sa_k = 1; g1.B = bp.w1; g1.sb_k = 1; g1.sb_n = D; g1.C = l.mid.p; g1.ldc = F; g1.bias = bp.b1;
+          const long nf = (long)N * F;
+          if (l.ff_act == GN_ACT_RELU) { g1.act = GN_ACT_RELU; GN_TRY(gemm(ctx, g1)); }
+          else if (l.ff_act == GN_ACT_GELU) {
+            // the pre-activation of every sequence's last token is what the backward pass differentiates at (layer.go:563-567)
+            GN_TRY(gemm(ctx, g1));
+            GN_LAUNCH(ctx, last_token_rows_kernel, ew_grid(ctx, (long)B * F), 256, 0, (const float*)l.mid.p, l.zlast.p, T, F, (long)B * F);
+            GN_LAUNCH(ctx, act_forward_kernel, ew_grid(ctx, nf), 256, 0, (const float*)l.mid.p, l.mid.p, nf, (int)GN_ACT_GELU, 0.f);
+          } else {              // SwiGLU: gate and up projections (no biases) share the input's operand planes
+            g1.C = l.gate.p; g1.bias = nullptr; GN_TRY(gemm(ctx, g1));
+            g1.B = bp.v1; g1.C = l.up.p; g1.reuse_a_planes = true; GN_TRY(gemm(ctx, g1));
+            GN_LAUNCH(ctx, swiglu_fwd_kernel, ew_grid(ctx, nf), 256, 0, (const float*)l.gate.p, (const float*)l.up.p, l.mid.p, nf);
+          }
+          GemmDesc g2; g2.M = N; g2.N = D; g2.K = F; g2.A = l.mid.p; g2.sa_m = F; g2.sa_k = 1; g2.B = bp.w2; g2.sb_k = 1; g2.sb_n = F; g2.C = l.r2.p; g2.ldc = D; g2.bias = bp.b2; g2.R = l.n1.p; g2.ldr = D;
+          GN_TRY(gemm(ctx, g2));
         }
-        GN_TRY(layernorm_forward(ctx, l.r2.p, bp.g2, bp.be2, l.out.p, st + 2 * N, st + 3 * N, (long)N, D));
+        GN_TRY(block_norm_forward(ctx, l.rms, l.r2.p, bp.g2, bp.be2, l.out.p, st + 2 * N, (long)N, D));
         cur = l.out.p; break; }
       case GN_LAYER_CLS_POOLING:
         GN_LAUNCH(ctx, cls_fwd_kernel, B, 128, 0, cur, l.out.p, d.seq_len, d.dim); cur = l.out.p; break;
@@ -541,27 +609,44 @@ static int inner_dense_param_grads(gn_model* m, const float* dz, int B, int T, i
 static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, const float* gout, float* dx) {
   Ctx* ctx = &m->ctx->c; const gn_layer_desc& d = l.d;
   const int T = d.seq_len, D = d.dim, F = d.ff_dim, Hh = d.heads, hd = D / Hh; const int N = B * T; const long ND = (long)N * D;
-  BlockParams bp = block_params(m->params.p + l.p_off, D, F); BlockParams gp = block_params(m->grads.p + l.p_off, D, F);
+  BlockParams bp = block_params(m->params.p + l.p_off, D, F, l.rms, l.ff_act); BlockParams gp = block_params(m->grads.p + l.p_off, D, F, l.rms, l.ff_act);
   float *dR2, *dM, *comb, *dR1, *dA, *P = nullptr, *dP = nullptr; float* st = l.stat.p;
   const bool fused = use_fused_attention(d);
   GN_TRY(ensure(m, S_ND0, ND, &dR2)); GN_TRY(ensure(m, S_NFF, (size_t)N * F, &dM)); GN_TRY(ensure(m, S_ND1, ND, &comb));
   GN_TRY(ensure(m, S_ND2, ND, &dR1)); GN_TRY(ensure(m, S_ND3, ND, &dA));
   if (!fused) { GN_TRY(ensure(m, S_ATT0, (size_t)B * Hh * T * T, &P)); GN_TRY(ensure(m, S_ATT1, (size_t)B * Hh * T * T, &dP)); }
-  // LayerNorm 2
-  GN_TRY(layernorm_backward(m, gout, l.r2.p, bp.g2, st + 2 * N, st + 3 * N, dR2, (float*)gp.g2, (float*)gp.be2, (long)N, D));
+  // norm 2
+  GN_TRY(block_norm_backward(m, l.rms, gout, l.r2.p, bp.g2, st + 2 * N, dR2, (float*)gp.g2, (float*)gp.be2, (long)N, D));
   // ff2 then ff1, token by token in the reference (transformer.go:1238-1250)
   GN_TRY(inner_dense_param_grads(m, dR2, B, T, D, l.mid.p, F, (float*)gp.w2, (float*)gp.b2));
   {
-    // dz1[s,t,:] = (W2^T dR2[s,t,:]) gated by the ReLU pattern of the LAST token of sequence s (fused into the epilogue)
+    // dM[s,t,:] = W2^T dR2[s,t,:]; with a ReLU first layer gated by the ReLU pattern of the LAST token of sequence s (fused into the epilogue)
     GemmDesc g; g.M = N; g.N = F; g.K = D; g.A = dR2; g.sa_m = D; g.sa_k = 1; g.B = bp.w2; g.sb_k = F; g.sb_n = 1; g.C = dM; g.ldc = F;
-    g.mask = l.mid.p + (long)(T - 1) * F; g.mask_ld = (long)T * F; g.mask_group = T;
-    GemmDesc h; h.M = N; h.N = D; h.K = F; h.A = dM; h.sa_m = F; h.sa_k = 1; h.B = bp.w1; h.sb_k = D; h.sb_n = 1; h.C = comb; h.ldc = D; h.R = dR2; h.ldr = D;   // combined = gradRes2 + W1^T dz1
+    if (l.ff_act == GN_ACT_RELU) { g.mask = l.mid.p + (long)(T - 1) * F; g.mask_ld = (long)T * F; g.mask_group = T; }
     GN_TRY(gemm(ctx, g));
-    GN_TRY(inner_dense_param_grads(m, dM, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1));
-    GN_TRY(gemm(ctx, h));
+    const long nf = (long)N * F;
+    if (l.ff_act != GN_ACT_SILU) {
+      if (l.ff_act == GN_ACT_GELU) GN_LAUNCH(ctx, scale_by_last_deriv_kernel, ew_grid(ctx, nf), 256, 0, dM, (const float*)l.zlast.p, T, F, nf, (int)GN_ACT_GELU);
+      GemmDesc h; h.M = N; h.N = D; h.K = F; h.A = dM; h.sa_m = F; h.sa_k = 1; h.B = bp.w1; h.sb_k = D; h.sb_n = 1; h.C = comb; h.ldc = D; h.R = dR2; h.ldr = D;   // combined = gradRes2 + W1^T dz1
+      GN_TRY(inner_dense_param_grads(m, dM, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1));
+      GN_TRY(gemm(ctx, h));
+    } else {
+      // SwiGLU keeps every call's state and pops it in reverse (swiglu.go:186-201): token t's gradient meets token T-1-t's
+      // input and projections.  The deltas are written at the partner's row, so the weight gradients are plain contractions
+      // over all tokens with the layer's inputs; the input gradient comes out in partner order and is reversed when it is
+      // added to the residual path.
+      float *dGP, *dUP, *Y;
+      GN_TRY(ensure(m, S_NFF2, (size_t)nf, &dGP)); GN_TRY(ensure(m, S_NFF3, (size_t)nf, &dUP)); GN_TRY(ensure(m, S_ND3, ND, &Y));
+      GN_LAUNCH(ctx, swiglu_bwd_paired_kernel, ew_grid(ctx, nf), 256, 0, (const float*)dM, (const float*)l.gate.p, (const float*)l.up.p, dGP, dUP, T, F, nf);
+      GN_TRY(gemm_tn(ctx, N, F, D, dGP, F, l.n1.p, D, (float*)gp.w1));
+      GN_TRY(gemm_tn(ctx, N, F, D, dUP, F, l.n1.p, D, (float*)gp.v1));
+      GN_TRY(gemm_nn(ctx, N, F, D, dGP, F, bp.w1, Y, D));
+      GN_TRY(gemm_nn(ctx, N, F, D, dUP, F, bp.v1, Y, D, Y, D));
+      GN_LAUNCH(ctx, add_token_reversed_kernel, ew_grid(ctx, ND), 256, 0, (const float*)dR2, (const float*)Y, comb, T, D, ND);
+    }
   }
-  // LayerNorm 1
-  GN_TRY(layernorm_backward(m, comb, l.r1.p, bp.g1, st, st + N, dR1, (float*)gp.g1, (float*)gp.be1, (long)N, D));
+  // norm 1
+  GN_TRY(block_norm_backward(m, l.rms, comb, l.r1.p, bp.g1, st, dR1, (float*)gp.g1, (float*)gp.be1, (long)N, D));
   // output projection
   GN_TRY(inner_dense_param_grads(m, dR1, B, T, D, l.att.p, D, (float*)gp.wo, (float*)gp.bo));
   GN_TRY(gemm_nn(ctx, N, D, D, dR1, D, bp.wo, dA, D));
@@ -585,6 +670,11 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
     q.A = dP; q.sa_m = T; q.sa_k = 1; q.B = l.k.p; q.C = dQ; q.flags = d.causal ? GEMM_KEND_AT_M0 : 0; GN_TRY(gemm(ctx, q));     // dQ = dS K
     q.A = dP; q.sa_m = 1; q.sa_k = T; q.B = l.q.p; q.C = dK; q.flags = d.causal ? GEMM_KBEG_AT_M0 : 0; GN_TRY(gemm(ctx, q));     // dK = dS^T Q
     q.A = P; q.B = dA; q.C = dV; GN_TRY(gemm(ctx, q));                                                                          // dV = P^T dA
+  }
+  if (l.use_rope) {   // the conjugate rotation on the gradients of q and k (transformer.go:659-663)
+    const long tot = (long)N * (D / 2);
+    GN_LAUNCH(ctx, rope_kernel, ew_grid(ctx, tot), 256, 0, dQ, (const float*)l.rope.p, (long)N, T, D, hd, -1.f);
+    GN_LAUNCH(ctx, rope_kernel, ew_grid(ctx, tot), 256, 0, dK, (const float*)l.rope.p, (long)N, T, D, hd, -1.f);
   }
   // q, k, v projections; gradIn = dq + dk + dv, block input gradient = gradRes1 + gradIn
   GN_TRY(inner_dense_param_grads(m, dQ, B, T, D, xin, D, (float*)gp.wq, (float*)gp.bq));
@@ -1053,8 +1143,9 @@ int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int 
       else if (d.kind == GN_LAYER_TRANSFORMER_BLOCK) {
         const int64_t dd = (int64_t)d.dim * d.dim + d.dim; int64_t o = l.p_off;
         for (int k = 0; k < 4; k++) { add(o, d.dim, d.dim); o += dd; }
-        o += 4 * (int64_t)d.dim;
-        add(o, d.ff_dim, d.dim); o += (int64_t)d.dim * d.ff_dim + d.ff_dim;
+        o += (l.rms ? 2 : 4) * (int64_t)d.dim;
+        if (l.ff_act == GN_ACT_SILU) { add(o, d.ff_dim, d.dim); add(o + (int64_t)d.dim * d.ff_dim, d.ff_dim, d.dim); o += 2 * (int64_t)d.dim * d.ff_dim; }
+        else { add(o, d.ff_dim, d.dim); o += (int64_t)d.dim * d.ff_dim + d.ff_dim; }
         add(o, d.dim, d.ff_dim);
       }
     }

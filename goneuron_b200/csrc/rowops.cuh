@@ -484,6 +484,52 @@ __global__ void relu_mask_last_token_kernel(float* __restrict__ dM, const float*
 }
 
 // ---------------------------------------------------------------- misc elementwise
+// ---------------------------------------------------------------- TransformerBlock variants
+// Rotary embeddings on a [tokens, D] tensor in place (transformer.go:212-236): within every head, element i of the first
+// half and element i + hd/2 are rotated by the angle of (position, i); `tab` holds cos | sin per (position, i), computed on
+// the host with the reference's float32 / float64 conversions.  sign = -1 applies the conjugate (backward pass).
+__global__ void rope_kernel(float* __restrict__ x, const float* __restrict__ tab, long tokens, int T, int D, int hd, float sign) {
+  const int half = hd >> 1; const long per = (long)(D >> 1), total = tokens * per;
+  for (long e = blockIdx.x * (long)blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
+    const long tok = e / per; const int r = (int)(e - tok * per), h = r / half, i = r - h * half, t = (int)(tok % T);
+    const float c = tab[((long)t * half + i) * 2], s = sign * tab[((long)t * half + i) * 2 + 1];
+    float* p = x + tok * D + (long)h * hd + i;
+    const float v1 = p[0], v2 = p[half];
+    p[0] = v1 * c - v2 * s; p[half] = v1 * s + v2 * c;
+  }
+}
+// rows [B, C] <- the last token's row of every sequence of in [B, T, C]
+__global__ void last_token_rows_kernel(const float* __restrict__ in, float* __restrict__ out, int T, int C, long total) {
+  for (long e = blockIdx.x * (long)blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) { const long s = e / C; out[e] = in[(s * T + (T - 1)) * C + (e - s * C)]; }
+}
+// dz[s,t,:] *= act'(z_last[s,:]): a Dense layer called token by token differentiates at its LAST call's pre-activation (layer.go:563-567)
+__global__ void scale_by_last_deriv_kernel(float* __restrict__ dz, const float* __restrict__ z_last, int T, int C, long total, int act) {
+  for (long e = blockIdx.x * (long)blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) { const long row = e / C; dz[e] *= act_der(act, z_last[(row / T) * C + (e - row * C)]); }
+}
+// SwiGLU (swiglu.go:163-170): out = swish(gate) * up
+__global__ void swiglu_fwd_kernel(const float* __restrict__ gate, const float* __restrict__ up, float* __restrict__ out, long n) {
+  for (long e = blockIdx.x * (long)blockDim.x + threadIdx.x; e < n; e += (long)gridDim.x * blockDim.x) { const float g = gate[e]; out[e] = (g * act_fwd(GN_ACT_SIGMOID, g)) * up[e]; }
+}
+// SwiGLU backward inside a TransformerBlock (swiglu.go:203-216 with the pairing of transformer.go:1238-1250): the gradient of
+// token t meets the saved state of token T-1-t.  Results are written at the PARTNER's row, where the weight-gradient
+// contraction with the layer's inputs needs them.
+__global__ void swiglu_bwd_paired_kernel(const float* __restrict__ dOut, const float* __restrict__ gate, const float* __restrict__ up,
+                                         float* __restrict__ dGateP, float* __restrict__ dUpP, int T, int C, long total) {
+  for (long e = blockIdx.x * (long)blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
+    const long row = e / C; const int c = (int)(e - row * C); const long s = row / T; const int t = (int)(row - s * T);
+    const long pe = (s * T + (T - 1 - t)) * C + c;            // partner element
+    const float g = gate[pe], u = up[pe], sig = act_fwd(GN_ACT_SIGMOID, g), sw = g * sig, go = dOut[e];
+    dUpP[pe] = go * sw; dGateP[pe] = go * (sw + sig * (1.f - sw)) * u;
+  }
+}
+// out[s,t,:] = a[s,t,:] + b[s,T-1-t,:]
+__global__ void add_token_reversed_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out, int T, int C, long total) {
+  for (long e = blockIdx.x * (long)blockDim.x + threadIdx.x; e < total; e += (long)gridDim.x * blockDim.x) {
+    const long row = e / C; const int c = (int)(e - row * C); const long s = row / T; const int t = (int)(row - s * T);
+    out[e] = a[e] + b[(s * T + (T - 1 - t)) * C + c];
+  }
+}
+
 __global__ void add3_kernel(const float* __restrict__ a, const float* __restrict__ b, const float* __restrict__ c, float* __restrict__ out, long n) {
   for (long i = blockIdx.x * (long)blockDim.x + threadIdx.x; i < n; i += (long)gridDim.x * blockDim.x) out[i] = a[i] + b[i] + (c ? c[i] : 0.f);
 }

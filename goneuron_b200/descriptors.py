@@ -89,9 +89,13 @@ def PositionalEncoding(seq_len, dim):
     return LayerDesc(kind=POSENC, seq_len=seq_len, dim=dim)
 
 
-def TransformerBlock(dim, heads, seq_len, ff_dim, causal=True):
-    """layer.NewTransformerBlock(dim, heads, T, ffDim, causal) -- transformer.go:859-1279."""
-    return LayerDesc(kind=TRANSFORMER_BLOCK, dim=dim, heads=heads, seq_len=seq_len, ff_dim=ff_dim, causal=int(causal))
+def TransformerBlock(dim, heads, seq_len, ff_dim, causal=True, ff_act=RELU, rms_norm=False, rope=False):
+    """layer.NewTransformerBlock(dim, heads, T, ffDim, causal) -- transformer.go:859-1279; with the keyword arguments
+    layer.NewTransformerBlockExt(..., actType, normType, useRoPE) -- transformer.go:899-957: ff_act RELU (ActReLU), GELU
+    (ActGELU) or SILU (ActSwiGLU: the first feed-forward layer is a SwiGLU, swiglu.go); rms_norm selects RMSNorm (NormRMS);
+    rope applies rotary embeddings to q and k (transformer.go:212-236).  Descriptor fields: activation, kernel, stride."""
+    return LayerDesc(kind=TRANSFORMER_BLOCK, dim=dim, heads=heads, seq_len=seq_len, ff_dim=ff_dim, causal=int(causal),
+                     activation=0 if ff_act == RELU else ff_act, kernel=int(bool(rms_norm)), stride=int(bool(rope)))
 
 
 def CLSPooling(seq_len, dim):

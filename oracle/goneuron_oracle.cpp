@@ -790,8 +790,75 @@ template <class R> struct BatchNorm2D : Layer<R> {
 };
 
 // reference: internal/layer/transformer.go:405-527 (forward), :557-690 (backward)
+// reference: internal/layer/swiglu.go:101-174 (forward), :180-241 (backward).  Two projections without biases, W (gate) and
+// V (up): out = swish(W x) * (V x).  Every forward call pushes its input and both projections on a stack (the arena
+// path, swiglu.go:108-121, :144-161) and every backward call pops the most recent entry (:186-201): a caller that runs
+// T forward calls and then T backward calls in the same order -- as TransformerBlock does, transformer.go:1126-1160,
+// :1238-1250 -- pairs the gradient of token s with the saved state of token T-1-s.
+template <class R> struct SwiGLU : Layer<R> {
+  int in, out; const R *W = nullptr, *V = nullptr; R *gW = nullptr, *gV = nullptr;
+  std::vector<std::vector<R>> sx, sg, su; std::vector<R> outBuf, gradIn;
+  SwiGLU(int in_, int out_) : in(in_), out(out_), outBuf(out_), gradIn(in_) {}
+  int64_t n_params() const override { return (int64_t)2 * in * out; }
+  void bind(const R* p, R* g) override { W = p; V = p + (int64_t)in * out; gW = g; gV = g ? g + (int64_t)in * out : nullptr; }
+  int in_size() const override { return in; } int out_size() const override { return out; }
+  void reset() override { sx.clear(); sg.clear(); su.clear(); }
+  const R* forward(const R* x) override {
+    std::vector<R> gate(out), up(out);
+    for (int o = 0; o < out; o++) {
+      R sw = 0, sv = 0;
+      for (int i = 0; i < in; i++) { sw += W[(int64_t)o * in + i] * x[i]; sv += V[(int64_t)o * in + i] * x[i]; }
+      gate[o] = sw; up[o] = sv;
+    }
+    for (int i = 0; i < out; i++) { const R g = gate[i]; const R sig = R(1) / (R(1) + r_exp<R>(-g)); outBuf[i] = (g * sig) * up[i]; }
+    sx.emplace_back(x, x + in); sg.push_back(std::move(gate)); su.push_back(std::move(up));
+    return outBuf.data();
+  }
+  const R* backward(R* grad) override {
+    if (sx.empty()) return nullptr;
+    const std::vector<R>& x = sx.back(); const std::vector<R>& gate = sg.back(); const std::vector<R>& up = su.back();
+    std::vector<R> dGate(out), dUp(out);
+    for (int i = 0; i < out; i++) {
+      const R g = gate[i], u = up[i]; const R sig = R(1) / (R(1) + r_exp<R>(-g)); const R swish = g * sig;
+      dUp[i] = grad[i] * swish;
+      const R dSwish = swish + sig * (R(1) - swish);
+      dGate[i] = grad[i] * dSwish * u;
+    }
+    std::fill(gradIn.begin(), gradIn.end(), R(0));
+    for (int o = 0; o < out; o++) {
+      const R dg = dGate[o], du = dUp[o];
+      for (int i = 0; i < in; i++) {
+        if (gW) { gW[(int64_t)o * in + i] += dg * x[i]; gV[(int64_t)o * in + i] += du * x[i]; }
+        gradIn[i] += dg * W[(int64_t)o * in + i] + du * V[(int64_t)o * in + i];
+      }
+    }
+    sx.pop_back(); sg.pop_back(); su.pop_back();
+    return gradIn.data();
+  }
+};
+
+// reference: internal/layer/transformer.go:212-236.  theta and the angle are rounded to float32 before cos / sin are
+// taken in double and rounded again; the double instantiation keeps everything in double.
+template <class R> void apply_rope(R* x, int T, int heads, int hd, bool conjugate) {
+  for (int t = 0; t < T; t++) for (int h = 0; h < heads; h++) for (int i = 0; i < hd / 2; i++) {
+    R c, s;
+    if (sizeof(R) == sizeof(float)) {
+      const float theta = (float)std::pow(10000.0, -(double)(2 * i) / (double)hd);
+      const float mt = (float)t * theta;
+      c = (R)(float)std::cos((double)mt); s = (R)(float)std::sin((double)mt);
+    } else {
+      const double theta = std::pow(10000.0, -(double)(2 * i) / (double)hd);
+      c = (R)std::cos((double)t * theta); s = (R)std::sin((double)t * theta);
+    }
+    if (conjugate) s = -s;
+    const size_t i1 = (size_t)t * heads * hd + (size_t)h * hd + i, i2 = i1 + hd / 2;
+    const R v1 = x[i1], v2 = x[i2];
+    x[i1] = v1 * c - v2 * s; x[i2] = v1 * s + v2 * c;
+  }
+}
+
 template <class R> struct MHA : Layer<R> {
-  int d, heads, hd, T; bool causal;
+  int d, heads, hd, T; bool causal; bool rope = false;
   Dense<R> wQ, wK, wV, wO;
   std::vector<R> q, k, v, fin, out, gFin, gQ, gK, gV, gIn, scores;
   MHA(int d_, int heads_, int T_, bool causal_) : d(d_), heads(heads_), hd(d_ / heads_), T(T_), causal(causal_),
@@ -811,6 +878,7 @@ template <class R> struct MHA : Layer<R> {
       a = wK.forward(xt); std::copy(a, a + d, k.begin() + (size_t)t * d);
       a = wV.forward(xt); std::copy(a, a + d, v.begin() + (size_t)t * d);
     }
+    if (rope) { apply_rope<R>(q.data(), T, heads, hd, false); apply_rope<R>(k.data(), T, heads, hd, false); }      // transformer.go:457-461
     R scale = r_sqrt<R>((R)hd);
     for (int h = 0; h < heads; h++) {
       for (int i = 0; i < T; i++) for (int j = 0; j < T; j++) {
@@ -867,6 +935,7 @@ template <class R> struct MHA : Layer<R> {
       }
       for (int j = 0; j < T; j++) { R sc = row[j]; for (int e = 0; e < hd; e++) gV[(size_t)j * d + h * hd + e] += sc * gFin[(size_t)i * d + h * hd + e]; }
     }
+    if (rope) { apply_rope<R>(gQ.data(), T, heads, hd, true); apply_rope<R>(gK.data(), T, heads, hd, true); }       // transformer.go:659-663
     for (int t = 0; t < T; t++) {
       const R* dq = wQ.backward(gQ.data() + (size_t)t * d);
       const R* dk = wK.backward(gK.data() + (size_t)t * d);
@@ -879,43 +948,52 @@ template <class R> struct MHA : Layer<R> {
 
 // reference: internal/layer/transformer.go:1081-1191 (forward), :1220-1279 (backward);
 // parameter order MHA | norm1 | norm2 | ff1 | ff2 (:1038-1056)
+// Variants (NewTransformerBlockExt, transformer.go:903-957): the feed-forward's first layer is Dense+ReLU, Dense+GELU or
+// SwiGLU; the two norms are LayerNorm or RMSNorm; rotary embeddings on q and k.
 template <class R> struct Block : Layer<R> {
   int d, T, ff;
-  MHA<R> mha; LayerNorm<R> n1, n2; Dense<R> ff1, ff2;
+  MHA<R> mha; std::unique_ptr<Layer<R>> n1, n2, ff1; Dense<R> ff2;
   std::vector<R> res1, n1out, ffout, res2, out, gRes2, gN1ff, comb, gRes1, gIn;
-  Block(int d_, int heads, int T_, int ff_, bool causal) : d(d_), T(T_), ff(ff_), mha(d_, heads, T_, causal), n1(T_, d_), n2(T_, d_),
-      ff1(d_, ff_, GN_ACT_RELU), ff2(ff_, d_, GN_ACT_LINEAR), res1((size_t)T_ * d_), n1out(res1.size()), ffout(res1.size()), res2(res1.size()), out(res1.size()),
-      gRes2(res1.size()), gN1ff(res1.size()), comb(res1.size()), gRes1(res1.size()), gIn(res1.size()) {}
-  int64_t n_params() const override { return mha.n_params() + n1.n_params() + n2.n_params() + ff1.n_params() + ff2.n_params(); }
+  Block(int d_, int heads, int T_, int ff_, bool causal, int ff_act = GN_ACT_RELU, bool rms = false, bool rope = false) : d(d_), T(T_), ff(ff_), mha(d_, heads, T_, causal),
+      ff2(ff_, d_, GN_ACT_LINEAR), res1((size_t)T_ * d_), n1out(res1.size()), ffout(res1.size()), res2(res1.size()), out(res1.size()),
+      gRes2(res1.size()), gN1ff(res1.size()), comb(res1.size()), gRes1(res1.size()), gIn(res1.size()) {
+    mha.rope = rope;
+    if (rms) { n1.reset(new RMSNorm<R>(T_, d_, (R)1e-5f)); n2.reset(new RMSNorm<R>(T_, d_, (R)1e-5f)); }
+    else { n1.reset(new LayerNorm<R>(T_, d_)); n2.reset(new LayerNorm<R>(T_, d_)); }
+    if (ff_act == GN_ACT_SILU) ff1.reset(new SwiGLU<R>(d_, ff_));
+    else ff1.reset(new Dense<R>(d_, ff_, ff_act == GN_ACT_GELU ? GN_ACT_GELU : GN_ACT_RELU));
+  }
+  int64_t n_params() const override { return mha.n_params() + n1->n_params() + n2->n_params() + ff1->n_params() + ff2.n_params(); }
   void bind(const R* p, R* g) override {
     int64_t o = 0;
     auto adv = [&](Layer<R>& l) { l.bind(p + o, g ? g + o : nullptr); o += l.n_params(); };
-    adv(mha); adv(n1); adv(n2); adv(ff1); adv(ff2);
+    adv(mha); adv(*n1); adv(*n2); adv(*ff1); adv(ff2);
   }
   int in_size() const override { return T * d; } int out_size() const override { return T * d; }
   const R* forward(const R* x) override {
     const R* att = mha.forward(x);
     for (size_t i = 0; i < res1.size(); i++) res1[i] = x[i] + att[i];
-    const R* a = n1.forward(res1.data()); std::copy(a, a + res1.size(), n1out.begin());
+    const R* a = n1->forward(res1.data()); std::copy(a, a + res1.size(), n1out.begin());
+    ff1->reset();                                        // the stack of a SwiGLU starts empty for every sample (balanced pushes and pops)
     for (int s = 0; s < T; s++) {
-      const R* mid = ff1.forward(n1out.data() + (size_t)s * d);
+      const R* mid = ff1->forward(n1out.data() + (size_t)s * d);
       const R* fo = ff2.forward(mid);
       std::copy(fo, fo + d, ffout.begin() + (size_t)s * d);
     }
     for (size_t i = 0; i < res2.size(); i++) res2[i] = n1out[i] + ffout[i];
-    a = n2.forward(res2.data()); std::copy(a, a + out.size(), out.begin());
+    a = n2->forward(res2.data()); std::copy(a, a + out.size(), out.begin());
     return out.data();
   }
   const R* backward(R* grad) override {
-    const R* g = n2.backward(grad); std::copy(g, g + gRes2.size(), gRes2.begin());
+    const R* g = n2->backward(grad); std::copy(g, g + gRes2.size(), gRes2.begin());
     for (int s = 0; s < T; s++) {
       // ff2/ff1 use their last-forward buffers (token T-1) for every token  transformer.go:1238-1250
       const R* mg = ff2.backward(gRes2.data() + (size_t)s * d);
-      const R* g1 = ff1.backward(const_cast<R*>(mg));
+      const R* g1 = ff1->backward(const_cast<R*>(mg));
       std::copy(g1, g1 + d, gN1ff.begin() + (size_t)s * d);
     }
     for (size_t i = 0; i < comb.size(); i++) comb[i] = gRes2[i] + gN1ff[i];
-    g = n1.backward(comb.data()); std::copy(g, g + gRes1.size(), gRes1.begin());
+    g = n1->backward(comb.data()); std::copy(g, g + gRes1.size(), gRes1.begin());
     const R* ga = mha.backward(gRes1.data());
     for (size_t i = 0; i < gIn.size(); i++) gIn[i] = gRes1[i] + ga[i];
     return gIn.data();
@@ -961,7 +1039,10 @@ template <class R> struct Net {
           if (T <= 0) { g_err = "Embedding needs seq_len"; return false; }
           p.reset(new Embedding<R>(l.in_size, l.out_size, T)); break; }
         case GN_LAYER_POSENC: p.reset(new PosEnc<R>(l.seq_len, l.dim)); break;
-        case GN_LAYER_TRANSFORMER_BLOCK: p.reset(new Block<R>(l.dim, l.heads, l.seq_len, l.ff_dim, l.causal != 0)); break;
+        case GN_LAYER_TRANSFORMER_BLOCK:
+          if (l.activation != 0 && l.activation != GN_ACT_RELU && l.activation != GN_ACT_GELU && l.activation != GN_ACT_SILU) { g_err = "TransformerBlock feed-forward activation"; return false; }
+          if (l.stride != 0 && (l.dim / std::max(1, l.heads)) % 2) { g_err = "rotary embeddings need an even head size"; return false; }
+          p.reset(new Block<R>(l.dim, l.heads, l.seq_len, l.ff_dim, l.causal != 0, l.activation == 0 ? GN_ACT_RELU : l.activation, l.kernel != 0, l.stride != 0)); break;
         case GN_LAYER_CLS_POOLING: p.reset(new CLS<R>(l.seq_len, l.dim)); break;
         case GN_LAYER_BATCHNORM2D: {
           float eps = 1e-5f, mom = 0.1f; if (l.reserved) memcpy(&eps, &l.reserved, 4); if (l.dim) memcpy(&mom, &l.dim, 4);

@@ -37,9 +37,13 @@ def tensor_slices(layers):
             d, f = l.dim, l.ff_dim
             for nm in ("wq", "wk", "wv", "wo"):
                 add(f"{i}.blk.{nm}.W", d * d); add(f"{i}.blk.{nm}.b", d)
-            for nm in ("ln1.g", "ln1.b", "ln2.g", "ln2.b"):
+            for nm in (("rms1.g", "rms2.g") if l.kernel else ("ln1.g", "ln1.b", "ln2.g", "ln2.b")):
                 add(f"{i}.blk.{nm}", d)
-            add(f"{i}.blk.ff1.W", d * f); add(f"{i}.blk.ff1.b", f); add(f"{i}.blk.ff2.W", f * d); add(f"{i}.blk.ff2.b", d)
+            if l.activation == D.SILU:
+                add(f"{i}.blk.swiglu.W", d * f); add(f"{i}.blk.swiglu.V", d * f)
+            else:
+                add(f"{i}.blk.ff1.W", d * f); add(f"{i}.blk.ff1.b", f)
+            add(f"{i}.blk.ff2.W", f * d); add(f"{i}.blk.ff2.b", d)
         elif k == D.LAYERNORM:
             add(f"{i}.ln.g", l.dim); add(f"{i}.ln.b", l.dim)
         elif k == D.RMSNORM:

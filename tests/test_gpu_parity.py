@@ -51,6 +51,16 @@ CASES = [
     ("mlp_rms", {}, 16, 1), ("mlp_rms", dict(in_size=10, hidden=300, norm=100, classes=3), 5, 1),            # RMSNorm
     ("cnn1d", {}, 12, 1), ("cnn1d", dict(length=17, c0=2, c1=5, c2=3, classes=3, act=D.GELU), 7, 1),           # Conv1D
     ("transformer_small", dict(vocab=7, dim=16, seq_len=24, heads=2, ff_dim=32, n_blocks=1), 3, 1),          # every token id repeats: table rows summed in position order
+    # TransformerBlock variants (NewTransformerBlockExt): GELU and SwiGLU feed-forward, RMSNorm, rotary embeddings; non-causal so
+    # that every token receives a gradient (with causal attention and CLS pooling only token 0 does)
+    ("transformer_small", dict(vocab=300, dim=48, seq_len=20, heads=3, ff_dim=100, n_blocks=2, ff_act=D.GELU, causal=False), 5, 1),
+    ("transformer_small", dict(vocab=300, dim=48, seq_len=20, heads=3, ff_dim=100, n_blocks=2, rms_norm=True, causal=False), 5, 1),
+    ("transformer_small", dict(vocab=300, dim=48, seq_len=20, heads=3, ff_dim=100, n_blocks=2, rope=True, causal=False), 5, 1),
+    ("transformer_small", dict(vocab=300, dim=48, seq_len=20, heads=3, ff_dim=100, n_blocks=2, ff_act=D.SILU, causal=False), 5, 2),
+    ("transformer_small", dict(vocab=300, dim=64, seq_len=24, heads=2, ff_dim=96, n_blocks=2, ff_act=D.SILU, rms_norm=True, rope=True, causal=False), 4, 1),
+    ("transformer_small", dict(vocab=300, dim=64, seq_len=24, heads=2, ff_dim=96, n_blocks=2, ff_act=D.SILU, rms_norm=True, rope=True), 4, 1),
+    ("transformer_large", dict(vocab=500, dim=128, seq_len=256, heads=2, ff_dim=512, n_blocks=2, ff_act=D.SILU, rms_norm=True, rope=True, causal=False), 3, 1),   # tensor-core paths
+    ("transformer_large", dict(vocab=500, dim=128, seq_len=256, heads=2, ff_dim=512, n_blocks=1, ff_act=D.GELU, causal=False), 3, 1),
     ("gru", {}, 32, 1), ("gru", dict(in_size=5, hidden=24, seq_len=7), 11, 1),                                # GRU with its literal backward pass
     ("gru", dict(in_size=6, hidden=20, seq_len=5, return_seq=True), 9, 1), ("gru", dict(init="reference"), 32, 1),
     # the reference's own deterministic initialisation (LCG seeded from the layer shapes) instead of uploaded Glorot weights
