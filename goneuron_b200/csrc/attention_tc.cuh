@@ -19,7 +19,8 @@
 //               moved, the output accumulator is rescaled in TMEM after the previous P V has completed.  One warp per
 //               scheduler could not keep up with the tensor pipe (measured: 25 % tensor activity); two do.
 // The issue order S_0, S_1, PV_0, S_2, PV_1, ... keeps the tensor pipe busy with S_{j+1} (and PV_{j-1}) while the
-// softmax of block j runs.  Every wait is bounded; a wait that gives up sets the status word.
+// softmax of block j runs.  Every wait is bounded; a wait that gives up sets the status word at once, which makes
+// every other wait of the launch give up within a few polls (see WAIT below).
 #pragma once
 #include "attention.cuh"
 #include "gemm_tc.cuh"
@@ -85,7 +86,7 @@ template <int N> struct AttnMaps { CUtensorMap m[N]; };
 // (the output accumulator is double-buffered for that).
 __global__ void __launch_bounds__(ATC_THREADS, 1)
 attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__ O, float* __restrict__ Mst, float* __restrict__ Lst, int T, int D, int H, int causal, float inv_scale,
-                   int ntiles, int* status) {
+                   int ntiles, int* status, unsigned spin_limit) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* sQ = smem;
@@ -99,6 +100,14 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Bounded waits that fail fast: the first wait that gives up records its role in the status word at once, and every
+  // later wait of every role and CTA (they all poll that word) gives up after at most 64 polls, so a launch whose pipeline
+  // is stuck runs its loops to their end in milliseconds instead of polling each wait to its limit.  The roles keep
+  // their loop structure (the elementwise warps meet at named barriers, so no warp may leave early); what they compute
+  // after that point is discarded by the host (GN_ERR_TIMEOUT).
+  const unsigned limit = spin_limit;
+  auto WAIT = [&](uint32_t bar, uint32_t parity, int code) -> bool { if (mbar_wait(bar, parity, limit, status)) return true; atomicCAS(status, 0, code); return false; };
+  auto WWAIT = [&](uint32_t bar, uint32_t parity, int code) -> bool { int w = 1; if (lane == 0) w = WAIT(bar, parity, code) ? 1 : 0; return __shfl_sync(0xffffffffu, w, 0) != 0; };
   const int ntq = T / ATC_BQ;
   // tile -> problem z, first query row, number of key blocks
   auto decode = [&](int id, int i, int& z, int& q0, int& nblk) {
@@ -107,7 +116,7 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 17; i++) mbar_init(BAR(i), (i == 11 || i == 12 || i == 15 || i == 16) ? 256 : 1);
+    for (int i = 0; i < 18; i++) mbar_init(BAR(i), (i == 11 || i == 12 || i == 15 || i == 16) ? 256 : 1);      // 17: drain
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -124,26 +133,26 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
       bool ok = true; uint32_t g = 0;
       for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
         int z, q0, nblk; decode(id, tt, z, q0, nblk);
-        if (tt > 0) ok &= mbar_wait(BAR(14), (tt - 1) & 1);
+        if (tt > 0) ok &= WAIT(BAR(14), (tt - 1) & 1, 11);
         mbar_expect_tx(BAR(0), ATC_Q_BYTES);
         for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sQ + c * 16384), &maps.m[0], c * 32, q0, z, BAR(0));
         tma_load_3d(smem_u32(sQ + 32768), &maps.m[1], 0, q0, z, BAR(0));
         tma_load_3d(smem_u32(sQ + 49152), &maps.m[2], 0, q0, z, BAR(0));
         for (int j = 0; j < nblk; j++, g++) {
           const uint32_t s = g & 1, u = g >> 1;
-          if (u > 0) ok &= mbar_wait(BAR(3 + s), (u - 1) & 1);
+          if (u > 0) ok &= WAIT(BAR(3 + s), (u - 1) & 1, 11);
           mbar_expect_tx(BAR(1 + s), ATC_K_BYTES);
           for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + c * 8192), &maps.m[3], c * 32, j * ATC_BK, z, BAR(1 + s));
           tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + 16384), &maps.m[4], 0, j * ATC_BK, z, BAR(1 + s));
           tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + 24576), &maps.m[5], 0, j * ATC_BK, z, BAR(1 + s));
-          if (u > 0) ok &= mbar_wait(BAR(7 + s), (u - 1) & 1);
+          if (u > 0) ok &= WAIT(BAR(7 + s), (u - 1) & 1, 11);
           mbar_expect_tx(BAR(5 + s), ATC_V_BYTES);
           for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + c * 8192), &maps.m[6], j * ATC_BK + c * 32, 0, z, BAR(5 + s));
           tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + 16384), &maps.m[7], j * ATC_BK, 0, z, BAR(5 + s));
           tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + 24576), &maps.m[8], j * ATC_BK, 0, z, BAR(5 + s));
         }
       }
-      if (!ok) atomicExch(status, 11);
+      if (!ok || *(volatile int*)status) for (int i = 0; i < 200; i++) __nanosleep(1000);                 // own copies in flight land before the CTA exits
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -154,7 +163,7 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
         const uint32_t ob = tt & 1;
         auto issue_s = [&](int j) {
           const uint32_t g = g0 + j, s = g & 1, u = g >> 1;
-          ok &= mbar_wait(BAR(1 + s), u & 1);
+          ok &= WAIT(BAR(1 + s), u & 1, 12);
           tc_fence_after();
           const uint32_t acc = tmem_base + ATC_COL_S + s * 64;
           const uint32_t kb = smem_u32(sK + s * ATC_K_BYTES), qa = smem_u32(sQ);
@@ -177,8 +186,8 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
         };
         auto issue_pv = [&](int j) {
           const uint32_t g = g0 + j, s = g & 1, u = g >> 1;
-          ok &= mbar_wait(BAR(11 + s), u & 1);
-          ok &= mbar_wait(BAR(5 + s), u & 1);
+          ok &= WAIT(BAR(11 + s), u & 1, 12);
+          ok &= WAIT(BAR(5 + s), u & 1, 12);
           tc_fence_after();
           const uint32_t vb = smem_u32(sV + s * ATC_V_BYTES);
           const uint32_t ph = tmem_base + ATC_COL_S + s * 64, pl = tmem_base + ATC_COL_PLO + s * 64, acc = tmem_base + ATC_COL_O + ob * 64;
@@ -196,8 +205,8 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
           tc_commit(BAR(7 + s));
           tc_commit(BAR(13));
         };
-        ok &= mbar_wait(BAR(0), tt & 1);
-        if (tt >= 2) ok &= mbar_wait(BAR(15 + ob), ((tt >> 1) - 1) & 1);     // this accumulator has been written out
+        ok &= WAIT(BAR(0), tt & 1, 12);
+        if (tt >= 2) ok &= WAIT(BAR(15 + ob), ((tt >> 1) - 1) & 1, 12);     // this accumulator has been written out
         issue_s(0);
         if (nblk > 1) issue_s(1);
         for (int j = 0; j < nblk; j++) {
@@ -206,7 +215,7 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
         }
         g0 += nblk;
       }
-      if (!ok) atomicExch(status, 12);
+      if (!ok || *(volatile int*)status) { tc_commit(BAR(17)); mbar_wait(BAR(17), 0, TC_DRAIN_LIMIT); }     // own instructions in flight finish before TMEM is released
     }
   } else {
     // two threads per query row: `half` selects 32 of the 64 columns of a block (and of the accumulator)
@@ -221,7 +230,7 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
       float m_run = -INFINITY, l_part = 0.f;                // running maximum (scaled scores), this thread's part of the row sum
       for (int j = 0; j < nblk; j++) {
         const uint32_t g = g0 + j, s = g & 1, u = g >> 1; const int key0 = j * ATC_BK + 32 * half;
-        ok &= warp_mbar_wait(BAR(9 + s), u & 1, lane);
+        ok &= WWAIT(BAR(9 + s), u & 1, 13);
         tc_fence_after();
         uint32_t a[32];
         tmem_ld32(lane_base + ATC_COL_S + s * 64, a);
@@ -252,7 +261,7 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
         // The accumulator may only be touched between P V products.  The wait is unconditional: a parity wait is only
         // unambiguous when no completion of this barrier has been skipped (the first block of a tile skips none: the
         // previous tile's write-out has waited for its last product).
-        if (j > 0) ok &= warp_mbar_wait(BAR(13), (g - 1) & 1, lane);
+        if (j > 0) ok &= WWAIT(BAR(13), (g - 1) & 1, 13);
         if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
           tc_fence_after();
           tmem_ld32(lane_base + ATC_COL_O + ob * 64, a);
@@ -265,7 +274,7 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
         tc_fence_before();
         mbar_arrive(BAR(11 + s));
       }
-      ok &= warp_mbar_wait(BAR(13), (g0 + nblk - 1) & 1, lane);
+      ok &= WWAIT(BAR(13), (g0 + nblk - 1) & 1, 13);
       tc_fence_after();
       {
         uint32_t a[32];
@@ -287,7 +296,7 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
       }
       g0 += nblk;
     }
-    if (!ok && lane == 0) atomicExch(status, 13);
+    (void)ok;
   }
   tc_fence_before();
   __syncthreads();
@@ -321,7 +330,7 @@ constexpr uint32_t ATB_COL_S = 0, ATB_COL_DP = 128, ATB_COL_LO = 256, ATB_COL_AC
 template <int MODE>
 __global__ void __launch_bounds__(ATB_THREADS, 1)
 attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __restrict__ Mst, const float* __restrict__ Lst, const float* __restrict__ Dv,
-                   float* __restrict__ Out, int T, int D, int H, int causal, float inv_scale, int ntiles, int* status) {
+                   float* __restrict__ Out, int T, int D, int H, int causal, float inv_scale, int ntiles, int* status, unsigned spin_limit) {
   constexpr int NR = AtbCfg<MODE>::NR;
   constexpr bool TRANS = MODE != 0;
   extern __shared__ uint8_t smem_raw[];
@@ -337,6 +346,14 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Bounded waits that fail fast: the first wait that gives up records its role in the status word at once, and every
+  // later wait of every role and CTA (they all poll that word) gives up after at most 64 polls, so a launch whose pipeline
+  // is stuck runs its loops to their end in milliseconds instead of polling each wait to its limit.  The roles keep
+  // their loop structure (the elementwise warps meet at named barriers, so no warp may leave early); what they compute
+  // after that point is discarded by the host (GN_ERR_TIMEOUT).
+  const unsigned limit = spin_limit;
+  auto WAIT = [&](uint32_t bar, uint32_t parity, int code) -> bool { if (mbar_wait(bar, parity, limit, status)) return true; atomicCAS(status, 0, code); return false; };
+  auto WWAIT = [&](uint32_t bar, uint32_t parity, int code) -> bool { int w = 1; if (lane == 0) w = WAIT(bar, parity, code) ? 1 : 0; return __shfl_sync(0xffffffffu, w, 0) != 0; };
   const int ntr = T / 128;
   // persistent, as in the forward kernel: tile id -> problem z, first row of the tile, first block and number of blocks
   auto decode = [&](int id, int i, int& z, int& r0, int& b0, int& nb) {
@@ -346,7 +363,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 13; i++) mbar_init(BAR(i), (i == 7 || i == 8 || i == 11 || i == 12) ? 256 : 1);
+    for (int i = 0; i < 14; i++) mbar_init(BAR(i), (i == 7 || i == 8 || i == 11 || i == 12) ? 256 : 1);      // 13: drain
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -363,7 +380,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
       bool ok = true; uint32_t g = 0;
       for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
         int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
-        if (tt > 0) ok &= mbar_wait(BAR(10), (tt - 1) & 1);
+        if (tt > 0) ok &= WAIT(BAR(10), (tt - 1) & 1, 21);
         mbar_expect_tx(BAR(0), NR * ATB_R_BYTES);
         // maps: R1 = 0..2, R2 = 3..5, C1 = 6..8, C2 = 9..11, C3 = 12..14 (hi | bf16 copy | bf16 lo each)
         for (int o = 0; o < NR; o++) {
@@ -374,7 +391,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
         }
         for (int n = 0; n < nb; n++, g++) {
           const int row = (b0 + n) * 64;
-          if (g > 0) ok &= mbar_wait(BAR(2), (g - 1) & 1);
+          if (g > 0) ok &= WAIT(BAR(2), (g - 1) & 1, 21);
           mbar_expect_tx(BAR(1), NR * ATB_C_BYTES);
           for (int o = 0; o < NR; o++) {
             const uint32_t base = smem_u32(sC + o * ATB_C_BYTES);
@@ -384,7 +401,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
           }
         }
       }
-      if (!ok) atomicExch(status, 21);
+      if (!ok || *(volatile int*)status) for (int i = 0; i < 200; i++) __nanosleep(1000);                 // own copies in flight land before the CTA exits
     }
   } else if (warp == 10) {
     if (lane == 0) {
@@ -393,14 +410,14 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
         int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
         for (int n = 0; n < nb; n++, g++) {
           const int col = (b0 + n) * 64;
-          if (g > 0) ok &= mbar_wait(BAR(4), (g - 1) & 1);
+          if (g > 0) ok &= WAIT(BAR(4), (g - 1) & 1, 22);
           mbar_expect_tx(BAR(3), ATB_C_BYTES);
           for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sC3 + c * 8192), &maps.m[12], col + c * 32, 0, z, BAR(3));
           tma_load_3d(smem_u32(sC3 + 16384), &maps.m[13], col, 0, z, BAR(3));
           tma_load_3d(smem_u32(sC3 + 24576), &maps.m[14], col, 0, z, BAR(3));
         }
       }
-      if (!ok) atomicExch(status, 22);
+      if (!ok || *(volatile int*)status) for (int i = 0; i < 200; i++) __nanosleep(1000);
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -411,7 +428,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
         const uint32_t ab = tt & 1;
         auto issue_sd = [&](int n) {
           const uint32_t g = g0 + n, s = g & 1;
-          ok &= mbar_wait(BAR(1), g & 1);
+          ok &= WAIT(BAR(1), g & 1, 23);
           tc_fence_after();
 #pragma unroll
           for (int prod = 0; prod < NR; prod++) {
@@ -437,8 +454,8 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
         };
         auto issue_acc = [&](int n) {
           const uint32_t g = g0 + n, s = g & 1, u = g >> 1;
-          ok &= mbar_wait(BAR(7 + s), u & 1);
-          ok &= mbar_wait(BAR(3), g & 1);
+          ok &= WAIT(BAR(7 + s), u & 1, 23);
+          ok &= WAIT(BAR(3), g & 1, 23);
           tc_fence_after();
           const uint32_t cb = smem_u32(sC3);
           const uint32_t ph = tmem_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, pl = tmem_base + ATB_COL_LO + s * 64,
@@ -457,8 +474,8 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
           tc_commit(BAR(4));
           if (n == nb - 1) tc_commit(BAR(9));
         };
-        ok &= mbar_wait(BAR(0), tt & 1);
-        if (tt >= 2) ok &= mbar_wait(BAR(11 + ab), ((tt >> 1) - 1) & 1);     // this accumulator has been written out
+        ok &= WAIT(BAR(0), tt & 1, 23);
+        if (tt >= 2) ok &= WAIT(BAR(11 + ab), ((tt >> 1) - 1) & 1, 23);     // this accumulator has been written out
         issue_sd(0);
         if (nb > 1) issue_sd(1);
         for (int n = 0; n < nb; n++) {
@@ -467,7 +484,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
         }
         g0 += nb;
       }
-      if (!ok) atomicExch(status, 23);
+      if (!ok || *(volatile int*)status) { tc_commit(BAR(13)); mbar_wait(BAR(13), 0, TC_DRAIN_LIMIT); }     // own instructions in flight finish before TMEM is released
     }
   } else {
     // two threads per tile row: `half` selects 32 of the 64 columns of a block (and of the accumulator)
@@ -489,7 +506,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
           if (et < 64) { stm[et] = -Mst[sb + c0 + et] * LOG2E; stl[et] = oscale / Lst[sb + c0 + et]; if (MODE == 1) std_[et] = Dv[sb + c0 + et]; }
           asm volatile("bar.sync 1, 256;" ::: "memory");
         }
-        ok &= warp_mbar_wait(BAR(5 + s), u & 1, lane);
+        ok &= WWAIT(BAR(5 + s), u & 1, 24);
         tc_fence_after();
         uint32_t a[32], b[32];
         tmem_ld32(lane_base + ATB_COL_S + s * 64, a);
@@ -514,7 +531,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
         tc_fence_before();
         mbar_arrive(BAR(7 + s));
       }
-      ok &= warp_mbar_wait(BAR(9), tt & 1, lane);
+      ok &= WWAIT(BAR(9), tt & 1, 24);
       tc_fence_after();
       {
         uint32_t a[32];
@@ -530,7 +547,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
       }
       g0 += nb;
     }
-    if (!ok && lane == 0) atomicExch(status, 24);
+    (void)ok;
   }
   tc_fence_before();
   __syncthreads();
@@ -623,7 +640,7 @@ inline int attn_tc_fwd(Ctx* ctx, const float* Q, const float* K, const float* V,
   GN_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_FWD_SMEM));
   const int ntq = T / ATC_BQ, ntiles = ntq * B * H;
   const int grid = std::min(ntiles, std::max(1, ctx->sm_count / ntq) * ntq);      // a multiple of the query blocks per problem
-  GN_LAUNCH(ctx, attn_tc_fwd_kernel, grid, ATC_THREADS, ATC_FWD_SMEM, maps, O, M, L, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status);
+  GN_LAUNCH(ctx, attn_tc_fwd_kernel, grid, ATC_THREADS, ATC_FWD_SMEM, maps, O, M, L, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status, ctx->spin_limit);
   return check_launch("attn_tc_fwd");
 }
 
@@ -636,7 +653,7 @@ inline int attn_tc_bwd_launch(Ctx* ctx, const TcPlanes& r1, const TcPlanes& r2, 
   GN_CUDA(cudaFuncSetAttribute(attn_tc_bwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, AtbCfg<MODE>::SMEM));
   const int ntr = T / 128, ntiles = ntr * B * H;
   const int grid = std::min(ntiles, std::max(1, ctx->sm_count / ntr) * ntr);      // a multiple of the row tiles per problem
-  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, grid, ATB_THREADS, AtbCfg<MODE>::SMEM, maps, M, L, Dv, out, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status);
+  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, grid, ATB_THREADS, AtbCfg<MODE>::SMEM, maps, M, L, Dv, out, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status, ctx->spin_limit);
   return check_launch("attn_tc_bwd");
 }
 // dQ, dK, dV from Q, K, V, O, dO and the forward's row statistics; Dv receives the row products dO . O

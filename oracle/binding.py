@@ -44,6 +44,7 @@ def lib():
         L.gno_loss.restype = C.c_float
         L.gno_loss_grad.argtypes = [C.c_int, f32p, f32p, f32p, C.c_int]
         L.gno_adam.argtypes = [f32p, f32p, f32p, f32p, C.c_int64, C.c_float, C.c_float, C.c_float, C.c_float, C.c_int, C.c_int]
+        L.gno_rope.argtypes = [f32p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
         L.gno_gemm_nt.argtypes = [C.c_int, C.c_int, C.c_int, f32p, f32p, f32p, f32p, C.c_int]
         _lib = L
     return _lib
@@ -144,6 +145,14 @@ def adam(p, g, m, v, lr, b1, b2, eps, t, precision=32):
     p, g, m, v = _f32(p).copy(), _f32(g), _f32(m).copy(), _f32(v).copy()
     lib().gno_adam(_p(p), _p(g), _p(m), _p(v), p.size, lr, b1, b2, eps, t, precision)
     return p, m, v
+
+
+def rope(x, T, heads, hd, conjugate=False, precision=32):
+    """Rotary embeddings on x [T, heads * hd] (transformer.go:212-236)."""
+    x = _f32(x).copy()
+    if lib().gno_rope(_p(x), T, heads, hd, 1 if conjugate else 0, precision):
+        raise ValueError(lib().gno_last_error().decode())
+    return x
 
 
 def gemm_nt(A, B, bias=None, precision=32):

@@ -1232,7 +1232,10 @@ int gno_state_count(const gn_layer_desc* layers, int n_layers, int64_t* n) {
 }
 int gno_param_count(const gn_layer_desc* layers, int n_layers, int64_t* n, int64_t* in_size, int64_t* out_size) {
   Net<float> net; if (!Net<float>::build(layers, n_layers, net)) return GN_ERR_INVALID_ARG;
-  if (n) *n = net.n_params; if (in_size) *in_size = net.in_size; if (out_size) *out_size = net.out_size; return GN_OK;
+  if (n) *n = net.n_params;
+  if (in_size) *in_size = net.in_size;
+  if (out_size) *out_size = net.out_size;
+  return GN_OK;
 }
 
 // One Network.TrainBatch.  With global_batch > 0 the call is ONE RANK's shard of a larger batch: gradients and
@@ -1272,6 +1275,14 @@ void gno_adam(float* p, const float* g, float* m, float* v, int64_t n, float lr,
   } else adam_step<float>(p, g, m, v, n, lr, b1, b2, eps, t);
 }
 // C[M,N] = A[M,K] B[N,K]^T + bias, in the reference's accumulation order (bias first)
+// Rotary embeddings in place on x [T, heads * hd] (transformer.go:212-236); precision 32 = the literal float arithmetic.
+int gno_rope(float* x, int T, int heads, int hd, int conjugate, int precision) {
+  if (!x || T <= 0 || heads <= 0 || hd <= 0 || hd % 2) { g_err = "gno_rope: bad argument"; return GN_ERR_INVALID_ARG; }
+  const size_t n = (size_t)T * heads * hd;
+  if (precision == 32) apply_rope<float>(x, T, heads, hd, conjugate != 0);
+  else { std::vector<double> d(x, x + n); apply_rope<double>(d.data(), T, heads, hd, conjugate != 0); for (size_t i = 0; i < n; i++) x[i] = (float)d[i]; }
+  return GN_OK;
+}
 void gno_gemm_nt(int M, int N, int K, const float* A, const float* B, const float* bias, float* C, int precision) {
   for (int m = 0; m < M; m++) for (int n = 0; n < N; n++) {
     if (precision == 64) { double s = bias ? bias[n] : 0.0; for (int k = 0; k < K; k++) s += (double)A[(size_t)m * K + k] * B[(size_t)n * K + k]; C[(size_t)m * N + n] = (float)s; }

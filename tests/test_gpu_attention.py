@@ -68,3 +68,30 @@ def test_attention_matches_fp64(device, engine, B, T, D, H, causal):
     for name, a, b in zip(("O", "dQ", "dK", "dV"), (got[0], got[3], got[4], got[5]), (ref[0], ref[3], ref[4], ref[5])):
         e = norm_err(a, b)
         assert e < TOL, f"{name}: normalised error {e:.3e}"
+
+
+def test_attention_bounded_waits_fail_fast_and_the_context_stays_usable(device):
+    """Failure detection without a GPU fault: with a poll limit of 1 the first wait of the tcgen05 attention kernels runs
+    out; the status word is set at once, every other wait of the launch then gives up within a few polls, the kernels run
+    their loops to the end and release tensor memory, the call reports GN_ERR_TIMEOUT quickly, and the next call is correct."""
+    import time
+    from goneuron_b200 import _lib
+    L = _lib.load()
+    B, T, D, H = 2, 512, 128, 2
+    rng = np.random.default_rng(77)
+    Q, K, V, dO = (rng.standard_normal((B * T, D)).astype(np.float32) for _ in range(4))
+    good = run(device, 1, Q, K, V, dO, B, T, D, H, 1)
+    f = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+    O, dQ, dK, dV = (np.empty_like(Q) for _ in range(4))
+    _lib.check(L.gn_ctx_set_spin_limit(device.handle, 1))
+    try:
+        t0 = time.perf_counter()
+        rc = L.gn_op_attention(device.handle, 1, B, T, D, H, 1, f(Q), f(K), f(V), f(dO), f(O), None, None, f(dQ), f(dK), f(dV))
+        dt = time.perf_counter() - t0
+    finally:
+        _lib.check(L.gn_ctx_set_spin_limit(device.handle, 0))
+    assert rc == -6 and b"bounded wait" in L.gn_last_error(), (rc, L.gn_last_error())
+    assert dt < 5.0, dt
+    again = run(device, 1, Q, K, V, dO, B, T, D, H, 1)
+    for a, b in zip(good, again):
+        assert np.array_equal(a, b)

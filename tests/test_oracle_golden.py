@@ -160,3 +160,71 @@ def test_conv1d_known_answer(oracle):
     st = oracle.OracleState([D.Conv1D(1, 1, 3, 1, 1, D.LINEAR, 5)], D.MSE, np.array([1, 0, 1, 0], np.float32))
     out = st.forward_batch(np.array([[0, 1, 2, 3, 4]], np.float32), precision=32)
     assert np.array_equal(out.ravel(), np.array([1, 2, 4, 6, 3], np.float32))
+
+
+def test_layernorm_known_answers(oracle):
+    """internal/layer/layernorm_test.go:8-35 (x = [1, 2, 3, 4], gamma 1, beta 0 -> (x - 2.5) / sqrt(1.25 + 1e-5)) and :98-123
+    (two rows [1..4], [5..8], each normalised on its own)."""
+    # (a normalisation layer takes its row count from the layer in front of it: an identity Dense supplies it)
+    params = np.concatenate([np.eye(8, dtype=np.float32).ravel(), np.zeros(8, np.float32), np.ones(4, np.float32), np.zeros(4, np.float32)])
+    st = oracle.OracleState([D.Dense(8, 8, D.LINEAR), D.LayerNorm(4)], D.MSE, params)
+    x = np.arange(1, 9, dtype=np.float32).reshape(1, 8)
+    std = np.float32(np.sqrt(1.25 + 1e-5))
+    want = np.concatenate([(x[0, :4] - np.float32(2.5)) / std, (x[0, 4:] - np.float32(6.5)) / std])
+    np.testing.assert_allclose(st.forward_batch(x, precision=32).ravel(), want, atol=1e-5, rtol=0)
+
+
+def test_maxpool2d_known_answers(oracle):
+    """internal/layer/maxpool2d_test.go:8-35 (2x2 stride 2 on 4x4 -> [6, 8, 14, 16]), :37-65 (2x2 stride 1 on 3x3 ->
+    [5, 6, 8, 9]), :84-108 (a gradient of ones reaches exactly the arg-max positions 5, 7, 13, 15)."""
+    st = oracle.OracleState([D.MaxPool2D(1, 2, 2, 0, 4, 4)], D.MSE, np.zeros(0, np.float32))
+    x = np.arange(1, 17, dtype=np.float32).reshape(1, 16)
+    assert np.array_equal(st.forward_batch(x, precision=32).ravel(), np.array([6, 8, 14, 16], np.float32))
+    st = oracle.OracleState([D.MaxPool2D(1, 2, 1, 0, 3, 3)], D.MSE, np.zeros(0, np.float32))
+    assert np.array_equal(st.forward_batch(np.arange(1, 10, dtype=np.float32).reshape(1, 9), precision=32).ravel(), np.array([5, 6, 8, 9], np.float32))
+    layers = [D.Dense(16, 16, D.LINEAR), D.MaxPool2D(1, 2, 2, 0, 4, 4)]
+    params = np.concatenate([np.eye(16, dtype=np.float32).ravel(), np.zeros(16, np.float32)])
+    st = oracle.OracleState(layers, D.MSE, params)
+    y = np.array([[6, 8, 14, 16]], np.float32) - 2.0                  # MSE gradient 2/n (p - y) = 1 for n = 4
+    st.train_batch(x, y, precision=32, step=False)
+    want = np.zeros(16, np.float32); want[[5, 7, 13, 15]] = 1
+    assert np.array_equal(st.grads[256:], want)                      # the identity Dense's bias gradient = the pool's input gradient
+
+
+def test_batchnorm2d_known_answer(oracle):
+    """internal/layer/batchnorm2d_test.go:8-30: two channels with two positions each, [1, 5 | 2, 6] -> [-1, 1, -1, 1]."""
+    params = np.array([1, 1, 0, 0], np.float32)                      # gamma 1, beta 0
+    st = oracle.OracleState([D.BatchNorm2D(2, 1, 2)], D.MSE, params)
+    out = st.forward_batch(np.array([[1, 5, 2, 6]], np.float32), precision=32, training=True)
+    np.testing.assert_allclose(out.ravel(), [-1, 1, -1, 1], atol=1e-5, rtol=0)
+
+
+def test_swiglu_known_answer(oracle):
+    """internal/layer/swiglu_test.go:30-53: w = 2, v = 3, x = 1 -> swish(2) * 3 = 5.284782.  The layer lives inside a
+    TransformerBlock here, so it is pinned through a block whose other parts are switched off by zero weights."""
+    # SwiGLU: block of width 1, one head, one token; attention output 0 (zero projections), RMSNorm with gain g:
+    # r1 = x, n1 = g * x / sqrt(x^2 + eps); choose x, g so that n1 = 1; ff2 = identity -> block output before norm 2 = n1 + swiglu(n1)
+    x0 = np.float32(1.0)
+    g = np.float32(np.sqrt(np.float64(x0 * x0) + 1e-5))
+    blk = D.TransformerBlock(1, 1, 1, 1, True, ff_act=D.SILU, rms_norm=True)
+    #        wq wk wv wo (W, b each)        rms1 rms2  swiglu W, V   ff2 W, b
+    params = np.array([0, 0, 0, 0, 0, 0, 0, 0, g, 1, 2, 3, 1, 0], np.float32)
+    st = oracle.OracleState([D.Dense(1, 1, D.LINEAR), blk], D.MSE, np.concatenate([np.array([1, 0], np.float32), params]))
+    out = st.forward_batch(np.array([[x0]], np.float32), precision=64)
+    # the block's output is RMSNorm(r2) with gain 1: r2 / sqrt(r2^2 + eps), r2 = 1 + 5.284782
+    r2 = 1.0 + 5.284782
+    np.testing.assert_allclose(out.ravel(), [r2 / np.sqrt(r2 * r2 + 1e-5)], atol=2e-6, rtol=0)
+
+
+def test_rope_known_answers(oracle):
+    """internal/layer/rope_test.go:8-49: head size 4, two positions of [1, 2, 3, 4]: position 0 is unchanged, at position 1
+    the pair (x0, x2) = (1, 3) turns by theta_0 = 1 radian; :51-79: the conjugate rotation undoes the rotation."""
+    x = np.array([1, 2, 3, 4, 1, 2, 3, 4], np.float32)
+    y = oracle.rope(x, 2, 1, 4)
+    assert np.array_equal(y[:4], x[:4])
+    c0, s0 = np.float32(np.cos(np.float64(np.float32(1.0)))), np.float32(np.sin(np.float64(np.float32(1.0))))
+    assert abs(y[4] - (1 * c0 - 3 * s0)) <= 1e-5 and abs(y[6] - (1 * s0 + 3 * c0)) <= 1e-5
+    rng = np.random.default_rng(3)
+    z = rng.standard_normal(10 * 4 * 32).astype(np.float32)
+    back = oracle.rope(oracle.rope(z, 10, 4, 32), 10, 4, 32, conjugate=True)
+    np.testing.assert_allclose(back, z, atol=1e-5, rtol=0)

@@ -15,7 +15,12 @@ import torch.multiprocessing as mp
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CASES = [("mlp", dict(in_size=20, hidden=9, classes=4), 8, 1),
          ("transformer_small", dict(vocab=64, dim=16, seq_len=6, heads=2, ff_dim=24, n_blocks=1), 6, 1),
-         ("transformer_small", dict(vocab=64, dim=16, seq_len=6, heads=2, ff_dim=24, n_blocks=1), 8, 4)]
+         ("transformer_small", dict(vocab=64, dim=16, seq_len=6, heads=2, ff_dim=24, n_blocks=1), 8, 4),
+         # LSTM: the clipping scan runs per reference worker chunk; with as many chunks as ranks (or a multiple) every chunk lies
+         # inside one rank's shard and the sum over ranks is the reference's sum over workers (net.go:694-700).  (A chunk that
+         # spans ranks needs the update factors gathered first: that route is tested on two GPUs.)
+         ("lstm", dict(in_size=5, hidden=8, seq_len=4), 8, 2), ("lstm", dict(in_size=5, hidden=8, seq_len=4), 8, 4),
+         ("gru", dict(in_size=5, hidden=8, seq_len=4), 6, 1)]
 
 
 def _worker(rank, world, port, out_dir):
