@@ -102,8 +102,10 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Bounded waits that fail fast: the first wait that gives up records its role in the status word at once, and every
   // later wait of every role and CTA (they all poll that word) gives up after at most 64 polls, so a launch whose pipeline
-  // is stuck runs its loops to their end in milliseconds instead of polling each wait to its limit.  The roles keep
-  // their loop structure (the elementwise warps meet at named barriers, so no warp may leave early); what they compute
+  // is stuck ends in milliseconds instead of polling each wait to its limit.  The copy and MMA threads stop issuing at
+  // their first failed wait (arming a barrier whose previous phase has not completed is undefined), then let what
+  // they have in flight finish.  The elementwise warps keep their loop structure (they meet at named barriers, so no
+  // warp may leave early) and only touch tensor memory, count-256 barriers and in-range global rows; what they compute
   // after that point is discarded by the host (GN_ERR_TIMEOUT).
   const unsigned limit = spin_limit;
   auto WAIT = [&](uint32_t bar, uint32_t parity, int code) -> bool { if (mbar_wait(bar, parity, limit, status)) return true; atomicCAS(status, 0, code); return false; };
@@ -131,21 +133,21 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true; uint32_t g = 0;
-      for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+      for (int id = blockIdx.x, tt = 0; id < ntiles && ok; id += gridDim.x, tt++) {
         int z, q0, nblk; decode(id, tt, z, q0, nblk);
-        if (tt > 0) ok &= WAIT(BAR(14), (tt - 1) & 1, 11);
+        if (tt > 0 && !WAIT(BAR(14), (tt - 1) & 1, 11)) { ok = false; break; }
         mbar_expect_tx(BAR(0), ATC_Q_BYTES);
         for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sQ + c * 16384), &maps.m[0], c * 32, q0, z, BAR(0));
         tma_load_3d(smem_u32(sQ + 32768), &maps.m[1], 0, q0, z, BAR(0));
         tma_load_3d(smem_u32(sQ + 49152), &maps.m[2], 0, q0, z, BAR(0));
         for (int j = 0; j < nblk; j++, g++) {
           const uint32_t s = g & 1, u = g >> 1;
-          if (u > 0) ok &= WAIT(BAR(3 + s), (u - 1) & 1, 11);
+          if (u > 0 && !WAIT(BAR(3 + s), (u - 1) & 1, 11)) { ok = false; break; }
           mbar_expect_tx(BAR(1 + s), ATC_K_BYTES);
           for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + c * 8192), &maps.m[3], c * 32, j * ATC_BK, z, BAR(1 + s));
           tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + 16384), &maps.m[4], 0, j * ATC_BK, z, BAR(1 + s));
           tma_load_3d(smem_u32(sK + s * ATC_K_BYTES + 24576), &maps.m[5], 0, j * ATC_BK, z, BAR(1 + s));
-          if (u > 0) ok &= WAIT(BAR(7 + s), (u - 1) & 1, 11);
+          if (u > 0 && !WAIT(BAR(7 + s), (u - 1) & 1, 11)) { ok = false; break; }
           mbar_expect_tx(BAR(5 + s), ATC_V_BYTES);
           for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + c * 8192), &maps.m[6], j * ATC_BK + c * 32, 0, z, BAR(5 + s));
           tma_load_3d(smem_u32(sV + s * ATC_V_BYTES + 16384), &maps.m[7], j * ATC_BK, 0, z, BAR(5 + s));
@@ -158,12 +160,12 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
     if (lane == 0) {
       bool ok = true; uint32_t g0 = 0;
       constexpr uint32_t idesc = make_idesc(ATC_BQ, 64), idesc_bf = make_idesc_bf16(ATC_BQ, 64);
-      for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+      for (int id = blockIdx.x, tt = 0; id < ntiles && ok; id += gridDim.x, tt++) {
         int z, q0, nblk; decode(id, tt, z, q0, nblk);
         const uint32_t ob = tt & 1;
         auto issue_s = [&](int j) {
           const uint32_t g = g0 + j, s = g & 1, u = g >> 1;
-          ok &= WAIT(BAR(1 + s), u & 1, 12);
+          if (!ok || !WAIT(BAR(1 + s), u & 1, 12)) { ok = false; return; }
           tc_fence_after();
           const uint32_t acc = tmem_base + ATC_COL_S + s * 64;
           const uint32_t kb = smem_u32(sK + s * ATC_K_BYTES), qa = smem_u32(sQ);
@@ -186,8 +188,7 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
         };
         auto issue_pv = [&](int j) {
           const uint32_t g = g0 + j, s = g & 1, u = g >> 1;
-          ok &= WAIT(BAR(11 + s), u & 1, 12);
-          ok &= WAIT(BAR(5 + s), u & 1, 12);
+          if (!ok || !WAIT(BAR(11 + s), u & 1, 12) || !WAIT(BAR(5 + s), u & 1, 12)) { ok = false; return; }
           tc_fence_after();
           const uint32_t vb = smem_u32(sV + s * ATC_V_BYTES);
           const uint32_t ph = tmem_base + ATC_COL_S + s * 64, pl = tmem_base + ATC_COL_PLO + s * 64, acc = tmem_base + ATC_COL_O + ob * 64;
@@ -205,8 +206,8 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<9> maps, float* __restrict__
           tc_commit(BAR(7 + s));
           tc_commit(BAR(13));
         };
-        ok &= WAIT(BAR(0), tt & 1, 12);
-        if (tt >= 2) ok &= WAIT(BAR(15 + ob), ((tt >> 1) - 1) & 1, 12);     // this accumulator has been written out
+        if (!WAIT(BAR(0), tt & 1, 12)) { ok = false; break; }
+        if (tt >= 2 && !WAIT(BAR(15 + ob), ((tt >> 1) - 1) & 1, 12)) { ok = false; break; }     // this accumulator has been written out
         issue_s(0);
         if (nblk > 1) issue_s(1);
         for (int j = 0; j < nblk; j++) {
@@ -348,8 +349,10 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Bounded waits that fail fast: the first wait that gives up records its role in the status word at once, and every
   // later wait of every role and CTA (they all poll that word) gives up after at most 64 polls, so a launch whose pipeline
-  // is stuck runs its loops to their end in milliseconds instead of polling each wait to its limit.  The roles keep
-  // their loop structure (the elementwise warps meet at named barriers, so no warp may leave early); what they compute
+  // is stuck ends in milliseconds instead of polling each wait to its limit.  The copy and MMA threads stop issuing at
+  // their first failed wait (arming a barrier whose previous phase has not completed is undefined), then let what
+  // they have in flight finish.  The elementwise warps keep their loop structure (they meet at named barriers, so no
+  // warp may leave early) and only touch tensor memory, count-256 barriers and in-range global rows; what they compute
   // after that point is discarded by the host (GN_ERR_TIMEOUT).
   const unsigned limit = spin_limit;
   auto WAIT = [&](uint32_t bar, uint32_t parity, int code) -> bool { if (mbar_wait(bar, parity, limit, status)) return true; atomicCAS(status, 0, code); return false; };
@@ -378,9 +381,9 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true; uint32_t g = 0;
-      for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+      for (int id = blockIdx.x, tt = 0; id < ntiles && ok; id += gridDim.x, tt++) {
         int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
-        if (tt > 0) ok &= WAIT(BAR(10), (tt - 1) & 1, 21);
+        if (tt > 0 && !WAIT(BAR(10), (tt - 1) & 1, 21)) { ok = false; break; }
         mbar_expect_tx(BAR(0), NR * ATB_R_BYTES);
         // maps: R1 = 0..2, R2 = 3..5, C1 = 6..8, C2 = 9..11, C3 = 12..14 (hi | bf16 copy | bf16 lo each)
         for (int o = 0; o < NR; o++) {
@@ -391,7 +394,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
         }
         for (int n = 0; n < nb; n++, g++) {
           const int row = (b0 + n) * 64;
-          if (g > 0) ok &= WAIT(BAR(2), (g - 1) & 1, 21);
+          if (g > 0 && !WAIT(BAR(2), (g - 1) & 1, 21)) { ok = false; break; }
           mbar_expect_tx(BAR(1), NR * ATB_C_BYTES);
           for (int o = 0; o < NR; o++) {
             const uint32_t base = smem_u32(sC + o * ATB_C_BYTES);
@@ -406,11 +409,11 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
   } else if (warp == 10) {
     if (lane == 0) {
       bool ok = true; uint32_t g = 0;
-      for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+      for (int id = blockIdx.x, tt = 0; id < ntiles && ok; id += gridDim.x, tt++) {
         int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
         for (int n = 0; n < nb; n++, g++) {
           const int col = (b0 + n) * 64;
-          if (g > 0) ok &= WAIT(BAR(4), (g - 1) & 1, 22);
+          if (g > 0 && !WAIT(BAR(4), (g - 1) & 1, 22)) { ok = false; break; }
           mbar_expect_tx(BAR(3), ATB_C_BYTES);
           for (int c = 0; c < 2; c++) tma_load_3d(smem_u32(sC3 + c * 8192), &maps.m[12], col + c * 32, 0, z, BAR(3));
           tma_load_3d(smem_u32(sC3 + 16384), &maps.m[13], col, 0, z, BAR(3));
@@ -423,12 +426,12 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
     if (lane == 0) {
       bool ok = true; uint32_t g0 = 0;
       constexpr uint32_t idesc = make_idesc(128, 64), idesc_bf = make_idesc_bf16(128, 64);
-      for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
+      for (int id = blockIdx.x, tt = 0; id < ntiles && ok; id += gridDim.x, tt++) {
         int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
         const uint32_t ab = tt & 1;
         auto issue_sd = [&](int n) {
           const uint32_t g = g0 + n, s = g & 1;
-          ok &= WAIT(BAR(1), g & 1, 23);
+          if (!ok || !WAIT(BAR(1), g & 1, 23)) { ok = false; return; }
           tc_fence_after();
 #pragma unroll
           for (int prod = 0; prod < NR; prod++) {
@@ -454,8 +457,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
         };
         auto issue_acc = [&](int n) {
           const uint32_t g = g0 + n, s = g & 1, u = g >> 1;
-          ok &= WAIT(BAR(7 + s), u & 1, 23);
-          ok &= WAIT(BAR(3), g & 1, 23);
+          if (!ok || !WAIT(BAR(7 + s), u & 1, 23) || !WAIT(BAR(3), g & 1, 23)) { ok = false; return; }
           tc_fence_after();
           const uint32_t cb = smem_u32(sC3);
           const uint32_t ph = tmem_base + (MODE == 2 ? ATB_COL_S : ATB_COL_DP) + s * 64, pl = tmem_base + ATB_COL_LO + s * 64,
@@ -474,8 +476,8 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<15> maps, const float* __res
           tc_commit(BAR(4));
           if (n == nb - 1) tc_commit(BAR(9));
         };
-        ok &= WAIT(BAR(0), tt & 1, 23);
-        if (tt >= 2) ok &= WAIT(BAR(11 + ab), ((tt >> 1) - 1) & 1, 23);     // this accumulator has been written out
+        if (!WAIT(BAR(0), tt & 1, 23)) { ok = false; break; }
+        if (tt >= 2 && !WAIT(BAR(11 + ab), ((tt >> 1) - 1) & 1, 23)) { ok = false; break; }     // this accumulator has been written out
         issue_sd(0);
         if (nb > 1) issue_sd(1);
         for (int n = 0; n < nb; n++) {

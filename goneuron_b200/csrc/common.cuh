@@ -44,6 +44,7 @@ struct Ctx {
   bool tc_ok = false;              // tcgen05 engine usable (driver entry point for tensor maps found)
   void* encode_tiled = nullptr;    // cuTensorMapEncodeTiled
   unsigned spin_limit = 1u << 24;  // polls per bounded device-side wait (gn_ctx_set_spin_limit)
+  bool tc_tail_split = true;       // left-over tiles of a short last round run as half tiles (GONEURON_CUDA_TC_TAIL_SPLIT=0 switches it off)
   int tc_force_bn = 0, tc_kslice = 0;   // experiment switches of the contraction engine (GONEURON_CUDA_TC_BN / _KSLICE); 0 = automatic
   void* tc_scratch = nullptr;      // operand planes of the contraction engine (TcScratch, owned)
   void* attn_scratch = nullptr;    // operand planes of the tcgen05 attention kernels (AttnTcScratch, owned)

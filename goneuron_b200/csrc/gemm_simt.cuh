@@ -27,6 +27,9 @@ struct GemmDesc {
   float alpha = 1.f;
   bool reuse_a_planes = false;                          // A is the same tensor as in the previous tensor-core call of this context
   const void* b_planes = nullptr;                       // tensor-core engine: prepared operand planes of B (a BfPlanes), e.g. of a weight matrix
+  const void* a_planes = nullptr;                       // ... and of A (written by the epilogue of the contraction that produced A)
+  const void* plane_out = nullptr;                      // tensor-core engine: a TcPlaneOut; the result is written as operand planes instead of fp32
+  float* a_rownorm = nullptr;                           // tensor-core engine: receives the L2 norm of every row of A (from the split pass)
   int batch1 = 1, batch2 = 1;                           // batch index b -> (b / batch2, b % batch2)
   long a_b1 = 0, a_b2 = 0, b_b1 = 0, b_b2 = 0, c_b1 = 0, c_b2 = 0, r_b1 = 0, r_b2 = 0;
   // Causal structure of attention: tiles that are entirely masked are never touched.

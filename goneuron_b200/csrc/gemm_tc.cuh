@@ -145,6 +145,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 
 
+// ------------------------------------------------------------------ splitting a value into operand planes
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&v);
+}
+// Power of two s that brings a row whose largest magnitude is mx into [2^14, 2^15) (fp16 overflows at 65504), and its
+// inverse.  s = 1 for a row of zeros (and for a row that holds an infinity or a NaN, which the products then carry on).
+__device__ __forceinline__ float row_scale(float mx, float* inv) {
+  if (!(mx > 0.f) || !(mx <= 3.0e38f)) { *inv = 1.f; return 1.f; }
+  int se = 14 - (((__float_as_int(mx) >> 23) & 0xff) - 127);
+  se = max(-100, min(100, se));
+  *inv = __int_as_float((127 - se) << 23); return __int_as_float((127 + se) << 23);
+}
+// (x s) -> (fp16(x s), fp16(x s - fp16(x s))) for two neighbouring elements, packed
+__device__ __forceinline__ void split2_pair(float a, float b, float s, uint32_t& p0, uint32_t& p1) {
+  a *= s; b *= s;
+  const __half2 h = __floats2half2_rn(a, b);
+  const float2 hf = __half22float2(h);
+  const __half2 l = __floats2half2_rn(a - hf.x, b - hf.y);
+  p0 = *reinterpret_cast<const uint32_t*>(&h); p1 = *reinterpret_cast<const uint32_t*>(&l);
+}
+
 // Output side of one launch.  Batched problems: problem z -> (z / batch2, z % batch2) selects the
 // output (and residual) sub-matrix; the operand planes of problem z are slice z of the 3-D tensor maps.
 struct TcParams {
@@ -154,6 +175,11 @@ struct TcParams {
   const float* isa = nullptr; const float* isb = nullptr;   // inverse row scales of the operand planes: [nbatch][M], [nbatch][N]
   unsigned spin_limit = TC_SPIN_LIMIT;                // polls per wait before the kernel gives up
   int nchw_P = 0;      // > 0: output row r = (sample r / P, position r % P) is stored as C[sample][col][position] (N channels of P positions)
+  // Plane output (out_p0 != null): the result is not stored as fp32 but directly as the operand planes of the next
+  // contraction (two fp16 planes [M][out_ldp] and an inverse scale per row), see TcPlaneOut.  C may then be null.
+  __half* out_p0 = nullptr; __half* out_p1 = nullptr; float* out_inv = nullptr; long out_ldp = 0;
+  const float* a_rownorm = nullptr; const int* b_maxabs = nullptr;     // the bound's factors: |row of A|_2 and max |entry of B (and bias)| as float bits
+  float* c_last = nullptr; int last_T = 0;                             // fp32 copy of the rows r with r % last_T == last_T - 1: c_last[(r / last_T) * N + col]
 };
 
 // Epilogue of one output tile, executed by one warp for its TMEM lane quadrant: one output row per thread
@@ -162,7 +188,7 @@ struct TcParams {
 // TMEM column offsets of the two accumulators of this tile (MERGED: there is only acc_main).
 template <int BN, bool MERGED>
 __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tmem_base, uint32_t acc_main, uint32_t acc_cross,
-                                                 int m0, int n0, int z, int quad, int lane, int nkb) {
+                                                 int m0, int n0, int z, int quad, int lane, int nkb, int bw) {
     const int z1 = z / ep.batch2, z2 = z % ep.batch2;
     float* C = ep.C + z1 * ep.c_b1 + z2 * ep.c_b2;
     const float* R = ep.R ? ep.R + z1 * ep.r_b1 + z2 * ep.r_b2 : nullptr;
@@ -174,7 +200,13 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
     const bool vec = (ep.flags & TC_FLAG_VEC) != 0;
     const float isa = row_ok ? ep.isa[(long)z * ep.M + row] : 1.f;       // 1 / (scale of this output row's A vector), a power of two
     const float* isb = ep.isb + (long)z * ep.N;
-    for (int c = 0; c < BN / 32; c++) {
+    float osc = 1.f;                                                       // plane output: this row's scale
+    if (ep.out_p0 && row_ok) {
+      const float an = ep.a_rownorm[row], bound = sqrtf(fmaf(an, an, 1.f)) * sqrtf((float)ep.K + 1.f) * __int_as_float(*ep.b_maxabs);
+      float oinv; osc = row_scale(bound, &oinv);
+      if (n0 == 0) ep.out_inv[row] = oinv;
+    }
+    for (int c = 0; c < bw / 32; c++) {                 // bw: width of this tile (BN, or BN / 2 for a half tile)
       const int col0 = n0 + c * 32;
       if (col0 >= ep.N) break;
       uint32_t r[32], q[MERGED ? 1 : 32];
@@ -206,7 +238,12 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
           v.z = acc(4 * j + 2) * isa * sv[j].z + bv.z + rv[j].z; v.w = acc(4 * j + 3) * isa * sv[j].w + bv.w + rv[j].w;
           if (ep.act == GN_ACT_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
           if (!(mv[j].x > 0.f)) v.x = 0.f; if (!(mv[j].y > 0.f)) v.y = 0.f; if (!(mv[j].z > 0.f)) v.z = 0.f; if (!(mv[j].w > 0.f)) v.w = 0.f;
-          *reinterpret_cast<float4*>(Crow + col0 + 4 * j) = v;
+          if (ep.out_p0) {
+            uint2 a, b; split2_pair(v.x, v.y, osc, a.x, b.x); split2_pair(v.z, v.w, osc, a.y, b.y);
+            const long o = (long)row * ep.out_ldp + col0 + 4 * j;
+            *reinterpret_cast<uint2*>(ep.out_p0 + o) = a; *reinterpret_cast<uint2*>(ep.out_p1 + o) = b;
+            if (ep.c_last && row % ep.last_T == ep.last_T - 1) *reinterpret_cast<float4*>(ep.c_last + (long)(row / ep.last_T) * ep.N + col0 + 4 * j) = v;
+          } else *reinterpret_cast<float4*>(Crow + col0 + 4 * j) = v;
         }
       } else {
         if (nkb > 0) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -232,7 +269,7 @@ template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
                        const __grid_constant__ CUtensorMap mapB0, const __grid_constant__ CUtensorMap mapB1,
-                       TcParams ep, int tiles_m, int tiles_n, int total_tiles) {
+                       TcParams ep, int tiles_m, int tiles_n, int total_tiles, int full_end, int n_half) {
   using Cfg = TcCfg<BN>;
   constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, BK = TC_BK;
   constexpr bool MERGED = Cfg::MERGED;
@@ -265,10 +302,20 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // tile -> coordinates and contraction range (identical in every role)
-  auto decode = [&](int tile, int& m0, int& n0, int& z, int& kb0, int& nkb) -> bool {
+  // Work list of this CTA (identical in every role): tiles blockIdx.x, + gridDim.x, ... below full_end; then, when the
+  // tiles left over would occupy at most half of the CTAs (n_half = twice their number, else 0), one HALF of a left-over
+  // tile each (BN / 2 columns), so that the last, short round costs about 0.6 instead of 1 tile time.
+  auto work = [&](int k, int& tile, int& half) -> bool {
+    const long t = (long)blockIdx.x + (long)k * gridDim.x;
+    if (t < full_end) { tile = (int)t; half = -1; return true; }
+    const long h = t - full_end;
+    if (h >= n_half) return false;
+    tile = full_end + (int)(h >> 1); half = (int)(h & 1); return true;
+  };
+  // tile -> coordinates and contraction range
+  auto decode = [&](int tile, int half, int& m0, int& n0, int& z, int& kb0, int& nkb) -> bool {
     const int nt = tile % tiles_n, q = tile / tiles_n, mt = q % tiles_m; z = q / tiles_m;
-    m0 = mt * TC_BM; n0 = nt * BN;
+    m0 = mt * TC_BM; n0 = nt * BN + (half > 0 ? BN / 2 : 0);
     if ((ep.flags & GEMM_SKIP_UPPER) && n0 > m0 + TC_BM - 1) return false;
     int kbeg = 0, kend = ep.K;
     if (ep.flags & GEMM_KBEG_AT_M0) kbeg = (m0 / BK) * BK;
@@ -283,17 +330,22 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
   if (warp == 0) {
     if (lane == 0) {
       bool ok = true; uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
+      int tile, half;
+      for (int w = 0; ok && work(w, tile, half); w++) {
+        int m0, n0, z, kb0, nkb; if (!decode(tile, half, m0, n0, z, kb0, nkb)) continue;
         for (int i = 0; i < nkb; i++, it++) {
           const uint32_t s = it % STAGES, use = it / STAGES; const int kc = (kb0 + i) * BK;
           if (use > 0 && !mbar_wait(empty0 + 8 * s, (use - 1) & 1, limit, abort_flag)) { ok = false; break; }
           const uint32_t base = smem_u32(smem + s * STAGE_BYTES), bar = full0 + 8 * s;
-          mbar_expect_tx(bar, STAGE_BYTES);
+          mbar_expect_tx(bar, half < 0 ? STAGE_BYTES : STAGE_BYTES - Cfg::B_PL);
           tma_load_3d(base, &mapA0, kc, m0, z, bar);
           tma_load_3d(base + OFF_A1, &mapA1, kc, m0, z, bar);
-          tma_load_3d(base + OFF_B0, &mapB0, kc, n0, z, bar);
+          tma_load_3d(base + OFF_B0, &mapB0, kc, n0, z, bar);          // the B copies are BN / 2 rows each
           tma_load_3d(base + OFF_B1, &mapB1, kc, n0, z, bar);
+          if (half < 0) {
+            tma_load_3d(base + OFF_B0 + Cfg::B_PL / 2, &mapB0, kc, n0 + BN / 2, z, bar);
+            tma_load_3d(base + OFF_B1 + Cfg::B_PL / 2, &mapB1, kc, n0 + BN / 2, z, bar);
+          }
         }
       }
       if (!ok && !*abort_flag) give_up(1);
@@ -302,9 +354,11 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true; uint32_t it = 0, lt = 0;
-      constexpr uint32_t idesc = make_idesc_f16(TC_BM, BN);
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
+      constexpr uint32_t idesc_full = make_idesc_f16(TC_BM, BN), idesc_half = make_idesc_f16(TC_BM, BN / 2);
+      int tile, half;
+      for (int w = 0; ok && work(w, tile, half); w++) {
+        int m0, n0, z, kb0, nkb; if (!decode(tile, half, m0, n0, z, kb0, nkb)) continue;
+        const uint32_t idesc = half < 0 ? idesc_full : idesc_half;
         const uint32_t slot = lt & 1, u = lt >> 1; lt++;
         if (!mbar_wait(tempty0 + 8 * slot, (u & 1) ^ 1, limit, abort_flag)) { ok = false; break; }     // slot drained by the epilogue (passes at once the first time)
         tc_fence_after();
@@ -341,15 +395,16 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
     }
   } else {
     const int quad = warp & 3; uint32_t lt = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-      int m0, n0, z, kb0, nkb; if (!decode(tile, m0, n0, z, kb0, nkb)) continue;
+    int tile, half;
+    for (int w = 0; work(w, tile, half); w++) {
+      int m0, n0, z, kb0, nkb; if (!decode(tile, half, m0, n0, z, kb0, nkb)) continue;
       const uint32_t slot = lt & 1, u = lt >> 1; lt++;
       int ok = 1;
       if (lane == 0) ok = mbar_wait(tfull0 + 8 * slot, u & 1, limit, abort_flag) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) { if (lane == 0 && !*abort_flag) give_up(3); break; }
       tc_fence_after();
-      tc_epilogue_tile<BN, MERGED>(ep, tmem_base, slot * SLOT_COLS, slot * SLOT_COLS + BN, m0, n0, z, quad, lane, nkb);
+      tc_epilogue_tile<BN, MERGED>(ep, tmem_base, slot * SLOT_COLS, slot * SLOT_COLS + BN, m0, n0, z, quad, lane, nkb, half < 0 ? BN : BN / 2);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * slot);
@@ -373,41 +428,26 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
 // s_c == 1 reads rows directly; s_r == 1 (the operand is the transpose of what is stored) goes through a shared tile.
 // Two fp16 planes per operand, p0 = fp16(x s), p1 = fp16(x s - p0), and the inverse 1/s of every plane row's scale.
 struct TcSrc { const float* p; long s_r, s_c, b1, b2; int batch2; };
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&v);
-}
-// Power of two s that brings a row whose largest magnitude is mx into [2^14, 2^15) (fp16 overflows at 65504), and its
-// inverse.  s = 1 for a row of zeros (and for a row that holds an infinity or a NaN, which the products then carry on).
-__device__ __forceinline__ float row_scale(float mx, float* inv) {
-  if (!(mx > 0.f) || !(mx <= 3.0e38f)) { *inv = 1.f; return 1.f; }
-  int se = 14 - (((__float_as_int(mx) >> 23) & 0xff) - 127);
-  se = max(-100, min(100, se));
-  *inv = __int_as_float((127 - se) << 23); return __int_as_float((127 + se) << 23);
-}
-// (x s) -> (fp16(x s), fp16(x s - fp16(x s))) for two neighbouring elements, packed
-__device__ __forceinline__ void split2_pair(float a, float b, float s, uint32_t& p0, uint32_t& p1) {
-  a *= s; b *= s;
-  const __half2 h = __floats2half2_rn(a, b);
-  const float2 hf = __half22float2(h);
-  const __half2 l = __floats2half2_rn(a - hf.x, b - hf.y);
-  p0 = *reinterpret_cast<const uint32_t*>(&h); p1 = *reinterpret_cast<const uint32_t*>(&l);
-}
 // One warp per plane row: first the row's largest magnitude (the row is read a second time from L1 / L2 afterwards),
 // then eight elements per lane and step (two 16-byte loads, one 16-byte store per plane).  blockIdx.y = problem index.
-__global__ void __launch_bounds__(256) split2_rows_kernel(TcSrc s, int rows, int cols, __half* __restrict__ p0, __half* __restrict__ p1, float* __restrict__ inv_scale, int ldp) {
+// `rownorm` (may be null): receives the L2 norm of every row (a factor of the bound of a plane-output contraction).
+__global__ void __launch_bounds__(256) split2_rows_kernel(TcSrc s, int rows, int cols, __half* __restrict__ p0, __half* __restrict__ p1, float* __restrict__ inv_scale, int ldp,
+                                                          float* __restrict__ rownorm) {
   const int z = blockIdx.y, lane = threadIdx.x & 31;
   const long r = (long)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (r >= rows) return;
   const float* src = s.p + (z / s.batch2) * s.b1 + (z % s.batch2) * s.b2 + r * s.s_r;
   const bool vec = (reinterpret_cast<uintptr_t>(src) & 15) == 0;
   const int cols8 = vec ? (cols & ~7) : 0;                  // columns handled with 16-byte loads
-  float mx = 0.f;
+  float mx = 0.f, sq = 0.f;
   for (int c = lane * 8; c < cols8; c += 256) {
     const float4 a = *reinterpret_cast<const float4*>(src + c), b = *reinterpret_cast<const float4*>(src + c + 4);
     mx = fmaxf(mx, fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))), fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w)))));
+    sq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w + b.x * b.x + b.y * b.y + b.z * b.z + b.w * b.w;
   }
-  for (int c = cols8 + lane; c < cols; c += 32) mx = fmaxf(mx, fabsf(src[c]));
+  for (int c = cols8 + lane; c < cols; c += 32) { const float v = src[c]; mx = fmaxf(mx, fabsf(v)); sq += v * v; }
   mx = warp_max(mx);
+  if (rownorm) { sq = warp_sum(sq); if (lane == 0) rownorm[(long)z * rows + r] = sqrtf(sq) * 1.0001f; }
   float inv; const float sc = row_scale(mx, &inv);
   if (lane == 0) inv_scale[(long)z * rows + r] = inv;
   const long o = ((long)z * rows + r) * ldp;
@@ -488,6 +528,14 @@ struct BfPlanes {
   __half* p0() const { return base; }
   __half* p1() const { return base + plane_elems(); }
 };
+// Where a contraction's result goes when it is only ever used as the A operand of another contraction (the FFN's hidden
+// activation and its gradient: half of all operand elements of a TransformerBlock).  A row's scale must be known before
+// its first element is written, and a tile sees only 256 of the row's columns, so the scale comes from a bound instead of
+// the row's maximum: |sum_k a_k b_k + bias| <= sqrt(|a|^2 + 1) * sqrt(K + 1) * max(|B|, |bias|) (Cauchy-Schwarz).  For
+// random-sign data the bound is about 8-16 times the row's actual maximum, i.e. 3-4 of the planes' 22 bits; it can never
+// be exceeded, so the fp16 planes cannot overflow.  `last`: fp32 copy of every sequence's last row (the only rows of
+// these tensors that are read as numbers: ReLU gate and weight-gradient input of the reference's last-token rule).
+struct TcPlaneOut { BfPlanes planes; const int* b_maxabs; float* last; int last_T; };
 inline int tc_ldp(int K) { return ((K + 7) / 8) * 8; }              // plane row stride: a multiple of 16 bytes for TMA
 inline size_t bf_plane_floats(long nbatch, long rows, long ldp) { return (size_t)nbatch * rows * ldp; }   // two fp16 planes = one float per element
 
@@ -518,6 +566,7 @@ inline void tc_init(Ctx* ctx) {
   ctx->encode_tiled = fn; ctx->tc_ok = true;
   if (const char* e = getenv("GONEURON_CUDA_TC_BN")) ctx->tc_force_bn = atoi(e);
   if (const char* e = getenv("GONEURON_CUDA_TC_KSLICE")) ctx->tc_kslice = atoi(e);
+  if (const char* e = getenv("GONEURON_CUDA_TC_TAIL_SPLIT")) ctx->tc_tail_split = atoi(e) != 0;
 }
 
 // fp32 plane, 32 columns (128 bytes, 128-byte swizzle) x box_rows per copy
@@ -551,10 +600,11 @@ inline int tc_make_map_bf16(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const
 }
 
 // Writes the planes and inverse row scales of an operand.  `mx` (only used by the transposing variant): nbatch * rows ints.
-inline int tc_split(Ctx* ctx, const TcSrc& src, const BfPlanes& p, int* mx) {
+inline int tc_split(Ctx* ctx, const TcSrc& src, const BfPlanes& p, int* mx, float* rownorm = nullptr) {
+  if (rownorm && src.s_c != 1) return fail(GN_ERR_UNSUPPORTED, "tc_split: row norms are only formed by the row-wise split");
   if (src.s_c == 1) {
     if (p.nbatch > 65535) return fail(GN_ERR_UNSUPPORTED, "tc_split: more than 65535 problems in a batch");
-    GN_LAUNCH(ctx, split2_rows_kernel, dim3(cdiv(p.rows, 8), p.nbatch), 256, 0, src, p.rows, p.K, p.p0(), p.p1(), p.inv_scale, p.ldp);
+    GN_LAUNCH(ctx, split2_rows_kernel, dim3(cdiv(p.rows, 8), p.nbatch), 256, 0, src, p.rows, p.K, p.p0(), p.p1(), p.inv_scale, p.ldp, rownorm);
   } else if (src.s_r == 1) {
     if (p.nbatch > 65535 || cdiv(p.rows, 64) > 65535 || cdiv(p.K, 256) > 65535) return fail(GN_ERR_UNSUPPORTED, "tc_split: operand too large for the transposing split");
     if (!mx) return fail(GN_ERR_INVALID_ARG, "tc_split: the transposing split needs a row-maximum buffer");
@@ -566,17 +616,27 @@ inline int tc_split(Ctx* ctx, const TcSrc& src, const BfPlanes& p, int* mx) {
   return check_launch("tc_split");
 }
 
+// Number of left-over tiles of the last round that are run as two half tiles each (0: none): only when they would keep at
+// most half of the CTAs busy, and not for the triangular products (their tiles differ in length anyway).
+inline long tc_tail_halves(Ctx* ctx, long total_tiles, int bn, int flags) {
+  if (!ctx->tc_tail_split || bn < 128 || total_tiles <= ctx->sm_count || (flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return 0;
+  const long left = total_tiles % ctx->sm_count;
+  return 2 * left <= ctx->sm_count ? left : 0;
+}
 template <int BN>
 inline int tc_launch_persist(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams& ep) {
   CUtensorMap mA0, mA1, mB0, mB1;
   constexpr CUtensorMapDataType F16 = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   GN_TRY(tc_make_map_bf16_raw(ctx, &mA0, A.p0(), A.K, A.rows, A.ldp, A.nbatch, A.koff, TC_BM, TC_BK, F16)); GN_TRY(tc_make_map_bf16_raw(ctx, &mA1, A.p1(), A.K, A.rows, A.ldp, A.nbatch, A.koff, TC_BM, TC_BK, F16));
-  GN_TRY(tc_make_map_bf16_raw(ctx, &mB0, B.p0(), B.K, B.rows, B.ldp, B.nbatch, B.koff, BN, TC_BK, F16)); GN_TRY(tc_make_map_bf16_raw(ctx, &mB1, B.p1(), B.K, B.rows, B.ldp, B.nbatch, B.koff, BN, TC_BK, F16));
+  // the B tile of a stage arrives as two copies of BN / 2 rows, so that a half tile (see the kernel's work list) is one of them
+  GN_TRY(tc_make_map_bf16_raw(ctx, &mB0, B.p0(), B.K, B.rows, B.ldp, B.nbatch, B.koff, BN / 2, TC_BK, F16)); GN_TRY(tc_make_map_bf16_raw(ctx, &mB1, B.p1(), B.K, B.rows, B.ldp, B.nbatch, B.koff, BN / 2, TC_BK, F16));
   const int tiles_m = cdiv(ep.M, TC_BM), tiles_n = cdiv(ep.N, BN); const long total = (long)tiles_m * tiles_n * A.nbatch;
   if (total > 0x7fffffffL) return fail(GN_ERR_UNSUPPORTED, "too many output tiles");
   const unsigned grid = (unsigned)std::min<long>(total, ctx->sm_count);
+  const long left = tc_tail_halves(ctx, total, BN, ep.flags);
+  const int full_end = (int)(total - left), n_half = (int)(2 * left);
   ProfScope prof(ctx);
-  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN>), grid, TC_THREADS, (TcCfg<BN>::SMEM_BYTES), mA0, mA1, mB0, mB1, ep, tiles_m, tiles_n, (int)total);
+  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN>), grid, TC_THREADS, (TcCfg<BN>::SMEM_BYTES), mA0, mA1, mB0, mB1, ep, tiles_m, tiles_n, (int)total, full_end, n_half);
   return check_launch("gemm_tc_persist");
 }
 // Output tile width for a problem: 64 for narrow outputs; 256 (three quarters of the shared-memory traffic per MMA
@@ -585,7 +645,12 @@ inline int tc_pick_bn(Ctx* ctx, int M, int N, long nbatch, int flags) {
   if (ctx->tc_force_bn == 64 || ctx->tc_force_bn == 128 || ctx->tc_force_bn == 256) return ctx->tc_force_bn;
   if (N <= 64) return 64;
   if (N <= 128 || (flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return 128;
-  auto cost = [&](int bn, double rate) { const double tiles = (double)cdiv(M, TC_BM) * cdiv(N, bn) * nbatch; const double waves = std::ceil(tiles / ctx->sm_count); return waves * bn / rate; };
+  auto cost = [&](int bn, double rate) {
+    const long tiles = (long)cdiv(M, TC_BM) * cdiv(N, bn) * nbatch;
+    double waves = std::ceil((double)tiles / ctx->sm_count);
+    if (tc_tail_halves(ctx, tiles, bn, flags) > 0) waves -= 0.38;       // a half tile costs about 0.62 of a whole one
+    return waves * bn / rate;
+  };
   return cost(256, 1.3) < cost(128, 1.0) ? 256 : 128;
 }
 // C[z] = A[z] * B[z]^T from prepared planes, one accumulator run over the whole contraction.
@@ -598,6 +663,11 @@ inline int tc_launch(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcPar
   if (ep.R) vec = vec && ep.ldr % 4 == 0 && ep.r_b1 % 4 == 0 && ep.r_b2 % 4 == 0 && a16(ep.R);
   if (ep.mask) vec = vec && ep.mask_ld % 4 == 0 && a16(ep.mask);
   if (ep.nchw_P > 0) { if (ep.R || A.nbatch != 1) return fail(GN_ERR_UNSUPPORTED, "tc_launch: NCHW store with a residual or a batch"); vec = false; }
+  if (ep.out_p0) {
+    if (!(ep.N % 4 == 0 && (!ep.bias || a16(ep.bias)) && a16(ep.isb) && (!ep.mask || (ep.mask_ld % 4 == 0 && a16(ep.mask))) && ep.out_ldp % 4 == 0 && (!ep.c_last || a16(ep.c_last))))
+      return fail(GN_ERR_INVALID_ARG, "tc_launch: plane output needs 16-byte aligned operands");
+    vec = true;
+  }
   if (vec) ep.flags |= TC_FLAG_VEC;
   {
     double by = 4.0 * ((double)ep.M + ep.N) * ep.K + 4.0 * (double)ep.M * ep.N * (ep.R ? 2 : 1);
@@ -616,6 +686,7 @@ inline int tc_launch(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcPar
 inline int tc_run_rows(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams& ep, int bn) {
   const int kslice = ctx->tc_kslice > 0 ? ctx->tc_kslice : (bn == 256 ? 2048 : 4096);
   if (ep.K <= kslice || (ep.flags & (GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return tc_launch(ctx, A, B, ep, bn);
+  if (ep.out_p0) return fail(GN_ERR_UNSUPPORTED, "a contraction that writes operand planes must fit one accumulator run (K = %d)", ep.K);
   for (int k0 = 0; k0 < ep.K; k0 += kslice) {
     const int kl = std::min(kslice, ep.K - k0); const bool first = k0 == 0, last = k0 + kl >= ep.K;
     BfPlanes As = A, Bs = B; As.koff = A.koff + k0; As.K = kl; Bs.koff = B.koff + k0; Bs.K = kl;
@@ -639,7 +710,7 @@ inline int tc_run(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams
 // GPUs.  Instead all registered matrices are split once per parameter update, both orientations from one read, by two
 // launches in all: the matrices get ONE power-of-two scale each (their entries are of similar size, unlike activation
 // rows), found by wplanes_max_kernel, and wplanes_split_kernel writes every 64 x 64 tile as stored and transposed.
-struct WPlaneJob { const float* src; int out, in, ldp_r, ldp_c; __half *r0, *r1, *c0, *c1; float *inv_r, *inv_c; int tile0, tiles_in; };
+struct WPlaneJob { const float* src; const float* bias; int out, in, ldp_r, ldp_c; __half *r0, *r1, *c0, *c1; float *inv_r, *inv_c; int tile0, tiles_in; };
 __device__ __forceinline__ int wplane_find(const WPlaneJob* jobs, int njobs, int tile) {
   int lo = 0, hi = njobs - 1;
   while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (jobs[mid].tile0 <= tile) lo = mid; else hi = mid - 1; }
@@ -651,6 +722,7 @@ __global__ void __launch_bounds__(256) wplanes_max_kernel(const WPlaneJob* __res
   const int t = blockIdx.x - jb.tile0, r0 = (t / jb.tiles_in) * 64, c0 = (t % jb.tiles_in) * 64;
   float m = 0.f;
   for (int e = threadIdx.x; e < 4096; e += 256) { const int r = r0 + (e >> 6), c = c0 + (e & 63); if (r < jb.out && c < jb.in) m = fmaxf(m, fabsf(jb.src[(long)r * jb.in + c])); }
+  if (jb.bias && c0 == 0 && threadIdx.x < 64 && r0 + (int)threadIdx.x < jb.out) m = fmaxf(m, fabsf(jb.bias[r0 + threadIdx.x]));      // the layer's biases count towards the maximum (bounds of plane-output contractions)
   m = block_max(m, red);
   if (threadIdx.x == 0) { if (!(m <= 3.0e38f)) m = 3.4e38f; atomicMax(mx + j, __float_as_int(m)); }
 }
@@ -682,7 +754,7 @@ __global__ void __launch_bounds__(256) wplanes_split_kernel(const WPlaneJob* __r
   }
 }
 // Host side of the table: one entry per registered matrix, looked up by the matrix's device address.
-struct WeightPlaneEntry { const float* src; int out, in; BfPlanes rows, cols; };
+struct WeightPlaneEntry { const float* src; int out, in; BfPlanes rows, cols; const float* bias = nullptr; const int* maxabs = nullptr; };
 struct WeightPlaneTable {
   std::vector<WeightPlaneEntry> e; DevBuf planes, scales, mx, jobs; int total_tiles = 0; bool dirty = true;
   const WeightPlaneEntry* find(const float* p) const { for (auto& x : e) if (x.src == p) return &x; return nullptr; }
@@ -703,7 +775,8 @@ inline int wplanes_build(Ctx* ctx, WeightPlaneTable& t, const std::vector<Weight
     const int lr = tc_ldp(x.in), lc = tc_ldp(x.out);
     x.rows = BfPlanes{hp, sp, x.out, x.in, lr, 1}; hp += 2 * (size_t)x.out * lr; sp += (x.out + 3) & ~3;
     x.cols = BfPlanes{hp, sp, x.in, x.out, lc, 1}; hp += 2 * (size_t)x.in * lc; sp += (x.in + 3) & ~3;
-    WPlaneJob jb{x.src, x.out, x.in, lr, lc, x.rows.p0(), x.rows.p1(), x.cols.p0(), x.cols.p1(), x.rows.inv_scale, x.cols.inv_scale, tiles, (int)cdiv(x.in, 64)};
+    x.maxabs = reinterpret_cast<const int*>(t.mx.p) + jobs.size();
+    WPlaneJob jb{x.src, x.bias, x.out, x.in, lr, lc, x.rows.p0(), x.rows.p1(), x.cols.p0(), x.cols.p1(), x.rows.inv_scale, x.cols.inv_scale, tiles, (int)cdiv(x.in, 64)};
     tiles += (int)cdiv(x.out, 64) * (int)cdiv(x.in, 64); jobs.push_back(jb);
   }
   t.total_tiles = tiles;
@@ -723,10 +796,11 @@ inline int wplanes_refresh(Ctx* ctx, WeightPlaneTable& t) {
   t.dirty = false; return check_launch("wplanes_refresh");
 }
 // Prepared planes for B of this contraction, if B is a registered matrix used in one of its two orientations.
-inline const BfPlanes* wplanes_lookup(Ctx* ctx, const GemmDesc& g) {
+inline const BfPlanes* wplanes_lookup(Ctx* ctx, const GemmDesc& g, const WeightPlaneEntry** entry = nullptr) {
   const WeightPlaneTable* t = static_cast<const WeightPlaneTable*>(ctx->weight_planes);
   if (!t || t->dirty || g.batch1 * g.batch2 != 1) return nullptr;
   const WeightPlaneEntry* x = t->find(g.B); if (!x) return nullptr;
+  if (entry) *entry = x;
   if (g.sb_k == 1 && g.sb_n == x->in && g.N == x->out && g.K == x->in) return &x->rows;     // B(k, n) = W[n, k]
   if (g.sb_n == 1 && g.sb_k == x->in && g.N == x->in && g.K == x->out) return &x->cols;     // B(k, n) = W[k, n]
   return nullptr;
@@ -756,10 +830,13 @@ inline int gemm_tc(Ctx* ctx, const GemmDesc& g) {
   BfPlanes A, B; GN_TRY(tc_planes(ctx, 0, nb, g.M, g.K, &A)); GN_TRY(tc_planes(ctx, 1, nb, g.N, g.K, &B));
   int* mx = tc_rowmax_buf(ctx);
   sc.last_a = (sc.a.p == pa && sc.sa.p == psa) ? last_a : nullptr;                          // still valid unless a buffer was replaced
-  if (g.reuse_a_planes && nb == 1 && sc.last_a == g.A && sc.last_m == g.M && sc.last_k == g.K && sc.last_ld == g.sa_m && g.sa_k == 1) {
+  if (g.a_planes) {
+    A = *static_cast<const BfPlanes*>(g.a_planes);
+    if (A.rows != g.M || A.K != g.K || A.nbatch != nb) return fail(GN_ERR_INVALID_ARG, "gemm_tc: prepared planes of A do not match the contraction");
+  } else if (!g.a_rownorm && g.reuse_a_planes && nb == 1 && sc.last_a == g.A && sc.last_m == g.M && sc.last_k == g.K && sc.last_ld == g.sa_m && g.sa_k == 1) {
     // same tensor as the previous call (the Q, K and V projections share their input): planes still valid
   } else {
-    GN_TRY(tc_split(ctx, TcSrc{g.A, g.sa_m, g.sa_k, g.a_b1, g.a_b2, g.batch2}, A, mx));
+    GN_TRY(tc_split(ctx, TcSrc{g.A, g.sa_m, g.sa_k, g.a_b1, g.a_b2, g.batch2}, A, mx, g.a_rownorm));
     sc.last_a = (nb == 1 && g.sa_k == 1) ? g.A : nullptr; sc.last_m = g.M; sc.last_k = g.K; sc.last_ld = g.sa_m;
   }
   if (g.b_planes) {
@@ -767,6 +844,13 @@ inline int gemm_tc(Ctx* ctx, const GemmDesc& g) {
     if (B.rows != g.N || B.K != g.K || B.nbatch != nb) return fail(GN_ERR_INVALID_ARG, "gemm_tc: prepared planes of B do not match the contraction");
   } else GN_TRY(tc_split(ctx, TcSrc{g.B, g.sb_n, g.sb_k, g.b_b1, g.b_b2, g.batch2}, B, mx));
   TcParams ep{g.C, g.ldc, g.c_b1, g.c_b2, g.bias, g.R, g.ldr, g.r_b1, g.r_b2, g.act, g.M, g.N, g.K, g.batch2, g.flags, ctx->d_status, g.mask, g.mask_ld, g.mask_group};
+  if (g.plane_out) {
+    const TcPlaneOut& po = *static_cast<const TcPlaneOut*>(g.plane_out);
+    if (nb != 1 || g.R || !g.a_rownorm || !po.b_maxabs || g.N % 32 || po.planes.rows != g.M || po.planes.K != g.N || (g.flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0)))
+      return fail(GN_ERR_INVALID_ARG, "gemm_tc: this contraction cannot write its result as operand planes");
+    ep.out_p0 = po.planes.p0(); ep.out_p1 = po.planes.p1(); ep.out_inv = po.planes.inv_scale; ep.out_ldp = po.planes.ldp;
+    ep.a_rownorm = g.a_rownorm; ep.b_maxabs = po.b_maxabs; ep.c_last = po.last; ep.last_T = po.last_T > 0 ? po.last_T : 1;
+  }
   return tc_run(ctx, A, B, ep);
 }
 

@@ -63,6 +63,9 @@ static int gemm_tn(Ctx* ctx, int R, int N, int K, const float* dZ, long ldz, con
   g.C = gW; g.ldc = K; return gemm(ctx, g);
 }
 
+struct LayerRT;
+static bool ffn_planes_possible(Ctx* ctx, const LayerRT& l, int N, const float* w1, const float* w2);
+
 // ------------------------------------------------------------------ model
 struct LayerRT {
   gn_layer_desc d{};
@@ -74,6 +77,8 @@ struct LayerRT {
   DevBuf att_m, att_l, att_d;          // fused attention: per-row softmax maximum, sum, and dO.O  [batch*heads*T]
   DevBuf gate, up, zlast, rope;        // TransformerBlock variants: SwiGLU projections [tokens, ff]; GELU: last token's pre-activation [batch, ff]; cos | sin table
   int ff_act = GN_ACT_RELU; bool rms = false, use_rope = false;
+  DevBuf mid_inv, mid_last;            // FFN hidden activation kept as operand planes (in `mid`): row scales [tokens], fp32 last-token rows [batch, ff]
+  bool mid_is_planes = false;          // set by the forward pass, read by the backward pass
   DevBuf pre_i, c_all, h_all, dgate;   // LSTM
   DevBuf idx;                          // int32 payload: MaxPool argmax / embedding token ids
   const float* fin = nullptr;          // input of the last forward call (device pointer, not owned)
@@ -111,7 +116,7 @@ struct gn_model {
 
 namespace gn {
 
-enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_NFF2, S_NFF3, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_NFF2, S_NFF3, S_RN, S_NFFI, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
 
 static int ensure(gn_model* m, int slot, size_t n, float** out) {
   if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
@@ -250,6 +255,7 @@ static int alloc_activations(gn_model* m, int cap) {
         GN_TRY(l.q.alloc(nd)); GN_TRY(l.k.alloc(nd)); GN_TRY(l.v.alloc(nd)); GN_TRY(l.att.alloc(nd)); GN_TRY(l.r1.alloc(nd)); GN_TRY(l.n1.alloc(nd));
         GN_TRY(l.mid.alloc(nf)); GN_TRY(l.r2.alloc(nd)); GN_TRY(l.out.alloc(nd)); GN_TRY(l.stat.alloc(4 * nt));
         GN_TRY(l.att_m.alloc(nt * d.heads)); GN_TRY(l.att_l.alloc(nt * d.heads)); GN_TRY(l.att_d.alloc(nt * d.heads));
+        GN_TRY(l.mid_inv.alloc(nt)); GN_TRY(l.mid_last.alloc(c * d.ff_dim));
         if (l.ff_act == GN_ACT_SILU) { GN_TRY(l.gate.alloc(nf)); GN_TRY(l.up.alloc(nf)); }
         if (l.ff_act == GN_ACT_GELU) GN_TRY(l.zlast.alloc(c * d.ff_dim));
         break; }
@@ -518,7 +524,16 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         {   // feed-forward: ff1 -> ff2, res2 = norm1 + ff
           GemmDesc g1; g1.M = N; g1.N = F; g1.K = D; g1.A = l.n1.p; g1.sa_m = D; g1.sa_k = 1; g1.B = bp.w1; g1.sb_k = 1; g1.sb_n = D; g1.C = l.mid.p; g1.ldc = F; g1.bias = bp.b1;
           const long nf = (long)N * F;
-          if (l.ff_act == GN_ACT_RELU) { g1.act = GN_ACT_RELU; GN_TRY(gemm(ctx, g1)); }
+          BfPlanes midp{reinterpret_cast<__half*>(l.mid.p), l.mid_inv.p, N, F, F, 1};
+          l.mid_is_planes = ffn_planes_possible(ctx, l, N, bp.w1, bp.w2);
+          if (l.mid_is_planes) {
+            // the hidden activation is only ever the A operand of ff2 (and, for its last-token rows, a gate and a weight-gradient
+            // input): the epilogue writes it as operand planes into the same buffer, no fp32 copy and no split pass
+            const WeightPlaneEntry* we = nullptr; wplanes_lookup(ctx, g1, &we);
+            float* rn; GN_TRY(ensure(m, S_RN, (size_t)N, &rn));
+            TcPlaneOut po{midp, we->maxabs, l.mid_last.p, T};
+            g1.act = GN_ACT_RELU; g1.C = nullptr; g1.plane_out = &po; g1.a_rownorm = rn; GN_TRY(gemm(ctx, g1));
+          } else if (l.ff_act == GN_ACT_RELU) { g1.act = GN_ACT_RELU; GN_TRY(gemm(ctx, g1)); }
           else if (l.ff_act == GN_ACT_GELU) {
             // the pre-activation of every sequence's last token is what the backward pass differentiates at (layer.go:563-567)
             GN_TRY(gemm(ctx, g1));
@@ -530,6 +545,7 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
             GN_LAUNCH(ctx, swiglu_fwd_kernel, ew_grid(ctx, nf), 256, 0, (const float*)l.gate.p, (const float*)l.up.p, l.mid.p, nf);
           }
           GemmDesc g2; g2.M = N; g2.N = D; g2.K = F; g2.A = l.mid.p; g2.sa_m = F; g2.sa_k = 1; g2.B = bp.w2; g2.sb_k = 1; g2.sb_n = F; g2.C = l.r2.p; g2.ldc = D; g2.bias = bp.b2; g2.R = l.n1.p; g2.ldr = D;
+          if (l.mid_is_planes) g2.a_planes = &midp;
           GN_TRY(gemm(ctx, g2));
         }
         GN_TRY(block_norm_forward(ctx, l.rms, l.r2.p, bp.g2, bp.be2, l.out.p, st + 2 * N, (long)N, D));
@@ -597,13 +613,32 @@ static int layernorm_backward(gn_model* m, const float* g, const float* x, const
 // ---------------------------------------------------------------- backward
 // Gradient of one inner Dense of a TransformerBlock at batch level:
 //   gb = sum over all tokens of dz ; gW = Delta^T * X_last with Delta[s] = sum_t dz[s,t], X_last[s] = x[s,T-1]
-static int inner_dense_param_grads(gn_model* m, const float* dz, int B, int T, int out, const float* x, int in, float* gW, float* gb) {
+// `x_last` != null: the last-token inputs as a dense [B, in] array instead of a strided view of x; `dz_planes` != null: dz
+// exists only as operand planes.
+static int inner_dense_param_grads(gn_model* m, const float* dz, int B, int T, int out, const float* x, int in, float* gW, float* gb,
+                                   const float* x_last = nullptr, const BfPlanes* dz_planes = nullptr) {
   Ctx* ctx = &m->ctx->c; float* delta; GN_TRY(ensure(m, S_DELTA, (size_t)B * out, &delta));
-  if (out % 4 == 0 && ((reinterpret_cast<uintptr_t>(dz) | reinterpret_cast<uintptr_t>(delta)) & 15) == 0)
+  if (dz_planes) GN_LAUNCH(ctx, token_sum_planes_kernel, dim3(cdiv(out, 128), B), dim3(32, 8), 0, (const __half*)dz_planes->p0(), (const __half*)dz_planes->p1(), (const float*)dz_planes->inv_scale, (long)dz_planes->ldp, T, out, delta);
+  else if (out % 4 == 0 && ((reinterpret_cast<uintptr_t>(dz) | reinterpret_cast<uintptr_t>(delta)) & 15) == 0)
     GN_LAUNCH(ctx, token_sum_vec_kernel, dim3(cdiv(out, 128), B), dim3(32, 8), 0, dz, T, out, delta);
   else GN_LAUNCH(ctx, token_sum_kernel, dim3(cdiv(out, 128), B), dim3(128, 4), 0, dz, T, out, delta);
   GN_TRY(colsum(m, delta, out, B, out, gb, false));
+  if (x_last) return gemm_tn(ctx, B, out, in, delta, out, x_last, (long)in, gW);
   return gemm_tn(ctx, B, out, in, delta, out, x + (long)(T - 1) * in, (long)T * in, gW);
+}
+// Can the FFN's hidden activation (and its gradient) of this block live as operand planes only?  The two contractions on
+// either side must both run on the tensor-core engine with prepared weight planes, and the plane-writing epilogue's shape
+// rules must hold.
+static bool ffn_planes_possible(Ctx* ctx, const LayerRT& l, int N, const float* w1, const float* w2) {
+  static const bool off = getenv("GONEURON_CUDA_NO_PLANE_OUTPUT") != nullptr;
+  const gn_layer_desc& d = l.d; const int D = d.dim, F = d.ff_dim;
+  if (off || force_simt_engine() || l.ff_act != GN_ACT_RELU || F % 32 || D % 32 || D > 2048 || F % 4) return false;
+  if ((reinterpret_cast<uintptr_t>(w1 + (long)D * F) & 15) != 0) return false;                                 // ff1's bias is read with 16-byte loads
+  GemmDesc a; a.M = N; a.N = F; a.K = D; a.B = w1; a.sb_k = 1; a.sb_n = D; a.sa_k = 1; a.sa_m = D;            // n1 W1^T        -> planes
+  GemmDesc b; b.M = N; b.N = F; b.K = D; b.B = w2; b.sb_k = F; b.sb_n = 1; b.sa_k = 1; b.sa_m = D;            // dR2 W2         -> planes
+  GemmDesc c; c.M = N; c.N = D; c.K = F; c.B = w2; c.sb_k = 1; c.sb_n = F; c.sa_k = 1; c.sa_m = F;            // planes W2^T    (consumer, forward)
+  GemmDesc e; e.M = N; e.N = D; e.K = F; e.B = w1; e.sb_k = D; e.sb_n = 1; e.sa_k = 1; e.sa_m = F;            // planes W1      (consumer, backward)
+  return gemm_tc_eligible(ctx, a) && gemm_tc_eligible(ctx, b) && gemm_tc_eligible(ctx, c) && gemm_tc_eligible(ctx, e) && wplanes_lookup(ctx, a) && wplanes_lookup(ctx, b);
 }
 
 static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, const float* gout, float* dx) {
@@ -618,19 +653,31 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
   // norm 2
   GN_TRY(block_norm_backward(m, l.rms, gout, l.r2.p, bp.g2, st + 2 * N, dR2, (float*)gp.g2, (float*)gp.be2, (long)N, D));
   // ff2 then ff1, token by token in the reference (transformer.go:1238-1250)
-  GN_TRY(inner_dense_param_grads(m, dR2, B, T, D, l.mid.p, F, (float*)gp.w2, (float*)gp.b2));
+  GN_TRY(inner_dense_param_grads(m, dR2, B, T, D, l.mid.p, F, (float*)gp.w2, (float*)gp.b2, l.mid_is_planes ? l.mid_last.p : nullptr));
   {
     // dM[s,t,:] = W2^T dR2[s,t,:]; with a ReLU first layer gated by the ReLU pattern of the LAST token of sequence s (fused into the epilogue)
     GemmDesc g; g.M = N; g.N = F; g.K = D; g.A = dR2; g.sa_m = D; g.sa_k = 1; g.B = bp.w2; g.sb_k = F; g.sb_n = 1; g.C = dM; g.ldc = F;
-    if (l.ff_act == GN_ACT_RELU) { g.mask = l.mid.p + (long)(T - 1) * F; g.mask_ld = (long)T * F; g.mask_group = T; }
-    GN_TRY(gemm(ctx, g));
+    if (l.mid_is_planes) { g.mask = l.mid_last.p; g.mask_ld = F; g.mask_group = T; }
+    else if (l.ff_act == GN_ACT_RELU) { g.mask = l.mid.p + (long)(T - 1) * F; g.mask_ld = (long)T * F; g.mask_group = T; }
     const long nf = (long)N * F;
-    if (l.ff_act != GN_ACT_SILU) {
+    if (l.mid_is_planes) {
+      // the gradient of the hidden activation likewise only feeds a token sum and the next contraction: planes only
+      const WeightPlaneEntry* we = nullptr; wplanes_lookup(ctx, g, &we);
+      float *rn, *dinv; GN_TRY(ensure(m, S_RN, (size_t)N, &rn)); GN_TRY(ensure(m, S_NFFI, (size_t)N, &dinv));
+      BfPlanes dMp{reinterpret_cast<__half*>(dM), dinv, N, F, F, 1};
+      TcPlaneOut po{dMp, we->maxabs, nullptr, 1};
+      g.C = nullptr; g.plane_out = &po; g.a_rownorm = rn; GN_TRY(gemm(ctx, g));
+      GemmDesc h; h.M = N; h.N = D; h.K = F; h.A = dM; h.sa_m = F; h.sa_k = 1; h.B = bp.w1; h.sb_k = D; h.sb_n = 1; h.C = comb; h.ldc = D; h.R = dR2; h.ldr = D; h.a_planes = &dMp;
+      GN_TRY(inner_dense_param_grads(m, nullptr, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1, nullptr, &dMp));
+      GN_TRY(gemm(ctx, h));
+    } else if (l.ff_act != GN_ACT_SILU) {
+      GN_TRY(gemm(ctx, g));
       if (l.ff_act == GN_ACT_GELU) GN_LAUNCH(ctx, scale_by_last_deriv_kernel, ew_grid(ctx, nf), 256, 0, dM, (const float*)l.zlast.p, T, F, nf, (int)GN_ACT_GELU);
       GemmDesc h; h.M = N; h.N = D; h.K = F; h.A = dM; h.sa_m = F; h.sa_k = 1; h.B = bp.w1; h.sb_k = D; h.sb_n = 1; h.C = comb; h.ldc = D; h.R = dR2; h.ldr = D;   // combined = gradRes2 + W1^T dz1
       GN_TRY(inner_dense_param_grads(m, dM, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1));
       GN_TRY(gemm(ctx, h));
     } else {
+      GN_TRY(gemm(ctx, g));
       // SwiGLU keeps every call's state and pops it in reverse (swiglu.go:186-201): token t's gradient meets token T-1-t's
       // input and projections.  The deltas are written at the partner's row, so the weight gradients are plain contractions
       // over all tokens with the layer's inputs; the input gradient comes out in partner order and is reversed when it is
@@ -1136,7 +1183,10 @@ int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int 
   if (ctx->c.tc_ok && !force_simt_engine() && !getenv("GONEURON_CUDA_NO_WEIGHT_PLANES")) {
     // weight matrices large enough to run on the tensor-core engine get prepared operand planes (both orientations)
     std::vector<WeightPlaneEntry> mats;
-    auto add = [&](int64_t off, int out, int in) { if ((double)out * in >= 64.0 * 64.0) mats.push_back(WeightPlaneEntry{m->params.p + off, out, in, {}, {}}); };
+    auto add = [&](int64_t off, int out, int in, bool has_bias = true) {
+      if ((double)out * in < 64.0 * 64.0) return;
+      WeightPlaneEntry e{m->params.p + off, out, in, {}, {}}; e.bias = has_bias ? m->params.p + off + (int64_t)out * in : nullptr; mats.push_back(e);
+    };
     for (auto& l : m->L) {
       const gn_layer_desc& d = l.d;
       if (d.kind == GN_LAYER_DENSE) add(l.p_off, d.out_size, d.in_size);
@@ -1144,7 +1194,7 @@ int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int 
         const int64_t dd = (int64_t)d.dim * d.dim + d.dim; int64_t o = l.p_off;
         for (int k = 0; k < 4; k++) { add(o, d.dim, d.dim); o += dd; }
         o += (l.rms ? 2 : 4) * (int64_t)d.dim;
-        if (l.ff_act == GN_ACT_SILU) { add(o, d.ff_dim, d.dim); add(o + (int64_t)d.dim * d.ff_dim, d.ff_dim, d.dim); o += 2 * (int64_t)d.dim * d.ff_dim; }
+        if (l.ff_act == GN_ACT_SILU) { add(o, d.ff_dim, d.dim, false); add(o + (int64_t)d.dim * d.ff_dim, d.ff_dim, d.dim, false); o += 2 * (int64_t)d.dim * d.ff_dim; }
         else { add(o, d.ff_dim, d.dim); o += (int64_t)d.dim * d.ff_dim + d.ff_dim; }
         add(o, d.dim, d.ff_dim);
       }

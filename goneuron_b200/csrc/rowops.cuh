@@ -4,6 +4,7 @@
 // samples and tokens, and the fused Adam update.  All are coalesced, 128-bit where the
 // shape allows, and reduce with warp shuffles.
 #pragma once
+#include <cuda_fp16.h>
 #include "common.cuh"
 
 namespace gn {
@@ -156,6 +157,33 @@ __global__ void __launch_bounds__(256) token_sum_vec_kernel(const float* __restr
       s.x += (a0.x + a1.x) + (a2.x + a3.x); s.y += (a0.y + a1.y) + (a2.y + a3.y); s.z += (a0.z + a1.z) + (a2.z + a3.z); s.w += (a0.w + a1.w) + (a2.w + a3.w);
     }
     for (; t < T; t += 8) { const float4 a = *reinterpret_cast<const float4*>(p + (long)t * C); s.x += a.x; s.y += a.y; s.z += a.z; s.w += a.w; }
+  }
+  part[grp][threadIdx.x] = s;
+  __syncthreads();
+  if (grp == 0 && c < C) {
+    float4 r = part[0][threadIdx.x];
+#pragma unroll
+    for (int g = 1; g < 8; g++) { const float4 q = part[g][threadIdx.x]; r.x += q.x; r.y += q.y; r.z += q.z; r.w += q.w; }
+    *reinterpret_cast<float4*>(out + (long)blockIdx.y * C + c) = r;
+  }
+}
+
+// The same sum over a tensor that exists only as operand planes (two fp16 planes and an inverse scale per row, written by a
+// contraction's epilogue): element = (p0 + p1) * inv_scale[row].  Same block shape as above: 4 columns per thread.
+__global__ void __launch_bounds__(256) token_sum_planes_kernel(const __half* __restrict__ p0, const __half* __restrict__ p1, const float* __restrict__ inv, long ldp,
+                                                               int T, int C, float* __restrict__ out) {
+  __shared__ float4 part[8][32];
+  const int c = (blockIdx.x * 32 + threadIdx.x) * 4, grp = threadIdx.y;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (c < C) {
+    const long row0 = (long)blockIdx.y * T;
+    for (int t = grp; t < T; t += 8) {
+      const long o = (row0 + t) * ldp + c; const float is = inv[row0 + t];
+      const uint2 a = *reinterpret_cast<const uint2*>(p0 + o), b = *reinterpret_cast<const uint2*>(p1 + o);
+      const float2 a0 = __half22float2(*reinterpret_cast<const __half2*>(&a.x)), a1 = __half22float2(*reinterpret_cast<const __half2*>(&a.y));
+      const float2 b0 = __half22float2(*reinterpret_cast<const __half2*>(&b.x)), b1 = __half22float2(*reinterpret_cast<const __half2*>(&b.y));
+      s.x += (a0.x + b0.x) * is; s.y += (a0.y + b0.y) * is; s.z += (a1.x + b1.x) * is; s.w += (a1.y + b1.y) * is;
+    }
   }
   part[grp][threadIdx.x] = s;
   __syncthreads();

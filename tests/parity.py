@@ -65,11 +65,21 @@ def assert_grads_close(layers, got, ref, tol=TOL, floor=None):
     `floor` (the literal-fp32 CPU path's own distance from the double twin) loosens the bound for tensors
     whose value the reference itself only resolves to fp32 cancellation noise."""
     worst, loosened = [], []
+    gmax = float(np.max(np.abs(ref))) if ref.size else 0.0
     for name, s, e in tensor_slices(layers):
         err = norm_err(got[s:e], ref[s:e])
         lim = tol
         if floor is not None:
-            lim = max(tol, 4.0 * norm_err(floor[s:e], ref[s:e]))
+            ferr = norm_err(floor[s:e], ref[s:e])
+            if ferr >= 1.0:
+                # The tensor is zero in exact arithmetic (the double twin holds 1e-16-sized residue) and the literal fp32
+                # path has not one correct digit of it: what any fp32 implementation returns here is the rounding noise
+                # of the terms that cancel.  It must be small against the gradient as a whole, nothing more can be asked.
+                err = float(np.max(np.abs(got[s:e]))) / gmax if gmax > 0 else 0.0
+                print(f"zero in exact arithmetic: {name}: largest entry {err:.3e} of the largest gradient entry (literal fp32 path: {float(np.max(np.abs(floor[s:e]))) / gmax:.3e})")
+                worst.append((err / tol, name, err, tol))
+                continue
+            lim = max(tol, 4.0 * ferr)
         if lim > tol:
             loosened.append((name, err, lim))
         worst.append((err / lim, name, err, lim))

@@ -28,7 +28,9 @@ def _gemm(device, engine, A, B, bias):
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 32), (128, 256, 64), (256, 512, 256), (300, 520, 100), (129, 70, 70), (1, 8, 5),
                                    (2048, 1024, 1024), (4096, 256, 4096),
-                                   (256, 384, 70000)])          # a weight-gradient shape: contraction over all tokens, cut into slices
+                                   (256, 384, 70000),           # a weight-gradient shape: contraction over all tokens, cut into slices
+                                   # more tiles than SMs with a short last round: its tiles run as half tiles (256- and 128-wide tilings)
+                                   (25600, 256, 96), (12800, 500, 64), (25600, 128, 96), (5760, 1024, 128)])
 def test_tc_gemm_matches_fp64(device, M, N, K):
     rng = np.random.default_rng(M * 7 + N * 3 + K)
     A = rng.standard_normal((M, K)).astype(np.float32)
