@@ -147,8 +147,53 @@ inline bool gemm_skinny_ok(const GemmDesc& g) {
          (g.act == GN_ACT_LINEAR || g.act == GN_ACT_RELU);
 }
 
+// Sum of at most 64 outer products: C[M,N] = sum_k A(m,k) B(k,n) with both operands stored contraction-major (A(m,k) at
+// A[k * sa_k + m], B(k,n) at B[k * sb_k + n]) -- the weight gradient of an inner Dense layer, which only sees one input
+// row per sample (layer.go:591-625), when the batch (or a rank's shard of it) is small.  Every block stages both operand
+// panels of its 64 x 64 output tile in shared memory once; each thread owns a 4 x 4 patch.  The general kernel runs such a
+// product on 64 blocks of 128 x 128 with a contraction of two 16-steps; this one fills the SMs and is bound by writing C.
+constexpr int OS_KMAX = 64;
+__global__ void __launch_bounds__(256) outer_sum_kernel(const float* __restrict__ A, long sa_k, const float* __restrict__ B, long sb_k, float* __restrict__ C, long ldc,
+                                                        int M, int N, int K, float alpha) {
+  __shared__ __align__(16) float As[OS_KMAX][64];
+  __shared__ __align__(16) float Bs[OS_KMAX][64];
+  const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64, tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (int i = tid; i < K * 64; i += 256) {
+    const int k = i >> 6, c = i & 63;
+    As[k][c] = m0 + c < M ? A[(long)k * sa_k + m0 + c] : 0.f;
+    Bs[k][c] = n0 + c < N ? B[(long)k * sb_k + n0 + c] : 0.f;
+  }
+  __syncthreads();
+  float acc[4][4] = {};
+  for (int k = 0; k < K; k++) {
+    const float4 a = *reinterpret_cast<const float4*>(&As[k][ty * 4]), b = *reinterpret_cast<const float4*>(&Bs[k][tx * 4]);
+    const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+      for (int j = 0; j < 4; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+  }
+  const bool vec = (ldc & 3) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 && n0 + tx * 4 + 3 < N;
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const int m = m0 + ty * 4 + i; if (m >= M) break;
+    float* crow = C + (long)m * ldc + n0 + tx * 4;
+    if (vec) *reinterpret_cast<float4*>(crow) = make_float4(alpha * acc[i][0], alpha * acc[i][1], alpha * acc[i][2], alpha * acc[i][3]);
+    else
+      for (int j = 0; j < 4; j++) if (n0 + tx * 4 + j < N) crow[j] = alpha * acc[i][j];
+  }
+}
+inline bool gemm_outer_small_ok(const GemmDesc& g) {
+  return g.sa_m == 1 && g.sb_n == 1 && g.K >= 1 && g.K <= OS_KMAX && g.batch1 * g.batch2 == 1 && !g.bias && !g.R && !g.mask && g.act == GN_ACT_LINEAR && g.flags == 0 &&
+         !g.a_planes && !g.b_planes && !g.plane_out && !g.a_rownorm && (long)g.M * g.N >= 64 * 64;
+}
+
 inline int gemm_simt(Ctx* ctx, const GemmDesc& g) {
   if (g.M <= 0 || g.N <= 0) return GN_OK;
+  if (gemm_outer_small_ok(g)) {
+    GN_LAUNCH(ctx, outer_sum_kernel, dim3(cdiv(g.N, 64), cdiv(g.M, 64)), 256, 0, g.A, g.sa_k, g.B, g.sb_k, g.C, g.ldc, g.M, g.N, g.K, g.alpha);
+    return check_launch("outer_sum");
+  }
   if (gemm_skinny_ok(g)) { GN_LAUNCH(ctx, gemm_skinny_kernel, g.M, 256, 0, g); return check_launch("gemm_skinny"); }
   dim3 grid(cdiv(g.N, SG_BN), cdiv(g.M, SG_BM), g.batch1 * g.batch2);
   bool ak = (g.sa_k == 1), bn = (g.sb_n == 1);

@@ -48,7 +48,9 @@
 
 namespace gn {
 
-constexpr int TC_BM = 128, TC_THREADS = 192;
+constexpr int TC_BM = 128;
+constexpr int TC_EPI_WARPS = 8;                 // two warps per TMEM lane quadrant, each takes half of a tile's columns
+constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;   // TMA warp, MMA warp, epilogue warps
 constexpr unsigned TC_SPIN_LIMIT = 1u << 24;    // default number of polls of one wait (Ctx::spin_limit overrides it)
 constexpr unsigned TC_DRAIN_LIMIT = 1u << 20;   // polls spent waiting for own work in flight after a wait gave up
 constexpr int TC_FLAG_VEC = 4096;   // epilogue may use 16-byte accesses (set by the host when every pointer and stride allows it)
@@ -58,7 +60,8 @@ template <int BN> struct TcCfg {
   static constexpr int A_PL = TC_BM * TC_BK * 2, B_PL = BN * TC_BK * 2;           // one plane of a stage: 8 KB, BN * 64 B
   static constexpr int STAGE_BYTES = 2 * A_PL + 2 * B_PL;
   static constexpr int STAGES = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+  static constexpr int COLV_FLOATS = TC_EPI_WARPS * BN;                           // per epilogue warp: scale and bias of its BN / 2 columns
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + COLV_FLOATS * 4;
   static constexpr bool MERGED = BN > 128;                                        // one accumulator per slot
   static constexpr int SLOT_COLS = MERGED ? BN : 2 * BN;
   static constexpr int TMEM_COLS = 2 * SLOT_COLS;
@@ -182,13 +185,30 @@ struct TcParams {
   float* c_last = nullptr; int last_T = 0;                             // fp32 copy of the rows r with r % last_T == last_T - 1: c_last[(r / last_T) * N + col]
 };
 
-// Epilogue of one output tile, executed by one warp for its TMEM lane quadrant: one output row per thread
-// (TMEM lane = row), 32 consecutive columns per tcgen05.ld, written as 8 float4.  Bias, residual and gate values
-// of a chunk are fetched before the TMEM wait so that their latency overlaps.  `acc_main` / `acc_cross` are the
-// TMEM column offsets of the two accumulators of this tile (MERGED: there is only acc_main).
+// Epilogue of one output tile.  Eight warps share it: a warp may only read the TMEM lanes of its quadrant (warp % 4), so
+// two warps serve each quadrant and take half of the tile's columns each (`chalf`); one output row per thread (TMEM lane
+// = row), 32 consecutive columns per tcgen05.ld, written as 8 float4.  The per-column factors (inverse scale of B's
+// rows, bias) of the warp's columns are staged in shared memory by tc_epilogue_stage BEFORE the warp waits for the
+// accumulator, so that their latency is hidden behind the MMAs; residual and gate values of a chunk are fetched before
+// the TMEM wait for the same reason.  (With four warps and the factors fetched per chunk the epilogue of a tile took as
+// long as its MMAs at K = 1024 and held the tensor pipe back.)  `acc_main` / `acc_cross` are the TMEM column offsets of
+// the two accumulators of this tile (MERGED: there is only acc_main); `bw` is the tile's width (BN, or BN / 2 for a half tile).
+template <int BN>
+__device__ __forceinline__ void tc_epilogue_stage(const TcParams& ep, int n0, int z, int chalf, int lane, int bw, float* colv) {
+    if (!(ep.flags & TC_FLAG_VEC)) return;
+    const int ncw = bw / 2, cbase = n0 + chalf * ncw;
+    const float* isb = ep.isb + (long)z * ep.N;
+    __syncwarp();
+    for (int i = lane * 4; i < ncw; i += 128) {
+      const int col = cbase + i; const bool in = col < ep.N;
+      *reinterpret_cast<float4*>(colv + i) = in ? __ldg(reinterpret_cast<const float4*>(isb + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(colv + BN / 2 + i) = (in && ep.bias) ? __ldg(reinterpret_cast<const float4*>(ep.bias + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    __syncwarp();
+}
 template <int BN, bool MERGED>
 __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tmem_base, uint32_t acc_main, uint32_t acc_cross,
-                                                 int m0, int n0, int z, int quad, int lane, int nkb, int bw) {
+                                                 int m0, int n0, int z, int quad, int chalf, int lane, int nkb, int bw, const float* colv) {
     const int z1 = z / ep.batch2, z2 = z % ep.batch2;
     float* C = ep.C + z1 * ep.c_b1 + z2 * ep.c_b2;
     const float* R = ep.R ? ep.R + z1 * ep.r_b1 + z2 * ep.r_b2 : nullptr;
@@ -204,10 +224,11 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
     if (ep.out_p0 && row_ok) {
       const float an = ep.a_rownorm[row], bound = sqrtf(fmaf(an, an, 1.f)) * sqrtf((float)ep.K + 1.f) * __int_as_float(*ep.b_maxabs);
       float oinv; osc = row_scale(bound, &oinv);
-      if (n0 == 0) ep.out_inv[row] = oinv;
+      if (n0 == 0 && chalf == 0) ep.out_inv[row] = oinv;
     }
-    for (int c = 0; c < bw / 32; c++) {                 // bw: width of this tile (BN, or BN / 2 for a half tile)
-      const int col0 = n0 + c * 32;
+    const int nch = bw / 64;                                               // chunks of 32 columns per warp
+    for (int cc = 0; cc < nch; cc++) {
+      const int c = chalf * nch + cc, col0 = n0 + c * 32;
       if (col0 >= ep.N) break;
       uint32_t r[32], q[MERGED ? 1 : 32];
       if (nkb > 0) {
@@ -220,11 +241,10 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
         if constexpr (MERGED) return __uint_as_float(r[j]); else return __uint_as_float(r[j]) + __uint_as_float(q[j]);
       };
       if (vec) {
-        float4 rv[8], mv[8], sv[8];
+        float4 rv[8], mv[8];
 #pragma unroll
         for (int j = 0; j < 8; j++) {
           const bool in = col0 + 4 * j < ep.N;
-          sv[j] = in ? __ldg(reinterpret_cast<const float4*>(isb + col0 + 4 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
           rv[j] = (Rrow && in) ? *reinterpret_cast<const float4*>(Rrow + col0 + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
           mv[j] = (Mrow && in) ? *reinterpret_cast<const float4*>(Mrow + col0 + 4 * j) : make_float4(1.f, 1.f, 1.f, 1.f);
         }
@@ -232,10 +252,10 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
 #pragma unroll
         for (int j = 0; j < 8; j++) {
           if (!row_ok || col0 + 4 * j >= ep.N) continue;
-          float4 bv = ep.bias ? __ldg(reinterpret_cast<const float4*>(ep.bias + col0 + 4 * j)) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float4 sv = *reinterpret_cast<const float4*>(colv + cc * 32 + 4 * j), bv = *reinterpret_cast<const float4*>(colv + BN / 2 + cc * 32 + 4 * j);
           float4 v;
-          v.x = acc(4 * j) * isa * sv[j].x + bv.x + rv[j].x; v.y = acc(4 * j + 1) * isa * sv[j].y + bv.y + rv[j].y;
-          v.z = acc(4 * j + 2) * isa * sv[j].z + bv.z + rv[j].z; v.w = acc(4 * j + 3) * isa * sv[j].w + bv.w + rv[j].w;
+          v.x = acc(4 * j) * isa * sv.x + bv.x + rv[j].x; v.y = acc(4 * j + 1) * isa * sv.y + bv.y + rv[j].y;
+          v.z = acc(4 * j + 2) * isa * sv.z + bv.z + rv[j].z; v.w = acc(4 * j + 3) * isa * sv.w + bv.w + rv[j].w;
           if (ep.act == GN_ACT_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
           if (!(mv[j].x > 0.f)) v.x = 0.f; if (!(mv[j].y > 0.f)) v.y = 0.f; if (!(mv[j].z > 0.f)) v.z = 0.f; if (!(mv[j].w > 0.f)) v.w = 0.f;
           if (ep.out_p0) {
@@ -279,6 +299,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);       // full[S], empty[S], tfull[2], tempty[2], drain
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 5);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);       // set by the first role whose wait gave up
+  float* colv_all = (float*)(smem + STAGES * STAGE_BYTES + 256);   // epilogue warps' column factors
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
   const uint32_t drain = smem_u32(bars + 2 * STAGES + 4);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -288,7 +309,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
-    for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+    for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, TC_EPI_WARPS); }
     mbar_init(drain, 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -394,17 +415,20 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
       }
     }
   } else {
-    const int quad = warp & 3; uint32_t lt = 0;
+    const int quad = warp & 3, chalf = (warp - 2) >> 2; uint32_t lt = 0;
+    float* colv = colv_all + (warp - 2) * BN;
     int tile, half;
     for (int w = 0; work(w, tile, half); w++) {
       int m0, n0, z, kb0, nkb; if (!decode(tile, half, m0, n0, z, kb0, nkb)) continue;
       const uint32_t slot = lt & 1, u = lt >> 1; lt++;
+      const int bw = half < 0 ? BN : BN / 2;
+      tc_epilogue_stage<BN>(ep, n0, z, chalf, lane, bw, colv);
       int ok = 1;
       if (lane == 0) ok = mbar_wait(tfull0 + 8 * slot, u & 1, limit, abort_flag) ? 1 : 0;
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) { if (lane == 0 && !*abort_flag) give_up(3); break; }
       tc_fence_after();
-      tc_epilogue_tile<BN, MERGED>(ep, tmem_base, slot * SLOT_COLS, slot * SLOT_COLS + BN, m0, n0, z, quad, lane, nkb, half < 0 ? BN : BN / 2);
+      tc_epilogue_tile<BN, MERGED>(ep, tmem_base, slot * SLOT_COLS, slot * SLOT_COLS + BN, m0, n0, z, quad, chalf, lane, nkb, bw, colv);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * slot);
@@ -716,20 +740,22 @@ __device__ __forceinline__ int wplane_find(const WPlaneJob* jobs, int njobs, int
   while (lo < hi) { const int mid = (lo + hi + 1) >> 1; if (jobs[mid].tile0 <= tile) lo = mid; else hi = mid - 1; }
   return lo;
 }
-__global__ void __launch_bounds__(256) wplanes_max_kernel(const WPlaneJob* __restrict__ jobs, int njobs, int* __restrict__ mx) {
+__global__ void __launch_bounds__(256) wplanes_max_kernel(const WPlaneJob* __restrict__ jobs, int njobs, int* __restrict__ mx, int tile_off) {
   __shared__ float red[33];
-  const int j = wplane_find(jobs, njobs, blockIdx.x); const WPlaneJob jb = jobs[j];
-  const int t = blockIdx.x - jb.tile0, r0 = (t / jb.tiles_in) * 64, c0 = (t % jb.tiles_in) * 64;
+  const int tile = blockIdx.x + tile_off;
+  const int j = wplane_find(jobs, njobs, tile); const WPlaneJob jb = jobs[j];
+  const int t = tile - jb.tile0, r0 = (t / jb.tiles_in) * 64, c0 = (t % jb.tiles_in) * 64;
   float m = 0.f;
   for (int e = threadIdx.x; e < 4096; e += 256) { const int r = r0 + (e >> 6), c = c0 + (e & 63); if (r < jb.out && c < jb.in) m = fmaxf(m, fabsf(jb.src[(long)r * jb.in + c])); }
   if (jb.bias && c0 == 0 && threadIdx.x < 64 && r0 + (int)threadIdx.x < jb.out) m = fmaxf(m, fabsf(jb.bias[r0 + threadIdx.x]));      // the layer's biases count towards the maximum (bounds of plane-output contractions)
   m = block_max(m, red);
   if (threadIdx.x == 0) { if (!(m <= 3.0e38f)) m = 3.4e38f; atomicMax(mx + j, __float_as_int(m)); }
 }
-__global__ void __launch_bounds__(256) wplanes_split_kernel(const WPlaneJob* __restrict__ jobs, int njobs, const int* __restrict__ mx) {
+__global__ void __launch_bounds__(256) wplanes_split_kernel(const WPlaneJob* __restrict__ jobs, int njobs, const int* __restrict__ mx, int tile_off) {
   __shared__ float tl[64][65];
-  const int j = wplane_find(jobs, njobs, blockIdx.x); const WPlaneJob jb = jobs[j];
-  const int t = blockIdx.x - jb.tile0, r0 = (t / jb.tiles_in) * 64, c0 = (t % jb.tiles_in) * 64;
+  const int tile = blockIdx.x + tile_off;
+  const int j = wplane_find(jobs, njobs, tile); const WPlaneJob jb = jobs[j];
+  const int t = tile - jb.tile0, r0 = (t / jb.tiles_in) * 64, c0 = (t % jb.tiles_in) * 64;
   float inv; const float sc = row_scale(__int_as_float(mx[j]), &inv);
   for (int e = threadIdx.x; e < 4096; e += 256) { const int rr = e >> 6, cc = e & 63; const int r = r0 + rr, c = c0 + cc; tl[rr][cc] = (r < jb.out && c < jb.in) ? jb.src[(long)r * jb.in + c] : 0.f; }
   __syncthreads();
@@ -754,9 +780,14 @@ __global__ void __launch_bounds__(256) wplanes_split_kernel(const WPlaneJob* __r
   }
 }
 // Host side of the table: one entry per registered matrix, looked up by the matrix's device address.
-struct WeightPlaneEntry { const float* src; int out, in; BfPlanes rows, cols; const float* bias = nullptr; const int* maxabs = nullptr; };
+struct WeightPlaneEntry { const float* src; int out, in; BfPlanes rows, cols; const float* bias = nullptr; const int* maxabs = nullptr; int layer = -1; int tile0 = 0, tiles = 0; };
 struct WeightPlaneTable {
   std::vector<WeightPlaneEntry> e; DevBuf planes, scales, mx, jobs; int total_tiles = 0; bool dirty = true;
+  // entries [j0, j1) that belong to model layer `layer` (they are registered layer by layer, so the range is contiguous)
+  void layer_range(int layer, int* j0, int* j1) const {
+    *j0 = *j1 = 0; bool in = false;
+    for (int j = 0; j < (int)e.size(); j++) if (e[j].layer == layer) { if (!in) { *j0 = j; in = true; } *j1 = j + 1; }
+  }
   const WeightPlaneEntry* find(const float* p) const { for (auto& x : e) if (x.src == p) return &x; return nullptr; }
 };
 // Lays the table out for the matrices (src, out, in) and allocates its buffers (planes zeroed once: the padding columns
@@ -777,7 +808,8 @@ inline int wplanes_build(Ctx* ctx, WeightPlaneTable& t, const std::vector<Weight
     x.cols = BfPlanes{hp, sp, x.in, x.out, lc, 1}; hp += 2 * (size_t)x.in * lc; sp += (x.in + 3) & ~3;
     x.maxabs = reinterpret_cast<const int*>(t.mx.p) + jobs.size();
     WPlaneJob jb{x.src, x.bias, x.out, x.in, lr, lc, x.rows.p0(), x.rows.p1(), x.cols.p0(), x.cols.p1(), x.rows.inv_scale, x.cols.inv_scale, tiles, (int)cdiv(x.in, 64)};
-    tiles += (int)cdiv(x.out, 64) * (int)cdiv(x.in, 64); jobs.push_back(jb);
+    x.tile0 = tiles; x.tiles = (int)cdiv(x.out, 64) * (int)cdiv(x.in, 64);
+    tiles += x.tiles; jobs.push_back(jb);
   }
   t.total_tiles = tiles;
   GN_TRY(t.jobs.alloc((jobs.size() * sizeof(WPlaneJob) + 3) / 4));
@@ -785,15 +817,22 @@ inline int wplanes_build(Ctx* ctx, WeightPlaneTable& t, const std::vector<Weight
   t.dirty = true; return GN_OK;
 }
 // Re-splits every registered matrix if the parameters changed since the last call.
+// Entries [j0, j1) only, on `stream`: used right behind a layer's parameter update when the update runs layer by layer.
+inline int wplanes_refresh_range(Ctx* ctx, WeightPlaneTable& t, int j0, int j1, cudaStream_t stream) {
+  if (j1 <= j0) return GN_OK;
+  const int nj = (int)t.e.size(), tile_off = t.e[j0].tile0, ntiles = t.e[j1 - 1].tile0 + t.e[j1 - 1].tiles - tile_off;
+  GN_CUDA(cudaMemsetAsync(reinterpret_cast<int*>(t.mx.p) + j0, 0, (size_t)(j1 - j0) * sizeof(int), stream));
+  wplanes_max_kernel<<<ntiles, 256, 0, stream>>>(reinterpret_cast<const WPlaneJob*>(t.jobs.p), nj, reinterpret_cast<int*>(t.mx.p), tile_off);
+  wplanes_split_kernel<<<ntiles, 256, 0, stream>>>(reinterpret_cast<const WPlaneJob*>(t.jobs.p), nj, reinterpret_cast<const int*>(t.mx.p), tile_off);
+  ctx->launches += 2;
+  double elems = 0; for (int j = j0; j < j1; j++) elems += (double)t.e[j].out * t.e[j].in;
+  ctx->split_bytes += 16.0 * elems;                          // 4 B read twice, 8 B written
+  return check_launch("wplanes_refresh");
+}
 inline int wplanes_refresh(Ctx* ctx, WeightPlaneTable& t) {
   if (t.e.empty() || !t.dirty) return GN_OK;
-  const int nj = (int)t.e.size();
-  GN_CUDA(cudaMemsetAsync(t.mx.p, 0, (size_t)nj * sizeof(int), ctx->stream));
-  GN_LAUNCH(ctx, wplanes_max_kernel, t.total_tiles, 256, 0, reinterpret_cast<const WPlaneJob*>(t.jobs.p), nj, reinterpret_cast<int*>(t.mx.p));
-  GN_LAUNCH(ctx, wplanes_split_kernel, t.total_tiles, 256, 0, reinterpret_cast<const WPlaneJob*>(t.jobs.p), nj, reinterpret_cast<const int*>(t.mx.p));
-  double elems = 0; for (auto& x : t.e) elems += (double)x.out * x.in;
-  ctx->split_bytes += 16.0 * elems;                          // 4 B read twice, 8 B written
-  t.dirty = false; return check_launch("wplanes_refresh");
+  GN_TRY(wplanes_refresh_range(ctx, t, 0, (int)t.e.size(), ctx->stream));
+  t.dirty = false; return GN_OK;
 }
 // Prepared planes for B of this contraction, if B is a registered matrix used in one of its two orientations.
 inline const BfPlanes* wplanes_lookup(Ctx* ctx, const GemmDesc& g, const WeightPlaneEntry** entry = nullptr) {

@@ -35,7 +35,7 @@ static bool force_simt_engine() { static const bool f = [] { const char* e = get
 // Chooses the tensor-core engine for large K-major x K-major products and the SIMT engine for the rest.
 static int gemm(Ctx* ctx, const GemmDesc& g) {
   int rc;
-  if (!force_simt_engine() && gemm_tc_eligible(ctx, g)) {                                 // brackets its kernel launches itself
+  if (!force_simt_engine() && gemm_tc_eligible(ctx, g) && !gemm_outer_small_ok(g)) {     // brackets its kernel launches itself
     GemmDesc h = g; if (!h.b_planes) h.b_planes = wplanes_lookup(ctx, g);                 // weight matrices come with prepared planes
     rc = gemm_tc(ctx, h);
   }
@@ -100,6 +100,7 @@ struct gn_model {
   gn::DevBuf params, grads, m1, v2, state; int64_t NS = 0;
   int cur_first_sample = 0;             // global index of the first sample of the batch being processed (Dropout's stream position)
   int cur_global_batch = 0;             // size of the global batch being processed (all ranks)
+  bool wplanes_layerwise = false;       // this step renewed the weight planes layer by layer behind the parameter update
   float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f; int timestep = 0;
   int cap = 0;                          // batch capacity of the activation buffers
   gn::DevBuf xin, yin, lossg, loss_s, loss_sum;
@@ -956,6 +957,12 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
       }
       GN_TRY(adam_launch(ctx, m->params.p + l.p_off, gr, m->m1.p + l.p_off, m->v2.p + l.p_off, l.p_cnt, m->lr, m->b1, m->b2, m->eps, m->timestep + 2,
                          (float)(1.0 / (double)global_batch), ctx->d_status, ctx->comm_stream));
+      // ... and the layer's prepared operand planes right behind the update, still hidden behind the earlier layers' backward pass
+      if (!m->wplanes.e.empty()) {
+        int j0, j1; m->wplanes.layer_range((int)li, &j0, &j1);
+        GN_TRY(wplanes_refresh_range(ctx, m->wplanes, j0, j1, ctx->comm_stream));
+        m->wplanes_layerwise = true;
+      }
     }
   }
   return GN_OK;
@@ -1032,6 +1039,7 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
   if (global_batch <= 0) { global_batch = B; first_sample = 0; }
   if (B > m->cap) GN_TRY(alloc_activations(m, B));
   int64_t launches0 = ctx->launches; ctx->gemm_flops = 0; ctx->gemm_launches = 0; ctx->gemm_ms = 0; ctx->ev_used = 0; ctx->gemm_bytes = 0; ctx->split_bytes = 0;
+  m->wplanes_layerwise = false;
   int rc = train_step_issue(m, x_dev, y_dev, B, global_batch, first_sample);
   if (rc != GN_OK) {
     // drain what was queued before the failure (both streams) so that nothing of this step runs after the call returned
@@ -1045,7 +1053,9 @@ static int train_step(gn_model* m, const float* x_dev, const float* y_dev, int B
     cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream); cudaStreamSynchronize(ctx->stream);
     return status_error(st);
   }
-  m->timestep += 1; m->wplanes.dirty = true;        // the parameters moved: their operand planes are stale
+  m->timestep += 1;
+  m->wplanes.dirty = !m->wplanes_layerwise;          // the parameters moved: their operand planes are stale, unless they were renewed layer by layer behind the update
+  m->wplanes_layerwise = false;
   if (mean_loss) *mean_loss = m->h_ret[0] / (float)global_batch;
   m->stats.kernel_launches = ctx->launches - launches0;
   cudaEventElapsedTime(&m->stats.step_ms, m->ev0, m->ev1);
@@ -1182,13 +1192,13 @@ int gn_model_create(gn_ctx* ctx, const gn_layer_desc* layers, int n_layers, int 
   }
   if (ctx->c.tc_ok && !force_simt_engine() && !getenv("GONEURON_CUDA_NO_WEIGHT_PLANES")) {
     // weight matrices large enough to run on the tensor-core engine get prepared operand planes (both orientations)
-    std::vector<WeightPlaneEntry> mats;
+    std::vector<WeightPlaneEntry> mats; int cur_layer = 0;
     auto add = [&](int64_t off, int out, int in, bool has_bias = true) {
       if ((double)out * in < 64.0 * 64.0) return;
-      WeightPlaneEntry e{m->params.p + off, out, in, {}, {}}; e.bias = has_bias ? m->params.p + off + (int64_t)out * in : nullptr; mats.push_back(e);
+      WeightPlaneEntry e{m->params.p + off, out, in, {}, {}}; e.bias = has_bias ? m->params.p + off + (int64_t)out * in : nullptr; e.layer = cur_layer; mats.push_back(e);
     };
     for (auto& l : m->L) {
-      const gn_layer_desc& d = l.d;
+      const gn_layer_desc& d = l.d; cur_layer = (int)(&l - m->L.data());
       if (d.kind == GN_LAYER_DENSE) add(l.p_off, d.out_size, d.in_size);
       else if (d.kind == GN_LAYER_TRANSFORMER_BLOCK) {
         const int64_t dd = (int64_t)d.dim * d.dim + d.dim; int64_t o = l.p_off;
