@@ -16,13 +16,17 @@
 // fetched by TMA into 128-byte-swizzled shared memory: 4 bytes per element instead of the 8 of the TF32 + 2 x BF16 planes
 // this engine used before, which is what makes room for multi-stage block operands.
 //
-// What bounds these kernels is not arithmetic: a trace of the previous version (one MMA-issuing thread, single-stage
-// block operands, 48 small MMAs per 64-key block) showed the issuing thread busy 5200 cycles per block for 1300 cycles
-// of tensor work, behind it a single-buffered TMA fetch, and the elementwise warps waiting.  Hence here:
-//   * two MMA-issuing warps per kernel (score products / accumulating products), ordered through mbarriers only;
+// What bounds these kernels is not arithmetic.  A clock trace of the previous version (one MMA-issuing thread,
+// single-stage block operands, 48 small MMAs per 64-key block) showed the issuing thread busy 5200 cycles per block for
+// 1300 cycles of tensor work, behind it a single-buffered TMA fetch, and the elementwise warps waiting.  Hence here:
+//   * one MMA-issuing warp per product of a block, ordered through mbarriers only;
 //   * 36 instead of 48 MMAs per block (three fp16 terms instead of two BF16 + a TF32 term at half the depth);
-//   * three or four shared-memory stages for the block operands;
-//   * sixteen elementwise warps (four threads per tile row, 16 columns each): their chain is latency-bound.
+//   * three or four shared-memory stages for the block operands, three or four TMEM stages for the score tiles;
+//   * sixteen elementwise warps (four threads per tile row, 16 columns each): their chain is latency-bound;
+//   * the write-out of a tile deferred until the next tile's first block has been handed on.
+// The same trace now: 2450 cycles per block in the backward kernels, i.e. 68 cycles per 128 x 64 x 16 MMA whichever
+// warp issues it -- the tensor pipe fetching its shared-memory operands (6 KB per MMA with both operands in shared
+// memory, against 32 cycles of arithmetic).  Keeping the row-tile operand in tensor memory would halve that traffic.
 // P (forward), dS / P^T (backward) go back to tensor memory as fp16 hi | lo pairs, written over the score columns they
 // were computed from -- each thread's 16 columns hold exactly its 8 + 8 packed words, so no thread overwrites what
 // another still has to read -- and are the A operand of the accumulating product.
@@ -36,10 +40,16 @@ namespace gn {
 
 constexpr int ATC_BQ = 128, ATC_BK = 64, ATC_HD = 64;
 constexpr int ATC_CW = 16, ATC_NPART = 64 / ATC_CW, ATC_EW_WARPS = 4 * ATC_NPART, ATC_EW_THREADS = 32 * ATC_EW_WARPS;
-constexpr int ATC_THREADS = 96 + ATC_EW_THREADS;      // warp 0 TMA, warp 1 and 2 MMA issuers, 16 elementwise warps
+constexpr int ATC_THREADS = 96 + ATC_EW_THREADS;      // forward: warp 0 TMA, warps 1 and 2 MMA issuers, 16 elementwise warps
+constexpr int ATB_THREADS = 128 + ATC_EW_THREADS;     // backward: warp 0 TMA, warps 1-3 MMA issuers, 16 elementwise warps
 constexpr int ATC_R_BYTES = 2 * 128 * 128;            // a 128-row tile: hi | lo, 128-byte rows: 32 KB
 constexpr int ATC_C_BYTES = 2 * 64 * 128;             // a 64-row block: hi | lo: 16 KB
 constexpr float ATC_PSCALE = 16384.f;                 // probabilities (at most 1) as fp16 pairs
+// Forward: the running maximum is only moved when it grows by more than 2^ATF_LAZY_LOG2 (then the accumulator is
+// rescaled); otherwise the stale maximum stays the reference point -- the row statistics kept for the backward pass are
+// the pair that was used, so exp(s - m) / l is the same probability either way.  The unnormalised p can then reach
+// 2^ATF_LAZY_LOG2, hence the smaller plane scale.
+constexpr float ATF_LAZY_LOG2 = 6.f, ATF_PSCALE = 256.f;
 
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}"
@@ -85,16 +95,19 @@ template <int N> struct AttnMaps { CUtensorMap m[N]; };
 // block), the query block being rotated by i so that every CTA sees short and long causal tiles alike (gridDim.x is a
 // multiple of the number of query blocks).  All counters run across tiles, so the barriers' phases simply continue.
 //   warp 0 : TMA producer: Q (two buffers, the next tile's Q arrives under the current tile), K and V^T blocks (four stages)
-//   warp 1 : issues S_j = Q K_j^T into one of two 64-column TMEM buffers, as soon as P V of block j-2 has left it
+//   warp 1 : issues S_j = Q K_j^T into one of four 64-column TMEM buffers, as soon as P V of block j-4 has left it
 //   warp 2 : issues O += P_j V_j (P from TMEM, V^T_j from shared memory) into one of two output accumulators
 //   warps 3-18 : softmax.  tcgen05.ld of S_j, running maximum (exchanged through shared memory) and sum, p = exp(s - m)
-//            written back as fp16 planes; when a row maximum moved, the output accumulator is rescaled in TMEM after
-//            the previous P V has completed.
-constexpr int ATF_NK = 4;
+//            written back as fp16 planes; when a row maximum moved by more than 2^6, the output accumulator is rescaled
+//            in TMEM after the previous P V has completed.  The write-out of a finished tile waits until the first
+//            block of the next tile has been handed to the P V issuer.
+// (A trace of the two-buffer version: S_{j+2} waited for P V_j, the softmax for S_{j+2}, 2700 cycles per block, and
+// 6000 cycles at every tile boundary for the write-out and the next tile's scale factors.)
+constexpr int ATF_NK = 4, ATF_NSS = 4;
 constexpr int ATF_SMEM = 2 * ATC_R_BYTES + 2 * ATF_NK * ATC_C_BYTES + 1024 + 512 + 2 * ATC_NPART * 128 * 4;
-constexpr uint32_t ATF_COL_S = 0, ATF_COL_O = 128, ATF_TMEM_COLS = 256;
-// barriers: q_full 0,1 | q_empty 2,3 | k_full 4-7 | k_empty 8-11 | v_full 12-15 | v_empty 16-19 | s_full 20,21 | p_full 22,23
-//           s_free 24,25 (P V of the buffer has completed) | o_free 26,27 | drains 28,29
+constexpr uint32_t ATF_COL_S = 0, ATF_COL_O = 64 * ATF_NSS, ATF_TMEM_COLS = 512;
+// barriers: q_full 0,1 | q_empty 2,3 | k_full 4-7 | k_empty 8-11 | v_full 12-15 | v_empty 16-19 | s_full 20-23 | p_full 24-27
+//           s_free 28-31 (P V of the buffer has completed) | o_free 32,33 | drains 34,35
 __global__ void __launch_bounds__(ATC_THREADS, 1)
 attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<6> maps, float* __restrict__ O, float* __restrict__ Mst, float* __restrict__ Lst,
                    const float* __restrict__ isq, const float* __restrict__ isk, const float* __restrict__ isv,
@@ -105,11 +118,11 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<6> maps, float* __restrict__
   uint8_t* sK = sQ + 2 * ATC_R_BYTES;                                 // ATF_NK stages of ATC_C_BYTES
   uint8_t* sV = sK + ATF_NK * ATC_C_BYTES;
   uint64_t* bars = (uint64_t*)(sV + ATF_NK * ATC_C_BYTES);
-  uint32_t* tmem_slot = (uint32_t*)(bars + 32);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 40);
   float* xch = (float*)(bars + 64);                                   // [2][ATC_NPART][128] row maxima / sums exchanged between the threads of a row
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
-  constexpr int QF = 0, QE = 2, KF = 4, KE = 8, VF = 12, VE = 16, SF = 20, PF = 22, SFREE = 24, OFREE = 26, DRAIN = 28;
+  constexpr int NSS = ATF_NSS, QF = 0, QE = 2, KF = 4, KE = 8, VF = 12, VE = 16, SF = 20, PF = 24, SFREE = 28, OFREE = 32, DRAIN = 34;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // Bounded waits that fail fast: the first wait that gives up records its role in the status word at once, and every
   // later wait of every role and CTA (they all poll that word) gives up after at most 64 polls, so a launch whose pipeline
@@ -129,7 +142,7 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<6> maps, float* __restrict__
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 30; i++) mbar_init(BAR(i), (i == PF || i == PF + 1 || i == OFREE || i == OFREE + 1) ? ATC_EW_THREADS : 1);
+    for (int i = 0; i < 36; i++) mbar_init(BAR(i), ((i >= PF && i < PF + NSS) || i == OFREE || i == OFREE + 1) ? ATC_EW_THREADS : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -176,9 +189,9 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<6> maps, float* __restrict__
         const uint32_t qa = smem_u32(sQ + qb * ATC_R_BYTES);
         const uint64_t q_hi = make_desc<32>(qa), q_lo = make_desc<32>(qa + ATC_R_BYTES / 2);
         for (int j = 0; j < nblk; j++, g++) {
-          const uint32_t s = g % ATF_NK, u = g / ATF_NK, sb = g & 1;
+          const uint32_t s = g % ATF_NK, u = g / ATF_NK, sb = g % NSS, su = g / NSS;
           if (!WAIT(BAR(KF + s), u & 1, 12)) { ok = false; break; }
-          if (g >= 2 && !WAIT(BAR(SFREE + sb), ((g >> 1) - 1) & 1, 12)) { ok = false; break; }      // P V of block g-2 has read this buffer
+          if (su > 0 && !WAIT(BAR(SFREE + sb), (su - 1) & 1, 12)) { ok = false; break; }      // P V of block g - NSS has read this buffer
           tc_fence_after();
           const uint32_t acc = tmem_base + ATF_COL_S + sb * 64, kb = smem_u32(sK + s * ATC_C_BYTES);
           const uint64_t k_hi = make_desc<32>(kb), k_lo = make_desc<32>(kb + ATC_C_BYTES / 2);
@@ -199,8 +212,8 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<6> maps, float* __restrict__
         const uint32_t ob = tt & 1;
         if (tt >= 2 && !WAIT(BAR(OFREE + ob), ((tt >> 1) - 1) & 1, 14)) { ok = false; break; }     // this accumulator has been written out
         for (int j = 0; j < nblk; j++, g++) {
-          const uint32_t s = g % ATF_NK, u = g / ATF_NK, sb = g & 1;
-          if (!WAIT(BAR(PF + sb), (g >> 1) & 1, 14) || !WAIT(BAR(VF + s), u & 1, 14)) { ok = false; break; }
+          const uint32_t s = g % ATF_NK, u = g / ATF_NK, sb = g % NSS, su = g / NSS;
+          if (!WAIT(BAR(PF + sb), su & 1, 14) || !WAIT(BAR(VF + s), u & 1, 14)) { ok = false; break; }
           tc_fence_after();
           const uint32_t acc = tmem_base + ATF_COL_O + ob * 64, pa = tmem_base + ATF_COL_S + sb * 64, vb = smem_u32(sV + s * ATC_C_BYTES);
           const uint64_t v_hi = make_desc<32>(vb), v_lo = make_desc<32>(vb + ATC_C_BYTES / 2);
@@ -218,15 +231,35 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<6> maps, float* __restrict__
     const int quad = warp & 3, part = (warp - 3) >> 2, row = quad * 32 + lane;
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + CW * part;
     bool ok = true; uint32_t g0 = 0, xc = 0;
+    constexpr float LOG2E = 1.44269504088896341f;
+    // write-out of a finished tile: wait for its last P V, scale, store
+    int pend_tt = -1; uint32_t pend_g = 0; float pend_il = 0.f; float* pend_row = nullptr;
+    auto write_out = [&]() {
+      ok &= WWAIT(BAR(SFREE + pend_g % NSS), (pend_g / NSS) & 1, 13);       // the tile's last P V has completed
+      tc_fence_after();
+      uint32_t a[CW];
+      tmem_ld16(lane_base + ATF_COL_O + (pend_tt & 1) * 64, a);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(BAR(OFREE + (pend_tt & 1)));              // the accumulator is in registers: the MMA warp may reuse it
+#pragma unroll
+      for (int e = 0; e < CW / 4; e++)
+        *reinterpret_cast<float4*>(pend_row + 4 * e) = make_float4(__uint_as_float(a[4 * e]) * pend_il, __uint_as_float(a[4 * e + 1]) * pend_il, __uint_as_float(a[4 * e + 2]) * pend_il, __uint_as_float(a[4 * e + 3]) * pend_il);
+      pend_tt = -1;
+    };
+    // scale factors of the first tile; those of the following tile are fetched while a tile runs
+    float nsc = 0.f, nisv = 0.f;
+    if (blockIdx.x < ntiles) { const int z0 = blockIdx.x / ntq; nsc = inv_scale * isq[z0] * isk[z0]; nisv = isv[z0]; }
     for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
       int z, q0, nblk; decode(id, tt, z, q0, nblk);
       const int qi = q0 + row; const uint32_t ob = tt & 1;
-      const float sc = inv_scale * isq[z] * isk[z];         // accumulator -> scaled score
-      const float cs = sc * 1.44269504088896341f;           // ... in log2 units
-      float m_run = -INFINITY, l_part = 0.f;                // running maximum (scaled scores), this thread's part of the row sum
+      const float sc = nsc, isv_z = nisv;                   // accumulator -> scaled score; 1 / scale of V
+      const float cs = sc * LOG2E;                          // ... in log2 units
+      if (id + (int)gridDim.x < ntiles) { const int zn = (id + (int)gridDim.x) / ntq; nsc = inv_scale * isq[zn] * isk[zn]; nisv = isv[zn]; }
+      float m_run = -INFINITY, l_part = 0.f;                // reference maximum (scaled scores), this thread's part of the row sum
       for (int j = 0; j < nblk; j++) {
-        const uint32_t g = g0 + j, sb = g & 1; const int key0 = j * ATC_BK + CW * part;
-        ok &= WWAIT(BAR(SF + sb), (g >> 1) & 1, 13);
+        const uint32_t g = g0 + j, sb = g % NSS, su = g / NSS; const int key0 = j * ATC_BK + CW * part;
+        ok &= WWAIT(BAR(SF + sb), su & 1, 13);
         tc_fence_after();
         uint32_t a[CW];
         tmem_ld16(lane_base + ATF_COL_S + sb * 64, a);
@@ -243,18 +276,22 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<6> maps, float* __restrict__
         asm volatile("bar.sync 1, %0;" ::"n"(ATC_EW_THREADS) : "memory");
 #pragma unroll
         for (int o = 1; o < ATC_NPART; o++) bm = fmaxf(bm, xb[((part + o) & (ATC_NPART - 1)) * 128 + row]);
-        const float m_new = fmaxf(m_run, bm * sc);
-        const float corr = fast_ex2((m_run - m_new) * 1.44269504088896341f);
-        const float mneg = -m_new * 1.44269504088896341f;
+        // the reference point moves only when the maximum grew by more than 2^ATF_LAZY_LOG2 (the four threads of a row
+        // hold the same bm and m_run, so they decide alike)
+        const float m_blk = bm * sc;
+        const bool move = !((m_blk - m_run) * LOG2E <= ATF_LAZY_LOG2);      // also true for the first block (m_run = -inf)
+        const float m_new = move ? fmaxf(m_run, m_blk) : m_run;
+        const float corr = move ? fast_ex2((m_run - m_new) * LOG2E) : 1.f;
+        const float mneg = -m_new * LOG2E;
         float rs = 0.f, p[CW];
 #pragma unroll
         for (int e = 0; e < CW; e++) { p[e] = fast_ex2(fmaf(__uint_as_float(a[e]), cs, mneg)); rs += p[e]; }
-        pack_planes16(p, ATC_PSCALE, a);
+        pack_planes16(p, ATF_PSCALE, a);
         tmem_st16(lane_base + ATF_COL_S + sb * 64, a);      // fp16 hi | lo of this thread's 16 keys = one 16-deep step of P V
         l_part = l_part * corr + rs; m_run = m_new;
         // The accumulator may only be touched between P V products; the previous one signals s_free of ITS buffer.
         if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
-          ok &= WWAIT(BAR(SFREE + (sb ^ 1)), ((g - 1) >> 1) & 1, 13);
+          ok &= WWAIT(BAR(SFREE + (g - 1) % NSS), ((g - 1) / NSS) & 1, 13);
           tc_fence_after();
           tmem_ld16(lane_base + ATF_COL_O + ob * 64, a);
           tmem_wait_ld();
@@ -265,31 +302,23 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<6> maps, float* __restrict__
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(BAR(PF + sb));
+        if (j == 0 && pend_tt >= 0) write_out();            // the previous tile, now that this tile's first block is on its way
       }
-      ok &= WWAIT(BAR(SFREE + ((g0 + nblk - 1) & 1)), ((g0 + nblk - 1) >> 1) & 1, 13);      // the tile's last P V has completed
-      tc_fence_after();
       {
-        uint32_t a[CW];
-        tmem_ld16(lane_base + ATF_COL_O + ob * 64, a);
         float* xb = xch + (xc++ & 1) * (ATC_NPART * 128);
         xb[part * 128 + row] = l_part;
         asm volatile("bar.sync 1, %0;" ::"n"(ATC_EW_THREADS) : "memory");
         float l_run = 0.f;
 #pragma unroll
         for (int o = 0; o < ATC_NPART; o++) l_run += xb[o * 128 + row];              // the same order in every thread of the row
-        tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(BAR(OFREE + ob));                       // the accumulator is in registers: the MMA warp may reuse it
-        const float il = isv[z] * (1.f / ATC_PSCALE) / l_run;
         const int bz = z / H, h = z % H;
-        float* orow = O + ((long)bz * T + qi) * D + (long)h * ATC_HD + CW * part;
-#pragma unroll
-        for (int e = 0; e < CW / 4; e++)
-          *reinterpret_cast<float4*>(orow + 4 * e) = make_float4(__uint_as_float(a[4 * e]) * il, __uint_as_float(a[4 * e + 1]) * il, __uint_as_float(a[4 * e + 2]) * il, __uint_as_float(a[4 * e + 3]) * il);
+        pend_tt = tt; pend_g = g0 + nblk - 1; pend_il = isv_z * (1.f / ATF_PSCALE) / l_run;
+        pend_row = O + ((long)bz * T + qi) * D + (long)h * ATC_HD + CW * part;
         if (part == 0) { Mst[(long)z * T + qi] = m_run; Lst[(long)z * T + qi] = l_run; }
       }
       g0 += nblk;
     }
+    if (pend_tt >= 0) write_out();
     (void)ok;
   }
   tc_fence_before();
@@ -313,24 +342,27 @@ attn_tc_fwd_kernel(const __grid_constant__ AttnMaps<6> maps, float* __restrict__
 // and |D_i| <= max_j |dP_ij|, P <= 1, so |dS_ij| <= (|dO_i| max_j |V_j| + |D_i|) / sqrt(hd) for a query row and
 // (max_i |dO_i| |V_j| + max_i |D_i|) / sqrt(hd) for a key row; the norms come from the scale pass over dO and V.  The
 // bound is loose by the usual Cauchy-Schwarz factor, which an fp16 pair absorbs (22 bits down to 2^-17 of the scale).
-// TMEM: two sets of {S, dP}; the planes of dS (P^T in MODE 2) are written over dP (over S); two accumulators.
-// Warps: 0 = TMA producer; 1 = issuer of the score products; 2 = issuer of the accumulating products; 3-18 elementwise.
+// TMEM: three sets of {S, dP}; the planes of dS (P^T in MODE 2) are written over dP (over S); two accumulators.
+// Warps: 0 = TMA producer; 1, 2 = issuers of the two score-shaped products (S, dP); 3 = issuer of the accumulating
+// product; 4-19 elementwise.  The write-out of a finished tile is deferred until the elementwise warps have done the
+// first block of the next tile, so that the score pipeline does not wait for it.
 constexpr int ATB_NS = 3;
 template <int MODE> struct AtbCfg {
   static constexpr int NR = MODE == 2 ? 1 : 2;                                 // row-tile operands, score-shaped products
   static constexpr int SMEM = NR * ATC_R_BYTES + ATB_NS * (NR + 1) * ATC_C_BYTES + 1024 + 512 + 2 * 3 * 64 * 4;
 };
-constexpr uint32_t ATB_COL_S = 0, ATB_COL_DP = 64, ATB_COL_ACC = 256, ATB_TMEM_COLS = 512;      // stage s at + 128 s; two accumulators of 64 columns
+constexpr int ATB_NT = 3;                                                                       // TMEM stages of {S, dP}
+constexpr uint32_t ATB_COL_S = 0, ATB_COL_DP = 64, ATB_COL_ACC = 128 * ATB_NT, ATB_TMEM_COLS = 512;      // stage t at + 128 t; two accumulators of 64 columns
 struct AtbScales {
   const float *ir1, *ir2, *ic1, *ic2, *ic3;      // inverse plane scales per problem
   const float* rnorm;                            // MODES 0, 1: 2-norm of every row of the tile's side of the bound (dO rows / V rows), [Z][T]
   const int* zmaxn;                              // MODES 0, 1: per problem, the largest row norm of the other side (V / dO), float bits
   const int* zmaxd;                              // MODE 1: per problem, max |Dv|, float bits
 };
-// barriers: r_full 0 | r_empty 1 | c_full 2-4 | c_empty 5-7 | c3_full 8-10 | c3_empty 11-13 | sd_full 14,15 | ds_full 16,17
-//           sd_free 18,19 (the accumulating product has read the stage) | tile_done 20 | acc_free 21,22 | drains 23,24
+// barriers: r_full 0 | r_empty 1 | c_full 2-4 | c_empty 5-7 | c3_full 8-10 | c3_empty 11-13 | sd_full 14-16 | ds_full 17-19
+//           sd_free 20-22 (the accumulating product has read the stage) | tile_done 23 | acc_free 24,25 | drains 26-28
 template <int MODE>
-__global__ void __launch_bounds__(ATC_THREADS, 1)
+__global__ void __launch_bounds__(ATB_THREADS, 1)
 attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __restrict__ Mst, const float* __restrict__ Lst, const float* __restrict__ Dv,
                    float* __restrict__ Out, const AtbScales sc, int T, int D, int H, int causal, float inv_scale, int ntiles, int* status, unsigned spin_limit) {
   constexpr int NR = AtbCfg<MODE>::NR, NS = ATB_NS;
@@ -343,7 +375,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
   uint64_t* bars = (uint64_t*)(sC3 + NS * ATC_C_BYTES);
   uint32_t* tmem_slot = (uint32_t*)(bars + 32);
   float* st = (float*)(bars + 64);                       // [2][3][64] column statistics (MODES 1, 2)
-  constexpr int RF = 0, RE = 1, CF = 2, CE = 5, C3F = 8, C3E = 11, SDF = 14, DSF = 16, SDFREE = 18, TDONE = 20, ACCFREE = 21, DRAIN = 23;
+  constexpr int NT = ATB_NT, RF = 0, RE = 1, CF = 2, CE = 5, C3F = 8, C3E = 11, SDF = 14, DSF = 17, SDFREE = 20, TDONE = 23, ACCFREE = 24, DRAIN = 26;
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * (uint32_t)i; };
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -360,7 +392,8 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
   };
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 25; i++) mbar_init(BAR(i), (i == DSF || i == DSF + 1 || i == ACCFREE || i == ACCFREE + 1) ? ATC_EW_THREADS : 1);
+    for (int i = 0; i < 29; i++)      // r_empty, c_empty and sd_full collect one commit per score-shaped product
+      mbar_init(BAR(i), ((i >= DSF && i < DSF + NT) || i == ACCFREE || i == ACCFREE + 1) ? ATC_EW_THREADS : (i == RE || (i >= CE && i < CE + NS) || (i >= SDF && i < SDF + NT)) ? NR : 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -403,33 +436,33 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
       }
       if (!ok || *(volatile int*)status) for (int i = 0; i < 200; i++) __nanosleep(1000);                 // own copies in flight land before the CTA exits
     }
-  } else if (warp == 1) {
-    if (lane == 0) {                                          // score-shaped products
+  } else if (warp == 1 || warp == 2) {
+    const int prod = warp - 1;                                // warp 1: S, warp 2: dP
+    if (lane == 0 && prod < NR) {
       bool ok = true; uint32_t g = 0;
       for (int id = blockIdx.x, tt = 0; id < ntiles && ok; id += gridDim.x, tt++) {
         int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
         if (!WAIT(BAR(RF), tt & 1, 23)) { ok = false; break; }
+        const uint32_t ra = smem_u32(sR + prod * ATC_R_BYTES);
+        const uint64_t r_hi = make_desc<32>(ra), r_lo = make_desc<32>(ra + ATC_R_BYTES / 2);
         for (int n = 0; n < nb; n++, g++) {
-          const uint32_t s = g % NS, u = g / NS, sb = g & 1;
+          const uint32_t s = g % NS, u = g / NS, sb = g % NT, su = g / NT;
           if (!WAIT(BAR(CF + s), u & 1, 23)) { ok = false; break; }
-          if (g >= 2 && !WAIT(BAR(SDFREE + sb), ((g >> 1) - 1) & 1, 23)) { ok = false; break; }    // the accumulating product of block g-2 has read this stage
+          if (su > 0 && !WAIT(BAR(SDFREE + sb), (su - 1) & 1, 23)) { ok = false; break; }    // the accumulating product of block g - NT has read this stage
           tc_fence_after();
+          const uint32_t acc = tmem_base + 128 * sb + (prod == 0 ? ATB_COL_S : ATB_COL_DP);
+          const uint32_t cb = smem_u32(sC + (s * NR + prod) * ATC_C_BYTES);
+          const uint64_t c_hi = make_desc<32>(cb), c_lo = make_desc<32>(cb + ATC_C_BYTES / 2);
 #pragma unroll
-          for (int prod = 0; prod < NR; prod++) {
-            const uint32_t acc = tmem_base + 128 * sb + (prod == 0 ? ATB_COL_S : ATB_COL_DP);
-            const uint32_t ra = smem_u32(sR + prod * ATC_R_BYTES), cb = smem_u32(sC + (s * NR + prod) * ATC_C_BYTES);
-            const uint64_t r_hi = make_desc<32>(ra), r_lo = make_desc<32>(ra + ATC_R_BYTES / 2), c_hi = make_desc<32>(cb), c_lo = make_desc<32>(cb + ATC_C_BYTES / 2);
-#pragma unroll
-            for (int k = 0; k < 4; k++) { const uint64_t adv = (uint64_t)(2 * k); mma3_ss(acc, r_hi + adv, r_lo + adv, c_hi + adv, c_lo + adv, idesc, k == 0); }
-          }
+          for (int k = 0; k < 4; k++) { const uint64_t adv = (uint64_t)(2 * k); mma3_ss(acc, r_hi + adv, r_lo + adv, c_hi + adv, c_lo + adv, idesc, k == 0); }
           tc_commit(BAR(CE + s));
           tc_commit(BAR(SDF + sb));
           if (n == nb - 1) tc_commit(BAR(RE));                 // the row tile may be replaced
         }
       }
-      if (!ok || *(volatile int*)status) { tc_commit(BAR(DRAIN)); mbar_wait(BAR(DRAIN), 0, TC_DRAIN_LIMIT); }     // own instructions in flight finish before TMEM is released
+      if (!ok || *(volatile int*)status) { tc_commit(BAR(DRAIN + prod)); mbar_wait(BAR(DRAIN + prod), 0, TC_DRAIN_LIMIT); }     // own instructions in flight finish before TMEM is released
     }
-  } else if (warp == 2) {
+  } else if (warp == 3) {
     if (lane == 0) {                                          // accumulating products
       bool ok = true; uint32_t g = 0;
       for (int id = blockIdx.x, tt = 0; id < ntiles && ok; id += gridDim.x, tt++) {
@@ -437,8 +470,8 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
         const uint32_t ab = tt & 1;
         if (tt >= 2 && !WAIT(BAR(ACCFREE + ab), ((tt >> 1) - 1) & 1, 25)) { ok = false; break; }     // this accumulator has been written out
         for (int n = 0; n < nb; n++, g++) {
-          const uint32_t s = g % NS, u = g / NS, sb = g & 1;
-          if (!WAIT(BAR(DSF + sb), (g >> 1) & 1, 25) || !WAIT(BAR(C3F + s), u & 1, 25)) { ok = false; break; }
+          const uint32_t s = g % NS, u = g / NS, sb = g % NT, su = g / NT;
+          if (!WAIT(BAR(DSF + sb), su & 1, 25) || !WAIT(BAR(C3F + s), u & 1, 25)) { ok = false; break; }
           tc_fence_after();
           const uint32_t cb = smem_u32(sC3 + s * ATC_C_BYTES);
           const uint64_t c_hi = make_desc<32>(cb), c_lo = make_desc<32>(cb + ATC_C_BYTES / 2);
@@ -450,19 +483,34 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
           if (n == nb - 1) tc_commit(BAR(TDONE));
         }
       }
-      if (!ok || *(volatile int*)status) { tc_commit(BAR(DRAIN + 1)); mbar_wait(BAR(DRAIN + 1), 0, TC_DRAIN_LIMIT); }
+      if (!ok || *(volatile int*)status) { tc_commit(BAR(DRAIN + 2)); mbar_wait(BAR(DRAIN + 2), 0, TC_DRAIN_LIMIT); }
     }
   } else {
     // four threads per tile row: `part` selects 16 of the 64 columns of a block (and of the accumulator)
     constexpr int CW = ATC_CW;
-    const int quad = warp & 3, part = (warp - 3) >> 2, row = quad * 32 + lane, et = (warp - 3) * 32 + lane;   // et: 0..511
+    const int quad = warp & 3, part = (warp - 4) >> 2, row = quad * 32 + lane, et = (warp - 4) * 32 + lane;   // et: 0..511
     const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16) + CW * part;
     constexpr float LOG2E = 1.44269504088896341f;
     const float oscale = MODE == 2 ? 1.f : inv_scale;
     bool ok = true; uint32_t g0 = 0;
+    // write-out of a finished tile: wait for its last accumulating product, scale, store
+    int pend_tt = -1; float pend_os = 0.f; float* pend_row = nullptr;
+    auto write_out = [&]() {
+      ok &= WWAIT(BAR(TDONE), pend_tt & 1, 24);
+      tc_fence_after();
+      uint32_t a[CW];
+      tmem_ld16(lane_base + ATB_COL_ACC + (pend_tt & 1) * 64, a);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(BAR(ACCFREE + (pend_tt & 1)));            // the accumulator is in registers: the MMA warp may reuse it
+#pragma unroll
+      for (int e = 0; e < CW / 4; e++)
+        *reinterpret_cast<float4*>(pend_row + 4 * e) = make_float4(__uint_as_float(a[4 * e]) * pend_os, __uint_as_float(a[4 * e + 1]) * pend_os, __uint_as_float(a[4 * e + 2]) * pend_os, __uint_as_float(a[4 * e + 3]) * pend_os);
+      pend_tt = -1;
+    };
     for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
       int z, r0, b0, nb; decode(id, tt, z, r0, b0, nb);
-      const int ri = r0 + row; const long sb_ = (long)z * T; const uint32_t ab = tt & 1;
+      const int ri = r0 + row; const long sb_ = (long)z * T;
       const float cs = inv_scale * LOG2E * sc.ir1[z] * sc.ic1[z];               // score accumulator -> scaled score in log2 units
       const float idp = MODE == 2 ? 0.f : sc.ir2[z] * sc.ic2[z];                // dP accumulator -> dP
       float mneg_r = 0.f, il_r = 0.f, d_r = 0.f;        // -m log2(e), scale / l, Dv of this row (MODE 0)
@@ -472,13 +520,13 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
       if (MODE == 0) a_scale = row_scale(1.001f * inv_scale * (sc.rnorm[sb_ + ri] * __int_as_float(sc.zmaxn[z]) + fabsf(d_r)), &a_inv);
       if (MODE == 1) a_scale = row_scale(1.001f * inv_scale * (sc.rnorm[sb_ + ri] * __int_as_float(sc.zmaxn[z]) + __int_as_float(sc.zmaxd[z])), &a_inv);
       for (int n = 0; n < nb; n++) {
-        const uint32_t g = g0 + n, s2 = g & 1; const int c0 = (b0 + n) * 64;
-        float* stm = st + s2 * 192; float* stl = stm + 64; float* std_ = stm + 128;
+        const uint32_t g = g0 + n, s2 = g % NT, su = g / NT; const int c0 = (b0 + n) * 64;
+        float* stm = st + (g & 1) * 192; float* stl = stm + 64; float* std_ = stm + 128;
         if (TRANS) {
           if (et < 64) { stm[et] = -Mst[sb_ + c0 + et] * LOG2E; stl[et] = oscale / Lst[sb_ + c0 + et]; if (MODE == 1) std_[et] = Dv[sb_ + c0 + et]; }
           asm volatile("bar.sync 1, %0;" ::"n"(ATC_EW_THREADS) : "memory");
         }
-        ok &= WWAIT(BAR(SDF + s2), (g >> 1) & 1, 24);
+        ok &= WWAIT(BAR(SDF + s2), su & 1, 24);
         tc_fence_after();
         uint32_t a[CW], b[CW];
         tmem_ld16(lane_base + 128 * s2 + ATB_COL_S, a);
@@ -500,24 +548,16 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(BAR(DSF + s2));
+        if (n == 0 && pend_tt >= 0) write_out();            // the previous tile, now that this tile's first block is on its way
       }
-      ok &= WWAIT(BAR(TDONE), tt & 1, 24);
-      tc_fence_after();
       {
-        uint32_t a[CW];
-        tmem_ld16(lane_base + ATB_COL_ACC + ab * 64, a);
-        tmem_wait_ld();
-        tc_fence_before();
-        mbar_arrive(BAR(ACCFREE + ab));                     // the accumulator is in registers: the MMA warp may reuse it
-        const float os = a_inv * sc.ic3[z];
         const int bz = z / H, h = z % H;
-        float* orow = Out + ((long)bz * T + ri) * D + (long)h * ATC_HD + CW * part;
-#pragma unroll
-        for (int e = 0; e < CW / 4; e++)
-          *reinterpret_cast<float4*>(orow + 4 * e) = make_float4(__uint_as_float(a[4 * e]) * os, __uint_as_float(a[4 * e + 1]) * os, __uint_as_float(a[4 * e + 2]) * os, __uint_as_float(a[4 * e + 3]) * os);
+        pend_tt = tt; pend_os = a_inv * sc.ic3[z];
+        pend_row = Out + ((long)bz * T + ri) * D + (long)h * ATC_HD + CW * part;
       }
       g0 += nb;
     }
+    if (pend_tt >= 0) write_out();
     (void)ok;
   }
   tc_fence_before();
@@ -683,7 +723,7 @@ inline int attn_tc_bwd_launch(Ctx* ctx, const AttnPlanes& r1, const AttnPlanes& 
   AtbScales sc{r1.inv, r2.inv, c1.inv, c2.inv, c3.inv, rnorm, zmaxn, zmaxd};
   const int ntr = T / 128, ntiles = ntr * Z;
   const int grid = std::min(ntiles, std::max(1, ctx->sm_count / ntr) * ntr);      // a multiple of the row tiles per problem
-  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, grid, ATC_THREADS, AtbCfg<MODE>::SMEM, maps, M, L, Dv, out, sc, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status, ctx->spin_limit);
+  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, grid, ATB_THREADS, AtbCfg<MODE>::SMEM, maps, M, L, Dv, out, sc, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status, ctx->spin_limit);
   return check_launch("attn_tc_bwd");
 }
 // dQ, dK, dV from Q, K, V, O, dO and the forward's row statistics; Dv receives the row products dO . O
