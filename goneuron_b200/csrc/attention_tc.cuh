@@ -25,8 +25,10 @@
 //   * sixteen elementwise warps (four threads per tile row, 16 columns each): their chain is latency-bound;
 //   * the write-out of a tile deferred until the next tile's first block has been handed on.
 // The same trace now: 2450 cycles per block in the backward kernels, i.e. 68 cycles per 128 x 64 x 16 MMA whichever
-// warp issues it -- the tensor pipe fetching its shared-memory operands (6 KB per MMA with both operands in shared
-// memory, against 32 cycles of arithmetic).  Keeping the row-tile operand in tensor memory would halve that traffic.
+// warp issues it, against 32 cycles of arithmetic.  Keeping the row-tile operand in tensor memory (copied there by the
+// elementwise warps when a tile starts, so that a score product fetches 2 instead of 6 KB per MMA from shared memory)
+// was built and measured: 3 to 14 % slower -- the products with the A operand in tensor memory take as long per MMA,
+// and the planes cost a score stage.  The MMA rate at N = 64 is what is left.
 // P (forward), dS / P^T (backward) go back to tensor memory as fp16 hi | lo pairs, written over the score columns they
 // were computed from -- each thread's 16 columns hold exactly its 8 + 8 packed words, so no thread overwrites what
 // another still has to read -- and are the A operand of the accumulating product.
