@@ -61,7 +61,8 @@ template <int BN> struct TcCfg {
   static constexpr int STAGE_BYTES = 2 * A_PL + 2 * B_PL;
   static constexpr int STAGES = (192 * 1024) / STAGE_BYTES > 8 ? 8 : (192 * 1024) / STAGE_BYTES;
   static constexpr int COLV_FLOATS = TC_EPI_WARPS * BN;                           // per epilogue warp: scale and bias of its BN / 2 columns
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + COLV_FLOATS * 4;
+  static constexpr int STG_FLOATS = TC_EPI_WARPS * 32 * 20;                       // per epilogue warp: 32 rows x 16 (+4) accumulators in transit
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/ + (COLV_FLOATS + STG_FLOATS) * 4;
   static constexpr bool MERGED = BN > 128;                                        // one accumulator per slot
   static constexpr int SLOT_COLS = MERGED ? BN : 2 * BN;
   static constexpr int TMEM_COLS = 2 * SLOT_COLS;
@@ -206,27 +207,103 @@ __device__ __forceinline__ void tc_epilogue_stage(const TcParams& ep, int n0, in
     }
     __syncwarp();
 }
+// `stg`: this warp's staging buffer of 32 rows x TC_STG_LD floats.  The TMEM load gives every thread ITS row (lane =
+// row), and a store of that shape touches 32 different 128-byte lines per instruction -- measured: 19 000 cycles of
+// epilogue per 128 x 256 tile, twice that for the two planes of a plane output, which then set the pace instead of the
+// MMAs.  So the accumulators of 16 columns go through shared memory and come back with four neighbouring lanes on one
+// row (8 rows per instruction); scale, bias, residual, activation and gate are applied on that side, where the residual
+// and gate reads are coalesced too.
+constexpr int TC_STG_LD = 20;
 template <int BN, bool MERGED>
 __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tmem_base, uint32_t acc_main, uint32_t acc_cross,
-                                                 int m0, int n0, int z, int quad, int chalf, int lane, int nkb, int bw, const float* colv) {
+                                                 int m0, int n0, int z, int quad, int chalf, int lane, int nkb, int bw, const float* colv, float* stg) {
     const int z1 = z / ep.batch2, z2 = z % ep.batch2;
     float* C = ep.C + z1 * ep.c_b1 + z2 * ep.c_b2;
     const float* R = ep.R ? ep.R + z1 * ep.r_b1 + z2 * ep.r_b2 : nullptr;
+    const bool vec = (ep.flags & TC_FLAG_VEC) != 0;
+    const float* isb = ep.isb + (long)z * ep.N;
+    const int nch = bw / 64;                                               // chunks of 32 columns per warp
+    if (vec) {
+      // after the transposition: lane -> row 8 t + lane / 4 of the warp's 32 (t = 0..3), columns 4 (lane % 4) .. + 3 of 16
+      const int rl = lane >> 2, c4 = (lane & 3) * 4, rbase = m0 + quad * 32;
+      float isa4[4], osc4[4];
+#pragma unroll
+      for (int t = 0; t < 4; t++) {
+        const int row = rbase + 8 * t + rl; const bool row_ok = row < ep.M;
+        isa4[t] = row_ok ? ep.isa[(long)z * ep.M + row] : 1.f;              // 1 / (scale of this output row's A vector), a power of two
+        osc4[t] = 1.f;                                                       // plane output: this row's scale
+        if (ep.out_p0 && row_ok) {
+          const float an = ep.a_rownorm[row], bound = sqrtf(fmaf(an, an, 1.f)) * sqrtf((float)ep.K + 1.f) * __int_as_float(*ep.b_maxabs);
+          float oinv; osc4[t] = row_scale(bound, &oinv);
+          if (n0 == 0 && chalf == 0 && c4 == 0) ep.out_inv[row] = oinv;
+        }
+      }
+      for (int cc = 0; cc < nch; cc++) {
+        const int c = chalf * nch + cc, col0 = n0 + c * 32;
+        if (col0 >= ep.N) break;
+        uint32_t r[32], q[MERGED ? 1 : 32];
+        if (nkb > 0) {
+          const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
+          tmem_ld32(taddr + acc_main, r);
+          if constexpr (!MERGED) tmem_ld32(taddr + acc_cross, q);
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if constexpr (!MERGED) {
+#pragma unroll
+            for (int j = 0; j < 32; j++) r[j] = __float_as_uint(__uint_as_float(r[j]) + __uint_as_float(q[j]));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j++) r[j] = 0u;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+          const int col = col0 + 16 * h + c4; const bool col_ok = col < ep.N;
+          // residual and gate of this half, fetched before the exchange so that their latency overlaps it
+          float4 rv[4], mv[4];
+#pragma unroll
+          for (int t = 0; t < 4; t++) {
+            const int row = rbase + 8 * t + rl; const bool in = col_ok && row < ep.M;
+            rv[t] = (R && in) ? *reinterpret_cast<const float4*>(R + (long)row * ep.ldr + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+            mv[t] = (ep.mask && in) ? *reinterpret_cast<const float4*>(ep.mask + (long)(row / ep.mask_group) * ep.mask_ld + col) : make_float4(1.f, 1.f, 1.f, 1.f);
+          }
+          __syncwarp();                                       // the previous half has been read back
+#pragma unroll
+          for (int j = 0; j < 16; j += 4) {
+            const float4 a = make_float4(__uint_as_float(r[16 * h + j]), __uint_as_float(r[16 * h + j + 1]), __uint_as_float(r[16 * h + j + 2]), __uint_as_float(r[16 * h + j + 3]));
+            *reinterpret_cast<float4*>(stg + lane * TC_STG_LD + j) = a;
+          }
+          __syncwarp();
+          const float4 sv = *reinterpret_cast<const float4*>(colv + cc * 32 + 16 * h + c4), bv = *reinterpret_cast<const float4*>(colv + BN / 2 + cc * 32 + 16 * h + c4);
+#pragma unroll
+          for (int t = 0; t < 4; t++) {
+            const int row = rbase + 8 * t + rl;
+            if (!col_ok || row >= ep.M) continue;
+            const float4 a = *reinterpret_cast<const float4*>(stg + (8 * t + rl) * TC_STG_LD + c4);
+            const float isa = isa4[t];
+            float4 v;
+            v.x = a.x * isa * sv.x + bv.x + rv[t].x; v.y = a.y * isa * sv.y + bv.y + rv[t].y;
+            v.z = a.z * isa * sv.z + bv.z + rv[t].z; v.w = a.w * isa * sv.w + bv.w + rv[t].w;
+            if (ep.act == GN_ACT_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+            if (!(mv[t].x > 0.f)) v.x = 0.f; if (!(mv[t].y > 0.f)) v.y = 0.f; if (!(mv[t].z > 0.f)) v.z = 0.f; if (!(mv[t].w > 0.f)) v.w = 0.f;
+            if (ep.out_p0) {
+              uint2 p0, p1; split2_pair(v.x, v.y, osc4[t], p0.x, p1.x); split2_pair(v.z, v.w, osc4[t], p0.y, p1.y);
+              const long o = (long)row * ep.out_ldp + col;
+              *reinterpret_cast<uint2*>(ep.out_p0 + o) = p0; *reinterpret_cast<uint2*>(ep.out_p1 + o) = p1;
+              if (ep.c_last && row % ep.last_T == ep.last_T - 1) *reinterpret_cast<float4*>(ep.c_last + (long)(row / ep.last_T) * ep.N + col) = v;
+            } else *reinterpret_cast<float4*>(C + (long)row * ep.ldc + col) = v;
+          }
+        }
+      }
+      __syncwarp();
+      return;
+    }
+    // scalar path (unaligned operands, NCHW store): one output row per thread
     const int row = m0 + quad * 32 + lane;
     const bool row_ok = row < ep.M;
     const float* Rrow = (R && row_ok) ? R + (long)row * ep.ldr : nullptr;
     const float* Mrow = (ep.mask && row_ok) ? ep.mask + (long)(row / ep.mask_group) * ep.mask_ld : nullptr;
     float* Crow = C + (long)row * ep.ldc;
-    const bool vec = (ep.flags & TC_FLAG_VEC) != 0;
-    const float isa = row_ok ? ep.isa[(long)z * ep.M + row] : 1.f;       // 1 / (scale of this output row's A vector), a power of two
-    const float* isb = ep.isb + (long)z * ep.N;
-    float osc = 1.f;                                                       // plane output: this row's scale
-    if (ep.out_p0 && row_ok) {
-      const float an = ep.a_rownorm[row], bound = sqrtf(fmaf(an, an, 1.f)) * sqrtf((float)ep.K + 1.f) * __int_as_float(*ep.b_maxabs);
-      float oinv; osc = row_scale(bound, &oinv);
-      if (n0 == 0 && chalf == 0) ep.out_inv[row] = oinv;
-    }
-    const int nch = bw / 64;                                               // chunks of 32 columns per warp
+    const float isa = row_ok ? ep.isa[(long)z * ep.M + row] : 1.f;
     for (int cc = 0; cc < nch; cc++) {
       const int c = chalf * nch + cc, col0 = n0 + c * 32;
       if (col0 >= ep.N) break;
@@ -235,50 +312,21 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(c * 32);
         tmem_ld32(taddr + acc_main, r);
         if constexpr (!MERGED) tmem_ld32(taddr + acc_cross, q);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
       }
-      auto acc = [&](int j) -> float {
-        if (nkb <= 0) return 0.f;
-        if constexpr (MERGED) return __uint_as_float(r[j]); else return __uint_as_float(r[j]) + __uint_as_float(q[j]);
-      };
-      if (vec) {
-        float4 rv[8], mv[8];
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-          const bool in = col0 + 4 * j < ep.N;
-          rv[j] = (Rrow && in) ? *reinterpret_cast<const float4*>(Rrow + col0 + 4 * j) : make_float4(0.f, 0.f, 0.f, 0.f);
-          mv[j] = (Mrow && in) ? *reinterpret_cast<const float4*>(Mrow + col0 + 4 * j) : make_float4(1.f, 1.f, 1.f, 1.f);
-        }
-        if (nkb > 0) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 8; j++) {
-          if (!row_ok || col0 + 4 * j >= ep.N) continue;
-          const float4 sv = *reinterpret_cast<const float4*>(colv + cc * 32 + 4 * j), bv = *reinterpret_cast<const float4*>(colv + BN / 2 + cc * 32 + 4 * j);
-          float4 v;
-          v.x = acc(4 * j) * isa * sv.x + bv.x + rv[j].x; v.y = acc(4 * j + 1) * isa * sv.y + bv.y + rv[j].y;
-          v.z = acc(4 * j + 2) * isa * sv.z + bv.z + rv[j].z; v.w = acc(4 * j + 3) * isa * sv.w + bv.w + rv[j].w;
-          if (ep.act == GN_ACT_RELU) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
-          if (!(mv[j].x > 0.f)) v.x = 0.f; if (!(mv[j].y > 0.f)) v.y = 0.f; if (!(mv[j].z > 0.f)) v.z = 0.f; if (!(mv[j].w > 0.f)) v.w = 0.f;
-          if (ep.out_p0) {
-            uint2 a, b; split2_pair(v.x, v.y, osc, a.x, b.x); split2_pair(v.z, v.w, osc, a.y, b.y);
-            const long o = (long)row * ep.out_ldp + col0 + 4 * j;
-            *reinterpret_cast<uint2*>(ep.out_p0 + o) = a; *reinterpret_cast<uint2*>(ep.out_p1 + o) = b;
-            if (ep.c_last && row % ep.last_T == ep.last_T - 1) *reinterpret_cast<float4*>(ep.c_last + (long)(row / ep.last_T) * ep.N + col0 + 4 * j) = v;
-          } else *reinterpret_cast<float4*>(Crow + col0 + 4 * j) = v;
-        }
-      } else {
-        if (nkb > 0) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-        for (int j = 0; j < 32; j++) {
-          const int col = col0 + j;
-          if (!row_ok || col >= ep.N) continue;
-          float v = acc(j) * isa * isb[col];
-          if (ep.bias) v += ep.bias[col];
-          if (Rrow) v += Rrow[col];
-          if (ep.act == GN_ACT_RELU) v = fmaxf(v, 0.f);
-          if (Mrow && !(Mrow[col] > 0.f)) v = 0.f;
-          if (ep.nchw_P > 0) C[((long)(row / ep.nchw_P) * ep.N + col) * ep.nchw_P + row % ep.nchw_P] = v;
-          else Crow[col] = v;
-        }
+      for (int j = 0; j < 32; j++) {
+        const int col = col0 + j;
+        if (!row_ok || col >= ep.N) continue;
+        float a = 0.f;
+        if (nkb > 0) { if constexpr (MERGED) a = __uint_as_float(r[j]); else a = __uint_as_float(r[j]) + __uint_as_float(q[j]); }
+        float v = a * isa * isb[col];
+        if (ep.bias) v += ep.bias[col];
+        if (Rrow) v += Rrow[col];
+        if (ep.act == GN_ACT_RELU) v = fmaxf(v, 0.f);
+        if (Mrow && !(Mrow[col] > 0.f)) v = 0.f;
+        if (ep.nchw_P > 0) C[((long)(row / ep.nchw_P) * ep.N + col) * ep.nchw_P + row % ep.nchw_P] = v;
+        else Crow[col] = v;
       }
     }
   }
@@ -417,6 +465,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
   } else {
     const int quad = warp & 3, chalf = (warp - 2) >> 2; uint32_t lt = 0;
     float* colv = colv_all + (warp - 2) * BN;
+    float* stg = colv_all + Cfg::COLV_FLOATS + (warp - 2) * 32 * TC_STG_LD;
     int tile, half;
     for (int w = 0; work(w, tile, half); w++) {
       int m0, n0, z, kb0, nkb; if (!decode(tile, half, m0, n0, z, kb0, nkb)) continue;
@@ -428,7 +477,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
       ok = __shfl_sync(0xffffffffu, ok, 0);
       if (!ok) { if (lane == 0 && !*abort_flag) give_up(3); break; }
       tc_fence_after();
-      tc_epilogue_tile<BN, MERGED>(ep, tmem_base, slot * SLOT_COLS, slot * SLOT_COLS + BN, m0, n0, z, quad, chalf, lane, nkb, bw, colv);
+      tc_epilogue_tile<BN, MERGED>(ep, tmem_base, slot * SLOT_COLS, slot * SLOT_COLS + BN, m0, n0, z, quad, chalf, lane, nkb, bw, colv, stg);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty0 + 8 * slot);
