@@ -496,6 +496,12 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
     const float oscale = MODE == 2 ? 1.f : inv_scale;
     bool ok = true; uint32_t g0 = 0;
     // write-out of a finished tile: wait for its last accumulating product, scale, store
+    float pf_m = 0.f, pf_l = 1.f, pf_d = 0.f;              // TRANS: prefetched statistics of column et of the coming block
+    if (TRANS && et < 64 && (int)blockIdx.x < ntiles) {
+      int z0, r00, b00, nb0; decode(blockIdx.x, 0, z0, r00, b00, nb0);
+      const long i0 = (long)z0 * T + b00 * 64 + et;
+      pf_m = Mst[i0]; pf_l = Lst[i0]; if (MODE == 1) pf_d = Dv[i0];
+    }
     int pend_tt = -1; float pend_os = 0.f; float* pend_row = nullptr;
     auto write_out = [&]() {
       ok &= WWAIT(BAR(TDONE), pend_tt & 1, 24);
@@ -525,7 +531,15 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
         const uint32_t g = g0 + n, s2 = g % NT, su = g / NT; const int c0 = (b0 + n) * 64;
         float* stm = st + (g & 1) * 192; float* stl = stm + 64; float* std_ = stm + 128;
         if (TRANS) {
-          if (et < 64) { stm[et] = -Mst[sb_ + c0 + et] * LOG2E; stl[et] = oscale / Lst[sb_ + c0 + et]; if (MODE == 1) std_[et] = Dv[sb_ + c0 + et]; }
+          // column statistics of this block, fetched while the previous block was processed; the next block's (the next
+          // tile's first block's) are requested here and arrive under this block's work
+          if (et < 64) {
+            stm[et] = -pf_m * LOG2E; stl[et] = oscale / pf_l; if (MODE == 1) std_[et] = pf_d;
+            long nxt = -1;
+            if (n + 1 < nb) nxt = sb_ + c0 + 64 + et;
+            else if (id + (int)gridDim.x < ntiles) { int zn, rn, bn0, nbn; decode(id + (int)gridDim.x, tt + 1, zn, rn, bn0, nbn); nxt = (long)zn * T + bn0 * 64 + et; }
+            if (nxt >= 0) { pf_m = Mst[nxt]; pf_l = Lst[nxt]; if (MODE == 1) pf_d = Dv[nxt]; }
+          }
           asm volatile("bar.sync 1, %0;" ::"n"(ATC_EW_THREADS) : "memory");
         }
         ok &= WWAIT(BAR(SDF + s2), su & 1, 24);
@@ -663,19 +677,28 @@ inline bool attn_tc_supported(Ctx* ctx, int hd, int T, int B, int H, int D) {
 }
 // The planes of one tensor: hi and lo, as rows [Z][T][64] and / or transposed [Z][64][T]; one inverse scale per problem.
 struct AttnPlanes { __half *rh = nullptr, *rl = nullptr, *ch = nullptr, *cl = nullptr; float* inv = nullptr; float* rnorm = nullptr; int* nmax = nullptr; };
-// Lays out the scratch for `n` tensors (rows / cols / norms wanted per tensor), runs the two passes.
-// Scratch slots: 2 i = row planes of tensor i, 2 i + 1 = its transposed planes, 8 = per-problem words, 9 = row norms.
+// Planes of Q, K and V that a training forward pass leaves behind for the backward pass of the same layer (row and
+// transposed planes of each, V's row norms): the backward pass then only has to prepare dO.  Costs 24 bytes per element
+// of a projection and layer, kept until the layer's backward pass; if the allocation fails the backward pass prepares
+// its operands itself as before.  GONEURON_CUDA_ATTENTION_KEEP_PLANES=0 switches it off.
+struct AttnSaved { DevBuf store; bool valid = false; AttnPlanes q, k, v; int B = 0; };
+inline bool attn_keep_planes() { static const bool on = [] { const char* e = getenv("GONEURON_CUDA_ATTENTION_KEEP_PLANES"); return !(e && !strcmp(e, "0")); }(); return on; }
+// Lays out the storage for `n` tensors (rows / cols / norms wanted per tensor) and runs the two passes.  Storage: the
+// context's scratch (slots 2 i = row planes of tensor i, 2 i + 1 = its transposed planes, 8 = per-problem words, 9 = row
+// norms), or, when `store` is given, that buffer (planes of tensor i at (2 i) ne and (2 i + 1) ne, then words, then norms).
+inline size_t attn_store_floats(int n, int Z, int T) { return (size_t)2 * n * Z * T * ATC_HD + (size_t)Z * 16 + (size_t)Z * T * 2; }
 inline int attn_tc_prepare(Ctx* ctx, int n, const float* const* X, const bool* want_rows, const bool* want_cols, const bool* want_norm, AttnPlanes* out,
-                           int B, int T, int D, int H, int** zwords_extra) {
+                           int B, int T, int D, int H, int** zwords_extra, float* store = nullptr) {
   const int Z = B * H; const size_t ne = (size_t)Z * T * ATC_HD;      // elements of a tensor; hi + lo planes = ne floats
-  float* words; GN_TRY(attn_tc_buf(ctx, 8, (size_t)Z * 16, &words));   // per tensor: amax, inv, nmax; one extra row for the caller
-  float* norms = nullptr; GN_TRY(attn_tc_buf(ctx, 9, (size_t)Z * T * 2, &norms));
+  float *words, *norms;
+  if (store) { words = store + (size_t)2 * n * ne; norms = words + (size_t)Z * 16; }
+  else { GN_TRY(attn_tc_buf(ctx, 8, (size_t)Z * 16, &words)); GN_TRY(attn_tc_buf(ctx, 9, (size_t)Z * T * 2, &norms)); }   // per tensor: amax, inv, nmax; one extra row for the caller
   GN_CUDA(cudaMemsetAsync(words, 0, (size_t)Z * 16 * sizeof(float), ctx->stream));
   AttnPrepJobs jobs{}; int nn = 0;
   for (int i = 0; i < n; i++) {
     AttnPrepJob& j = jobs.j[i]; j.X = X[i];
-    if (want_rows[i]) { float* p; GN_TRY(attn_tc_buf(ctx, 2 * i, ne, &p)); j.rh = reinterpret_cast<__half*>(p); j.rl = j.rh + ne; }
-    if (want_cols[i]) { float* p; GN_TRY(attn_tc_buf(ctx, 2 * i + 1, ne, &p)); j.ch = reinterpret_cast<__half*>(p); j.cl = j.ch + ne; }
+    if (want_rows[i]) { float* p; if (store) p = store + (size_t)(2 * i) * ne; else GN_TRY(attn_tc_buf(ctx, 2 * i, ne, &p)); j.rh = reinterpret_cast<__half*>(p); j.rl = j.rh + ne; }
+    if (want_cols[i]) { float* p; if (store) p = store + (size_t)(2 * i + 1) * ne; else GN_TRY(attn_tc_buf(ctx, 2 * i + 1, ne, &p)); j.ch = reinterpret_cast<__half*>(p); j.cl = j.ch + ne; }
     j.amax = reinterpret_cast<int*>(words) + (size_t)(3 * i) * Z; j.inv = words + (size_t)(3 * i + 1) * Z;
     if (want_norm[i]) {
       if (nn >= 2) return fail(GN_ERR_INVALID_ARG, "attn_tc_prepare: at most two tensors with row norms");
@@ -698,11 +721,27 @@ inline int attn_tc_maps_cols(Ctx* ctx, CUtensorMap* m, const AttnPlanes& p, int 
   GN_TRY(tc_make_map_bf16_raw(ctx, &m[0], p.ch, T, ATC_HD, T, Z, 0, ATC_HD, 64, CU_TENSOR_MAP_DATA_TYPE_FLOAT16));
   return tc_make_map_bf16_raw(ctx, &m[1], p.cl, T, ATC_HD, T, Z, 0, ATC_HD, 64, CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
 }
-inline int attn_tc_fwd(Ctx* ctx, const float* Q, const float* K, const float* V, float* O, float* M, float* L, int B, int T, int D, int H, int causal) {
+inline int attn_tc_fwd(Ctx* ctx, const float* Q, const float* K, const float* V, float* O, float* M, float* L, int B, int T, int D, int H, int causal,
+                       AttnSaved* save = nullptr) {
   const int Z = B * H;
-  const float* X[3] = {Q, K, V}; const bool rows[3] = {true, true, false}, cols[3] = {false, false, true}, norm[3] = {false, false, false};
+  const float* X[3] = {Q, K, V};
   AttnPlanes p[3];
-  GN_TRY(attn_tc_prepare(ctx, 3, X, rows, cols, norm, p, B, T, D, H, nullptr));
+  if (save) save->valid = false;
+  if (save && attn_keep_planes()) {
+    const size_t need = attn_store_floats(3, Z, T);
+    if (save->store.n < need) {
+      GN_CUDA(cudaStreamSynchronize(ctx->stream));
+      if (save->store.alloc(need) != GN_OK) { cudaGetLastError(); save = nullptr; }      // no room: the backward pass prepares its own operands
+    }
+  } else save = nullptr;
+  if (save) {
+    const bool all[3] = {true, true, true}, norm[3] = {false, false, true};
+    GN_TRY(attn_tc_prepare(ctx, 3, X, all, all, norm, p, B, T, D, H, nullptr, save->store.p));
+    save->q = p[0]; save->k = p[1]; save->v = p[2]; save->B = B; save->valid = true;
+  } else {
+    const bool rows[3] = {true, true, false}, cols[3] = {false, false, true}, norm[3] = {false, false, false};
+    GN_TRY(attn_tc_prepare(ctx, 3, X, rows, cols, norm, p, B, T, D, H, nullptr));
+  }
   AttnMaps<6> maps;
   GN_TRY(attn_tc_maps_rows(ctx, &maps.m[0], p[0], T, Z, ATC_BQ)); GN_TRY(attn_tc_maps_rows(ctx, &maps.m[2], p[1], T, Z, ATC_BK)); GN_TRY(attn_tc_maps_cols(ctx, &maps.m[4], p[2], T, Z));
   GN_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATF_SMEM));
@@ -730,15 +769,22 @@ inline int attn_tc_bwd_launch(Ctx* ctx, const AttnPlanes& r1, const AttnPlanes& 
 }
 // dQ, dK, dV from Q, K, V, O, dO and the forward's row statistics; Dv receives the row products dO . O
 inline int attn_tc_bwd(Ctx* ctx, const float* Q, const float* K, const float* V, const float* O, const float* dO, const float* M, const float* L, float* Dv,
-                       float* dQ, float* dK, float* dV, int B, int T, int D, int H, int causal) {
+                       float* dQ, float* dK, float* dV, int B, int T, int D, int H, int causal, AttnSaved* saved = nullptr) {
   const long rows = (long)B * T * H; const int Z = B * H;
   if (D == H * ATC_HD && ((reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(O)) & 15) == 0)
     GN_LAUNCH(ctx, attn_rowdot64_kernel, (unsigned)std::min<long>(cdiv(rows, 32), (long)ctx->sm_count * 16), 256, 0, dO, O, Dv, T, H, rows);
   else GN_LAUNCH(ctx, attn_rowdot_kernel, cdiv(rows, 8), 256, 0, dO, O, Dv, T, D, H, ATC_HD, rows);
-  // tensors: 0 = Q, 1 = K, 2 = V, 3 = dO
-  const float* X[4] = {Q, K, V, dO}; const bool rw[4] = {true, true, true, true}, cl[4] = {true, true, false, true}, nm[4] = {false, false, true, true};
   AttnPlanes p[4]; int* zmaxd = nullptr;
-  GN_TRY(attn_tc_prepare(ctx, 4, X, rw, cl, nm, p, B, T, D, H, &zmaxd));
+  if (saved && saved->valid && saved->B == B) {
+    // Q, K, V were prepared by this layer's forward pass: only dO is left
+    const float* X[1] = {dO}; const bool yes[1] = {true};
+    GN_TRY(attn_tc_prepare(ctx, 1, X, yes, yes, yes, &p[3], B, T, D, H, &zmaxd));
+    p[0] = saved->q; p[1] = saved->k; p[2] = saved->v; saved->valid = false;
+  } else {
+    // tensors: 0 = Q, 1 = K, 2 = V, 3 = dO
+    const float* X[4] = {Q, K, V, dO}; const bool rw[4] = {true, true, true, true}, cl[4] = {true, true, false, true}, nm[4] = {false, false, true, true};
+    GN_TRY(attn_tc_prepare(ctx, 4, X, rw, cl, nm, p, B, T, D, H, &zmaxd));
+  }
   GN_LAUNCH(ctx, attn_dmax_kernel, Z, 128, 0, (const float*)Dv, T, zmaxd);
   const AttnPlanes &q = p[0], &k = p[1], &v = p[2], &g = p[3];
   GN_TRY(attn_tc_bwd_launch<0>(ctx, q, g, k, v, k, g.rnorm, v.nmax, nullptr, M, L, Dv, dQ, B, T, D, H, causal));

@@ -75,6 +75,7 @@ struct LayerRT {
   DevBuf out, z;                       // activation / pre-activation  [cap, out_size]
   DevBuf q, k, v, att, r1, n1, mid, r2, stat;   // TransformerBlock
   DevBuf att_m, att_l, att_d;          // fused attention: per-row softmax maximum, sum, and dO.O  [batch*heads*T]
+  AttnSaved attn_saved;                // tcgen05 attention: operand planes of Q, K, V kept from the training forward pass for the backward pass
   DevBuf gate, up, zlast, rope;        // TransformerBlock variants: SwiGLU projections [tokens, ff]; GELU: last token's pre-activation [batch, ff]; cos | sin table
   int ff_act = GN_ACT_RELU; bool rms = false, use_rope = false;
   DevBuf mid_inv, mid_last;            // FFN hidden activation kept as operand planes (in `mid`): row scales [tokens], fp32 last-token rows [batch, ff]
@@ -513,7 +514,7 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
           GN_LAUNCH(ctx, rope_kernel, ew_grid(ctx, tot), 256, 0, l.k.p, (const float*)l.rope.p, (long)N, T, D, D / d.heads, 1.f);
         }
         if (use_fused_attention(d)) {
-          if (attn_tc_supported(ctx, D / d.heads, T, B, d.heads, D)) GN_TRY(attn_tc_fwd(ctx, l.q.p, l.k.p, l.v.p, l.att.p, l.att_m.p, l.att_l.p, B, T, D, d.heads, d.causal));
+          if (attn_tc_supported(ctx, D / d.heads, T, B, d.heads, D)) GN_TRY(attn_tc_fwd(ctx, l.q.p, l.k.p, l.v.p, l.att.p, l.att_m.p, l.att_l.p, B, T, D, d.heads, d.causal, training ? &l.attn_saved : nullptr));
           else GN_TRY(attn_fwd(ctx, D / d.heads, l.q.p, l.k.p, l.v.p, l.att.p, l.att_m.p, l.att_l.p, B, T, D, d.heads, d.causal));
         } else {
           float* P; GN_TRY(ensure(m, S_ATT0, (size_t)B * d.heads * T * T, &P));
@@ -703,7 +704,7 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
   GN_TRY(ensure(m, S_ND0, ND, &dQ)); GN_TRY(ensure(m, S_ND1, ND, &dK)); GN_TRY(ensure(m, S_ND4, ND, &dV));   // dR2 / comb are dead by now
   if (fused) {
     static const bool tc_bwd = [] { const char* e = getenv("GONEURON_CUDA_ATTENTION_BWD"); return !(e && !strcmp(e, "mma")); }();
-    if (tc_bwd && attn_tc_supported(ctx, hd, T, B, Hh, D)) GN_TRY(attn_tc_bwd(ctx, l.q.p, l.k.p, l.v.p, l.att.p, dA, l.att_m.p, l.att_l.p, l.att_d.p, dQ, dK, dV, B, T, D, Hh, d.causal));
+    if (tc_bwd && attn_tc_supported(ctx, hd, T, B, Hh, D)) GN_TRY(attn_tc_bwd(ctx, l.q.p, l.k.p, l.v.p, l.att.p, dA, l.att_m.p, l.att_l.p, l.att_d.p, dQ, dK, dV, B, T, D, Hh, d.causal, &l.attn_saved));
     else GN_TRY(attn_bwd(ctx, hd, l.q.p, l.k.p, l.v.p, l.att.p, dA, l.att_m.p, l.att_l.p, l.att_d.p, dQ, dK, dV, B, T, D, Hh, d.causal));
   } else {
     const long TD = (long)T * D, TT = (long)T * T; const float inv_scale = 1.f / sqrtf((float)hd); const long rows = (long)B * Hh * T;
