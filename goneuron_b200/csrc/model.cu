@@ -102,6 +102,7 @@ struct gn_model {
   int cur_first_sample = 0;             // global index of the first sample of the batch being processed (Dropout's stream position)
   int cur_global_batch = 0;             // size of the global batch being processed (all ranks)
   bool wplanes_layerwise = false;       // this step renewed the weight planes layer by layer behind the parameter update
+  const float* fwd_planes_src = nullptr; gn::BfPlanes fwd_planes{};     // operand planes of the tensor at fwd_planes_src, written by the LayerNorm that produced it
   float lr = 1e-3f, b1 = 0.9f, b2 = 0.999f, eps = 1e-8f; int timestep = 0;
   int cap = 0;                          // batch capacity of the activation buffers
   gn::DevBuf xin, yin, lossg, loss_s, loss_sum;
@@ -118,7 +119,7 @@ struct gn_model {
 
 namespace gn {
 
-enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_NFF2, S_NFF3, S_RN, S_NFFI, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_NFF2, S_NFF3, S_RN, S_NFFI, S_LNP0, S_LNI0, S_LNP1, S_LNI1, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
 
 static int ensure(gn_model* m, int slot, size_t n, float** out) {
   if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
@@ -283,13 +284,19 @@ static int colsum(gn_model* m, const float* in, long ld, int R, int C, float* ou
 }
 
 // LayerNorm forward: the row-in-registers kernel when the row length allows it.
-static int layernorm_forward(Ctx* ctx, const float* x, const float* gamma, const float* beta, float* y, float* mean, float* sd, long rows, int n) {
+// `po` (optional): the output also as operand planes; *emitted tells the caller whether the kernel that ran could do it
+// (the row-in-registers kernels for widths 128, 256, 512, 1024).
+static bool layernorm_vec_width(int n) { return n == 128 || n == 256 || n == 512 || n == 1024; }
+static int layernorm_forward(Ctx* ctx, const float* x, const float* gamma, const float* beta, float* y, float* mean, float* sd, long rows, int n,
+                             const RowPlaneOut* po = nullptr, bool* emitted = nullptr) {
   const bool vec = n % 128 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(beta)) & 15) == 0;
+  const RowPlaneOut out = (po && vec && layernorm_vec_width(n)) ? *po : RowPlaneOut{};
+  if (emitted) *emitted = out.p0 != nullptr;
   switch (vec ? n / 128 : 0) {
-    case 1: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<1>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f); break;
-    case 2: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<2>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f); break;
-    case 4: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<4>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f); break;
-    case 8: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<8>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f); break;
+    case 1: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<1>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f, out); break;
+    case 2: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<2>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f, out); break;
+    case 4: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<4>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f, out); break;
+    case 8: GN_LAUNCH(ctx, layernorm_fwd_vec_kernel<8>, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, 1e-5f, out); break;
     default: GN_LAUNCH(ctx, layernorm_fwd_kernel, cdiv(rows, 8), 256, 0, x, gamma, beta, y, mean, sd, rows, n, 1e-5f);
   }
   return check_launch("layernorm_forward");
@@ -298,15 +305,19 @@ static int layernorm_forward(Ctx* ctx, const float* x, const float* gamma, const
 
 // The two norms of a TransformerBlock: LayerNorm (row mean and deviation in stat[0:rows], stat[rows:2 rows]) or RMSNorm
 // (row RMS in stat[0:rows]); rmsnorm.go:157-240, :246-336.
-static int block_norm_forward(Ctx* ctx, bool rms, const float* x, const float* gamma, const float* beta, float* y, float* stat, long rows, int n) {
-  if (!rms) return layernorm_forward(ctx, x, gamma, beta, y, stat, stat + rows, rows, n);
+static int block_norm_forward(Ctx* ctx, bool rms, const float* x, const float* gamma, const float* beta, float* y, float* stat, long rows, int n,
+                              const RowPlaneOut* po = nullptr, bool* emitted = nullptr) {
+  if (emitted) *emitted = false;
+  if (!rms) return layernorm_forward(ctx, x, gamma, beta, y, stat, stat + rows, rows, n, po, emitted);
   GN_LAUNCH(ctx, rmsnorm_fwd_kernel, cdiv(rows, 8), 256, 0, x, gamma, y, stat, rows, n, 1e-5f);
   return check_launch("rmsnorm_forward");
 }
 static int layernorm_backward(gn_model* m, const float* g, const float* x, const float* gamma, const float* mean, const float* sd, float* dx,
-                              float* gGamma, float* gBeta, long rows, int n);
-static int block_norm_backward(gn_model* m, bool rms, const float* g, const float* x, const float* gamma, const float* stat, float* dx, float* gGamma, float* gBeta, long rows, int n) {
-  if (!rms) return layernorm_backward(m, g, x, gamma, stat, stat + rows, dx, gGamma, gBeta, rows, n);
+                              float* gGamma, float* gBeta, long rows, int n, const RowPlaneOut* po = nullptr, bool* emitted = nullptr);
+static int block_norm_backward(gn_model* m, bool rms, const float* g, const float* x, const float* gamma, const float* stat, float* dx, float* gGamma, float* gBeta, long rows, int n,
+                               const RowPlaneOut* po = nullptr, bool* emitted = nullptr) {
+  if (emitted) *emitted = false;
+  if (!rms) return layernorm_backward(m, g, x, gamma, stat, stat + rows, dx, gGamma, gBeta, rows, n, po, emitted);
   Ctx* ctx = &m->ctx->c;
   const int chunks = (int)std::max<long>(1, std::min<long>(rows / 64, 128));
   float* part; GN_TRY(ensure(m, S_PART2, (size_t)chunks * n, &part));
@@ -328,6 +339,21 @@ static int rope_table(Ctx* ctx, LayerRT& l) {
   }
   GN_TRY(l.rope.alloc(tab.size()));
   GN_CUDA(copy_h2d(ctx, l.rope.p, tab.data(), tab.size() * 4)); return GN_OK;
+}
+
+// A LayerNorm of a block can hand its output to the next contraction as operand planes (RowPlaneOut) when that
+// contraction runs on the tensor-core engine; `slotp` / `sloti` receive the planes and the inverse row scales.
+static bool norm_planes_wanted(Ctx* ctx, bool rms, int rows, int n, int consumer_n) {
+  static const bool off = getenv("GONEURON_CUDA_NO_NORM_PLANES") != nullptr;
+  if (off || rms || force_simt_engine() || !layernorm_vec_width(n)) return false;
+  GemmDesc g; g.M = rows; g.N = consumer_n; g.K = n; g.sa_m = n; g.sa_k = 1; g.sb_k = 1; g.sb_n = n;
+  return gemm_tc_eligible(ctx, g) && !gemm_outer_small_ok(g);
+}
+static int norm_planes_alloc(gn_model* m, int slotp, int sloti, int rows, int n, RowPlaneOut* po, BfPlanes* planes, float* rownorm) {
+  float *pp, *pi; GN_TRY(ensure(m, slotp, (size_t)rows * n, &pp)); GN_TRY(ensure(m, sloti, (size_t)rows, &pi));
+  *planes = BfPlanes{reinterpret_cast<__half*>(pp), pi, rows, n, n, 1};
+  *po = RowPlaneOut{planes->p0(), planes->p1(), pi, rownorm};
+  return GN_OK;
 }
 
 // The fused kernels (attention.cuh) are the default; GONEURON_CUDA_ATTENTION=unfused selects the path that
@@ -415,6 +441,7 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
   Ctx* ctx = &m->ctx->c;
   GN_TRY(wplanes_refresh(ctx, m->wplanes));          // no-op unless the parameters changed since the last pass
   ctx->weight_planes = &m->wplanes;
+  m->fwd_planes_src = nullptr;
   const float* cur = x;
   for (size_t li = 0; li < m->L.size(); li++) {
     LayerRT& l = m->L[li]; const gn_layer_desc& d = l.d; const float* p = m->params.p + l.p_off;
@@ -501,11 +528,16 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         cur = l.out.p; break; }
       case GN_LAYER_TRANSFORMER_BLOCK: {
         const int T = d.seq_len, D = d.dim, F = d.ff_dim; const int N = B * T; BlockParams bp = block_params(p, D, F, l.rms, l.ff_act);
-        GN_TRY(gemm_nt(ctx, N, D, D, cur, D, bp.wq, bp.bq, l.q.p, D));
-        {   // the K and V projections read the same input: its operand planes are still in the engine's scratch
-          GemmDesc g; g.M = N; g.N = D; g.K = D; g.A = cur; g.sa_m = D; g.sa_k = 1; g.sb_k = 1; g.sb_n = D; g.ldc = D; g.reuse_a_planes = true;
+        {   // the Q, K and V projections read the same input: its operand planes come from the LayerNorm that produced it
+            // (the previous block's), or are still in the engine's scratch after the first of the three
+          GemmDesc g; g.M = N; g.N = D; g.K = D; g.A = cur; g.sa_m = D; g.sa_k = 1; g.sb_k = 1; g.sb_n = D; g.ldc = D;
+          const bool have = m->fwd_planes_src == cur && m->fwd_planes.rows == N && m->fwd_planes.K == D;
+          if (have) g.a_planes = &m->fwd_planes;
+          g.B = bp.wq; g.bias = bp.bq; g.C = l.q.p; GN_TRY(gemm(ctx, g));
+          g.reuse_a_planes = true;
           g.B = bp.wk; g.bias = bp.bk; g.C = l.k.p; GN_TRY(gemm(ctx, g));
           g.B = bp.wv; g.bias = bp.bv; g.C = l.v.p; GN_TRY(gemm(ctx, g));
+          m->fwd_planes_src = nullptr;
         }
         if (l.use_rope) {   // rotary embeddings on q and k, in place: attention and its backward pass see the rotated tensors (transformer.go:457-461)
           GN_TRY(rope_table(ctx, l));
@@ -522,9 +554,13 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
         }
         GN_TRY(gemm_nt(ctx, N, D, D, l.att.p, D, bp.wo, bp.bo, l.r1.p, D, GN_ACT_LINEAR, cur, D));          // res1 = x + att
         float* st = l.stat.p;
-        GN_TRY(block_norm_forward(ctx, l.rms, l.r1.p, bp.g1, bp.be1, l.n1.p, st, (long)N, D));
+        // norm 1 hands its output to ff1 as operand planes (and the row norms ff1's plane-writing epilogue needs)
+        RowPlaneOut po1{}; BfPlanes n1p{}; bool n1_planes = false; float* rn1 = nullptr;
+        if (norm_planes_wanted(ctx, l.rms, N, D, F)) { GN_TRY(ensure(m, S_RN, (size_t)N, &rn1)); GN_TRY(norm_planes_alloc(m, S_LNP0, S_LNI0, N, D, &po1, &n1p, rn1)); }
+        GN_TRY(block_norm_forward(ctx, l.rms, l.r1.p, bp.g1, bp.be1, l.n1.p, st, (long)N, D, po1.p0 ? &po1 : nullptr, &n1_planes));
         {   // feed-forward: ff1 -> ff2, res2 = norm1 + ff
           GemmDesc g1; g1.M = N; g1.N = F; g1.K = D; g1.A = l.n1.p; g1.sa_m = D; g1.sa_k = 1; g1.B = bp.w1; g1.sb_k = 1; g1.sb_n = D; g1.C = l.mid.p; g1.ldc = F; g1.bias = bp.b1;
+          if (n1_planes) g1.a_planes = &n1p;
           const long nf = (long)N * F;
           BfPlanes midp{reinterpret_cast<__half*>(l.mid.p), l.mid_inv.p, N, F, F, 1};
           l.mid_is_planes = ffn_planes_possible(ctx, l, N, bp.w1, bp.w2);
@@ -550,7 +586,13 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
           if (l.mid_is_planes) g2.a_planes = &midp;
           GN_TRY(gemm(ctx, g2));
         }
-        GN_TRY(block_norm_forward(ctx, l.rms, l.r2.p, bp.g2, bp.be2, l.out.p, st + 2 * N, (long)N, D));
+        {   // norm 2 hands its output to the next block's projections as operand planes
+          RowPlaneOut po2{}; BfPlanes outp{}; bool emitted = false;
+          const bool next_is_block = li + 1 < m->L.size() && m->L[li + 1].d.kind == GN_LAYER_TRANSFORMER_BLOCK && m->L[li + 1].d.dim == D && m->L[li + 1].d.seq_len == T;
+          if (next_is_block && norm_planes_wanted(ctx, l.rms, N, D, D)) GN_TRY(norm_planes_alloc(m, S_LNP1, S_LNI1, N, D, &po2, &outp, nullptr));
+          GN_TRY(block_norm_forward(ctx, l.rms, l.r2.p, bp.g2, bp.be2, l.out.p, st + 2 * N, (long)N, D, po2.p0 ? &po2 : nullptr, &emitted));
+          if (emitted) { m->fwd_planes = outp; m->fwd_planes_src = l.out.p; }
+        }
         cur = l.out.p; break; }
       case GN_LAYER_CLS_POOLING:
         GN_LAUNCH(ctx, cls_fwd_kernel, B, 128, 0, cur, l.out.p, d.seq_len, d.dim); cur = l.out.p; break;
@@ -588,9 +630,11 @@ static int forward(gn_model* m, const float* x, int B, const float** y_out, bool
 
 // LayerNorm backward: dx, and gGamma / gBeta accumulated into the gradient slice.
 static int layernorm_backward(gn_model* m, const float* g, const float* x, const float* gamma, const float* mean, const float* sd, float* dx,
-                              float* gGamma, float* gBeta, long rows, int n) {
+                              float* gGamma, float* gBeta, long rows, int n, const RowPlaneOut* po, bool* emitted) {
   Ctx* ctx = &m->ctx->c;
   const bool vec = n % 128 == 0 && ((reinterpret_cast<uintptr_t>(g) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dx) | reinterpret_cast<uintptr_t>(gamma)) & 15) == 0;
+  const RowPlaneOut out = (po && vec && layernorm_vec_width(n)) ? *po : RowPlaneOut{};
+  if (emitted) *emitted = out.p0 != nullptr;
   if (vec) {
     const int chunks = (int)std::max<long>(1, std::min<long>(rows / 32, 4L * ctx->sm_count));
     float* part; GN_TRY(ensure(m, S_PART2, (size_t)chunks * 2 * n, &part));
@@ -603,10 +647,10 @@ static int layernorm_backward(gn_model* m, const float* g, const float* x, const
     GN_LAUNCH(ctx, layernorm_pgrad_final_kernel, cdiv(n, 32), 1024, 0, part, chunks, n, gGamma, gBeta);
   }
   switch (vec ? n / 128 : 0) {
-    case 1: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<1>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows); break;
-    case 2: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<2>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows); break;
-    case 4: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<4>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows); break;
-    case 8: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<8>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows); break;
+    case 1: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<1>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows, out); break;
+    case 2: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<2>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows, out); break;
+    case 4: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<4>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows, out); break;
+    case 8: GN_LAUNCH(ctx, layernorm_bwd_vec_kernel<8>, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows, out); break;
     default: GN_LAUNCH(ctx, layernorm_bwd_kernel, cdiv(rows, 8), 256, 0, g, x, gamma, mean, sd, dx, rows, n);
   }
   return check_launch("layernorm_backward");
@@ -653,12 +697,16 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
   GN_TRY(ensure(m, S_ND2, ND, &dR1)); GN_TRY(ensure(m, S_ND3, ND, &dA));
   if (!fused) { GN_TRY(ensure(m, S_ATT0, (size_t)B * Hh * T * T, &P)); GN_TRY(ensure(m, S_ATT1, (size_t)B * Hh * T * T, &dP)); }
   // norm 2
-  GN_TRY(block_norm_backward(m, l.rms, gout, l.r2.p, bp.g2, st + 2 * N, dR2, (float*)gp.g2, (float*)gp.be2, (long)N, D));
+  // its result goes to the contraction with W2 as operand planes, with the row norms that contraction's plane-writing epilogue needs
+  RowPlaneOut pob{}; BfPlanes dR2p{}; bool dR2_planes = false; float* rnb = nullptr;
+  if (norm_planes_wanted(ctx, l.rms, N, D, F)) { GN_TRY(ensure(m, S_RN, (size_t)N, &rnb)); GN_TRY(norm_planes_alloc(m, S_LNP0, S_LNI0, N, D, &pob, &dR2p, rnb)); }
+  GN_TRY(block_norm_backward(m, l.rms, gout, l.r2.p, bp.g2, st + 2 * N, dR2, (float*)gp.g2, (float*)gp.be2, (long)N, D, pob.p0 ? &pob : nullptr, &dR2_planes));
   // ff2 then ff1, token by token in the reference (transformer.go:1238-1250)
   GN_TRY(inner_dense_param_grads(m, dR2, B, T, D, l.mid.p, F, (float*)gp.w2, (float*)gp.b2, l.mid_is_planes ? l.mid_last.p : nullptr));
   {
     // dM[s,t,:] = W2^T dR2[s,t,:]; with a ReLU first layer gated by the ReLU pattern of the LAST token of sequence s (fused into the epilogue)
     GemmDesc g; g.M = N; g.N = F; g.K = D; g.A = dR2; g.sa_m = D; g.sa_k = 1; g.B = bp.w2; g.sb_k = F; g.sb_n = 1; g.C = dM; g.ldc = F;
+    if (dR2_planes) g.a_planes = &dR2p;
     if (l.mid_is_planes) { g.mask = l.mid_last.p; g.mask_ld = F; g.mask_group = T; }
     else if (l.ff_act == GN_ACT_RELU) { g.mask = l.mid.p + (long)(T - 1) * F; g.mask_ld = (long)T * F; g.mask_group = T; }
     const long nf = (long)N * F;
@@ -695,10 +743,16 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
     }
   }
   // norm 1
-  GN_TRY(block_norm_backward(m, l.rms, comb, l.r1.p, bp.g1, st, dR1, (float*)gp.g1, (float*)gp.be1, (long)N, D));
+  RowPlaneOut poa{}; BfPlanes dR1p{}; bool dR1_planes = false;
+  if (norm_planes_wanted(ctx, l.rms, N, D, D)) GN_TRY(norm_planes_alloc(m, S_LNP0, S_LNI0, N, D, &poa, &dR1p, nullptr));      // the planes of dR2 are dead by now
+  GN_TRY(block_norm_backward(m, l.rms, comb, l.r1.p, bp.g1, st, dR1, (float*)gp.g1, (float*)gp.be1, (long)N, D, poa.p0 ? &poa : nullptr, &dR1_planes));
   // output projection
   GN_TRY(inner_dense_param_grads(m, dR1, B, T, D, l.att.p, D, (float*)gp.wo, (float*)gp.bo));
-  GN_TRY(gemm_nn(ctx, N, D, D, dR1, D, bp.wo, dA, D));
+  {
+    GemmDesc g; g.M = N; g.N = D; g.K = D; g.A = dR1; g.sa_m = D; g.sa_k = 1; g.B = bp.wo; g.sb_k = D; g.sb_n = 1; g.C = dA; g.ldc = D;      // dA = dR1 Wo
+    if (dR1_planes) g.a_planes = &dR1p;
+    GN_TRY(gemm(ctx, g));
+  }
   // attention: recompute P (transformer.go:610-622), then dP, dS, dQ, dK, dV
   float *dQ, *dK, *dV;
   GN_TRY(ensure(m, S_ND0, ND, &dQ)); GN_TRY(ensure(m, S_ND1, ND, &dK)); GN_TRY(ensure(m, S_ND4, ND, &dV));   // dR2 / comb are dead by now

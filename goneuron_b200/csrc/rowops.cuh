@@ -257,9 +257,34 @@ __global__ void __launch_bounds__(1024) layernorm_pgrad_final_kernel(const float
 
 // Row-in-registers variants for n = 128 * NV (NV <= 16): one warp per row, the row is read once with 16-byte loads
 // and kept in registers between the reduction and the output pass.  Same arithmetic as the kernels above.
+// Optional second output of the row-in-registers kernels: the row as operand planes of the contraction engine (two fp16
+// planes with row stride n, the row's inverse scale, its 2-norm) -- the kernel holds the whole row, so the row maximum
+// costs two shuffles, and the separate split pass (a second read of the tensor) is not needed for the contraction that
+// consumes this output.
+struct RowPlaneOut { __half* p0 = nullptr; __half* p1 = nullptr; float* inv = nullptr; float* rownorm = nullptr; };
+template <int NV>
+__device__ __forceinline__ void row_planes_emit(const float4 (&o)[NV], long row, int lane, const RowPlaneOut& po) {
+  constexpr int n = 128 * NV;
+  float mx = 0.f, sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; k++) {
+    mx = fmaxf(mx, fmaxf(fmaxf(fabsf(o[k].x), fabsf(o[k].y)), fmaxf(fabsf(o[k].z), fabsf(o[k].w))));
+    sq += (o[k].x * o[k].x + o[k].y * o[k].y) + (o[k].z * o[k].z + o[k].w * o[k].w);
+  }
+  mx = warp_max(mx); sq = warp_sum(sq);
+  float inv; const float sc = row_scale(mx, &inv);
+  if (lane == 0) { po.inv[row] = inv; if (po.rownorm) po.rownorm[row] = sqrtf(sq) * 1.0001f; }
+  uint2* h = reinterpret_cast<uint2*>(po.p0 + row * n) + lane; uint2* l = reinterpret_cast<uint2*>(po.p1 + row * n) + lane;
+#pragma unroll
+  for (int k = 0; k < NV; k++) {
+    uint2 a, b; split2_pair(o[k].x, o[k].y, sc, a.x, b.x); split2_pair(o[k].z, o[k].w, sc, a.y, b.y);
+    h[32 * k] = a; l[32 * k] = b;
+  }
+}
 template <int NV>
 __global__ void __launch_bounds__(256) layernorm_fwd_vec_kernel(const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
-                                                                float* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ std_out, long rows, float eps) {
+                                                                float* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ std_out, long rows, float eps,
+                                                                const RowPlaneOut po) {
   constexpr int n = 128 * NV;
   const long row = (long)blockIdx.x * 8 + (threadIdx.x >> 5); if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -279,13 +304,16 @@ __global__ void __launch_bounds__(256) layernorm_fwd_vec_kernel(const float* __r
 #pragma unroll
   for (int k = 0; k < NV; k++) {
     const float4 ga = __ldg(reinterpret_cast<const float4*>(gamma) + lane + 32 * k), be = __ldg(reinterpret_cast<const float4*>(beta) + lane + 32 * k);
-    yr[32 * k] = make_float4(ga.x * ((v[k].x - mean) * isd) + be.x, ga.y * ((v[k].y - mean) * isd) + be.y, ga.z * ((v[k].z - mean) * isd) + be.z, ga.w * ((v[k].w - mean) * isd) + be.w);
+    v[k] = make_float4(ga.x * ((v[k].x - mean) * isd) + be.x, ga.y * ((v[k].y - mean) * isd) + be.y, ga.z * ((v[k].z - mean) * isd) + be.z, ga.w * ((v[k].w - mean) * isd) + be.w);
+    yr[32 * k] = v[k];
   }
   if (lane == 0) { mean_out[row] = mean; std_out[row] = sd; }
+  if (po.p0) row_planes_emit<NV>(v, row, lane, po);
 }
 template <int NV>
 __global__ void __launch_bounds__(256) layernorm_bwd_vec_kernel(const float* __restrict__ g, const float* __restrict__ x, const float* __restrict__ gamma,
-                                                                const float* __restrict__ mean_in, const float* __restrict__ std_in, float* dx, long rows) {
+                                                                const float* __restrict__ mean_in, const float* __restrict__ std_in, float* dx, long rows,
+                                                                const RowPlaneOut po) {
   constexpr int n = 128 * NV;
   const long row = (long)blockIdx.x * 8 + (threadIdx.x >> 5); if (row >= rows) return;
   const int lane = threadIdx.x & 31;
@@ -308,9 +336,12 @@ __global__ void __launch_bounds__(256) layernorm_bwd_vec_kernel(const float* __r
   const float fn = (float)n, sgn = sg / fn, isd = 1.f / sd, w = sgx / (fn * sd * sd);     // reciprocals per row, not per element
   float4* dr = reinterpret_cast<float4*>(dx + row * n) + lane;
 #pragma unroll
-  for (int k = 0; k < NV; k++)
-    dr[32 * k] = make_float4((q[k].x - sgn) * isd - d[k].x * w, (q[k].y - sgn) * isd - d[k].y * w,
-                             (q[k].z - sgn) * isd - d[k].z * w, (q[k].w - sgn) * isd - d[k].w * w);
+  for (int k = 0; k < NV; k++) {
+    q[k] = make_float4((q[k].x - sgn) * isd - d[k].x * w, (q[k].y - sgn) * isd - d[k].y * w,
+                       (q[k].z - sgn) * isd - d[k].z * w, (q[k].w - sgn) * isd - d[k].w * w);
+    dr[32 * k] = q[k];
+  }
+  if (po.p0) row_planes_emit<NV>(q, row, lane, po);
 }
 // Partial column sums for gGamma / gBeta with 16-byte loads: block = 256 threads = up to 1024 columns, grid.x covers the
 // columns, grid.y the row chunks; part layout as in layernorm_pgrad_partial_kernel.
