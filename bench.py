@@ -199,7 +199,7 @@ def measure_tf32_peak(seconds=1.5):
 # capture under profiles/): measured bytes over the launch's algorithmic bytes.  Traffic grows in proportion with the
 # operand and output sizes, so a full step's figure is this ratio times the step's algorithmic bytes.
 # (Below 1: most of the 67 MB output is still in the 126 MB L2 when the launch ends and is written back later.)
-NCU_TRAFFIC_RATIO = {"captured_bytes": 71.464192e6 + 15.773440e6, "algorithmic_bytes": 4.0 * (16384 + 1024) * 1024 + 4.0 * 16384 * 1024}
+NCU_TRAFFIC_RATIO = {"captured_bytes": 71.455744e6 + 24.339968e6, "algorithmic_bytes": 4.0 * (16384 + 1024) * 1024 + 4.0 * 16384 * 1024}
 
 
 def run_workload(torch, dist, dev, workload, rank, world, local, steps, warmup, e2e=True, sampler=None):
