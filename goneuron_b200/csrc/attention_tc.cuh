@@ -746,7 +746,7 @@ inline int attn_tc_fwd(Ctx* ctx, const float* Q, const float* K, const float* V,
   GN_TRY(attn_tc_maps_rows(ctx, &maps.m[0], p[0], T, Z, ATC_BQ)); GN_TRY(attn_tc_maps_rows(ctx, &maps.m[2], p[1], T, Z, ATC_BK)); GN_TRY(attn_tc_maps_cols(ctx, &maps.m[4], p[2], T, Z));
   GN_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATF_SMEM));
   const int ntq = T / ATC_BQ, ntiles = ntq * Z;
-  const int grid = std::min(ntiles, std::max(1, ctx->sm_count / ntq) * ntq);      // a multiple of the query blocks per problem
+  const int grid = std::min(ntiles, std::max(1, persist_sms(ctx) / ntq) * ntq);      // a multiple of the query blocks per problem
   GN_LAUNCH(ctx, attn_tc_fwd_kernel, grid, ATC_THREADS, ATF_SMEM, maps, O, M, L, (const float*)p[0].inv, (const float*)p[1].inv, (const float*)p[2].inv,
             T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status, ctx->spin_limit);
   return check_launch("attn_tc_fwd");
@@ -763,7 +763,7 @@ inline int attn_tc_bwd_launch(Ctx* ctx, const AttnPlanes& r1, const AttnPlanes& 
   GN_CUDA(cudaFuncSetAttribute(attn_tc_bwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, AtbCfg<MODE>::SMEM));
   AtbScales sc{r1.inv, r2.inv, c1.inv, c2.inv, c3.inv, rnorm, zmaxn, zmaxd};
   const int ntr = T / 128, ntiles = ntr * Z;
-  const int grid = std::min(ntiles, std::max(1, ctx->sm_count / ntr) * ntr);      // a multiple of the row tiles per problem
+  const int grid = std::min(ntiles, std::max(1, persist_sms(ctx) / ntr) * ntr);      // a multiple of the row tiles per problem
   GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, grid, ATB_THREADS, AtbCfg<MODE>::SMEM, maps, M, L, Dv, out, sc, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status, ctx->spin_limit);
   return check_launch("attn_tc_bwd");
 }

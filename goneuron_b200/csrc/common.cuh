@@ -34,6 +34,7 @@ struct Ctx {
   void* comm = nullptr;            // ncclComm_t
   NcclApi* nccl = nullptr;
   int sm_count = 148;
+  int sm_reserve = 0;              // SMs the persistent kernels leave free (for the collectives' CTAs when several ranks run); see persist_sms()
   int64_t launches = 0;            // kernels launched by this library on this context
   // contraction profiling (gn_model_set_profiling)
   int profile = 0;

@@ -689,12 +689,15 @@ inline int tc_split(Ctx* ctx, const TcSrc& src, const BfPlanes& p, int* mx, floa
   return check_launch("tc_split");
 }
 
+// SMs a persistent kernel spreads over.  With several ranks the gradient all-reduces run beside the backward pass; a
+// persistent kernel that waits for the SMs their CTAs hold takes as long as the collective, so it leaves them some.
+inline int persist_sms(const Ctx* ctx) { return std::max(1, ctx->sm_count - ctx->sm_reserve); }
 // Number of left-over tiles of the last round that are run as two half tiles each (0: none): only when they would keep at
 // most half of the CTAs busy, and not for the triangular products (their tiles differ in length anyway).
 inline long tc_tail_halves(Ctx* ctx, long total_tiles, int bn, int flags) {
-  if (!ctx->tc_tail_split || bn < 128 || total_tiles <= ctx->sm_count || (flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return 0;
-  const long left = total_tiles % ctx->sm_count;
-  return 2 * left <= ctx->sm_count ? left : 0;
+  if (!ctx->tc_tail_split || bn < 128 || total_tiles <= persist_sms(ctx) || (flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return 0;
+  const long left = total_tiles % persist_sms(ctx);
+  return 2 * left <= persist_sms(ctx) ? left : 0;
 }
 template <int BN>
 inline int tc_launch_persist(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams& ep) {
@@ -705,7 +708,7 @@ inline int tc_launch_persist(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, con
   GN_TRY(tc_make_map_bf16_raw(ctx, &mB0, B.p0(), B.K, B.rows, B.ldp, B.nbatch, B.koff, BN / 2, TC_BK, F16)); GN_TRY(tc_make_map_bf16_raw(ctx, &mB1, B.p1(), B.K, B.rows, B.ldp, B.nbatch, B.koff, BN / 2, TC_BK, F16));
   const int tiles_m = cdiv(ep.M, TC_BM), tiles_n = cdiv(ep.N, BN); const long total = (long)tiles_m * tiles_n * A.nbatch;
   if (total > 0x7fffffffL) return fail(GN_ERR_UNSUPPORTED, "too many output tiles");
-  const unsigned grid = (unsigned)std::min<long>(total, ctx->sm_count);
+  const unsigned grid = (unsigned)std::min<long>(total, persist_sms(ctx));
   const long left = tc_tail_halves(ctx, total, BN, ep.flags);
   const int full_end = (int)(total - left), n_half = (int)(2 * left);
   ProfScope prof(ctx);
@@ -720,7 +723,7 @@ inline int tc_pick_bn(Ctx* ctx, int M, int N, long nbatch, int flags) {
   if (N <= 128 || (flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0))) return 128;
   auto cost = [&](int bn, double rate) {
     const long tiles = (long)cdiv(M, TC_BM) * cdiv(N, bn) * nbatch;
-    double waves = std::ceil((double)tiles / ctx->sm_count);
+    double waves = std::ceil((double)tiles / persist_sms(ctx));
     if (tc_tail_halves(ctx, tiles, bn, flags) > 0) waves -= 0.38;       // a half tile costs about 0.62 of a whole one
     return waves * bn / rate;
   };

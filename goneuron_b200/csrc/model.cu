@@ -872,6 +872,31 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
   float* pp[2] = {nullptr, nullptr}; int flip = 0;
   size_t maxio = 0; for (auto& l : m->L) maxio = std::max<size_t>(maxio, std::max(l.in_size, l.out_size));
   GN_TRY(ensure(m, S_G0, (size_t)B * maxio, &pp[0])); GN_TRY(ensure(m, S_G1, (size_t)B * maxio, &pp[1]));
+  // This layer's slice of the flat gradient buffer is final: sum it over the ranks while earlier layers still compute
+  // (unless every rank already holds the whole sum), and apply this slice's Adam update right behind it on the
+  // communication stream -- the layer's parameters are not read again in this step -- so that neither the exchange
+  // nor the optimiser pass is left over when the backward pass ends.  GONEURON_CUDA_COMM=end issues the same sequence
+  // for all layers after the backward pass instead (no overlap; for measurements).
+  static const bool comm_at_end = [] { const char* e = getenv("GONEURON_CUDA_COMM"); return e && !strcmp(e, "end"); }();
+  std::vector<int> deferred;
+  auto layer_comm = [&](int li) -> int {
+    LayerRT& l = m->L[li]; float* gr = m->grads.p + l.p_off;
+    GN_CUDA(cudaEventRecord(m->layer_ev[li], ctx->stream));
+    GN_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->layer_ev[li], 0));
+    if (!l.grad_replicated) {
+      int rc = ctx->nccl->AllReduce(gr, gr, (size_t)l.p_cnt, NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->comm_stream);
+      if (rc) return fail(GN_ERR_NCCL, "ncclAllReduce(grads of layer %d): %s", li, ctx->nccl->GetErrorString(rc));
+    }
+    GN_TRY(adam_launch(ctx, m->params.p + l.p_off, gr, m->m1.p + l.p_off, m->v2.p + l.p_off, l.p_cnt, m->lr, m->b1, m->b2, m->eps, m->timestep + 2,
+                       (float)(1.0 / (double)global_batch), ctx->d_status, ctx->comm_stream));
+    // ... and the layer's prepared operand planes right behind the update, still hidden behind the earlier layers' backward pass
+    if (!m->wplanes.e.empty()) {
+      int j0, j1; m->wplanes.layer_range(li, &j0, &j1);
+      GN_TRY(wplanes_refresh_range(ctx, m->wplanes, j0, j1, ctx->comm_stream));
+      m->wplanes_layerwise = true;
+    }
+    return GN_OK;
+  };
   for (int li = (int)m->L.size() - 1; li >= 0; li--) {
     LayerRT& l = m->L[li]; const gn_layer_desc& d = l.d;
     const float* xin = l.fin;
@@ -1000,26 +1025,10 @@ static int backward(gn_model* m, const float* /*x*/, int B, const float* gloss, 
     }
     GN_TRY(check_launch("backward"));
     if (ctx->world > 1 && l.p_cnt > 0) {
-      // This layer's slice of the flat gradient buffer is final: sum it over the ranks while earlier layers still compute
-      // (unless every rank already holds the whole sum), and apply this slice's Adam update right behind it on the
-      // communication stream -- the layer's parameters are not read again in this step -- so that neither the exchange
-      // nor the optimiser pass is left over when the backward pass ends.
-      GN_CUDA(cudaEventRecord(m->layer_ev[li], ctx->stream));
-      GN_CUDA(cudaStreamWaitEvent(ctx->comm_stream, m->layer_ev[li], 0));
-      if (!l.grad_replicated) {
-        int rc = ctx->nccl->AllReduce(gr, gr, (size_t)l.p_cnt, NCCL_FLOAT32, NCCL_SUM, ctx->comm, ctx->comm_stream);
-        if (rc) return fail(GN_ERR_NCCL, "ncclAllReduce(grads of layer %d): %s", li, ctx->nccl->GetErrorString(rc));
-      }
-      GN_TRY(adam_launch(ctx, m->params.p + l.p_off, gr, m->m1.p + l.p_off, m->v2.p + l.p_off, l.p_cnt, m->lr, m->b1, m->b2, m->eps, m->timestep + 2,
-                         (float)(1.0 / (double)global_batch), ctx->d_status, ctx->comm_stream));
-      // ... and the layer's prepared operand planes right behind the update, still hidden behind the earlier layers' backward pass
-      if (!m->wplanes.e.empty()) {
-        int j0, j1; m->wplanes.layer_range((int)li, &j0, &j1);
-        GN_TRY(wplanes_refresh_range(ctx, m->wplanes, j0, j1, ctx->comm_stream));
-        m->wplanes_layerwise = true;
-      }
+      if (comm_at_end) deferred.push_back(li); else GN_TRY(layer_comm(li));
     }
   }
+  for (int li : deferred) GN_TRY(layer_comm(li));
   return GN_OK;
 }
 
@@ -1138,6 +1147,7 @@ static int make_ctx(int device, int rank, int world, const unsigned char* id, gn
       delete c; } } guard{new gn_ctx()};
   gn_ctx* c = guard.c;
   c->c.device = device; c->c.rank = rank; c->c.world = world; c->c.sm_count = prop.multiProcessorCount;
+  if (const char* e = getenv("GONEURON_CUDA_SM_RESERVE")) c->c.sm_reserve = std::max(0, std::min(atoi(e), prop.multiProcessorCount / 2));
   GN_CUDA(cudaStreamCreateWithFlags(&c->c.stream, cudaStreamNonBlocking));
   GN_CUDA(cudaMalloc(&c->c.d_status, sizeof(int)));
   GN_CUDA(cudaMemsetAsync(c->c.d_status, 0, sizeof(int), c->c.stream)); GN_CUDA(cudaStreamSynchronize(c->c.stream));
