@@ -184,6 +184,7 @@ struct TcParams {
   __half* out_p0 = nullptr; __half* out_p1 = nullptr; float* out_inv = nullptr; long out_ldp = 0;
   const float* a_rownorm = nullptr; const int* b_maxabs = nullptr;     // the bound's factors: |row of A|_2 and max |entry of B (and bias)| as float bits
   float* c_last = nullptr; int last_T = 0;                             // fp32 copy of the rows r with r % last_T == last_T - 1: c_last[(r / last_T) * N + col]
+  float* rowsum32 = nullptr;                                           // plane output: sums of the result over every 32 consecutive rows, [ceil(M / 32)][N]
 };
 
 // Epilogue of one output tile.  Eight warps share it: a warp may only read the TMEM lanes of its quadrant (warp % 4), so
@@ -274,6 +275,7 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
           }
           __syncwarp();
           const float4 sv = *reinterpret_cast<const float4*>(colv + cc * 32 + 16 * h + c4), bv = *reinterpret_cast<const float4*>(colv + BN / 2 + cc * 32 + 16 * h + c4);
+          float4 csum = make_float4(0.f, 0.f, 0.f, 0.f);      // plane output: this lane's part of the warp's 32-row column sums
 #pragma unroll
           for (int t = 0; t < 4; t++) {
             const int row = rbase + 8 * t + rl;
@@ -290,7 +292,18 @@ __device__ __forceinline__ void tc_epilogue_tile(const TcParams& ep, uint32_t tm
               const long o = (long)row * ep.out_ldp + col;
               *reinterpret_cast<uint2*>(ep.out_p0 + o) = p0; *reinterpret_cast<uint2*>(ep.out_p1 + o) = p1;
               if (ep.c_last && row % ep.last_T == ep.last_T - 1) *reinterpret_cast<float4*>(ep.c_last + (long)(row / ep.last_T) * ep.N + col) = v;
+              csum.x += v.x; csum.y += v.y; csum.z += v.z; csum.w += v.w;
             } else *reinterpret_cast<float4*>(C + (long)row * ep.ldc + col) = v;
+          }
+          if (ep.rowsum32) {
+            // the consumer of a plane output's token sums (the weight gradient of the layer below) gets them from here instead
+            // of re-reading the planes: rows 8 t + rl of this lane, then the eight lanes that share its columns, in a fixed order
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+              csum.x += __shfl_xor_sync(0xffffffffu, csum.x, o); csum.y += __shfl_xor_sync(0xffffffffu, csum.y, o);
+              csum.z += __shfl_xor_sync(0xffffffffu, csum.z, o); csum.w += __shfl_xor_sync(0xffffffffu, csum.w, o);
+            }
+            if (rl == 0 && col_ok && rbase < ep.M) *reinterpret_cast<float4*>(ep.rowsum32 + (long)(rbase >> 5) * ep.N + col) = csum;
           }
         }
       }
@@ -608,7 +621,7 @@ struct BfPlanes {
 // random-sign data the bound is about 8-16 times the row's actual maximum, i.e. 3-4 of the planes' 22 bits; it can never
 // be exceeded, so the fp16 planes cannot overflow.  `last`: fp32 copy of every sequence's last row (the only rows of
 // these tensors that are read as numbers: ReLU gate and weight-gradient input of the reference's last-token rule).
-struct TcPlaneOut { BfPlanes planes; const int* b_maxabs; float* last; int last_T; };
+struct TcPlaneOut { BfPlanes planes; const int* b_maxabs; float* last; int last_T; float* rowsum32 = nullptr; };
 inline int tc_ldp(int K) { return ((K + 7) / 8) * 8; }              // plane row stride: a multiple of 16 bytes for TMA
 inline size_t bf_plane_floats(long nbatch, long rows, long ldp) { return (size_t)nbatch * rows * ldp; }   // two fp16 planes = one float per element
 
@@ -940,7 +953,7 @@ inline int gemm_tc(Ctx* ctx, const GemmDesc& g) {
     if (nb != 1 || g.R || !g.a_rownorm || !po.b_maxabs || g.N % 32 || po.planes.rows != g.M || po.planes.K != g.N || (g.flags & (GEMM_SKIP_UPPER | GEMM_KBEG_AT_M0 | GEMM_KEND_AT_M0)))
       return fail(GN_ERR_INVALID_ARG, "gemm_tc: this contraction cannot write its result as operand planes");
     ep.out_p0 = po.planes.p0(); ep.out_p1 = po.planes.p1(); ep.out_inv = po.planes.inv_scale; ep.out_ldp = po.planes.ldp;
-    ep.a_rownorm = g.a_rownorm; ep.b_maxabs = po.b_maxabs; ep.c_last = po.last; ep.last_T = po.last_T > 0 ? po.last_T : 1;
+    ep.a_rownorm = g.a_rownorm; ep.b_maxabs = po.b_maxabs; ep.c_last = po.last; ep.last_T = po.last_T > 0 ? po.last_T : 1; ep.rowsum32 = po.rowsum32;
   }
   return tc_run(ctx, A, B, ep);
 }

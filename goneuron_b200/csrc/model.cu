@@ -119,7 +119,7 @@ struct gn_model {
 
 namespace gn {
 
-enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_NFF2, S_NFF3, S_RN, S_NFFI, S_LNP0, S_LNI0, S_LNP1, S_LNI1, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_NFF2, S_NFF3, S_RN, S_NFFI, S_LNP0, S_LNI0, S_LNP1, S_LNI1, S_RS32, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
 
 static int ensure(gn_model* m, int slot, size_t n, float** out) {
   if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
@@ -662,9 +662,10 @@ static int layernorm_backward(gn_model* m, const float* g, const float* x, const
 // `x_last` != null: the last-token inputs as a dense [B, in] array instead of a strided view of x; `dz_planes` != null: dz
 // exists only as operand planes.
 static int inner_dense_param_grads(gn_model* m, const float* dz, int B, int T, int out, const float* x, int in, float* gW, float* gb,
-                                   const float* x_last = nullptr, const BfPlanes* dz_planes = nullptr) {
+                                   const float* x_last = nullptr, const BfPlanes* dz_planes = nullptr, const float* dz_rowsum32 = nullptr) {
   Ctx* ctx = &m->ctx->c; float* delta; GN_TRY(ensure(m, S_DELTA, (size_t)B * out, &delta));
-  if (dz_planes) GN_LAUNCH(ctx, token_sum_planes_kernel, dim3(cdiv(out, 128), B), dim3(32, 8), 0, (const __half*)dz_planes->p0(), (const __half*)dz_planes->p1(), (const float*)dz_planes->inv_scale, (long)dz_planes->ldp, T, out, delta);
+  if (dz_rowsum32) GN_LAUNCH(ctx, token_sum_part32_kernel, dim3(cdiv(out, 512), B), 128, 0, dz_rowsum32, T / 32, out, delta);
+  else if (dz_planes) GN_LAUNCH(ctx, token_sum_planes_kernel, dim3(cdiv(out, 128), B), dim3(32, 8), 0, (const __half*)dz_planes->p0(), (const __half*)dz_planes->p1(), (const float*)dz_planes->inv_scale, (long)dz_planes->ldp, T, out, delta);
   else if (out % 4 == 0 && ((reinterpret_cast<uintptr_t>(dz) | reinterpret_cast<uintptr_t>(delta)) & 15) == 0)
     GN_LAUNCH(ctx, token_sum_vec_kernel, dim3(cdiv(out, 128), B), dim3(32, 8), 0, dz, T, out, delta);
   else GN_LAUNCH(ctx, token_sum_kernel, dim3(cdiv(out, 128), B), dim3(128, 4), 0, dz, T, out, delta);
@@ -716,9 +717,11 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
       float *rn, *dinv; GN_TRY(ensure(m, S_RN, (size_t)N, &rn)); GN_TRY(ensure(m, S_NFFI, (size_t)N, &dinv));
       BfPlanes dMp{reinterpret_cast<__half*>(dM), dinv, N, F, F, 1};
       TcPlaneOut po{dMp, we->maxabs, nullptr, 1};
+      float* rs32 = nullptr;                               // 32-row sums of dM from the epilogue: the token sums of the ff1 weight gradient
+      if (T % 32 == 0 && F % 4 == 0) { GN_TRY(ensure(m, S_RS32, (size_t)(N / 32) * F, &rs32)); po.rowsum32 = rs32; }
       g.C = nullptr; g.plane_out = &po; g.a_rownorm = rn; GN_TRY(gemm(ctx, g));
       GemmDesc h; h.M = N; h.N = D; h.K = F; h.A = dM; h.sa_m = F; h.sa_k = 1; h.B = bp.w1; h.sb_k = D; h.sb_n = 1; h.C = comb; h.ldc = D; h.R = dR2; h.ldr = D; h.a_planes = &dMp;
-      GN_TRY(inner_dense_param_grads(m, nullptr, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1, nullptr, &dMp));
+      GN_TRY(inner_dense_param_grads(m, nullptr, B, T, F, l.n1.p, D, (float*)gp.w1, (float*)gp.b1, nullptr, &dMp, rs32));
       GN_TRY(gemm(ctx, h));
     } else if (l.ff_act != GN_ACT_SILU) {
       GN_TRY(gemm(ctx, g));

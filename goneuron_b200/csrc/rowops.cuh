@@ -168,6 +168,15 @@ __global__ void __launch_bounds__(256) token_sum_vec_kernel(const float* __restr
   }
 }
 
+// Token sums from the 32-row partial sums a plane-writing contraction leaves behind (TcParams::rowsum32): T / 32 rows per
+// sequence, added in order.
+__global__ void __launch_bounds__(128) token_sum_part32_kernel(const float* __restrict__ part, int groups, int C, float* __restrict__ out) {
+  const int c = (blockIdx.x * 128 + threadIdx.x) * 4; if (c >= C) return;
+  const float* p = part + (long)blockIdx.y * groups * C + c;
+  float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int g = 0; g < groups; g++) { const float4 q = *reinterpret_cast<const float4*>(p + (long)g * C); s.x += q.x; s.y += q.y; s.z += q.z; s.w += q.w; }
+  *reinterpret_cast<float4*>(out + (long)blockIdx.y * C + c) = s;
+}
 // The same sum over a tensor that exists only as operand planes (two fp16 planes and an inverse scale per row, written by a
 // contraction's epilogue): element = (p0 + p1) * inv_scale[row].  Same block shape as above: 4 columns per thread.
 __global__ void __launch_bounds__(256) token_sum_planes_kernel(const __half* __restrict__ p0, const __half* __restrict__ p1, const float* __restrict__ inv, long ldp,
