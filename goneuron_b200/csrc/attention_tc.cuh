@@ -366,8 +366,7 @@ struct AtbScales {
 template <int MODE>
 __global__ void __launch_bounds__(ATB_THREADS, 1)
 attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __restrict__ Mst, const float* __restrict__ Lst, const float* __restrict__ Dv,
-                   float* __restrict__ Out, float* __restrict__ rowsum32, const AtbScales sc, int T, int D, int H, int causal, float inv_scale, int ntiles, int* status,
-                   unsigned spin_limit) {
+                   float* __restrict__ Out, const AtbScales sc, int T, int D, int H, int causal, float inv_scale, int ntiles, int* status, unsigned spin_limit) {
   constexpr int NR = AtbCfg<MODE>::NR, NS = ATB_NS;
   constexpr bool TRANS = MODE != 0;
   extern __shared__ uint8_t smem_raw[];
@@ -503,7 +502,7 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
       const long i0 = (long)z0 * T + b00 * 64 + et;
       pf_m = Mst[i0]; pf_l = Lst[i0]; if (MODE == 1) pf_d = Dv[i0];
     }
-    int pend_tt = -1; float pend_os = 0.f; float* pend_row = nullptr; float* pend_sum = nullptr;
+    int pend_tt = -1; float pend_os = 0.f; float* pend_row = nullptr;
     auto write_out = [&]() {
       ok &= WWAIT(BAR(TDONE), pend_tt & 1, 24);
       tc_fence_after();
@@ -515,15 +514,6 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
 #pragma unroll
       for (int e = 0; e < CW / 4; e++)
         *reinterpret_cast<float4*>(pend_row + 4 * e) = make_float4(__uint_as_float(a[4 * e]) * pend_os, __uint_as_float(a[4 * e + 1]) * pend_os, __uint_as_float(a[4 * e + 2]) * pend_os, __uint_as_float(a[4 * e + 3]) * pend_os);
-      if (rowsum32) {
-        // sums of the result over this warp's 32 rows, per column: the token sums the weight gradient of the projection
-        // needs are then 16 additions per sequence instead of another pass over the tensor
-#pragma unroll
-        for (int e = 0; e < CW; e++) {
-          const float s = warp_sum(__uint_as_float(a[e]) * pend_os);
-          if (lane == 0) pend_sum[e] = s;
-        }
-      }
       pend_tt = -1;
     };
     for (int id = blockIdx.x, tt = 0; id < ntiles; id += gridDim.x, tt++) {
@@ -580,7 +570,6 @@ attn_tc_bwd_kernel(const __grid_constant__ AttnMaps<10> maps, const float* __res
         const int bz = z / H, h = z % H;
         pend_tt = tt; pend_os = a_inv * sc.ic3[z];
         pend_row = Out + ((long)bz * T + ri) * D + (long)h * ATC_HD + CW * part;
-        if (rowsum32) pend_sum = rowsum32 + (((long)bz * T + r0 + quad * 32) >> 5) * D + (long)h * ATC_HD + CW * part;
       }
       g0 += nb;
     }
@@ -766,7 +755,7 @@ inline int attn_tc_fwd(Ctx* ctx, const float* Q, const float* K, const float* V,
 template <int MODE>
 inline int attn_tc_bwd_launch(Ctx* ctx, const AttnPlanes& r1, const AttnPlanes& r2, const AttnPlanes& c1, const AttnPlanes& c2, const AttnPlanes& c3,
                               const float* rnorm, const int* zmaxn, const int* zmaxd,
-                              const float* M, const float* L, const float* Dv, float* out, float* rowsum32, int B, int T, int D, int H, int causal) {
+                              const float* M, const float* L, const float* Dv, float* out, int B, int T, int D, int H, int causal) {
   const int Z = B * H;
   AttnMaps<10> maps;
   GN_TRY(attn_tc_maps_rows(ctx, &maps.m[0], r1, T, Z, 128)); GN_TRY(attn_tc_maps_rows(ctx, &maps.m[2], r2, T, Z, 128));
@@ -775,12 +764,12 @@ inline int attn_tc_bwd_launch(Ctx* ctx, const AttnPlanes& r1, const AttnPlanes& 
   AtbScales sc{r1.inv, r2.inv, c1.inv, c2.inv, c3.inv, rnorm, zmaxn, zmaxd};
   const int ntr = T / 128, ntiles = ntr * Z;
   const int grid = std::min(ntiles, std::max(1, persist_sms(ctx) / ntr) * ntr);      // a multiple of the row tiles per problem
-  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, grid, ATB_THREADS, AtbCfg<MODE>::SMEM, maps, M, L, Dv, out, rowsum32, sc, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status, ctx->spin_limit);
+  GN_LAUNCH(ctx, attn_tc_bwd_kernel<MODE>, grid, ATB_THREADS, AtbCfg<MODE>::SMEM, maps, M, L, Dv, out, sc, T, D, H, causal, 1.f / sqrtf((float)ATC_HD), ntiles, ctx->d_status, ctx->spin_limit);
   return check_launch("attn_tc_bwd");
 }
 // dQ, dK, dV from Q, K, V, O, dO and the forward's row statistics; Dv receives the row products dO . O
 inline int attn_tc_bwd(Ctx* ctx, const float* Q, const float* K, const float* V, const float* O, const float* dO, const float* M, const float* L, float* Dv,
-                       float* dQ, float* dK, float* dV, int B, int T, int D, int H, int causal, AttnSaved* saved = nullptr, float* const* rowsum32 = nullptr) {
+                       float* dQ, float* dK, float* dV, int B, int T, int D, int H, int causal, AttnSaved* saved = nullptr) {
   const long rows = (long)B * T * H; const int Z = B * H;
   if (D == H * ATC_HD && ((reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(O)) & 15) == 0)
     GN_LAUNCH(ctx, attn_rowdot64_kernel, (unsigned)std::min<long>(cdiv(rows, 32), (long)ctx->sm_count * 16), 256, 0, dO, O, Dv, T, H, rows);
@@ -798,9 +787,9 @@ inline int attn_tc_bwd(Ctx* ctx, const float* Q, const float* K, const float* V,
   }
   GN_LAUNCH(ctx, attn_dmax_kernel, Z, 128, 0, (const float*)Dv, T, zmaxd);
   const AttnPlanes &q = p[0], &k = p[1], &v = p[2], &g = p[3];
-  GN_TRY(attn_tc_bwd_launch<0>(ctx, q, g, k, v, k, g.rnorm, v.nmax, nullptr, M, L, Dv, dQ, rowsum32 ? rowsum32[0] : nullptr, B, T, D, H, causal));
-  GN_TRY(attn_tc_bwd_launch<1>(ctx, k, v, q, g, q, v.rnorm, g.nmax, zmaxd, M, L, Dv, dK, rowsum32 ? rowsum32[1] : nullptr, B, T, D, H, causal));
-  GN_TRY(attn_tc_bwd_launch<2>(ctx, k, k, q, q, g, nullptr, nullptr, nullptr, M, L, Dv, dV, rowsum32 ? rowsum32[2] : nullptr, B, T, D, H, causal));
+  GN_TRY(attn_tc_bwd_launch<0>(ctx, q, g, k, v, k, g.rnorm, v.nmax, nullptr, M, L, Dv, dQ, B, T, D, H, causal));
+  GN_TRY(attn_tc_bwd_launch<1>(ctx, k, v, q, g, q, v.rnorm, g.nmax, zmaxd, M, L, Dv, dK, B, T, D, H, causal));
+  GN_TRY(attn_tc_bwd_launch<2>(ctx, k, k, q, q, g, nullptr, nullptr, nullptr, M, L, Dv, dV, B, T, D, H, causal));
   return GN_OK;
 }
 

@@ -119,7 +119,7 @@ struct gn_model {
 
 namespace gn {
 
-enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_NFF2, S_NFF3, S_RN, S_NFFI, S_LNP0, S_LNI0, S_LNP1, S_LNI1, S_RS32, S_RS32Q, S_RS32K, S_RS32V, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
+enum Slot { S_BNG = 0, S_EMB, S_GRAM0, S_GRAM1, S_DM, S_ZM, S_W, S_TV, S_G0, S_G1, S_ND0, S_ND1, S_ND2, S_ND3, S_ND4, S_NFF, S_NFF2, S_NFF3, S_RN, S_NFFI, S_LNP0, S_LNI0, S_LNP1, S_LNI1, S_RS32, S_ATT0, S_ATT1, S_DELTA, S_PART, S_PART2, S_DZ, S_SCAN, S_COUNT };
 
 static int ensure(gn_model* m, int slot, size_t n, float** out) {
   if ((int)m->scratch.size() < S_COUNT) m->scratch.resize(S_COUNT);
@@ -759,15 +759,9 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
   // attention: recompute P (transformer.go:610-622), then dP, dS, dQ, dK, dV
   float *dQ, *dK, *dV;
   GN_TRY(ensure(m, S_ND0, ND, &dQ)); GN_TRY(ensure(m, S_ND1, ND, &dK)); GN_TRY(ensure(m, S_ND4, ND, &dV));   // dR2 / comb are dead by now
-  float* rs[3] = {nullptr, nullptr, nullptr};       // 32-row sums of dQ, dK, dV written by the tcgen05 attention kernels (the token sums of the projections' weight gradients)
   if (fused) {
     static const bool tc_bwd = [] { const char* e = getenv("GONEURON_CUDA_ATTENTION_BWD"); return !(e && !strcmp(e, "mma")); }();
-    if (tc_bwd && attn_tc_supported(ctx, hd, T, B, Hh, D)) {
-      if (!l.use_rope) {                               // (with rotary embeddings dQ and dK are rotated afterwards: their sums are taken then)
-        GN_TRY(ensure(m, S_RS32Q, (size_t)(N / 32) * D, &rs[0])); GN_TRY(ensure(m, S_RS32K, (size_t)(N / 32) * D, &rs[1])); GN_TRY(ensure(m, S_RS32V, (size_t)(N / 32) * D, &rs[2]));
-      }
-      GN_TRY(attn_tc_bwd(ctx, l.q.p, l.k.p, l.v.p, l.att.p, dA, l.att_m.p, l.att_l.p, l.att_d.p, dQ, dK, dV, B, T, D, Hh, d.causal, &l.attn_saved, rs[0] ? rs : nullptr));
-    }
+    if (tc_bwd && attn_tc_supported(ctx, hd, T, B, Hh, D)) GN_TRY(attn_tc_bwd(ctx, l.q.p, l.k.p, l.v.p, l.att.p, dA, l.att_m.p, l.att_l.p, l.att_d.p, dQ, dK, dV, B, T, D, Hh, d.causal, &l.attn_saved));
     else GN_TRY(attn_bwd(ctx, hd, l.q.p, l.k.p, l.v.p, l.att.p, dA, l.att_m.p, l.att_l.p, l.att_d.p, dQ, dK, dV, B, T, D, Hh, d.causal));
   } else {
     const long TD = (long)T * D, TT = (long)T * T; const float inv_scale = 1.f / sqrtf((float)hd); const long rows = (long)B * Hh * T;
@@ -789,9 +783,9 @@ static int block_backward(gn_model* m, LayerRT& l, int B, const float* xin, cons
     GN_LAUNCH(ctx, rope_kernel, ew_grid(ctx, tot), 256, 0, dK, (const float*)l.rope.p, (long)N, T, D, hd, -1.f);
   }
   // q, k, v projections; gradIn = dq + dk + dv, block input gradient = gradRes1 + gradIn
-  GN_TRY(inner_dense_param_grads(m, dQ, B, T, D, xin, D, (float*)gp.wq, (float*)gp.bq, nullptr, nullptr, rs[0]));
-  GN_TRY(inner_dense_param_grads(m, dK, B, T, D, xin, D, (float*)gp.wk, (float*)gp.bk, nullptr, nullptr, rs[1]));
-  GN_TRY(inner_dense_param_grads(m, dV, B, T, D, xin, D, (float*)gp.wv, (float*)gp.bv, nullptr, nullptr, rs[2]));
+  GN_TRY(inner_dense_param_grads(m, dQ, B, T, D, xin, D, (float*)gp.wq, (float*)gp.bq));
+  GN_TRY(inner_dense_param_grads(m, dK, B, T, D, xin, D, (float*)gp.wk, (float*)gp.bk));
+  GN_TRY(inner_dense_param_grads(m, dV, B, T, D, xin, D, (float*)gp.wv, (float*)gp.bv));
   GN_TRY(gemm_nn(ctx, N, D, D, dQ, D, bp.wq, dx, D, dR1, D));
   GN_TRY(gemm_nn(ctx, N, D, D, dK, D, bp.wk, dx, D, dx, D));
   GN_TRY(gemm_nn(ctx, N, D, D, dV, D, bp.wv, dx, D, dx, D));
