@@ -99,3 +99,18 @@ def test_reference_generator_and_initialisers():
     from goneuron_b200 import descriptors as D
     q = configs.reference_init_params([D.Dense(8, 8, D.RELU), D.Dense(8, 8, D.RELU)])
     assert np.array_equal(q[:72], q[72:])
+
+
+def test_every_environment_switch_is_documented():
+    """Each GONEURON_CUDA_* variable the library reads has a row in the integration notes' table of switches."""
+    import glob
+    import os
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    read = set()
+    for path in glob.glob(os.path.join(root, "goneuron_b200", "csrc", "*.cu*")):
+        read |= set(re.findall(r'getenv\("(GONEURON_CUDA_[A-Z0-9_]+)"\)', open(path).read()))
+    assert len(read) >= 10
+    doc = open(os.path.join(root, "INTEGRATION.md")).read()
+    missing = sorted(v for v in read if v not in doc)
+    assert not missing, missing
