@@ -45,6 +45,8 @@ struct Ctx {
   bool tc_ok = false;              // tcgen05 engine usable (driver entry point for tensor maps found)
   void* encode_tiled = nullptr;    // cuTensorMapEncodeTiled
   unsigned spin_limit = 1u << 24;  // polls per bounded device-side wait (gn_ctx_set_spin_limit)
+  bool tc_tile_queue = false;      // persistent contraction draws its tiles from a queue instead of a fixed share per CTA (GONEURON_CUDA_TC_TILE_QUEUE)
+  int* tc_queue_pool = nullptr; int tc_queue_used = 0;      // zeroed counters for those queues
   bool tc_tail_split = true;       // left-over tiles of a short last round run as half tiles (GONEURON_CUDA_TC_TAIL_SPLIT=0 switches it off)
   int tc_force_bn = 0, tc_kslice = 0;   // experiment switches of the contraction engine (GONEURON_CUDA_TC_BN / _KSLICE); 0 = automatic
   void* tc_scratch = nullptr;      // operand planes of the contraction engine (TcScratch, owned)

@@ -53,6 +53,7 @@ constexpr int TC_EPI_WARPS = 8;                 // two warps per TMEM lane quadr
 constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;   // TMA warp, MMA warp, epilogue warps
 constexpr unsigned TC_SPIN_LIMIT = 1u << 24;    // default number of polls of one wait (Ctx::spin_limit overrides it)
 constexpr unsigned TC_DRAIN_LIMIT = 1u << 20;   // polls spent waiting for own work in flight after a wait gave up
+constexpr int TC_QUEUE_POOL = 2048;   // tile-queue counters per context before the pool is cleared again
 constexpr int TC_FLAG_VEC = 4096;   // epilogue may use 16-byte accesses (set by the host when every pointer and stride allows it)
 // One stage = 32 contraction indices of both operands: two fp16 planes each, 64-byte rows.
 constexpr int TC_BK = 32;
@@ -350,7 +351,7 @@ template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1,
                        const __grid_constant__ CUtensorMap mapB0, const __grid_constant__ CUtensorMap mapB1,
-                       TcParams ep, int tiles_m, int tiles_n, int total_tiles, int full_end, int n_half) {
+                       TcParams ep, int tiles_m, int tiles_n, int total_tiles, int full_end, int n_half, int* tile_queue) {
   using Cfg = TcCfg<BN>;
   constexpr int STAGES = Cfg::STAGES, STAGE_BYTES = Cfg::STAGE_BYTES, BK = TC_BK;
   constexpr bool MERGED = Cfg::MERGED;
@@ -360,6 +361,9 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);       // full[S], empty[S], tfull[2], tempty[2], drain
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 5);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);       // set by the first role whose wait gave up
+  uint64_t* qbars = bars + 2 * STAGES + 6;                         // tile queue: qfull[4], qempty[4], then the four queued items
+  volatile int* qitem = (volatile int*)(qbars + 8);
+  const uint32_t qfull0 = smem_u32(qbars), qempty0 = smem_u32(qbars + 4);
   float* colv_all = (float*)(smem + STAGES * STAGE_BYTES + 256);   // epilogue warps' column factors
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES), tfull0 = smem_u32(bars + 2 * STAGES), tempty0 = smem_u32(bars + 2 * STAGES + 2);
   const uint32_t drain = smem_u32(bars + 2 * STAGES + 4);
@@ -372,6 +376,7 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
     for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
     for (int b = 0; b < 2; b++) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, TC_EPI_WARPS); }
     mbar_init(drain, 1);
+    for (int b = 0; b < 4; b++) { mbar_init(qfull0 + 8 * b, 1); mbar_init(qempty0 + 8 * b, 1 + TC_EPI_WARPS); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -387,12 +392,36 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
   // Work list of this CTA (identical in every role): tiles blockIdx.x, + gridDim.x, ... below full_end; then, when the
   // tiles left over would occupy at most half of the CTAs (n_half = twice their number, else 0), one HALF of a left-over
   // tile each (BN / 2 columns), so that the last, short round costs about 0.6 instead of 1 tile time.
-  auto work = [&](int k, int& tile, int& half) -> bool {
-    const long t = (long)blockIdx.x + (long)k * gridDim.x;
+  // a wait gave up: record which role, and tell the other roles of this CTA to stop
+  auto give_up = [&](int code) { atomicExch(ep.status, code); *abort_flag = 1; __threadfence_block(); };
+  auto item = [&](long t, int& tile, int& half) -> bool {
     if (t < full_end) { tile = (int)t; half = -1; return true; }
     const long h = t - full_end;
     if (h >= n_half) return false;
     tile = full_end + (int)(h >> 1); half = (int)(h & 1); return true;
+  };
+  // With a tile queue (tile_queue != null: a zeroed counter in global memory) the producer thread draws the items with
+  // atomicAdd and hands each to the MMA thread and the epilogue warps through a four-entry ring in shared memory, so a
+  // CTA that gets its SM late (other kernels -- the collectives of a multi-GPU step -- holding SMs when the launch
+  // starts) simply finds less left to do, instead of the whole launch waiting for its fixed share.
+  const bool queued = tile_queue != nullptr;
+  auto work = [&](int k, int& tile, int& half) -> bool {
+    if (!queued) return item((long)blockIdx.x + (long)k * gridDim.x, tile, half);
+    const uint32_t qs = (uint32_t)k & 3, qu = (uint32_t)k >> 2; int t = -1;
+    if (warp == 0) {                                      // producer thread: draw and publish
+      if (qu > 0 && !mbar_wait(qempty0 + 8 * qs, (qu - 1) & 1, limit, abort_flag)) { if (!*abort_flag) give_up(4); return false; }
+      t = atomicAdd(tile_queue, 1);
+      if ((long)t >= (long)full_end + n_half) t = -1;
+      qitem[qs] = t;
+      mbar_arrive(qfull0 + 8 * qs);
+    } else {                                              // consumers: one thread per warp reads
+      if (lane == 0) {
+        if (mbar_wait(qfull0 + 8 * qs, qu & 1, limit, abort_flag)) { t = qitem[qs]; mbar_arrive(qempty0 + 8 * qs); }
+        else if (!*abort_flag) give_up(5);
+      }
+      if (warp >= 2) t = __shfl_sync(0xffffffffu, t, 0);
+    }
+    return t >= 0 && item(t, tile, half);
   };
   // tile -> coordinates and contraction range
   auto decode = [&](int tile, int half, int& m0, int& n0, int& z, int& kb0, int& nkb) -> bool {
@@ -405,8 +434,6 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
     kb0 = kbeg / BK; nkb = (kend - kbeg + BK - 1) / BK;
     return true;
   };
-  // a wait gave up: record which role, and tell the other roles of this CTA to stop
-  auto give_up = [&](int code) { atomicExch(ep.status, code); *abort_flag = 1; __threadfence_block(); };
 
   uint32_t issued = 0;          // producer thread: stages whose copies it has started
   if (warp == 0) {
@@ -653,6 +680,14 @@ inline void tc_init(Ctx* ctx) {
   if (const char* e = getenv("GONEURON_CUDA_TC_BN")) ctx->tc_force_bn = atoi(e);
   if (const char* e = getenv("GONEURON_CUDA_TC_KSLICE")) ctx->tc_kslice = atoi(e);
   if (const char* e = getenv("GONEURON_CUDA_TC_TAIL_SPLIT")) ctx->tc_tail_split = atoi(e) != 0;
+  if (const char* e = getenv("GONEURON_CUDA_TC_TILE_QUEUE")) ctx->tc_tile_queue = atoi(e) != 0;
+  if (!ctx->tc_queue_pool) {
+    // (cleared on the legacy stream, which the context's non-blocking stream does not wait for: hence the device-wide wait)
+    if (cudaMalloc(&ctx->tc_queue_pool, TC_QUEUE_POOL * sizeof(int)) != cudaSuccess || cudaMemset(ctx->tc_queue_pool, 0, TC_QUEUE_POOL * sizeof(int)) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess) {
+      cudaGetLastError(); ctx->tc_queue_pool = nullptr; ctx->tc_tile_queue = false;
+    }
+  }
 }
 
 // fp32 plane, 32 columns (128 bytes, 128-byte swizzle) x box_rows per copy
@@ -712,6 +747,13 @@ inline long tc_tail_halves(Ctx* ctx, long total_tiles, int bn, int flags) {
   const long left = total_tiles % persist_sms(ctx);
   return 2 * left <= persist_sms(ctx) ? left : 0;
 }
+// A zeroed counter for one launch's tile queue, from a pool that is cleared when it has been used up (in stream order, so
+// every earlier launch has finished with its counter by then).
+inline int tc_next_queue(Ctx* ctx, int** out) {
+  if (!ctx->tc_queue_pool) return fail(GN_ERR_CUDA, "tile-queue pool missing");
+  if (ctx->tc_queue_used >= TC_QUEUE_POOL) { GN_CUDA(cudaMemsetAsync(ctx->tc_queue_pool, 0, TC_QUEUE_POOL * sizeof(int), ctx->stream)); ctx->tc_queue_used = 0; }
+  *out = ctx->tc_queue_pool + ctx->tc_queue_used++; return GN_OK;
+}
 template <int BN>
 inline int tc_launch_persist(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, const TcParams& ep) {
   CUtensorMap mA0, mA1, mB0, mB1;
@@ -724,8 +766,10 @@ inline int tc_launch_persist(Ctx* ctx, const BfPlanes& A, const BfPlanes& B, con
   const unsigned grid = (unsigned)std::min<long>(total, persist_sms(ctx));
   const long left = tc_tail_halves(ctx, total, BN, ep.flags);
   const int full_end = (int)(total - left), n_half = (int)(2 * left);
+  int* queue = nullptr;
+  if (ctx->tc_tile_queue && total > grid) GN_TRY(tc_next_queue(ctx, &queue));
   ProfScope prof(ctx);
-  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN>), grid, TC_THREADS, (TcCfg<BN>::SMEM_BYTES), mA0, mA1, mB0, mB1, ep, tiles_m, tiles_n, (int)total, full_end, n_half);
+  GN_LAUNCH(ctx, (gemm_tc_persist_kernel<BN>), grid, TC_THREADS, (TcCfg<BN>::SMEM_BYTES), mA0, mA1, mB0, mB1, ep, tiles_m, tiles_n, (int)total, full_end, n_half, queue);
   return check_launch("gemm_tc_persist");
 }
 // Output tile width for a problem: 64 for narrow outputs; 256 (three quarters of the shared-memory traffic per MMA

@@ -1146,6 +1146,7 @@ static int make_ctx(int device, int rank, int world, const unsigned char* id, gn
       if (c->c.comm && c->c.nccl) c->c.nccl->CommDestroy(c->c.comm);
       if (c->c.comm_stream) cudaStreamDestroy(c->c.comm_stream);
       if (c->c.d_status) cudaFree(c->c.d_status);
+      if (c->c.tc_queue_pool) cudaFree(c->c.tc_queue_pool);
       if (c->c.stream) cudaStreamDestroy(c->c.stream);
       delete c; } } guard{new gn_ctx()};
   gn_ctx* c = guard.c;
@@ -1203,6 +1204,7 @@ int gn_shutdown(gn_ctx* ctx) {
   ctx->c.ev_pool.clear();
   ctx->c.release_owned();                               // operand-plane scratch of the contraction and attention engines
   if (ctx->c.d_status) cudaFree(ctx->c.d_status);
+  if (ctx->c.tc_queue_pool) { cudaFree(ctx->c.tc_queue_pool); ctx->c.tc_queue_pool = nullptr; }
   if (ctx->c.t0) { cudaEventDestroy(ctx->c.t0); cudaEventDestroy(ctx->c.t1); ctx->c.t0 = ctx->c.t1 = nullptr; }
   if (ctx->c.stream) cudaStreamDestroy(ctx->c.stream);
   if (ctx->c.comm_stream) cudaStreamDestroy(ctx->c.comm_stream);
