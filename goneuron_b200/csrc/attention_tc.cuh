@@ -78,9 +78,9 @@ __device__ __forceinline__ void pack_planes16(const float (&v)[16], float s, uin
 }
 // The three MMAs of one 16-deep step of an fp32-accurate product, small terms first.  SS: both operands in shared memory.
 __device__ __forceinline__ void mma3_ss(uint32_t acc, uint64_t a_hi, uint64_t a_lo, uint64_t b_hi, uint64_t b_lo, uint32_t idesc, bool first) {
-  tc_mma_bf16(acc, a_lo, b_hi, idesc, first ? 0u : 1u);
-  tc_mma_bf16(acc, a_hi, b_lo, idesc, 1u);
-  tc_mma_bf16(acc, a_hi, b_hi, idesc, 1u);
+  tc_mma_f16(acc, a_lo, b_hi, idesc, first ? 0u : 1u);
+  tc_mma_f16(acc, a_hi, b_lo, idesc, 1u);
+  tc_mma_f16(acc, a_hi, b_hi, idesc, 1u);
 }
 // TS: the A operand (hi at tmem_a, lo 8 columns further) in tensor memory.
 __device__ __forceinline__ void mma3_ts(uint32_t acc, uint32_t tmem_a, uint64_t b_hi, uint64_t b_lo, uint32_t idesc, bool first) {

@@ -108,11 +108,7 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
-__device__ __forceinline__ void tc_mma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-  asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n}"
-               ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
                ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
@@ -125,21 +121,12 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
   constexpr uint64_t sbo = (8 * BK * 4) >> 4, layout = BK == 32 ? 2 : 4;
   return (uint64_t)((saddr >> 4) & 0x3FFF) | (1ull << 16) | (sbo << 32) | (1ull << 46) | (layout << 61);
 }
-// Instruction descriptor: D = f32 (bits 4-5 = 1), A = B = tf32 (bits 7-9, 10-12 = 2), both K-major,
-// N >> 3 at bits 17-22, M >> 4 at bits 24-28.
-__host__ __device__ constexpr uint32_t make_idesc(int M, int N) {
-  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-// The same for kind::f16 with A = B = bf16 (format code 1), D = f32.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
-}
-// kind::f16 with A = B = fp16 (format code 0), D = f32.
+// Instruction descriptor of kind::f16 with A = B = fp16 (format code 0 at bits 7-9 and 10-12), D = f32 (bits 4-5 = 1), both
+// operands K-major, N >> 3 at bits 17-22, M >> 4 at bits 24-28.
 __host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N) {
   return (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-__device__ __forceinline__ float tf32_round(float x) { uint32_t u; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(x)); return __uint_as_float(u); }
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -151,9 +138,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 
 
 // ------------------------------------------------------------------ splitting a value into operand planes
-__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(a, b); return *reinterpret_cast<uint32_t*>(&v);
-}
 // Power of two s that brings a row whose largest magnitude is mx into [2^14, 2^15) (fp16 overflows at 65504), and its
 // inverse.  s = 1 for a row of zeros (and for a row that holds an infinity or a NaN, which the products then carry on).
 __device__ __forceinline__ float row_scale(float mx, float* inv) {
@@ -483,13 +467,13 @@ gemm_tc_persist_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_c
             const uint64_t adv = (uint64_t)(2 * k);
             if constexpr (MERGED) {
               // small terms first, so that they meet the accumulator before the large term of this group is added
-              tc_mma_bf16(acc_main, a1 + adv, b0 + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
-              tc_mma_bf16(acc_main, a0 + adv, b1 + adv, idesc, 1u);
-              tc_mma_bf16(acc_main, a0 + adv, b0 + adv, idesc, 1u);
+              tc_mma_f16(acc_main, a1 + adv, b0 + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
+              tc_mma_f16(acc_main, a0 + adv, b1 + adv, idesc, 1u);
+              tc_mma_f16(acc_main, a0 + adv, b0 + adv, idesc, 1u);
             } else {
-              tc_mma_bf16(acc_cross, a1 + adv, b0 + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
-              tc_mma_bf16(acc_cross, a0 + adv, b1 + adv, idesc, 1u);
-              tc_mma_bf16(acc_main, a0 + adv, b0 + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
+              tc_mma_f16(acc_cross, a1 + adv, b0 + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
+              tc_mma_f16(acc_cross, a0 + adv, b1 + adv, idesc, 1u);
+              tc_mma_f16(acc_main, a0 + adv, b0 + adv, idesc, (i > 0 || k > 0) ? 1u : 0u);
             }
           }
           tc_commit(empty0 + 8 * s);
@@ -625,14 +609,6 @@ __global__ void __launch_bounds__(256) split2_cols_kernel(TcSrc s, int rows, int
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                     CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// Operand planes of the attention kernels, [nbatch][rows][ldp] each, K valid columns starting at column koff:
-// `hi` fp32 (tf32-rounded values); `lo` is a buffer of the same size holding two bf16 planes one after the other
-// (bf16 copy, then bf16 of the remainder).
-struct TcPlanes {
-  float* hi; float* lo; int rows, K, ldp, nbatch; int koff = 0;
-  __nv_bfloat16* xb() const { return reinterpret_cast<__nv_bfloat16*>(lo); }
-  __nv_bfloat16* lob() const { return xb() + (size_t)nbatch * rows * ldp; }
-};
 // Operand planes of the contraction engine: two fp16 planes [nbatch][rows][ldp] in one buffer, plane 1 after plane 0, and
 // the inverse scale of every plane row [nbatch][rows].
 struct BfPlanes {
@@ -690,18 +666,7 @@ inline void tc_init(Ctx* ctx) {
   }
 }
 
-// fp32 plane, 32 columns (128 bytes, 128-byte swizzle) x box_rows per copy
-inline int tc_make_map(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const float* base, int box_rows, int bk = 32) {
-  cuuint64_t dims[3] = {(cuuint64_t)p.K, (cuuint64_t)p.rows, (cuuint64_t)p.nbatch};
-  cuuint64_t strides[2] = {(cuuint64_t)p.ldp * 4, (cuuint64_t)p.rows * p.ldp * 4};
-  cuuint32_t box[3] = {(cuuint32_t)bk, (cuuint32_t)box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = ((PFN_encodeTiled)ctx->encode_tiled)(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)(base + p.koff), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                                    bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(GN_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d (rows %d K %d ld %d batch %d)", (int)r, p.rows, p.K, p.ldp, p.nbatch);
-  return GN_OK;
-}
-// bf16 plane [nbatch][rows][ldp], K valid columns from column koff, box_cols columns x box_rows per copy: 32 columns = 64
+// 16-bit plane [nbatch][rows][ldp], K valid columns from column koff, box_cols columns x box_rows per copy: 32 columns = 64
 // bytes with the 64-byte swizzle (contraction engine), 64 columns = 128 bytes with the 128-byte swizzle (attention tiles)
 inline int tc_make_map_bf16_raw(Ctx* ctx, CUtensorMap* map, const void* base_v, int K, int rows, int ldp, int nbatch, int koff, int box_rows, int box_cols,
                                 CUtensorMapDataType dtype = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16) {
@@ -715,9 +680,6 @@ inline int tc_make_map_bf16_raw(Ctx* ctx, CUtensorMap* map, const void* base_v, 
                                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(GN_ERR_CUDA, "cuTensorMapEncodeTiled (16-bit) failed with %d (rows %d K %d ld %d batch %d)", (int)r, rows, K, ldp, nbatch);
   return GN_OK;
-}
-inline int tc_make_map_bf16(Ctx* ctx, CUtensorMap* map, const TcPlanes& p, const __nv_bfloat16* base, int box_rows, int box_cols = TC_BK) {
-  return tc_make_map_bf16_raw(ctx, map, base, p.K, p.rows, p.ldp, p.nbatch, p.koff, box_rows, box_cols);
 }
 
 // Writes the planes and inverse row scales of an operand.  `mx` (only used by the transposing variant): nbatch * rows ints.
