@@ -268,7 +268,7 @@ __global__ void __launch_bounds__(1024) layernorm_pgrad_final_kernel(const float
 // and kept in registers between the reduction and the output pass.  Same arithmetic as the kernels above.
 // Optional second output of the row-in-registers kernels: the row as operand planes of the contraction engine (two fp16
 // planes with row stride n, the row's inverse scale, its 2-norm) -- the kernel holds the whole row, so the row maximum
-// costs two shuffles, and the separate split pass (a second read of the tensor) is not needed for the contraction that
+// and norm cost two warp reductions, and the separate split pass (a second read of the tensor) is not needed for the contraction that
 // consumes this output.
 struct RowPlaneOut { __half* p0 = nullptr; __half* p1 = nullptr; float* inv = nullptr; float* rownorm = nullptr; };
 template <int NV>
