@@ -228,3 +228,24 @@ def test_rope_known_answers(oracle):
     z = rng.standard_normal(10 * 4 * 32).astype(np.float32)
     back = oracle.rope(oracle.rope(z, 10, 4, 32), 10, 4, 32, conjugate=True)
     np.testing.assert_allclose(back, z, atol=1e-5, rtol=0)
+
+
+def test_embedding_known_answers(oracle):
+    """internal/layer/embedding_test.go:8-34: the output is the table's rows of the given ids; :36-82: a gradient of ones
+    reaches exactly the rows that were looked up, one per dimension, and every other row stays zero."""
+    V, d, T = 5, 3, 3
+    table = np.arange(V * d, dtype=np.float32) * np.float32(0.25) - np.float32(1.0)
+    ids = np.array([[0, 2, 4]], np.float32)
+    st = oracle.OracleState([D.Embedding(V, d, T)], D.MSE, table)
+    out = st.forward_batch(ids, precision=32).ravel()
+    assert np.array_equal(out, table.reshape(V, d)[[0, 2, 4]].ravel())
+    # MSE gradient 2 (p - y) / n with n = 9: targets 4.5 below the outputs make it exactly 1 everywhere
+    st.train_batch(ids, (out - np.float32(4.5)).reshape(1, -1), precision=32, step=False)
+    g = st.grads.reshape(V, d)
+    np.testing.assert_allclose(g[[0, 2, 4]], 1.0, atol=1e-6, rtol=0)
+    assert not g[[1, 3]].any()
+
+
+def test_gru_parameter_layout_size(oracle):
+    """internal/layer/gru_test.go:62-75: NewGRU(4, 8) holds 3*8*4 input weights, 2*8*8 recurrent weights and 3*8 biases."""
+    assert oracle.param_count([D.SequenceUnrollerGRU(4, 8, 5)])[0] == 3 * 8 * 4 + 2 * 8 * 8 + 3 * 8
