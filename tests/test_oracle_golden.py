@@ -249,3 +249,19 @@ def test_embedding_known_answers(oracle):
 def test_gru_parameter_layout_size(oracle):
     """internal/layer/gru_test.go:62-75: NewGRU(4, 8) holds 3*8*4 input weights, 2*8*8 recurrent weights and 3*8 biases."""
     assert oracle.param_count([D.SequenceUnrollerGRU(4, 8, 5)])[0] == 3 * 8 * 4 + 2 * 8 * 8 + 3 * 8
+
+
+def test_dropout_known_answers(oracle):
+    """internal/layer/dropout_test.go:8-34: with rate 0.5 and an input of 100 ones, between 30 and 70 outputs survive in
+    training mode (and a survivor is scaled by 1 / keep); :36-54: in inference mode the input passes through unchanged;
+    :101-108: the layer has no parameters."""
+    layers = [D.Dropout(0.5, 100)]
+    assert oracle.param_count(layers)[0] == 0
+    st = oracle.OracleState(layers, D.MSE, np.zeros(0, np.float32))
+    ones = np.ones((1, 100), np.float32)
+    out = st.forward_batch(ones, precision=32, training=True).ravel()
+    kept = out != 0
+    assert 30 <= int(kept.sum()) <= 70
+    assert np.array_equal(out[kept], np.full(int(kept.sum()), 2.0, np.float32))
+    ramp = np.arange(100, dtype=np.float32).reshape(1, -1)
+    assert np.array_equal(st.forward_batch(ramp, precision=32, training=False).ravel(), ramp.ravel())
