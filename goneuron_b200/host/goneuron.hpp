@@ -25,9 +25,18 @@ inline gn_layer_desc AvgPool2D(int inC, int k, int stride, int pad, int h, int w
 inline gn_layer_desc MaxPool2D(int inC, int k, int stride, int pad, int h, int w) { gn_layer_desc d{}; d.kind = GN_LAYER_MAXPOOL2D; d.in_size = inC; d.kernel = k; d.stride = stride; d.padding = pad; d.in_h = h; d.in_w = w; return d; }
 inline gn_layer_desc Flatten() { gn_layer_desc d{}; d.kind = GN_LAYER_FLATTEN; return d; }
 inline gn_layer_desc SequenceUnrollerLSTM(int in, int hidden, int T, bool returnSeq = false) { gn_layer_desc d{}; d.kind = GN_LAYER_LSTM_UNROLLED; d.in_size = in; d.out_size = hidden; d.seq_len = T; d.return_seq = returnSeq; return d; }
+// layer.NewSequenceUnroller(layer.NewGRU(in, hidden), T, returnSeq) -- unroller.go:57, gru.go:81
+inline gn_layer_desc SequenceUnrollerGRU(int in, int hidden, int T, bool returnSeq = false) { gn_layer_desc d{}; d.kind = GN_LAYER_GRU_UNROLLED; d.in_size = in; d.out_size = hidden; d.seq_len = T; d.return_seq = returnSeq; return d; }
 inline gn_layer_desc Embedding(int vocab, int dim, int T = 0) { gn_layer_desc d{}; d.kind = GN_LAYER_EMBEDDING; d.in_size = vocab; d.out_size = dim; d.seq_len = T; return d; }
 inline gn_layer_desc PositionalEncoding(int T, int dim) { gn_layer_desc d{}; d.kind = GN_LAYER_POSENC; d.seq_len = T; d.dim = dim; return d; }
 inline gn_layer_desc TransformerBlock(int dim, int heads, int T, int ff, bool causal) { gn_layer_desc d{}; d.kind = GN_LAYER_TRANSFORMER_BLOCK; d.dim = dim; d.heads = heads; d.seq_len = T; d.ff_dim = ff; d.causal = causal; return d; }
+// layer.NewTransformerBlockExt(dim, heads, T, ff, causal, actType, normType, useRoPE) -- transformer.go:899-957: ffAct is
+// GN_ACT_RELU (ActReLU), GN_ACT_GELU (ActGELU) or GN_ACT_SILU (ActSwiGLU); the descriptor carries them in activation / kernel / stride
+inline gn_layer_desc TransformerBlockExt(int dim, int heads, int T, int ff, bool causal, gn_activation ffAct, bool rmsNorm, bool useRoPE) {
+  gn_layer_desc d = TransformerBlock(dim, heads, T, ff, causal); d.activation = ffAct == GN_ACT_RELU ? 0 : ffAct; d.kernel = rmsNorm ? 1 : 0; d.stride = useRoPE ? 1 : 0; return d; }
+// layer.NewBatchNorm2D(C, eps, momentum, true) + SetInputDimensions(h, w) -- batchnorm2d.go:67-160
+inline gn_layer_desc BatchNorm2D(int numFeatures, int h, int w, float eps = 1e-5f, float momentum = 0.1f) {
+  gn_layer_desc d{}; d.kind = GN_LAYER_BATCHNORM2D; d.in_size = numFeatures; d.in_h = h; d.in_w = w; memcpy(&d.dim, &momentum, 4); memcpy(&d.reserved, &eps, 4); return d; }
 inline gn_layer_desc CLSPooling(int T, int dim) { gn_layer_desc d{}; d.kind = GN_LAYER_CLS_POOLING; d.seq_len = T; d.dim = dim; return d; }
 inline gn_layer_desc LayerNorm(int dim) { gn_layer_desc d{}; d.kind = GN_LAYER_LAYERNORM; d.dim = dim; return d; }
 

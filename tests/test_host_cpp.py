@@ -12,6 +12,9 @@ SRC = r'''
 #include "goneuron_b200/host/goneuron.hpp"
 int main() {
   using namespace goneuron;
+  // descriptor constructors of the newer layers
+  gn_layer_desc g = SequenceUnrollerGRU(4, 8, 5), b = TransformerBlockExt(64, 2, 16, 128, true, GN_ACT_SILU, true, true), n = BatchNorm2D(3, 8, 8);
+  if (g.kind != GN_LAYER_GRU_UNROLLED || b.activation != GN_ACT_SILU || b.kernel != 1 || b.stride != 1 || n.kind != GN_LAYER_BATCHNORM2D) return 4;
   try { Device dev(0); Sequential m(dev, {Dense(4, 3, GN_ACT_RELU), Dense(3, 2, GN_ACT_SOFTMAX)}); Adam opt(1e-3f); m.Compile(&opt, GN_LOSS_CROSS_ENTROPY);
         std::printf("params %lld\n", (long long)m.NumParams()); }
   catch (const std::exception& e) { std::printf("error: %s\n", e.what()); return 3; }
