@@ -354,7 +354,7 @@ def main():
                 "frac_of_scheme_ceiling": achieved / (pk["bf16_tflops_sustained"] / 3.0),
                 "split_passes": {"bytes_per_step": pf["split_bytes"], "fp32_operand_bytes_per_step": operand_elems_bytes,
                                  "operand_traffic_ratio": (pf["split_bytes"] + operand_elems_bytes) / operand_elems_bytes if operand_elems_bytes else None,
-                                 "note": "every fp32 operand element is read once (4 B) and written as two fp16 planes (4 B) by the split pass, then read once (4 B) by the contraction: 12 B against 4 B algorithmic"},
+                                 "note": "bytes moved by the separate split passes that are left (4 B read + 4 B written per element they handle; weight matrices once per update); operands whose planes are written by their producer -- the LayerNorm kernels, the plane-writing contraction epilogues -- do not appear here"},
                 "peak_source": pk["source"] + " cuBLAS bf16 (sustained); an fp32-accurate product here is three fp16 MMAs (fp16 and bf16 run at the same rate), so its arithmetic ceiling is 1/3 of this"}
 
     side, tf32 = None, None
